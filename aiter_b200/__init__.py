@@ -1,0 +1,39 @@
+"""aiter_b200 - the quantised-GEMM hot path of the aiter operator library, rebuilt for B200 (sm_100a).
+
+Same operator names and argument meaning as the reference package; underneath, hand-written
+tcgen05 / TMA kernels behind a C ABI (include/aiter_b200.h).  Importing this package loads the
+CUDA library and fails loudly when it has not been built.
+"""
+import logging
+import os
+
+logger = logging.getLogger("aiter")
+if not logger.handlers:
+    _h = logging.StreamHandler()
+    _h.setFormatter(logging.Formatter("[aiter] %(levelname)s: %(message)s"))
+    logger.addHandler(_h)
+    logger.setLevel(getattr(logging, os.getenv("AITER_LOG_LEVEL", "WARNING").upper(), logging.WARNING))
+    logger.propagate = False
+
+from . import dtypes, fp4_utils  # noqa: E402
+from ._ffi import device_status, get_padded_m, heuristic_name, kernel_list, launch_count  # noqa: E402,F401
+from .dtypes import MX_DEFAULT_ROUND_MODE, MxDtype, MxScaleRoundMode, QuantType  # noqa: E402,F401
+from .gemm_op_a4w4 import (  # noqa: E402,F401
+    gemm_a4w4,
+    gemm_a4w4_asm,
+    gemm_a4w4_blockscale,
+    gemm_a4w4_blockscale_tune,
+    gemm_mxfp4_asm,
+)
+from .gemm_op_a8w4 import gemm_a8w4_mxfp8  # noqa: E402,F401
+from .gemm_op_a8w8 import gemm_a8w8_mxfp8  # noqa: E402,F401
+from .gemm_op_a16w16 import gemm_a16w16_asm, gemm_a16w16_opus, opus_gemm, opus_gemm_a16w16_tune  # noqa: E402,F401
+from .quant import get_torch_quant, per_1x32_f4_quant, per_1x32_f8_scale_f8_quant  # noqa: E402,F401
+from .shuffle import (  # noqa: E402,F401
+    shuffle_mxfp8fp4_a,
+    shuffle_mxfp8fp4_b,
+    shuffle_mxfp8fp4_scale,
+    shuffle_scale,
+    shuffle_weight,
+)
+from .tuned_gemm import TunedGemm, gemm_a16w16, tgemm  # noqa: E402,F401

@@ -1,0 +1,145 @@
+"""ctypes binding of libaiter_b200.so.
+
+Mirrors the reference's ctypes caller (aiter/jit/core.py:1457-1553): tensors go in as
+`aiter_tensor_t*` (NULL for None), ints as C ints (-1 for None), strings as `const char*`
+(NULL for None), bools as ints, floats as floats, and the current CUDA stream is appended as
+the trailing `void*`.  A non-zero return raises RuntimeError("<name> failed: <message>").
+There is no fallback: if the library is missing the import of this module fails.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from .dtypes import aiter_dtype_id
+
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc", "libaiter_b200.so")
+
+
+class aiter_tensor_t(ctypes.Structure):
+    _fields_ = [
+        ("ptr", ctypes.c_void_p),
+        ("numel_", ctypes.c_size_t),
+        ("ndim", ctypes.c_int),
+        ("shape", ctypes.c_int64 * 8),
+        ("strides", ctypes.c_int64 * 8),
+        ("dtype_", ctypes.c_int),
+        ("device_id", ctypes.c_int),
+    ]
+
+
+assert ctypes.sizeof(aiter_tensor_t) == 160, "aiter_tensor_t layout drifted from include/aiter_b200.h"
+
+
+def torch_to_aiter(t: torch.Tensor) -> aiter_tensor_t:
+    shape, strides = t.shape, t.stride()
+    ndim = len(shape)
+    assert ndim <= 8, f"aiter_tensor_t supports at most 8 dims, got {ndim}"
+    at = aiter_tensor_t()
+    at.ptr = t.data_ptr()
+    at.numel_ = t.numel()
+    at.ndim = ndim
+    at.shape[:ndim] = shape
+    at.strides[:ndim] = strides
+    at.dtype_ = aiter_dtype_id(t.dtype)
+    idx = t.device.index
+    at.device_id = -1 if (t.device.type != "cuda" or idx is None) else idx
+    return at
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m aiter_b200.build` (needs nvcc). "
+            "aiter_b200 has no CPU or PyTorch fallback."
+        )
+    return ctypes.CDLL(LIB_PATH)
+
+
+_lib = _load()
+_lib.aiter_get_last_error.restype = ctypes.c_char_p
+_lib.aiter_b200_kernel_list.restype = ctypes.c_char_p
+_lib.aiter_b200_heuristic_name.restype = ctypes.c_char_p
+_lib.aiter_b200_launch_count.restype = ctypes.c_ulonglong
+assert _lib.aiter_ctypes_abi_version() == 2
+
+T, I, S, F = "tensor", "int", "str", "float"
+# name -> argument kinds (the stream is appended automatically)
+SIGNATURES = {
+    "gemm_a4w4_asm": (T, T, T, T, T, S, T, F, F, I, I),
+    "gemm_a4w4_blockscale": (T, T, T, T, T, I, S),
+    "gemm_a4w4_blockscale_tune": (T, T, T, T, T, I, I),
+    "mxfp8_mxfp8_gemm_asm": (T, T, T, T, T, S, I),
+    "mxfp8_mxfp4_gemm_asm": (T, T, T, T, T, S, I),
+    "mxfp4_gemm_asm": (T, T, T, T, T, T, S, I),
+    "gemm_a16w16_asm": (T, T, T, T, T, I, S, I),
+    "opus_gemm_a16w16_tune": (T, T, T, T, I, I),
+    "opus_gemm": (T, T, T, T, T, T, T),
+}
+EXPORTS = sorted(
+    list(SIGNATURES)
+    + ["getPaddedM", "aiter_ctypes_abi_version", "aiter_get_last_error", "aiter_clear_last_error",
+       "opus_gemm_workspace_init", "aiter_b200_device_status", "aiter_b200_kernel_list",
+       "aiter_b200_heuristic_name", "aiter_b200_launch_count"]
+)
+
+
+def _convert(kind, value, keep):
+    if kind == T:
+        if value is None:
+            return None
+        at = torch_to_aiter(value)
+        keep.append(at)
+        return ctypes.byref(at)
+    if kind == I:
+        return ctypes.c_int(-1 if value is None else int(value))
+    if kind == F:
+        return ctypes.c_float(float(value))
+    if kind == S:
+        return None if value is None else ctypes.c_char_p(str(value).encode())
+    raise TypeError(kind)
+
+
+def call(name: str, *args):
+    """Call an entry point on the current CUDA stream of the first tensor's device."""
+    kinds = SIGNATURES[name]
+    assert len(args) == len(kinds), f"{name} takes {len(kinds)} arguments, got {len(args)}"
+    keep = []
+    cargs = [_convert(k, a, keep) for k, a in zip(kinds, args)]
+    dev = next((a.device for a in args if isinstance(a, torch.Tensor) and a.is_cuda), None)
+    stream = torch.cuda.current_stream(dev).cuda_stream if dev is not None else 0
+    rc = getattr(_lib, name)(*cargs, ctypes.c_void_p(stream))
+    if rc != 0:
+        msg = _lib.aiter_get_last_error()
+        raise RuntimeError(f"{name} failed: {msg.decode() if msg else 'unknown error'}")
+
+
+def get_padded_m(M: int, N: int, K: int, gl: int) -> int:
+    return int(_lib.getPaddedM(int(M), int(N), int(K), int(gl)))
+
+
+def device_status(device: int = 0):
+    """(code, block, split, iteration) of the last expired in-kernel wait on `device`; zeros = healthy.
+    Synchronises the device and clears the record."""
+    words = (ctypes.c_uint * 4)()
+    rc = _lib.aiter_b200_device_status(int(device), words)
+    if rc != 0:
+        msg = _lib.aiter_get_last_error()
+        raise RuntimeError(f"aiter_b200_device_status failed: {msg.decode() if msg else ''}")
+    return tuple(int(w) for w in words)
+
+
+def kernel_list() -> str:
+    return _lib.aiter_b200_kernel_list().decode()
+
+
+def heuristic_name(kind: int, M: int, N: int, K: int):
+    l2 = ctypes.c_int(0)
+    name = _lib.aiter_b200_heuristic_name(int(kind), int(M), int(N), int(K), ctypes.byref(l2))
+    return name.decode(), int(l2.value)
+
+
+def launch_count() -> int:
+    return int(_lib.aiter_b200_launch_count())

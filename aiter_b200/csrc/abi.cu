@@ -1,0 +1,390 @@
+// extern "C" entry points: argument checking, aiter_tensor_t -> GemmProblem, error bridge.
+#include "../../include/aiter_b200.h"
+#include "gemm_kernel.cuh"
+#include "launch.h"
+
+#include <climits>
+#include <string>
+
+using namespace b200;
+
+static thread_local std::string g_last_error;
+static thread_local std::string g_heuristic_name;
+
+template <typename Fn>
+static int safe_call(Fn&& fn)
+{
+    g_last_error.clear();
+    try
+    {
+        fn();
+        return 0;
+    }
+    catch(const std::exception& e)
+    {
+        g_last_error = e.what();
+    }
+    catch(...)
+    {
+        g_last_error = "unknown C++ exception";
+    }
+    return -1;
+}
+
+static const char* dtype_name(int d)
+{
+    static const char* names[] = {"fp8", "fp8_e8m0", "fp16", "bf16", "fp32", "i4x2", "fp4x2",
+                                  "u32", "i32", "i16", "i8", "u8", "i64", "u64"};
+    return (d >= 0 && d < 14) ? names[d] : "?";
+}
+
+static bool is_byte_dtype(int d)
+{
+    return d == AITER_DTYPE_fp8 || d == AITER_DTYPE_fp8_e8m0 || d == AITER_DTYPE_fp4x2 || d == AITER_DTYPE_u8 ||
+           d == AITER_DTYPE_i8 || d == AITER_DTYPE_i4x2;
+}
+
+static void require_tensor(const aiter_tensor_t* t, const char* fn, const char* name, int ndim)
+{
+    B200_CHECK(t != nullptr, fn, ": ", name, " is required");
+    B200_CHECK(t->ndim == ndim, fn, ": ", name, " must be ", ndim, "-D (got ", t->ndim, "-D)");
+    B200_CHECK(t->device_id >= 0, fn, ": ", name, " must live on a GPU");
+    B200_CHECK(t->ptr != nullptr || t->numel_ == 0, fn, ": ", name, " has a null data pointer");
+}
+
+static void require_rows_contiguous(const aiter_tensor_t* t, const char* fn, const char* name)
+{
+    B200_CHECK(t->strides[t->ndim - 1] == 1 || t->shape[t->ndim - 1] == 1, fn, ": ", name,
+               " must be contiguous along its last dimension");
+}
+
+static void require_dense(const aiter_tensor_t* t, const char* fn, const char* name)
+{
+    int64_t expect = 1;
+    for(int d = t->ndim - 1; d >= 0; --d)
+    {
+        B200_CHECK(t->shape[d] == 1 || t->strides[d] == expect, fn, ": ", name, " must be contiguous");
+        expect *= t->shape[d];
+    }
+}
+
+static ScaleOperand scale_operand(const aiter_tensor_t* s, int wire, const char* fn, const char* name)
+{
+    require_tensor(s, fn, name, 2);
+    B200_CHECK(is_byte_dtype(s->dtype_), fn, ": ", name, " must be e8m0 / uint8 (got ", dtype_name(s->dtype_), ")");
+    require_dense(s, fn, name);
+    ScaleOperand so;
+    so.ptr         = s->ptr;
+    so.wire        = wire;
+    so.padded_rows = s->shape[0];
+    so.padded_cols = s->shape[1];
+    return so;
+}
+
+static void set_out(GemmProblem& p, const aiter_tensor_t* out, const char* fn, long long M, long long N)
+{
+    require_tensor(out, fn, "out", 2);
+    B200_CHECK(out->dtype_ == AITER_DTYPE_bf16, fn, " only support BFloat16 output now!");
+    B200_CHECK(out->shape[0] >= M && out->shape[1] == N, fn, ": out must be [>=", M, ", ", N, "] (got [", out->shape[0],
+               ", ", out->shape[1], "])");
+    require_rows_contiguous(out, fn, "out");
+    p.out = out->ptr;
+    p.ldo = out->strides[0];
+}
+
+static void apply_config(GemmProblem& p, const char* kernelName, int log2_splitk, const char* fn)
+{
+    if(kernelName != nullptr && kernelName[0] != 0)
+        B200_CHECK(parse_config_name(kernelName, p.cfg), fn, ": not find kernel ", kernelName);
+    p.cfg.log2_splitk = log2_splitk;
+}
+
+// ------------------------------------------------------------------------------------------- MXFP4
+static void run_mxfp4(const char* fn, aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* A_scale,
+                      aiter_tensor_t* B_scale, aiter_tensor_t* out, aiter_tensor_t* bias, float alpha, float beta,
+                      int a_mode, int b_mode, int wire, const KernelConfig& cfg, void* stream)
+{
+    require_tensor(A, fn, "A", 2);
+    require_tensor(B, fn, "B", 2);
+    B200_CHECK(A->dtype_ == AITER_DTYPE_fp4x2 || A->dtype_ == AITER_DTYPE_u8, fn, " Unsupported input_type:",
+               dtype_name(A->dtype_));
+    B200_CHECK(B->dtype_ == AITER_DTYPE_fp4x2 || B->dtype_ == AITER_DTYPE_u8, fn, " Unsupported input_type:",
+               dtype_name(B->dtype_));
+    const long long M = A->shape[0], N = B->shape[0], Kb = A->shape[1];
+    B200_CHECK(B->shape[1] == Kb, fn, ": A and B disagree on K (", Kb * 2, " vs ", B->shape[1] * 2, ")");
+    B200_CHECK(Kb % 16 == 0, fn, ": K must be a multiple of 32");
+    require_rows_contiguous(A, fn, "A");
+    require_dense(B, fn, "B");
+    GemmProblem p;
+    p.kind = PK_MXFP4;
+    p.M = M; p.N = N; p.K = Kb * 2;
+    p.act = Operand{A->ptr, M, Kb, A->strides[0], a_mode};
+    if(a_mode != OPM_ROWMAJOR)
+        require_dense(A, fn, "A");
+    p.wgt    = Operand{B->ptr, N, Kb, Kb, b_mode};
+    p.act_sf = scale_operand(A_scale, wire, fn, "A_scale");
+    p.wgt_sf = scale_operand(B_scale, wire, fn, "B_scale");
+    set_out(p, out, fn, M, N);
+    if(bias != nullptr)
+    {
+        B200_CHECK(bias->dtype_ == AITER_DTYPE_fp32 && static_cast<long long>(bias->numel_) == N, fn,
+                   ": bias must be fp32 with N elements");
+        p.bias = bias->ptr;
+    }
+    p.alpha  = alpha;
+    p.beta   = beta;
+    p.device = A->device_id;
+    p.stream = static_cast<cudaStream_t>(stream);
+    p.cfg    = cfg;
+    launch_gemm(p);
+}
+
+extern "C" int gemm_a4w4_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* A_scale, aiter_tensor_t* B_scale,
+                             aiter_tensor_t* out, const char* kernelName, aiter_tensor_t* bias, float alpha, float beta,
+                             int bpreshuffle, int log2_k_split, void* stream)
+{
+    return safe_call([&] {
+        GemmProblem tmp;
+        apply_config(tmp, kernelName, log2_k_split, "gemm_a4w4_asm");
+        run_mxfp4("gemm_a4w4_asm", A, B, A_scale, B_scale, out, bias, alpha, beta, OPM_ROWMAJOR,
+                  bpreshuffle ? OPM_TILE16 : OPM_ROWMAJOR, SFW_E8M0_SHUFFLE, tmp.cfg, stream);
+    });
+}
+
+extern "C" int gemm_a4w4_blockscale(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
+                                    aiter_tensor_t* w_scale, aiter_tensor_t* Out, int splitK, const char* kernelName,
+                                    void* stream)
+{
+    return safe_call([&] {
+        GemmProblem tmp;
+        apply_config(tmp, kernelName, splitK, "gemm_a4w4_blockscale");
+        run_mxfp4("gemm_a4w4_blockscale", XQ, WQ, x_scale, w_scale, Out, nullptr, 1.f, 0.f, OPM_ROWMAJOR, OPM_TILE16,
+                  SFW_E8M0_SHUFFLE, tmp.cfg, stream);
+    });
+}
+
+extern "C" int gemm_a4w4_blockscale_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
+                                         aiter_tensor_t* w_scale, aiter_tensor_t* Out, int kernelId, int splitK,
+                                         void* stream)
+{
+    return safe_call([&] {
+        KernelConfig cfg;
+        B200_CHECK(config_from_id(kernelId, cfg), "gemm_a4w4_blockscale_tune: Kernel id ", kernelId, " not found");
+        cfg.log2_splitk = splitK;
+        run_mxfp4("gemm_a4w4_blockscale_tune", XQ, WQ, x_scale, w_scale, Out, nullptr, 1.f, 0.f, OPM_ROWMAJOR, OPM_TILE16,
+                  SFW_E8M0_SHUFFLE, cfg, stream);
+    });
+}
+
+extern "C" int mxfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* ScaleA, aiter_tensor_t* ScaleB,
+                              aiter_tensor_t* out, aiter_tensor_t* out_scale, const char* kernelName, int a_preshuffle,
+                              void* stream)
+{
+    return safe_call([&] {
+        B200_CHECK(out_scale == nullptr, "mxfp4_gemm_asm: only the bf16 output form is built (out_scale must be absent)");
+        B200_CHECK(a_preshuffle == 0 || a_preshuffle == 1, "mxfp4_gemm_asm a_preshuffle must be 0 or 1");
+        GemmProblem tmp;
+        apply_config(tmp, kernelName, -1, "mxfp4_gemm_asm");
+        B200_CHECK(A != nullptr && A->ndim == 2 && (A->shape[1] * 2) % 256 == 0, "mxfp4_gemm_asm K must be divisible by 256");
+        run_mxfp4("mxfp4_gemm_asm", A, B, ScaleA, ScaleB, out, nullptr, 1.f, 0.f, a_preshuffle ? OPM_A2X128 : OPM_ROWMAJOR,
+                  OPM_TILE16, SFW_G1250, tmp.cfg, stream);
+    });
+}
+
+// ------------------------------------------------------------------------------------------- MXFP8
+static void run_mxfp8(const char* fn, int b_is_fp4, aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* ScaleA,
+                      aiter_tensor_t* ScaleB, aiter_tensor_t* out, const char* kernelName, int a_preshuffle, void* stream)
+{
+    require_tensor(out, fn, "out", 2);
+    B200_CHECK(out->dtype_ == AITER_DTYPE_bf16, fn, " only supports BFloat16 output");
+    B200_CHECK(a_preshuffle == 0 || a_preshuffle == 1, fn, " a_preshuffle must be 0 or 1");
+    require_tensor(A, fn, "A", 2);
+    require_tensor(B, fn, "B", 2);
+    const long long M = A->shape[0], N = B->shape[0], K = A->shape[1];
+    B200_CHECK(K % 128 == 0, fn, " K must be divisible by 128 (got K=", K, ")");
+    B200_CHECK(is_byte_dtype(A->dtype_) && is_byte_dtype(B->dtype_), fn, ": A and B must be 1-byte tensors");
+    B200_CHECK(B->shape[1] == (b_is_fp4 ? K / 2 : K), fn, ": B must be [N, ", (b_is_fp4 ? "K/2" : "K"), "]");
+    require_dense(A, fn, "A");
+    require_dense(B, fn, "B");
+    GemmProblem p;
+    p.kind = b_is_fp4 ? PK_MXF8F4 : PK_MXFP8;
+    p.M = M; p.N = N; p.K = K;
+    p.act    = Operand{A->ptr, M, K, K, a_preshuffle ? OPM_A2X128 : OPM_ROWMAJOR};
+    p.wgt    = Operand{B->ptr, N, b_is_fp4 ? K / 2 : K, b_is_fp4 ? K / 2 : K, OPM_TILE16};
+    p.act_sf = scale_operand(ScaleA, SFW_G1250, fn, "ScaleA");
+    p.wgt_sf = scale_operand(ScaleB, SFW_G1250, fn, "ScaleB");
+    set_out(p, out, fn, M, N);
+    p.device = A->device_id;
+    p.stream = static_cast<cudaStream_t>(stream);
+    apply_config(p, kernelName, -1, fn);
+    launch_gemm(p);
+}
+
+extern "C" int mxfp8_mxfp8_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* ScaleA, aiter_tensor_t* ScaleB,
+                                    aiter_tensor_t* out, const char* kernelName, int a_preshuffle, void* stream)
+{
+    return safe_call([&] { run_mxfp8("mxfp8_mxfp8_gemm_asm", 0, A, B, ScaleA, ScaleB, out, kernelName, a_preshuffle, stream); });
+}
+
+extern "C" int mxfp8_mxfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* ScaleA, aiter_tensor_t* ScaleB,
+                                    aiter_tensor_t* out, const char* kernelName, int a_preshuffle, void* stream)
+{
+    return safe_call([&] { run_mxfp8("mxfp8_mxfp4_gemm_asm", 1, A, B, ScaleA, ScaleB, out, kernelName, a_preshuffle, stream); });
+}
+
+// ------------------------------------------------------------------------------------------- bf16
+static void run_bf16(const char* fn, const aiter_tensor_t* A, const aiter_tensor_t* B, const aiter_tensor_t* out,
+                     const aiter_tensor_t* bias, int bpreshuffle, const KernelConfig& cfg, int batch_index, void* stream)
+{
+    // A [.., M, K], B [.., N, K], out [.., M, N]; the leading batch dimension (3-D form) is walked by the caller
+    const int a0 = A->ndim - 2;
+    B200_CHECK(A->dtype_ == AITER_DTYPE_bf16 && B->dtype_ == AITER_DTYPE_bf16, fn, ": only bf16 inputs are supported (got ",
+               dtype_name(A->dtype_), ", ", dtype_name(B->dtype_), ")");
+    B200_CHECK(out->dtype_ == AITER_DTYPE_bf16, fn, ": only bf16 output is supported (got ", dtype_name(out->dtype_), ")");
+    const long long M = A->shape[a0], K = A->shape[a0 + 1], N = B->shape[a0];
+    B200_CHECK(B->shape[a0 + 1] == K, fn, ": A and B disagree on K");
+    B200_CHECK(out->shape[a0] == M && out->shape[a0 + 1] == N, fn, ": out must be [M, N]");
+    B200_CHECK(A->strides[a0 + 1] == 1 && B->strides[a0 + 1] == 1 && out->strides[a0 + 1] == 1, fn,
+               ": tensors must be contiguous along their last dimension");
+    B200_CHECK(K % 8 == 0, fn, ": K must be a multiple of 8 for bf16 (16-byte rows)");
+    GemmProblem p;
+    p.kind = PK_BF16;
+    p.M = M; p.N = N; p.K = K;
+    const char* a_ptr = static_cast<const char*>(A->ptr) + (a0 ? batch_index * A->strides[0] * 2 : 0);
+    const char* b_ptr = static_cast<const char*>(B->ptr) + (a0 ? batch_index * B->strides[0] * 2 : 0);
+    char* o_ptr       = static_cast<char*>(out->ptr) + (a0 ? batch_index * out->strides[0] * 2 : 0);
+    p.act = Operand{a_ptr, M, K * 2, A->strides[a0] * 2, OPM_ROWMAJOR};
+    if(bpreshuffle)
+    {
+        B200_CHECK(B->strides[a0] == K, fn, ": a shuffled weight must be contiguous");
+        p.wgt = Operand{b_ptr, N, K * 2, K * 2, OPM_TILE16};
+    }
+    else
+        p.wgt = Operand{b_ptr, N, K * 2, B->strides[a0] * 2, OPM_ROWMAJOR};
+    p.out = o_ptr;
+    p.ldo = out->strides[a0];
+    if(bias != nullptr)
+    {
+        B200_CHECK(bias->dtype_ == AITER_DTYPE_bf16 || bias->dtype_ == AITER_DTYPE_fp32, fn, ": bias must be bf16 or fp32");
+        B200_CHECK(static_cast<long long>(bias->numel_) == N, fn, ": bias must have N elements");
+        p.bias         = bias->ptr;
+        p.bias_is_bf16 = (bias->dtype_ == AITER_DTYPE_bf16);
+    }
+    p.alpha  = 1.f;
+    p.beta   = 1.f;
+    p.device = A->device_id;
+    p.stream = static_cast<cudaStream_t>(stream);
+    p.cfg    = cfg;
+    launch_gemm(p);
+}
+
+extern "C" int gemm_a16w16_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* out, aiter_tensor_t* semaphore,
+                               aiter_tensor_t* bias, int splitK, const char* kernelName, int bpreshuffle, void* stream)
+{
+    (void)semaphore; // the split-K tickets live in the library's own per-stream workspace
+    return safe_call([&] {
+        require_tensor(A, "gemm_a16w16_asm", "A", 2);
+        require_tensor(B, "gemm_a16w16_asm", "B", 2);
+        require_tensor(out, "gemm_a16w16_asm", "out", 2);
+        GemmProblem tmp;
+        // python passes None as -1; the reference's splitK here is a split count, 0/1 = none
+        int l2 = -1;
+        if(splitK >= 0)
+        {
+            l2 = 0;
+            while((2 << l2) <= splitK)
+                ++l2;
+        }
+        apply_config(tmp, kernelName, l2, "gemm_a16w16_asm");
+        run_bf16("gemm_a16w16_asm", A, B, out, bias, bpreshuffle, tmp.cfg, 0, stream);
+    });
+}
+
+extern "C" int opus_gemm_a16w16_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* Y, aiter_tensor_t* bias,
+                                     int kernelId, int splitK, void* stream)
+{
+    return safe_call([&] {
+        require_tensor(XQ, "opus_gemm_a16w16_tune", "XQ", 3);
+        require_tensor(WQ, "opus_gemm_a16w16_tune", "WQ", 3);
+        require_tensor(Y, "opus_gemm_a16w16_tune", "Y", 3);
+        KernelConfig cfg;
+        B200_CHECK(config_from_id(kernelId, cfg), "opus_gemm_a16w16_tune: Kernel id ", kernelId, " not found in a16w16 tune lookup table");
+        cfg.log2_splitk = splitK;
+        const long long batch = XQ->shape[0];
+        B200_CHECK(WQ->shape[0] == batch && Y->shape[0] == batch, "opus_gemm_a16w16_tune: batch mismatch");
+        for(long long b = 0; b < batch; ++b)
+            run_bf16("opus_gemm_a16w16_tune", XQ, WQ, Y, bias, 0, cfg, static_cast<int>(b), stream);
+    });
+}
+
+extern "C" int opus_gemm(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* Y, aiter_tensor_t* group_layout,
+                         aiter_tensor_t* x_scale, aiter_tensor_t* w_scale, aiter_tensor_t* bias, void* stream)
+{
+    return safe_call([&] {
+        B200_CHECK(group_layout == nullptr && x_scale == nullptr && w_scale == nullptr,
+                   "opus_gemm: only the bf16 no-scale form is built");
+        require_tensor(XQ, "opus_gemm", "XQ", 3);
+        require_tensor(WQ, "opus_gemm", "WQ", 3);
+        require_tensor(Y, "opus_gemm", "Y", 3);
+        const long long batch = XQ->shape[0];
+        B200_CHECK(WQ->shape[0] == batch && Y->shape[0] == batch, "opus_gemm: batch mismatch");
+        KernelConfig cfg;
+        for(long long b = 0; b < batch; ++b)
+            run_bf16("opus_gemm", XQ, WQ, Y, bias, 0, cfg, static_cast<int>(b), stream);
+    });
+}
+
+extern "C" int opus_gemm_workspace_init(void) { return 0; }
+
+// ------------------------------------------------------------------------------------------- misc
+static constexpr int next_pow2(unsigned int v)
+{
+    if(v <= 1)
+        return 1;
+    return 1 << (CHAR_BIT * sizeof(v) - __builtin_clz(v - 1));
+}
+
+extern "C" int getPaddedM(int M, int N, int K, int gl)
+{
+    (void)K;
+    int padded = M;
+    if(gl == 0)
+    {
+        const int g = M <= 256 ? 16 : M <= 1024 ? 32 : M <= 4096 ? 64 : 128;
+        padded      = (M + g - 1) / g * g;
+    }
+    else if(gl == 1)
+        padded = (M > 8192 && N > 4096) ? 8192 : next_pow2(static_cast<unsigned int>(M));
+    return padded;
+}
+
+extern "C" int aiter_ctypes_abi_version(void) { return 2; }
+extern "C" const char* aiter_get_last_error(void) { return g_last_error.empty() ? nullptr : g_last_error.c_str(); }
+extern "C" void aiter_clear_last_error(void) { g_last_error.clear(); }
+
+extern "C" int aiter_b200_device_status(int device, unsigned int out_words[4])
+{
+    return safe_call([&] { read_device_status(device, out_words); });
+}
+extern "C" const char* aiter_b200_kernel_list(void) { return kernel_menu_text(); }
+extern "C" const char* aiter_b200_heuristic_name(int kind, int M, int N, int K, int* log2_splitk)
+{
+    KernelConfig cfg;
+    int sms = 148;
+    try
+    {
+        int dev = 0;
+        if(cudaGetDevice(&dev) == cudaSuccess)
+            sms = device_sm_count(dev);
+    }
+    catch(...)
+    {
+        cudaGetLastError();
+    }
+    choose_config(kind, M, N, K, sms, cfg);
+    if(log2_splitk != nullptr)
+        *log2_splitk = cfg.log2_splitk;
+    g_heuristic_name = config_name(cfg);
+    return g_heuristic_name.c_str();
+}
+extern "C" unsigned long long aiter_b200_launch_count(void) { return launch_count(); }

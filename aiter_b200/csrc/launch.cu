@@ -1,0 +1,480 @@
+// Host side of the tcgen05 GEMM: tensor-map construction, configuration choice, per-stream
+// split-K workspace, launch.  No torch types; only the CUDA runtime (the one driver entry point
+// needed, cuTensorMapEncodeTiled, is resolved at run time so the library loads without libcuda).
+#include "launch.h"
+#include "gemm_kernel.cuh"
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <vector>
+
+namespace b200 {
+
+// ---------------------------------------------------------------------------------------------
+// driver entry point
+// ---------------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+        if(e != cudaSuccess || q != cudaDriverEntryPointSuccess || p == nullptr)
+            fail("cuTensorMapEncodeTiled is not available from the CUDA driver (", cudaGetErrorString(e), ")");
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+static CUtensorMap encode_map(const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes,
+                              const cuuint32_t* box, CUtensorMapSwizzle swz, const char* what)
+{
+    CUtensorMap m;
+    cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
+    CUresult r = encode_tiled_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, static_cast<cuuint32_t>(rank),
+                                   const_cast<void*>(base), dims, strides_bytes, box, elem_strides,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if(r != CUDA_SUCCESS)
+    {
+        std::ostringstream os;
+        os << "tensor map for " << what << " rejected (CUresult " << static_cast<int>(r) << "): base=" << base << " dims=";
+        for(int i = 0; i < rank; ++i)
+            os << dims[i] << (i + 1 < rank ? "x" : "");
+        os << " strides=";
+        for(int i = 0; i + 1 < rank; ++i)
+            os << strides_bytes[i] << (i + 2 < rank ? "," : "");
+        os << " box=";
+        for(int i = 0; i < rank; ++i)
+            os << box[i] << (i + 1 < rank ? "x" : "");
+        fail(os.str());
+    }
+    return m;
+}
+
+// Operand tile map; box_rows rows by 128 bytes of K per load.
+static CUtensorMap operand_map(const Operand& op, int box_rows, const char* what)
+{
+    B200_CHECK((reinterpret_cast<uintptr_t>(op.ptr) & 15) == 0, what, ": base address must be 16-byte aligned");
+    if(op.mode == OPM_ROWMAJOR)
+    {
+        B200_CHECK(op.ld_bytes % 16 == 0, what, ": row pitch must be a multiple of 16 bytes (got ", op.ld_bytes, ")");
+        cuuint64_t dims[2]    = {static_cast<cuuint64_t>(op.kbytes), static_cast<cuuint64_t>(op.rows)};
+        cuuint64_t strides[1] = {static_cast<cuuint64_t>(op.ld_bytes)};
+        cuuint32_t box[2]     = {kTileKBytes, static_cast<cuuint32_t>(box_rows)};
+        return encode_map(op.ptr, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, what);
+    }
+    if(op.mode == OPM_TILE16)
+    {
+        B200_CHECK(op.rows % 16 == 0 && op.kbytes % 32 == 0, what,
+                   ": a (16,16)-shuffled operand needs rows % 16 == 0 and K bytes % 32 == 0 (got ", op.rows, " x ",
+                   op.kbytes, ")");
+        B200_CHECK(box_rows % 16 == 0, what, ": internal: box rows must be a multiple of 16");
+        // [rows/16][kbytes/16][256 B]; smem wants [k chunk][row][16 B], so the row-block index runs
+        // faster than the k-chunk index in the box.
+        cuuint64_t dims[3]    = {256, static_cast<cuuint64_t>(op.rows / 16), static_cast<cuuint64_t>(op.kbytes / 16)};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(op.kbytes) * 16, 256};
+        cuuint32_t box[3]     = {256, static_cast<cuuint32_t>(box_rows / 16), kTileKBytes / 16};
+        return encode_map(op.ptr, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, what);
+    }
+    B200_CHECK(op.mode == OPM_A2X128, what, ": unknown operand mode ", op.mode);
+    B200_CHECK(op.rows % 2 == 0 && op.kbytes % 128 == 0, what,
+               ": the (m/2,k/128,2,128) tiling needs rows % 2 == 0 and K bytes % 128 == 0");
+    B200_CHECK(box_rows % 2 == 0, what, ": internal: box rows must be even");
+    cuuint64_t dims[4]    = {128, 2, static_cast<cuuint64_t>(op.rows / 2), static_cast<cuuint64_t>(op.kbytes / 128)};
+    cuuint64_t strides[3] = {128, static_cast<cuuint64_t>(op.kbytes) * 2, 256};
+    cuuint32_t box[4]     = {128, 2, static_cast<cuuint32_t>(box_rows / 2), 1};
+    return encode_map(op.ptr, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, what);
+}
+
+// Scale map: one row per 32-row group, `chunk` wire bytes per group per K tile.
+static CUtensorMap scale_map(const ScaleOperand& sf, int chunk, int groups_per_tile, const char* what)
+{
+    B200_CHECK((reinterpret_cast<uintptr_t>(sf.ptr) & 15) == 0, what, ": base address must be 16-byte aligned");
+    B200_CHECK(sf.padded_rows % 32 == 0, what, ": scale rows must be padded to a multiple of 32 (got ", sf.padded_rows, ")");
+    const cuuint64_t row_bytes = static_cast<cuuint64_t>(sf.padded_cols) * 32;
+    cuuint64_t dims[2]    = {row_bytes, static_cast<cuuint64_t>(sf.padded_rows / 32)};
+    cuuint64_t strides[1] = {row_bytes};
+    cuuint32_t box[2]     = {static_cast<cuuint32_t>(chunk), static_cast<cuuint32_t>(groups_per_tile)};
+    return encode_map(sf.ptr, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, what);
+}
+
+// ---------------------------------------------------------------------------------------------
+// per-device / per-stream state
+// ---------------------------------------------------------------------------------------------
+struct StreamWorkspace
+{
+    float* partial        = nullptr;
+    size_t partial_bytes  = 0;
+    unsigned int* counter = nullptr;
+};
+constexpr int kCounterSlots = 1 << 16;
+
+struct DeviceState
+{
+    int sm_count         = 0;
+    int smem_optin       = 0;
+    unsigned int* status = nullptr;
+    std::map<cudaStream_t, StreamWorkspace> ws;
+};
+
+static std::mutex g_mutex;
+static std::map<int, DeviceState> g_devices;
+static std::atomic<unsigned long long> g_launches{0};
+
+static DeviceState& device_state(int device)
+{
+    // caller holds g_mutex and has made `device` current
+    auto it = g_devices.find(device);
+    if(it != g_devices.end())
+        return it->second;
+    DeviceState st;
+    cudaDeviceProp prop;
+    B200_CUDA(cudaGetDeviceProperties(&prop, device));
+    B200_CHECK(prop.major == 10, "this library only runs on sm_100 class GPUs (device ", device, " is sm_", prop.major,
+               prop.minor, ")");
+    st.sm_count   = prop.multiProcessorCount;
+    st.smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
+    B200_CUDA(cudaMalloc(&st.status, 4 * sizeof(unsigned int)));
+    B200_CUDA(cudaMemset(st.status, 0, 4 * sizeof(unsigned int)));
+    return g_devices.emplace(device, st).first->second;
+}
+
+static StreamWorkspace& stream_workspace(DeviceState& st, cudaStream_t stream, size_t partial_bytes)
+{
+    StreamWorkspace& w = st.ws[stream];
+    const bool need_counter = (w.counter == nullptr);
+    const bool need_grow    = (partial_bytes > w.partial_bytes);
+    if(need_counter || need_grow)
+    {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(stream, &cap);
+        B200_CHECK(cap == cudaStreamCaptureStatusNone,
+                   "split-K workspace must grow (", partial_bytes, " bytes) but the stream is being captured; run this "
+                   "shape once outside capture first");
+    }
+    if(need_counter)
+    {
+        B200_CUDA(cudaMalloc(&w.counter, kCounterSlots * sizeof(unsigned int)));
+        B200_CUDA(cudaMemset(w.counter, 0, kCounterSlots * sizeof(unsigned int)));
+    }
+    if(need_grow)
+    {
+        if(w.partial != nullptr)
+        {
+            B200_CUDA(cudaStreamSynchronize(stream));
+            B200_CUDA(cudaFree(w.partial));
+            w.partial       = nullptr;
+            w.partial_bytes = 0;
+        }
+        size_t bytes = std::max(partial_bytes, static_cast<size_t>(8) << 20);
+        B200_CUDA(cudaMalloc(&w.partial, bytes));
+        w.partial_bytes = bytes;
+    }
+    return w;
+}
+
+int device_sm_count(int device)
+{
+    int prev = 0;
+    B200_CUDA(cudaGetDevice(&prev));
+    B200_CUDA(cudaSetDevice(device));
+    std::lock_guard<std::mutex> lk(g_mutex);
+    int n = device_state(device).sm_count;
+    cudaSetDevice(prev);
+    return n;
+}
+
+void read_device_status(int device, unsigned int out_words[4])
+{
+    int prev = 0;
+    B200_CUDA(cudaGetDevice(&prev));
+    B200_CUDA(cudaSetDevice(device));
+    std::lock_guard<std::mutex> lk(g_mutex);
+    DeviceState& st = device_state(device);
+    B200_CUDA(cudaDeviceSynchronize());
+    B200_CUDA(cudaMemcpy(out_words, st.status, 4 * sizeof(unsigned int), cudaMemcpyDeviceToHost));
+    B200_CUDA(cudaMemset(st.status, 0, 4 * sizeof(unsigned int)));
+    cudaSetDevice(prev);
+}
+
+unsigned long long launch_count() { return g_launches.load(); }
+
+// ---------------------------------------------------------------------------------------------
+// configuration menu / heuristic
+// ---------------------------------------------------------------------------------------------
+static const int kBnMenu[] = {16, 32, 64, 128, 256};
+
+static int kernel_kind_of(int problem_kind)
+{
+    switch(problem_kind)
+    {
+    case PK_BF16: return KIND_BF16;
+    case PK_MXFP8: return KIND_MXF8;
+    case PK_MXFP4: return KIND_MXF4;
+    default: fail("problem kind ", problem_kind, " has no kernel in this build");
+    }
+}
+
+static int max_stages(int kernel_kind, int bn, int smem_limit)
+{
+    for(int s = kMaxStages; s >= 1; --s)
+        if(static_cast<int>(make_smem_layout(kernel_kind, bn, s).total) + 1024 <= smem_limit)
+            return s;
+    return 0;
+}
+
+void choose_config(int kind, long long M, long long N, long long K, int num_sms, KernelConfig& cfg)
+{
+    if(cfg.swap < 0)
+        cfg.swap = (M <= 64) ? 1 : 0;
+    const long long rows_q = cfg.swap ? M : N;
+    const long long rows_p = cfg.swap ? N : M;
+    if(cfg.bn <= 0)
+    {
+        if(cfg.swap)
+            cfg.bn = rows_q <= 16 ? 16 : rows_q <= 32 ? 32 : rows_q <= 64 ? 64 : rows_q <= 128 ? 128 : 256;
+        else
+        {
+            // largest tile whose grid still covers the machine, else the largest that divides N well
+            cfg.bn = 256;
+            const long long tiles_p = (rows_p + kTileP - 1) / kTileP;
+            while(cfg.bn > 64 && tiles_p * ((rows_q + cfg.bn - 1) / cfg.bn) < num_sms)
+                cfg.bn >>= 1;
+            if(rows_q < cfg.bn)
+                cfg.bn = rows_q <= 16 ? 16 : rows_q <= 32 ? 32 : rows_q <= 64 ? 64 : rows_q <= 128 ? 128 : 256;
+        }
+    }
+    const int elems_per_iter = (kind == PK_BF16) ? 64 : (kind == PK_MXFP4 ? 256 : 128);
+    const long long k_iters  = (K + elems_per_iter - 1) / elems_per_iter;
+    if(cfg.log2_splitk < 0)
+    {
+        const long long tiles = ((rows_p + kTileP - 1) / kTileP) * ((rows_q + cfg.bn - 1) / cfg.bn);
+        int l2 = 0;
+        // split while the grid under-fills the machine and every split keeps >= 4 K iterations
+        while(l2 < 5 && tiles * (2LL << l2) <= num_sms && (k_iters >> (l2 + 1)) >= 4)
+            ++l2;
+        cfg.log2_splitk = l2;
+    }
+    if(cfg.stages <= 0)
+    {
+        const int kk = (kind == PK_BF16) ? KIND_BF16 : (kind == PK_MXFP4 ? KIND_MXF4 : KIND_MXF8);
+        int s        = max_stages(kk, cfg.bn, 227 * 1024);
+        cfg.stages   = s > kMaxStages ? kMaxStages : s;
+    }
+}
+
+std::string config_name(const KernelConfig& cfg)
+{
+    char buf[64];
+    std::snprintf(buf, sizeof(buf), "tc5_128x%d_%c_s%d", cfg.bn, cfg.swap ? 't' : 'n', cfg.stages);
+    return buf;
+}
+
+bool parse_config_name(const char* name, KernelConfig& cfg)
+{
+    if(name == nullptr || name[0] == 0)
+        return false;
+    int bn = 0, stages = 0;
+    char sw = 0;
+    if(std::sscanf(name, "tc5_128x%d_%c_s%d", &bn, &sw, &stages) != 3)
+        return false;
+    bool ok = false;
+    for(int b : kBnMenu)
+        ok |= (b == bn);
+    if(!ok || (sw != 'n' && sw != 't') || stages < 1 || stages > kMaxStages)
+        return false;
+    cfg.bn     = bn;
+    cfg.swap   = (sw == 't');
+    cfg.stages = stages;
+    return true;
+}
+
+// kernelId = swap * 100 + index(bn) * 10 + stages   (stages 0 = as many as fit)
+bool config_from_id(int kernel_id, KernelConfig& cfg)
+{
+    if(kernel_id < 0)
+        return false;
+    const int swap = kernel_id / 100, bi = (kernel_id / 10) % 10, st = kernel_id % 10;
+    if(swap > 1 || bi >= static_cast<int>(sizeof(kBnMenu) / sizeof(int)) || st > kMaxStages)
+        return false;
+    cfg.swap   = swap;
+    cfg.bn     = kBnMenu[bi];
+    cfg.stages = st;
+    return true;
+}
+
+const char* kernel_menu_text()
+{
+    static std::string text = [] {
+        std::ostringstream os;
+        os << "kernelName = tc5_128x<bn>_<n|t>_s<stages>; kernelId = swap*100 + bn_index*10 + stages (0 = max)\n";
+        for(int swap = 0; swap < 2; ++swap)
+            for(size_t bi = 0; bi < sizeof(kBnMenu) / sizeof(int); ++bi)
+                os << "  id " << swap * 100 + bi * 10 << "..: tile 128x" << kBnMenu[bi]
+                   << (swap ? "  weights on the 128-row slot (decode shapes), transposed store"
+                            : "  activations on the 128-row slot")
+                   << "\n";
+        return os.str();
+    }();
+    return text.c_str();
+}
+
+// ---------------------------------------------------------------------------------------------
+// launch
+// ---------------------------------------------------------------------------------------------
+template <int KIND, int SFW>
+static void launch_instance(dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap& mp, const CUtensorMap& mq,
+                            const CUtensorMap& msp, const CUtensorMap& msq, const GemmParams& prm)
+{
+    auto kernel = gemm_tcgen05_kernel<KIND, SFW>;
+    static std::once_flag once; // one flag per instantiation: raise the dynamic shared-memory limit
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    });
+    B200_CUDA(attr_err);
+    kernel<<<grid, kNumThreads, smem, stream>>>(mp, mq, msp, msq, prm);
+    B200_CUDA(cudaGetLastError());
+    g_launches.fetch_add(1);
+}
+
+void launch_gemm(const GemmProblem& prob)
+{
+    B200_CHECK(prob.M > 0 && prob.N > 0 && prob.K > 0, "empty GEMM: M=", prob.M, " N=", prob.N, " K=", prob.K);
+    B200_CHECK(prob.M < (1LL << 31) && prob.N < (1LL << 31) && prob.K < (1LL << 31), "dimension too large");
+    const int kkind = kernel_kind_of(prob.kind);
+
+    int prev_dev = 0;
+    B200_CUDA(cudaGetDevice(&prev_dev));
+    if(prev_dev != prob.device)
+        B200_CUDA(cudaSetDevice(prob.device));
+    struct Restore
+    {
+        int prev, cur;
+        ~Restore()
+        {
+            if(prev != cur)
+                cudaSetDevice(prev);
+        }
+    } restore{prev_dev, prob.device};
+
+    std::lock_guard<std::mutex> lk(g_mutex);
+    DeviceState& st = device_state(prob.device);
+
+    KernelConfig cfg = prob.cfg;
+    choose_config(prob.kind, prob.M, prob.N, prob.K, st.sm_count, cfg);
+    {
+        bool ok = false;
+        for(int b : kBnMenu)
+            ok |= (b == cfg.bn);
+        B200_CHECK(ok, "unsupported tile width ", cfg.bn);
+    }
+    const Operand& P       = cfg.swap ? prob.wgt : prob.act;
+    const Operand& Q       = cfg.swap ? prob.act : prob.wgt;
+    const ScaleOperand& SP = cfg.swap ? prob.wgt_sf : prob.act_sf;
+    const ScaleOperand& SQ = cfg.swap ? prob.act_sf : prob.wgt_sf;
+    B200_CHECK(P.kbytes == Q.kbytes, "operands disagree on K bytes: ", P.kbytes, " vs ", Q.kbytes);
+    B200_CHECK(cfg.bn >= 32 || Q.rows <= 16, "a 16-wide tile only serves problems with at most 16 rows on that side");
+    if(Q.mode == OPM_TILE16)
+        B200_CHECK(cfg.bn % 16 == 0, "internal: tile width");
+
+    const int num_k_iters = static_cast<int>((P.kbytes + kTileKBytes - 1) / kTileKBytes);
+    int splits            = 1 << cfg.log2_splitk;
+    while(splits > num_k_iters)
+        splits >>= 1;
+    const int max_st = max_stages(kkind, cfg.bn, st.smem_optin);
+    B200_CHECK(max_st >= 2, "tile 128x", cfg.bn, " does not fit in shared memory");
+    int stages = cfg.stages <= 0 ? max_st : std::min(cfg.stages, max_st);
+
+    const int tiles_p = static_cast<int>((P.rows + kTileP - 1) / kTileP);
+    const int tiles_q = static_cast<int>((Q.rows + cfg.bn - 1) / cfg.bn);
+    B200_CHECK(tiles_q <= 65535 && splits <= 65535, "grid too large");
+    B200_CHECK(splits == 1 || static_cast<long long>(tiles_p) * tiles_q <= kCounterSlots,
+               "split-K supports at most ", kCounterSlots, " output tiles");
+
+    GemmParams prm{};
+    prm.rows_p         = static_cast<int>(P.rows);
+    prm.rows_q         = static_cast<int>(Q.rows);
+    prm.num_k_iters    = num_k_iters;
+    prm.kblocks        = static_cast<int>(prob.K / 32);
+    prm.bn             = cfg.bn;
+    prm.stages         = stages;
+    prm.p_mode         = P.mode;
+    prm.q_mode         = Q.mode;
+    prm.sf_groups_p    = 4;
+    prm.sf_groups_q    = (cfg.bn + 31) / 32;
+    prm.transposed_out = cfg.swap;
+    prm.out            = static_cast<__nv_bfloat16*>(prob.out);
+    prm.ldo            = prob.ldo;
+    prm.bias           = prob.bias;
+    prm.bias_is_bf16   = prob.bias_is_bf16;
+    prm.bias_on_q      = cfg.swap ? 0 : 1;
+    prm.alpha          = prob.alpha;
+    prm.beta           = prob.beta;
+    prm.status         = st.status;
+
+    const int atoms_k  = (kkind == KIND_MXF4) ? 2 : 1;
+    const int nq128    = (cfg.bn + 127) / 128;
+    const int sf_cols  = (kkind == KIND_BF16) ? 0 : 2 * (4 * atoms_k + 4 * atoms_k * nq128);
+    prm.sf_tmem_base   = (cfg.bn + 31) & ~31;
+    int cols           = 32;
+    while(cols < prm.sf_tmem_base + sf_cols)
+        cols <<= 1;
+    B200_CHECK(cols <= 512, "internal: TMEM budget exceeded");
+    prm.tmem_cols = cols;
+
+    if(splits > 1)
+    {
+        const size_t bytes =
+            static_cast<size_t>(tiles_p) * tiles_q * splits * static_cast<size_t>(cfg.bn) * kTileP * sizeof(float);
+        StreamWorkspace& w = stream_workspace(st, prob.stream, bytes);
+        prm.ws_partial     = w.partial;
+        prm.ws_counter     = w.counter;
+    }
+
+    CUtensorMap mp = operand_map(P, kTileP, cfg.swap ? "weight operand" : "activation operand");
+    CUtensorMap mq = operand_map(Q, cfg.bn, cfg.swap ? "activation operand" : "weight operand");
+    CUtensorMap msp = mp, msq = mq;
+    int sfw = SFW_NONE;
+    if(kkind != KIND_BF16)
+    {
+        B200_CHECK(SP.wire == SQ.wire && SP.wire != SFW_NONE, "both scale tensors must use the same wire layout");
+        sfw             = SP.wire;
+        const int chunk = (sfw == SFW_E8M0_SHUFFLE) ? 256 : 128 * atoms_k;
+        B200_CHECK(sfw != SFW_E8M0_SHUFFLE || kkind == KIND_MXF4, "the e8m0_shuffle scale layout is only wired for MXFP4");
+        const long long need_cols = (sfw == SFW_E8M0_SHUFFLE) ? (prm.kblocks + 7) / 8 * 8 : prm.kblocks;
+        B200_CHECK(SP.padded_cols >= need_cols && SQ.padded_cols >= need_cols, "scale tensors have too few columns: need ",
+                   need_cols, ", got ", SP.padded_cols, " and ", SQ.padded_cols);
+        B200_CHECK(SP.padded_rows >= (P.rows + 31) / 32 * 32 && SQ.padded_rows >= (Q.rows + 31) / 32 * 32,
+                   "scale tensors have too few rows");
+        if(sfw == SFW_G1250)
+            B200_CHECK(prm.kblocks % (4 * atoms_k) == 0, "K must be a multiple of ", 128 * atoms_k, " for this scale layout");
+        msp = scale_map(SP, chunk, prm.sf_groups_p, cfg.swap ? "weight scales" : "activation scales");
+        msq = scale_map(SQ, chunk, prm.sf_groups_q, cfg.swap ? "activation scales" : "weight scales");
+    }
+
+    const SmemLayout L = make_smem_layout(kkind, cfg.bn, stages);
+    const size_t smem  = L.total + 1024;
+    dim3 grid(tiles_p, tiles_q, splits);
+
+    if(kkind == KIND_BF16)
+        launch_instance<KIND_BF16, SFW_NONE>(grid, smem, prob.stream, mp, mq, msp, msq, prm);
+    else if(kkind == KIND_MXF8 && sfw == SFW_G1250)
+        launch_instance<KIND_MXF8, SFW_G1250>(grid, smem, prob.stream, mp, mq, msp, msq, prm);
+    else if(kkind == KIND_MXF4 && sfw == SFW_E8M0_SHUFFLE)
+        launch_instance<KIND_MXF4, SFW_E8M0_SHUFFLE>(grid, smem, prob.stream, mp, mq, msp, msq, prm);
+    else if(kkind == KIND_MXF4 && sfw == SFW_G1250)
+        launch_instance<KIND_MXF4, SFW_G1250>(grid, smem, prob.stream, mp, mq, msp, msq, prm);
+    else
+        fail("no kernel instance for kind ", kkind, " with scale layout ", sfw);
+}
+
+} // namespace b200

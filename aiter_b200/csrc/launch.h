@@ -1,0 +1,97 @@
+// Host-side description of one GEMM launch and the configuration record the dispatcher works with.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <stdexcept>
+#include <sstream>
+#include <string>
+
+namespace b200 {
+
+// Throwing check used below the C ABI; the ABI wrapper turns it into "-1 + thread-local message"
+// (the reference's AITER_CHECK + aiter_safe_call pair, csrc/include/aiter_hip_common.h:67-74).
+template <typename... Args>
+[[noreturn]] inline void fail(Args&&... args)
+{
+    std::ostringstream os;
+    (os << ... << args);
+    throw std::runtime_error(os.str());
+}
+#define B200_CHECK(cond, ...)            \
+    do                                   \
+    {                                    \
+        if(!(cond))                      \
+            ::b200::fail(__VA_ARGS__);   \
+    } while(0)
+#define B200_CUDA(expr)                                                                     \
+    do                                                                                      \
+    {                                                                                       \
+        cudaError_t e_ = (expr);                                                            \
+        if(e_ != cudaSuccess)                                                               \
+            ::b200::fail(#expr, " failed: ", cudaGetErrorString(e_));                       \
+    } while(0)
+
+enum ProblemKind : int
+{
+    PK_BF16   = 0, // bf16 x bf16
+    PK_MXFP8  = 1, // e4m3 x e4m3, e8m0 per 32
+    PK_MXFP4  = 2, // e2m1 x e2m1, e8m0 per 32
+    PK_MXF8F4 = 3, // e4m3 activations x e2m1 weights
+};
+
+struct Operand
+{
+    const void* ptr = nullptr;
+    long long rows  = 0;
+    long long kbytes = 0;    // bytes along K per row
+    long long ld_bytes = 0;  // row pitch in bytes (row-major mode only)
+    int mode = 0;            // OperandMode
+};
+
+struct ScaleOperand
+{
+    const void* ptr = nullptr;
+    int wire = 0;              // SfWire
+    long long padded_rows = 0; // rows of the (padded) scale array, multiple of 32
+    long long padded_cols = 0; // scale columns of the (padded) array
+};
+
+struct KernelConfig
+{
+    int swap   = -1; // 1: weights fill the 128-row slot; 0: activations do; -1: choose
+    int bn     = 0;  // UMMA N (0: choose)
+    int stages = 0;  // 0: choose
+    int log2_splitk = -1; // -1: choose
+};
+
+struct GemmProblem
+{
+    int kind = PK_BF16;
+    long long M = 0, N = 0, K = 0; // K in elements
+    Operand act, wgt;
+    ScaleOperand act_sf, wgt_sf;
+    void* out = nullptr;
+    long long ldo = 0;          // elements
+    const void* bias = nullptr; // indexed by n
+    int bias_is_bf16 = 0;
+    float alpha = 1.f, beta = 1.f;
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    KernelConfig cfg;
+};
+
+// Fills the unset fields of cfg with the heuristic choice for (kind, M, N, K).
+void choose_config(int kind, long long M, long long N, long long K, int num_sms, KernelConfig& cfg);
+// "tc5_128x<bn>_<n|t>_s<stages>" <-> KernelConfig (t = swapped / transposed store).
+std::string config_name(const KernelConfig& cfg);
+bool parse_config_name(const char* name, KernelConfig& cfg);
+// kernelId <-> configuration (index into the fixed menu printed by aiter_b200_kernel_list()).
+bool config_from_id(int kernel_id, KernelConfig& cfg);
+const char* kernel_menu_text();
+
+void launch_gemm(const GemmProblem& prob);
+void read_device_status(int device, unsigned int out_words[4]);
+unsigned long long launch_count();
+int device_sm_count(int device);
+
+} // namespace b200

@@ -1,0 +1,128 @@
+/*
+ * aiter_b200 - C ABI of the B200 (sm_100a) quantised-GEMM library.
+ *
+ * Every entry point mirrors, name for name and argument for argument, the C-ABI / pybind
+ * function the reference binds for the same job; the reference location is cited beside each
+ * declaration (paths inside the reference project).  Conventions (reference:
+ * csrc/include/aiter_ctypes_error.h:60-150, aiter/jit/core.py:1457-1553):
+ *   - tensors travel as `aiter_tensor_t*` (160-byte POD, strides in elements, NULL = absent);
+ *   - python int -> int64-compatible `int`, bool -> int, str -> const char* (NULL = absent);
+ *   - the CUDA stream is the trailing `void*` argument (a cudaStream_t);
+ *   - the return value is 0 on success and -1 on error; the message is kept per thread and read
+ *     with aiter_get_last_error(); no C++ exception crosses the boundary;
+ *   - the caller owns every buffer, outputs included; launches are asynchronous on the stream.
+ */
+#ifndef AITER_B200_H
+#define AITER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* reference: csrc/include/aiter_enum.h:34-50 (same numbering) */
+typedef enum
+{
+    AITER_DTYPE_fp8      = 0,
+    AITER_DTYPE_fp8_e8m0 = 1,
+    AITER_DTYPE_fp16     = 2,
+    AITER_DTYPE_bf16     = 3,
+    AITER_DTYPE_fp32     = 4,
+    AITER_DTYPE_i4x2     = 5,
+    AITER_DTYPE_fp4x2    = 6,
+    AITER_DTYPE_u32      = 7,
+    AITER_DTYPE_i32      = 8,
+    AITER_DTYPE_i16      = 9,
+    AITER_DTYPE_i8       = 10,
+    AITER_DTYPE_u8       = 11,
+    AITER_DTYPE_i64      = 12,
+    AITER_DTYPE_u64      = 13
+} AiterDtype;
+
+/* reference: csrc/include/aiter_tensor.h:8-17; python mirror aiter/utility/aiter_types.py:68-88 */
+typedef struct aiter_tensor_t
+{
+    void* ptr;
+    size_t numel_;
+    int ndim;
+    int64_t shape[8];
+    int64_t strides[8];
+    AiterDtype dtype_;
+    int device_id; /* -1 = host memory */
+} aiter_tensor_t;
+
+#define AITER_B200_API __attribute__((visibility("default")))
+
+/* ---- error bridge: csrc/include/aiter_ctypes_error.h:60-77 ---- */
+AITER_B200_API int aiter_ctypes_abi_version(void); /* returns 2 */
+AITER_B200_API const char* aiter_get_last_error(void);
+AITER_B200_API void aiter_clear_last_error(void);
+
+/* ---- M bucket for tuned-table look-ups: csrc/py_itfs_cu/gemm_common.cu:12-41 ---- */
+AITER_B200_API int getPaddedM(int M, int N, int K, int gl);
+
+/* ---- MXFP4 x MXFP4 -> bf16.  csrc/py_itfs_cu/asm_gemm_a4w4.cu:158-173
+ * A [M,K/2] packed e2m1, B [N,K/2] packed e2m1 ((16,16)-shuffled when bpreshuffle != 0),
+ * A_scale / B_scale e8m0 in the e8m0_shuffle layout, out [>=M, N] bf16, bias fp32 [1,N] or NULL,
+ * out = alpha * A.B^T + beta * bias, split-K = 2^log2_k_split (0 = none, <0 = library's choice). */
+AITER_B200_API int gemm_a4w4_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* A_scale,
+                                 aiter_tensor_t* B_scale, aiter_tensor_t* out, const char* kernelName,
+                                 aiter_tensor_t* bias, float alpha, float beta, int bpreshuffle,
+                                 int log2_k_split, void* stream);
+
+/* ---- same math through the reference's second back-end names.
+ * csrc/include/rocm_ops.hpp:713-723, csrc/ck_gemm_a4w4_blockscale/gemm_a4w4_blockscale.cu:69-93 */
+AITER_B200_API int gemm_a4w4_blockscale(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
+                                        aiter_tensor_t* w_scale, aiter_tensor_t* Out, int splitK,
+                                        const char* kernelName, void* stream);
+AITER_B200_API int gemm_a4w4_blockscale_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
+                                             aiter_tensor_t* w_scale, aiter_tensor_t* Out, int kernelId,
+                                             int splitK, void* stream);
+
+/* ---- MXFP8 x MXFP8 and MXFP8 x MXFP4 -> bf16.  csrc/py_itfs_cu/asm_mxfp8fp4gemm.cu:272-302
+ * A [M,K] e4m3 ((m/2,k/128,2,128)-tiled when a_preshuffle != 0), B 16x16-byte tile transposed,
+ * scales e8m0 in the (m/32,k/4,32,4) layout, out [M,N] bf16, K % 128 == 0. */
+AITER_B200_API int mxfp8_mxfp8_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* ScaleA,
+                                        aiter_tensor_t* ScaleB, aiter_tensor_t* out, const char* kernelName,
+                                        int a_preshuffle, void* stream);
+AITER_B200_API int mxfp8_mxfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* ScaleA,
+                                        aiter_tensor_t* ScaleB, aiter_tensor_t* out, const char* kernelName,
+                                        int a_preshuffle, void* stream);
+
+/* ---- MXFP4 x MXFP4 with the (m/32,k/4,32,4) scale layout.  csrc/py_itfs_cu/asm_f4gemm.cu:396-412
+ * (bf16 output only: out_scale must be NULL). */
+AITER_B200_API int mxfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* ScaleA,
+                                  aiter_tensor_t* ScaleB, aiter_tensor_t* out, aiter_tensor_t* out_scale,
+                                  const char* kernelName, int a_preshuffle, void* stream);
+
+/* ---- bf16 x bf16 -> bf16/fp32-accumulated.  aiter/ops/gemm_op_a16w16.py:12-26 (asm form),
+ * csrc/opus_gemm/include/opus_gemm.h:16-39 and csrc/opus_gemm/opus_gemm.cu:133-209,294-350 (opus forms).
+ * A [M,K], B [N,K] ((16,16)-shuffled when bpreshuffle != 0), out [M,N] bf16, bias bf16/fp32 [N] or NULL.
+ * The opus forms take [batch,M,K] x [batch,N,K] -> [batch,M,N]. splitK: log2 of the K split, <0 = auto. */
+AITER_B200_API int gemm_a16w16_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* out,
+                                   aiter_tensor_t* semaphore, aiter_tensor_t* bias, int splitK,
+                                   const char* kernelName, int bpreshuffle, void* stream);
+AITER_B200_API int opus_gemm_a16w16_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* Y,
+                                         aiter_tensor_t* bias, int kernelId, int splitK, void* stream);
+AITER_B200_API int opus_gemm(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* Y,
+                             aiter_tensor_t* group_layout, aiter_tensor_t* x_scale, aiter_tensor_t* w_scale,
+                             aiter_tensor_t* bias, void* stream);
+AITER_B200_API int opus_gemm_workspace_init(void);
+
+/* ---- library state ---- */
+/* Copies the 4-word device status record of `device` (0 = healthy; non-zero = a bounded wait
+ * inside a kernel expired: code, block, split, iteration) and clears it.  Synchronises the device. */
+AITER_B200_API int aiter_b200_device_status(int device, unsigned int out_words[4]);
+/* Human-readable list of the kernel configurations behind `kernelName`/`kernelId`. */
+AITER_B200_API const char* aiter_b200_kernel_list(void);
+/* Name of the configuration the heuristic picks for a problem (kind: 0 bf16, 1 mxfp8, 2 mxfp4, 3 mxfp8 x mxfp4). */
+AITER_B200_API const char* aiter_b200_heuristic_name(int kind, int M, int N, int K, int* log2_splitk);
+/* Number of kernel launches issued by this library since load (all threads). */
+AITER_B200_API unsigned long long aiter_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AITER_B200_H */

@@ -1,0 +1,213 @@
+"""CUDA path vs the numpy oracle, through the operator surface and the C ABI (needs a B200)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import mx_oracle as ox
+from tests.helpers import bf16_bits, check, quant_fp4, quant_fp8, randn_bf16, to_cuda_u8
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ab():
+    import aiter_b200
+
+    return aiter_b200
+
+
+def assert_healthy(ab):
+    st = ab.device_status(0)
+    assert st == (0, 0, 0, 0), f"kernel recorded an expired wait: {[hex(w) for w in st]}"
+
+
+# ------------------------------------------------------------------------------------------- bf16
+BF16_SHAPES = [
+    (64, 1024, 1024),  # the reference's own CPU-runnable case
+    (1, 256, 512), (3, 512, 1024), (16, 1024, 4096), (33, 384, 520), (127, 272, 1032), (129, 512, 512),
+    (300, 1000, 264), (512, 2048, 2048),
+]
+
+
+@pytest.mark.parametrize("M,N,K", BF16_SHAPES)
+def test_bf16_tgemm(ab, M, N, K):
+    a = randn_bf16(M, K, 1, 0.1)
+    b = randn_bf16(N, K, 2, 0.1)
+    ref = ox.gemm_a16w16_ref(bf16_bits(a), bf16_bits(b))
+    out = ab.tgemm.mm(a.cuda(), b.cuda())
+    assert out.shape == (M, N) and out.dtype == torch.bfloat16
+    check(ref, out, what=f"tgemm.mm {M}x{N}x{K}")
+    assert_healthy(ab)
+
+
+@pytest.mark.parametrize("kernel_id,log2_split", [(100, 0), (100, 2), (113, 1), (120, 3), (20, 0), (32, 1), (30, 2), (40, 0), (44, 1), (140, 0)])
+def test_bf16_every_tile_shape(ab, kernel_id, log2_split):
+    M = 16 if kernel_id == 100 else 200
+    N, K = 768, 2048
+    a = randn_bf16(M, K, 3, 0.1)
+    b = randn_bf16(N, K, 4, 0.1)
+    bias = randn_bf16(1, N, 5).view(-1)
+    ref = ox.gemm_a16w16_ref(bf16_bits(a), bf16_bits(b), bias.float().numpy())
+    y = torch.full((1, M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ab.opus_gemm_a16w16_tune(a.cuda()[None], b.cuda()[None], y, bias.cuda(), kernel_id, log2_split)
+    check(ref, y[0], what=f"kernelId {kernel_id} splitK 2^{log2_split}")
+    assert_healthy(ab)
+
+
+def test_bf16_split_k_twice_in_a_row(ab):
+    # the ticket counters must be back at zero after a launch
+    a = randn_bf16(8, 8192, 6, 0.1)
+    b = randn_bf16(256, 8192, 7, 0.1)
+    ref = ox.gemm_a16w16_ref(bf16_bits(a), bf16_bits(b))
+    for _ in range(3):
+        y = torch.zeros((1, 8, 256), dtype=torch.bfloat16, device="cuda")
+        ab.opus_gemm_a16w16_tune(a.cuda()[None], b.cuda()[None], y, None, 100, 4)
+        check(ref, y[0], what="split-K x16 repeat")
+    assert_healthy(ab)
+
+
+def test_bf16_shuffled_weight_and_batch(ab):
+    a = randn_bf16(2 * 40, 512, 8, 0.1).view(2, 40, 512)
+    b = randn_bf16(320, 512, 9, 0.1)
+    ref = ox.gemm_a16w16_ref(bf16_bits(a.view(80, 512)), bf16_bits(b)).reshape(2, 40, 320)
+    bs = ab.shuffle_weight(b.cuda(), layout=(16, 16))
+    assert bs.is_shuffled
+    out = ab.gemm_a16w16(a.cuda(), bs)
+    check(ref.reshape(80, 320), out.view(80, 320), what="shuffled weight, 3-D activations")
+    out2 = ab.gemm_a16w16_opus(a.cuda(), b.cuda()[None].expand(2, -1, -1).contiguous())
+    check(ref.reshape(80, 320), out2.reshape(80, 320), what="opus batched")
+    assert_healthy(ab)
+
+
+def test_bf16_padded_row_pitch(ab):
+    big = randn_bf16(70, 1024 + 64, 10, 0.1).cuda()
+    a = big[:, :1024]  # row pitch 1088 elements
+    b = randn_bf16(128, 1024, 11, 0.1)
+    ref = ox.gemm_a16w16_ref(bf16_bits(a), bf16_bits(b))
+    y = torch.empty((1, 70, 128), dtype=torch.bfloat16, device="cuda")
+    ab.opus_gemm(a[None], b.cuda()[None], y)
+    check(ref, y[0], what="padded lda")
+    assert_healthy(ab)
+
+
+# ------------------------------------------------------------------------------------------- MXFP8
+def mxfp8_case(ab, M, N, K, apre, seed=0):
+    x, w = randn_bf16(M, K, seed + 1), randn_bf16(N, K, seed + 2)
+    xq, xs = quant_fp8(x)
+    wq, ws = quant_fp8(w)
+    ref = ox.gemm_a8w8_mxfp8_ref(xq, wq, xs, ws)
+    A = to_cuda_u8(xq, torch.float8_e4m3fn)
+    if apre:
+        A = ab.shuffle_mxfp8fp4_a(A)
+    B = ab.shuffle_mxfp8fp4_b(to_cuda_u8(wq, torch.float8_e4m3fn))
+    sA = ab.shuffle_mxfp8fp4_scale(to_cuda_u8(xs))
+    sB = ab.shuffle_mxfp8fp4_scale(to_cuda_u8(ws))
+    return ref, (A, B, sA, sB)
+
+
+@pytest.mark.parametrize("M,N,K,apre", [
+    (1, 256, 128, 0), (16, 512, 1024, 0), (16, 512, 1024, 1), (128, 4096, 4096, 1), (130, 304, 640, 1),
+    (300, 1024, 2048, 0), (1024, 512, 512, 1), (33, 4096, 4096, 0),
+])
+def test_mxfp8(ab, M, N, K, apre):
+    ref, args = mxfp8_case(ab, M, N, K, apre)
+    out = ab.gemm_a8w8_mxfp8(*args, a_preshuffle=bool(apre))
+    check(ref, out, what=f"gemm_a8w8_mxfp8 {M}x{N}x{K} apre={apre}")
+    assert_healthy(ab)
+
+
+@pytest.mark.parametrize("name", ["tc5_128x16_t_s4", "tc5_128x32_t_s3", "tc5_128x64_t_s2", "tc5_128x128_t_s4",
+                                  "tc5_128x32_n_s4", "tc5_128x64_n_s4", "tc5_128x128_n_s4", "tc5_128x256_n_s4"])
+def test_mxfp8_every_tile_shape(ab, name):
+    M = 16 if "x16_" in name else 160
+    ref, args = mxfp8_case(ab, M, 768, 1536, 0, seed=5)
+    out = ab.gemm_a8w8_mxfp8(*args, a_preshuffle=False, kernelName=name)
+    check(ref, out, what=name)
+    assert_healthy(ab)
+
+
+def test_mxfp8_constant_known_answer(ab):
+    # A = B = 0.5, unit scales: every output is 0.25 * K
+    M, N, K = 64, 256, 512
+    A = torch.full((M, K), 0.5).to(torch.float8_e4m3fn).cuda()
+    B = ab.shuffle_mxfp8fp4_b(torch.full((N, K), 0.5).to(torch.float8_e4m3fn).cuda())
+    s = torch.full((M, K // 32), 0x7F, dtype=torch.uint8).cuda()
+    sb = torch.full((N, K // 32), 0x7F, dtype=torch.uint8).cuda()
+    out = ab.gemm_a8w8_mxfp8(A, B, ab.shuffle_mxfp8fp4_scale(s), ab.shuffle_mxfp8fp4_scale(sb), a_preshuffle=False)
+    assert (out.float() == 0.25 * K).all()
+    assert_healthy(ab)
+
+
+# ------------------------------------------------------------------------------------------- MXFP4
+def mxfp4_case(ab, M, N, K, seed=0):
+    x, w = randn_bf16(M, K, seed + 1), randn_bf16(N, K, seed + 2)
+    xq, xs = quant_fp4(x)
+    wq, ws = quant_fp4(w)
+    ref = ox.gemm_a4w4_ref(xq, wq, xs, ws)
+    return ref, xq, wq, xs, ws
+
+
+@pytest.mark.parametrize("M,N,K,bpre", [
+    (1, 256, 256, True), (32, 512, 1024, True), (32, 512, 1024, False), (256, 7168, 2048, True), (100, 304, 352, True),
+    (129, 1024, 1536, True), (17, 2048, 4096, True), (512, 512, 768, False),
+])
+def test_mxfp4_gemm_a4w4(ab, M, N, K, bpre):
+    ref, xq, wq, xs, ws = mxfp4_case(ab, M, N, K)
+    A = to_cuda_u8(xq, ab.dtypes.fp4x2)
+    B = to_cuda_u8(wq)
+    if bpre:
+        B = ab.shuffle_weight(B, layout=(16, 16))
+    sA = ab.fp4_utils.e8m0_shuffle(to_cuda_u8(xs))
+    sB = ab.fp4_utils.e8m0_shuffle(to_cuda_u8(ws))
+    out = ab.gemm_a4w4(A, B, sA, sB, bpreshuffle=bpre)
+    assert out.shape == (M, N)
+    check(ref, out, what=f"gemm_a4w4 {M}x{N}x{K} bpre={bpre}")
+    assert_healthy(ab)
+
+
+@pytest.mark.parametrize("kernel_id,log2_split", [(100, 0), (110, 2), (123, 1), (132, 0), (14, 1), (24, 0), (34, 2), (42, 0)])
+def test_mxfp4_every_tile_shape(ab, kernel_id, log2_split):
+    M = 16 if kernel_id == 100 else 192
+    ref, xq, wq, xs, ws = mxfp4_case(ab, M, 512, 2048, seed=7)
+    out = torch.full((M, 512), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ab.gemm_a4w4_blockscale_tune(
+        to_cuda_u8(xq), ab.shuffle_weight(to_cuda_u8(wq)), ab.fp4_utils.e8m0_shuffle(to_cuda_u8(xs)),
+        ab.fp4_utils.e8m0_shuffle(to_cuda_u8(ws)), out, kernel_id, log2_split)
+    check(ref, out, what=f"a4w4 kernelId {kernel_id} splitK 2^{log2_split}")
+    assert_healthy(ab)
+
+
+def test_mxfp4_alpha_bias(ab):
+    M, N, K = 48, 256, 512
+    ref, xq, wq, xs, ws = mxfp4_case(ab, M, N, K, seed=9)
+    bias = torch.randn(1, N, generator=torch.Generator().manual_seed(3))
+    want = ox.f32_to_bf16_bits((0.5 * ox.bf16_bits_to_f32(ox.gemm_a4w4_ref(xq, wq, xs, ws)) + 2.0 * bias.numpy()).astype(np.float32))
+    out = torch.empty((64, N), dtype=torch.bfloat16, device="cuda")
+    ab.gemm_a4w4_asm(to_cuda_u8(xq), ab.shuffle_weight(to_cuda_u8(wq)), ab.fp4_utils.e8m0_shuffle(to_cuda_u8(xs)),
+                     ab.fp4_utils.e8m0_shuffle(to_cuda_u8(ws)), out, "", bias.cuda(), 0.5, 2.0, True)
+    check(want, out[:M], rtol=2e-2, atol=2e-2, what="alpha/beta/bias")  # the oracle rounds to bf16 before scaling
+    assert_healthy(ab)
+
+
+def test_mxfp4_g1250_scale_layout(ab):
+    M, N, K = 64, 512, 1024
+    ref, xq, wq, xs, ws = mxfp4_case(ab, M, N, K, seed=11)
+    out = ab.gemm_mxfp4_asm(
+        ab.shuffle_mxfp8fp4_a(to_cuda_u8(xq)), ab.shuffle_mxfp8fp4_b(to_cuda_u8(wq)),
+        ab.shuffle_mxfp8fp4_scale(to_cuda_u8(xs)), ab.shuffle_mxfp8fp4_scale(to_cuda_u8(ws)), a_preshuffle=True)
+    check(ref, out, what="mxfp4_gemm_asm")
+    assert_healthy(ab)
+
+
+# ------------------------------------------------------------------------------------------- errors
+def test_errors_are_python_exceptions(ab):
+    a = torch.zeros((4, 100), dtype=torch.float8_e4m3fn, device="cuda")
+    b = torch.zeros((16, 100), dtype=torch.float8_e4m3fn, device="cuda")
+    s = torch.zeros((32, 4), dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError, match="K must be divisible by 128"):
+        ab.gemm_a8w8_mxfp8(a, b, s, s, a_preshuffle=False)
+    with pytest.raises(RuntimeError, match="not find kernel"):
+        x = torch.zeros((4, 128), dtype=torch.float8_e4m3fn, device="cuda")
+        w = torch.zeros((16, 128), dtype=torch.float8_e4m3fn, device="cuda")
+        ab.gemm_a8w8_mxfp8(x, w, s, s, a_preshuffle=False, kernelName="no_such_kernel")
+    assert_healthy(ab)
