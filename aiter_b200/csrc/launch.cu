@@ -335,12 +335,16 @@ static void launch_instance(dim3 grid, size_t smem, cudaStream_t stream, const C
                             const CUtensorMap& msp, const CUtensorMap& msq, const GemmParams& prm)
 {
     auto kernel = gemm_tcgen05_kernel<KIND, SFW>;
-    static std::once_flag once; // one flag per instantiation: raise the dynamic shared-memory limit
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    });
-    B200_CUDA(attr_err);
+    // raise the dynamic shared-memory limit once per device for this instantiation (caller holds g_mutex)
+    static bool attr_done[64] = {};
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    if(dev < 0 || dev >= 64 || !attr_done[dev])
+    {
+        B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        if(dev >= 0 && dev < 64)
+            attr_done[dev] = true;
+    }
     kernel<<<grid, kNumThreads, smem, stream>>>(mp, mq, msp, msq, prm);
     B200_CUDA(cudaGetLastError());
     g_launches.fetch_add(1);
