@@ -69,6 +69,7 @@ struct GemmParams
     float* ws_partial;        // split-K partials (null when gridDim.z == 1)
     unsigned int* ws_counter; // one ticket counter per output tile, zero between launches
     unsigned int* status;     // 4 words
+    unsigned long long* trace; // optional 64-slot timestamp record of CTA (0,0,0); null = off
 };
 
 struct SmemLayout
@@ -179,6 +180,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const bool tracing = (prm.trace != nullptr) && (blockIdx.x | blockIdx.y | blockIdx.z) == 0;
+    auto stamp = [&](int slot) { if(tracing && slot < 64) prm.trace[slot] = global_timer_ns(); };
+    if(threadIdx.x == 0) stamp(0);
     const int bn   = prm.bn;
     const int S    = prm.stages;
 
@@ -232,6 +236,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
+    if(threadIdx.x == 0) stamp(1);
 
     const uint32_t q_box_bytes = static_cast<uint32_t>(bn) * kTileKBytes;
     const uint32_t sfp_bytes   = kScaled ? static_cast<uint32_t>(prm.sf_groups_p) * kSfChunk : 0u;
@@ -262,6 +267,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                     tma_load_2d(stage + L.sfq_off, &map_sfq, bar, (it_beg + i) * kSfChunk, row_q0 >> 5);
                 }
                 issued = i + 1;
+                if(i < 14) stamp(2 + 4 * i);
             }
             if(*abort_f)
             {
@@ -314,6 +320,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 if(!ok)
                     break;
                 tc_fence_after_sync();
+                if(i < 14) stamp(5 + 4 * i);
                 const uint32_t stage = smem_base + s * L.stage_bytes;
                 uint32_t tsfp = 0, tsfq = 0;
                 if(kScaled)
@@ -346,6 +353,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 }
                 tc_commit(empty_bar(s));
             }
+            stamp(60);
             if(ok)
                 tc_commit(accum_bar);
             else
@@ -368,6 +376,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 if(!bounded_wait(full_bar(s), (i / S) & 1, abort_f, prm.status, ST_TIMEOUT_SFWARP, i))
                     break;
                 uint8_t* stage = smem_gen + s * L.stage_bytes;
+                if(lane == 0 && i < 14) stamp(3 + 4 * i);
                 for(int op = 0; op < 2; ++op)
                 {
                     uint32_t* region = reinterpret_cast<uint32_t*>(stage + (op == 0 ? L.sfp_off : L.sfq_off));
@@ -440,7 +449,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
                 fence_proxy_async_smem();
                 __syncwarp();
                 if(lane == 0)
+                {
                     mbar_arrive(sf_bar(s));
+                    if(i < 14) stamp(4 + 4 * i);
+                }
             }
         }
     }
@@ -453,6 +465,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
         bool ok = bounded_wait(accum_bar, 0, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, 0);
         ok      = __all_sync(0xffffffffu, ok);
         tc_fence_after_sync();
+        if(warp == 3 && lane == 0) stamp(61);
         const uint32_t tlane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
         const int chunk      = bn < 32 ? 16 : 32;
         const int n_chunks   = bn / chunk;
@@ -595,10 +608,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
             if(split && warp == 3 && lane == 0)
                 prm.ws_counter[tile_lin] = 0; // ready for the next launch
         }
+        if(warp == 3 && lane == 0) stamp(62);
         tc_fence_before_sync();
     }
 
     __syncthreads();
+    if(threadIdx.x == 0) stamp(63);
     if(warp == 1)
     {
         tc_fence_after_sync();

@@ -6,6 +6,7 @@
 
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -122,6 +123,7 @@ struct DeviceState
     int sm_count         = 0;
     int smem_optin       = 0;
     unsigned int* status = nullptr;
+    unsigned long long* trace = nullptr; // debugging aid, allocated when AITER_B200_TRACE is set
     std::map<cudaStream_t, StreamWorkspace> ws;
 };
 
@@ -424,6 +426,14 @@ void launch_gemm(const GemmProblem& prob)
     prm.alpha          = prob.alpha;
     prm.beta           = prob.beta;
     prm.status         = st.status;
+    static const bool trace_on = (std::getenv("AITER_B200_TRACE") != nullptr);
+    if(trace_on)
+    {
+        if(st.trace == nullptr)
+            B200_CUDA(cudaMalloc(&st.trace, 64 * sizeof(unsigned long long)));
+        B200_CUDA(cudaMemsetAsync(st.trace, 0, 64 * sizeof(unsigned long long), prob.stream));
+        prm.trace = st.trace;
+    }
 
     const int atoms_k  = (kkind == KIND_MXF4) ? 2 : 1;
     const int nq128    = (cfg.bn + 127) / 128;
@@ -479,6 +489,20 @@ void launch_gemm(const GemmProblem& prob)
         launch_instance<KIND_MXF4, SFW_G1250>(grid, smem, prob.stream, mp, mq, msp, msq, prm);
     else
         fail("no kernel instance for kind ", kkind, " with scale layout ", sfw);
+
+    if(prm.trace != nullptr)
+    {
+        // debugging aid: print the timestamp record of CTA (0,0,0), nanoseconds relative to kernel entry
+        unsigned long long t[64];
+        B200_CUDA(cudaStreamSynchronize(prob.stream));
+        B200_CUDA(cudaMemcpy(t, st.trace, sizeof(t), cudaMemcpyDeviceToHost));
+        std::fprintf(stderr, "[trace] kind %d %lldx%lldx%lld %s grid %dx%dx%d stages %d:", prob.kind, prob.M, prob.N, prob.K,
+                     config_name(cfg).c_str(), tiles_p, tiles_q, splits, stages);
+        for(int i = 0; i < 64; ++i)
+            if(t[i] != 0)
+                std::fprintf(stderr, " %d:%lld", i, static_cast<long long>(t[i] - t[0]));
+        std::fprintf(stderr, "\n");
+    }
 }
 
 } // namespace b200

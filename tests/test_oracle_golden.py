@@ -96,3 +96,25 @@ def test_padded_m():
     assert [ox.get_padded_m(m, 4096, 4096, 0) for m in (1, 16, 17, 256, 257, 1024, 1025, 4096, 4097)] == [16, 16, 32, 256, 288, 1024, 1088, 4096, 4224]
     assert [ox.get_padded_m(m, 4096, 4096, 1) for m in (1, 2, 3, 17, 8193)] == [1, 2, 4, 32, 16384]
     assert ox.get_padded_m(8193, 4097, 128, 1) == 8192
+
+
+def test_torch_form_of_the_oracle(golden):
+    import torch
+
+    from oracle import torch_ref as tr
+
+    def t(name):
+        return torch.from_numpy(golden[name].copy())
+
+    def bits(x):
+        return x.view(torch.int16).numpy().view(np.uint16)
+
+    out = tr.gemm_a8w8_mxfp8(t("gemm_a8w8_x"), t("gemm_a8w8_w"), t("gemm_a8w8_xs"), t("gemm_a8w8_ws"))
+    assert ox.mismatch_ratio(golden["gemm_a8w8_out"], bits(out)) == 0.0
+    out = tr.gemm_a4w4(t("gemm_a4w4_x"), t("gemm_a4w4_w"), t("gemm_a4w4_xs"), t("gemm_a4w4_ws"))
+    assert ox.mismatch_ratio(golden["gemm_a4w4_out"], bits(out)) == 0.0
+    out = tr.gemm_a8w4_mxfp8(t("gemm_a8w8_x"), t("gemm_a4w4_w"), t("gemm_a8w8_xs"), t("gemm_a4w4_ws"))
+    assert ox.mismatch_ratio(golden["gemm_a8w4_out"], bits(out)) == 0.0
+    a = torch.from_numpy(golden["gemm_bf16_a"].view(np.int16).copy()).view(torch.bfloat16)
+    b = torch.from_numpy(golden["gemm_bf16_b"].view(np.int16).copy()).view(torch.bfloat16)
+    assert ox.mismatch_ratio(golden["gemm_bf16_out"], bits(tr.gemm_a16w16(a, b))) == 0.0
