@@ -1,0 +1,88 @@
+// Shared pieces of the tcgen05 GEMM kernels: enums, status codes, bounded waits, small device helpers.
+#pragma once
+#include <cuda_bf16.h>
+#include "ptx.cuh"
+
+namespace b200 {
+
+enum GemmKind : int { KIND_BF16 = 0, KIND_MXF8 = 1, KIND_MXF4 = 2 };
+enum OperandMode : int { OPM_ROWMAJOR = 0, OPM_TILE16 = 1, OPM_A2X128 = 2 };
+enum SfWire : int { SFW_NONE = 0, SFW_G1250 = 1, SFW_E8M0_SHUFFLE = 2 };
+
+constexpr int kMaxStages  = 8;
+constexpr int kTileP      = 128;
+constexpr int kTileKBytes = 128;
+constexpr int kNumThreads = 224;
+constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull; // 1 s per wait
+
+// status codes (word 0 of the status buffer); words 1..3 carry blockIdx / iteration detail
+constexpr uint32_t ST_TIMEOUT_PRODUCER = 0x101;
+constexpr uint32_t ST_TIMEOUT_MMA_FULL = 0x102;
+constexpr uint32_t ST_TIMEOUT_MMA_SF   = 0x103;
+constexpr uint32_t ST_TIMEOUT_SFWARP   = 0x104;
+constexpr uint32_t ST_TIMEOUT_EPILOGUE = 0x105;
+constexpr uint32_t ST_TIMEOUT_DRAIN    = 0x106;
+
+__device__ __forceinline__ uint64_t global_timer_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
+    return t;
+}
+
+// Wait for an mbarrier phase for at most kWaitLimitNs of wall time.  Returns false when the wait
+// expired (first expiry records `code` in the status words and raises the CTA abort flag) or when
+// another role of this CTA already aborted.
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                             unsigned int* status, uint32_t code, uint32_t detail)
+{
+    if(mbar_try_wait(bar, parity))
+        return true;
+    const uint64_t t0 = global_timer_ns();
+    for(uint32_t i = 1;; ++i)
+    {
+        if(mbar_try_wait(bar, parity))
+            return true;
+        if((i & 15u) == 0u)
+        {
+            if(*abort_flag)
+                return false;
+            if(global_timer_ns() - t0 > kWaitLimitNs)
+                break;
+        }
+    }
+    *abort_flag = 1;
+    if(atomicCAS(status, 0u, code) == 0u)
+    {
+        status[1] = blockIdx.x | (blockIdx.y << 16);
+        status[2] = blockIdx.z;
+        status[3] = detail;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void issue_operand_load(int mode, uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                                   int row0, int k_iter)
+{
+    if(mode == OPM_ROWMAJOR)
+        tma_load_2d(dst, map, bar, k_iter * kTileKBytes, row0);
+    else if(mode == OPM_TILE16)
+        tma_load_3d(dst, map, bar, 0, row0 >> 4, k_iter * (kTileKBytes / 16));
+    else
+        tma_load_4d(dst, map, bar, 0, 0, row0 >> 1, k_iter);
+}
+
+__device__ __forceinline__ float load_bias(const void* bias, int is_bf16, int idx)
+{
+    return is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[idx])
+                   : __ldg(static_cast<const float*>(bias) + idx);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b)
+{
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+
+} // namespace b200

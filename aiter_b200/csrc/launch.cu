@@ -3,6 +3,7 @@
 // needed, cuTensorMapEncodeTiled, is resolved at run time so the library loads without libcuda).
 #include "launch.h"
 #include "gemm_kernel.cuh"
+#include "gemm_persistent.cuh"
 
 #include <atomic>
 #include <cstdio>
@@ -212,7 +213,7 @@ unsigned long long launch_count() { return g_launches.load(); }
 // ---------------------------------------------------------------------------------------------
 // configuration menu / heuristic
 // ---------------------------------------------------------------------------------------------
-static const int kBnMenu[] = {16, 32, 64, 128, 256};
+static const int kBnMenu[] = {16, 32, 64, 128, 256, 192, 224, 96, 160};
 
 static int kernel_kind_of(int problem_kind)
 {
@@ -225,11 +226,21 @@ static int kernel_kind_of(int problem_kind)
     }
 }
 
-static int max_stages(int kernel_kind, int bn, int smem_limit)
+static bool use_v1()
+{
+    static const bool v1 = (std::getenv("AITER_B200_V1") != nullptr);
+    return v1;
+}
+
+static int max_stages(int kernel_kind, int bn, int cg, int smem_limit)
 {
     for(int s = kMaxStages; s >= 1; --s)
-        if(static_cast<int>(make_smem_layout(kernel_kind, bn, s).total) + 1024 <= smem_limit)
+    {
+        const int total = use_v1() ? static_cast<int>(make_smem_layout(kernel_kind, bn, s).total)
+                                   : static_cast<int>(make_persistent_smem(kernel_kind, bn, cg, s).total);
+        if(total + 1024 <= smem_limit)
             return s;
+    }
     return 0;
 }
 
@@ -254,11 +265,17 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
                 cfg.bn = rows_q <= 16 ? 16 : rows_q <= 32 ? 32 : rows_q <= 64 ? 64 : rows_q <= 128 ? 128 : 256;
         }
     }
+    if(cfg.cg <= 0)
+    {
+        // a CTA pair halves the Q bytes each SM stages per flop; worth it once there are enough 256-row tiles
+        const long long pair_tiles = ((rows_p + 2 * kTileP - 1) / (2 * kTileP)) * ((rows_q + cfg.bn - 1) / cfg.bn);
+        cfg.cg = (!cfg.swap && cfg.bn >= 128 && cfg.bn % 32 == 0 && rows_p >= 512 && pair_tiles * 2 >= num_sms) ? 2 : 1;
+    }
     const int elems_per_iter = (kind == PK_BF16) ? 64 : (kind == PK_MXFP4 ? 256 : 128);
     const long long k_iters  = (K + elems_per_iter - 1) / elems_per_iter;
     if(cfg.log2_splitk < 0)
     {
-        const long long tiles = ((rows_p + kTileP - 1) / kTileP) * ((rows_q + cfg.bn - 1) / cfg.bn);
+        const long long tiles = ((rows_p + kTileP * cfg.cg - 1) / (kTileP * cfg.cg)) * ((rows_q + cfg.bn - 1) / cfg.bn) * cfg.cg;
         int l2 = 0;
         // split while the grid under-fills the machine and every split keeps >= 4 K iterations
         while(l2 < 5 && tiles * (2LL << l2) <= num_sms && (k_iters >> (l2 + 1)) >= 4)
@@ -268,7 +285,7 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
     if(cfg.stages <= 0)
     {
         const int kk = (kind == PK_BF16) ? KIND_BF16 : (kind == PK_MXFP4 ? KIND_MXF4 : KIND_MXF8);
-        int s        = max_stages(kk, cfg.bn, 227 * 1024);
+        int s        = max_stages(kk, cfg.bn, cfg.cg, 227 * 1024);
         cfg.stages   = s > kMaxStages ? kMaxStages : s;
     }
 }
@@ -276,7 +293,7 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
 std::string config_name(const KernelConfig& cfg)
 {
     char buf[64];
-    std::snprintf(buf, sizeof(buf), "tc5_128x%d_%c_s%d", cfg.bn, cfg.swap ? 't' : 'n', cfg.stages);
+    std::snprintf(buf, sizeof(buf), "tc5_%dx%d_%c_s%d", 128 * (cfg.cg > 0 ? cfg.cg : 1), cfg.bn, cfg.swap ? 't' : 'n', cfg.stages);
     return buf;
 }
 
@@ -284,9 +301,9 @@ bool parse_config_name(const char* name, KernelConfig& cfg)
 {
     if(name == nullptr || name[0] == 0)
         return false;
-    int bn = 0, stages = 0;
+    int bm = 0, bn = 0, stages = 0;
     char sw = 0;
-    if(std::sscanf(name, "tc5_128x%d_%c_s%d", &bn, &sw, &stages) != 3)
+    if(std::sscanf(name, "tc5_%dx%d_%c_s%d", &bm, &bn, &sw, &stages) != 4 || (bm != 128 && bm != 256))
         return false;
     bool ok = false;
     for(int b : kBnMenu)
@@ -296,17 +313,19 @@ bool parse_config_name(const char* name, KernelConfig& cfg)
     cfg.bn     = bn;
     cfg.swap   = (sw == 't');
     cfg.stages = stages;
+    cfg.cg     = bm / 128;
     return true;
 }
 
-// kernelId = swap * 100 + index(bn) * 10 + stages   (stages 0 = as many as fit)
+// kernelId = pair * 1000 + swap * 100 + index(bn) * 10 + stages   (stages 0 = as many as fit)
 bool config_from_id(int kernel_id, KernelConfig& cfg)
 {
     if(kernel_id < 0)
         return false;
-    const int swap = kernel_id / 100, bi = (kernel_id / 10) % 10, st = kernel_id % 10;
-    if(swap > 1 || bi >= static_cast<int>(sizeof(kBnMenu) / sizeof(int)) || st > kMaxStages)
+    const int pair = kernel_id / 1000, swap = (kernel_id / 100) % 10, bi = (kernel_id / 10) % 10, st = kernel_id % 10;
+    if(pair > 1 || swap > 1 || bi >= static_cast<int>(sizeof(kBnMenu) / sizeof(int)) || st > kMaxStages)
         return false;
+    cfg.cg     = pair + 1;
     cfg.swap   = swap;
     cfg.bn     = kBnMenu[bi];
     cfg.stages = st;
@@ -317,7 +336,8 @@ const char* kernel_menu_text()
 {
     static std::string text = [] {
         std::ostringstream os;
-        os << "kernelName = tc5_128x<bn>_<n|t>_s<stages>; kernelId = swap*100 + bn_index*10 + stages (0 = max)\n";
+        os << "kernelName = tc5_<128|256>x<bn>_<n|t>_s<stages>; kernelId = pair*1000 + swap*100 + bn_index*10 + stages (0 = max)\n"
+           << "  256-row tiles (pair = 1) run on CTA pairs (cta_group::2)\n";
         for(int swap = 0; swap < 2; ++swap)
             for(size_t bi = 0; bi < sizeof(kBnMenu) / sizeof(int); ++bi)
                 os << "  id " << swap * 100 + bi * 10 << "..: tile 128x" << kBnMenu[bi]
@@ -332,13 +352,11 @@ const char* kernel_menu_text()
 // ---------------------------------------------------------------------------------------------
 // launch
 // ---------------------------------------------------------------------------------------------
-template <int KIND, int SFW>
-static void launch_instance(dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap& mp, const CUtensorMap& mq,
-                            const CUtensorMap& msp, const CUtensorMap& msq, const GemmParams& prm)
+// Raise the dynamic shared-memory limit once per device for one kernel; `attr_done` is the caller's
+// per-instantiation flag array (caller holds g_mutex).
+template <typename Kernel>
+static void raise_smem_limit(Kernel kernel, bool (&attr_done)[64])
 {
-    auto kernel = gemm_tcgen05_kernel<KIND, SFW>;
-    // raise the dynamic shared-memory limit once per device for this instantiation (caller holds g_mutex)
-    static bool attr_done[64] = {};
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
     if(dev < 0 || dev >= 64 || !attr_done[dev])
@@ -347,9 +365,67 @@ static void launch_instance(dim3 grid, size_t smem, cudaStream_t stream, const C
         if(dev >= 0 && dev < 64)
             attr_done[dev] = true;
     }
+}
+
+template <int KIND, int SFW>
+static void launch_v1(dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap& mp, const CUtensorMap& mq,
+                      const CUtensorMap& msp, const CUtensorMap& msq, const GemmParams& prm)
+{
+    auto kernel = gemm_tcgen05_kernel<KIND, SFW>;
+    static bool attr_done[64] = {};
+    raise_smem_limit(kernel, attr_done);
     kernel<<<grid, kNumThreads, smem, stream>>>(mp, mq, msp, msq, prm);
     B200_CUDA(cudaGetLastError());
     g_launches.fetch_add(1);
+}
+
+template <int KIND, int SFW, int CG>
+static void launch_persistent(int ctas, size_t smem, cudaStream_t stream, const CUtensorMap& mp, const CUtensorMap& mq,
+                              const CUtensorMap& msp, const CUtensorMap& msq, const PersistentParams& prm)
+{
+    auto kernel = gemm_persistent_kernel<KIND, SFW, CG>;
+    static bool attr_done[64] = {};
+    raise_smem_limit(kernel, attr_done);
+    cudaLaunchConfig_t lc{};
+    lc.gridDim          = dim3(ctas, 1, 1);
+    lc.blockDim         = dim3(kPersistentThreads, 1, 1);
+    lc.dynamicSmemBytes = smem;
+    lc.stream           = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id               = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CG;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    lc.attrs    = attr;
+    lc.numAttrs = 1;
+    B200_CUDA(cudaLaunchKernelEx(&lc, kernel, mp, mq, msp, msq, prm));
+    g_launches.fetch_add(1);
+}
+
+template <int KIND, int SFW>
+static void launch_persistent_cg(int cg, int ctas, size_t smem, cudaStream_t stream, const CUtensorMap& mp,
+                                 const CUtensorMap& mq, const CUtensorMap& msp, const CUtensorMap& msq,
+                                 const PersistentParams& prm)
+{
+    if(cg == 2)
+        launch_persistent<KIND, SFW, 2>(ctas, smem, stream, mp, mq, msp, msq, prm);
+    else
+        launch_persistent<KIND, SFW, 1>(ctas, smem, stream, mp, mq, msp, msq, prm);
+}
+
+static void print_trace(DeviceState& st, const GemmProblem& prob, const KernelConfig& cfg, int tiles_p, int tiles_q, int splits,
+                        int stages)
+{
+    // debugging aid: timestamp record of the first CTA, nanoseconds relative to kernel entry
+    unsigned long long t[64];
+    B200_CUDA(cudaStreamSynchronize(prob.stream));
+    B200_CUDA(cudaMemcpy(t, st.trace, sizeof(t), cudaMemcpyDeviceToHost));
+    std::fprintf(stderr, "[trace] kind %d %lldx%lldx%lld %s tiles %dx%d splits %d stages %d:", prob.kind, prob.M, prob.N, prob.K,
+                 config_name(cfg).c_str(), tiles_p, tiles_q, splits, stages);
+    for(int i = 0; i < 64; ++i)
+        if(t[i] != 0)
+            std::fprintf(stderr, " %d:%lld", i, static_cast<long long>(t[i] - t[0]));
+    std::fprintf(stderr, "\n");
 }
 
 void launch_gemm(const GemmProblem& prob)
@@ -376,6 +452,8 @@ void launch_gemm(const GemmProblem& prob)
     DeviceState& st = device_state(prob.device);
 
     KernelConfig cfg = prob.cfg;
+    if(use_v1())
+        cfg.cg = 1;
     choose_config(prob.kind, prob.M, prob.N, prob.K, st.sm_count, cfg);
     {
         bool ok = false;
@@ -383,126 +461,185 @@ void launch_gemm(const GemmProblem& prob)
             ok |= (b == cfg.bn);
         B200_CHECK(ok, "unsupported tile width ", cfg.bn);
     }
+    const int cg = cfg.cg;
+    B200_CHECK(cg == 1 || cg == 2, "internal: CTAs per tile");
+    B200_CHECK(cg == 1 || cfg.bn % 32 == 0, "a CTA-pair tile needs a width that is a multiple of 32");
     const Operand& P       = cfg.swap ? prob.wgt : prob.act;
     const Operand& Q       = cfg.swap ? prob.act : prob.wgt;
     const ScaleOperand& SP = cfg.swap ? prob.wgt_sf : prob.act_sf;
     const ScaleOperand& SQ = cfg.swap ? prob.act_sf : prob.wgt_sf;
     B200_CHECK(P.kbytes == Q.kbytes, "operands disagree on K bytes: ", P.kbytes, " vs ", Q.kbytes);
-    B200_CHECK(cfg.bn >= 32 || Q.rows <= 16, "a 16-wide tile only serves problems with at most 16 rows on that side");
-    if(Q.mode == OPM_TILE16)
-        B200_CHECK(cfg.bn % 16 == 0, "internal: tile width");
+    B200_CHECK(cfg.bn % 32 == 0 || Q.rows <= cfg.bn, "a tile width of ", cfg.bn,
+               " only serves problems with at most that many rows on that side");
 
     const int num_k_iters = static_cast<int>((P.kbytes + kTileKBytes - 1) / kTileKBytes);
     int splits            = 1 << cfg.log2_splitk;
     while(splits > num_k_iters)
         splits >>= 1;
-    const int max_st = max_stages(kkind, cfg.bn, st.smem_optin);
-    B200_CHECK(max_st >= 2, "tile 128x", cfg.bn, " does not fit in shared memory");
+    const int atoms_k  = (kkind == KIND_MXF4) ? 2 : 1;
+    const int nq128    = (cfg.bn + 127) / 128;
+    const int sf_cols  = (kkind == KIND_BF16) ? 0 : (4 * atoms_k + 4 * atoms_k * nq128);
+    const int max_st = max_stages(kkind, cfg.bn, cg, st.smem_optin);
+    B200_CHECK(max_st >= 2, "tile ", 128 * cg, "x", cfg.bn, " does not fit in shared memory");
     int stages = cfg.stages <= 0 ? max_st : std::min(cfg.stages, max_st);
 
-    const int tiles_p = static_cast<int>((P.rows + kTileP - 1) / kTileP);
+    const int tile_rows_p = kTileP * cg;
+    const int tiles_p = static_cast<int>((P.rows + tile_rows_p - 1) / tile_rows_p);
     const int tiles_q = static_cast<int>((Q.rows + cfg.bn - 1) / cfg.bn);
     B200_CHECK(tiles_q <= 65535 && splits <= 65535, "grid too large");
-    B200_CHECK(splits == 1 || static_cast<long long>(tiles_p) * tiles_q <= kCounterSlots,
+    B200_CHECK(splits == 1 || static_cast<long long>(tiles_p) * tiles_q * cg <= kCounterSlots,
                "split-K supports at most ", kCounterSlots, " output tiles");
 
-    GemmParams prm{};
-    prm.rows_p         = static_cast<int>(P.rows);
-    prm.rows_q         = static_cast<int>(Q.rows);
-    prm.num_k_iters    = num_k_iters;
-    prm.kblocks        = static_cast<int>(prob.K / 32);
-    prm.bn             = cfg.bn;
-    prm.stages         = stages;
-    prm.p_mode         = P.mode;
-    prm.q_mode         = Q.mode;
-    prm.sf_groups_p    = 4;
-    prm.sf_groups_q    = (cfg.bn + 31) / 32;
-    prm.transposed_out = cfg.swap;
-    prm.out            = static_cast<__nv_bfloat16*>(prob.out);
-    prm.ldo            = prob.ldo;
-    prm.bias           = prob.bias;
-    prm.bias_is_bf16   = prob.bias_is_bf16;
-    prm.bias_on_q      = cfg.swap ? 0 : 1;
-    prm.alpha          = prob.alpha;
-    prm.beta           = prob.beta;
-    prm.status         = st.status;
     static const bool trace_on = (std::getenv("AITER_B200_TRACE") != nullptr);
+    unsigned long long* trace = nullptr;
     if(trace_on)
     {
         if(st.trace == nullptr)
             B200_CUDA(cudaMalloc(&st.trace, 64 * sizeof(unsigned long long)));
         B200_CUDA(cudaMemsetAsync(st.trace, 0, 64 * sizeof(unsigned long long), prob.stream));
-        prm.trace = st.trace;
+        trace = st.trace;
     }
 
-    const int atoms_k  = (kkind == KIND_MXF4) ? 2 : 1;
-    const int nq128    = (cfg.bn + 127) / 128;
-    const int sf_cols  = (kkind == KIND_BF16) ? 0 : 2 * (4 * atoms_k + 4 * atoms_k * nq128);
-    prm.sf_tmem_base   = (cfg.bn + 31) & ~31;
-    int cols           = 32;
-    while(cols < prm.sf_tmem_base + sf_cols)
-        cols <<= 1;
-    B200_CHECK(cols <= 512, "internal: TMEM budget exceeded");
-    prm.tmem_cols = cols;
-
+    float* ws_partial        = nullptr;
+    unsigned int* ws_counter = nullptr;
     if(splits > 1)
     {
-        const size_t bytes =
-            static_cast<size_t>(tiles_p) * tiles_q * splits * static_cast<size_t>(cfg.bn) * kTileP * sizeof(float);
+        const size_t bytes = static_cast<size_t>(tiles_p) * tiles_q * cg * splits * static_cast<size_t>(cfg.bn) * kTileP * sizeof(float);
         StreamWorkspace& w = stream_workspace(st, prob.stream, bytes);
-        prm.ws_partial     = w.partial;
-        prm.ws_counter     = w.counter;
+        ws_partial         = w.partial;
+        ws_counter         = w.counter;
     }
 
-    CUtensorMap mp = operand_map(P, kTileP, cfg.swap ? "weight operand" : "activation operand");
-    CUtensorMap mq = operand_map(Q, cfg.bn, cfg.swap ? "activation operand" : "weight operand");
+    // tensor maps: every CTA stages 128 rows of P and bn / cg rows of Q per K tile
+    const int sf_groups_q = (cfg.bn + 31) / 32;
+    CUtensorMap mp  = operand_map(P, kTileP, cfg.swap ? "weight operand" : "activation operand");
+    CUtensorMap mq  = operand_map(Q, cfg.bn / cg, cfg.swap ? "activation operand" : "weight operand");
     CUtensorMap msp = mp, msq = mq;
     int sfw = SFW_NONE;
+    const int kblocks = static_cast<int>(prob.K / 32);
     if(kkind != KIND_BF16)
     {
         B200_CHECK(SP.wire == SQ.wire && SP.wire != SFW_NONE, "both scale tensors must use the same wire layout");
         sfw             = SP.wire;
         const int chunk = (sfw == SFW_E8M0_SHUFFLE) ? 256 : 128 * atoms_k;
         B200_CHECK(sfw != SFW_E8M0_SHUFFLE || kkind == KIND_MXF4, "the e8m0_shuffle scale layout is only wired for MXFP4");
-        const long long need_cols = (sfw == SFW_E8M0_SHUFFLE) ? (prm.kblocks + 7) / 8 * 8 : prm.kblocks;
+        const long long need_cols = (sfw == SFW_E8M0_SHUFFLE) ? (kblocks + 7) / 8 * 8 : kblocks;
         B200_CHECK(SP.padded_cols >= need_cols && SQ.padded_cols >= need_cols, "scale tensors have too few columns: need ",
                    need_cols, ", got ", SP.padded_cols, " and ", SQ.padded_cols);
         B200_CHECK(SP.padded_rows >= (P.rows + 31) / 32 * 32 && SQ.padded_rows >= (Q.rows + 31) / 32 * 32,
                    "scale tensors have too few rows");
         if(sfw == SFW_G1250)
-            B200_CHECK(prm.kblocks % (4 * atoms_k) == 0, "K must be a multiple of ", 128 * atoms_k, " for this scale layout");
-        msp = scale_map(SP, chunk, prm.sf_groups_p, cfg.swap ? "weight scales" : "activation scales");
-        msq = scale_map(SQ, chunk, prm.sf_groups_q, cfg.swap ? "activation scales" : "weight scales");
+            B200_CHECK(kblocks % (4 * atoms_k) == 0, "K must be a multiple of ", 128 * atoms_k, " for this scale layout");
+        msp = scale_map(SP, chunk, 4, cfg.swap ? "weight scales" : "activation scales");
+        msq = scale_map(SQ, chunk, sf_groups_q, cfg.swap ? "activation scales" : "weight scales");
     }
 
-    const SmemLayout L = make_smem_layout(kkind, cfg.bn, stages);
-    const size_t smem  = L.total + 1024;
-    dim3 grid(tiles_p, tiles_q, splits);
-
-    if(kkind == KIND_BF16)
-        launch_instance<KIND_BF16, SFW_NONE>(grid, smem, prob.stream, mp, mq, msp, msq, prm);
-    else if(kkind == KIND_MXF8 && sfw == SFW_G1250)
-        launch_instance<KIND_MXF8, SFW_G1250>(grid, smem, prob.stream, mp, mq, msp, msq, prm);
-    else if(kkind == KIND_MXF4 && sfw == SFW_E8M0_SHUFFLE)
-        launch_instance<KIND_MXF4, SFW_E8M0_SHUFFLE>(grid, smem, prob.stream, mp, mq, msp, msq, prm);
-    else if(kkind == KIND_MXF4 && sfw == SFW_G1250)
-        launch_instance<KIND_MXF4, SFW_G1250>(grid, smem, prob.stream, mp, mq, msp, msq, prm);
-    else
-        fail("no kernel instance for kind ", kkind, " with scale layout ", sfw);
-
-    if(prm.trace != nullptr)
+    if(use_v1())
     {
-        // debugging aid: print the timestamp record of CTA (0,0,0), nanoseconds relative to kernel entry
-        unsigned long long t[64];
-        B200_CUDA(cudaStreamSynchronize(prob.stream));
-        B200_CUDA(cudaMemcpy(t, st.trace, sizeof(t), cudaMemcpyDeviceToHost));
-        std::fprintf(stderr, "[trace] kind %d %lldx%lldx%lld %s grid %dx%dx%d stages %d:", prob.kind, prob.M, prob.N, prob.K,
-                     config_name(cfg).c_str(), tiles_p, tiles_q, splits, stages);
-        for(int i = 0; i < 64; ++i)
-            if(t[i] != 0)
-                std::fprintf(stderr, " %d:%lld", i, static_cast<long long>(t[i] - t[0]));
-        std::fprintf(stderr, "\n");
+        B200_CHECK(cfg.bn <= 256 && (cfg.bn & (cfg.bn - 1)) == 0, "the non-persistent kernel takes power-of-two tile widths");
+        GemmParams prm{};
+        prm.rows_p         = static_cast<int>(P.rows);
+        prm.rows_q         = static_cast<int>(Q.rows);
+        prm.num_k_iters    = num_k_iters;
+        prm.kblocks        = kblocks;
+        prm.bn             = cfg.bn;
+        prm.stages         = stages;
+        prm.p_mode         = P.mode;
+        prm.q_mode         = Q.mode;
+        prm.sf_groups_p    = 4;
+        prm.sf_groups_q    = sf_groups_q;
+        prm.transposed_out = cfg.swap;
+        prm.out            = static_cast<__nv_bfloat16*>(prob.out);
+        prm.ldo            = prob.ldo;
+        prm.bias           = prob.bias;
+        prm.bias_is_bf16   = prob.bias_is_bf16;
+        prm.bias_on_q      = cfg.swap ? 0 : 1;
+        prm.alpha          = prob.alpha;
+        prm.beta           = prob.beta;
+        prm.status         = st.status;
+        prm.trace          = trace;
+        prm.ws_partial     = ws_partial;
+        prm.ws_counter     = ws_counter;
+        prm.sf_tmem_base   = (cfg.bn + 31) & ~31;
+        int cols           = 32;
+        while(cols < prm.sf_tmem_base + 2 * sf_cols)
+            cols <<= 1;
+        B200_CHECK(cols <= 512, "internal: TMEM budget exceeded");
+        prm.tmem_cols = cols;
+        const SmemLayout L = make_smem_layout(kkind, cfg.bn, stages);
+        const size_t smem  = L.total + 1024;
+        dim3 grid(tiles_p, tiles_q, splits);
+        if(kkind == KIND_BF16)
+            launch_v1<KIND_BF16, SFW_NONE>(grid, smem, prob.stream, mp, mq, msp, msq, prm);
+        else if(kkind == KIND_MXF8 && sfw == SFW_G1250)
+            launch_v1<KIND_MXF8, SFW_G1250>(grid, smem, prob.stream, mp, mq, msp, msq, prm);
+        else if(kkind == KIND_MXF4 && sfw == SFW_E8M0_SHUFFLE)
+            launch_v1<KIND_MXF4, SFW_E8M0_SHUFFLE>(grid, smem, prob.stream, mp, mq, msp, msq, prm);
+        else if(kkind == KIND_MXF4 && sfw == SFW_G1250)
+            launch_v1<KIND_MXF4, SFW_G1250>(grid, smem, prob.stream, mp, mq, msp, msq, prm);
+        else
+            fail("no kernel instance for kind ", kkind, " with scale layout ", sfw);
     }
+    else
+    {
+        PersistentParams prm{};
+        prm.rows_p         = static_cast<int>(P.rows);
+        prm.rows_q         = static_cast<int>(Q.rows);
+        prm.num_k_iters    = num_k_iters;
+        prm.kblocks        = kblocks;
+        prm.bn             = cfg.bn;
+        prm.p_mode         = P.mode;
+        prm.q_mode         = Q.mode;
+        prm.sf_groups_p    = 4;
+        prm.sf_groups_q    = sf_groups_q;
+        prm.transposed_out = cfg.swap;
+        prm.tiles_p        = tiles_p;
+        prm.tiles_q        = tiles_q;
+        prm.splits         = splits;
+        prm.out            = static_cast<__nv_bfloat16*>(prob.out);
+        prm.ldo            = prob.ldo;
+        prm.bias           = prob.bias;
+        prm.bias_is_bf16   = prob.bias_is_bf16;
+        prm.bias_on_q      = cfg.swap ? 0 : 1;
+        prm.alpha          = prob.alpha;
+        prm.beta           = prob.beta;
+        prm.status         = st.status;
+        prm.trace          = trace;
+        prm.ws_partial     = ws_partial;
+        prm.ws_counter     = ws_counter;
+        // TMEM: n_acc accumulators of acc_stride columns, then one scale buffer per shared-memory stage
+        prm.acc_stride = (cfg.bn + 31) & ~31;
+        prm.sf_cols    = sf_cols;
+        const long long units = static_cast<long long>(tiles_p) * tiles_q * splits;
+        const int clusters    = static_cast<int>(std::min<long long>(units, st.sm_count / cg));
+        const bool multi_unit = units > clusters;
+        prm.n_acc = (multi_unit && 2 * prm.acc_stride + stages * sf_cols <= 512) ? 2 : 1;
+        while(prm.n_acc * prm.acc_stride + stages * sf_cols > 512 && stages > 2)
+            --stages;
+        B200_CHECK(prm.n_acc * prm.acc_stride + stages * sf_cols <= 512, "internal: TMEM budget exceeded");
+        prm.stages       = stages;
+        prm.sf_tmem_base = prm.n_acc * prm.acc_stride;
+        int cols         = 32;
+        while(cols < prm.sf_tmem_base + stages * sf_cols)
+            cols <<= 1;
+        prm.tmem_cols = cols;
+        const PersistentSmem L = make_persistent_smem(kkind, cfg.bn, cg, stages);
+        const size_t smem      = L.total + 1024;
+        const int ctas         = clusters * cg;
+        if(kkind == KIND_BF16)
+            launch_persistent_cg<KIND_BF16, SFW_NONE>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
+        else if(kkind == KIND_MXF8 && sfw == SFW_G1250)
+            launch_persistent_cg<KIND_MXF8, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
+        else if(kkind == KIND_MXF4 && sfw == SFW_E8M0_SHUFFLE)
+            launch_persistent_cg<KIND_MXF4, SFW_E8M0_SHUFFLE>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
+        else if(kkind == KIND_MXF4 && sfw == SFW_G1250)
+            launch_persistent_cg<KIND_MXF4, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
+        else
+            fail("no kernel instance for kind ", kkind, " with scale layout ", sfw);
+    }
+
+    if(trace != nullptr)
+        print_trace(st, prob, cfg, tiles_p, tiles_q, splits, stages);
 }
 
 } // namespace b200

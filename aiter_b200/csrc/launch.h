@@ -62,6 +62,7 @@ struct KernelConfig
     int bn     = 0;  // UMMA N (0: choose)
     int stages = 0;  // 0: choose
     int log2_splitk = -1; // -1: choose
+    int cg = 0;      // CTAs per tile: 1, or 2 (a 256-row tile on a CTA pair); 0: choose
 };
 
 struct GemmProblem
@@ -82,7 +83,7 @@ struct GemmProblem
 
 // Fills the unset fields of cfg with the heuristic choice for (kind, M, N, K).
 void choose_config(int kind, long long M, long long N, long long K, int num_sms, KernelConfig& cfg);
-// "tc5_128x<bn>_<n|t>_s<stages>" <-> KernelConfig (t = swapped / transposed store).
+// "tc5_<128|256>x<bn>_<n|t>_s<stages>" <-> KernelConfig (t = swapped / transposed store; 256 = CTA pair).
 std::string config_name(const KernelConfig& cfg);
 bool parse_config_name(const char* name, KernelConfig& cfg);
 // kernelId <-> configuration (index into the fixed menu printed by aiter_b200_kernel_list()).

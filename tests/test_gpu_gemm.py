@@ -40,9 +40,10 @@ def test_bf16_tgemm(ab, M, N, K):
     assert_healthy(ab)
 
 
-@pytest.mark.parametrize("kernel_id,log2_split", [(100, 0), (100, 2), (113, 1), (120, 3), (20, 0), (32, 1), (30, 2), (40, 0), (44, 1), (140, 0)])
+@pytest.mark.parametrize("kernel_id,log2_split", [(100, 0), (100, 2), (113, 1), (120, 3), (20, 0), (32, 1), (30, 2), (40, 0), (44, 1), (140, 0),
+                                                  (50, 0), (60, 1), (70, 0), (80, 0), (1040, 0), (1030, 1), (1053, 0), (1060, 0), (1130, 0)])
 def test_bf16_every_tile_shape(ab, kernel_id, log2_split):
-    M = 16 if kernel_id == 100 else 200
+    M = 16 if kernel_id == 100 else (600 if kernel_id >= 1000 else 200)
     N, K = 768, 2048
     a = randn_bf16(M, K, 3, 0.1)
     b = randn_bf16(N, K, 4, 0.1)
@@ -117,9 +118,11 @@ def test_mxfp8(ab, M, N, K, apre):
 
 
 @pytest.mark.parametrize("name", ["tc5_128x16_t_s4", "tc5_128x32_t_s3", "tc5_128x64_t_s2", "tc5_128x128_t_s4",
-                                  "tc5_128x32_n_s4", "tc5_128x64_n_s4", "tc5_128x128_n_s4", "tc5_128x256_n_s4"])
+                                  "tc5_128x32_n_s4", "tc5_128x64_n_s4", "tc5_128x128_n_s4", "tc5_128x256_n_s4",
+                                  "tc5_128x192_n_s4", "tc5_128x224_n_s3", "tc5_128x96_n_s4", "tc5_128x160_n_s4",
+                                  "tc5_256x256_n_s4", "tc5_256x128_n_s6", "tc5_256x192_n_s5", "tc5_256x224_n_s4", "tc5_256x64_n_s4"])
 def test_mxfp8_every_tile_shape(ab, name):
-    M = 16 if "x16_" in name else 160
+    M = 16 if "x16_" in name else (700 if name.startswith("tc5_256") else 160)
     ref, args = mxfp8_case(ab, M, 768, 1536, 0, seed=5)
     out = ab.gemm_a8w8_mxfp8(*args, a_preshuffle=False, kernelName=name)
     check(ref, out, what=name)
@@ -165,9 +168,10 @@ def test_mxfp4_gemm_a4w4(ab, M, N, K, bpre):
     assert_healthy(ab)
 
 
-@pytest.mark.parametrize("kernel_id,log2_split", [(100, 0), (110, 2), (123, 1), (132, 0), (14, 1), (24, 0), (34, 2), (42, 0)])
+@pytest.mark.parametrize("kernel_id,log2_split", [(100, 0), (110, 2), (123, 1), (132, 0), (14, 1), (24, 0), (34, 2), (42, 0),
+                                                  (52, 0), (62, 0), (1040, 0), (1044, 1), (1030, 0), (1050, 0), (1060, 0)])
 def test_mxfp4_every_tile_shape(ab, kernel_id, log2_split):
-    M = 16 if kernel_id == 100 else 192
+    M = 16 if kernel_id == 100 else (520 if kernel_id >= 1000 else 192)
     ref, xq, wq, xs, ws = mxfp4_case(ab, M, 512, 2048, seed=7)
     out = torch.full((M, 512), float("nan"), dtype=torch.bfloat16, device="cuda")
     ab.gemm_a4w4_blockscale_tune(
@@ -196,6 +200,34 @@ def test_mxfp4_g1250_scale_layout(ab):
         ab.shuffle_mxfp8fp4_a(to_cuda_u8(xq)), ab.shuffle_mxfp8fp4_b(to_cuda_u8(wq)),
         ab.shuffle_mxfp8fp4_scale(to_cuda_u8(xs)), ab.shuffle_mxfp8fp4_scale(to_cuda_u8(ws)), a_preshuffle=True)
     check(ref, out, what="mxfp4_gemm_asm")
+    assert_healthy(ab)
+
+
+# ------------------------------------------------------------------------------------------- persistent paths
+def test_many_units_per_cta(ab):
+    # more output tiles than SMs: the persistent loop, both accumulators and the stage ring wrap many times
+    M, N, K = 2048, 4096, 512
+    ref, args = mxfp8_case(ab, M, N, K, 0, seed=21)
+    for name in ("tc5_128x64_n_s3", "tc5_256x128_n_s4", "tc5_256x256_n_s5", ""):
+        out = ab.gemm_a8w8_mxfp8(*args, a_preshuffle=False, kernelName=name)
+        check(ref, out, what=f"mxfp8 {M}x{N}x{K} {name or 'heuristic'}")
+    assert_healthy(ab)
+    a = randn_bf16(M, K, 31, 0.1)
+    b = randn_bf16(N, K, 32, 0.1)
+    refb = ox.gemm_a16w16_ref(bf16_bits(a), bf16_bits(b))
+    for kid in (22, 1034, 1043):
+        y = torch.full((1, M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ab.opus_gemm_a16w16_tune(a.cuda()[None], b.cuda()[None], y, None, kid, 0)
+        check(refb, y[0], what=f"bf16 kernelId {kid}")
+    assert_healthy(ab)
+
+
+def test_mxfp4_large_pair_tiles(ab):
+    M, N, K = 1024, 7168, 2048
+    ref, xq, wq, xs, ws = mxfp4_case(ab, M, N, K, seed=23)
+    out = ab.gemm_a4w4(to_cuda_u8(xq, ab.dtypes.fp4x2), ab.shuffle_weight(to_cuda_u8(wq)),
+                       ab.fp4_utils.e8m0_shuffle(to_cuda_u8(xs)), ab.fp4_utils.e8m0_shuffle(to_cuda_u8(ws)))
+    check(ref, out, what="gemm_a4w4 1024x7168x2048 (heuristic)")
     assert_healthy(ab)
 
 
