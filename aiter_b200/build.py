@@ -9,7 +9,7 @@ import sys
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
 LIB_PATH = os.path.join(CSRC, "libaiter_b200.so")
 SOURCES = ["abi.cu", "launch.cu"]
-HEADERS = ["ptx.cuh", "gemm_kernel.cuh", "launch.h", os.path.join("..", "..", "include", "aiter_b200.h")]
+PUBLIC_HEADER = os.path.join("..", "..", "include", "aiter_b200.h")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
@@ -29,7 +29,8 @@ def is_stale() -> bool:
     if not os.path.exists(LIB_PATH):
         return True
     built = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS]
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cuh", ".h"))]
+    deps.append(os.path.join(CSRC, PUBLIC_HEADER))
     return any(os.path.getmtime(d) > built for d in deps if os.path.exists(d))
 
 

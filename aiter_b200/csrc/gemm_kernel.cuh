@@ -101,7 +101,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const bool tracing = (prm.trace != nullptr) && (blockIdx.x | blockIdx.y | blockIdx.z) == 0;
-    auto stamp = [&](int slot) { if(tracing && slot < 64) prm.trace[slot] = global_timer_ns(); };
+    auto stamp = [&](int slot) { if(tracing && slot < 64) prm.trace[slot] = static_cast<unsigned long long>(clock64()); };
     if(threadIdx.x == 0) stamp(0);
     const int bn   = prm.bn;
     const int S    = prm.stages;

@@ -115,7 +115,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     const int n_clusters = gridDim.x / CG;
 
     const bool tracing = (prm.trace != nullptr) && blockIdx.x == 0;
-    auto stamp = [&](int slot) { if(tracing && slot < 64) prm.trace[slot] = global_timer_ns(); };
+    auto stamp = [&](int slot) { if(tracing && slot < 64) prm.trace[slot] = static_cast<unsigned long long>(clock64()); };
     if(threadIdx.x == 0) stamp(0);
 
     const int splits      = prm.splits;
@@ -212,15 +212,21 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                         break;
                     const uint32_t stage = smem_base + s * L.stage_bytes;
                     const uint32_t bar   = full_bar(s);
+                    if(g == 5) stamp(34);
                     mbar_arrive_expect_tx(bar, kTileP * kTileKBytes + q_box_bytes + sfp_bytes + sfq_bytes);
+                    if(g == 5) stamp(35);
                     issue_operand_load(prm.p_mode, stage, &map_p, bar, row_p0, it_beg + i);
+                    if(g == 5) stamp(36);
                     issue_operand_load(prm.q_mode, stage + L.q_off, &map_q, bar, row_q0, it_beg + i);
+                    if(g == 5) stamp(37);
                     if(kScaled)
                     {
                         tma_load_2d(stage + L.sfp_off, &map_sfp, bar, (it_beg + i) * kSfChunk, row_p0 >> 5);
+                        if(g == 5) stamp(38);
                         tma_load_2d(stage + L.sfq_off, &map_sfq, bar, (it_beg + i) * kSfChunk, sfq_g0);
+                        if(g == 5) stamp(39);
                     }
-                    if(g < 14) stamp(2 + 4 * g);
+                    if(g < 8) stamp(2 + 4 * g);
                 }
             }
             if(*abort_f)
@@ -284,7 +290,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                     if(!ok)
                         break;
                     tc_fence_after_sync();
-                    if(g < 14) stamp(5 + 4 * g);
+                    if(g < 8) stamp(5 + 4 * g);
                     const uint32_t stage = smem_base + s * L.stage_bytes;
                     const uint32_t tsfp  = tmem_base + prm.sf_tmem_base + s * prm.sf_cols;
                     const uint32_t tsfq  = tsfp + sfp_cols;
@@ -315,10 +321,12 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                                               tsfp + (k >> 1) * 4, tsfq + (k >> 1) * 4 * nq128);
                         }
                     }
+                    if(g == 5) stamp(42);
                     if(CG == 1)
                         tc_commit(empty_bar(s));
                     else
                         tc_commit_2cta(empty_bar(s), 3);
+                    if(g == 5) stamp(43);
                 }
                 if(ok)
                 {
@@ -382,7 +390,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                     ok = __all_sync(0xffffffffu, ok);
                     if(!ok)
                         break;
-                    if(warp == 2 && lane == 0 && g < 14) stamp(3 + 4 * g);
+                    if(warp == 2 && lane == 0 && g < 8) stamp(3 + 4 * g);
                     const uint8_t* stage = smem_gen + s * L.stage_bytes;
                     const uint32_t tsfp  = tlane + prm.sf_tmem_base + s * prm.sf_cols;
                     const uint32_t tsfq  = tsfp + sfp_cols;
@@ -447,7 +455,9 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                             }
                         }
                     }
+                    if(warp == 2 && lane == 0 && g == 5) stamp(40);
                     tmem_st_wait();
+                    if(warp == 2 && lane == 0 && g == 5) stamp(41);
                     tc_fence_before_sync();
                     __syncwarp();
                     if(lane == 0)
@@ -456,7 +466,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                             mbar_arrive_cluster(ready_remote + 8u * s);
                         else
                             mbar_arrive(ready_bar(s));
-                        if(warp == 2 && g < 14) stamp(4 + 4 * g);
+                        if(warp == 2 && g < 8) stamp(4 + 4 * g);
                     }
                 }
             }

@@ -416,7 +416,7 @@ static void launch_persistent_cg(int cg, int ctas, size_t smem, cudaStream_t str
 static void print_trace(DeviceState& st, const GemmProblem& prob, const KernelConfig& cfg, int tiles_p, int tiles_q, int splits,
                         int stages)
 {
-    // debugging aid: timestamp record of the first CTA, nanoseconds relative to kernel entry
+    // debugging aid: timestamp record of the first CTA, SM clock cycles relative to kernel entry
     unsigned long long t[64];
     B200_CUDA(cudaStreamSynchronize(prob.stream));
     B200_CUDA(cudaMemcpy(t, st.trace, sizeof(t), cudaMemcpyDeviceToHost));

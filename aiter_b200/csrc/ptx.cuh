@@ -180,7 +180,9 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t ran
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
 {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    // default semantics (release at CTA scope): what travels with this arrival is ordered by the tcgen05
+    // fences / the async proxy, not by generic-proxy memory, so no cluster-scope fence is paid for
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 // cta_group::2 forms (issued by one warp / thread of the pair's CTAs as noted at the call sites)
