@@ -77,6 +77,7 @@ SIGNATURES = {
     "gemm_a16w16_asm": (T, T, T, T, T, I, S, I),
     "opus_gemm_a16w16_tune": (T, T, T, T, I, I),
     "opus_gemm": (T, T, T, T, T, T, T),
+    "aiter_b200_gemm_a8w8_mxfp8_noalloc": (T, T, T, T, T, I, I),
 }
 EXPORTS = sorted(
     list(SIGNATURES)

@@ -8,7 +8,7 @@ import sys
 
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
 LIB_PATH = os.path.join(CSRC, "libaiter_b200.so")
-SOURCES = ["abi.cu", "launch.cu"]
+SOURCES = ["abi.cu", "launch.cu", "noalloc.cu"]
 PUBLIC_HEADER = os.path.join("..", "..", "include", "aiter_b200.h")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -11,6 +11,9 @@ using namespace b200;
 static thread_local std::string g_last_error;
 static thread_local std::string g_heuristic_name;
 
+// used by entry points that live in other translation units
+void aiter_b200_set_last_error(const std::string& msg) { g_last_error = msg; }
+
 template <typename Fn>
 static int safe_call(Fn&& fn)
 {

@@ -449,7 +449,19 @@ void launch_gemm(const GemmProblem& prob)
     } restore{prev_dev, prob.device};
 
     std::lock_guard<std::mutex> lk(g_mutex);
-    DeviceState& st = device_state(prob.device);
+    // With caller-provided scratch nothing may be allocated: the device facts come from attribute queries and
+    // the library's own per-device record (which owns a cudaMalloc'ed status buffer) is left alone.
+    DeviceState local_state;
+    if(prob.scratch != nullptr)
+    {
+        B200_CUDA(cudaDeviceGetAttribute(&local_state.sm_count, cudaDevAttrMultiProcessorCount, prob.device));
+        B200_CUDA(cudaDeviceGetAttribute(&local_state.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, prob.device));
+        int cc_major = 0;
+        B200_CUDA(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, prob.device));
+        B200_CHECK(cc_major == 10, "this library only runs on sm_100 class GPUs");
+        local_state.status = prob.scratch->status;
+    }
+    DeviceState& st = (prob.scratch != nullptr) ? local_state : device_state(prob.device);
 
     KernelConfig cfg = prob.cfg;
     if(use_v1())
@@ -487,12 +499,13 @@ void launch_gemm(const GemmProblem& prob)
     const int tiles_p = static_cast<int>((P.rows + tile_rows_p - 1) / tile_rows_p);
     const int tiles_q = static_cast<int>((Q.rows + cfg.bn - 1) / cfg.bn);
     B200_CHECK(tiles_q <= 65535 && splits <= 65535, "grid too large");
-    B200_CHECK(splits == 1 || static_cast<long long>(tiles_p) * tiles_q * cg <= kCounterSlots,
-               "split-K supports at most ", kCounterSlots, " output tiles");
+    const int counter_slots = (prob.scratch != nullptr) ? prob.scratch->counter_slots : kCounterSlots;
+    B200_CHECK(splits == 1 || static_cast<long long>(tiles_p) * tiles_q * cg <= counter_slots,
+               "split-K supports at most ", counter_slots, " output tiles here");
 
     static const bool trace_on = (std::getenv("AITER_B200_TRACE") != nullptr);
     unsigned long long* trace = nullptr;
-    if(trace_on)
+    if(trace_on && prob.scratch == nullptr)
     {
         if(st.trace == nullptr)
             B200_CUDA(cudaMalloc(&st.trace, 64 * sizeof(unsigned long long)));
@@ -505,9 +518,19 @@ void launch_gemm(const GemmProblem& prob)
     if(splits > 1)
     {
         const size_t bytes = static_cast<size_t>(tiles_p) * tiles_q * cg * splits * static_cast<size_t>(cfg.bn) * kTileP * sizeof(float);
-        StreamWorkspace& w = stream_workspace(st, prob.stream, bytes);
-        ws_partial         = w.partial;
-        ws_counter         = w.counter;
+        if(prob.scratch != nullptr)
+        {
+            B200_CHECK(bytes <= prob.scratch->partial_bytes, "this shape needs ", bytes, " bytes of split-K scratch, more than the ",
+                       prob.scratch->partial_bytes, " bytes of static scratch this entry point owns");
+            ws_partial = prob.scratch->partial;
+            ws_counter = prob.scratch->counter;
+        }
+        else
+        {
+            StreamWorkspace& w = stream_workspace(st, prob.stream, bytes);
+            ws_partial         = w.partial;
+            ws_counter         = w.counter;
+        }
     }
 
     // tensor maps: every CTA stages 128 rows of P and bn / cg rows of Q per K tile

@@ -65,6 +65,17 @@ struct KernelConfig
     int cg = 0;      // CTAs per tile: 1, or 2 (a 256-row tile on a CTA pair); 0: choose
 };
 
+// Caller-provided scratch for a launch that must not allocate: split-K partials, ticket counters and the
+// status record all live in memory the caller already owns.
+struct ExternalScratch
+{
+    float* partial          = nullptr;
+    size_t partial_bytes    = 0;
+    unsigned int* counter   = nullptr; // zero before the launch
+    int counter_slots       = 0;
+    unsigned int* status    = nullptr; // 4 words
+};
+
 struct GemmProblem
 {
     int kind = PK_BF16;
@@ -79,6 +90,7 @@ struct GemmProblem
     int device = 0;
     cudaStream_t stream = nullptr;
     KernelConfig cfg;
+    const ExternalScratch* scratch = nullptr; // null: the library's own per-device / per-stream buffers
 };
 
 // Fills the unset fields of cfg with the heuristic choice for (kind, M, N, K).

@@ -26,3 +26,16 @@ def gemm_a8w8_mxfp8(A: Tensor, B: Tensor, ScaleA: Tensor, ScaleB: Tensor, dtype:
             kernelName = cfg.get("kernelName") or ""
     _ffi.call("mxfp8_mxfp8_gemm_asm", A, B, ScaleA, ScaleB, out, kernelName if kernelName else None, int(bool(a_preshuffle)))
     return out
+
+
+def gemm_a8w8_mxfp8_noalloc(A: Tensor, B: Tensor, ScaleA: Tensor, ScaleB: Tensor, out: Tensor, a_preshuffle: bool = True,
+                            log2_k_split: int | None = None) -> Tensor:
+    """Same GEMM as gemm_a8w8_mxfp8, for callers that may not allocate device memory: `out` [M,N] bf16 is
+    supplied by the caller, and the library keeps its split-K partial sums, tickets and status record in a
+    fixed 8 MiB + 32 KiB array that is part of its image instead of cudaMalloc'ing them.  Think of a server
+    that gave all memory to one arena at start-up, or a plugin that must not touch its host's allocator.
+    Shapes whose split-K scratch would not fit raise RuntimeError.  Make the first call on a device before any
+    CUDA-graph capture; calls that overlap on the GPU share (and race on) the one array."""
+    _ffi.call("aiter_b200_gemm_a8w8_mxfp8_noalloc", A, B, ScaleA, ScaleB, out, int(bool(a_preshuffle)),
+              -1 if log2_k_split is None else int(log2_k_split))
+    return out

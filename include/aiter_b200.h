@@ -111,6 +111,18 @@ AITER_B200_API int opus_gemm(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tenso
                              aiter_tensor_t* bias, void* stream);
 AITER_B200_API int opus_gemm_workspace_init(void);
 
+/* ---- MXFP8 x MXFP8 -> bf16 without any device allocation.  No counterpart in the reference.
+ * For callers that must not call cudaMalloc (a pre-sized arena, a plugin that may not touch the host's
+ * allocator, a latency-critical loop): same arguments and results as mxfp8_mxfp8_gemm_asm, but the split-K
+ * partial sums, ticket counters and status record live in a fixed 8 MiB + 32 KiB array inside the library
+ * image (held by every GPU that loads the library until the process exits).  A shape whose split-K partials
+ * exceed 8 MiB, or that has more than 4096 output tiles under split-K, is refused with an error.  The first
+ * call on a device looks up the array's address (no allocation) and should be made before any stream
+ * capture.  All calls share the array: calls that overlap on the GPU race. log2_k_split < 0: library's choice. */
+AITER_B200_API int aiter_b200_gemm_a8w8_mxfp8_noalloc(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* ScaleA,
+                                                      aiter_tensor_t* ScaleB, aiter_tensor_t* out, int a_preshuffle,
+                                                      int log2_k_split, void* stream);
+
 /* ---- library state ---- */
 /* Copies the 4-word device status record of `device` (0 = healthy; non-zero = a bounded wait
  * inside a kernel expired: code, block, split, iteration) and clears it.  Synchronises the device. */
