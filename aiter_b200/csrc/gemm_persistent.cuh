@@ -40,6 +40,7 @@ struct PersistentParams
     int stages;
     int p_mode, q_mode;
     int sf_groups_p, sf_groups_q; // 32-row scale groups staged per CTA per stage
+    int f4_operand;               // mixed kind only: which operand arrives as packed e2m1 (1 = P, 2 = Q)
     int transposed_out;
     int tiles_p, tiles_q, splits; // tiles_p counts 128*CG-row tiles
     int n_acc;                    // accumulators in TMEM (1 or 2)
@@ -61,10 +62,11 @@ struct PersistentParams
 
 struct PersistentSmem
 {
-    uint32_t stage_bytes, q_off, sfp_off, sfq_off, bar_off, total;
+    uint32_t stage_bytes, q_off, sfp_off, sfq_off, stg_off, bar_off, total;
 };
 
-__host__ __device__ inline PersistentSmem make_persistent_smem(int kind, int bn, int cg, int stages)
+// f4_operand: 0 none, 1 = P, 2 = Q arrives as packed e2m1 and needs a staging area of rows x 64 bytes
+__host__ __device__ inline PersistentSmem make_persistent_smem(int kind, int bn, int cg, int stages, int f4_operand = 0)
 {
     PersistentSmem L;
     uint32_t q_bytes = static_cast<uint32_t>(bn / cg) * kTileKBytes;
@@ -72,10 +74,25 @@ __host__ __device__ inline PersistentSmem make_persistent_smem(int kind, int bn,
     L.q_off          = kTileP * kTileKBytes;
     L.sfp_off        = L.q_off + q_bytes;
     L.sfq_off        = L.sfp_off + (kind == KIND_BF16 ? 0u : 1024u);
-    L.stage_bytes    = L.sfq_off + (kind == KIND_BF16 ? 0u : 2048u);
+    L.stg_off        = L.sfq_off + (kind == KIND_BF16 ? 0u : 2048u);
+    uint32_t stg     = f4_operand == 1 ? kTileP * 64u : (f4_operand == 2 ? static_cast<uint32_t>(bn / cg) * 64u : 0u);
+    stg              = (stg + 1023u) & ~1023u;
+    L.stage_bytes    = L.stg_off + stg;
     L.bar_off        = L.stage_bytes * static_cast<uint32_t>(stages);
     L.total          = L.bar_off + 512u;
     return L;
+}
+
+// 8 packed e2m1 codes (one 32-bit word, element n in nibble n) -> 8 e4m3 bytes (exact: every e2m1 value
+// is an e4m3 value).  Magnitude by table look-up (prmt), sign moved to bit 7 of each byte.
+__device__ __forceinline__ void e2m1x8_to_e4m3x8(uint32_t w, uint32_t& lo, uint32_t& hi)
+{
+    constexpr uint32_t kLutLo = 0x3C383000u; // 0, 0.5, 1, 1.5
+    constexpr uint32_t kLutHi = 0x4C484440u; // 2, 3, 4, 6
+    constexpr uint32_t kSign  = 0x00008000u; // byte 0 = 0x00, byte 1 = 0x80
+    lo = __byte_perm(kLutLo, kLutHi, w & 0x7777u) | __byte_perm(kSign, 0u, (w >> 3) & 0x1111u);
+    const uint32_t h = w >> 16;
+    hi = __byte_perm(kLutLo, kLutHi, h & 0x7777u) | __byte_perm(kSign, 0u, (h >> 3) & 0x1111u);
 }
 
 template <int KIND, int SFW, int CG>
@@ -85,6 +102,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                        const PersistentParams prm)
 {
     constexpr bool kScaled = (KIND != KIND_BF16);
+    constexpr bool kMixed  = (KIND == KIND_MXF8F4);
     constexpr int kAtomsK  = (KIND == KIND_MXF4) ? 2 : 1;
     constexpr int kSfChunk = (SFW == SFW_E8M0_SHUFFLE) ? 256 : 128 * kAtomsK;
 
@@ -93,7 +111,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     uint8_t* smem_gen        = smem_raw + (smem_base - smem_u32(smem_raw));
     const int bn             = prm.bn;
     const int S              = prm.stages;
-    const PersistentSmem L   = make_persistent_smem(KIND, bn, CG, S);
+    const PersistentSmem L   = make_persistent_smem(KIND, bn, CG, S, kMixed ? prm.f4_operand : 0);
 
     const uint32_t bar_base  = smem_base + L.bar_off;
     auto full_bar            = [&](int s) { return bar_base + 8u * s; };
@@ -213,11 +231,20 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                     const uint32_t stage = smem_base + s * L.stage_bytes;
                     const uint32_t bar   = full_bar(s);
                     if(g == 5) stamp(34);
-                    mbar_arrive_expect_tx(bar, kTileP * kTileKBytes + q_box_bytes + sfp_bytes + sfq_bytes);
+                    const bool p_f4 = kMixed && prm.f4_operand == 1, q_f4 = kMixed && prm.f4_operand == 2;
+                    mbar_arrive_expect_tx(bar, (p_f4 ? kTileP * 64u : kTileP * kTileKBytes) + (q_f4 ? q_box_bytes / 2 : q_box_bytes) +
+                                                   sfp_bytes + sfq_bytes);
                     if(g == 5) stamp(35);
-                    issue_operand_load(prm.p_mode, stage, &map_p, bar, row_p0, it_beg + i);
+                    // a packed e2m1 operand (always 16x16-byte tiled) lands in the staging area: 4 chunks of 16 bytes per row
+                    if(p_f4)
+                        tma_load_3d(stage + L.stg_off, &map_p, bar, 0, row_p0 >> 4, (it_beg + i) * 4);
+                    else
+                        issue_operand_load(prm.p_mode, stage, &map_p, bar, row_p0, it_beg + i);
                     if(g == 5) stamp(36);
-                    issue_operand_load(prm.q_mode, stage + L.q_off, &map_q, bar, row_q0, it_beg + i);
+                    if(q_f4)
+                        tma_load_3d(stage + L.stg_off, &map_q, bar, 0, row_q0 >> 4, (it_beg + i) * 4);
+                    else
+                        issue_operand_load(prm.q_mode, stage + L.q_off, &map_q, bar, row_q0, it_beg + i);
                     if(g == 5) stamp(37);
                     if(kScaled)
                     {
@@ -253,8 +280,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             uint32_t idesc;
             if(KIND == KIND_BF16)
                 idesc = idesc_bf16(kM, bn);
-            else if(KIND == KIND_MXF8)
-                idesc = idesc_block_scaled(0, 0, kM, bn);
+            else if(KIND == KIND_MXF8 || KIND == KIND_MXF8F4)
+                idesc = idesc_block_scaled(0, 0, kM, bn); // the e2m1 operand has been widened to e4m3 in shared memory
             else
                 idesc = idesc_block_scaled(1, 1, kM, bn);
             const bool p_tiled   = (prm.p_mode == OPM_TILE16);
@@ -304,7 +331,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                         {
                             if(KIND == KIND_BF16)
                                 mma_f16(d_col, pd, qd, idesc, acc);
-                            else if(KIND == KIND_MXF8)
+                            else if(KIND == KIND_MXF8 || KIND == KIND_MXF8F4)
                                 mma_mxf8f6f4(d_col, pd, qd, idesc_with_sf(idesc, k, k), acc, tsfp, tsfq);
                             else
                                 mma_mxf4(d_col, pd, qd, idesc_with_sf(idesc, (k & 1) * 2, (k & 1) * 2), acc,
@@ -314,7 +341,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                         {
                             if(KIND == KIND_BF16)
                                 mma_f16_2cta(d_col, pd, qd, idesc, acc);
-                            else if(KIND == KIND_MXF8)
+                            else if(KIND == KIND_MXF8 || KIND == KIND_MXF8F4)
                                 mma_mxf8f6f4_2cta(d_col, pd, qd, idesc_with_sf(idesc, k, k), acc, tsfp, tsfq);
                             else
                                 mma_mxf4_2cta(d_col, pd, qd, idesc_with_sf(idesc, (k & 1) * 2, (k & 1) * 2), acc,
@@ -391,9 +418,32 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                     if(!ok)
                         break;
                     if(warp == 2 && lane == 0 && g < 8) stamp(3 + 4 * g);
-                    const uint8_t* stage = smem_gen + s * L.stage_bytes;
+                    uint8_t* stage = smem_gen + s * L.stage_bytes;
                     const uint32_t tsfp  = tlane + prm.sf_tmem_base + s * prm.sf_cols;
                     const uint32_t tsfq  = tsfp + sfp_cols;
+                    if(kMixed)
+                    {
+                        // widen the packed e2m1 operand of this stage to e4m3 in the MMA's un-swizzled layout:
+                        // staging [4 chunks][rows][16 B] (32 codes) -> tile [8 chunks][rows][16 B]
+                        const int rows     = (prm.f4_operand == 1) ? kTileP : q_rows_cta;
+                        const uint4* src   = reinterpret_cast<const uint4*>(stage + L.stg_off);
+                        uint4* dst         = reinterpret_cast<uint4*>(stage + (prm.f4_operand == 1 ? 0u : L.q_off));
+                        const int items    = rows * 4;
+                        for(int it = (warp - 2) * 32 + lane; it < items; it += 128)
+                        {
+                            const int kc  = it / rows;
+                            const int r   = it - kc * rows;
+                            const uint4 v = src[it];
+                            uint4 o0, o1;
+                            e2m1x8_to_e4m3x8(v.x, o0.x, o0.y);
+                            e2m1x8_to_e4m3x8(v.y, o0.z, o0.w);
+                            e2m1x8_to_e4m3x8(v.z, o1.x, o1.y);
+                            e2m1x8_to_e4m3x8(v.w, o1.z, o1.w);
+                            dst[(2 * kc) * rows + r]     = o0;
+                            dst[(2 * kc + 1) * rows + r] = o1;
+                        }
+                        fence_proxy_async_smem(); // these generic-proxy writes are read by the tensor core
+                    }
                     for(int op = 0; op < 2; ++op)
                     {
                         const uint32_t* region = reinterpret_cast<const uint32_t*>(stage + (op == 0 ? L.sfp_off : L.sfq_off));

@@ -61,9 +61,11 @@ static CUtensorMap encode_map(const void* base, int rank, const cuuint64_t* dims
     return m;
 }
 
-// Operand tile map; box_rows rows by 128 bytes of K per load.
-static CUtensorMap operand_map(const Operand& op, int box_rows, const char* what)
+// Operand tile map; box_rows rows by box_kbytes (128, or 64 for a packed e2m1 operand of the mixed kind)
+// bytes of K per load.
+static CUtensorMap operand_map(const Operand& op, int box_rows, const char* what, int box_kbytes = kTileKBytes)
 {
+    B200_CHECK(box_kbytes == kTileKBytes || op.mode == OPM_TILE16, what, ": a packed e2m1 operand must be 16x16-byte tiled");
     B200_CHECK((reinterpret_cast<uintptr_t>(op.ptr) & 15) == 0, what, ": base address must be 16-byte aligned");
     if(op.mode == OPM_ROWMAJOR)
     {
@@ -83,7 +85,7 @@ static CUtensorMap operand_map(const Operand& op, int box_rows, const char* what
         // faster than the k-chunk index in the box.
         cuuint64_t dims[3]    = {256, static_cast<cuuint64_t>(op.rows / 16), static_cast<cuuint64_t>(op.kbytes / 16)};
         cuuint64_t strides[2] = {static_cast<cuuint64_t>(op.kbytes) * 16, 256};
-        cuuint32_t box[3]     = {256, static_cast<cuuint32_t>(box_rows / 16), kTileKBytes / 16};
+        cuuint32_t box[3]     = {256, static_cast<cuuint32_t>(box_rows / 16), static_cast<cuuint32_t>(box_kbytes / 16)};
         return encode_map(op.ptr, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, what);
     }
     B200_CHECK(op.mode == OPM_A2X128, what, ": unknown operand mode ", op.mode);
@@ -222,6 +224,7 @@ static int kernel_kind_of(int problem_kind)
     case PK_BF16: return KIND_BF16;
     case PK_MXFP8: return KIND_MXF8;
     case PK_MXFP4: return KIND_MXF4;
+    case PK_MXF8F4: return KIND_MXF8F4;
     default: fail("problem kind ", problem_kind, " has no kernel in this build");
     }
 }
@@ -232,12 +235,12 @@ static bool use_v1()
     return v1;
 }
 
-static int max_stages(int kernel_kind, int bn, int cg, int smem_limit)
+static int max_stages(int kernel_kind, int bn, int cg, int smem_limit, int f4_operand = 0)
 {
     for(int s = kMaxStages; s >= 1; --s)
     {
         const int total = use_v1() ? static_cast<int>(make_smem_layout(kernel_kind, bn, s).total)
-                                   : static_cast<int>(make_persistent_smem(kernel_kind, bn, cg, s).total);
+                                   : static_cast<int>(make_persistent_smem(kernel_kind, bn, cg, s, f4_operand).total);
         if(total + 1024 <= smem_limit)
             return s;
     }
@@ -284,8 +287,8 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
     }
     if(cfg.stages <= 0)
     {
-        const int kk = (kind == PK_BF16) ? KIND_BF16 : (kind == PK_MXFP4 ? KIND_MXF4 : KIND_MXF8);
-        int s        = max_stages(kk, cfg.bn, cfg.cg, 227 * 1024);
+        const int kk = (kind == PK_BF16) ? KIND_BF16 : (kind == PK_MXFP4 ? KIND_MXF4 : (kind == PK_MXF8F4 ? KIND_MXF8F4 : KIND_MXF8));
+        int s        = max_stages(kk, cfg.bn, cfg.cg, 227 * 1024, kind == PK_MXF8F4 ? (cfg.swap ? 1 : 2) : 0);
         cfg.stages   = s > kMaxStages ? kMaxStages : s;
     }
 }
@@ -480,18 +483,24 @@ void launch_gemm(const GemmProblem& prob)
     const Operand& Q       = cfg.swap ? prob.act : prob.wgt;
     const ScaleOperand& SP = cfg.swap ? prob.wgt_sf : prob.act_sf;
     const ScaleOperand& SQ = cfg.swap ? prob.act_sf : prob.wgt_sf;
-    B200_CHECK(P.kbytes == Q.kbytes, "operands disagree on K bytes: ", P.kbytes, " vs ", Q.kbytes);
+    const bool mixed     = (kkind == KIND_MXF8F4);
+    const int f4_operand = mixed ? (cfg.swap ? 1 : 2) : 0; // the weight is the packed e2m1 operand
+    if(mixed)
+        B200_CHECK(prob.act.kbytes == 2 * prob.wgt.kbytes && prob.wgt.mode == OPM_TILE16 && !use_v1(),
+                   "mixed MXFP8 x MXFP4: the weight must be packed e2m1 in the 16x16-byte tiled layout");
+    else
+        B200_CHECK(P.kbytes == Q.kbytes, "operands disagree on K bytes: ", P.kbytes, " vs ", Q.kbytes);
     B200_CHECK(cfg.bn % 32 == 0 || Q.rows <= cfg.bn, "a tile width of ", cfg.bn,
                " only serves problems with at most that many rows on that side");
 
-    const int num_k_iters = static_cast<int>((P.kbytes + kTileKBytes - 1) / kTileKBytes);
+    const int num_k_iters = static_cast<int>((prob.act.kbytes + kTileKBytes - 1) / kTileKBytes);
     int splits            = 1 << cfg.log2_splitk;
     while(splits > num_k_iters)
         splits >>= 1;
     const int atoms_k  = (kkind == KIND_MXF4) ? 2 : 1;
     const int nq128    = (cfg.bn + 127) / 128;
     const int sf_cols  = (kkind == KIND_BF16) ? 0 : (4 * atoms_k + 4 * atoms_k * nq128);
-    const int max_st = max_stages(kkind, cfg.bn, cg, st.smem_optin);
+    const int max_st = max_stages(kkind, cfg.bn, cg, st.smem_optin, f4_operand);
     B200_CHECK(max_st >= 2, "tile ", 128 * cg, "x", cfg.bn, " does not fit in shared memory");
     int stages = cfg.stages <= 0 ? max_st : std::min(cfg.stages, max_st);
 
@@ -535,8 +544,8 @@ void launch_gemm(const GemmProblem& prob)
 
     // tensor maps: every CTA stages 128 rows of P and bn / cg rows of Q per K tile
     const int sf_groups_q = (cfg.bn + 31) / 32;
-    CUtensorMap mp  = operand_map(P, kTileP, cfg.swap ? "weight operand" : "activation operand");
-    CUtensorMap mq  = operand_map(Q, cfg.bn / cg, cfg.swap ? "activation operand" : "weight operand");
+    CUtensorMap mp  = operand_map(P, kTileP, cfg.swap ? "weight operand" : "activation operand", f4_operand == 1 ? 64 : kTileKBytes);
+    CUtensorMap mq  = operand_map(Q, cfg.bn / cg, cfg.swap ? "activation operand" : "weight operand", f4_operand == 2 ? 64 : kTileKBytes);
     CUtensorMap msp = mp, msq = mq;
     int sfw = SFW_NONE;
     const int kblocks = static_cast<int>(prob.K / 32);
@@ -615,6 +624,7 @@ void launch_gemm(const GemmProblem& prob)
         prm.q_mode         = Q.mode;
         prm.sf_groups_p    = 4;
         prm.sf_groups_q    = sf_groups_q;
+        prm.f4_operand     = f4_operand;
         prm.transposed_out = cfg.swap;
         prm.tiles_p        = tiles_p;
         prm.tiles_q        = tiles_q;
@@ -646,7 +656,7 @@ void launch_gemm(const GemmProblem& prob)
         while(cols < prm.sf_tmem_base + stages * sf_cols)
             cols <<= 1;
         prm.tmem_cols = cols;
-        const PersistentSmem L = make_persistent_smem(kkind, cfg.bn, cg, stages);
+        const PersistentSmem L = make_persistent_smem(kkind, cfg.bn, cg, stages, f4_operand);
         const size_t smem      = L.total + 1024;
         const int ctas         = clusters * cg;
         if(kkind == KIND_BF16)
@@ -657,6 +667,8 @@ void launch_gemm(const GemmProblem& prob)
             launch_persistent_cg<KIND_MXF4, SFW_E8M0_SHUFFLE>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
         else if(kkind == KIND_MXF4 && sfw == SFW_G1250)
             launch_persistent_cg<KIND_MXF4, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
+        else if(kkind == KIND_MXF8F4 && sfw == SFW_G1250)
+            launch_persistent_cg<KIND_MXF8F4, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
         else
             fail("no kernel instance for kind ", kkind, " with scale layout ", sfw);
     }

@@ -203,6 +203,81 @@ def test_mxfp4_g1250_scale_layout(ab):
     assert_healthy(ab)
 
 
+# ------------------------------------------------------------------------------------------- mixed MXFP8 x MXFP4
+def a8w4_case(ab, M, N, K, apre, seed=0):
+    x, w = randn_bf16(M, K, seed + 1), randn_bf16(N, K, seed + 2)
+    xq, xs = quant_fp8(x)
+    wq, ws = quant_fp4(w)
+    ref = ox.gemm_a8w4_mxfp8_ref(xq, wq, xs, ws)
+    A = to_cuda_u8(xq, torch.float8_e4m3fn)
+    if apre:
+        A = ab.shuffle_mxfp8fp4_a(A)
+    B = ab.shuffle_mxfp8fp4_b(to_cuda_u8(wq))
+    return ref, (A, B, ab.shuffle_mxfp8fp4_scale(to_cuda_u8(xs)), ab.shuffle_mxfp8fp4_scale(to_cuda_u8(ws)))
+
+
+@pytest.mark.parametrize("M,N,K,apre", [
+    (1, 256, 128, 0), (2, 512, 1024, 1), (16, 512, 1024, 0), (64, 1024, 2048, 1), (128, 8192, 8192, 1), (300, 1024, 2048, 0),
+    (1024, 2048, 1024, 1), (130, 304, 640, 1),
+])
+def test_a8w4_mxfp8(ab, M, N, K, apre):
+    ref, args = a8w4_case(ab, M, N, K, apre, seed=13)
+    out = ab.gemm_a8w4_mxfp8(*args, a_preshuffle=bool(apre))
+    assert out.shape == (M, N) and out.dtype == torch.bfloat16
+    check(ref, out, what=f"gemm_a8w4_mxfp8 {M}x{N}x{K} apre={apre}")
+    assert_healthy(ab)
+
+
+@pytest.mark.parametrize("name", ["tc5_128x16_t_s4", "tc5_128x64_t_s3", "tc5_128x128_n_s4", "tc5_128x256_n_s3", "tc5_256x256_n_s4",
+                                  "tc5_256x128_n_s5", "tc5_256x192_n_s4"])
+def test_a8w4_every_tile_shape(ab, name):
+    M = 16 if "x16_" in name else (600 if name.startswith("tc5_256") else 64 if "_t_" in name else 200)
+    ref, args = a8w4_case(ab, M, 768, 1536, 0, seed=15)
+    out = ab.gemm_a8w4_mxfp8(*args, a_preshuffle=False, kernelName=name)
+    check(ref, out, what=name)
+    assert_healthy(ab)
+
+
+def test_a8w4_constant_known_answer(ab):
+    # A = 0.5 (e4m3), B nibbles 0x1 = 0.5 (e2m1), unit scales: every output is 0.25 * K
+    M, N, K = 32, 256, 512
+    A = torch.full((M, K), 0.5).to(torch.float8_e4m3fn).cuda()
+    B = ab.shuffle_mxfp8fp4_b(torch.full((N, K // 2), 0x11, dtype=torch.uint8).cuda())
+    sa = ab.shuffle_mxfp8fp4_scale(torch.full((M, K // 32), 0x7F, dtype=torch.uint8).cuda())
+    sb = ab.shuffle_mxfp8fp4_scale(torch.full((N, K // 32), 0x7F, dtype=torch.uint8).cuda())
+    out = ab.gemm_a8w4_mxfp8(A, B, sa, sb, a_preshuffle=False)
+    assert (out.float() == 0.25 * K).all()
+    assert_healthy(ab)
+
+
+def test_a8w4_table_dispatch(ab, tmp_path, monkeypatch):
+    # the (M,N,K) table chooses the kernel: a row naming a tile that cannot exist must surface as an error,
+    # a valid row must be honoured, and an untuned shape must still run (heuristic)
+    from aiter_b200 import gemm_op_a8w4
+    from aiter_b200.config import get_cu_num, get_gfx
+
+    csv = tmp_path / "a8w4.csv"
+    csv.write_text(
+        "gfx,cu_num,M,N,K,kernelId,splitK,us,kernelName,tflops,bw,errRatio\n"
+        f"{get_gfx()},{get_cu_num()},32,512,1024,0,0,1.0,tc5_128x32_t_s4,0,0,0\n"
+        f"{get_gfx()},{get_cu_num()},48,512,1024,0,0,1.0,tc5_128x999_t_s4,0,0,0\n")
+    monkeypatch.setenv("AITER_CONFIG_GEMM_A8W4_MXFP8", str(csv))
+    gemm_op_a8w4._table.clear()
+    try:
+        assert gemm_op_a8w4.get_A8W4_config(32, 512, 1024)["kernelName"] == "tc5_128x32_t_s4"
+        assert gemm_op_a8w4.get_A8W4_config(17, 512, 1024)["kernelName"] == "tc5_128x32_t_s4"  # padded M (gl=0: 32)
+        ref, args = a8w4_case(ab, 32, 512, 1024, 0, seed=17)
+        check(ref, ab.gemm_a8w4_mxfp8(*args, a_preshuffle=False), what="table row honoured")
+        ref, args = a8w4_case(ab, 48, 512, 1024, 0, seed=18)
+        with pytest.raises(RuntimeError, match="not find kernel"):
+            ab.gemm_a8w4_mxfp8(*args, a_preshuffle=False)
+        ref, args = a8w4_case(ab, 100, 512, 1024, 0, seed=19)
+        check(ref, ab.gemm_a8w4_mxfp8(*args, a_preshuffle=False), what="untuned shape")
+    finally:
+        gemm_op_a8w4._table.clear()
+    assert_healthy(ab)
+
+
 # ------------------------------------------------------------------------------------------- persistent paths
 def test_many_units_per_cta(ab):
     # more output tiles than SMs: the persistent loop, both accumulators and the stage ring wrap many times
