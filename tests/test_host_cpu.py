@@ -1,0 +1,167 @@
+"""Host-side logic that needs no GPU: the library loads and exports every declared symbol, the torch
+host functions reproduce the reference-generated golden vectors bit for bit, errors cross the C ABI as
+RuntimeError, and the tuned-table look-up follows the reference's rules."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def ab():
+    import aiter_b200
+
+    return aiter_b200
+
+
+def test_library_exports_every_declared_symbol(ab):
+    header = open(os.path.join(ROOT, "include", "aiter_b200.h")).read()
+    declared = re.findall(r"AITER_B200_API\s+[\w\s\*]+?\b(\w+)\s*\(", header)
+    assert len(declared) >= 18, declared
+    lib = ctypes.CDLL(ab._ffi.LIB_PATH)
+    missing = [name for name in declared if not hasattr(lib, name)]
+    assert not missing, f"declared in include/aiter_b200.h but not exported: {missing}"
+    assert lib.aiter_ctypes_abi_version() == 2
+    assert set(ab._ffi.SIGNATURES) <= set(declared)
+
+
+def test_struct_layout_matches_header(ab):
+    assert ctypes.sizeof(ab._ffi.aiter_tensor_t) == 160
+    t = ab._ffi.torch_to_aiter(torch.zeros(3, 5, dtype=torch.bfloat16)[:, 1:4])
+    assert (t.ndim, t.shape[0], t.shape[1], t.strides[0], t.strides[1], t.dtype_, t.device_id) == (2, 3, 3, 5, 1, 3, -1)
+    assert ab.dtypes.aiter_dtype_id(torch.uint8) == 11 and ab.dtypes.aiter_dtype_id(ab.dtypes.fp4x2) == 6
+
+
+def test_padded_m_matches_oracle(ab):
+    from oracle import mx_oracle as ox
+
+    for m in (1, 15, 16, 17, 255, 256, 257, 1000, 1024, 1025, 4095, 4097, 8191, 8193, 20000):
+        for n in (1024, 4096, 8192):
+            for gl in (0, 1):
+                assert ab.get_padded_m(m, n, 4096, gl) == ox.get_padded_m(m, n, 4096, gl), (m, n, gl)
+
+
+def test_errors_cross_the_abi_as_runtime_error(ab):
+    a = torch.zeros((4, 128), dtype=torch.float8_e4m3fn)
+    s = torch.zeros((32, 4), dtype=torch.uint8)
+    with pytest.raises(RuntimeError, match="mxfp8_mxfp8_gemm_asm failed: .*must live on a GPU"):
+        ab.gemm_a8w8_mxfp8(a, a, s, s, a_preshuffle=False)  # CPU tensors are refused before any launch
+    with pytest.raises(RuntimeError, match="opus_gemm_a16w16_tune failed: .*XQ must live on a GPU"):
+        x = torch.zeros((1, 4, 64), dtype=torch.bfloat16)
+        ab.opus_gemm_a16w16_tune(x, x, torch.zeros((1, 4, 4), dtype=torch.bfloat16), None, 999, 0)
+    with pytest.raises(ValueError, match="must be 3D"):
+        ab.opus_gemm_a16w16_tune(torch.zeros(4, 64), torch.zeros(4, 64), torch.zeros(4, 4))
+
+
+def test_heuristic_and_kernel_menu(ab):
+    name, l2 = ab.heuristic_name(1, 8192, 4096, 4096)
+    assert name.startswith("tc5_256x") and l2 == 0  # tall problems run on CTA pairs
+    name, l2 = ab.heuristic_name(2, 1, 7168, 16384)
+    assert "_t_" in name and l2 >= 1  # decode shapes: weights on the 128-row slot, K split
+    assert "kernelId" in ab.kernel_list()
+
+
+def test_host_numerics_against_golden(ab, golden):
+    x = torch.from_numpy(golden["quant_in_bf16"].view(np.int16).copy()).view(torch.bfloat16)
+    q4, s4 = ab.per_1x32_f4_quant(x)
+    assert np.array_equal(q4.view(torch.uint8).numpy(), golden["quant_fp4_data"])
+    assert np.array_equal(s4.view(torch.uint8).numpy(), golden["quant_fp4_scale"])
+    q8, s8 = ab.per_1x32_f8_scale_f8_quant(x, scale_type=ab.dtypes.fp8_e8m0)
+    assert np.array_equal(q8.view(torch.uint8).numpy(), golden["quant_fp8_data"])
+    assert np.array_equal(s8.view(torch.uint8).numpy(), golden["quant_fp8_scale"])
+    assert np.array_equal(ab.fp4_utils.f32_to_e2m1_code(torch.from_numpy(golden["e2m1_probe_in"])).numpy(), golden["e2m1_probe_out"])
+    amax = torch.from_numpy(golden["amax_in"])
+    assert np.array_equal(ab.fp4_utils.f32_to_mx_e8m0_scale(amax, dtype=ab.MxDtype.FP4_E2M1).view(torch.uint8).numpy(), golden["amax_e8m0_fp4"])
+    assert np.array_equal(ab.fp4_utils.f32_to_mx_e8m0_scale(amax, dtype=ab.MxDtype.FP8_E4M3).view(torch.uint8).numpy(), golden["amax_e8m0_fp8"])
+    assert np.array_equal(ab.fp4_utils.mxfp4_to_f32(torch.arange(256, dtype=torch.uint8).view(-1, 1)).numpy().view(np.uint32),
+                          golden["e2m1_lut"].view(np.uint32))
+    assert ab.get_torch_quant(ab.QuantType.per_1x32) is ab.per_1x32_f4_quant
+
+
+def test_shuffles_against_golden(ab, golden):
+    t = torch.from_numpy
+    w = ab.shuffle_weight(t(golden["shufw_u8_in"]))
+    assert w.is_shuffled and np.array_equal(w.numpy(), golden["shufw_u8_out"])
+    assert np.array_equal(ab.shuffle_weight(t(golden["shufw_i16_in"])).numpy(), golden["shufw_i16_out"])
+    assert np.array_equal(ab.shuffle_scale(t(golden["shufs_in"])).numpy(), golden["shufs_out"])
+    ragged = ab.shuffle_scale(t(golden["shufs_ragged_in"])).numpy()
+    src = golden["shufs_ragged_in"]
+    from oracle import mx_oracle as ox
+
+    mm, kk = np.meshgrid(np.arange(src.shape[0]), np.arange(src.shape[1]), indexing="ij")
+    assert np.array_equal(ragged.reshape(-1)[ox.e8m0_shuffle_offset(mm, kk, ragged.shape[1])], src)  # valid slots
+    assert np.array_equal(ab.shuffle_mxfp8fp4_a(t(golden["g1250_a_in"])).numpy(), golden["g1250_a_out"])
+    assert np.array_equal(ab.shuffle_mxfp8fp4_b(t(golden["g1250_b_in"])).numpy(), golden["g1250_b_out"])
+    assert np.array_equal(ab.shuffle_mxfp8fp4_scale(t(golden["g1250_s_in"])).numpy(), golden["g1250_s_out"])
+    with pytest.raises(AssertionError):
+        ab.shuffle_weight(torch.zeros(8, 64, dtype=torch.uint8))  # N not a multiple of 16
+
+
+def _write_csv(path, rows, header="gfx,cu_num,M,N,K,kernelId,splitK,us,kernelName,tflops,bw,errRatio"):
+    path.write_text(header + "\n" + "\n".join(rows) + "\n")
+
+
+def test_table_lookup_rules(ab, tmp_path, monkeypatch):
+    """The (gfx, cu_num, M, N, K) key: other targets' rows are ignored, padded-M buckets are tried after the
+    exact M, merged files keep the fastest row, a legacy file without `gfx` falls back to a cu_num-only key,
+    and edits take effect after a cache clear (reference: op_tests/test_gemm_codegen.py:292-390)."""
+    from aiter_b200.config import TunedTable, get_cu_num, get_gfx
+
+    gfx, cu = get_gfx(), get_cu_num()
+    f1, f2 = tmp_path / "a.csv", tmp_path / "b.csv"
+    _write_csv(f1, [f"{gfx},{cu},64,4096,4096,0,1,9.0,tc5_128x64_t_s4,0,0,0",
+                    f"gfx950,256,1,4096,4096,0,3,1.0,amd_kernel,0,0,0",
+                    f"{gfx},{cu},128,4096,4096,0,0,5.0,tc5_128x128_n_s4,0,0,0"])
+    _write_csv(f2, [f"{gfx},{cu},64,4096,4096,0,2,3.0,tc5_128x64_t_s6,0,0,0"])
+    monkeypatch.setenv("AITER_CONFIG_GEMM_A4W4", f"{f1}{os.pathsep}{f2}{os.pathsep}{tmp_path / 'missing.csv'}")
+    table = TunedTable("a4w4")
+    assert table.lookup(64, 4096, 4096)["kernelName"] == "tc5_128x64_t_s6"  # lowest `us` wins across files
+    assert table.lookup(50, 4096, 4096)["kernelName"] == "tc5_128x64_t_s6"  # gl=0 bucket: 50 -> 64
+    assert table.lookup(100, 4096, 4096)["kernelName"] == "tc5_128x128_n_s4"  # 100 -> 112 (miss) -> 128 (gl=1)
+    assert table.lookup(1, 4096, 4096) is None  # the row tuned for another target (gfx950, 256 CUs) is ignored
+    assert table.lookup(64, 4096, 1024) is None  # untuned shape: the caller falls back to the heuristic
+
+    # edits take effect after a cache clear, without rebuilding anything
+    _write_csv(f2, [f"{gfx},{cu},64,4096,4096,0,2,3.0,tc5_128x32_t_s8,0,0,0"])
+    assert table.lookup(64, 4096, 4096)["kernelName"] == "tc5_128x64_t_s6"
+    table.clear()
+    assert table.lookup(64, 4096, 4096)["kernelName"] == "tc5_128x32_t_s8"
+
+    # legacy schema without a gfx column: cu_num-only key
+    legacy = tmp_path / "legacy.csv"
+    _write_csv(legacy, [f"{cu},32,512,512,0,0,1.0,tc5_128x32_t_s4,0,0,0"],
+               header="cu_num,M,N,K,kernelId,splitK,us,kernelName,tflops,bw,errRatio")
+    monkeypatch.setenv("AITER_CONFIG_GEMM_A4W4", str(legacy))
+    table.clear()
+    assert table.lookup(32, 512, 512)["kernelName"] == "tc5_128x32_t_s4"
+
+
+def test_a4w4_forwards_table_row_to_the_entry_point(ab, tmp_path, monkeypatch):
+    """kernelName and splitK of the tuned row are forwarded verbatim; no row -> no kernel name and the
+    library's own split choice (reference: op_tests/test_gemm_codegen.py:468-682)."""
+    from aiter_b200 import gemm_op_a4w4
+    from aiter_b200.config import get_cu_num, get_gfx
+
+    csv = tmp_path / "a4w4.csv"
+    _write_csv(csv, [f"{get_gfx()},{get_cu_num()},32,256,512,0,2,1.0,tc5_128x32_t_s4,0,0,0"])
+    monkeypatch.setenv("AITER_CONFIG_GEMM_A4W4", str(csv))
+    gemm_op_a4w4._table.clear()
+    calls = []
+    monkeypatch.setattr(gemm_op_a4w4._ffi, "call", lambda name, *args: calls.append((name, args)))
+    A = torch.zeros((32, 256), dtype=torch.uint8)
+    B = torch.zeros((256, 256), dtype=torch.uint8)
+    S = torch.zeros((256, 16), dtype=torch.uint8)
+    out = ab.gemm_a4w4(A, B, S, S)
+    assert out.shape == (32, 256)
+    name, args = calls[-1]
+    assert name == "gemm_a4w4_asm" and args[5] == "tc5_128x32_t_s4" and args[10] == 2 and args[9] == 1
+    assert args[4].shape == (32, 256)  # output rows padded to a multiple of 32
+    ab.gemm_a4w4(torch.zeros((5, 256), dtype=torch.uint8), B, S, S)  # untuned M bucket
+    name, args = calls[-1]
+    assert args[5] is None and args[10] == -1 and args[4].shape == (32, 256)
+    gemm_op_a4w4._table.clear()
