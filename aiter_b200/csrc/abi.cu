@@ -1,6 +1,6 @@
 // extern "C" entry points: argument checking, aiter_tensor_t -> GemmProblem, error bridge.
 #include "../../include/aiter_b200.h"
-#include "gemm_kernel.cuh"
+#include "gemm_common.cuh"
 #include "launch.h"
 
 #include <climits>

@@ -5,42 +5,49 @@
 // One CTA (CG = 1) or one pair of CTAs on neighbouring SMs (CG = 2) walks a static list of work units
 // (output tile x K split).  In a pair every CTA stages its own 128 rows of P and its own half of the BN
 // rows of Q; the leader's MMA thread issues 256 x BN instructions that read both CTAs' shared memory, so
-// each SM moves 2/3 of the bytes per flop of the single-CTA tile.  No TMA multicast is used anywhere:
-// every CTA fetches exactly the bytes it stages.
+// each SM moves 2/3 of the bytes per flop of the single-CTA tile (the fill rate of shared memory, 64 B per
+// clock per SM, is what bounds these kernels).  No TMA multicast is used anywhere: every CTA fetches
+// exactly the bytes it stages.
 //
-// Warps (320 threads per CTA):
-//   0      TMA producer: operand tiles + raw scale bytes into a ring of shared-memory stages
-//   1      MMA issuer (leader CTA) and TMEM owner; in a pair's second CTA it forwards "stage landed"
-//   2..5   scale warps: read the raw scale bytes of a stage (any wire layout), re-order them in registers
-//          and write them to TMEM with tcgen05.st, one warp per TMEM lane quarter
+// Warps (384 threads per CTA):
+//   0, 10  TMA producers for the P and the Q operand tiles (one thread each: issuing a 16 KB tile load keeps
+//          a thread busy for a few hundred cycles, so the two operands are issued in parallel); completion
+//          bytes of BOTH CTAs of a pair are counted on the leader's barrier
+//   11     TMA producer for the raw UE8M0 block scales (wire layout) of each stage
+//   1      MMA issuer (leader CTA) and TMEM owner
+//   2..5   scale warps, one per TMEM lane quarter: read a stage's raw scale bytes from shared memory in
+//          whatever wire layout the caller uses, re-order them in registers and write them to a per-stage
+//          TMEM buffer with tcgen05.st.  For the mixed e4m3 x e2m1 kind they also widen the packed e2m1
+//          operand to e4m3 in shared memory.
 //   6..9   epilogue: TMEM -> registers -> alpha/bias -> bf16 -> global (or split-K partials + last-arriver
 //          reduction), overlapped with the next unit's main loop when two accumulators fit in TMEM
 //
 // Barriers (all waits bounded by wall time):
-//   full[s]       stage s of THIS CTA has landed (TMA transaction bytes)
-//   ready[s]      leader only: scale warps of all CTAs have written stage s's scales to TMEM (scaled kinds),
-//                 or the second CTA's stage s has landed (bf16 pair)
+//   full[s]       leader: the operand tiles of stage s of every CTA of the pair have landed
+//   staged[s]     mixed kind: this CTA's packed e2m1 tile of stage s has landed (local)
+//   sfraw[s]      this CTA's raw scale bytes of stage s have landed (local)
+//   xch[s]        e8m0_shuffle wire layout: the four scale warps have re-ordered their share of stage s (local)
+//   ready[s]      leader: every scale warp of every CTA has written stage s's scales to TMEM
 //   empty[s]      the MMAs reading stage s (and its TMEM scales) are done (tcgen05.commit, both CTAs)
 //   acc_full[a]   accumulator a is complete (tcgen05.commit, both CTAs)
-//   acc_empty[a]  leader only: all epilogue warps of all CTAs have drained accumulator a
+//   acc_empty[a]  leader: all epilogue warps of all CTAs have drained accumulator a
 #pragma once
 #include "gemm_common.cuh"
 
 namespace b200 {
 
-constexpr int kPersistentThreads = 320;
+constexpr int kPersistentThreads = 384;
 constexpr int kMaxAcc            = 2;
 
 struct PersistentParams
 {
     int rows_p, rows_q;
-    int num_k_iters;  // ceil(K bytes / 128)
+    int num_k_iters;  // ceil(K elements / elements per 128-byte tile)
     int kblocks;      // valid 32-element scale blocks along K
     int bn;           // UMMA N (multiple of 16, <= 256; multiple of 32 unless there is a single Q tile)
     int stages;
     int p_mode, q_mode;
-    int sf_groups_p, sf_groups_q; // 32-row scale groups staged per CTA per stage
-    int f4_operand;               // mixed kind only: which operand arrives as packed e2m1 (1 = P, 2 = Q)
+    int f4_operand;   // mixed kind only: which operand arrives as packed e2m1 (1 = P, 2 = Q)
     int transposed_out;
     int tiles_p, tiles_q, splits; // tiles_p counts 128*CG-row tiles
     int n_acc;                    // accumulators in TMEM (1 or 2)
@@ -48,6 +55,11 @@ struct PersistentParams
     int sf_tmem_base;             // first TMEM column of the per-stage scale buffers
     int sf_cols;                  // TMEM columns per stage for scales
     int tmem_cols;                // allocation (power of two)
+    // block scales in global memory (wire layout), one "group" = 32 rows; a group row is `sf_row_words` words
+    const uint32_t* sfp;
+    const uint32_t* sfq;
+    int sfp_groups, sfq_groups;   // groups present in each scale tensor
+    int sfp_row_words, sfq_row_words;
     __nv_bfloat16* out;
     long long ldo;
     const void* bias;
@@ -65,16 +77,17 @@ struct PersistentSmem
     uint32_t stage_bytes, q_off, sfp_off, sfq_off, stg_off, bar_off, total;
 };
 
+// scaled: the stage carries 1 KB + 2 KB of raw scale bytes (P groups, Q groups)
 // f4_operand: 0 none, 1 = P, 2 = Q arrives as packed e2m1 and needs a staging area of rows x 64 bytes
-__host__ __device__ inline PersistentSmem make_persistent_smem(int kind, int bn, int cg, int stages, int f4_operand = 0)
+__host__ __device__ inline PersistentSmem make_persistent_smem(int bn, int cg, int stages, int f4_operand, bool scaled)
 {
     PersistentSmem L;
     uint32_t q_bytes = static_cast<uint32_t>(bn / cg) * kTileKBytes;
     q_bytes          = (q_bytes + 1023u) & ~1023u;
     L.q_off          = kTileP * kTileKBytes;
     L.sfp_off        = L.q_off + q_bytes;
-    L.sfq_off        = L.sfp_off + (kind == KIND_BF16 ? 0u : 1024u);
-    L.stg_off        = L.sfq_off + (kind == KIND_BF16 ? 0u : 2048u);
+    L.sfq_off        = L.sfp_off + (scaled ? 1024u : 0u);
+    L.stg_off        = L.sfq_off + (scaled ? 2048u : 0u);
     uint32_t stg     = f4_operand == 1 ? kTileP * 64u : (f4_operand == 2 ? static_cast<uint32_t>(bn / cg) * 64u : 0u);
     stg              = (stg + 1023u) & ~1023u;
     L.stage_bytes    = L.stg_off + stg;
@@ -82,6 +95,9 @@ __host__ __device__ inline PersistentSmem make_persistent_smem(int kind, int bn,
     L.total          = L.bar_off + 512u;
     return L;
 }
+
+// TMEM columns one stage's scales occupy: [P atoms: 4 per K atom][Q atoms: 8 per K atom (two 128-row blocks)]
+__host__ __device__ constexpr int sf_cols_per_stage(int kind) { return kind == KIND_BF16 ? 0 : (kind == KIND_MXF4 ? 24 : 16); }
 
 // 8 packed e2m1 codes (one 32-bit word, element n in nibble n) -> 8 e4m3 bytes (exact: every e2m1 value
 // is an e4m3 value).  Magnitude by table look-up (prmt), sign moved to bit 7 of each byte.
@@ -95,6 +111,13 @@ __device__ __forceinline__ void e2m1x8_to_e4m3x8(uint32_t w, uint32_t& lo, uint3
     hi = __byte_perm(kLutLo, kLutHi, h & 0x7777u) | __byte_perm(kSign, 0u, (h >> 3) & 0x1111u);
 }
 
+// Position in the static work list shared by all roles of a CTA.
+struct WorkIter
+{
+    int u, i, tp, tq, it_beg, n_iters, z;
+    bool valid;
+};
+
 template <int KIND, int SFW, int CG>
 __global__ void __launch_bounds__(kPersistentThreads, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
@@ -103,27 +126,32 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
 {
     constexpr bool kScaled = (KIND != KIND_BF16);
     constexpr bool kMixed  = (KIND == KIND_MXF8F4);
-    constexpr int kAtomsK  = (KIND == KIND_MXF4) ? 2 : 1;
-    constexpr int kSfChunk = (SFW == SFW_E8M0_SHUFFLE) ? 256 : 128 * kAtomsK;
+    constexpr int kAtomsK  = (KIND == KIND_MXF4) ? 2 : 1;      // 4-k-block scale atoms per 128-byte K tile
+    constexpr int kSfCols  = sf_cols_per_stage(KIND);
+    constexpr int kTWords  = kSfCols > 16 ? 24 : 16;
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen        = smem_raw + (smem_base - smem_u32(smem_raw));
     const int bn             = prm.bn;
     const int S              = prm.stages;
-    const PersistentSmem L   = make_persistent_smem(KIND, bn, CG, S, kMixed ? prm.f4_operand : 0);
+    const PersistentSmem L   = make_persistent_smem(bn, CG, S, kMixed ? prm.f4_operand : 0, kScaled);
+    constexpr int kSfChunk   = (SFW == SFW_E8M0_SHUFFLE) ? 256 : 128 * kAtomsK; // raw scale bytes per 32-row group per stage
 
     const uint32_t bar_base  = smem_base + L.bar_off;
     auto full_bar            = [&](int s) { return bar_base + 8u * s; };
     auto ready_bar           = [&](int s) { return bar_base + 64u + 8u * s; };
     auto empty_bar           = [&](int s) { return bar_base + 128u + 8u * s; };
-    auto acc_full_bar        = [&](int a) { return bar_base + 192u + 8u * a; };
-    auto acc_empty_bar       = [&](int a) { return bar_base + 208u + 8u * a; };
-    const uint32_t epi_bar   = bar_base + 224u;
-    const uint32_t drain_bar = bar_base + 232u;
-    uint32_t* tmem_ptr_smem    = reinterpret_cast<uint32_t*>(smem_gen + L.bar_off + 240);
-    volatile uint32_t* abort_f = reinterpret_cast<volatile uint32_t*>(smem_gen + L.bar_off + 244);
-    uint32_t* ticket_smem      = reinterpret_cast<uint32_t*>(smem_gen + L.bar_off + 248);
+    auto staged_bar          = [&](int s) { return bar_base + 192u + 8u * s; };
+    auto sfraw_bar           = [&](int s) { return bar_base + 256u + 8u * s; };
+    auto xch_bar             = [&](int s) { return bar_base + 320u + 8u * s; };
+    auto acc_full_bar        = [&](int a) { return bar_base + 384u + 8u * a; };
+    auto acc_empty_bar       = [&](int a) { return bar_base + 400u + 8u * a; };
+    const uint32_t epi_bar   = bar_base + 416u;
+    const uint32_t drain_bar = bar_base + 424u;
+    uint32_t* tmem_ptr_smem    = reinterpret_cast<uint32_t*>(smem_gen + L.bar_off + 432);
+    volatile uint32_t* abort_f = reinterpret_cast<volatile uint32_t*>(smem_gen + L.bar_off + 436);
+    uint32_t* ticket_smem      = reinterpret_cast<uint32_t*>(smem_gen + L.bar_off + 440);
 
     const int warp       = threadIdx.x >> 5;
     const int lane       = threadIdx.x & 31;
@@ -138,16 +166,17 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
 
     const int splits      = prm.splits;
     const int total_units = prm.tiles_p * prm.tiles_q * splits;
-    // ready[s] arrivals per phase: scaled kinds - one per scale warp of every CTA; bf16 pair - the second CTA
-    const int ready_count = kScaled ? 4 * CG : (CG - 1);
 
     if(threadIdx.x == 0)
     {
         for(int s = 0; s < S; ++s)
         {
-            mbar_init(full_bar(s), 1);
-            mbar_init(ready_bar(s), ready_count > 0 ? ready_count : 1);
+            mbar_init(full_bar(s), 2 * CG);   // one expect_tx arrival per operand producer of every CTA of the pair
+            mbar_init(ready_bar(s), 4 * CG);  // one arrival per scale warp of every CTA
             mbar_init(empty_bar(s), 1);
+            mbar_init(staged_bar(s), 1);
+            mbar_init(sfraw_bar(s), 1);
+            mbar_init(xch_bar(s), 4);
         }
         for(int a = 0; a < kMaxAcc; ++a)
         {
@@ -193,81 +222,124 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
 
     const int q_rows_cta       = bn / CG;
     const uint32_t q_box_bytes = static_cast<uint32_t>(q_rows_cta) * kTileKBytes;
-    const uint32_t sfp_bytes   = kScaled ? static_cast<uint32_t>(prm.sf_groups_p) * kSfChunk : 0u;
-    const uint32_t sfq_bytes   = kScaled ? static_cast<uint32_t>(prm.sf_groups_q) * kSfChunk : 0u;
     const int nq128            = (bn + 127) / 128;
-    const int sfp_cols         = 4 * kAtomsK;
+    const bool p_f4            = kMixed && prm.f4_operand == 1;
+    const bool q_f4            = kMixed && prm.f4_operand == 2;
 
     // unit -> (tile_p, tile_q, k range); q runs fastest so that concurrently running CTAs share P tiles
-    auto decode = [&](int u, int& tp, int& tq, int& it_beg, int& n_iters, int& z) {
-        z              = u % splits;
-        const int tile = u / splits;
-        tq             = tile % prm.tiles_q;
-        tp             = tile / prm.tiles_q;
-        it_beg         = static_cast<int>((static_cast<long long>(prm.num_k_iters) * z) / splits);
-        n_iters        = static_cast<int>((static_cast<long long>(prm.num_k_iters) * (z + 1)) / splits) - it_beg;
+    auto decode = [&](WorkIter& w) {
+        w.valid = w.u < total_units;
+        if(!w.valid)
+            return;
+        w.z            = w.u % splits;
+        const int tile = w.u / splits;
+        w.tq           = tile % prm.tiles_q;
+        w.tp           = tile / prm.tiles_q;
+        w.it_beg       = static_cast<int>((static_cast<long long>(prm.num_k_iters) * w.z) / splits);
+        w.n_iters      = static_cast<int>((static_cast<long long>(prm.num_k_iters) * (w.z + 1)) / splits) - w.it_beg;
+        w.i            = 0;
+    };
+    auto first_work = [&]() {
+        WorkIter w;
+        w.u = cluster_id;
+        decode(w);
+        return w;
+    };
+    auto next_unit = [&](WorkIter& w) {
+        w.u += n_clusters;
+        decode(w);
+    };
+    auto next_iter = [&](WorkIter& w) {
+        if(++w.i == w.n_iters)
+            next_unit(w);
     };
 
-    if(warp == 0)
+    if(warp == 0 || warp == 10)
     {
-        // ------------------------------------------------------------------ TMA producer (every CTA)
+        // ------------------------------------------------------------------ operand producers (every CTA)
+        // warp 0 loads this CTA's P tile, warp 10 its Q tile; both count their bytes on the leader's full[s]
         if(lane == 0)
         {
-            int g = 0; // running stage counter
+            const bool is_p   = (warp == 0);
+            const bool is_f4  = is_p ? p_f4 : q_f4;
+            const int mode    = is_p ? prm.p_mode : prm.q_mode;
+            const CUtensorMap* map = is_p ? &map_p : &map_q;
+            const uint32_t my_bytes = is_f4 ? 0u : (is_p ? kTileP * kTileKBytes : q_box_bytes);
+            const uint32_t tile_off = is_p ? 0u : L.q_off;
+            int g = 0;
             bool ok = true;
-            for(int u = cluster_id; u < total_units && ok; u += n_clusters)
+            for(WorkIter w = first_work(); w.valid && ok; next_iter(w), ++g)
             {
-                int tp, tq, it_beg, n_iters, z;
-                decode(u, tp, tq, it_beg, n_iters, z);
-                const int row_p0 = (tp * CG + static_cast<int>(crank)) * kTileP;
-                const int row_q0 = tq * bn + static_cast<int>(crank) * q_rows_cta;
-                const int sfq_g0 = (tq * bn) >> 5;
-                for(int i = 0; i < n_iters; ++i, ++g)
+                const int s = g % S;
+                ok = bounded_wait(empty_bar(s), ((g / S) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_PRODUCER, g);
+                if(!ok)
+                    break;
+                const int row0 = is_p ? (w.tp * CG + static_cast<int>(crank)) * kTileP
+                                      : w.tq * bn + static_cast<int>(crank) * q_rows_cta;
+                const int kt         = w.it_beg + w.i;
+                const uint32_t stage = smem_base + s * L.stage_bytes;
+                if(is_f4)
                 {
-                    const int s = g % S;
-                    ok = bounded_wait(empty_bar(s), ((g / S) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_PRODUCER, g);
-                    if(!ok)
-                        break;
-                    const uint32_t stage = smem_base + s * L.stage_bytes;
-                    const uint32_t bar   = full_bar(s);
-                    if(g == 5) stamp(34);
-                    const bool p_f4 = kMixed && prm.f4_operand == 1, q_f4 = kMixed && prm.f4_operand == 2;
-                    mbar_arrive_expect_tx(bar, (p_f4 ? kTileP * 64u : kTileP * kTileKBytes) + (q_f4 ? q_box_bytes / 2 : q_box_bytes) +
-                                                   sfp_bytes + sfq_bytes);
-                    if(g == 5) stamp(35);
-                    // a packed e2m1 operand (always 16x16-byte tiled) lands in the staging area: 4 chunks of 16 bytes per row
-                    if(p_f4)
-                        tma_load_3d(stage + L.stg_off, &map_p, bar, 0, row_p0 >> 4, (it_beg + i) * 4);
-                    else
-                        issue_operand_load(prm.p_mode, stage, &map_p, bar, row_p0, it_beg + i);
-                    if(g == 5) stamp(36);
-                    if(q_f4)
-                        tma_load_3d(stage + L.stg_off, &map_q, bar, 0, row_q0 >> 4, (it_beg + i) * 4);
-                    else
-                        issue_operand_load(prm.q_mode, stage + L.q_off, &map_q, bar, row_q0, it_beg + i);
-                    if(g == 5) stamp(37);
-                    if(kScaled)
-                    {
-                        tma_load_2d(stage + L.sfp_off, &map_sfp, bar, (it_beg + i) * kSfChunk, row_p0 >> 5);
-                        if(g == 5) stamp(38);
-                        tma_load_2d(stage + L.sfq_off, &map_sfq, bar, (it_beg + i) * kSfChunk, sfq_g0);
-                        if(g == 5) stamp(39);
-                    }
-                    if(g < 8) stamp(2 + 4 * g);
+                    // the packed e2m1 operand (always 16x16-byte tiled) lands in this CTA's staging area:
+                    // 4 chunks of 16 bytes per row, counted on a local barrier for the scale warps
+                    const uint32_t sbar = staged_bar(s);
+                    mbar_arrive_expect_tx(sbar, (is_p ? kTileP : q_rows_cta) * 64u);
+                    tma_load_3d(stage + L.stg_off, map, sbar, 0, row0 >> 4, kt * 4);
                 }
+                if(CG == 1)
+                {
+                    const uint32_t bar = full_bar(s);
+                    mbar_arrive_expect_tx(bar, my_bytes);
+                    if(!is_f4)
+                        issue_operand_load(mode, stage + tile_off, map, bar, row0, kt);
+                }
+                else
+                {
+                    const uint32_t bar = map_to_cta(full_bar(s), 0); // the leader's barrier counts both CTAs' bytes
+                    mbar_arrive_expect_tx_cluster(bar, my_bytes);
+                    if(!is_f4)
+                    {
+                        if(mode == OPM_ROWMAJOR)
+                            tma_load_2d_pair(stage + tile_off, map, bar, kt * kTileKBytes, row0);
+                        else if(mode == OPM_TILE16)
+                            tma_load_3d_pair(stage + tile_off, map, bar, 0, row0 >> 4, kt * (kTileKBytes / 16));
+                        else
+                            tma_load_4d_pair(stage + tile_off, map, bar, 0, 0, row0 >> 1, kt);
+                    }
+                }
+                if(is_p && g < 14) stamp(2 + 4 * g);
             }
             if(*abort_f)
             {
-                // wait (bounded) for loads still in flight so that none lands after exit
-                for(int j = g - 1; j >= 0 && j >= g - S; --j)
-                {
-                    bool done = false;
-                    const uint64_t t0 = global_timer_ns();
-                    while(!done && global_timer_ns() - t0 < kWaitLimitNs)
-                        done = mbar_try_wait(full_bar(j % S), (j / S) & 1);
-                    if(!done)
-                        atomicCAS(prm.status, 0u, ST_TIMEOUT_DRAIN);
-                }
+                // give loads still in flight time to land before this CTA's shared memory is released (bounded);
+                // the final CTA / cluster barrier keeps the CTAs resident meanwhile
+                const uint64_t t0 = global_timer_ns();
+                while(global_timer_ns() - t0 < 200000ull) {}
+            }
+        }
+    }
+    else if(warp == 11)
+    {
+        // ------------------------------------------------------------------ raw scale producer (every CTA)
+        if(kScaled && lane == 0)
+        {
+            const uint32_t sfp_bytes = 4u * kSfChunk;
+            const uint32_t sfq_bytes = static_cast<uint32_t>((bn + 31) / 32) * kSfChunk;
+            int g = 0;
+            bool ok = true;
+            for(WorkIter w = first_work(); w.valid && ok; next_iter(w), ++g)
+            {
+                const int s = g % S;
+                ok = bounded_wait(empty_bar(s), ((g / S) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_PRODUCER, 0x20000 + g);
+                if(!ok)
+                    break;
+                const int row_p0     = (w.tp * CG + static_cast<int>(crank)) * kTileP;
+                const int kt         = w.it_beg + w.i;
+                const uint32_t stage = smem_base + s * L.stage_bytes;
+                const uint32_t bar   = sfraw_bar(s);
+                mbar_arrive_expect_tx(bar, sfp_bytes + sfq_bytes);
+                tma_load_2d(stage + L.sfp_off, &map_sfp, bar, kt * kSfChunk, row_p0 >> 5);
+                tma_load_2d(stage + L.sfq_off, &map_sfq, bar, kt * kSfChunk, (w.tq * bn) >> 5);
             }
         }
     }
@@ -297,30 +369,28 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
 
             int g = 0, uc = 0;
             bool ok = true;
-            for(int u = cluster_id; u < total_units && ok; u += n_clusters, ++uc)
+            for(WorkIter w = first_work(); w.valid && ok; next_unit(w), ++uc)
             {
-                int tp, tq, it_beg, n_iters, z;
-                decode(u, tp, tq, it_beg, n_iters, z);
                 const int a          = uc % prm.n_acc;
                 const uint32_t d_col = tmem_base + a * prm.acc_stride;
                 ok = bounded_wait(acc_empty_bar(a), ((uc / prm.n_acc) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_MMA_FULL, 0x10000 + uc);
                 if(!ok)
                     break;
                 tc_fence_after_sync();
-                for(int i = 0; i < n_iters; ++i, ++g)
+                for(int i = 0; i < w.n_iters; ++i, ++g)
                 {
                     const int s          = g % S;
                     const uint32_t phase = (g / S) & 1;
                     ok = bounded_wait(full_bar(s), phase, abort_f, prm.status, ST_TIMEOUT_MMA_FULL, g);
-                    if(ok && ready_count > 0)
+                    if(ok && kScaled)
                         ok = bounded_wait(ready_bar(s), phase, abort_f, prm.status, ST_TIMEOUT_MMA_SF, g);
                     if(!ok)
                         break;
                     tc_fence_after_sync();
-                    if(g < 8) stamp(5 + 4 * g);
+                    if(g < 14) stamp(5 + 4 * g);
                     const uint32_t stage = smem_base + s * L.stage_bytes;
                     const uint32_t tsfp  = tmem_base + prm.sf_tmem_base + s * prm.sf_cols;
-                    const uint32_t tsfq  = tsfp + sfp_cols;
+                    const uint32_t tsfq  = tsfp + 4 * kAtomsK;
 #pragma unroll
                     for(int k = 0; k < 4; ++k)
                     {
@@ -334,8 +404,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                             else if(KIND == KIND_MXF8 || KIND == KIND_MXF8F4)
                                 mma_mxf8f6f4(d_col, pd, qd, idesc_with_sf(idesc, k, k), acc, tsfp, tsfq);
                             else
-                                mma_mxf4(d_col, pd, qd, idesc_with_sf(idesc, (k & 1) * 2, (k & 1) * 2), acc,
-                                         tsfp + (k >> 1) * 4, tsfq + (k >> 1) * 4 * nq128);
+                                mma_mxf4(d_col, pd, qd, idesc_with_sf(idesc, (k & 1) * 2, (k & 1) * 2), acc, tsfp + (k >> 1) * 4,
+                                         tsfq + (k >> 1) * 8);
                         }
                         else
                         {
@@ -344,16 +414,14 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                             else if(KIND == KIND_MXF8 || KIND == KIND_MXF8F4)
                                 mma_mxf8f6f4_2cta(d_col, pd, qd, idesc_with_sf(idesc, k, k), acc, tsfp, tsfq);
                             else
-                                mma_mxf4_2cta(d_col, pd, qd, idesc_with_sf(idesc, (k & 1) * 2, (k & 1) * 2), acc,
-                                              tsfp + (k >> 1) * 4, tsfq + (k >> 1) * 4 * nq128);
+                                mma_mxf4_2cta(d_col, pd, qd, idesc_with_sf(idesc, (k & 1) * 2, (k & 1) * 2), acc, tsfp + (k >> 1) * 4,
+                                              tsfq + (k >> 1) * 8);
                         }
                     }
-                    if(g == 5) stamp(42);
                     if(CG == 1)
                         tc_commit(empty_bar(s));
                     else
                         tc_commit_2cta(empty_bar(s), 3);
-                    if(g == 5) stamp(43);
                 }
                 if(ok)
                 {
@@ -375,149 +443,151 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                 while(!mbar_try_wait(drain_bar, 0) && global_timer_ns() - t0 < kWaitLimitNs) {}
             }
         }
-        else if(lane == 0 && CG == 2 && !kScaled)
-        {
-            // ------------------------------------------------------------------ second CTA of a bf16 pair:
-            // tell the leader when this CTA's half of a stage has landed
-            int g = 0;
-            bool ok = true;
-            for(int u = cluster_id; u < total_units && ok; u += n_clusters)
-            {
-                int tp, tq, it_beg, n_iters, z;
-                decode(u, tp, tq, it_beg, n_iters, z);
-                for(int i = 0; i < n_iters; ++i, ++g)
-                {
-                    const int s = g % S;
-                    ok = bounded_wait(full_bar(s), (g / S) & 1, abort_f, prm.status, ST_TIMEOUT_SFWARP, g);
-                    if(!ok)
-                        break;
-                    mbar_arrive_cluster(map_to_cta(ready_bar(s), 0));
-                }
-            }
-        }
     }
     else if(warp < 6)
     {
         // ------------------------------------------------------------------ scale warps (every CTA)
+        // A single warp executes this loop once per K tile, so it is kept short: a handful of shared-memory
+        // loads of the stage's raw scale bytes, a few byte permutes, one tcgen05.st.
         if(kScaled)
         {
+            constexpr bool kE8 = (SFW == SFW_E8M0_SHUFFLE);
             const int quarter    = warp & 3;
             const uint32_t tlane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
             const uint32_t ready_remote = (CG == 2) ? map_to_cta(ready_bar(0), 0) : 0u;
+            const int r16 = lane & 15, hi = lane >> 4;
+            const int q_groups = (bn + 31) / 32; // 32-row groups of Q staged per stage (P always stages 4)
+
             int g = 0;
             bool ok = true;
-            for(int u = cluster_id; u < total_units && ok; u += n_clusters)
+            for(WorkIter w = first_work(); w.valid && ok; next_iter(w), ++g)
             {
-                int tp, tq, it_beg, n_iters, z;
-                decode(u, tp, tq, it_beg, n_iters, z);
-                for(int i = 0; i < n_iters; ++i, ++g)
+                const int s = g % S;
+                // raw scales of stage s have landed (their producer waited for the previous pass's MMAs, so the
+                // TMEM scale buffer of stage s is free as well); mixed kind: so has the packed e2m1 tile
+                ok = bounded_wait(sfraw_bar(s), (g / S) & 1, abort_f, prm.status, ST_TIMEOUT_SFWARP, g);
+                if(ok && kMixed)
+                    ok = bounded_wait(staged_bar(s), (g / S) & 1, abort_f, prm.status, ST_TIMEOUT_SFWARP, 0x10000 + g);
+                ok = __all_sync(0xffffffffu, ok);
+                if(!ok)
+                    break;
+                if(warp == 2 && lane == 0 && g < 14) stamp(3 + 4 * g);
+                uint8_t* stage = smem_gen + s * L.stage_bytes;
+                if(kMixed)
                 {
-                    const int s = g % S;
-                    ok = bounded_wait(full_bar(s), (g / S) & 1, abort_f, prm.status, ST_TIMEOUT_SFWARP, g);
+                    // widen the packed e2m1 operand of this stage to e4m3 in the MMA's un-swizzled layout:
+                    // staging [4 chunks][rows][16 B] (32 codes each) -> tile [8 chunks][rows][16 B]
+                    const int rows   = p_f4 ? kTileP : q_rows_cta;
+                    const uint4* src = reinterpret_cast<const uint4*>(stage + L.stg_off);
+                    uint4* dst       = reinterpret_cast<uint4*>(stage + (p_f4 ? 0u : L.q_off));
+                    const int items  = rows * 4;
+                    for(int it = (warp - 2) * 32 + lane; it < items; it += 128)
+                    {
+                        const int kc  = it / rows;
+                        const int r   = it - kc * rows;
+                        const uint4 v = src[it];
+                        uint4 o0, o1;
+                        e2m1x8_to_e4m3x8(v.x, o0.x, o0.y);
+                        e2m1x8_to_e4m3x8(v.y, o0.z, o0.w);
+                        e2m1x8_to_e4m3x8(v.z, o1.x, o1.y);
+                        e2m1x8_to_e4m3x8(v.w, o1.z, o1.w);
+                        dst[(2 * kc) * rows + r]     = o0;
+                        dst[(2 * kc + 1) * rows + r] = o1;
+                    }
+                    fence_proxy_async_smem(); // these generic-proxy writes are read by the tensor core
+                }
+                // TMEM words of this stage, column order [P atom a][Q atom a, block 0][Q atom a, block 1]
+                const uint32_t* rawp = reinterpret_cast<const uint32_t*>(stage + L.sfp_off);
+                const uint32_t* rawq = reinterpret_cast<const uint32_t*>(stage + L.sfq_off);
+                const int kt = w.it_beg + w.i;
+                uint32_t t[kTWords];
+#pragma unroll
+                for(int c = 0; c < kTWords; ++c)
+                    t[c] = 0x7F7F7F7Fu;
+                if(kE8)
+                {
+                    // raw: per 32-row group j a 256-byte chunk, byte (k%4)*64 + (m%16)*4 + ((k%8)/4)*2 + (m%32)/16:
+                    // word column kk = k%4, byte kh*2 + mh (mh = this lane's row half).  The re-ordering is the
+                    // same for all four TMEM lane quarters, so the warps share it: warp q re-orders groups q, q+4
+                    // and q+8 and writes the two result words per row back over the chunk it just read
+                    // ([k half][row 0..31]); after a (bounded) rendezvous every warp reads all 24 columns.
+                    uint32_t* chunks = reinterpret_cast<uint32_t*>(stage + L.sfp_off); // 12 chunks, P's 4 then Q's 8
+                    const bool tail  = (kt * 8 + 8 > prm.kblocks);
+                    uint32_t v0[3], v1[3];
+#pragma unroll
+                    for(int jj = 0; jj < 3; ++jj)
+                    {
+                        const int j         = (warp - 2) + 4 * jj;
+                        const uint32_t* grp = chunks + j * 64;
+                        const uint32_t w0 = grp[r16], w1 = grp[16 + r16], w2 = grp[32 + r16], w3 = grp[48 + r16];
+                        const uint32_t sel     = hi ? 0x7351u : 0x6240u; // bytes {kh=0, kh=1} of this lane's row half
+                        const uint32_t lo_part = __byte_perm(w0, w1, sel); // k%4 = 0,1 for both k halves
+                        const uint32_t hi_part = __byte_perm(w2, w3, sel); // k%4 = 2,3
+                        v0[jj] = __byte_perm(lo_part, hi_part, 0x5410); // k-blocks 0..3 of this row
+                        v1[jj] = __byte_perm(lo_part, hi_part, 0x7632); // k-blocks 4..7
+                        if(tail)
+                        {
+                            const int valid0  = min(max(prm.kblocks - kt * 8, 0), 4);
+                            const int valid1  = min(max(prm.kblocks - kt * 8 - 4, 0), 4);
+                            const uint32_t m0 = valid0 >= 4 ? 0xFFFFFFFFu : ((1u << (8 * valid0)) - 1u);
+                            const uint32_t m1 = valid1 >= 4 ? 0xFFFFFFFFu : ((1u << (8 * valid1)) - 1u);
+                            v0[jj] = (v0[jj] & m0) | (0x7F7F7F7Fu & ~m0);
+                            v1[jj] = (v1[jj] & m1) | (0x7F7F7F7Fu & ~m1);
+                        }
+                        const bool in = (j < 4) || (j - 4 < q_groups);
+                        if(!in)
+                            v0[jj] = v1[jj] = 0x7F7F7F7Fu;
+                    }
+                    __syncwarp(); // every lane has read this warp's chunks
+#pragma unroll
+                    for(int jj = 0; jj < 3; ++jj)
+                    {
+                        uint32_t* grp = chunks + ((warp - 2) + 4 * jj) * 64;
+                        grp[lane]      = v0[jj];
+                        grp[32 + lane] = v1[jj];
+                    }
+                    __syncwarp();
+                    if(lane == 0)
+                        mbar_arrive(xch_bar(s));
+                    ok = bounded_wait(xch_bar(s), (g / S) & 1, abort_f, prm.status, ST_TIMEOUT_SFWARP, 0x30000 + g);
                     ok = __all_sync(0xffffffffu, ok);
                     if(!ok)
                         break;
-                    if(warp == 2 && lane == 0 && g < 8) stamp(3 + 4 * g);
-                    uint8_t* stage = smem_gen + s * L.stage_bytes;
-                    const uint32_t tsfp  = tlane + prm.sf_tmem_base + s * prm.sf_cols;
-                    const uint32_t tsfq  = tsfp + sfp_cols;
-                    if(kMixed)
+#pragma unroll
+                    for(int j = 0; j < 12; ++j)
                     {
-                        // widen the packed e2m1 operand of this stage to e4m3 in the MMA's un-swizzled layout:
-                        // staging [4 chunks][rows][16 B] (32 codes) -> tile [8 chunks][rows][16 B]
-                        const int rows     = (prm.f4_operand == 1) ? kTileP : q_rows_cta;
-                        const uint4* src   = reinterpret_cast<const uint4*>(stage + L.stg_off);
-                        uint4* dst         = reinterpret_cast<uint4*>(stage + (prm.f4_operand == 1 ? 0u : L.q_off));
-                        const int items    = rows * 4;
-                        for(int it = (warp - 2) * 32 + lane; it < items; it += 128)
-                        {
-                            const int kc  = it / rows;
-                            const int r   = it - kc * rows;
-                            const uint4 v = src[it];
-                            uint4 o0, o1;
-                            e2m1x8_to_e4m3x8(v.x, o0.x, o0.y);
-                            e2m1x8_to_e4m3x8(v.y, o0.z, o0.w);
-                            e2m1x8_to_e4m3x8(v.z, o1.x, o1.y);
-                            e2m1x8_to_e4m3x8(v.w, o1.z, o1.w);
-                            dst[(2 * kc) * rows + r]     = o0;
-                            dst[(2 * kc + 1) * rows + r] = o1;
-                        }
-                        fence_proxy_async_smem(); // these generic-proxy writes are read by the tensor core
+                        t[(j < 4) ? j : 8 + (j - 4)]      = chunks[j * 64 + lane];      // K atom 0: P cols 0..3, Q cols 8..15
+                        t[(j < 4) ? 4 + j : 16 + (j - 4)] = chunks[j * 64 + 32 + lane]; // K atom 1: P cols 4..7, Q cols 16..23
                     }
-                    for(int op = 0; op < 2; ++op)
-                    {
-                        const uint32_t* region = reinterpret_cast<const uint32_t*>(stage + (op == 0 ? L.sfp_off : L.sfq_off));
-                        const int groups       = (op == 0) ? prm.sf_groups_p : prm.sf_groups_q;
-                        const int blocks       = (op == 0) ? 1 : nq128;
-                        const uint32_t tbase   = (op == 0) ? tsfp : tsfq;
-                        if(SFW == SFW_G1250)
+                }
+                else
+                {
+                    // raw: [group][k quarter a][row 0..31][4 k-blocks]: one word per row per K atom
+#pragma unroll
+                    for(int j = 0; j < 12; ++j)
+#pragma unroll
+                        for(int a = 0; a < kAtomsK; ++a)
                         {
-                            // wire: [group][k quarter a][row 0..31][4 k-blocks]
-                            for(int nb = 0; nb < blocks; ++nb)
-#pragma unroll
-                                for(int a = 0; a < kAtomsK; ++a)
-                                {
-                                    uint32_t w[4];
-#pragma unroll
-                                    for(int g4 = 0; g4 < 4; ++g4)
-                                    {
-                                        const int gg = nb * 4 + g4;
-                                        w[g4]        = (gg < groups) ? region[gg * (32 * kAtomsK) + a * 32 + lane] : 0x7F7F7F7Fu;
-                                    }
-                                    tmem_st_x4(tbase + (a * blocks + nb) * 4, w[0], w[1], w[2], w[3]);
-                                }
+                            const bool in       = (j < 4) || (j - 4 < q_groups);
+                            const uint32_t* grp = (j < 4) ? rawp + j * (32 * kAtomsK) : rawq + (j - 4) * (32 * kAtomsK);
+                            const int col       = (j < 4) ? a * 4 + j : 4 * kAtomsK + a * 8 + (j - 4);
+                            t[col]              = in ? grp[a * 32 + lane] : 0x7F7F7F7Fu;
                         }
-                        else if(SFW == SFW_E8M0_SHUFFLE)
-                        {
-                            // wire: per 32-row group and 8 k-blocks a 256-byte chunk, byte offset
-                            // (k%4)*64 + (m%16)*4 + ((k%8)/4)*2 + (m%32)/16
-                            const int r16 = lane & 15, mh = lane >> 4;
-                            for(int nb = 0; nb < blocks; ++nb)
-                            {
-                                uint32_t w[4][4];
-#pragma unroll
-                                for(int g4 = 0; g4 < 4; ++g4)
-#pragma unroll
-                                    for(int kk = 0; kk < 4; ++kk)
-                                    {
-                                        const int gg = nb * 4 + g4;
-                                        w[g4][kk]    = (gg < groups) ? region[gg * 64 + kk * 16 + r16] : 0x7F7F7F7Fu;
-                                    }
-#pragma unroll
-                                for(int kh = 0; kh < 2; ++kh)
-                                {
-                                    const uint32_t b    = kh * 2 + mh;
-                                    const uint32_t sel  = b | ((4u + b) << 4);
-                                    const int first_kb  = (it_beg + i) * 8 + kh * 4;
-                                    const int valid     = min(max(prm.kblocks - first_kb, 0), 4);
-                                    const uint32_t mask = valid >= 4 ? 0xFFFFFFFFu : ((1u << (8 * valid)) - 1u);
-                                    uint32_t o[4];
-#pragma unroll
-                                    for(int g4 = 0; g4 < 4; ++g4)
-                                    {
-                                        const uint32_t t01 = __byte_perm(w[g4][0], w[g4][1], sel);
-                                        const uint32_t t23 = __byte_perm(w[g4][2], w[g4][3], sel);
-                                        const uint32_t v   = __byte_perm(t01, t23, 0x5410);
-                                        o[g4]              = (v & mask) | (0x7F7F7F7Fu & ~mask);
-                                    }
-                                    tmem_st_x4(tbase + (kh * blocks + nb) * 4, o[0], o[1], o[2], o[3]);
-                                }
-                            }
-                        }
-                    }
-                    if(warp == 2 && lane == 0 && g == 5) stamp(40);
-                    tmem_st_wait();
-                    if(warp == 2 && lane == 0 && g == 5) stamp(41);
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if(lane == 0)
-                    {
-                        if(CG == 2)
-                            mbar_arrive_cluster(ready_remote + 8u * s);
-                        else
-                            mbar_arrive(ready_bar(s));
-                        if(warp == 2 && g < 8) stamp(4 + 4 * g);
-                    }
+                }
+                const uint32_t tsf = tlane + prm.sf_tmem_base + s * prm.sf_cols;
+                tmem_st_x16(tsf, t);
+                if(kTWords > 16)
+                    tmem_st_x8(tsf + 16, t + 16);
+                tmem_st_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if(lane == 0)
+                {
+                    if(CG == 2)
+                        mbar_arrive_cluster(ready_remote + 8u * s);
+                    else
+                        mbar_arrive(ready_bar(s));
+                    if(warp == 2 && g < 14) stamp(4 + 4 * g);
                 }
             }
         }
@@ -536,14 +606,12 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
         uint32_t epi_phase = 0;
         int uc = 0;
         bool ok = true;
-        for(int u = cluster_id; u < total_units && ok; u += n_clusters, ++uc)
+        for(WorkIter w = first_work(); w.valid && ok; next_unit(w), ++uc)
         {
-            int tp, tq, it_beg, n_iters, z;
-            decode(u, tp, tq, it_beg, n_iters, z);
             const int a       = uc % prm.n_acc;
-            const int p       = (tp * CG + static_cast<int>(crank)) * kTileP + p_local;
-            const int row_q0  = tq * bn;
-            const int slot    = (tp * prm.tiles_q + tq) * CG + static_cast<int>(crank); // one ticket / partial slot per CTA tile
+            const int p       = (w.tp * CG + static_cast<int>(crank)) * kTileP + p_local;
+            const int row_q0  = w.tq * bn;
+            const int slot    = (w.tp * prm.tiles_q + w.tq) * CG + static_cast<int>(crank); // ticket / partial slot of this CTA tile
             ok = bounded_wait(acc_full_bar(a), (uc / prm.n_acc) & 1, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, uc);
             ok = __all_sync(0xffffffffu, ok);
             if(!ok)
@@ -552,10 +620,21 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             if(warp == 6 && lane == 0 && uc == 0) stamp(61);
             const uint32_t tacc = tlane + a * prm.acc_stride;
             bool is_last        = !split;
+            auto release_acc = [&]() {
+                tc_fence_before_sync();
+                __syncwarp();
+                if(lane == 0)
+                {
+                    if(CG == 2)
+                        mbar_arrive_cluster(acc_empty_remote + 8u * a);
+                    else
+                        mbar_arrive(acc_empty_bar(a));
+                }
+            };
 
             if(split)
             {
-                float* mine = prm.ws_partial + (static_cast<size_t>(slot) * splits + z) * (static_cast<size_t>(bn) * kTileP);
+                float* mine = prm.ws_partial + (static_cast<size_t>(slot) * splits + w.z) * (static_cast<size_t>(bn) * kTileP);
                 for(int c = 0; c < n_chunks; ++c)
                 {
                     uint32_t r[32];
@@ -569,16 +648,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                         if(j < chunk)
                             mine[static_cast<size_t>(c * chunk + j) * kTileP + p_local] = __uint_as_float(r[j]);
                 }
-                // the accumulator is drained: hand it back before the reduction
-                tc_fence_before_sync();
-                __syncwarp();
-                if(lane == 0)
-                {
-                    if(CG == 2)
-                        mbar_arrive_cluster(acc_empty_remote + 8u * a);
-                    else
-                        mbar_arrive(acc_empty_bar(a));
-                }
+                release_acc(); // the accumulator is drained: hand it back before the reduction
                 __threadfence();
                 __syncwarp();
                 if(lane == 0)
@@ -625,18 +695,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                         for(int j = 0; j < 32; ++j)
                             v[j] = __uint_as_float(r[j]);
                         if(c == n_chunks - 1)
-                        {
-                            // every column of this accumulator is in registers now: hand it back
-                            tc_fence_before_sync();
-                            __syncwarp();
-                            if(lane == 0)
-                            {
-                                if(CG == 2)
-                                    mbar_arrive_cluster(acc_empty_remote + 8u * a);
-                                else
-                                    mbar_arrive(acc_empty_bar(a));
-                            }
-                        }
+                            release_acc(); // every column of this accumulator is in registers now
                     }
                     else
                     {
@@ -707,10 +766,6 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                 }
                 if(split && warp == 6 && lane == 0)
                     prm.ws_counter[slot] = 0; // ready for the next launch
-            }
-            else if(!split)
-            {
-                // unreachable: without split-K every unit is final
             }
         }
         if(warp == 6 && lane == 0) stamp(62);

@@ -2,7 +2,6 @@
 // split-K workspace, launch.  No torch types; only the CUDA runtime (the one driver entry point
 // needed, cuTensorMapEncodeTiled, is resolved at run time so the library loads without libcuda).
 #include "launch.h"
-#include "gemm_kernel.cuh"
 #include "gemm_persistent.cuh"
 
 #include <atomic>
@@ -229,21 +228,11 @@ static int kernel_kind_of(int problem_kind)
     }
 }
 
-static bool use_v1()
-{
-    static const bool v1 = (std::getenv("AITER_B200_V1") != nullptr);
-    return v1;
-}
-
-static int max_stages(int kernel_kind, int bn, int cg, int smem_limit, int f4_operand = 0)
+static int max_stages(int bn, int cg, int smem_limit, int f4_operand, bool scaled)
 {
     for(int s = kMaxStages; s >= 1; --s)
-    {
-        const int total = use_v1() ? static_cast<int>(make_smem_layout(kernel_kind, bn, s).total)
-                                   : static_cast<int>(make_persistent_smem(kernel_kind, bn, cg, s, f4_operand).total);
-        if(total + 1024 <= smem_limit)
+        if(static_cast<int>(make_persistent_smem(bn, cg, s, f4_operand, scaled).total) + 1024 <= smem_limit)
             return s;
-    }
     return 0;
 }
 
@@ -287,8 +276,7 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
     }
     if(cfg.stages <= 0)
     {
-        const int kk = (kind == PK_BF16) ? KIND_BF16 : (kind == PK_MXFP4 ? KIND_MXF4 : (kind == PK_MXF8F4 ? KIND_MXF8F4 : KIND_MXF8));
-        int s        = max_stages(kk, cfg.bn, cfg.cg, 227 * 1024, kind == PK_MXF8F4 ? (cfg.swap ? 1 : 2) : 0);
+        int s        = max_stages(cfg.bn, cfg.cg, 227 * 1024, kind == PK_MXF8F4 ? (cfg.swap ? 1 : 2) : 0, kind != PK_BF16);
         cfg.stages   = s > kMaxStages ? kMaxStages : s;
     }
 }
@@ -368,18 +356,6 @@ static void raise_smem_limit(Kernel kernel, bool (&attr_done)[64])
         if(dev >= 0 && dev < 64)
             attr_done[dev] = true;
     }
-}
-
-template <int KIND, int SFW>
-static void launch_v1(dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap& mp, const CUtensorMap& mq,
-                      const CUtensorMap& msp, const CUtensorMap& msq, const GemmParams& prm)
-{
-    auto kernel = gemm_tcgen05_kernel<KIND, SFW>;
-    static bool attr_done[64] = {};
-    raise_smem_limit(kernel, attr_done);
-    kernel<<<grid, kNumThreads, smem, stream>>>(mp, mq, msp, msq, prm);
-    B200_CUDA(cudaGetLastError());
-    g_launches.fetch_add(1);
 }
 
 template <int KIND, int SFW, int CG>
@@ -467,8 +443,6 @@ void launch_gemm(const GemmProblem& prob)
     DeviceState& st = (prob.scratch != nullptr) ? local_state : device_state(prob.device);
 
     KernelConfig cfg = prob.cfg;
-    if(use_v1())
-        cfg.cg = 1;
     choose_config(prob.kind, prob.M, prob.N, prob.K, st.sm_count, cfg);
     {
         bool ok = false;
@@ -486,7 +460,7 @@ void launch_gemm(const GemmProblem& prob)
     const bool mixed     = (kkind == KIND_MXF8F4);
     const int f4_operand = mixed ? (cfg.swap ? 1 : 2) : 0; // the weight is the packed e2m1 operand
     if(mixed)
-        B200_CHECK(prob.act.kbytes == 2 * prob.wgt.kbytes && prob.wgt.mode == OPM_TILE16 && !use_v1(),
+        B200_CHECK(prob.act.kbytes == 2 * prob.wgt.kbytes && prob.wgt.mode == OPM_TILE16,
                    "mixed MXFP8 x MXFP4: the weight must be packed e2m1 in the 16x16-byte tiled layout");
     else
         B200_CHECK(P.kbytes == Q.kbytes, "operands disagree on K bytes: ", P.kbytes, " vs ", Q.kbytes);
@@ -498,9 +472,8 @@ void launch_gemm(const GemmProblem& prob)
     while(splits > num_k_iters)
         splits >>= 1;
     const int atoms_k  = (kkind == KIND_MXF4) ? 2 : 1;
-    const int nq128    = (cfg.bn + 127) / 128;
-    const int sf_cols  = (kkind == KIND_BF16) ? 0 : (4 * atoms_k + 4 * atoms_k * nq128);
-    const int max_st = max_stages(kkind, cfg.bn, cg, st.smem_optin, f4_operand);
+    const int sf_cols  = sf_cols_per_stage(kkind);
+    const int max_st = max_stages(cfg.bn, cg, st.smem_optin, f4_operand, kkind != KIND_BF16);
     B200_CHECK(max_st >= 2, "tile ", 128 * cg, "x", cfg.bn, " does not fit in shared memory");
     int stages = cfg.stages <= 0 ? max_st : std::min(cfg.stages, max_st);
 
@@ -543,7 +516,6 @@ void launch_gemm(const GemmProblem& prob)
     }
 
     // tensor maps: every CTA stages 128 rows of P and bn / cg rows of Q per K tile
-    const int sf_groups_q = (cfg.bn + 31) / 32;
     CUtensorMap mp  = operand_map(P, kTileP, cfg.swap ? "weight operand" : "activation operand", f4_operand == 1 ? 64 : kTileKBytes);
     CUtensorMap mq  = operand_map(Q, cfg.bn / cg, cfg.swap ? "activation operand" : "weight operand", f4_operand == 2 ? 64 : kTileKBytes);
     CUtensorMap msp = mp, msq = mq;
@@ -552,126 +524,84 @@ void launch_gemm(const GemmProblem& prob)
     if(kkind != KIND_BF16)
     {
         B200_CHECK(SP.wire == SQ.wire && SP.wire != SFW_NONE, "both scale tensors must use the same wire layout");
-        sfw             = SP.wire;
+        sfw = SP.wire;
         const int chunk = (sfw == SFW_E8M0_SHUFFLE) ? 256 : 128 * atoms_k;
+        msp = scale_map(SP, chunk, 4, cfg.swap ? "weight scales" : "activation scales");
+        msq = scale_map(SQ, chunk, (cfg.bn + 31) / 32, cfg.swap ? "activation scales" : "weight scales");
         B200_CHECK(sfw != SFW_E8M0_SHUFFLE || kkind == KIND_MXF4, "the e8m0_shuffle scale layout is only wired for MXFP4");
         const long long need_cols = (sfw == SFW_E8M0_SHUFFLE) ? (kblocks + 7) / 8 * 8 : kblocks;
         B200_CHECK(SP.padded_cols >= need_cols && SQ.padded_cols >= need_cols, "scale tensors have too few columns: need ",
                    need_cols, ", got ", SP.padded_cols, " and ", SQ.padded_cols);
+        B200_CHECK(SP.padded_rows % 32 == 0 && SQ.padded_rows % 32 == 0, "scale rows must be padded to a multiple of 32");
         B200_CHECK(SP.padded_rows >= (P.rows + 31) / 32 * 32 && SQ.padded_rows >= (Q.rows + 31) / 32 * 32,
                    "scale tensors have too few rows");
+        B200_CHECK(((reinterpret_cast<uintptr_t>(SP.ptr) | reinterpret_cast<uintptr_t>(SQ.ptr)) & 3) == 0,
+                   "scale tensors must be 4-byte aligned");
         if(sfw == SFW_G1250)
             B200_CHECK(kblocks % (4 * atoms_k) == 0, "K must be a multiple of ", 128 * atoms_k, " for this scale layout");
-        msp = scale_map(SP, chunk, 4, cfg.swap ? "weight scales" : "activation scales");
-        msq = scale_map(SQ, chunk, sf_groups_q, cfg.swap ? "activation scales" : "weight scales");
     }
 
-    if(use_v1())
-    {
-        B200_CHECK(cfg.bn <= 256 && (cfg.bn & (cfg.bn - 1)) == 0, "the non-persistent kernel takes power-of-two tile widths");
-        GemmParams prm{};
-        prm.rows_p         = static_cast<int>(P.rows);
-        prm.rows_q         = static_cast<int>(Q.rows);
-        prm.num_k_iters    = num_k_iters;
-        prm.kblocks        = kblocks;
-        prm.bn             = cfg.bn;
-        prm.stages         = stages;
-        prm.p_mode         = P.mode;
-        prm.q_mode         = Q.mode;
-        prm.sf_groups_p    = 4;
-        prm.sf_groups_q    = sf_groups_q;
-        prm.transposed_out = cfg.swap;
-        prm.out            = static_cast<__nv_bfloat16*>(prob.out);
-        prm.ldo            = prob.ldo;
-        prm.bias           = prob.bias;
-        prm.bias_is_bf16   = prob.bias_is_bf16;
-        prm.bias_on_q      = cfg.swap ? 0 : 1;
-        prm.alpha          = prob.alpha;
-        prm.beta           = prob.beta;
-        prm.status         = st.status;
-        prm.trace          = trace;
-        prm.ws_partial     = ws_partial;
-        prm.ws_counter     = ws_counter;
-        prm.sf_tmem_base   = (cfg.bn + 31) & ~31;
-        int cols           = 32;
-        while(cols < prm.sf_tmem_base + 2 * sf_cols)
-            cols <<= 1;
-        B200_CHECK(cols <= 512, "internal: TMEM budget exceeded");
-        prm.tmem_cols = cols;
-        const SmemLayout L = make_smem_layout(kkind, cfg.bn, stages);
-        const size_t smem  = L.total + 1024;
-        dim3 grid(tiles_p, tiles_q, splits);
-        if(kkind == KIND_BF16)
-            launch_v1<KIND_BF16, SFW_NONE>(grid, smem, prob.stream, mp, mq, msp, msq, prm);
-        else if(kkind == KIND_MXF8 && sfw == SFW_G1250)
-            launch_v1<KIND_MXF8, SFW_G1250>(grid, smem, prob.stream, mp, mq, msp, msq, prm);
-        else if(kkind == KIND_MXF4 && sfw == SFW_E8M0_SHUFFLE)
-            launch_v1<KIND_MXF4, SFW_E8M0_SHUFFLE>(grid, smem, prob.stream, mp, mq, msp, msq, prm);
-        else if(kkind == KIND_MXF4 && sfw == SFW_G1250)
-            launch_v1<KIND_MXF4, SFW_G1250>(grid, smem, prob.stream, mp, mq, msp, msq, prm);
-        else
-            fail("no kernel instance for kind ", kkind, " with scale layout ", sfw);
-    }
+    PersistentParams prm{};
+    prm.rows_p         = static_cast<int>(P.rows);
+    prm.rows_q         = static_cast<int>(Q.rows);
+    prm.num_k_iters    = num_k_iters;
+    prm.kblocks        = kblocks;
+    prm.bn             = cfg.bn;
+    prm.p_mode         = P.mode;
+    prm.q_mode         = Q.mode;
+    prm.f4_operand     = f4_operand;
+    prm.transposed_out = cfg.swap;
+    prm.tiles_p        = tiles_p;
+    prm.tiles_q        = tiles_q;
+    prm.splits         = splits;
+    prm.sfp            = static_cast<const uint32_t*>(SP.ptr);
+    prm.sfq            = static_cast<const uint32_t*>(SQ.ptr);
+    prm.sfp_groups     = static_cast<int>(SP.padded_rows / 32);
+    prm.sfq_groups     = static_cast<int>(SQ.padded_rows / 32);
+    prm.sfp_row_words  = static_cast<int>(SP.padded_cols * 8);
+    prm.sfq_row_words  = static_cast<int>(SQ.padded_cols * 8);
+    prm.out            = static_cast<__nv_bfloat16*>(prob.out);
+    prm.ldo            = prob.ldo;
+    prm.bias           = prob.bias;
+    prm.bias_is_bf16   = prob.bias_is_bf16;
+    prm.bias_on_q      = cfg.swap ? 0 : 1;
+    prm.alpha          = prob.alpha;
+    prm.beta           = prob.beta;
+    prm.status         = st.status;
+    prm.trace          = trace;
+    prm.ws_partial     = ws_partial;
+    prm.ws_counter     = ws_counter;
+    // TMEM: n_acc accumulators of acc_stride columns, then one scale buffer per shared-memory stage
+    prm.acc_stride = (cfg.bn + 31) & ~31;
+    prm.sf_cols    = sf_cols;
+    const long long units = static_cast<long long>(tiles_p) * tiles_q * splits;
+    const int clusters    = static_cast<int>(std::min<long long>(units, st.sm_count / cg));
+    const bool multi_unit = units > clusters;
+    prm.n_acc = (multi_unit && 2 * prm.acc_stride + 2 * sf_cols <= 512) ? 2 : 1;
+    while(prm.n_acc * prm.acc_stride + stages * sf_cols > 512 && stages > 2)
+        --stages;
+    B200_CHECK(prm.n_acc * prm.acc_stride + stages * sf_cols <= 512, "internal: TMEM budget exceeded");
+    prm.stages       = stages;
+    prm.sf_tmem_base = prm.n_acc * prm.acc_stride;
+    int cols         = 32;
+    while(cols < prm.sf_tmem_base + stages * sf_cols)
+        cols <<= 1;
+    prm.tmem_cols = cols;
+    const PersistentSmem L = make_persistent_smem(cfg.bn, cg, stages, f4_operand, kkind != KIND_BF16);
+    const size_t smem      = L.total + 1024;
+    const int ctas         = clusters * cg;
+    if(kkind == KIND_BF16)
+        launch_persistent_cg<KIND_BF16, SFW_NONE>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
+    else if(kkind == KIND_MXF8 && sfw == SFW_G1250)
+        launch_persistent_cg<KIND_MXF8, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
+    else if(kkind == KIND_MXF4 && sfw == SFW_E8M0_SHUFFLE)
+        launch_persistent_cg<KIND_MXF4, SFW_E8M0_SHUFFLE>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
+    else if(kkind == KIND_MXF4 && sfw == SFW_G1250)
+        launch_persistent_cg<KIND_MXF4, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
+    else if(kkind == KIND_MXF8F4 && sfw == SFW_G1250)
+        launch_persistent_cg<KIND_MXF8F4, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
     else
-    {
-        PersistentParams prm{};
-        prm.rows_p         = static_cast<int>(P.rows);
-        prm.rows_q         = static_cast<int>(Q.rows);
-        prm.num_k_iters    = num_k_iters;
-        prm.kblocks        = kblocks;
-        prm.bn             = cfg.bn;
-        prm.p_mode         = P.mode;
-        prm.q_mode         = Q.mode;
-        prm.sf_groups_p    = 4;
-        prm.sf_groups_q    = sf_groups_q;
-        prm.f4_operand     = f4_operand;
-        prm.transposed_out = cfg.swap;
-        prm.tiles_p        = tiles_p;
-        prm.tiles_q        = tiles_q;
-        prm.splits         = splits;
-        prm.out            = static_cast<__nv_bfloat16*>(prob.out);
-        prm.ldo            = prob.ldo;
-        prm.bias           = prob.bias;
-        prm.bias_is_bf16   = prob.bias_is_bf16;
-        prm.bias_on_q      = cfg.swap ? 0 : 1;
-        prm.alpha          = prob.alpha;
-        prm.beta           = prob.beta;
-        prm.status         = st.status;
-        prm.trace          = trace;
-        prm.ws_partial     = ws_partial;
-        prm.ws_counter     = ws_counter;
-        // TMEM: n_acc accumulators of acc_stride columns, then one scale buffer per shared-memory stage
-        prm.acc_stride = (cfg.bn + 31) & ~31;
-        prm.sf_cols    = sf_cols;
-        const long long units = static_cast<long long>(tiles_p) * tiles_q * splits;
-        const int clusters    = static_cast<int>(std::min<long long>(units, st.sm_count / cg));
-        const bool multi_unit = units > clusters;
-        prm.n_acc = (multi_unit && 2 * prm.acc_stride + stages * sf_cols <= 512) ? 2 : 1;
-        while(prm.n_acc * prm.acc_stride + stages * sf_cols > 512 && stages > 2)
-            --stages;
-        B200_CHECK(prm.n_acc * prm.acc_stride + stages * sf_cols <= 512, "internal: TMEM budget exceeded");
-        prm.stages       = stages;
-        prm.sf_tmem_base = prm.n_acc * prm.acc_stride;
-        int cols         = 32;
-        while(cols < prm.sf_tmem_base + stages * sf_cols)
-            cols <<= 1;
-        prm.tmem_cols = cols;
-        const PersistentSmem L = make_persistent_smem(kkind, cfg.bn, cg, stages, f4_operand);
-        const size_t smem      = L.total + 1024;
-        const int ctas         = clusters * cg;
-        if(kkind == KIND_BF16)
-            launch_persistent_cg<KIND_BF16, SFW_NONE>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
-        else if(kkind == KIND_MXF8 && sfw == SFW_G1250)
-            launch_persistent_cg<KIND_MXF8, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
-        else if(kkind == KIND_MXF4 && sfw == SFW_E8M0_SHUFFLE)
-            launch_persistent_cg<KIND_MXF4, SFW_E8M0_SHUFFLE>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
-        else if(kkind == KIND_MXF4 && sfw == SFW_G1250)
-            launch_persistent_cg<KIND_MXF4, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
-        else if(kkind == KIND_MXF8F4 && sfw == SFW_G1250)
-            launch_persistent_cg<KIND_MXF8F4, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
-        else
-            fail("no kernel instance for kind ", kkind, " with scale layout ", sfw);
-    }
+        fail("no kernel instance for kind ", kkind, " with scale layout ", sfw);
 
     if(trace != nullptr)
         print_trace(st, prob, cfg, tiles_p, tiles_q, splits, stages);
