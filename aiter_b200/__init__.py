@@ -26,7 +26,12 @@ from .gemm_op_a4w4 import (  # noqa: E402,F401
     gemm_mxfp4_asm,
 )
 from .gemm_op_a8w4 import gemm_a8w4_mxfp8  # noqa: E402,F401
-from .gemm_op_a8w8 import gemm_a8w8_mxfp8, gemm_a8w8_mxfp8_noalloc  # noqa: E402,F401
+from .gemm_op_a8w8 import (  # noqa: E402,F401
+    gemm_a8w8_blockscale,
+    gemm_a8w8_blockscale_bpreshuffle,
+    gemm_a8w8_mxfp8,
+    gemm_a8w8_mxfp8_noalloc,
+)
 from .gemm_op_a16w16 import gemm_a16w16_asm, gemm_a16w16_opus, opus_gemm, opus_gemm_a16w16_tune  # noqa: E402,F401
 from .quant import get_torch_quant, per_1x32_f4_quant, per_1x32_f8_scale_f8_quant  # noqa: E402,F401
 from .shuffle import (  # noqa: E402,F401

@@ -77,6 +77,10 @@ SIGNATURES = {
     "gemm_a16w16_asm": (T, T, T, T, T, I, S, I),
     "opus_gemm_a16w16_tune": (T, T, T, T, I, I),
     "opus_gemm": (T, T, T, T, T, T, T),
+    "gemm_a8w8_blockscale": (T, T, T, T, T, I, S),
+    "gemm_a8w8_blockscale_tune": (T, T, T, T, T, I, I),
+    "gemm_a8w8_blockscale_bpreshuffle": (T, T, T, T, T, I, S),
+    "gemm_a8w8_blockscale_bpreshuffle_tune": (T, T, T, T, T, I, I),
     "aiter_b200_gemm_a8w8_mxfp8_noalloc": (T, T, T, T, T, I, I),
 }
 EXPORTS = sorted(

@@ -97,9 +97,9 @@ static void set_out(GemmProblem& p, const aiter_tensor_t* out, const char* fn, l
 
 static void apply_config(GemmProblem& p, const char* kernelName, int log2_splitk, const char* fn)
 {
-    if(kernelName != nullptr && kernelName[0] != 0)
-        B200_CHECK(parse_config_name(kernelName, p.cfg), fn, ": not find kernel ", kernelName);
     p.cfg.log2_splitk = log2_splitk;
+    if(kernelName != nullptr && kernelName[0] != 0) // a "_k<n>" suffix of the name overrides the split argument
+        B200_CHECK(parse_config_name(kernelName, p.cfg), fn, ": not find kernel ", kernelName);
 }
 
 // ------------------------------------------------------------------------------------------- MXFP4
@@ -233,6 +233,85 @@ extern "C" int mxfp8_mxfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_
                                     aiter_tensor_t* out, const char* kernelName, int a_preshuffle, void* stream)
 {
     return safe_call([&] { run_mxfp8("mxfp8_mxfp4_gemm_asm", 1, A, B, ScaleA, ScaleB, out, kernelName, a_preshuffle, stream); });
+}
+
+// ------------------------------------------------------------------------------------------- fp8, fp32 128-block scales
+static void run_blockscale(const char* fn, aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
+                           aiter_tensor_t* w_scale, aiter_tensor_t* Out, int bpreshuffle, void* stream)
+{
+    require_tensor(XQ, fn, "XQ", 2);
+    require_tensor(WQ, fn, "WQ", 2);
+    require_tensor(x_scale, fn, "x_scale", 2);
+    require_tensor(w_scale, fn, "w_scale", 2);
+    require_tensor(Out, fn, "Out", 2);
+    B200_CHECK(is_byte_dtype(XQ->dtype_) && is_byte_dtype(WQ->dtype_), fn, ": XQ and WQ must be fp8 (1-byte) tensors");
+    B200_CHECK(x_scale->dtype_ == AITER_DTYPE_fp32 && w_scale->dtype_ == AITER_DTYPE_fp32, fn,
+               ": scales must be fp32 (convert e8m0 scales first)");
+    B200_CHECK(Out->dtype_ == AITER_DTYPE_bf16, fn, ": only bf16 output is built");
+    const long long M = XQ->shape[0], K = XQ->shape[1], N = WQ->shape[0];
+    B200_CHECK(WQ->shape[1] == K, fn, ": XQ and WQ disagree on K");
+    B200_CHECK(K % 128 == 0, fn, ": K must be a multiple of 128");
+    B200_CHECK(Out->shape[0] == M && Out->shape[1] == N && Out->strides[1] == 1, fn, ": Out must be [M, N], row-contiguous");
+    B200_CHECK(x_scale->shape[0] == M && x_scale->shape[1] == K / 128, fn, ": x_scale must be [M, K/128]");
+    B200_CHECK(w_scale->shape[0] == (N + 127) / 128 && w_scale->shape[1] == K / 128, fn, ": w_scale must be [ceil(N/128), K/128]");
+    require_dense(WQ, fn, "WQ");
+    require_dense(w_scale, fn, "w_scale");
+    require_rows_contiguous(XQ, fn, "XQ");
+    BlockScaleProblem p;
+    p.M = M; p.N = N; p.K = K;
+    p.act = Operand{XQ->ptr, M, K, XQ->strides[0], OPM_ROWMAJOR};
+    p.wgt = Operand{WQ->ptr, N, K, K, bpreshuffle ? OPM_TILE16 : OPM_ROWMAJOR};
+    p.x_scale = static_cast<const float*>(x_scale->ptr);
+    if(bpreshuffle && x_scale->strides[1] == 1 && x_scale->strides[0] == K / 128 && M > 1 && K / 128 > 1)
+    {
+        // the pre-shuffled-weight path takes x_scale stored K-block-major ([K/128][M] in memory), possibly
+        // presented under an [M, K/128] view with contiguous-looking strides (the reference's convention)
+        p.xs_stride_m = 1;
+        p.xs_stride_k = M;
+    }
+    else
+    {
+        p.xs_stride_m = x_scale->strides[0];
+        p.xs_stride_k = x_scale->strides[1];
+    }
+    p.w_scale = static_cast<const float*>(w_scale->ptr);
+    p.out     = Out->ptr;
+    p.ldo     = Out->strides[0];
+    p.device  = XQ->device_id;
+    p.stream  = static_cast<cudaStream_t>(stream);
+    launch_blockscale(p);
+}
+
+extern "C" int gemm_a8w8_blockscale(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale, aiter_tensor_t* w_scale,
+                                    aiter_tensor_t* Out, int splitK, const char* kernelName, void* stream)
+{
+    (void)splitK; (void)kernelName; // one kernel instance serves this path
+    return safe_call([&] { run_blockscale("gemm_a8w8_blockscale", XQ, WQ, x_scale, w_scale, Out, 0, stream); });
+}
+extern "C" int gemm_a8w8_blockscale_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale, aiter_tensor_t* w_scale,
+                                         aiter_tensor_t* Out, int kernelId, int splitK, void* stream)
+{
+    (void)splitK;
+    return safe_call([&] {
+        B200_CHECK(kernelId == 0, "gemm_a8w8_blockscale_tune: Kernel id ", kernelId, " not found");
+        run_blockscale("gemm_a8w8_blockscale_tune", XQ, WQ, x_scale, w_scale, Out, 0, stream);
+    });
+}
+extern "C" int gemm_a8w8_blockscale_bpreshuffle(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
+                                                aiter_tensor_t* w_scale, aiter_tensor_t* Out, int splitK, const char* kernelName,
+                                                void* stream)
+{
+    (void)splitK; (void)kernelName;
+    return safe_call([&] { run_blockscale("gemm_a8w8_blockscale_bpreshuffle", XQ, WQ, x_scale, w_scale, Out, 1, stream); });
+}
+extern "C" int gemm_a8w8_blockscale_bpreshuffle_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
+                                                     aiter_tensor_t* w_scale, aiter_tensor_t* Out, int kernelId, int splitK, void* stream)
+{
+    (void)splitK;
+    return safe_call([&] {
+        B200_CHECK(kernelId == 0, "gemm_a8w8_blockscale_bpreshuffle_tune: Kernel id ", kernelId, " not found");
+        run_blockscale("gemm_a8w8_blockscale_bpreshuffle_tune", XQ, WQ, x_scale, w_scale, Out, 1, stream);
+    });
 }
 
 // ------------------------------------------------------------------------------------------- bf16

@@ -3,6 +3,7 @@
 // needed, cuTensorMapEncodeTiled, is resolved at run time so the library loads without libcuda).
 #include "launch.h"
 #include "gemm_persistent.cuh"
+#include "gemm_blockscale.cuh"
 
 #include <atomic>
 #include <cstdio>
@@ -292,19 +293,27 @@ bool parse_config_name(const char* name, KernelConfig& cfg)
 {
     if(name == nullptr || name[0] == 0)
         return false;
-    int bm = 0, bn = 0, stages = 0;
+    int bm = 0, bn = 0, stages = 0, l2 = -1, consumed = 0;
     char sw = 0;
-    if(std::sscanf(name, "tc5_%dx%d_%c_s%d", &bm, &bn, &sw, &stages) != 4 || (bm != 128 && bm != 256))
+    if(std::sscanf(name, "tc5_%dx%d_%c_s%d%n", &bm, &bn, &sw, &stages, &consumed) != 4 || (bm != 128 && bm != 256))
         return false;
+    if(name[consumed] != 0) // optional "_k<log2 of the K split>"
+    {
+        int more = 0;
+        if(std::sscanf(name + consumed, "_k%d%n", &l2, &more) != 1 || name[consumed + more] != 0 || l2 < 0 || l2 > 8)
+            return false;
+    }
     bool ok = false;
     for(int b : kBnMenu)
         ok |= (b == bn);
-    if(!ok || (sw != 'n' && sw != 't') || stages < 1 || stages > kMaxStages)
+    if(!ok || (sw != 'n' && sw != 't') || stages < 0 || stages > kMaxStages)
         return false;
     cfg.bn     = bn;
     cfg.swap   = (sw == 't');
-    cfg.stages = stages;
+    cfg.stages = stages; // 0 = as many as fit
     cfg.cg     = bm / 128;
+    if(l2 >= 0)
+        cfg.log2_splitk = l2;
     return true;
 }
 
@@ -327,7 +336,7 @@ const char* kernel_menu_text()
 {
     static std::string text = [] {
         std::ostringstream os;
-        os << "kernelName = tc5_<128|256>x<bn>_<n|t>_s<stages>; kernelId = pair*1000 + swap*100 + bn_index*10 + stages (0 = max)\n"
+        os << "kernelName = tc5_<128|256>x<bn>_<n|t>_s<stages>[_k<log2 K split>]; kernelId = pair*1000 + swap*100 + bn_index*10 + stages (0 = max)\n"
            << "  256-row tiles (pair = 1) run on CTA pairs (cta_group::2)\n";
         for(int swap = 0; swap < 2; ++swap)
             for(size_t bi = 0; bi < sizeof(kBnMenu) / sizeof(int); ++bi)
@@ -605,6 +614,56 @@ void launch_gemm(const GemmProblem& prob)
 
     if(trace != nullptr)
         print_trace(st, prob, cfg, tiles_p, tiles_q, splits, stages);
+}
+
+void launch_blockscale(const BlockScaleProblem& prob)
+{
+    B200_CHECK(prob.M > 0 && prob.N > 0 && prob.K > 0, "empty GEMM: M=", prob.M, " N=", prob.N, " K=", prob.K);
+    B200_CHECK(prob.K % 128 == 0, "K must be a multiple of 128 for 128-wide scale blocks (got ", prob.K, ")");
+    int prev_dev = 0;
+    B200_CUDA(cudaGetDevice(&prev_dev));
+    if(prev_dev != prob.device)
+        B200_CUDA(cudaSetDevice(prob.device));
+    struct Restore
+    {
+        int prev, cur;
+        ~Restore()
+        {
+            if(prev != cur)
+                cudaSetDevice(prev);
+        }
+    } restore{prev_dev, prob.device};
+    std::lock_guard<std::mutex> lk(g_mutex);
+    DeviceState& st = device_state(prob.device);
+
+    BlockScaleParams prm{};
+    prm.M           = static_cast<int>(prob.M);
+    prm.N           = static_cast<int>(prob.N);
+    prm.k_blocks    = static_cast<int>(prob.K / 128);
+    prm.a_mode      = prob.act.mode;
+    prm.b_mode      = prob.wgt.mode;
+    prm.x_scale     = prob.x_scale;
+    prm.xs_stride_m = prob.xs_stride_m;
+    prm.xs_stride_k = prob.xs_stride_k;
+    prm.w_scale     = prob.w_scale;
+    prm.out         = static_cast<__nv_bfloat16*>(prob.out);
+    prm.ldo         = prob.ldo;
+    prm.status      = st.status;
+    const int stage_bytes = (kTileP + kBsTileN) * kTileKBytes;
+    int stages            = (st.smem_optin - 2048) / stage_bytes;
+    stages                = std::min(stages, kMaxStages);
+    stages                = std::max(2, std::min(stages, prm.k_blocks));
+    prm.stages            = stages;
+    const size_t smem     = static_cast<size_t>(stage_bytes) * stages + 512 + 1024;
+    CUtensorMap ma = operand_map(prob.act, kTileP, "activation operand");
+    CUtensorMap mb = operand_map(prob.wgt, kBsTileN, "weight operand");
+    static bool attr_done[64] = {};
+    raise_smem_limit(gemm_a8w8_blockscale_kernel, attr_done);
+    dim3 grid(static_cast<unsigned>((prob.M + kTileP - 1) / kTileP), static_cast<unsigned>((prob.N + kBsTileN - 1) / kBsTileN), 1);
+    B200_CHECK(grid.y <= 65535, "N too large");
+    gemm_a8w8_blockscale_kernel<<<grid, kBlockScaleThreads, smem, prob.stream>>>(ma, mb, prm);
+    B200_CUDA(cudaGetLastError());
+    g_launches.fetch_add(1);
 }
 
 } // namespace b200

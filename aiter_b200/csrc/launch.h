@@ -103,6 +103,22 @@ bool config_from_id(int kernel_id, KernelConfig& cfg);
 const char* kernel_menu_text();
 
 void launch_gemm(const GemmProblem& prob);
+
+// FP8 x FP8 with fp32 scales per 128-wide K block (x_scale[m][kb] at x_scale + m*xs_stride_m + kb*xs_stride_k,
+// w_scale [ceil(N/128)][K/128] dense), bf16 output.
+struct BlockScaleProblem
+{
+    long long M = 0, N = 0, K = 0;
+    Operand act, wgt;
+    const float* x_scale = nullptr;
+    long long xs_stride_m = 0, xs_stride_k = 0;
+    const float* w_scale = nullptr;
+    void* out = nullptr;
+    long long ldo = 0;
+    int device = 0;
+    cudaStream_t stream = nullptr;
+};
+void launch_blockscale(const BlockScaleProblem& prob);
 void read_device_status(int device, unsigned int out_words[4]);
 unsigned long long launch_count();
 int device_sm_count(int device);

@@ -4,10 +4,50 @@ from __future__ import annotations
 import torch
 from torch import Tensor
 
-from . import _ffi, dtypes
+from . import _ffi, dtypes, fp4_utils
 from .config import TunedTable
 
 _mxfp8_table = TunedTable("a8w8_mxfp8")
+_blockscale_table = TunedTable("a8w8_blockscale")
+_blockscale_bpreshuffle_table = TunedTable("a8w8_blockscale_bpreshuffle")
+
+
+def get_CKGEMM_config(M: int, N: int, K: int, bpreshuffle: bool = False):
+    """Tuned row of the fp32-blockscale tables for (M, N, K), or None (reference: gemm_op_a8w8.py:441-483)."""
+    return (_blockscale_bpreshuffle_table if bpreshuffle else _blockscale_table).lookup(M, N, K)
+
+
+def _fp32_scale(s: Tensor) -> Tensor:
+    return fp4_utils.e8m0_to_f32(s) if s.dtype in (dtypes.fp8_e8m0, torch.uint8) else s
+
+
+def gemm_a8w8_blockscale(XQ: Tensor, WQ: Tensor, x_scale: Tensor, w_scale: Tensor, dtype: torch.dtype = dtypes.bf16,
+                         isBpreshuffled: bool = False) -> Tensor:
+    """Y[M,N] = (XQ * x_scale) @ (WQ * w_scale)^T with fp32 scales per 128-wide K block: x_scale [M, K/128],
+    w_scale [ceil(N/128), K/128]; WQ row-major [N, K] (reference: gemm_op_a8w8.py:797-865)."""
+    assert dtype in (dtypes.bf16,), f"Output {dtype=} is currently not supported in gemm_a8w8"
+    if isBpreshuffled:
+        return gemm_a8w8_blockscale_bpreshuffle(XQ, WQ, x_scale, w_scale, dtype)
+    m, n, k = XQ.shape[0], WQ.shape[0], XQ.shape[1]
+    Y = torch.empty(m, n, dtype=dtype, device=XQ.device)
+    cfg = get_CKGEMM_config(m, n, k)
+    splitK, kernelName = (int(cfg.get("splitK") or 0), str(cfg.get("kernelName") or "")) if cfg is not None else (0, "")
+    _ffi.call("gemm_a8w8_blockscale", XQ, WQ, _fp32_scale(x_scale), _fp32_scale(w_scale), Y, splitK, kernelName or None)
+    return Y
+
+
+def gemm_a8w8_blockscale_bpreshuffle(XQ: Tensor, WQ: Tensor, x_scale: Tensor, w_scale: Tensor,
+                                     dtype: torch.dtype = dtypes.bf16) -> Tensor:
+    """Same math with WQ (16,16)-shuffled and x_scale stored K-block-major ([K/128][M] in memory, passed either
+    as the transposed-strided [M, K/128] view or re-viewed as a contiguous [M, K/128]); e8m0 scales are widened
+    to fp32 first (reference: gemm_op_a8w8.py:895-1055)."""
+    assert dtype in (dtypes.bf16,), f"Output {dtype=} is currently not supported in gemm_a8w8"
+    m, n, k = XQ.shape[0], WQ.shape[0], XQ.shape[1]
+    Y = torch.empty(m, n, dtype=dtype, device=XQ.device)
+    cfg = get_CKGEMM_config(m, n, k, bpreshuffle=True)
+    splitK, kernelName = (int(cfg.get("splitK") or 0), str(cfg.get("kernelName") or "")) if cfg is not None else (0, "")
+    _ffi.call("gemm_a8w8_blockscale_bpreshuffle", XQ, WQ, _fp32_scale(x_scale), _fp32_scale(w_scale), Y, splitK, kernelName or None)
+    return Y
 
 
 def get_MXFP8_config(M: int, N: int, K: int):

@@ -1,0 +1,276 @@
+"""Tuner: measures every candidate kernel configuration for a list of (M, N, K) shapes on the GPU it runs on
+and writes the winners into a tuned table in the reference's CSV schema.
+
+    python -m aiter_b200.tune --family a8w8_mxfp8 --baseline            # the benchmark shapes
+    python -m aiter_b200.tune --family a4w4 --shapes "32,7168,2048;4096,7168,2048" -o my.csv
+
+Same flow as the reference's tuners (aiter/utility/base_tuner.py:1537-1722,
+csrc/ck_gemm_a4w4_blockscale/gemm_a4w4_blockscale_tune.py): candidates come from the kernel menu, every
+candidate is checked against a torch reference before it may win (errRatio gate, tolerance rtol = atol = 1e-2),
+timing is device time with rotating inputs larger than L2 (CUDA-graph replay), rows carry
+us / tflops / bw / errRatio, shapes already present in the output file are skipped unless --retune, and the
+file is rewritten after every shape so an interrupted run can be resumed.
+"""
+from __future__ import annotations
+
+import argparse
+import csv
+import os
+import sys
+
+import torch
+
+from . import _ffi, config, dtypes, fp4_utils, shuffle
+
+FAMILIES = {
+    # family -> (table name, problem kind id of aiter_b200_heuristic_name, csv header)
+    "a4w4": ("a4w4", 2),
+    "a8w8_mxfp8": ("a8w8_mxfp8", 1),
+    "a8w4_mxfp8": ("a8w4_mxfp8", 3),
+    "bf16": ("bf16", 0),
+}
+HEADER = ["gfx", "cu_num", "M", "N", "K", "kernelId", "splitK", "us", "kernelName", "tflops", "bw", "errRatio"]
+BF16_HEADER = ["gfx", "cu_num", "M", "N", "K", "bias", "dtype", "outdtype", "scaleAB", "bpreshuffle", "libtype", "solidx", "splitK",
+               "us", "kernelName", "err_ratio", "tflops", "bw"]
+BASELINE_SHAPES = {
+    "bf16": [(64, 1024, 1024), (1024, 8192, 8192), (8192, 8192, 8192)],
+    "a8w8_mxfp8": [(m, 4096, 4096) for m in (1, 16, 128, 1024, 8192)],
+    "a4w4": [(m, n, k) for (n, k) in ((7168, 2048), (24576, 1536), (7168, 16384)) for m in (1, 32, 256, 4096, 16384)] + [(16384, 7168, 7168)],
+    "a8w4_mxfp8": [(1 << e, 8192, 8192) for e in range(15)],
+}
+BN_MENU = [16, 32, 64, 128, 256, 192, 224, 96, 160]
+
+
+def kernel_id(pair: int, swap: int, bn: int, stages: int) -> int:
+    return pair * 1000 + swap * 100 + BN_MENU.index(bn) * 10 + stages
+
+
+def kernel_name(pair: int, swap: int, bn: int, stages: int, log2_splitk: int | None = None) -> str:
+    name = f"tc5_{256 if pair else 128}x{bn}_{'t' if swap else 'n'}_s{stages}"
+    return name if log2_splitk is None else f"{name}_k{log2_splitk}"
+
+
+def candidates(M: int, N: int, K: int, family: str):
+    """(pair, swap, bn, stages, log2_splitk) tuples worth timing for this shape."""
+    elems = {"bf16": 64, "a4w4": 256}.get(family, 128)
+    k_iters = max(1, (K + elems - 1) // elems)
+    out = []
+    splits = [s for s in range(0, 6) if (k_iters >> s) >= 2] or [0]
+    if M <= 256:
+        for bn in (16, 32, 64, 128, 256):
+            if bn < M or (bn >= 2 * max(M, 16) and bn > 16):
+                continue
+            for st in (4, 8):
+                for sk in splits:
+                    out.append((0, 1, bn, st, sk))
+    if M >= 64:
+        for pair in (0, 1):
+            for bn in (64, 128, 192, 224, 256):
+                if pair and (M < 512 or bn < 128):
+                    continue
+                if bn > 128 and N % bn and N % 128 == 0 and bn not in (256,):
+                    pass  # ragged last tile is allowed, just less efficient
+                for sk in ([0] if M >= 2048 else splits[:4]):
+                    out.append((pair, 0, bn, 0, sk))
+    return out
+
+
+# --------------------------------------------------------------------------------------- problems
+def _rand_u8(lo, hi, *shape, device):
+    return torch.randint(lo, hi, shape, dtype=torch.uint8, device=device)
+
+
+def make_problem(family: str, M: int, N: int, K: int, device, seed: int):
+    """-> (args for the entry point, reference fp32 output of the first `ref_rows` rows, ref_rows)."""
+    torch.manual_seed(seed)
+    ref_rows = min(M, 256)
+    if family == "bf16":
+        a = (torch.randn(M, K, device=device) * 0.1).to(torch.bfloat16)
+        b = (torch.randn(N, K, device=device) * 0.1).to(torch.bfloat16)
+        ref = a[:ref_rows].float() @ b.float().T
+        return (a, b), ref, ref_rows
+    sa = _rand_u8(122, 130, M, K // 32, device=device)
+    sb = _rand_u8(122, 130, N, K // 32, device=device)
+    sa_f = fp4_utils.e8m0_to_f32(sa[:ref_rows]).repeat_interleave(32, dim=1)
+    sb_f = fp4_utils.e8m0_to_f32(sb).repeat_interleave(32, dim=1)
+    if family == "a4w4":
+        a, b = _rand_u8(0, 256, M, K // 2, device=device), _rand_u8(0, 256, N, K // 2, device=device)
+        ref = (fp4_utils.mxfp4_to_f32(a[:ref_rows]) * sa_f) @ (fp4_utils.mxfp4_to_f32(b) * sb_f).T
+        out = torch.empty(((M + 31) // 32 * 32, N), dtype=torch.bfloat16, device=device)
+        return (a, shuffle.shuffle_weight(b), shuffle.shuffle_scale(sa), shuffle.shuffle_scale(sb), out), ref, ref_rows
+    a = _rand_u8(0, 0x78, M, K, device=device).view(torch.float8_e4m3fn)
+    if family == "a8w8_mxfp8":
+        b = _rand_u8(0, 0x78, N, K, device=device).view(torch.float8_e4m3fn)
+        ref = (a[:ref_rows].float() * sa_f) @ (b.float() * sb_f).T
+    else:
+        b = _rand_u8(0, 256, N, K // 2, device=device)
+        ref = (a[:ref_rows].float() * sa_f) @ (fp4_utils.mxfp4_to_f32(b) * sb_f).T
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+    return (a, shuffle.shuffle_mxfp8fp4_b(b), shuffle.shuffle_mxfp8fp4_scale(sa), shuffle.shuffle_mxfp8fp4_scale(sb), out), ref, ref_rows
+
+
+def run_candidate(family: str, args, cand):
+    pair, swap, bn, st, sk = cand
+    kid = kernel_id(pair, swap, bn, st)
+    if family == "bf16":
+        a, b = args
+        y = torch.empty((1, a.shape[0], b.shape[0]), dtype=torch.bfloat16, device=a.device)
+        _ffi.call("opus_gemm_a16w16_tune", a[None], b[None], y, None, kid, sk)
+        return y[0]
+    if family == "a4w4":
+        a, b, sa, sb, out = args
+        _ffi.call("gemm_a4w4_blockscale_tune", a, b, sa, sb, out, kid, sk)
+        return out[: a.shape[0]]
+    a, b, sa, sb, out = args
+    # these entry points take only a kernel name: the K split travels as its "_k<n>" suffix
+    fn = "mxfp8_mxfp8_gemm_asm" if family == "a8w8_mxfp8" else "mxfp8_mxfp4_gemm_asm"
+    _ffi.call(fn, a, b, sa, sb, out, kernel_name(pair, swap, bn, st, sk), 0)
+    return out
+
+
+def err_ratio(ref: torch.Tensor, out: torch.Tensor, rows: int, rtol=1e-2, atol=1e-2) -> float:
+    o = out[:rows].float()
+    bad = ~((ref - o).abs() <= atol + rtol * o.abs())
+    return float(bad.float().mean().item())
+
+
+def time_candidate(family, arg_sets, cand, iters=20) -> float:
+    """Device microseconds per call, CUDA-graph replay over rotating argument sets."""
+    n = len(arg_sets)
+    s = _side_stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for i in range(max(3, n)):
+            run_candidate(family, arg_sets[i % n], cand)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for i in range(iters):
+                run_candidate(family, arg_sets[i % n], cand)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        g.replay()
+        e1.record(s)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / iters
+
+
+_STREAM = None
+
+
+def _side_stream():
+    """One capture stream for the whole run: the library keeps a split-K workspace per stream."""
+    global _STREAM
+    if _STREAM is None:
+        _STREAM = torch.cuda.Stream()
+    return _STREAM
+
+
+def bytes_of(family, M, N, K):
+    bpe = {"bf16": (2, 2), "a4w4": (0.5, 0.5), "a8w8_mxfp8": (1, 1), "a8w4_mxfp8": (1, 0.5)}[family]
+    return int(M * K * bpe[0] + N * K * bpe[1] + 2 * M * N)  # scale bytes not counted, as in the reference's `bw`
+
+
+def tune_shape(family, M, N, K, device, verbose=False):
+    problem_bytes = bytes_of(family, M, N, K)
+    n_sets = max(2, min(8, int(2.2 * 126e6 // max(problem_bytes, 1)) + 1))
+    sets, ref, rows = [], None, 0
+    for i in range(n_sets):
+        args, r, rows_i = make_problem(family, M, N, K, device, seed=i)
+        sets.append(args)
+        if i == 0:
+            ref, rows = r, rows_i
+    best = None
+    for cand in candidates(M, N, K, family):
+        try:
+            out = run_candidate(family, sets[0], cand)
+            torch.cuda.synchronize()
+            if _ffi.device_status(device.index or 0) != (0, 0, 0, 0):
+                continue
+            err = err_ratio(ref, out, rows)
+            if err > 0.0:
+                if verbose:
+                    print(f"  {cand}: rejected, errRatio {err:.4f}", file=sys.stderr)
+                continue
+            us = time_candidate(family, sets, cand)
+        except RuntimeError as e:
+            if verbose:
+                print(f"  {cand}: {str(e)[:100]}", file=sys.stderr)
+            continue
+        if verbose:
+            print(f"  {cand}: {us:.2f} us", file=sys.stderr)
+        if best is None or us < best[1]:
+            best = (cand, us, err)
+    return best
+
+
+def write_rows(path, family, rows):
+    header = BF16_HEADER if family == "bf16" else HEADER
+    tmp = path + ".tmp"
+    with open(tmp, "w", newline="") as f:
+        w = csv.DictWriter(f, fieldnames=header)
+        w.writeheader()
+        for key in sorted(rows):
+            w.writerow(rows[key])
+    os.replace(tmp, path)
+
+
+def read_rows(path, family):
+    rows = {}
+    if os.path.exists(path):
+        with open(path, newline="") as f:
+            for r in csv.DictReader(f):
+                if r.get("M"):
+                    rows[(r["gfx"], int(r["cu_num"]), int(r["M"]), int(r["N"]), int(r["K"]))] = r
+    return rows
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--family", choices=sorted(FAMILIES), required=True)
+    ap.add_argument("--shapes", default="", help='"M,N,K;M,N,K;..."')
+    ap.add_argument("--baseline", action="store_true", help="tune the benchmark shapes of this family")
+    ap.add_argument("-o", "--output", default=None, help="CSV to update (default: the packaged table)")
+    ap.add_argument("--retune", action="store_true", help="re-measure shapes already in the file")
+    ap.add_argument("-v", "--verbose", action="store_true")
+    args = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        raise SystemExit("the tuner measures on the GPU: no CUDA device found")
+    device = torch.device("cuda", torch.cuda.current_device())
+    table, _ = FAMILIES[args.family]
+    path = args.output or os.path.join(config.CONFIG_DIR, config.TABLES[table][1])
+    shapes = [tuple(int(v) for v in s.split(",")) for s in args.shapes.split(";") if s.strip()]
+    if args.baseline:
+        shapes += BASELINE_SHAPES[args.family]
+    gfx, cu = config.get_gfx(), config.get_cu_num()
+    rows = read_rows(path, args.family)
+    for (M, N, K) in shapes:
+        key = (gfx, cu, M, N, K)
+        if key in rows and not args.retune:
+            print(f"{args.family} {M}x{N}x{K}: already tuned, skipped")
+            continue
+        best = tune_shape(args.family, M, N, K, device, args.verbose)
+        if best is None:
+            print(f"{args.family} {M}x{N}x{K}: no valid candidate")
+            continue
+        (pair, swap, bn, st, sk), us, err = best
+        name = kernel_name(pair, swap, bn, st) if args.family in ("a4w4", "bf16") else kernel_name(pair, swap, bn, st, sk)
+        tflops = round(2.0 * M * N * K / us / 1e6, 2)
+        bw = round(bytes_of(args.family, M, N, K) / us / 1e3, 2)
+        row = {"gfx": gfx, "cu_num": cu, "M": M, "N": N, "K": K, "splitK": sk, "us": round(us, 4), "kernelName": name,
+               "tflops": tflops, "bw": bw}
+        if args.family == "bf16":
+            row.update({"bias": False, "dtype": "torch.bfloat16", "outdtype": "torch.bfloat16", "scaleAB": False,
+                        "bpreshuffle": False, "libtype": "opus", "solidx": kernel_id(pair, swap, bn, st), "err_ratio": err})
+        else:
+            row.update({"kernelId": kernel_id(pair, swap, bn, st), "errRatio": err})
+        rows[key] = row
+        write_rows(path, args.family, rows)
+        print(f"{args.family} {M}x{N}x{K}: {name} splitK 2^{sk}  {us:.2f} us  {tflops} TFLOPS  {bw} GB/s")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

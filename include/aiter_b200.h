@@ -91,6 +91,24 @@ AITER_B200_API int mxfp8_mxfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, ai
                                         aiter_tensor_t* ScaleB, aiter_tensor_t* out, const char* kernelName,
                                         int a_preshuffle, void* stream);
 
+/* ---- FP8 x FP8 with fp32 scales per 128-wide K block -> bf16.  csrc/include/rocm_ops.hpp:725-765,
+ * csrc/ck_gemm_a8w8_blockscale/gemm_a8w8_blockscale.cu:82-112, csrc/py_itfs_cu/asm_a8w8_blockscale_bpreshuffle.cu:59-73.
+ * XQ [M,K] e4m3, WQ [N,K] e4m3 (plain, or (16,16)-shuffled for the _bpreshuffle forms), x_scale [M,K/128] fp32
+ * (stored K-block-major for the _bpreshuffle forms), w_scale [ceil(N/128),K/128] fp32, Out [M,N] bf16, K % 128 == 0.
+ * One kernel instance serves the path: kernelName / splitK are accepted and ignored, kernelId must be 0. */
+AITER_B200_API int gemm_a8w8_blockscale(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
+                                        aiter_tensor_t* w_scale, aiter_tensor_t* Out, int splitK,
+                                        const char* kernelName, void* stream);
+AITER_B200_API int gemm_a8w8_blockscale_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
+                                             aiter_tensor_t* w_scale, aiter_tensor_t* Out, int kernelId,
+                                             int splitK, void* stream);
+AITER_B200_API int gemm_a8w8_blockscale_bpreshuffle(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
+                                                    aiter_tensor_t* w_scale, aiter_tensor_t* Out, int splitK,
+                                                    const char* kernelName, void* stream);
+AITER_B200_API int gemm_a8w8_blockscale_bpreshuffle_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ,
+                                                         aiter_tensor_t* x_scale, aiter_tensor_t* w_scale,
+                                                         aiter_tensor_t* Out, int kernelId, int splitK, void* stream);
+
 /* ---- MXFP4 x MXFP4 with the (m/32,k/4,32,4) scale layout.  csrc/py_itfs_cu/asm_f4gemm.cu:396-412
  * (bf16 output only: out_scale must be NULL). */
 AITER_B200_API int mxfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* ScaleA,

@@ -278,6 +278,43 @@ def test_a8w4_table_dispatch(ab, tmp_path, monkeypatch):
     assert_healthy(ab)
 
 
+# ------------------------------------------------------------------------------------------- fp8, fp32 128-block scales
+@pytest.mark.parametrize("M,N,K,bpre", [(1, 128, 128, False), (48, 512, 1024, False), (48, 512, 1024, True), (300, 1024, 2048, True),
+                                       (128, 4096, 4096, False), (130, 320, 640, True), (1024, 2048, 512, False)])
+def test_a8w8_blockscale_fp32_scales(ab, M, N, K, bpre):
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn)
+    w = torch.randn(N, K, generator=g).to(torch.float8_e4m3fn)
+    xs = torch.rand(M, K // 128, generator=g) + 0.25
+    ws = torch.rand((N + 127) // 128, K // 128, generator=g) + 0.25
+    ref = ox.gemm_a8w8_blockscale_ref(x.view(torch.uint8).numpy(), w.view(torch.uint8).numpy(), xs.numpy(), ws.numpy())
+    if bpre:
+        xs_t = xs.T.contiguous().cuda()  # K-block-major storage
+        wq = ab.shuffle_weight(w.cuda(), layout=(16, 16))
+        out = ab.gemm_a8w8_blockscale_bpreshuffle(x.cuda(), wq, xs_t.view(M, K // 128), ws.cuda())
+        check(ref, out, what=f"blockscale bpreshuffle (re-viewed x_scale) {M}x{N}x{K}")
+        out = ab.gemm_a8w8_blockscale_bpreshuffle(x.cuda(), wq, xs_t.T, ws.cuda())
+        check(ref, out, what=f"blockscale bpreshuffle (strided x_scale) {M}x{N}x{K}")
+    else:
+        out = ab.gemm_a8w8_blockscale(x.cuda(), w.cuda(), xs.cuda(), ws.cuda())
+        check(ref, out, what=f"blockscale {M}x{N}x{K}")
+    assert_healthy(ab)
+
+
+def test_a8w8_blockscale_e8m0_scales_are_widened(ab):
+    M, N, K = 64, 256, 512
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn)
+    w = torch.randn(N, K, generator=g).to(torch.float8_e4m3fn)
+    xs = torch.randint(124, 130, (M, K // 128), generator=g, dtype=torch.uint8)
+    ws = torch.randint(124, 130, (N // 128, K // 128), generator=g, dtype=torch.uint8)
+    ref = ox.gemm_a8w8_blockscale_ref(x.view(torch.uint8).numpy(), w.view(torch.uint8).numpy(),
+                                      ox.e8m0_to_f32(xs.numpy()), ox.e8m0_to_f32(ws.numpy()))
+    out = ab.gemm_a8w8_blockscale(x.cuda(), w.cuda(), xs.cuda().view(ab.dtypes.fp8_e8m0), ws.cuda().view(ab.dtypes.fp8_e8m0))
+    check(ref, out, what="blockscale with e8m0 scales")
+    assert_healthy(ab)
+
+
 # ------------------------------------------------------------------------------------------- persistent paths
 def test_many_units_per_cta(ab):
     # more output tiles than SMs: the persistent loop, both accumulators and the stage ring wrap many times
