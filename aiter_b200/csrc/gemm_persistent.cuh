@@ -111,6 +111,22 @@ __device__ __forceinline__ void e2m1x8_to_e4m3x8(uint32_t w, uint32_t& lo, uint3
     hi = __byte_perm(kLutLo, kLutHi, h & 0x7777u) | __byte_perm(kSign, 0u, (h >> 3) & 0x1111u);
 }
 
+// Stage ring position kept by increments: these loops run on one thread (or one warp) per K tile, where a
+// division by the run-time stage count would cost more than the work itself.
+struct Ring
+{
+    int s;
+    uint32_t phase;
+    __device__ __forceinline__ void advance(int stages)
+    {
+        if(++s == stages)
+        {
+            s = 0;
+            phase ^= 1u;
+        }
+    }
+};
+
 // Position in the static work list shared by all roles of a CTA.
 struct WorkIter
 {
@@ -163,6 +179,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     const bool tracing = (prm.trace != nullptr) && blockIdx.x == 0;
     auto stamp = [&](int slot) { if(tracing && slot < 64) prm.trace[slot] = static_cast<unsigned long long>(clock64()); };
     if(threadIdx.x == 0) stamp(0);
+    if(prm.trace != nullptr && threadIdx.x == 0 && blockIdx.x < 160)
+        prm.trace[64 + 2 * blockIdx.x] = global_timer_ns();
 
     const int splits      = prm.splits;
     const int total_units = prm.tiles_p * prm.tiles_q * splits;
@@ -235,8 +253,9 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
         const int tile = w.u / splits;
         w.tq           = tile % prm.tiles_q;
         w.tp           = tile / prm.tiles_q;
-        w.it_beg       = static_cast<int>((static_cast<long long>(prm.num_k_iters) * w.z) / splits);
-        w.n_iters      = static_cast<int>((static_cast<long long>(prm.num_k_iters) * (w.z + 1)) / splits) - w.it_beg;
+        // num_k_iters * splits < 2^31 (checked on the host): 32-bit divisions keep this off the critical path
+        w.it_beg       = static_cast<int>(static_cast<uint32_t>(prm.num_k_iters * w.z) / static_cast<uint32_t>(splits));
+        w.n_iters      = static_cast<int>(static_cast<uint32_t>(prm.num_k_iters * (w.z + 1)) / static_cast<uint32_t>(splits)) - w.it_beg;
         w.i            = 0;
     };
     auto first_work = [&]() {
@@ -268,10 +287,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             const uint32_t tile_off = is_p ? 0u : L.q_off;
             int g = 0;
             bool ok = true;
-            for(WorkIter w = first_work(); w.valid && ok; next_iter(w), ++g)
+            Ring ring{0, 0};
+            for(WorkIter w = first_work(); w.valid && ok; next_iter(w), ++g, ring.advance(S))
             {
-                const int s = g % S;
-                ok = bounded_wait(empty_bar(s), ((g / S) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_PRODUCER, g);
+                const int s = ring.s;
+                ok = bounded_wait(empty_bar(s), ring.phase ^ 1u, abort_f, prm.status, ST_TIMEOUT_PRODUCER, g);
                 if(!ok)
                     break;
                 const int row0 = is_p ? (w.tp * CG + static_cast<int>(crank)) * kTileP
@@ -327,10 +347,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             const uint32_t sfq_bytes = static_cast<uint32_t>((bn + 31) / 32) * kSfChunk;
             int g = 0;
             bool ok = true;
-            for(WorkIter w = first_work(); w.valid && ok; next_iter(w), ++g)
+            Ring ring{0, 0};
+            for(WorkIter w = first_work(); w.valid && ok; next_iter(w), ++g, ring.advance(S))
             {
-                const int s = g % S;
-                ok = bounded_wait(empty_bar(s), ((g / S) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_PRODUCER, 0x20000 + g);
+                const int s = ring.s;
+                ok = bounded_wait(empty_bar(s), ring.phase ^ 1u, abort_f, prm.status, ST_TIMEOUT_PRODUCER, 0x20000 + g);
                 if(!ok)
                     break;
                 const int row_p0     = (w.tp * CG + static_cast<int>(crank)) * kTileP;
@@ -367,55 +388,71 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             const uint32_t q_lay = q_tiled ? 0u : 2u;
             const uint32_t q_adv = q_tiled ? 2u * q_rows_cta * 16u : 32u;
 
+            // The issue loop runs on one thread and must stay well under the 512 cycles the four MMAs of a stage
+            // take: descriptors are a base word plus small adds, nothing is divided, nothing is re-derived.
+            const uint32_t p_hi = static_cast<uint32_t>(make_smem_desc(0, p_lbo, p_sbo, p_lay) >> 32);
+            const uint32_t q_hi = static_cast<uint32_t>(make_smem_desc(0, q_lbo, q_sbo, q_lay) >> 32);
+            const uint32_t p_lo0 = static_cast<uint32_t>(make_smem_desc(smem_base, p_lbo, p_sbo, p_lay));
+            const uint32_t q_lo0 = static_cast<uint32_t>(make_smem_desc(smem_base + L.q_off, q_lbo, q_sbo, q_lay));
+            const uint32_t stage_step = L.stage_bytes >> 4, p_step = p_adv >> 4, q_step = q_adv >> 4;
+            uint32_t idk[4];
+#pragma unroll
+            for(int k = 0; k < 4; ++k)
+                idk[k] = (KIND == KIND_BF16) ? idesc
+                         : (KIND == KIND_MXF4) ? idesc_with_sf(idesc, (k & 1) * 2, (k & 1) * 2)
+                                               : idesc_with_sf(idesc, k, k);
+            const uint32_t sf0 = tmem_base + prm.sf_tmem_base;
+
             int g = 0, uc = 0;
             bool ok = true;
+            Ring ring{0, 0};
+            int a = 0;
+            uint32_t acc_phase = 1; // parity to wait on for "accumulator a is free"; a fresh barrier passes parity 1
             for(WorkIter w = first_work(); w.valid && ok; next_unit(w), ++uc)
             {
-                const int a          = uc % prm.n_acc;
                 const uint32_t d_col = tmem_base + a * prm.acc_stride;
-                ok = bounded_wait(acc_empty_bar(a), ((uc / prm.n_acc) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_MMA_FULL, 0x10000 + uc);
+                ok = bounded_wait(acc_empty_bar(a), acc_phase, abort_f, prm.status, ST_TIMEOUT_MMA_FULL, 0x10000 + uc);
                 if(!ok)
                     break;
                 tc_fence_after_sync();
-                for(int i = 0; i < w.n_iters; ++i, ++g)
+                const int n_iters = w.n_iters;
+                for(int i = 0; i < n_iters; ++i, ++g, ring.advance(S))
                 {
-                    const int s          = g % S;
-                    const uint32_t phase = (g / S) & 1;
-                    ok = bounded_wait(full_bar(s), phase, abort_f, prm.status, ST_TIMEOUT_MMA_FULL, g);
+                    const int s = ring.s;
+                    ok = bounded_wait(full_bar(s), ring.phase, abort_f, prm.status, ST_TIMEOUT_MMA_FULL, g);
                     if(ok && kScaled)
-                        ok = bounded_wait(ready_bar(s), phase, abort_f, prm.status, ST_TIMEOUT_MMA_SF, g);
+                        ok = bounded_wait(ready_bar(s), ring.phase, abort_f, prm.status, ST_TIMEOUT_MMA_SF, g);
                     if(!ok)
                         break;
                     tc_fence_after_sync();
                     if(g < 14) stamp(5 + 4 * g);
-                    const uint32_t stage = smem_base + s * L.stage_bytes;
-                    const uint32_t tsfp  = tmem_base + prm.sf_tmem_base + s * prm.sf_cols;
-                    const uint32_t tsfq  = tsfp + 4 * kAtomsK;
+                    const uint32_t p_lo = p_lo0 + s * stage_step;
+                    const uint32_t q_lo = q_lo0 + s * stage_step;
+                    const uint32_t tsfp = sf0 + s * prm.sf_cols;
+                    const uint32_t tsfq = tsfp + 4 * kAtomsK;
 #pragma unroll
                     for(int k = 0; k < 4; ++k)
                     {
-                        const uint64_t pd  = make_smem_desc(stage + k * p_adv, p_lbo, p_sbo, p_lay);
-                        const uint64_t qd  = make_smem_desc(stage + L.q_off + k * q_adv, q_lbo, q_sbo, q_lay);
-                        const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                        const uint64_t pd  = pack_u64(p_lo + k * p_step, p_hi);
+                        const uint64_t qd  = pack_u64(q_lo + k * q_step, q_hi);
+                        const uint32_t acc = (k > 0) ? 1u : static_cast<uint32_t>(i > 0);
                         if(CG == 1)
                         {
                             if(KIND == KIND_BF16)
-                                mma_f16(d_col, pd, qd, idesc, acc);
+                                mma_f16(d_col, pd, qd, idk[k], acc);
                             else if(KIND == KIND_MXF8 || KIND == KIND_MXF8F4)
-                                mma_mxf8f6f4(d_col, pd, qd, idesc_with_sf(idesc, k, k), acc, tsfp, tsfq);
+                                mma_mxf8f6f4(d_col, pd, qd, idk[k], acc, tsfp, tsfq);
                             else
-                                mma_mxf4(d_col, pd, qd, idesc_with_sf(idesc, (k & 1) * 2, (k & 1) * 2), acc, tsfp + (k >> 1) * 4,
-                                         tsfq + (k >> 1) * 8);
+                                mma_mxf4(d_col, pd, qd, idk[k], acc, tsfp + (k >> 1) * 4, tsfq + (k >> 1) * 8);
                         }
                         else
                         {
                             if(KIND == KIND_BF16)
-                                mma_f16_2cta(d_col, pd, qd, idesc, acc);
+                                mma_f16_2cta(d_col, pd, qd, idk[k], acc);
                             else if(KIND == KIND_MXF8 || KIND == KIND_MXF8F4)
-                                mma_mxf8f6f4_2cta(d_col, pd, qd, idesc_with_sf(idesc, k, k), acc, tsfp, tsfq);
+                                mma_mxf8f6f4_2cta(d_col, pd, qd, idk[k], acc, tsfp, tsfq);
                             else
-                                mma_mxf4_2cta(d_col, pd, qd, idesc_with_sf(idesc, (k & 1) * 2, (k & 1) * 2), acc, tsfp + (k >> 1) * 4,
-                                              tsfq + (k >> 1) * 8);
+                                mma_mxf4_2cta(d_col, pd, qd, idk[k], acc, tsfp + (k >> 1) * 4, tsfq + (k >> 1) * 8);
                         }
                     }
                     if(CG == 1)
@@ -429,6 +466,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                         tc_commit(acc_full_bar(a));
                     else
                         tc_commit_2cta(acc_full_bar(a), 3);
+                }
+                if(++a == prm.n_acc)
+                {
+                    a = 0;
+                    acc_phase ^= 1u;
                 }
             }
             stamp(60);
@@ -460,14 +502,15 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
 
             int g = 0;
             bool ok = true;
-            for(WorkIter w = first_work(); w.valid && ok; next_iter(w), ++g)
+            Ring ring{0, 0};
+            for(WorkIter w = first_work(); w.valid && ok; next_iter(w), ++g, ring.advance(S))
             {
-                const int s = g % S;
+                const int s = ring.s;
                 // raw scales of stage s have landed (their producer waited for the previous pass's MMAs, so the
                 // TMEM scale buffer of stage s is free as well); mixed kind: so has the packed e2m1 tile
-                ok = bounded_wait(sfraw_bar(s), (g / S) & 1, abort_f, prm.status, ST_TIMEOUT_SFWARP, g);
+                ok = bounded_wait(sfraw_bar(s), ring.phase, abort_f, prm.status, ST_TIMEOUT_SFWARP, g);
                 if(ok && kMixed)
-                    ok = bounded_wait(staged_bar(s), (g / S) & 1, abort_f, prm.status, ST_TIMEOUT_SFWARP, 0x10000 + g);
+                    ok = bounded_wait(staged_bar(s), ring.phase, abort_f, prm.status, ST_TIMEOUT_SFWARP, 0x10000 + g);
                 ok = __all_sync(0xffffffffu, ok);
                 if(!ok)
                     break;
@@ -549,7 +592,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                     __syncwarp();
                     if(lane == 0)
                         mbar_arrive(xch_bar(s));
-                    ok = bounded_wait(xch_bar(s), (g / S) & 1, abort_f, prm.status, ST_TIMEOUT_SFWARP, 0x30000 + g);
+                    ok = bounded_wait(xch_bar(s), ring.phase, abort_f, prm.status, ST_TIMEOUT_SFWARP, 0x30000 + g);
                     ok = __all_sync(0xffffffffu, ok);
                     if(!ok)
                         break;
@@ -776,6 +819,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     if(CG == 2)
         cluster_sync_all(); // nobody leaves while the partner may still arrive on this CTA's barriers
     if(threadIdx.x == 0) stamp(63);
+    if(prm.trace != nullptr && threadIdx.x == 0 && blockIdx.x < 160)
+        prm.trace[65 + 2 * blockIdx.x] = global_timer_ns();
     if(warp == 1)
     {
         tc_fence_after_sync();

@@ -401,11 +401,14 @@ static void launch_persistent_cg(int cg, int ctas, size_t smem, cudaStream_t str
         launch_persistent<KIND, SFW, 1>(ctas, smem, stream, mp, mq, msp, msq, prm);
 }
 
+constexpr int kTraceCtas  = 160;
+constexpr int kTraceWords = 64 + 2 * kTraceCtas;
+
 static void print_trace(DeviceState& st, const GemmProblem& prob, const KernelConfig& cfg, int tiles_p, int tiles_q, int splits,
                         int stages)
 {
     // debugging aid: timestamp record of the first CTA, SM clock cycles relative to kernel entry
-    unsigned long long t[64];
+    static unsigned long long t[kTraceWords];
     B200_CUDA(cudaStreamSynchronize(prob.stream));
     B200_CUDA(cudaMemcpy(t, st.trace, sizeof(t), cudaMemcpyDeviceToHost));
     std::fprintf(stderr, "[trace] kind %d %lldx%lldx%lld %s tiles %dx%d splits %d stages %d:", prob.kind, prob.M, prob.N, prob.K,
@@ -413,6 +416,16 @@ static void print_trace(DeviceState& st, const GemmProblem& prob, const KernelCo
     for(int i = 0; i < 64; ++i)
         if(t[i] != 0)
             std::fprintf(stderr, " %d:%lld", i, static_cast<long long>(t[i] - t[0]));
+    // every CTA's begin / end on the global nanosecond timer, relative to the earliest begin
+    unsigned long long first = ~0ull;
+    for(int b = 0; b < kTraceCtas; ++b)
+        if(t[64 + 2 * b] != 0 && t[64 + 2 * b] < first)
+            first = t[64 + 2 * b];
+    std::fprintf(stderr, "\n[trace] cta begin-end ns:");
+    for(int b = 0; b < kTraceCtas; ++b)
+        if(t[64 + 2 * b] != 0)
+            std::fprintf(stderr, " %d:%lld-%lld", b, static_cast<long long>(t[64 + 2 * b] - first),
+                         static_cast<long long>(t[65 + 2 * b] - first));
     std::fprintf(stderr, "\n");
 }
 
@@ -480,6 +493,7 @@ void launch_gemm(const GemmProblem& prob)
     int splits            = 1 << cfg.log2_splitk;
     while(splits > num_k_iters)
         splits >>= 1;
+    B200_CHECK(static_cast<long long>(num_k_iters) * (splits + 1) < (1LL << 31), "K x split count too large");
     const int atoms_k  = (kkind == KIND_MXF4) ? 2 : 1;
     const int sf_cols  = sf_cols_per_stage(kkind);
     const int max_st = max_stages(cfg.bn, cg, st.smem_optin, f4_operand, kkind != KIND_BF16);
@@ -499,8 +513,8 @@ void launch_gemm(const GemmProblem& prob)
     if(trace_on && prob.scratch == nullptr)
     {
         if(st.trace == nullptr)
-            B200_CUDA(cudaMalloc(&st.trace, 64 * sizeof(unsigned long long)));
-        B200_CUDA(cudaMemsetAsync(st.trace, 0, 64 * sizeof(unsigned long long), prob.stream));
+            B200_CUDA(cudaMalloc(&st.trace, kTraceWords * sizeof(unsigned long long)));
+        B200_CUDA(cudaMemsetAsync(st.trace, 0, kTraceWords * sizeof(unsigned long long), prob.stream));
         trace = st.trace;
     }
 

@@ -308,6 +308,13 @@ __host__ __device__ constexpr uint32_t idesc_block_scaled(uint32_t afmt, uint32_
 {
     return (afmt << 7) | (bfmt << 10) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24);
 }
+__device__ __forceinline__ uint64_t pack_u64(uint32_t lo, uint32_t hi)
+{
+    uint64_t v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(lo), "r"(hi));
+    return v;
+}
+
 __host__ __device__ constexpr uint32_t idesc_with_sf(uint32_t idesc, uint32_t a_sf, uint32_t b_sf)
 {
     return idesc | (a_sf << 29) | (b_sf << 4);

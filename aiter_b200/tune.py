@@ -80,6 +80,12 @@ def _rand_u8(lo, hi, *shape, device):
     return torch.randint(lo, hi, shape, dtype=torch.uint8, device=device)
 
 
+def _rand_e4m3(rows, cols, device):
+    """Signed e4m3 values of magnitude 2^-3 .. 2, so that long sums stay inside the fp32 reference's accuracy."""
+    mag = _rand_u8(0x20, 0x40, rows, cols, device=device)
+    return (mag | (_rand_u8(0, 2, rows, cols, device=device) << 7)).view(torch.float8_e4m3fn)
+
+
 def make_problem(family: str, M: int, N: int, K: int, device, seed: int):
     """-> (args for the entry point, reference fp32 output of the first `ref_rows` rows, ref_rows)."""
     torch.manual_seed(seed)
@@ -89,8 +95,8 @@ def make_problem(family: str, M: int, N: int, K: int, device, seed: int):
         b = (torch.randn(N, K, device=device) * 0.1).to(torch.bfloat16)
         ref = a[:ref_rows].float() @ b.float().T
         return (a, b), ref, ref_rows
-    sa = _rand_u8(122, 130, M, K // 32, device=device)
-    sb = _rand_u8(122, 130, N, K // 32, device=device)
+    sa = _rand_u8(125, 129, M, K // 32, device=device)
+    sb = _rand_u8(125, 129, N, K // 32, device=device)
     sa_f = fp4_utils.e8m0_to_f32(sa[:ref_rows]).repeat_interleave(32, dim=1)
     sb_f = fp4_utils.e8m0_to_f32(sb).repeat_interleave(32, dim=1)
     if family == "a4w4":
@@ -98,9 +104,9 @@ def make_problem(family: str, M: int, N: int, K: int, device, seed: int):
         ref = (fp4_utils.mxfp4_to_f32(a[:ref_rows]) * sa_f) @ (fp4_utils.mxfp4_to_f32(b) * sb_f).T
         out = torch.empty(((M + 31) // 32 * 32, N), dtype=torch.bfloat16, device=device)
         return (a, shuffle.shuffle_weight(b), shuffle.shuffle_scale(sa), shuffle.shuffle_scale(sb), out), ref, ref_rows
-    a = _rand_u8(0, 0x78, M, K, device=device).view(torch.float8_e4m3fn)
+    a = _rand_e4m3(M, K, device)
     if family == "a8w8_mxfp8":
-        b = _rand_u8(0, 0x78, N, K, device=device).view(torch.float8_e4m3fn)
+        b = _rand_e4m3(N, K, device)
         ref = (a[:ref_rows].float() * sa_f) @ (b.float() * sb_f).T
     else:
         b = _rand_u8(0, 256, N, K // 2, device=device)
