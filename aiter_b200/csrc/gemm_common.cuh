@@ -16,6 +16,7 @@ constexpr int kNumThreads = 224;
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull; // 1 s per wait
 
 // status codes (word 0 of the status buffer); words 1..3 carry blockIdx / iteration detail
+constexpr uint32_t kParkNs = 20000; // longest single park of a waiting thread; the wall-time bound is checked between parks
 constexpr uint32_t ST_TIMEOUT_PRODUCER = 0x101;
 constexpr uint32_t ST_TIMEOUT_MMA_FULL = 0x102;
 constexpr uint32_t ST_TIMEOUT_MMA_SF   = 0x103;
@@ -39,17 +40,14 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
     if(mbar_try_wait(bar, parity))
         return true;
     const uint64_t t0 = global_timer_ns();
-    for(uint32_t i = 1;; ++i)
+    for(;;)
     {
-        if(mbar_try_wait(bar, parity))
+        if(mbar_try_wait_parked(bar, parity, kParkNs))
             return true;
-        if((i & 15u) == 0u)
-        {
-            if(*abort_flag)
-                return false;
-            if(global_timer_ns() - t0 > kWaitLimitNs)
-                break;
-        }
+        if(*abort_flag)
+            return false;
+        if(global_timer_ns() - t0 > kWaitLimitNs)
+            break;
     }
     *abort_flag = 1;
     if(atomicCAS(status, 0u, code) == 0u)

@@ -54,6 +54,7 @@ struct PersistentParams
     int acc_stride;               // TMEM columns between accumulators
     int sf_tmem_base;             // first TMEM column of the per-stage scale buffers
     int sf_cols;                  // TMEM columns per stage for scales
+    int tma_store;                // the output goes through shared memory and TMA tile stores (map_out is valid)
     int tmem_cols;                // allocation (power of two)
     // block scales in global memory (wire layout), one "group" = 32 rows; a group row is `sf_row_words` words
     const uint32_t* sfp;
@@ -74,12 +75,16 @@ struct PersistentParams
 
 struct PersistentSmem
 {
-    uint32_t stage_bytes, q_off, sfp_off, sfq_off, stg_off, bar_off, total;
+    uint32_t stage_bytes, q_off, sfp_off, sfq_off, stg_off, epi_off, bar_off, total;
 };
+
+constexpr uint32_t kEpiStageBytes = 16384; // 4 epilogue warps x 2 buffers x (32 rows x 64 bytes)
 
 // scaled: the stage carries 1 KB + 2 KB of raw scale bytes (P groups, Q groups)
 // f4_operand: 0 none, 1 = P, 2 = Q arrives as packed e2m1 and needs a staging area of rows x 64 bytes
-__host__ __device__ inline PersistentSmem make_persistent_smem(int bn, int cg, int stages, int f4_operand, bool scaled)
+// epi_stage: reserve the epilogue's output staging area (tile stores through TMA)
+__host__ __device__ inline PersistentSmem make_persistent_smem(int bn, int cg, int stages, int f4_operand, bool scaled,
+                                                               bool epi_stage)
 {
     PersistentSmem L;
     uint32_t q_bytes = static_cast<uint32_t>(bn / cg) * kTileKBytes;
@@ -91,7 +96,8 @@ __host__ __device__ inline PersistentSmem make_persistent_smem(int bn, int cg, i
     uint32_t stg     = f4_operand == 1 ? kTileP * 64u : (f4_operand == 2 ? static_cast<uint32_t>(bn / cg) * 64u : 0u);
     stg              = (stg + 1023u) & ~1023u;
     L.stage_bytes    = L.stg_off + stg;
-    L.bar_off        = L.stage_bytes * static_cast<uint32_t>(stages);
+    L.epi_off        = L.stage_bytes * static_cast<uint32_t>(stages);
+    L.bar_off        = L.epi_off + (epi_stage ? kEpiStageBytes : 0u);
     L.total          = L.bar_off + 512u;
     return L;
 }
@@ -138,7 +144,7 @@ template <int KIND, int SFW, int CG>
 __global__ void __launch_bounds__(kPersistentThreads, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                        const __grid_constant__ CUtensorMap map_sfp, const __grid_constant__ CUtensorMap map_sfq,
-                       const PersistentParams prm)
+                       const __grid_constant__ CUtensorMap map_out, const PersistentParams prm)
 {
     constexpr bool kScaled = (KIND != KIND_BF16);
     constexpr bool kMixed  = (KIND == KIND_MXF8F4);
@@ -151,7 +157,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     uint8_t* smem_gen        = smem_raw + (smem_base - smem_u32(smem_raw));
     const int bn             = prm.bn;
     const int S              = prm.stages;
-    const PersistentSmem L   = make_persistent_smem(bn, CG, S, kMixed ? prm.f4_operand : 0, kScaled);
+    const PersistentSmem L   = make_persistent_smem(bn, CG, S, kMixed ? prm.f4_operand : 0, kScaled, prm.tma_store != 0);
     constexpr int kSfChunk   = (SFW == SFW_E8M0_SHUFFLE) ? 256 : 128 * kAtomsK; // raw scale bytes per 32-row group per stage
 
     const uint32_t bar_base  = smem_base + L.bar_off;
@@ -327,7 +333,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                             tma_load_4d_pair(stage + tile_off, map, bar, 0, 0, row0 >> 1, kt);
                     }
                 }
-                if(is_p && g < 14) stamp(2 + 4 * g);
+                if(is_p && g < 8) stamp(2 + 4 * g);
             }
             if(*abort_f)
             {
@@ -425,7 +431,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                     if(!ok)
                         break;
                     tc_fence_after_sync();
-                    if(g < 14) stamp(5 + 4 * g);
+                    if(g < 8) stamp(5 + 4 * g);
                     const uint32_t p_lo = p_lo0 + s * stage_step;
                     const uint32_t q_lo = q_lo0 + s * stage_step;
                     const uint32_t tsfp = sf0 + s * prm.sf_cols;
@@ -514,7 +520,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                 ok = __all_sync(0xffffffffu, ok);
                 if(!ok)
                     break;
-                if(warp == 2 && lane == 0 && g < 14) stamp(3 + 4 * g);
+                if(warp == 2 && lane == 0 && g < 8) stamp(3 + 4 * g);
                 uint8_t* stage = smem_gen + s * L.stage_bytes;
                 if(kMixed)
                 {
@@ -630,7 +636,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                         mbar_arrive_cluster(ready_remote + 8u * s);
                     else
                         mbar_arrive(ready_bar(s));
-                    if(warp == 2 && g < 14) stamp(4 + 4 * g);
+                    if(warp == 2 && g < 8) stamp(4 + 4 * g);
                 }
             }
         }
@@ -646,6 +652,14 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
         const bool split     = (splits > 1);
         const uint32_t acc_empty_remote = (CG == 2) ? map_to_cta(acc_empty_bar(0), 0) : 0u;
         const bool vec_ok = (!prm.transposed_out) && ((prm.ldo & 7) == 0) && ((reinterpret_cast<uintptr_t>(prm.out) & 15) == 0);
+        // Output staging: every epilogue warp owns two 2 KB buffers (32 rows x 64 bytes) and stores them with its
+        // own TMA tile stores, so the warps never wait for one another and global memory sees whole 64-byte runs.
+        const bool use_tma   = prm.tma_store != 0;
+        uint8_t* epi_gen     = smem_gen + L.epi_off + (warp - 6) * 4096;
+        const uint32_t epi_s = smem_base + L.epi_off + (warp - 6) * 4096;
+        int ebuf             = 0;
+        if(use_tma && lane == 0)
+            tma_prefetch_desc(&map_out);
         uint32_t epi_phase = 0;
         int uc = 0;
         bool ok = true;
@@ -723,37 +737,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             if(is_last)
             {
                 const float* part = split ? prm.ws_partial + static_cast<size_t>(slot) * splits * (static_cast<size_t>(bn) * kTileP) : nullptr;
-                for(int c = 0; c < n_chunks; ++c)
-                {
-                    float v[32];
-                    if(!split)
-                    {
-                        uint32_t r[32];
-                        if(chunk == 32)
-                            tmem_ld_x32(tacc + c * 32, r);
-                        else
-                            tmem_ld_x16(tacc + c * 16, r);
-                        tmem_ld_wait();
-#pragma unroll
-                        for(int j = 0; j < 32; ++j)
-                            v[j] = __uint_as_float(r[j]);
-                        if(c == n_chunks - 1)
-                            release_acc(); // every column of this accumulator is in registers now
-                    }
-                    else
-                    {
-#pragma unroll
-                        for(int j = 0; j < 32; ++j)
-                            v[j] = 0.f;
-                        for(int zz = 0; zz < splits; ++zz)
-                        {
-                            const float* src = part + static_cast<size_t>(zz) * (static_cast<size_t>(bn) * kTileP);
-#pragma unroll
-                            for(int j = 0; j < 32; ++j)
-                                if(j < chunk)
-                                    v[j] += __ldcg(src + static_cast<size_t>(c * chunk + j) * kTileP + p_local);
-                        }
-                    }
+                // finish one chunk of columns: alpha / bias, bf16, store
+                auto finish = [&](float (&v)[32], const int c) {
                     const int q_first = row_q0 + c * chunk;
                     if(prm.bias != nullptr)
                     {
@@ -773,7 +758,43 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                         for(int j = 0; j < 32; ++j)
                             v[j] *= prm.alpha;
                     }
-                    if(p < prm.rows_p)
+                    if(use_tma)
+                    {
+                        if(lane == 0)
+                            bulk_wait_group_read<1>(); // the store issued from this buffer two chunks ago has read it
+                        __syncwarp();
+                        uint8_t* buf = epi_gen + ebuf * 2048;
+                        if(!prm.transposed_out)
+                        {
+                            // row = lane, 64 bytes (32 columns); 16-byte pieces swizzled (64B mode) against bank conflicts
+#pragma unroll
+                            for(int j = 0; j < 4; ++j)
+                                *reinterpret_cast<uint4*>(buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) * 16)) =
+                                    make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
+                                               pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
+                        }
+                        else
+                        {
+                            // row = output row q (chunk of them), 64 bytes = this warp's 32 values of p
+#pragma unroll
+                            for(int j = 0; j < 32; ++j)
+                                if(j < chunk)
+                                    reinterpret_cast<__nv_bfloat16*>(buf)[j * 32 + lane] = __float2bfloat16_rn(v[j]);
+                        }
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        const int p_warp0 = (w.tp * CG + static_cast<int>(crank)) * kTileP + quarter * 32;
+                        if(lane == 0 && p_warp0 < prm.rows_p && q_first < prm.rows_q) // partly outside: the store clips
+                        {
+                            if(!prm.transposed_out)
+                                tma_store_2d(&map_out, epi_s + ebuf * 2048, q_first * 2, p_warp0);
+                            else
+                                tma_store_2d(&map_out, epi_s + ebuf * 2048, p_warp0 * 2, q_first);
+                            bulk_commit_group();
+                        }
+                        ebuf ^= 1;
+                    }
+                    else if(p < prm.rows_p)
                     {
                         if(!prm.transposed_out)
                         {
@@ -806,11 +827,100 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                             }
                         }
                     }
+                };
+                if(!split && prm.tma_store == 2)
+                {
+                    // Wide path (row-major output, tile width a multiple of 64): 64 columns per step, so that the
+                    // one warp per scheduler that runs this code has long runs of independent instructions: one
+                    // TMEM load, 32 conversions, 8 shared-memory stores (128B-swizzled rows), one tile store.
+                    const bool epi_math = (prm.bias != nullptr) || (prm.alpha != 1.0f);
+                    const int p_warp0   = (w.tp * CG + static_cast<int>(crank)) * kTileP + quarter * 32;
+                    const int n64       = bn >> 6;
+                    for(int c = 0; c < n64; ++c)
+                    {
+                        uint32_t r[64];
+                        tmem_ld_x64(tacc + c * 64, r);
+                        tmem_ld_wait();
+                        if(c == n64 - 1)
+                            release_acc(); // every column of this accumulator is in registers now
+                        const int q_first = row_q0 + c * 64;
+                        if(epi_math)
+                        {
+                            const float bp = (prm.bias != nullptr && !prm.bias_on_q && p < prm.rows_p) ? load_bias(prm.bias, prm.bias_is_bf16, p) : 0.f;
+#pragma unroll
+                            for(int j = 0; j < 64; ++j)
+                            {
+                                float b = bp;
+                                if(prm.bias != nullptr && prm.bias_on_q)
+                                    b = (q_first + j < prm.rows_q) ? load_bias(prm.bias, prm.bias_is_bf16, q_first + j) : 0.f;
+                                r[j] = __float_as_uint(prm.alpha * __uint_as_float(r[j]) + prm.beta * b);
+                            }
+                        }
+                        if(lane == 0)
+                            bulk_wait_group_read<0>(); // the previous tile store has read this warp's buffer
+                        __syncwarp();
+                        uint8_t* row = epi_gen + lane * 128;
+#pragma unroll
+                        for(int j = 0; j < 8; ++j)
+                            *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) * 16)) =
+                                make_uint4(pack_bf16x2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1])),
+                                           pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
+                                           pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])),
+                                           pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])));
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if(lane == 0 && p_warp0 < prm.rows_p && q_first < prm.rows_q)
+                        {
+                            tma_store_2d(&map_out, epi_s, q_first * 2, p_warp0);
+                            bulk_commit_group();
+                        }
+                    }
                 }
+                else if(!split)
+                {
+                    for(int c = 0; c < n_chunks; ++c)
+                    {
+                        uint32_t r[32];
+                        if(chunk == 32)
+                            tmem_ld_x32(tacc + c * 32, r);
+                        else
+                            tmem_ld_x16(tacc + c * 16, r);
+                        tmem_ld_wait();
+                        if(c == n_chunks - 1)
+                            release_acc(); // every column of this accumulator is in registers now
+                        float v[32];
+#pragma unroll
+                        for(int j = 0; j < 32; ++j)
+                            v[j] = __uint_as_float(r[j]);
+                        finish(v, c);
+                    }
+                }
+                else
+                {
+                    for(int c = 0; c < n_chunks; ++c)
+                    {
+                        float v[32];
+#pragma unroll
+                        for(int j = 0; j < 32; ++j)
+                            v[j] = 0.f;
+                        for(int zz = 0; zz < splits; ++zz)
+                        {
+                            const float* src = part + static_cast<size_t>(zz) * (static_cast<size_t>(bn) * kTileP);
+#pragma unroll
+                            for(int j = 0; j < 32; ++j)
+                                if(j < chunk)
+                                    v[j] += __ldcg(src + static_cast<size_t>(c * chunk + j) * kTileP + p_local);
+                        }
+                        finish(v, c);
+                    }
+                }
+                if(warp == 6 && lane == 0 && uc == 0) stamp(59);
                 if(split && warp == 6 && lane == 0)
                     prm.ws_counter[slot] = 0; // ready for the next launch
             }
         }
+        if(use_tma && lane == 0)
+            bulk_wait_group<0>(); // this warp's tile stores are complete before the CTA retires
         if(warp == 6 && lane == 0) stamp(62);
         tc_fence_before_sync();
     }

@@ -229,10 +229,10 @@ static int kernel_kind_of(int problem_kind)
     }
 }
 
-static int max_stages(int bn, int cg, int smem_limit, int f4_operand, bool scaled)
+static int max_stages(int bn, int cg, int smem_limit, int f4_operand, bool scaled, bool epi_stage)
 {
     for(int s = kMaxStages; s >= 1; --s)
-        if(static_cast<int>(make_persistent_smem(bn, cg, s, f4_operand, scaled).total) + 1024 <= smem_limit)
+        if(static_cast<int>(make_persistent_smem(bn, cg, s, f4_operand, scaled, epi_stage).total) + 1024 <= smem_limit)
             return s;
     return 0;
 }
@@ -277,7 +277,7 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
     }
     if(cfg.stages <= 0)
     {
-        int s        = max_stages(cfg.bn, cfg.cg, 227 * 1024, kind == PK_MXF8F4 ? (cfg.swap ? 1 : 2) : 0, kind != PK_BF16);
+        int s        = max_stages(cfg.bn, cfg.cg, 227 * 1024, kind == PK_MXF8F4 ? (cfg.swap ? 1 : 2) : 0, kind != PK_BF16, true);
         cfg.stages   = s > kMaxStages ? kMaxStages : s;
     }
 }
@@ -369,7 +369,7 @@ static void raise_smem_limit(Kernel kernel, bool (&attr_done)[64])
 
 template <int KIND, int SFW, int CG>
 static void launch_persistent(int ctas, size_t smem, cudaStream_t stream, const CUtensorMap& mp, const CUtensorMap& mq,
-                              const CUtensorMap& msp, const CUtensorMap& msq, const PersistentParams& prm)
+                              const CUtensorMap& msp, const CUtensorMap& msq, const CUtensorMap& mo, const PersistentParams& prm)
 {
     auto kernel = gemm_persistent_kernel<KIND, SFW, CG>;
     static bool attr_done[64] = {};
@@ -386,19 +386,19 @@ static void launch_persistent(int ctas, size_t smem, cudaStream_t stream, const 
     attr[0].val.clusterDim.z = 1;
     lc.attrs    = attr;
     lc.numAttrs = 1;
-    B200_CUDA(cudaLaunchKernelEx(&lc, kernel, mp, mq, msp, msq, prm));
+    B200_CUDA(cudaLaunchKernelEx(&lc, kernel, mp, mq, msp, msq, mo, prm));
     g_launches.fetch_add(1);
 }
 
 template <int KIND, int SFW>
 static void launch_persistent_cg(int cg, int ctas, size_t smem, cudaStream_t stream, const CUtensorMap& mp,
                                  const CUtensorMap& mq, const CUtensorMap& msp, const CUtensorMap& msq,
-                                 const PersistentParams& prm)
+                                 const CUtensorMap& mo, const PersistentParams& prm)
 {
     if(cg == 2)
-        launch_persistent<KIND, SFW, 2>(ctas, smem, stream, mp, mq, msp, msq, prm);
+        launch_persistent<KIND, SFW, 2>(ctas, smem, stream, mp, mq, msp, msq, mo, prm);
     else
-        launch_persistent<KIND, SFW, 1>(ctas, smem, stream, mp, mq, msp, msq, prm);
+        launch_persistent<KIND, SFW, 1>(ctas, smem, stream, mp, mq, msp, msq, mo, prm);
 }
 
 constexpr int kTraceCtas  = 160;
@@ -496,7 +496,9 @@ void launch_gemm(const GemmProblem& prob)
     B200_CHECK(static_cast<long long>(num_k_iters) * (splits + 1) < (1LL << 31), "K x split count too large");
     const int atoms_k  = (kkind == KIND_MXF4) ? 2 : 1;
     const int sf_cols  = sf_cols_per_stage(kkind);
-    const int max_st = max_stages(cfg.bn, cg, st.smem_optin, f4_operand, kkind != KIND_BF16);
+    // the output leaves through shared memory and TMA tile stores when its pitch and base allow a tensor map
+    const bool tma_store = ((reinterpret_cast<uintptr_t>(prob.out) & 15) == 0) && (prob.ldo % 8 == 0) && (cfg.swap || cfg.bn >= 32);
+    const int max_st = max_stages(cfg.bn, cg, st.smem_optin, f4_operand, kkind != KIND_BF16, tma_store);
     B200_CHECK(max_st >= 2, "tile ", 128 * cg, "x", cfg.bn, " does not fit in shared memory");
     int stages = cfg.stages <= 0 ? max_st : std::min(cfg.stages, max_st);
 
@@ -610,19 +612,33 @@ void launch_gemm(const GemmProblem& prob)
     while(cols < prm.sf_tmem_base + stages * sf_cols)
         cols <<= 1;
     prm.tmem_cols = cols;
-    const PersistentSmem L = make_persistent_smem(cfg.bn, cg, stages, f4_operand, kkind != KIND_BF16);
+    const PersistentSmem L = make_persistent_smem(cfg.bn, cg, stages, f4_operand, kkind != KIND_BF16, tma_store);
     const size_t smem      = L.total + 1024;
+    // 2: 64 columns per store (row-major output, tile width a multiple of 64, no K split); 1: 32 per store
+    const bool wide_store  = tma_store && !cfg.swap && cfg.bn % 64 == 0 && splits == 1;
+    prm.tma_store          = tma_store ? (wide_store ? 2 : 1) : 0;
+    CUtensorMap mo         = mp;
+    if(tma_store)
+    {
+        // bf16 [M][N] seen as bytes; one box = 32 values of the fast dimension by 32 rows (or the tile's chunk of rows
+        // when the 128-row slot holds the weights and the store is transposed)
+        const cuuint64_t dims[2]    = {static_cast<cuuint64_t>(prob.N) * 2, static_cast<cuuint64_t>(prob.M)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(prob.ldo) * 2};
+        const cuuint32_t box[2]     = {wide_store ? 128u : 64u, static_cast<cuuint32_t>(cfg.swap ? (cfg.bn < 32 ? 16 : 32) : 32)};
+        mo = encode_map(prob.out, 2, dims, strides, box,
+                        cfg.swap ? CU_TENSOR_MAP_SWIZZLE_NONE : (wide_store ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B), "output");
+    }
     const int ctas         = clusters * cg;
     if(kkind == KIND_BF16)
-        launch_persistent_cg<KIND_BF16, SFW_NONE>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
+        launch_persistent_cg<KIND_BF16, SFW_NONE>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else if(kkind == KIND_MXF8 && sfw == SFW_G1250)
-        launch_persistent_cg<KIND_MXF8, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
+        launch_persistent_cg<KIND_MXF8, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else if(kkind == KIND_MXF4 && sfw == SFW_E8M0_SHUFFLE)
-        launch_persistent_cg<KIND_MXF4, SFW_E8M0_SHUFFLE>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
+        launch_persistent_cg<KIND_MXF4, SFW_E8M0_SHUFFLE>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else if(kkind == KIND_MXF4 && sfw == SFW_G1250)
-        launch_persistent_cg<KIND_MXF4, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
+        launch_persistent_cg<KIND_MXF4, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else if(kkind == KIND_MXF8F4 && sfw == SFW_G1250)
-        launch_persistent_cg<KIND_MXF8F4, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, prm);
+        launch_persistent_cg<KIND_MXF8F4, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else
         fail("no kernel instance for kind ", kkind, " with scale layout ", sfw);
 
