@@ -1,6 +1,7 @@
 // Shared pieces of the tcgen05 GEMM kernels: enums, status codes, bounded waits, small device helpers.
 #pragma once
 #include <cuda_bf16.h>
+#include <type_traits>
 #include "ptx.cuh"
 
 namespace b200 {

@@ -23,11 +23,11 @@
 //          reduction), overlapped with the next unit's main loop when two accumulators fit in TMEM
 //
 // Barriers (all waits bounded by wall time):
-//   full[s]       leader: the operand tiles of stage s of every CTA of the pair have landed
+//   full[s]       leader: the operand tiles of stage s of every CTA of the pair have landed and every scale warp
+//                 of every CTA has written the stage's scales to TMEM (one wait for the MMA issuer)
 //   staged[s]     mixed kind: this CTA's packed e2m1 tile of stage s has landed (local)
 //   sfraw[s]      this CTA's raw scale bytes of stage s have landed (local)
 //   xch[s]        e8m0_shuffle wire layout: the four scale warps have re-ordered their share of stage s (local)
-//   ready[s]      leader: every scale warp of every CTA has written stage s's scales to TMEM
 //   empty[s]      the MMAs reading stage s (and its TMEM scales) are done (tcgen05.commit, both CTAs)
 //   acc_full[a]   accumulator a is complete (tcgen05.commit, both CTAs)
 //   acc_empty[a]  leader: all epilogue warps of all CTAs have drained accumulator a
@@ -162,7 +162,6 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
 
     const uint32_t bar_base  = smem_base + L.bar_off;
     auto full_bar            = [&](int s) { return bar_base + 8u * s; };
-    auto ready_bar           = [&](int s) { return bar_base + 64u + 8u * s; };
     auto empty_bar           = [&](int s) { return bar_base + 128u + 8u * s; };
     auto staged_bar          = [&](int s) { return bar_base + 192u + 8u * s; };
     auto sfraw_bar           = [&](int s) { return bar_base + 256u + 8u * s; };
@@ -195,8 +194,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     {
         for(int s = 0; s < S; ++s)
         {
-            mbar_init(full_bar(s), 2 * CG);   // one expect_tx arrival per operand producer of every CTA of the pair
-            mbar_init(ready_bar(s), 4 * CG);  // one arrival per scale warp of every CTA
+            // one expect_tx arrival per operand producer and one arrival per scale warp, of every CTA of the pair
+            mbar_init(full_bar(s), (kScaled ? 6 : 2) * CG);
             mbar_init(empty_bar(s), 1);
             mbar_init(staged_bar(s), 1);
             mbar_init(sfraw_bar(s), 1);
@@ -290,51 +289,72 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             const int mode    = is_p ? prm.p_mode : prm.q_mode;
             const CUtensorMap* map = is_p ? &map_p : &map_q;
             const uint32_t my_bytes = is_f4 ? 0u : (is_p ? kTileP * kTileKBytes : q_box_bytes);
-            const uint32_t tile_off = is_p ? 0u : L.q_off;
+            const uint32_t tile0    = smem_base + (is_p ? 0u : L.q_off);
+            const uint32_t full0    = (CG == 2) ? map_to_cta(full_bar(0), 0) : full_bar(0); // the leader's barrier counts both CTAs' bytes
+            const uint32_t empty0   = empty_bar(0);
             int g = 0;
             bool ok = true;
             Ring ring{0, 0};
-            for(WorkIter w = first_work(); w.valid && ok; next_iter(w), ++g, ring.advance(S))
-            {
-                const int s = ring.s;
-                ok = bounded_wait(empty_bar(s), ring.phase ^ 1u, abort_f, prm.status, ST_TIMEOUT_PRODUCER, g);
-                if(!ok)
-                    break;
-                const int row0 = is_p ? (w.tp * CG + static_cast<int>(crank)) * kTileP
-                                      : w.tq * bn + static_cast<int>(crank) * q_rows_cta;
-                const int kt         = w.it_beg + w.i;
-                const uint32_t stage = smem_base + s * L.stage_bytes;
-                if(is_f4)
+            // One loop per operand layout, so that the per-K-tile path is a wait, an expect_tx and the tile load.
+            auto run = [&](auto mode_tag) {
+                constexpr int MODE = decltype(mode_tag)::value;
+                for(WorkIter w = first_work(); w.valid && ok; next_unit(w))
                 {
-                    // the packed e2m1 operand (always 16x16-byte tiled) lands in this CTA's staging area:
-                    // 4 chunks of 16 bytes per row, counted on a local barrier for the scale warps
-                    const uint32_t sbar = staged_bar(s);
-                    mbar_arrive_expect_tx(sbar, (is_p ? kTileP : q_rows_cta) * 64u);
-                    tma_load_3d(stage + L.stg_off, map, sbar, 0, row0 >> 4, kt * 4);
-                }
-                if(CG == 1)
-                {
-                    const uint32_t bar = full_bar(s);
-                    mbar_arrive_expect_tx(bar, my_bytes);
-                    if(!is_f4)
-                        issue_operand_load(mode, stage + tile_off, map, bar, row0, kt);
-                }
-                else
-                {
-                    const uint32_t bar = map_to_cta(full_bar(s), 0); // the leader's barrier counts both CTAs' bytes
-                    mbar_arrive_expect_tx_cluster(bar, my_bytes);
-                    if(!is_f4)
+                    const int row0 = is_p ? (w.tp * CG + static_cast<int>(crank)) * kTileP
+                                          : w.tq * bn + static_cast<int>(crank) * q_rows_cta;
+                    int kt         = w.it_beg;
+                    for(int i = 0; i < w.n_iters; ++i, ++kt, ++g, ring.advance(S))
                     {
-                        if(mode == OPM_ROWMAJOR)
-                            tma_load_2d_pair(stage + tile_off, map, bar, kt * kTileKBytes, row0);
-                        else if(mode == OPM_TILE16)
-                            tma_load_3d_pair(stage + tile_off, map, bar, 0, row0 >> 4, kt * (kTileKBytes / 16));
+                        const int s = ring.s;
+                        ok = bounded_wait(empty0 + 8u * s, ring.phase ^ 1u, abort_f, prm.status, ST_TIMEOUT_PRODUCER, g);
+                        if(!ok)
+                            break;
+                        const uint32_t dst = tile0 + s * L.stage_bytes;
+                        const uint32_t bar = full0 + 8u * s;
+                        if(MODE == 3)
+                        {
+                            // the packed e2m1 operand (always 16x16-byte tiled) lands in this CTA's staging area:
+                            // 4 chunks of 16 bytes per row, counted on a local barrier for the scale warps
+                            const uint32_t sbar = staged_bar(s);
+                            mbar_arrive_expect_tx(sbar, (is_p ? kTileP : q_rows_cta) * 64u);
+                            tma_load_3d(smem_base + s * L.stage_bytes + L.stg_off, map, sbar, 0, row0 >> 4, kt * 4);
+                            if(CG == 1)
+                                mbar_arrive_expect_tx(bar, 0u);
+                            else
+                                mbar_arrive_expect_tx_cluster(bar, 0u);
+                        }
+                        else if(CG == 1)
+                        {
+                            mbar_arrive_expect_tx(bar, my_bytes);
+                            if(MODE == OPM_ROWMAJOR)
+                                tma_load_2d(dst, map, bar, kt * kTileKBytes, row0);
+                            else if(MODE == OPM_TILE16)
+                                tma_load_3d(dst, map, bar, 0, row0 >> 4, kt * (kTileKBytes / 16));
+                            else
+                                tma_load_4d(dst, map, bar, 0, 0, row0 >> 1, kt);
+                        }
                         else
-                            tma_load_4d_pair(stage + tile_off, map, bar, 0, 0, row0 >> 1, kt);
+                        {
+                            mbar_arrive_expect_tx_cluster(bar, my_bytes);
+                            if(MODE == OPM_ROWMAJOR)
+                                tma_load_2d_pair(dst, map, bar, kt * kTileKBytes, row0);
+                            else if(MODE == OPM_TILE16)
+                                tma_load_3d_pair(dst, map, bar, 0, row0 >> 4, kt * (kTileKBytes / 16));
+                            else
+                                tma_load_4d_pair(dst, map, bar, 0, 0, row0 >> 1, kt);
+                        }
+                        if(tracing && is_p && g < 8) stamp(2 + 4 * g);
                     }
                 }
-                if(is_p && g < 8) stamp(2 + 4 * g);
-            }
+            };
+            if(is_f4)
+                run(std::integral_constant<int, 3>{});
+            else if(mode == OPM_ROWMAJOR)
+                run(std::integral_constant<int, OPM_ROWMAJOR>{});
+            else if(mode == OPM_TILE16)
+                run(std::integral_constant<int, OPM_TILE16>{});
+            else
+                run(std::integral_constant<int, OPM_A2X128>{});
             if(*abort_f)
             {
                 // give loads still in flight time to land before this CTA's shared memory is released (bounded);
@@ -354,19 +374,23 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             int g = 0;
             bool ok = true;
             Ring ring{0, 0};
-            for(WorkIter w = first_work(); w.valid && ok; next_iter(w), ++g, ring.advance(S))
+            for(WorkIter w = first_work(); w.valid && ok; next_unit(w))
             {
-                const int s = ring.s;
-                ok = bounded_wait(empty_bar(s), ring.phase ^ 1u, abort_f, prm.status, ST_TIMEOUT_PRODUCER, 0x20000 + g);
-                if(!ok)
-                    break;
-                const int row_p0     = (w.tp * CG + static_cast<int>(crank)) * kTileP;
-                const int kt         = w.it_beg + w.i;
-                const uint32_t stage = smem_base + s * L.stage_bytes;
-                const uint32_t bar   = sfraw_bar(s);
-                mbar_arrive_expect_tx(bar, sfp_bytes + sfq_bytes);
-                tma_load_2d(stage + L.sfp_off, &map_sfp, bar, kt * kSfChunk, row_p0 >> 5);
-                tma_load_2d(stage + L.sfq_off, &map_sfq, bar, kt * kSfChunk, (w.tq * bn) >> 5);
+                const int grp_p = ((w.tp * CG + static_cast<int>(crank)) * kTileP) >> 5;
+                const int grp_q = (w.tq * bn) >> 5;
+                int kc          = w.it_beg * kSfChunk;
+                for(int i = 0; i < w.n_iters; ++i, kc += kSfChunk, ++g, ring.advance(S))
+                {
+                    const int s = ring.s;
+                    ok = bounded_wait(empty_bar(s), ring.phase ^ 1u, abort_f, prm.status, ST_TIMEOUT_PRODUCER, 0x20000 + g);
+                    if(!ok)
+                        break;
+                    const uint32_t stage = smem_base + s * L.stage_bytes;
+                    const uint32_t bar   = sfraw_bar(s);
+                    mbar_arrive_expect_tx(bar, sfp_bytes + sfq_bytes);
+                    tma_load_2d(stage + L.sfp_off, &map_sfp, bar, kc, grp_p);
+                    tma_load_2d(stage + L.sfq_off, &map_sfq, bar, kc, grp_q);
+                }
             }
         }
     }
@@ -408,6 +432,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                          : (KIND == KIND_MXF4) ? idesc_with_sf(idesc, (k & 1) * 2, (k & 1) * 2)
                                                : idesc_with_sf(idesc, k, k);
             const uint32_t sf0 = tmem_base + prm.sf_tmem_base;
+            const uint32_t full0 = full_bar(0), empty0 = empty_bar(0);
 
             int g = 0, uc = 0;
             bool ok = true;
@@ -425,13 +450,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                 for(int i = 0; i < n_iters; ++i, ++g, ring.advance(S))
                 {
                     const int s = ring.s;
-                    ok = bounded_wait(full_bar(s), ring.phase, abort_f, prm.status, ST_TIMEOUT_MMA_FULL, g);
-                    if(ok && kScaled)
-                        ok = bounded_wait(ready_bar(s), ring.phase, abort_f, prm.status, ST_TIMEOUT_MMA_SF, g);
+                    ok = bounded_wait(full0 + 8u * s, ring.phase, abort_f, prm.status, ST_TIMEOUT_MMA_FULL, g);
                     if(!ok)
                         break;
                     tc_fence_after_sync();
-                    if(g < 8) stamp(5 + 4 * g);
+                    if(tracing && g < 8) stamp(5 + 4 * g);
                     const uint32_t p_lo = p_lo0 + s * stage_step;
                     const uint32_t q_lo = q_lo0 + s * stage_step;
                     const uint32_t tsfp = sf0 + s * prm.sf_cols;
@@ -462,9 +485,9 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                         }
                     }
                     if(CG == 1)
-                        tc_commit(empty_bar(s));
+                        tc_commit(empty0 + 8u * s);
                     else
-                        tc_commit_2cta(empty_bar(s), 3);
+                        tc_commit_2cta(empty0 + 8u * s, 3);
                 }
                 if(ok)
                 {
@@ -502,7 +525,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             constexpr bool kE8 = (SFW == SFW_E8M0_SHUFFLE);
             const int quarter    = warp & 3;
             const uint32_t tlane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-            const uint32_t ready_remote = (CG == 2) ? map_to_cta(ready_bar(0), 0) : 0u;
+            const uint32_t full_leader = (CG == 2) ? map_to_cta(full_bar(0), 0) : full_bar(0);
             const int r16 = lane & 15, hi = lane >> 4;
             const int q_groups = (bn + 31) / 32; // 32-row groups of Q staged per stage (P always stages 4)
 
@@ -520,7 +543,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                 ok = __all_sync(0xffffffffu, ok);
                 if(!ok)
                     break;
-                if(warp == 2 && lane == 0 && g < 8) stamp(3 + 4 * g);
+                if(tracing && warp == 2 && lane == 0 && g < 8) stamp(3 + 4 * g);
                 uint8_t* stage = smem_gen + s * L.stage_bytes;
                 if(kMixed)
                 {
@@ -633,10 +656,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                 if(lane == 0)
                 {
                     if(CG == 2)
-                        mbar_arrive_cluster(ready_remote + 8u * s);
+                        mbar_arrive_cluster(full_leader + 8u * s);
                     else
-                        mbar_arrive(ready_bar(s));
-                    if(warp == 2 && g < 8) stamp(4 + 4 * g);
+                        mbar_arrive(full_leader + 8u * s);
+                    if(tracing && warp == 2 && g < 8) stamp(4 + 4 * g);
                 }
             }
         }
