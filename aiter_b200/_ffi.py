@@ -15,7 +15,8 @@ import torch
 
 from .dtypes import aiter_dtype_id
 
-LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc", "libaiter_b200.so")
+# AITER_B200_LIBRARY points at another build of the library (comparing two builds on one machine)
+LIB_PATH = os.environ.get("AITER_B200_LIBRARY") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc", "libaiter_b200.so")
 
 
 class aiter_tensor_t(ctypes.Structure):
