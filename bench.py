@@ -31,6 +31,9 @@ if ROOT not in sys.path:
 
 N_DIM, K_DIM, M_DIM = 4096, 4096, 8192
 METRIC = "GEMM TFLOPS/GPU (MXFP8 A8W8, N=K=4096, M=8192)"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload's kernel, from the ncu capture
+# summarised under profiles/ (52.0 MB read + 32.0 MB written; the 126 MB L2 holds part of the 119 MB working set)
+NCU_TRAFFIC_BYTES = 84.0e6
 NOMINAL = {"bf16": 2250.0, "mxfp8": 4500.0, "mxfp4": 9000.0, "a8w4": 4500.0, "hbm_gbs": 8000.0}
 
 
@@ -157,6 +160,24 @@ def graph_time_calls(torch, fn, arg_sets, iters, warmup):
     return e0.elapsed_time(e1) * 1e3 / iters
 
 
+def kernel_in_use(ab, kind, M, N, K):
+    """Name of the kernel configuration the operator picks: the tuned table's row, else the heuristic."""
+    from aiter_b200 import gemm_op_a4w4, gemm_op_a8w4, gemm_op_a8w8
+
+    row = None
+    if kind == "mxfp8":
+        row = gemm_op_a8w8._mxfp8_table.lookup(M, N, K)
+    elif kind == "mxfp4":
+        row = gemm_op_a4w4.get_GEMM_config(M, N, K)
+    elif kind == "a8w4":
+        row = gemm_op_a8w4.get_A8W4_config(M, N, K)
+    if row is not None and row.get("kernelName"):
+        name = str(row["kernelName"])
+        split = row.get("splitK")
+        return name if "_k" in name or not split else f"{name}_k{int(split)}"
+    return ab.heuristic_name({"bf16": 0, "mxfp8": 1, "mxfp4": 2, "a8w4": 3}[kind], M, N, K)[0]
+
+
 def rotating_sets(make, bytes_per_set, l2_bytes=126e6):
     n = max(2, min(24, int(2.2 * l2_bytes // max(bytes_per_set, 1)) + 1))
     return [make(i) for i in range(n)]
@@ -179,7 +200,7 @@ def run_sweep(torch, ab, device, peaks):
         peak_tf = peaks["bf16"] * {"bf16": 1, "mxfp8": 2, "a8w4": 2, "mxfp4": 4}[kind]
         rows.append({"kind": kind, "M": M, "N": N, "K": K, "us": round(us, 2), "tflops": round(tf, 1), "gbs": round(gbs, 1),
                      "frac_tensor": round(tf / peak_tf, 4), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4),
-                     "kernel": ab.heuristic_name({"bf16": 0, "mxfp8": 1, "mxfp4": 2, "a8w4": 3}[kind], M, N, K)[0]})
+                     "kernel": kernel_in_use(ab, kind, M, N, K)})
 
     # bf16 a16w16 (the reference's CPU-runnable case)
     add("bf16", 64, 1024, 1024, lambda a, b: ab.tgemm.mm(a, b),
@@ -193,10 +214,14 @@ def run_sweep(torch, ab, device, peaks):
     for (N, K) in ((7168, 2048), (24576, 1536), (7168, 16384)):
         for M in (1, 32, 256, 4096, 16384):
             kb = (K // 32 + 7) // 8 * 8
-            add("mxfp4", M, N, K, lambda a, b, sa, sb, o: ab.gemm_a4w4_asm(a, b, sa, sb, o, "", None, 1.0, 0.0, True, None),
+            add("mxfp4", M, N, K, lambda a, b, sa, sb: ab.gemm_a4w4(a, b, sa, sb),
                 lambda i, M=M, N=N, K=K, kb=kb: (rand_u8(0, 256, M, K // 2), rand_u8(0, 256, N, K // 2),
-                                                 rand_u8(120, 130, (M + 255) // 256 * 256, kb), rand_u8(120, 130, (N + 255) // 256 * 256, kb),
-                                                 torch.empty(((M + 31) // 32 * 32, N), dtype=torch.bfloat16, device=device)))
+                                                 rand_u8(120, 130, (M + 255) // 256 * 256, kb), rand_u8(120, 130, (N + 255) // 256 * 256, kb)))
+    # MXFP8 activations x MXFP4 weights, N = K = 8192
+    for M in (1, 16, 128, 1024, 4096, 16384):
+        add("a8w4", M, 8192, 8192, lambda a, b, sa, sb: ab.gemm_a8w4_mxfp8(a, b, sa, sb, a_preshuffle=False),
+            lambda i, M=M: (rand_u8(0, 0x78, M, 8192).view(torch.float8_e4m3fn), rand_u8(0, 256, 8192, 4096),
+                            rand_u8(120, 130, (M + 31) // 32 * 32, 256), rand_u8(120, 130, 8192, 256)))
     return rows
 
 
@@ -341,7 +366,7 @@ def run_ours(args, rank, world, local_rank):
         peak_fp8 = 2.0 * peaks["bf16"]
         roofline = {
             "bound": "tensor", "achieved": round(kernel_tf, 1), "peak": round(peak_fp8, 1), "unit": "TFLOP/s",
-            "frac": round(kernel_tf / peak_fp8, 4), "traffic": None,
+            "frac": round(kernel_tf / peak_fp8, 4), "traffic": NCU_TRAFFIC_BYTES, "traffic_unit": "bytes per launch",
             "peak_source": f"2 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16']} TFLOP/s); FP8 tensor rate is twice the bf16 rate",
             "frac_of_nominal_4500": round(kernel_tf / NOMINAL["mxfp8"], 4),
             "algorithmic_flops_per_launch": flops, "algorithmic_bytes_per_launch": bytes_alg,
@@ -358,7 +383,7 @@ def run_ours(args, rank, world, local_rank):
             "dtype": "e4m3 x e4m3 (UE8M0 scales) -> f32 accumulate -> bf16", "data": "synthetic",
             "config": {"workload": f"mxfp8_a8w8 M={M} N={N} K={K} per GPU (N-sharded weight, one 4096-column shard per rank)",
                        "l2_policy": f"{len(sets)} rotating input sets of {bytes_alg / 1e6:.0f} MB (> 126 MB L2 in total)",
-                       "kernel": ab.heuristic_name(1, M, N, K)[0], "e2e_copies": "activations + their scales H2D, output D2H, weight resident"},
+                       "kernel": kernel_in_use(ab, "mxfp8", M, N, K), "e2e_copies": "activations + their scales H2D, output D2H, weight resident"},
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches, "clocks": clocks, "device_status": list(status),
