@@ -374,9 +374,10 @@ def run_ours(args, rank, world, local_rank):
         }
         if not (args.no_sweep or args.kernel_only):
             sweep = run_sweep(torch, ab, device, peaks)
-        cpu_tf, cpu_dt = (0.0, 0.0) if args.kernel_only else time_cpu(256, 3)
-        cpu = {"value": round(cpu_tf, 4), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-               "sample": f"256 of {M} rows of M, full N and K ({cpu_dt * 1e3:.0f} ms per pass, torch-on-CPU restatement of the reference path)"}
+        if world == 1 and not args.kernel_only:  # the CPU baseline is a single-GPU-run figure
+            cpu_tf, cpu_dt = time_cpu(256, 3)
+            cpu = {"value": round(cpu_tf, 4), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                   "sample": f"256 of {M} rows of M, full N and K ({cpu_dt * 1e3:.0f} ms per pass, torch-on-CPU restatement of the reference path)"}
         line = {
             "metric": METRIC, "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
