@@ -42,3 +42,4 @@ from .shuffle import (  # noqa: E402,F401
     shuffle_weight,
 )
 from .tuned_gemm import TunedGemm, gemm_a16w16, tgemm  # noqa: E402,F401
+from . import torch_ops  # noqa: E402,F401  (registers torch.ops.aiter.* with fake-tensor implementations)

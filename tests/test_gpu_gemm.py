@@ -355,3 +355,18 @@ def test_errors_are_python_exceptions(ab):
         w = torch.zeros((16, 128), dtype=torch.float8_e4m3fn, device="cuda")
         ab.gemm_a8w8_mxfp8(x, w, s, s, a_preshuffle=False, kernelName="no_such_kernel")
     assert_healthy(ab)
+
+
+def test_torch_ops_namespace_runs_the_cuda_path(ab):
+    M, N, K = 64, 256, 512
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16)
+    xq, xs = ox.quant_mxfp4(x.float().numpy())
+    wq, ws = ox.quant_mxfp4(w.float().numpy())
+    ref = ox.gemm_a4w4_ref(xq, wq, xs, ws)
+    before = ab.launch_count()
+    out = torch.ops.aiter.gemm_a4w4(torch.from_numpy(xq).cuda(), ab.shuffle_weight(torch.from_numpy(wq).cuda(), layout=(16, 16)),
+                                    ab.shuffle_scale(torch.from_numpy(xs).cuda()), ab.shuffle_scale(torch.from_numpy(ws).cuda()))
+    assert ab.launch_count() == before + 1
+    check(ref, out, what="torch.ops.aiter.gemm_a4w4")

@@ -165,3 +165,22 @@ def test_a4w4_forwards_table_row_to_the_entry_point(ab, tmp_path, monkeypatch):
     name, args = calls[-1]
     assert args[5] is None and args[10] == -1 and args[4].shape == (32, 256)
     gemm_op_a4w4._table.clear()
+
+
+def test_torch_library_ops_have_fake_implementations():
+    """torch.ops.aiter.* trace on the meta device: output shape and dtype without touching a GPU."""
+    import aiter_b200  # noqa: F401
+
+    a = torch.empty(3, 5, 64, dtype=torch.uint8, device="meta")
+    b = torch.empty(256, 64, dtype=torch.uint8, device="meta")
+    s = torch.empty(256, 8, dtype=torch.uint8, device="meta")
+    for op in (torch.ops.aiter.gemm_a4w4, torch.ops.aiter.gemm_a8w8_mxfp8, torch.ops.aiter.gemm_a8w4_mxfp8):
+        o = op(a, b, s, s)
+        assert o.shape == (3, 5, 256) and o.dtype == torch.bfloat16 and o.device.type == "meta"
+    o = torch.ops.aiter.gemm_a16w16(torch.empty(7, 32, dtype=torch.bfloat16, device="meta"),
+                                    torch.empty(48, 32, dtype=torch.bfloat16, device="meta"))
+    assert o.shape == (7, 48)
+    o = torch.ops.aiter.gemm_a8w8_blockscale(torch.empty(9, 256, dtype=torch.float8_e4m3fn, device="meta"),
+                                             torch.empty(128, 256, dtype=torch.float8_e4m3fn, device="meta"),
+                                             torch.empty(9, 2, device="meta"), torch.empty(1, 2, device="meta"))
+    assert o.shape == (9, 128)
