@@ -54,6 +54,7 @@ struct PersistentParams
     int acc_stride;               // TMEM columns between accumulators
     int sf_tmem_base;             // first TMEM column of the per-stage scale buffers
     int sf_cols;                  // TMEM columns per stage for scales
+    int csplit;                   // K split across the CTAs of a thread-block cluster (1 = none; CG == 1 only, one tile per cluster)
     int tma_store;                // the output goes through shared memory and TMA tile stores (map_out is valid)
     int tmem_cols;                // allocation (power of two)
     // block scales in global memory (wire layout), one "group" = 32 rows; a group row is `sf_row_words` words
@@ -75,7 +76,7 @@ struct PersistentParams
 
 struct PersistentSmem
 {
-    uint32_t stage_bytes, q_off, sfp_off, sfq_off, stg_off, epi_off, bar_off, total;
+    uint32_t stage_bytes, q_off, sfp_off, sfq_off, stg_off, epi_off, red_off, bar_off, total;
 };
 
 constexpr uint32_t kEpiStageBytes = 16384; // 4 epilogue warps x 2 buffers x (32 rows x 64 bytes)
@@ -83,8 +84,9 @@ constexpr uint32_t kEpiStageBytes = 16384; // 4 epilogue warps x 2 buffers x (32
 // scaled: the stage carries 1 KB + 2 KB of raw scale bytes (P groups, Q groups)
 // f4_operand: 0 none, 1 = P, 2 = Q arrives as packed e2m1 and needs a staging area of rows x 64 bytes
 // epi_stage: reserve the epilogue's output staging area (tile stores through TMA)
+// csplit: cluster K split; its leader keeps (csplit - 1) partial tiles of 128 x bn floats
 __host__ __device__ inline PersistentSmem make_persistent_smem(int bn, int cg, int stages, int f4_operand, bool scaled,
-                                                               bool epi_stage)
+                                                               bool epi_stage, int csplit)
 {
     PersistentSmem L;
     uint32_t q_bytes = static_cast<uint32_t>(bn / cg) * kTileKBytes;
@@ -97,7 +99,8 @@ __host__ __device__ inline PersistentSmem make_persistent_smem(int bn, int cg, i
     stg              = (stg + 1023u) & ~1023u;
     L.stage_bytes    = L.stg_off + stg;
     L.epi_off        = L.stage_bytes * static_cast<uint32_t>(stages);
-    L.bar_off        = L.epi_off + (epi_stage ? kEpiStageBytes : 0u);
+    L.red_off        = L.epi_off + (epi_stage ? kEpiStageBytes : 0u);
+    L.bar_off        = L.red_off + (csplit > 1 ? static_cast<uint32_t>(csplit - 1) * static_cast<uint32_t>(bn) * kTileP * 4u : 0u);
     L.total          = L.bar_off + 512u;
     return L;
 }
@@ -157,7 +160,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     uint8_t* smem_gen        = smem_raw + (smem_base - smem_u32(smem_raw));
     const int bn             = prm.bn;
     const int S              = prm.stages;
-    const PersistentSmem L   = make_persistent_smem(bn, CG, S, kMixed ? prm.f4_operand : 0, kScaled, prm.tma_store != 0);
+    const PersistentSmem L   = make_persistent_smem(bn, CG, S, kMixed ? prm.f4_operand : 0, kScaled, prm.tma_store != 0, prm.csplit);
     constexpr int kSfChunk   = (SFW == SFW_E8M0_SHUFFLE) ? 256 : 128 * kAtomsK; // raw scale bytes per 32-row group per stage
 
     const uint32_t bar_base  = smem_base + L.bar_off;
@@ -170,16 +173,21 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     auto acc_empty_bar       = [&](int a) { return bar_base + 400u + 8u * a; };
     const uint32_t epi_bar   = bar_base + 416u;
     const uint32_t drain_bar = bar_base + 424u;
+    const uint32_t red_bar   = bar_base + 448u;
     uint32_t* tmem_ptr_smem    = reinterpret_cast<uint32_t*>(smem_gen + L.bar_off + 432);
     volatile uint32_t* abort_f = reinterpret_cast<volatile uint32_t*>(smem_gen + L.bar_off + 436);
     uint32_t* ticket_smem      = reinterpret_cast<uint32_t*>(smem_gen + L.bar_off + 440);
 
     const int warp       = threadIdx.x >> 5;
     const int lane       = threadIdx.x & 31;
-    const uint32_t crank = (CG == 2) ? cluster_ctarank() : 0u; // 0 = leader
-    const bool leader    = (crank == 0);
-    const int cluster_id = blockIdx.x / CG;
-    const int n_clusters = gridDim.x / CG;
+    const int csplit        = (CG == 1) ? prm.csplit : 1;
+    const uint32_t hw_rank  = (CG == 2 || csplit > 1) ? cluster_ctarank() : 0u;
+    const uint32_t crank    = (CG == 2) ? hw_rank : 0u; // 0 = leader of a CTA pair
+    const uint32_t zrank    = (csplit > 1) ? hw_rank : 0u; // K slice of a cluster-split tile; 0 = the reducing CTA
+    const bool leader       = (crank == 0);
+    const int cluster_ctas  = CG * csplit;
+    const int cluster_id    = blockIdx.x / cluster_ctas;
+    const int n_clusters    = gridDim.x / cluster_ctas;
 
     const bool tracing = (prm.trace != nullptr) && blockIdx.x == 0;
     auto stamp = [&](int slot) { if(tracing && slot < 64) prm.trace[slot] = static_cast<unsigned long long>(clock64()); };
@@ -188,7 +196,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
         prm.trace[64 + 2 * blockIdx.x] = global_timer_ns();
 
     const int splits      = prm.splits;
-    const int total_units = prm.tiles_p * prm.tiles_q * splits;
+    const int total_units = prm.tiles_p * prm.tiles_q * (prm.csplit > 1 ? 1 : splits);
 
     if(threadIdx.x == 0)
     {
@@ -208,6 +216,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
         }
         mbar_init(epi_bar, 4);
         mbar_init(drain_bar, 1);
+        mbar_init(red_bar, 1);
         *abort_f = 0;
         mbar_fence_init();
         fence_proxy_async_smem();
@@ -237,7 +246,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     }
     tc_fence_before_sync();
     __syncthreads();
-    if(CG == 2)
+    if(CG == 2 || csplit > 1)
         cluster_sync_all(); // the partner's barriers exist before anything arrives on them remotely
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
@@ -254,13 +263,14 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
         w.valid = w.u < total_units;
         if(!w.valid)
             return;
-        w.z            = w.u % splits;
-        const int tile = w.u / splits;
+        const int ksplit = (csplit > 1) ? csplit : splits;
+        w.z            = (csplit > 1) ? static_cast<int>(zrank) : w.u % splits;
+        const int tile = (csplit > 1) ? w.u : w.u / splits;
         w.tq           = tile % prm.tiles_q;
         w.tp           = tile / prm.tiles_q;
         // num_k_iters * splits < 2^31 (checked on the host): 32-bit divisions keep this off the critical path
-        w.it_beg       = static_cast<int>(static_cast<uint32_t>(prm.num_k_iters * w.z) / static_cast<uint32_t>(splits));
-        w.n_iters      = static_cast<int>(static_cast<uint32_t>(prm.num_k_iters * (w.z + 1)) / static_cast<uint32_t>(splits)) - w.it_beg;
+        w.it_beg       = static_cast<int>(static_cast<uint32_t>(prm.num_k_iters * w.z) / static_cast<uint32_t>(ksplit));
+        w.n_iters      = static_cast<int>(static_cast<uint32_t>(prm.num_k_iters * (w.z + 1)) / static_cast<uint32_t>(ksplit)) - w.it_beg;
         w.i            = 0;
     };
     auto first_work = [&]() {
@@ -712,6 +722,36 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                 }
             };
 
+            if(csplit > 1 && zrank != 0)
+            {
+                // K slice of a cluster-split tile: send this CTA's partial accumulator to the reducing CTA's shared
+                // memory ([slice][row][bn floats]); the bytes are counted on its red barrier, nothing is waited for
+                const uint32_t dst_row = map_to_cta(smem_base + L.red_off, 0) +
+                                         ((zrank - 1u) * kTileP + static_cast<uint32_t>(p_local)) * static_cast<uint32_t>(bn) * 4u;
+                const uint32_t dst_bar = map_to_cta(red_bar, 0);
+                for(int c = 0; c < n_chunks; ++c)
+                {
+                    uint32_t r[32];
+                    if(chunk == 32)
+                        tmem_ld_x32(tacc + c * 32, r);
+                    else
+                        tmem_ld_x16(tacc + c * 16, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for(int j = 0; j < 32; j += 4)
+                        if(j < chunk)
+                            st_async_v4(dst_row + static_cast<uint32_t>(c * chunk + j) * 4u, r[j], r[j + 1], r[j + 2], r[j + 3], dst_bar);
+                }
+                release_acc();
+                continue;
+            }
+            if(csplit > 1)
+            {
+                // reducing CTA: expect the other slices' bytes for this tile
+                if(warp == 6 && lane == 0)
+                    mbar_arrive_expect_tx(red_bar, static_cast<uint32_t>(csplit - 1) * static_cast<uint32_t>(bn) * kTileP * 4u);
+            }
+
             if(split)
             {
                 float* mine = prm.ws_partial + (static_cast<size_t>(slot) * splits + w.z) * (static_cast<size_t>(bn) * kTileP);
@@ -915,6 +955,31 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
 #pragma unroll
                         for(int j = 0; j < 32; ++j)
                             v[j] = __uint_as_float(r[j]);
+                        if(csplit > 1)
+                        {
+                            if(c == 0)
+                            {
+                                ok = bounded_wait(red_bar, uc & 1, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, 0x3000 + uc);
+                                ok = __all_sync(0xffffffffu, ok);
+                                if(!ok)
+                                    break;
+                            }
+                            const float4* red = reinterpret_cast<const float4*>(smem_gen + L.red_off);
+                            for(int z = 0; z < csplit - 1; ++z)
+                            {
+                                const float4* row = red + (static_cast<size_t>(z * kTileP + p_local) * bn + c * chunk) / 4;
+#pragma unroll
+                                for(int j = 0; j < 32; j += 4)
+                                    if(j < chunk)
+                                    {
+                                        const float4 t = row[j / 4];
+                                        v[j] += t.x;
+                                        v[j + 1] += t.y;
+                                        v[j + 2] += t.z;
+                                        v[j + 3] += t.w;
+                                    }
+                            }
+                        }
                         finish(v, c);
                     }
                 }
@@ -949,7 +1014,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     }
 
     __syncthreads();
-    if(CG == 2)
+    if(CG == 2 || csplit > 1)
         cluster_sync_all(); // nobody leaves while the partner may still arrive on this CTA's barriers
     if(threadIdx.x == 0) stamp(63);
     if(prm.trace != nullptr && threadIdx.x == 0 && blockIdx.x < 160)

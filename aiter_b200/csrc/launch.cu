@@ -229,10 +229,10 @@ static int kernel_kind_of(int problem_kind)
     }
 }
 
-static int max_stages(int bn, int cg, int smem_limit, int f4_operand, bool scaled, bool epi_stage)
+static int max_stages(int bn, int cg, int smem_limit, int f4_operand, bool scaled, bool epi_stage, int csplit = 1)
 {
     for(int s = kMaxStages; s >= 1; --s)
-        if(static_cast<int>(make_persistent_smem(bn, cg, s, f4_operand, scaled, epi_stage).total) + 1024 <= smem_limit)
+        if(static_cast<int>(make_persistent_smem(bn, cg, s, f4_operand, scaled, epi_stage, csplit).total) + 1024 <= smem_limit)
             return s;
     return 0;
 }
@@ -381,7 +381,7 @@ static void launch_persistent(int ctas, size_t smem, cudaStream_t stream, const 
     lc.stream           = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id               = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CG;
+    attr[0].val.clusterDim.x = CG * (prm.csplit > 1 ? prm.csplit : 1);
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     lc.attrs    = attr;
@@ -403,6 +403,12 @@ static void launch_persistent_cg(int cg, int ctas, size_t smem, cudaStream_t str
 
 constexpr int kTraceCtas  = 160;
 constexpr int kTraceWords = 64 + 2 * kTraceCtas;
+
+static bool cluster_split_disabled()
+{
+    static const bool off = (std::getenv("AITER_B200_NO_CLUSTER_SPLIT") != nullptr);
+    return off;
+}
 
 static void print_trace(DeviceState& st, const GemmProblem& prob, const KernelConfig& cfg, int tiles_p, int tiles_q, int splits,
                         int stages)
@@ -498,7 +504,16 @@ void launch_gemm(const GemmProblem& prob)
     const int sf_cols  = sf_cols_per_stage(kkind);
     // the output leaves through shared memory and TMA tile stores when its pitch and base allow a tensor map
     const bool tma_store = ((reinterpret_cast<uintptr_t>(prob.out) & 15) == 0) && (prob.ldo % 8 == 0) && (cfg.swap || cfg.bn >= 32);
-    const int max_st = max_stages(cfg.bn, cg, st.smem_optin, f4_operand, kkind != KIND_BF16, tma_store);
+    // Decode shapes: the K split runs across the CTAs of a thread-block cluster, one output tile per cluster; the
+    // partial accumulators meet in the first CTA's shared memory instead of a global workspace.
+    int csplit = 1;
+    if(cfg.swap && cg == 1 && splits > 1 && splits <= 8 && prob.scratch == nullptr && !cluster_split_disabled() &&
+       max_stages(cfg.bn, cg, st.smem_optin, f4_operand, kkind != KIND_BF16, tma_store, splits) >= 4)
+    {
+        csplit = splits;
+        splits = 1;
+    }
+    const int max_st = max_stages(cfg.bn, cg, st.smem_optin, f4_operand, kkind != KIND_BF16, tma_store, csplit);
     B200_CHECK(max_st >= 2, "tile ", 128 * cg, "x", cfg.bn, " does not fit in shared memory");
     int stages = cfg.stages <= 0 ? max_st : std::min(cfg.stages, max_st);
 
@@ -599,8 +614,10 @@ void launch_gemm(const GemmProblem& prob)
     // TMEM: n_acc accumulators of acc_stride columns, then one scale buffer per shared-memory stage
     prm.acc_stride = (cfg.bn + 31) & ~31;
     prm.sf_cols    = sf_cols;
+    prm.csplit            = csplit;
     const long long units = static_cast<long long>(tiles_p) * tiles_q * splits;
-    const int clusters    = static_cast<int>(std::min<long long>(units, st.sm_count / cg));
+    // a cluster-split tile owns its cluster for the whole launch: one cluster per tile, however many run at once
+    const int clusters    = csplit > 1 ? static_cast<int>(units) : static_cast<int>(std::min<long long>(units, st.sm_count / cg));
     const bool multi_unit = units > clusters;
     prm.n_acc = (multi_unit && 2 * prm.acc_stride + 2 * sf_cols <= 512) ? 2 : 1;
     while(prm.n_acc * prm.acc_stride + stages * sf_cols > 512 && stages > 2)
@@ -612,7 +629,7 @@ void launch_gemm(const GemmProblem& prob)
     while(cols < prm.sf_tmem_base + stages * sf_cols)
         cols <<= 1;
     prm.tmem_cols = cols;
-    const PersistentSmem L = make_persistent_smem(cfg.bn, cg, stages, f4_operand, kkind != KIND_BF16, tma_store);
+    const PersistentSmem L = make_persistent_smem(cfg.bn, cg, stages, f4_operand, kkind != KIND_BF16, tma_store, csplit);
     const size_t smem      = L.total + 1024;
     // 2: 64 columns per store (row-major output, tile width a multiple of 64, no K split); 1: 32 per store
     const bool wide_store  = tma_store && !cfg.swap && cfg.bn % 64 == 0 && splits == 1;
@@ -628,7 +645,7 @@ void launch_gemm(const GemmProblem& prob)
         mo = encode_map(prob.out, 2, dims, strides, box,
                         cfg.swap ? CU_TENSOR_MAP_SWIZZLE_NONE : (wide_store ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B), "output");
     }
-    const int ctas         = clusters * cg;
+    const int ctas         = clusters * cg * csplit;
     if(kkind == KIND_BF16)
         launch_persistent_cg<KIND_BF16, SFW_NONE>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else if(kkind == KIND_MXF8 && sfw == SFW_G1250)
