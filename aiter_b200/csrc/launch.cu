@@ -696,20 +696,52 @@ void launch_blockscale(const BlockScaleProblem& prob)
     prm.out         = static_cast<__nv_bfloat16*>(prob.out);
     prm.ldo         = prob.ldo;
     prm.status      = st.status;
-    const int stage_bytes = (kTileP + kBsTileN) * kTileKBytes;
-    int stages            = (st.smem_optin - 2048) / stage_bytes;
-    stages                = std::min(stages, kMaxStages);
-    stages                = std::max(2, std::min(stages, prm.k_blocks));
-    prm.stages            = stages;
-    const size_t smem     = static_cast<size_t>(stage_bytes) * stages + 512 + 1024;
-    CUtensorMap ma = operand_map(prob.act, kTileP, "activation operand");
-    CUtensorMap mb = operand_map(prob.wgt, kBsTileN, "weight operand");
-    static bool attr_done[64] = {};
-    raise_smem_limit(gemm_a8w8_blockscale_kernel, attr_done);
-    dim3 grid(static_cast<unsigned>((prob.M + kTileP - 1) / kTileP), static_cast<unsigned>((prob.N + kBsTileN - 1) / kBsTileN), 1);
-    B200_CHECK(grid.y <= 65535, "N too large");
-    gemm_a8w8_blockscale_kernel<<<grid, kBlockScaleThreads, smem, prob.stream>>>(ma, mb, prm);
-    B200_CUDA(cudaGetLastError());
+    if(prob.M > kTileP)
+    {
+        // 256 x 256 tiles on CTA pairs
+        const int stage_bytes = 2 * kTileP * kTileKBytes;
+        int stages            = std::min((st.smem_optin - 2048) / stage_bytes, kMaxStages);
+        stages                = std::max(2, std::min(stages, prm.k_blocks));
+        prm.stages            = stages;
+        const size_t smem     = static_cast<size_t>(stage_bytes) * stages + 512 + 1024;
+        CUtensorMap ma = operand_map(prob.act, kTileP, "activation operand");
+        CUtensorMap mb = operand_map(prob.wgt, kTileP, "weight operand");
+        static bool attr_done[64] = {};
+        raise_smem_limit(gemm_a8w8_blockscale_pair_kernel, attr_done);
+        const unsigned pairs_m = static_cast<unsigned>((prob.M + 2 * kTileP - 1) / (2 * kTileP));
+        const unsigned tiles_n = static_cast<unsigned>((prob.N + kBsPairN - 1) / kBsPairN);
+        B200_CHECK(tiles_n <= 65535, "N too large");
+        cudaLaunchConfig_t lc{};
+        lc.gridDim          = dim3(pairs_m * 2, tiles_n, 1);
+        lc.blockDim         = dim3(kBlockScalePairThreads, 1, 1);
+        lc.dynamicSmemBytes = smem;
+        lc.stream           = prob.stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id               = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        lc.attrs    = attr;
+        lc.numAttrs = 1;
+        B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_pair_kernel, ma, mb, prm));
+    }
+    else
+    {
+        const int stage_bytes = (kTileP + kBsTileN) * kTileKBytes;
+        int stages            = (st.smem_optin - 2048) / stage_bytes;
+        stages                = std::min(stages, kMaxStages);
+        stages                = std::max(2, std::min(stages, prm.k_blocks));
+        prm.stages            = stages;
+        const size_t smem     = static_cast<size_t>(stage_bytes) * stages + 512 + 1024;
+        CUtensorMap ma = operand_map(prob.act, kTileP, "activation operand");
+        CUtensorMap mb = operand_map(prob.wgt, kBsTileN, "weight operand");
+        static bool attr_done[64] = {};
+        raise_smem_limit(gemm_a8w8_blockscale_kernel, attr_done);
+        dim3 grid(static_cast<unsigned>((prob.M + kTileP - 1) / kTileP), static_cast<unsigned>((prob.N + kBsTileN - 1) / kBsTileN), 1);
+        B200_CHECK(grid.y <= 65535, "N too large");
+        gemm_a8w8_blockscale_kernel<<<grid, kBlockScaleThreads, smem, prob.stream>>>(ma, mb, prm);
+        B200_CUDA(cudaGetLastError());
+    }
     g_launches.fetch_add(1);
 }
 
