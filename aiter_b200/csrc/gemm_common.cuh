@@ -60,6 +60,18 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
     return false;
 }
 
+// 8 packed e2m1 codes (one 32-bit word, element n in nibble n) -> 8 e4m3 bytes (exact: every e2m1 value
+// is an e4m3 value).  Magnitude by table look-up (prmt), sign moved to bit 7 of each byte.
+__device__ __forceinline__ void e2m1x8_to_e4m3x8(uint32_t w, uint32_t& lo, uint32_t& hi)
+{
+    constexpr uint32_t kLutLo = 0x3C383000u; // 0, 0.5, 1, 1.5
+    constexpr uint32_t kLutHi = 0x4C484440u; // 2, 3, 4, 6
+    constexpr uint32_t kSign  = 0x00008000u; // byte 0 = 0x00, byte 1 = 0x80
+    lo = __byte_perm(kLutLo, kLutHi, w & 0x7777u) | __byte_perm(kSign, 0u, (w >> 3) & 0x1111u);
+    const uint32_t h = w >> 16;
+    hi = __byte_perm(kLutLo, kLutHi, h & 0x7777u) | __byte_perm(kSign, 0u, (h >> 3) & 0x1111u);
+}
+
 __device__ __forceinline__ void issue_operand_load(int mode, uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                                    int row0, int k_iter)
 {

@@ -108,18 +108,6 @@ __host__ __device__ inline PersistentSmem make_persistent_smem(int bn, int cg, i
 // TMEM columns one stage's scales occupy: [P atoms: 4 per K atom][Q atoms: 8 per K atom (two 128-row blocks)]
 __host__ __device__ constexpr int sf_cols_per_stage(int kind) { return kind == KIND_BF16 ? 0 : (kind == KIND_MXF4 ? 24 : 16); }
 
-// 8 packed e2m1 codes (one 32-bit word, element n in nibble n) -> 8 e4m3 bytes (exact: every e2m1 value
-// is an e4m3 value).  Magnitude by table look-up (prmt), sign moved to bit 7 of each byte.
-__device__ __forceinline__ void e2m1x8_to_e4m3x8(uint32_t w, uint32_t& lo, uint32_t& hi)
-{
-    constexpr uint32_t kLutLo = 0x3C383000u; // 0, 0.5, 1, 1.5
-    constexpr uint32_t kLutHi = 0x4C484440u; // 2, 3, 4, 6
-    constexpr uint32_t kSign  = 0x00008000u; // byte 0 = 0x00, byte 1 = 0x80
-    lo = __byte_perm(kLutLo, kLutHi, w & 0x7777u) | __byte_perm(kSign, 0u, (w >> 3) & 0x1111u);
-    const uint32_t h = w >> 16;
-    hi = __byte_perm(kLutLo, kLutHi, h & 0x7777u) | __byte_perm(kSign, 0u, (h >> 3) & 0x1111u);
-}
-
 // Stage ring position kept by increments: these loops run on one thread (or one warp) per K tile, where a
 // division by the run-time stage count would cost more than the work itself.
 struct Ring

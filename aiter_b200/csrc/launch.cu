@@ -118,6 +118,10 @@ struct StreamWorkspace
     float* partial        = nullptr;
     size_t partial_bytes  = 0;
     unsigned int* counter = nullptr;
+    void* widened         = nullptr; // e4m3 copy of a packed e2m1 weight (mixed kind, tall problems)
+    size_t widened_bytes  = 0;
+    void* relaid          = nullptr; // block scales re-laid from e8m0_shuffle to the (m/32,k/4,32,4) order (MXFP4, tall problems)
+    size_t relaid_bytes   = 0;
 };
 constexpr int kCounterSlots = 1 << 16;
 
@@ -435,7 +439,217 @@ static void print_trace(DeviceState& st, const GemmProblem& prob, const KernelCo
     std::fprintf(stderr, "\n");
 }
 
+// Packed e2m1 weight in the 16x16-byte tiled layout -> e4m3 in the same tiling (twice the K chunks).  Exact: every
+// e2m1 value is an e4m3 value.  One thread per 16-byte chunk (32 codes of one row).
+__global__ void widen_e2m1_tile16_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long row_blocks, int chunks_in)
+{
+    const long long total = row_blocks * chunks_in * 16;
+    for(long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+        i += static_cast<long long>(gridDim.x) * blockDim.x)
+    {
+        const int r         = static_cast<int>(i & 15);
+        const long long t   = i >> 4;
+        const int kc        = static_cast<int>(t % chunks_in);
+        const long long nb  = t / chunks_in;
+        const uint4 v       = src[i];
+        uint4 o0, o1;
+        e2m1x8_to_e4m3x8(v.x, o0.x, o0.y);
+        e2m1x8_to_e4m3x8(v.y, o0.z, o0.w);
+        e2m1x8_to_e4m3x8(v.z, o1.x, o1.y);
+        e2m1x8_to_e4m3x8(v.w, o1.z, o1.w);
+        const long long base = (nb * (2LL * chunks_in) + 2LL * kc) * 16 + r;
+        dst[base]      = o0;
+        dst[base + 16] = o1;
+    }
+}
+
+// e8m0_shuffle scale bytes -> (m/32, k/4, 32, 4) order, one thread per output word (one row, four K blocks).
+// src byte index: (m/32 * cols_pad) * 32 + (k/8) * 256 + (k%4) * 64 + (m%16) * 4 + ((k%8)/4) * 2 + (m%32)/16.
+__global__ void relay_e8m0_shuffle_kernel(const uint8_t* __restrict__ src, uint32_t* __restrict__ dst, int groups, int cols_pad, int kblocks)
+{
+    const int atoms       = kblocks / 4;
+    const long long total = static_cast<long long>(groups) * atoms * 32;
+    for(long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+        i += static_cast<long long>(gridDim.x) * blockDim.x)
+    {
+        const int r        = static_cast<int>(i & 31);
+        const long long t  = i >> 5;
+        const int a        = static_cast<int>(t % atoms);
+        const long long g  = t / atoms;
+        const uint8_t* p   = src + (g * cols_pad) * 32 + (a >> 1) * 256 + (r & 15) * 4 + (a & 1) * 2 + (r >> 4);
+        dst[i]             = static_cast<uint32_t>(p[0]) | (static_cast<uint32_t>(p[64]) << 8) | (static_cast<uint32_t>(p[128]) << 16) |
+                             (static_cast<uint32_t>(p[192]) << 24);
+    }
+}
+
+static bool relay_prepass_disabled()
+{
+    static const bool off = (std::getenv("AITER_B200_NO_SCALE_PREPASS") != nullptr);
+    return off;
+}
+
+static bool widen_prepass_disabled()
+{
+    static const bool off = (std::getenv("AITER_B200_NO_WIDEN_PREPASS") != nullptr);
+    return off;
+}
+
+static void launch_gemm_locked(const GemmProblem& prob);
+
+// Tall mixed MXFP8 x MXFP4 problems: widening the weight once (N x K bytes through HBM) is cheaper than widening
+// every tile of it in shared memory M / 256 times; the GEMM itself then runs as plain MXFP8.  Below the
+// threshold, inside stream capture without a buffer, or with caller-provided scratch the in-kernel path runs.
+constexpr long long kWidenPrepassMinM = 512;
+// Tall MXFP4 problems with e8m0_shuffle scales: that byte order costs the scale warps a transpose through shared
+// memory on every K tile; re-laying both scale tensors once into the (m/32,k/4,32,4) order (a few MB) lets the
+// main loop run the cheaper path.
+constexpr long long kScalePrepassMinM = 1024;
+constexpr long long kScalePrepassMinK = 4096; // the two extra launches (~6 us) must be won back over the K loop
+
 void launch_gemm(const GemmProblem& prob)
+{
+    if(prob.kind == PK_MXFP4 && prob.M >= kScalePrepassMinM && prob.scratch == nullptr && prob.act_sf.wire == SFW_E8M0_SHUFFLE &&
+       prob.wgt_sf.wire == SFW_E8M0_SHUFFLE && prob.K % 256 == 0 && prob.K >= kScalePrepassMinK && !relay_prepass_disabled())
+    {
+        int prev_dev = 0;
+        B200_CUDA(cudaGetDevice(&prev_dev));
+        if(prev_dev != prob.device)
+            B200_CUDA(cudaSetDevice(prob.device));
+        struct Restore
+        {
+            int prev, cur;
+            ~Restore()
+            {
+                if(prev != cur)
+                    cudaSetDevice(prev);
+            }
+        } restore{prev_dev, prob.device};
+        const int kblocks    = static_cast<int>(prob.K / 32);
+        const long long ga   = (prob.M + 31) / 32, gw = (prob.N + 31) / 32;
+        const bool fits      = prob.act_sf.padded_rows >= ga * 32 && prob.wgt_sf.padded_rows >= gw * 32 &&
+                               prob.act_sf.padded_cols >= kblocks && prob.wgt_sf.padded_cols >= kblocks &&
+                               prob.act_sf.padded_cols % 8 == 0 && prob.wgt_sf.padded_cols % 8 == 0;
+        uint32_t* relaid = nullptr;
+        if(fits)
+        {
+            std::lock_guard<std::mutex> lk(g_mutex);
+            DeviceState& st    = device_state(prob.device);
+            StreamWorkspace& w = st.ws[prob.stream];
+            const size_t bytes = static_cast<size_t>(ga + gw) * 32 * kblocks;
+            bool usable        = w.relaid_bytes >= bytes;
+            if(!usable)
+            {
+                cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+                cudaStreamIsCapturing(prob.stream, &cap);
+                if(cap == cudaStreamCaptureStatusNone)
+                {
+                    if(w.relaid != nullptr)
+                    {
+                        B200_CUDA(cudaStreamSynchronize(prob.stream));
+                        B200_CUDA(cudaFree(w.relaid));
+                        w.relaid       = nullptr;
+                        w.relaid_bytes = 0;
+                    }
+                    B200_CUDA(cudaMalloc(&w.relaid, bytes));
+                    w.relaid_bytes = bytes;
+                    usable         = true;
+                }
+            }
+            if(usable)
+            {
+                relaid = static_cast<uint32_t*>(w.relaid);
+                auto run = [&](const ScaleOperand& sf, uint32_t* dst, long long groups) {
+                    const long long total = groups * (kblocks / 4) * 32;
+                    const int blocks      = static_cast<int>(std::min<long long>((total + 255) / 256, 148LL * 16));
+                    relay_e8m0_shuffle_kernel<<<blocks, 256, 0, prob.stream>>>(static_cast<const uint8_t*>(sf.ptr), dst, static_cast<int>(groups),
+                                                                               static_cast<int>(sf.padded_cols), kblocks);
+                    B200_CUDA(cudaGetLastError());
+                    g_launches.fetch_add(1);
+                };
+                run(prob.act_sf, relaid, ga);
+                run(prob.wgt_sf, relaid + ga * 32 * (kblocks / 4), gw);
+            }
+        }
+        if(relaid != nullptr)
+        {
+            GemmProblem p2 = prob;
+            p2.act_sf      = ScaleOperand{relaid, SFW_G1250, ga * 32, kblocks};
+            p2.wgt_sf      = ScaleOperand{relaid + ga * 32 * (kblocks / 4), SFW_G1250, gw * 32, kblocks};
+            launch_gemm_locked(p2);
+            return;
+        }
+    }
+
+    if(prob.kind == PK_MXF8F4 && prob.M >= kWidenPrepassMinM && prob.scratch == nullptr && prob.wgt.mode == OPM_TILE16 &&
+       prob.N % 16 == 0 && prob.K % 64 == 0 && !widen_prepass_disabled())
+    {
+        int prev_dev = 0;
+        B200_CUDA(cudaGetDevice(&prev_dev));
+        if(prev_dev != prob.device)
+            B200_CUDA(cudaSetDevice(prob.device));
+        struct Restore
+        {
+            int prev, cur;
+            ~Restore()
+            {
+                if(prev != cur)
+                    cudaSetDevice(prev);
+            }
+        } restore{prev_dev, prob.device};
+        void* widened = nullptr;
+        {
+            std::lock_guard<std::mutex> lk(g_mutex);
+            DeviceState& st    = device_state(prob.device);
+            StreamWorkspace& w = st.ws[prob.stream];
+            const size_t bytes = static_cast<size_t>(prob.N) * static_cast<size_t>(prob.K);
+            bool usable        = w.widened_bytes >= bytes;
+            if(!usable)
+            {
+                cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+                cudaStreamIsCapturing(prob.stream, &cap);
+                if(cap == cudaStreamCaptureStatusNone)
+                {
+                    if(w.widened != nullptr)
+                    {
+                        B200_CUDA(cudaStreamSynchronize(prob.stream));
+                        B200_CUDA(cudaFree(w.widened));
+                        w.widened       = nullptr;
+                        w.widened_bytes = 0;
+                    }
+                    B200_CUDA(cudaMalloc(&w.widened, bytes));
+                    w.widened_bytes = bytes;
+                    usable          = true;
+                }
+            }
+            if(usable)
+            {
+                widened                 = w.widened;
+                const int chunks_in     = static_cast<int>(prob.K / 2 / 16);
+                const long long rblocks = prob.N / 16;
+                const long long total   = rblocks * chunks_in * 16;
+                const int threads       = 256;
+                const int blocks        = static_cast<int>(std::min<long long>((total + threads - 1) / threads, 148LL * 16));
+                widen_e2m1_tile16_kernel<<<blocks, threads, 0, prob.stream>>>(static_cast<const uint4*>(prob.wgt.ptr),
+                                                                              static_cast<uint4*>(widened), rblocks, chunks_in);
+                B200_CUDA(cudaGetLastError());
+                g_launches.fetch_add(1);
+            }
+        }
+        if(widened != nullptr)
+        {
+            GemmProblem p2 = prob;
+            p2.kind        = PK_MXFP8;
+            p2.wgt.ptr     = widened;
+            p2.wgt.kbytes  = prob.K;
+            p2.wgt.ld_bytes = prob.K;
+            launch_gemm_locked(p2);
+            return;
+        }
+    }
+    launch_gemm_locked(prob);
+}
+
+static void launch_gemm_locked(const GemmProblem& prob)
 {
     B200_CHECK(prob.M > 0 && prob.N > 0 && prob.K > 0, "empty GEMM: M=", prob.M, " N=", prob.N, " K=", prob.K);
     B200_CHECK(prob.M < (1LL << 31) && prob.N < (1LL << 31) && prob.K < (1LL << 31), "dimension too large");

@@ -238,6 +238,19 @@ def test_a8w4_every_tile_shape(ab, name):
     assert_healthy(ab)
 
 
+def test_a8w4_tall_problem_takes_the_widening_prepass(ab):
+    # M >= 1024: the packed e2m1 weight is widened to e4m3 once (one extra launch) and the GEMM runs as MXFP8;
+    # the result must match the in-kernel path's oracle all the same, twice in a row (buffer re-use)
+    M, N, K = 1024, 512, 1024
+    ref, args = a8w4_case(ab, M, N, K, 0, seed=21)
+    before = ab.launch_count()
+    out = ab.gemm_a8w4_mxfp8(*args, a_preshuffle=False)
+    assert ab.launch_count() == before + 2
+    check(ref, out, what="a8w4 with widening pre-pass")
+    check(ref, ab.gemm_a8w4_mxfp8(*args, a_preshuffle=False), what="a8w4 with widening pre-pass, second call")
+    assert_healthy(ab)
+
+
 def test_a8w4_constant_known_answer(ab):
     # A = 0.5 (e4m3), B nibbles 0x1 = 0.5 (e2m1), unit scales: every output is 0.25 * K
     M, N, K = 32, 256, 512
@@ -335,11 +348,28 @@ def test_many_units_per_cta(ab):
 
 
 def test_mxfp4_large_pair_tiles(ab):
-    M, N, K = 1024, 7168, 2048
+    # M >= 1024, K >= 4096 and K % 256 == 0: both e8m0_shuffle scale tensors are re-laid once (two extra launches)
+    M, N, K = 1024, 1792, 4096
     ref, xq, wq, xs, ws = mxfp4_case(ab, M, N, K, seed=23)
+    args = (to_cuda_u8(xq, ab.dtypes.fp4x2), ab.shuffle_weight(to_cuda_u8(wq)),
+            ab.fp4_utils.e8m0_shuffle(to_cuda_u8(xs)), ab.fp4_utils.e8m0_shuffle(to_cuda_u8(ws)))
+    before = ab.launch_count()
+    out = ab.gemm_a4w4(*args)
+    assert ab.launch_count() == before + 3
+    check(ref, out, what="gemm_a4w4 1024x1792x4096 (heuristic)")
+    check(ref, ab.gemm_a4w4(*args), what="gemm_a4w4 1024x1792x4096, second call")
+    assert_healthy(ab)
+
+
+def test_mxfp4_tall_ragged_keeps_the_in_kernel_scale_path(ab):
+    # K % 256 != 0: no re-layout pass, the e8m0_shuffle order is consumed by the kernel itself
+    M, N, K = 1100, 512, 1216
+    ref, xq, wq, xs, ws = mxfp4_case(ab, M, N, K, seed=25)
+    before = ab.launch_count()
     out = ab.gemm_a4w4(to_cuda_u8(xq, ab.dtypes.fp4x2), ab.shuffle_weight(to_cuda_u8(wq)),
                        ab.fp4_utils.e8m0_shuffle(to_cuda_u8(xs)), ab.fp4_utils.e8m0_shuffle(to_cuda_u8(ws)))
-    check(ref, out, what="gemm_a4w4 1024x7168x2048 (heuristic)")
+    assert ab.launch_count() == before + 1
+    check(ref, out, what="gemm_a4w4 1100x512x1216")
     assert_healthy(ab)
 
 
