@@ -33,7 +33,15 @@ from .gemm_op_a8w8 import (  # noqa: E402,F401
     gemm_a8w8_mxfp8_noalloc,
 )
 from .gemm_op_a16w16 import gemm_a16w16_asm, gemm_a16w16_opus, opus_gemm, opus_gemm_a16w16_tune  # noqa: E402,F401
-from .quant import get_torch_quant, per_1x32_f4_quant, per_1x32_f8_scale_f8_quant  # noqa: E402,F401
+from .quant import (  # noqa: E402,F401
+    dynamic_per_group_scaled_quant,
+    get_hip_quant,
+    get_torch_quant,
+    per_1x32_f4_quant,
+    per_1x32_f4_quant_hip,
+    per_1x32_f8_scale_f8_quant,
+    per_1x32_mx_quant_hip,
+)
 from .shuffle import (  # noqa: E402,F401
     shuffle_mxfp8fp4_a,
     shuffle_mxfp8fp4_b,

@@ -78,6 +78,7 @@ SIGNATURES = {
     "gemm_a16w16_asm": (T, T, T, T, T, I, S, I),
     "opus_gemm_a16w16_tune": (T, T, T, T, I, I),
     "opus_gemm": (T, T, T, T, T, T, T),
+    "dynamic_per_group_scaled_quant": (T, T, T, I, I, T, I),
     "gemm_a8w8_blockscale": (T, T, T, T, T, I, S),
     "gemm_a8w8_blockscale_tune": (T, T, T, T, T, I, I),
     "gemm_a8w8_blockscale_bpreshuffle": (T, T, T, T, T, I, S),

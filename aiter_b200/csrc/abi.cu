@@ -2,6 +2,7 @@
 #include "../../include/aiter_b200.h"
 #include "gemm_common.cuh"
 #include "launch.h"
+#include "quant_mx.cuh"
 
 #include <climits>
 #include <string>
@@ -470,3 +471,69 @@ extern "C" const char* aiter_b200_heuristic_name(int kind, int M, int N, int K, 
     return g_heuristic_name.c_str();
 }
 extern "C" unsigned long long aiter_b200_launch_count(void) { return launch_count(); }
+
+// ------------------------------------------------------------------------------------------- dynamic 1x32 MX quantisation
+extern "C" int dynamic_per_group_scaled_quant(aiter_tensor_t* out, aiter_tensor_t* input, aiter_tensor_t* scales, int group_size,
+                                              int shuffle_scale, aiter_tensor_t* num_rows, int num_rows_factor, void* stream)
+{
+    return safe_call([&] {
+        const char* fn = "dynamic_per_group_scaled_quant";
+        require_tensor(out, fn, "out", 2);
+        require_tensor(input, fn, "input", 2);
+        B200_CHECK(scales != nullptr && scales->device_id >= 0 && scales->ptr != nullptr, fn, ": scales must be a GPU tensor");
+        B200_CHECK(group_size == 32, fn, ": only group_size 32 (MX blocks) is built, got ", group_size);
+        B200_CHECK(num_rows == nullptr && num_rows_factor == 1, fn, ": num_rows / num_rows_factor (MoE row masks) are not built");
+        B200_CHECK(shuffle_scale >= 0 && shuffle_scale <= 2, fn, ": shuffle_scale must be 0 (plain), 1 (e8m0_shuffle) or 2 ((m/32,k/4,32,4))");
+        B200_CHECK(input->dtype_ == AITER_DTYPE_bf16 || input->dtype_ == AITER_DTYPE_fp16, fn, ": input must be bf16 or fp16, got ",
+                   dtype_name(input->dtype_));
+        const bool fp4 = (out->dtype_ == AITER_DTYPE_fp4x2 || out->dtype_ == AITER_DTYPE_u8);
+        B200_CHECK(fp4 || out->dtype_ == AITER_DTYPE_fp8, fn, ": out must be fp4x2 / uint8 (MXFP4) or fp8 (MXFP8), got ", dtype_name(out->dtype_));
+        B200_CHECK(scales->dtype_ == AITER_DTYPE_fp8_e8m0 || scales->dtype_ == AITER_DTYPE_u8, fn,
+                   ": only e8m0 byte scales are built (fp32 scales: use the torch path), got ", dtype_name(scales->dtype_));
+        const long long M = input->shape[0], K = input->shape[1];
+        B200_CHECK(M > 0 && K > 0 && K % 32 == 0, fn, ": input must be [M, K] with K a multiple of 32");
+        require_rows_contiguous(input, fn, "input");
+        require_rows_contiguous(out, fn, "out");
+        B200_CHECK(input->strides[0] % 8 == 0 && (reinterpret_cast<uintptr_t>(input->ptr) & 15) == 0, fn,
+                   ": input rows must start on 16-byte boundaries");
+        B200_CHECK(out->shape[0] == M && out->shape[1] == (fp4 ? K / 2 : K), fn, ": out must be [M, ", (fp4 ? "K/2" : "K"), "]");
+        B200_CHECK((reinterpret_cast<uintptr_t>(out->ptr) & 7) == 0 && out->strides[0] % 8 == 0, fn, ": out rows must start on 8-byte boundaries");
+        const long long kblocks = K / 32;
+        B200_CHECK(scales->ndim == 2 && (scales->strides[1] == 1 || scales->shape[1] == 1) && scales->strides[0] == scales->shape[1], fn,
+                   ": scales must be a dense 2-D tensor");
+        QuantParams prm{};
+        prm.layout = shuffle_scale;
+        if(shuffle_scale == QSL_E8M0_SHUFFLE)
+        {
+            B200_CHECK(scales->shape[0] >= (M + 31) / 32 * 32 && scales->shape[1] >= (kblocks + 7) / 8 * 8 && scales->shape[1] % 8 == 0, fn,
+                       ": shuffled scales must be [>= pad32(M), pad8(K/32)] (the reference allocates [pad256(M), pad8(K/32)])");
+            B200_CHECK((reinterpret_cast<uintptr_t>(scales->ptr) & 7) == 0, fn, ": scales must be 8-byte aligned");
+        }
+        else if(shuffle_scale == QSL_M32K4)
+        {
+            B200_CHECK(K % 128 == 0, fn, ": the (m/32,k/4,32,4) scale layout needs K % 128 == 0");
+            B200_CHECK(scales->shape[0] >= (M + 31) / 32 * 32 && scales->shape[1] == kblocks, fn, ": scales must be [pad32(M), K/32]");
+            B200_CHECK((reinterpret_cast<uintptr_t>(scales->ptr) & 7) == 0, fn, ": scales must be 8-byte aligned");
+        }
+        else
+            B200_CHECK(scales->shape[0] >= M && scales->shape[1] >= kblocks, fn, ": scales must be [M, K/32]");
+        prm.in         = input->ptr;
+        prm.in_ld      = input->strides[0];
+        prm.out        = static_cast<uint8_t*>(out->ptr);
+        prm.out_ld     = out->strides[0];
+        prm.scale      = static_cast<uint8_t*>(scales->ptr);
+        prm.M          = M;
+        prm.kblocks    = static_cast<int>(kblocks);
+        prm.scale_cols = static_cast<int>(scales->shape[1]);
+        int prev = 0;
+        B200_CUDA(cudaGetDevice(&prev));
+        if(prev != input->device_id)
+            B200_CUDA(cudaSetDevice(input->device_id));
+        launch_quant_mx(prm, fp4, input->dtype_ == AITER_DTYPE_bf16, static_cast<cudaStream_t>(stream));
+        const cudaError_t e = cudaGetLastError();
+        if(prev != input->device_id)
+            cudaSetDevice(prev);
+        B200_CHECK(e == cudaSuccess, fn, ": launch failed: ", cudaGetErrorString(e));
+        count_launch();
+    });
+}

@@ -215,6 +215,7 @@ void read_device_status(int device, unsigned int out_words[4])
 }
 
 unsigned long long launch_count() { return g_launches.load(); }
+void count_launch() { g_launches.fetch_add(1); }
 
 // ---------------------------------------------------------------------------------------------
 // configuration menu / heuristic

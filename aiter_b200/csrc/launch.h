@@ -121,6 +121,7 @@ struct BlockScaleProblem
 void launch_blockscale(const BlockScaleProblem& prob);
 void read_device_status(int device, unsigned int out_words[4]);
 unsigned long long launch_count();
+void count_launch(); // kernels launched outside launch.cu report themselves here
 int device_sm_count(int device);
 
 } // namespace b200

@@ -66,6 +66,70 @@ def per_1x32_f8_scale_f8_quant(x: Tensor, scale=None, quant_dtype=dtypes.fp8, sc
     return y, sb
 
 
+def dynamic_per_group_scaled_quant(out: Tensor, input: Tensor, scales: Tensor, group_size: int = 32, shuffle_scale=True,
+                                   num_rows: Tensor | None = None, num_rows_factor: int = 1) -> None:
+    """CUDA 1x32 MX quantiser (aiter/ops/quant.py:766-791): `out.dtype` selects MXFP4 (fp4x2 / uint8) or MXFP8 (fp8);
+    `scales` receives e8m0 bytes.  shuffle_scale: False plain [M, K/32]; True e8m0_shuffle order; 2 the
+    (m/32, k/4, 32, 4) order the MXFP8 GEMM entry points take."""
+    from . import _ffi
+
+    _ffi.call("dynamic_per_group_scaled_quant", out, input, scales, group_size, int(shuffle_scale), num_rows, num_rows_factor)
+
+
+def per_1x32_mx_quant_hip(x: Tensor, scale=None, quant_dtype=dtypes.fp4x2, shuffle=False, num_rows: Tensor | None = None,
+                          num_rows_factor: int = 1, scale_type=None):
+    """Fused dynamic 1x32 MX quantisation on the GPU (aiter/ops/quant.py:486-597): returns (y, scale) with the scales
+    already in the layout the GEMM reads.  fp4x2: y [M, K/2], e8m0 scales [M, K/32], or [pad256(M), pad8(K/32)] in
+    e8m0_shuffle order when shuffle=True.  fp8 (scale_type must be fp8_e8m0 here): y [M, K] e4m3, same scale shapes;
+    shuffle=2 gives the (m/32, k/4, 32, 4) order of the MXFP8 GEMMs in a [pad32(M), K/32] array."""
+    if scale is not None:
+        raise ValueError("unsupported: static per token quant")
+    assert x.dim() == 2, "per_1x32_mx_quant_hip takes a 2-D input"
+    m, n = x.shape
+    assert n % 32 == 0, f"n={n} must be divisible by 32"
+    if quant_dtype == dtypes.fp4x2:
+        if scale_type is not None and scale_type != dtypes.fp8_e8m0:
+            raise ValueError(f"per_1x32_mx_quant_hip: fp4x2 output requires e8m0 scale; got scale_type={scale_type}")
+        out_cols = n // 2
+    elif quant_dtype == dtypes.fp8:
+        if scale_type is None or scale_type == dtypes.fp32:
+            raise NotImplementedError("per_1x32_mx_quant_hip(fp8): only scale_type=dtypes.fp8_e8m0 runs on the GPU here; "
+                                      "fp32 scales: per_1x32_f8_scale_f8_quant")
+        if scale_type != dtypes.fp8_e8m0:
+            raise ValueError(f"per_1x32_mx_quant_hip: fp8 output expects scale_type in {{fp32, fp8_e8m0}}, got {scale_type}")
+        out_cols = n
+    else:
+        raise ValueError(f"per_1x32_mx_quant_hip: unsupported quant_dtype {quant_dtype}, expected one of (dtypes.fp4x2, dtypes.fp8)")
+    kb = n // 32
+    if shuffle == 2:
+        shape = ((m + 31) // 32 * 32, kb)
+    elif shuffle:
+        shape = ((m + 255) // 256 * 256, (kb + 7) // 8 * 8)
+    else:
+        shape = (m, kb)
+    scale = torch.empty(shape, dtype=torch.uint8, device=x.device).view(dtypes.fp8_e8m0)
+    y = torch.empty((m, out_cols), dtype=torch.uint8, device=x.device).view(quant_dtype)
+    dynamic_per_group_scaled_quant(y, x, scale, 32, shuffle_scale=shuffle, num_rows=num_rows, num_rows_factor=num_rows_factor)
+    return y, scale
+
+
+def per_1x32_f4_quant_hip(x: Tensor, scale=None, quant_dtype=dtypes.fp4x2, shuffle=False, num_rows: Tensor | None = None,
+                          num_rows_factor: int = 1):
+    """fp4-only wrapper kept for callers of the older name (aiter/ops/quant.py:600-626)."""
+    assert quant_dtype == dtypes.fp4x2, "per_1x32_f4_quant_hip is fp4-only; use per_1x32_mx_quant_hip for fp8"
+    return per_1x32_mx_quant_hip(x, scale=scale, quant_dtype=quant_dtype, shuffle=shuffle, num_rows=num_rows,
+                                 num_rows_factor=num_rows_factor)
+
+
+def get_hip_quant(qType):
+    """QuantType.per_1x32 -> the fused GPU quantiser; other quant types are outside this library's path."""
+    from .dtypes import QuantType
+
+    if qType == QuantType.per_1x32:
+        return per_1x32_mx_quant_hip
+    raise NotImplementedError(f"get_hip_quant({qType}): only QuantType.per_1x32 is built")
+
+
 def get_torch_quant(qType):
     table = {
         QuantType.No: lambda *a, **k: (a[0], None),

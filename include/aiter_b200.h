@@ -141,6 +141,17 @@ AITER_B200_API int aiter_b200_gemm_a8w8_mxfp8_noalloc(aiter_tensor_t* A, aiter_t
                                                       aiter_tensor_t* ScaleB, aiter_tensor_t* out, int a_preshuffle,
                                                       int log2_k_split, void* stream);
 
+/* ---- dynamic 1x32 MX quantisation of activations (the step in front of the GEMM) ----
+ * Replaces dynamic_per_group_scaled_quant (csrc/include/quant.h:29-35, kernel csrc/kernels/quant_mxfp4.cu:88-212;
+ * Python: per_1x32_mx_quant_hip, aiter/ops/quant.py:486-597).  input [M, K] bf16 / fp16; out [M, K/2] fp4x2 / uint8
+ * (MXFP4) or [M, K] fp8 (MXFP8); scales: e8m0 bytes, RoundUp(amax / max) per 32 elements.
+ * shuffle_scale 0: scales [M, K/32]; 1: e8m0_shuffle order in a [pad256(M), pad8(K/32)] array (what gemm_a4w4 takes);
+ * 2 (no counterpart in the reference): the (m/32, k/4, 32, 4) order in a [pad32(M), K/32] array, what the MXFP8 /
+ * mixed GEMM entry points take.  group_size must be 32; num_rows must be NULL and num_rows_factor 1. */
+AITER_B200_API int dynamic_per_group_scaled_quant(aiter_tensor_t* out, aiter_tensor_t* input, aiter_tensor_t* scales,
+                                                  int group_size, int shuffle_scale, aiter_tensor_t* num_rows,
+                                                  int num_rows_factor, void* stream);
+
 /* ---- library state ---- */
 /* Copies the 4-word device status record of `device` (0 = healthy; non-zero = a bounded wait
  * inside a kernel expired: code, block, split, iteration) and clears it.  Synchronises the device. */
