@@ -222,6 +222,15 @@ def run_sweep(torch, ab, device, peaks):
         add("a8w4", M, 8192, 8192, lambda a, b, sa, sb: ab.gemm_a8w4_mxfp8(a, b, sa, sb, a_preshuffle=False),
             lambda i, M=M: (rand_u8(0, 0x78, M, 8192).view(torch.float8_e4m3fn), rand_u8(0, 256, 8192, 4096),
                             rand_u8(120, 130, (M + 31) // 32 * 32, 256), rand_u8(120, 130, 8192, 256)))
+    # fused activation quantiser (bf16 -> MX data + scales in the GEMM's layout): HBM-bound
+    for (kind, M, K, kw) in (("quant_mxfp4", 16384, 16384, dict(quant_dtype=ab.dtypes.fp4x2, shuffle=True)),
+                             ("quant_mxfp8", 8192, 4096, dict(quant_dtype=ab.dtypes.fp8, scale_type=ab.dtypes.fp8_e8m0, shuffle=2)),
+                             ("quant_mxfp4", 32, 16384, dict(quant_dtype=ab.dtypes.fp4x2, shuffle=True))):
+        b = int(M * K * 2 + M * K * (0.5 if kind == "quant_mxfp4" else 1.0) + M * K / 32)
+        sets = rotating_sets(lambda i, M=M, K=K: (torch.randn(M, K, device=device).to(torch.bfloat16),), M * K * 2)
+        us = graph_time_calls(torch, lambda x, kw=kw: ab.per_1x32_mx_quant_hip(x, **kw), sets, 20, 3)
+        rows.append({"kind": kind, "M": M, "N": 0, "K": K, "us": round(us, 2), "tflops": 0.0, "gbs": round(b / us / 1e3, 1),
+                     "frac_tensor": 0.0, "frac_hbm": round(b / us / 1e3 / peaks["hbm_gbs"], 4), "kernel": "quant_mx_kernel"})
     return rows
 
 
