@@ -246,8 +246,10 @@ static void run_blockscale(const char* fn, aiter_tensor_t* XQ, aiter_tensor_t* W
     require_tensor(w_scale, fn, "w_scale", 2);
     require_tensor(Out, fn, "Out", 2);
     B200_CHECK(is_byte_dtype(XQ->dtype_) && is_byte_dtype(WQ->dtype_), fn, ": XQ and WQ must be fp8 (1-byte) tensors");
-    B200_CHECK(x_scale->dtype_ == AITER_DTYPE_fp32 && w_scale->dtype_ == AITER_DTYPE_fp32, fn,
-               ": scales must be fp32 (convert e8m0 scales first)");
+    const bool sx8 = (x_scale->dtype_ == AITER_DTYPE_fp8_e8m0 || x_scale->dtype_ == AITER_DTYPE_u8);
+    const bool sw8 = (w_scale->dtype_ == AITER_DTYPE_fp8_e8m0 || w_scale->dtype_ == AITER_DTYPE_u8);
+    B200_CHECK((x_scale->dtype_ == AITER_DTYPE_fp32 && w_scale->dtype_ == AITER_DTYPE_fp32) || (sx8 && sw8), fn,
+               ": scales must both be fp32 or both be e8m0 bytes");
     B200_CHECK(Out->dtype_ == AITER_DTYPE_bf16, fn, ": only bf16 output is built");
     const long long M = XQ->shape[0], K = XQ->shape[1], N = WQ->shape[0];
     B200_CHECK(WQ->shape[1] == K, fn, ": XQ and WQ disagree on K");
@@ -276,6 +278,7 @@ static void run_blockscale(const char* fn, aiter_tensor_t* XQ, aiter_tensor_t* W
         p.xs_stride_k = x_scale->strides[1];
     }
     p.w_scale = static_cast<const float*>(w_scale->ptr);
+    p.scales_are_e8m0 = sx8 && sw8;
     p.out     = Out->ptr;
     p.ldo     = Out->strides[0];
     p.device  = XQ->device_id;

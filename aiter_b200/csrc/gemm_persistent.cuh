@@ -209,8 +209,9 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
         mbar_fence_init();
         fence_proxy_async_smem();
     }
-    if(warp == 0 && lane == 0)
+    if(warp == 10 && lane == 0)
     {
+        // the descriptor fetch (about a microsecond, cold) runs while thread 0 initialises the barriers
         tma_prefetch_desc(&map_p);
         tma_prefetch_desc(&map_q);
         if(kScaled)
@@ -239,6 +240,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
     if(threadIdx.x == 0) stamp(1);
+    // Programmatic dependent launch: everything above (barriers, TMEM, descriptor prefetch) may overlap the tail of
+    // the previous kernel in the stream; nothing below may touch global memory before that kernel has completed.
+    // The next kernel's CTAs may in turn be scheduled as soon as every CTA of this grid has got here.
+    grid_dependency_wait();
+    grid_launch_dependents();
 
     const int q_rows_cta       = bn / CG;
     const uint32_t q_box_bytes = static_cast<uint32_t>(q_rows_cta) * kTileKBytes;

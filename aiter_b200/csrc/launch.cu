@@ -357,6 +357,12 @@ const char* kernel_menu_text()
 // ---------------------------------------------------------------------------------------------
 // launch
 // ---------------------------------------------------------------------------------------------
+static bool pdl_disabled()
+{
+    static const bool off = (std::getenv("AITER_B200_NO_PDL") != nullptr);
+    return off;
+}
+
 // Raise the dynamic shared-memory limit once per device for one kernel; `attr_done` is the caller's
 // per-instantiation flag array (caller holds g_mutex).
 template <typename Kernel>
@@ -384,13 +390,17 @@ static void launch_persistent(int ctas, size_t smem, cudaStream_t stream, const 
     lc.blockDim         = dim3(kPersistentThreads, 1, 1);
     lc.dynamicSmemBytes = smem;
     lc.stream           = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id               = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CG * (prm.csplit > 1 ? prm.csplit : 1);
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // this kernel's prologue may start while the previous kernel of the stream drains (it waits with
+    // griddepcontrol.wait before its first global access)
+    attr[1].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs    = attr;
-    lc.numAttrs = 1;
+    lc.numAttrs = pdl_disabled() ? 1 : 2;
     B200_CUDA(cudaLaunchKernelEx(&lc, kernel, mp, mq, msp, msq, mo, prm));
     g_launches.fetch_add(1);
 }
@@ -509,6 +519,8 @@ constexpr long long kScalePrepassMinK = 4096; // the two extra launches (~6 us) 
 
 void launch_gemm(const GemmProblem& prob)
 {
+    if(prob.M == 0 && prob.N > 0 && prob.K > 0)
+        return; // no activation rows: nothing to compute, the (empty) output is already complete
     if(prob.kind == PK_MXFP4 && prob.M >= kScalePrepassMinM && prob.scratch == nullptr && prob.act_sf.wire == SFW_E8M0_SHUFFLE &&
        prob.wgt_sf.wire == SFW_E8M0_SHUFFLE && prob.K % 256 == 0 && prob.K >= kScalePrepassMinK && !relay_prepass_disabled())
     {
@@ -878,8 +890,98 @@ static void launch_gemm_locked(const GemmProblem& prob)
         print_trace(st, prob, cfg, tiles_p, tiles_q, splits, stages);
 }
 
+// One UE8M0 byte per (row, 128-wide K block) -> the (m/32, k/4, 32, 4) order of the MXFP8 kernel: the four 32-blocks
+// of a 128 block share the byte.  rows_per_scale = 1 (activations) or 128 (weights: one byte per 128 x 128 block).
+__global__ void expand_block128_scales_kernel(const uint8_t* __restrict__ src, long long stride_row, long long stride_k, uint32_t* __restrict__ dst,
+                                              long long rows, long long groups, int kb128, int rows_per_scale)
+{
+    const long long total = groups * kb128 * 32;
+    for(long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+        i += static_cast<long long>(gridDim.x) * blockDim.x)
+    {
+        const int r         = static_cast<int>(i & 31);
+        const long long t   = i >> 5;
+        const int kb        = static_cast<int>(t % kb128);
+        const long long row = (t / kb128) * 32 + r;
+        const uint32_t b    = row < rows ? src[(row / rows_per_scale) * stride_row + kb * stride_k] : 0x7Fu;
+        dst[i]              = b * 0x01010101u;
+    }
+}
+
+static void launch_blockscale_e8m0(const BlockScaleProblem& prob)
+{
+    int prev_dev = 0;
+    B200_CUDA(cudaGetDevice(&prev_dev));
+    if(prev_dev != prob.device)
+        B200_CUDA(cudaSetDevice(prob.device));
+    struct Restore
+    {
+        int prev, cur;
+        ~Restore()
+        {
+            if(prev != cur)
+                cudaSetDevice(prev);
+        }
+    } restore{prev_dev, prob.device};
+    const int kb128    = static_cast<int>(prob.K / 128);
+    const long long ga = (prob.M + 31) / 32, gw = (prob.N + 31) / 32;
+    uint32_t* buf      = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_mutex);
+        DeviceState& st    = device_state(prob.device);
+        StreamWorkspace& w = st.ws[prob.stream];
+        const size_t bytes = static_cast<size_t>(ga + gw) * 32 * kb128 * 4;
+        if(w.relaid_bytes < bytes)
+        {
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            cudaStreamIsCapturing(prob.stream, &cap);
+            B200_CHECK(cap == cudaStreamCaptureStatusNone, "the scale buffer must grow (", bytes,
+                       " bytes) but the stream is being captured; run this shape once outside capture first");
+            if(w.relaid != nullptr)
+            {
+                B200_CUDA(cudaStreamSynchronize(prob.stream));
+                B200_CUDA(cudaFree(w.relaid));
+                w.relaid       = nullptr;
+                w.relaid_bytes = 0;
+            }
+            B200_CUDA(cudaMalloc(&w.relaid, bytes));
+            w.relaid_bytes = bytes;
+        }
+        buf = static_cast<uint32_t*>(w.relaid);
+        auto run = [&](const uint8_t* src, long long sr, long long sk, uint32_t* dst, long long rows, long long groups, int per) {
+            const long long total = groups * kb128 * 32;
+            const int blocks      = static_cast<int>(std::min<long long>((total + 255) / 256, 148LL * 8));
+            expand_block128_scales_kernel<<<blocks, 256, 0, prob.stream>>>(src, sr, sk, dst, rows, groups, kb128, per);
+            B200_CUDA(cudaGetLastError());
+            g_launches.fetch_add(1);
+        };
+        run(reinterpret_cast<const uint8_t*>(prob.x_scale), prob.xs_stride_m, prob.xs_stride_k, buf, prob.M, ga, 1);
+        run(reinterpret_cast<const uint8_t*>(prob.w_scale), kb128, 1, buf + ga * 32 * kb128, prob.N, gw, 128);
+    }
+    GemmProblem p;
+    p.kind   = PK_MXFP8;
+    p.M = prob.M; p.N = prob.N; p.K = prob.K;
+    p.act    = prob.act;
+    p.wgt    = prob.wgt;
+    p.act_sf = ScaleOperand{buf, SFW_G1250, ga * 32, prob.K / 32};
+    p.wgt_sf = ScaleOperand{buf + ga * 32 * kb128, SFW_G1250, gw * 32, prob.K / 32};
+    p.out    = prob.out;
+    p.ldo    = prob.ldo;
+    p.device = prob.device;
+    p.stream = prob.stream;
+    launch_gemm(p);
+}
+
 void launch_blockscale(const BlockScaleProblem& prob)
 {
+    if(prob.M == 0 && prob.N > 0 && prob.K > 0)
+        return;
+    if(prob.scales_are_e8m0)
+    {
+        B200_CHECK(prob.K % 128 == 0, "K must be a multiple of 128 for 128-wide scale blocks (got ", prob.K, ")");
+        launch_blockscale_e8m0(prob);
+        return;
+    }
     B200_CHECK(prob.M > 0 && prob.N > 0 && prob.K > 0, "empty GEMM: M=", prob.M, " N=", prob.N, " K=", prob.K);
     B200_CHECK(prob.K % 128 == 0, "K must be a multiple of 128 for 128-wide scale blocks (got ", prob.K, ")");
     int prev_dev = 0;

@@ -113,6 +113,9 @@ struct BlockScaleProblem
     const float* x_scale = nullptr;
     long long xs_stride_m = 0, xs_stride_k = 0;
     const float* w_scale = nullptr;
+    // both scale tensors hold UE8M0 bytes instead of floats (same shapes and strides, in bytes): powers of two ride
+    // the block-scaled MMA, so the problem runs on the MXFP8 kernel after a small expansion of the scales
+    bool scales_are_e8m0 = false;
     void* out = nullptr;
     long long ldo = 0;
     int device = 0;

@@ -356,6 +356,10 @@ __host__ __device__ constexpr uint32_t idesc_block_scaled(uint32_t afmt, uint32_
 {
     return (afmt << 7) | (bfmt << 10) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24);
 }
+// programmatic dependent launch (no-ops when the launch carries no programmatic dependency)
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint64_t pack_u64(uint32_t lo, uint32_t hi)
 {
     uint64_t v;

@@ -17,8 +17,17 @@ def get_CKGEMM_config(M: int, N: int, K: int, bpreshuffle: bool = False):
     return (_blockscale_bpreshuffle_table if bpreshuffle else _blockscale_table).lookup(M, N, K)
 
 
-def _fp32_scale(s: Tensor) -> Tensor:
-    return fp4_utils.e8m0_to_f32(s) if s.dtype in (dtypes.fp8_e8m0, torch.uint8) else s
+def _is_e8m0(s: Tensor) -> bool:
+    return s.dtype in (dtypes.fp8_e8m0, torch.uint8)
+
+
+def _blockscale_scales(x_scale: Tensor, w_scale: Tensor):
+    """Both e8m0: passed on as bytes (powers of two ride the block-scaled MMA: the problem runs on the MXFP8 kernel).
+    Otherwise both go to fp32, e8m0 ones widened first as the reference does (gemm_op_a8w8.py:952-956)."""
+    if _is_e8m0(x_scale) and _is_e8m0(w_scale):
+        return x_scale, w_scale
+    return (fp4_utils.e8m0_to_f32(x_scale) if _is_e8m0(x_scale) else x_scale,
+            fp4_utils.e8m0_to_f32(w_scale) if _is_e8m0(w_scale) else w_scale)
 
 
 def gemm_a8w8_blockscale(XQ: Tensor, WQ: Tensor, x_scale: Tensor, w_scale: Tensor, dtype: torch.dtype = dtypes.bf16,
@@ -32,7 +41,8 @@ def gemm_a8w8_blockscale(XQ: Tensor, WQ: Tensor, x_scale: Tensor, w_scale: Tenso
     Y = torch.empty(m, n, dtype=dtype, device=XQ.device)
     cfg = get_CKGEMM_config(m, n, k)
     splitK, kernelName = (int(cfg.get("splitK") or 0), str(cfg.get("kernelName") or "")) if cfg is not None else (0, "")
-    _ffi.call("gemm_a8w8_blockscale", XQ, WQ, _fp32_scale(x_scale), _fp32_scale(w_scale), Y, splitK, kernelName or None)
+    xs, ws = _blockscale_scales(x_scale, w_scale)
+    _ffi.call("gemm_a8w8_blockscale", XQ, WQ, xs, ws, Y, splitK, kernelName or None)
     return Y
 
 
@@ -46,7 +56,8 @@ def gemm_a8w8_blockscale_bpreshuffle(XQ: Tensor, WQ: Tensor, x_scale: Tensor, w_
     Y = torch.empty(m, n, dtype=dtype, device=XQ.device)
     cfg = get_CKGEMM_config(m, n, k, bpreshuffle=True)
     splitK, kernelName = (int(cfg.get("splitK") or 0), str(cfg.get("kernelName") or "")) if cfg is not None else (0, "")
-    _ffi.call("gemm_a8w8_blockscale_bpreshuffle", XQ, WQ, _fp32_scale(x_scale), _fp32_scale(w_scale), Y, splitK, kernelName or None)
+    xs, ws = _blockscale_scales(x_scale, w_scale)
+    _ffi.call("gemm_a8w8_blockscale_bpreshuffle", XQ, WQ, xs, ws, Y, splitK, kernelName or None)
     return Y
 
 

@@ -314,17 +314,28 @@ def test_a8w8_blockscale_fp32_scales(ab, M, N, K, bpre):
     assert_healthy(ab)
 
 
-def test_a8w8_blockscale_e8m0_scales_are_widened(ab):
-    M, N, K = 64, 256, 512
-    g = torch.Generator().manual_seed(5)
+@pytest.mark.parametrize("M,N,K,bpre", [(64, 256, 512, False), (300, 1024, 2048, True), (1, 128, 128, False)])
+def test_a8w8_blockscale_e8m0_scales_run_as_mxfp8(ab, M, N, K, bpre):
+    # power-of-two scales ride the block-scaled MMA: two small expansion launches + the MXFP8 kernel
+    g = torch.Generator().manual_seed(5 + M)
     x = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn)
     w = torch.randn(N, K, generator=g).to(torch.float8_e4m3fn)
     xs = torch.randint(124, 130, (M, K // 128), generator=g, dtype=torch.uint8)
-    ws = torch.randint(124, 130, (N // 128, K // 128), generator=g, dtype=torch.uint8)
+    ws = torch.randint(124, 130, ((N + 127) // 128, K // 128), generator=g, dtype=torch.uint8)
     ref = ox.gemm_a8w8_blockscale_ref(x.view(torch.uint8).numpy(), w.view(torch.uint8).numpy(),
                                       ox.e8m0_to_f32(xs.numpy()), ox.e8m0_to_f32(ws.numpy()))
-    out = ab.gemm_a8w8_blockscale(x.cuda(), w.cuda(), xs.cuda().view(ab.dtypes.fp8_e8m0), ws.cuda().view(ab.dtypes.fp8_e8m0))
-    check(ref, out, what="blockscale with e8m0 scales")
+    before = ab.launch_count()
+    if bpre:
+        xs_t = xs.T.contiguous().cuda()  # K-block-major storage
+        out = ab.gemm_a8w8_blockscale_bpreshuffle(x.cuda(), ab.shuffle_weight(w.cuda(), layout=(16, 16)),
+                                                  xs_t.T.view(ab.dtypes.fp8_e8m0), ws.cuda().view(ab.dtypes.fp8_e8m0))
+    else:
+        out = ab.gemm_a8w8_blockscale(x.cuda(), w.cuda(), xs.cuda().view(ab.dtypes.fp8_e8m0), ws.cuda().view(ab.dtypes.fp8_e8m0))
+    assert ab.launch_count() == before + 3
+    check(ref, out, what=f"blockscale with e8m0 scales {M}x{N}x{K} bpre={bpre}")
+    # one e8m0 and one fp32 scale tensor: the e8m0 one is widened, the fp32 kernel runs
+    out = ab.gemm_a8w8_blockscale(x.cuda(), w.cuda(), xs.cuda().view(ab.dtypes.fp8_e8m0), ab.fp4_utils.e8m0_to_f32(ws.cuda()))
+    check(ref, out, what="blockscale with mixed scale dtypes")
     assert_healthy(ab)
 
 
@@ -400,3 +411,18 @@ def test_torch_ops_namespace_runs_the_cuda_path(ab):
                                     ab.shuffle_scale(torch.from_numpy(xs).cuda()), ab.shuffle_scale(torch.from_numpy(ws).cuda()))
     assert ab.launch_count() == before + 1
     check(ref, out, what="torch.ops.aiter.gemm_a4w4")
+
+
+def test_empty_activation_batch_is_a_no_op(ab):
+    # M = 0: every operator returns an empty [0, N] tensor and launches nothing
+    N, K = 256, 512
+    before = ab.launch_count()
+    w8 = ab.shuffle_mxfp8fp4_b(torch.zeros(N, K, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn))
+    s_w = ab.shuffle_mxfp8fp4_scale(torch.full((N, K // 32), 0x7F, dtype=torch.uint8, device="cuda"))
+    s_a = torch.empty(0, K // 32, dtype=torch.uint8, device="cuda")
+    out = ab.gemm_a8w8_mxfp8(torch.empty(0, K, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn), w8, s_a, s_w, a_preshuffle=False)
+    assert out.shape == (0, N)
+    out = ab.tgemm.mm(torch.empty(0, K, dtype=torch.bfloat16, device="cuda"), torch.zeros(N, K, dtype=torch.bfloat16, device="cuda"))
+    assert out.shape == (0, N)
+    assert ab.launch_count() == before
+    assert_healthy(ab)

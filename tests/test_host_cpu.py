@@ -184,3 +184,23 @@ def test_torch_library_ops_have_fake_implementations():
                                              torch.empty(128, 256, dtype=torch.float8_e4m3fn, device="meta"),
                                              torch.empty(9, 2, device="meta"), torch.empty(1, 2, device="meta"))
     assert o.shape == (9, 128)
+
+
+def test_fused_quantiser_wrappers_validate_arguments_on_cpu():
+    """Argument rules of per_1x32_mx_quant_hip (aiter/ops/quant.py:486-597) that need no GPU."""
+    import aiter_b200 as ab
+
+    x = torch.zeros(4, 64, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="static per token"):
+        ab.per_1x32_mx_quant_hip(x, scale=torch.zeros(1))
+    with pytest.raises(ValueError, match="requires e8m0"):
+        ab.per_1x32_mx_quant_hip(x, quant_dtype=ab.dtypes.fp4x2, scale_type=ab.dtypes.fp32)
+    with pytest.raises(ValueError, match="unsupported quant_dtype"):
+        ab.per_1x32_mx_quant_hip(x, quant_dtype=torch.int8)
+    with pytest.raises(AssertionError):
+        ab.per_1x32_mx_quant_hip(torch.zeros(4, 48, dtype=torch.bfloat16))
+    with pytest.raises(AssertionError, match="fp4-only"):
+        ab.per_1x32_f4_quant_hip(x, quant_dtype=ab.dtypes.fp8)
+    assert ab.get_hip_quant(ab.QuantType.per_1x32) is ab.per_1x32_mx_quant_hip
+    with pytest.raises(NotImplementedError):
+        ab.get_hip_quant(ab.QuantType.per_Tensor)
