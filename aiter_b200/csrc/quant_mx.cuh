@@ -68,80 +68,107 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const QuantParams prm)
     uint8_t* sf = sf_tile[warp];
     const T* in = static_cast<const T*>(prm.in);
 
-#pragma unroll 4
-    for(int r = 0; r < 32; ++r)
-    {
+    // Rows go through in groups of four; the next group's loads are issued before the current group is converted, so
+    // every lane keeps 4 to 8 sixteen-byte loads in flight.
+    const long long col_off = static_cast<long long>(tk) * 256 + lane * 8;
+    auto load_row = [&](int r) {
         const long long row = tm * 32 + r;
-        const bool ok       = blk_ok && row < prm.M;
         uint4 raw           = make_uint4(0, 0, 0, 0);
-        if(ok)
-            raw = *reinterpret_cast<const uint4*>(in + row * prm.in_ld + static_cast<long long>(tk) * 256 + lane * 8);
-        const T* e = reinterpret_cast<const T*>(&raw);
-        float v[8];
-        float amax = 0.f;
+        if(blk_ok && row < prm.M)
+            raw = __ldg(reinterpret_cast<const uint4*>(in + row * prm.in_ld + col_off));
+        return raw;
+    };
+    uint4 next[4];
 #pragma unroll
-        for(int i = 0; i < 8; ++i)
-        {
-            v[i] = to_f32<T>(e[i]);
-            amax = fmaxf(amax, fabsf(v[i]));
-        }
-        // NaN must survive the maximum (fmaxf drops it): carry it separately
-        bool has_nan = false;
+    for(int i = 0; i < 4; ++i)
+        next[i] = load_row(i);
+#pragma unroll 1
+    for(int r0 = 0; r0 < 32; r0 += 4)
+    {
+        uint4 cur[4];
 #pragma unroll
-        for(int i = 0; i < 8; ++i)
-            has_nan |= (v[i] != v[i]);
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        has_nan |= __shfl_xor_sync(0xffffffffu, has_nan ? 1 : 0, 1) != 0;
-        has_nan |= __shfl_xor_sync(0xffffffffu, has_nan ? 1 : 0, 2) != 0;
-        if(has_nan)
-            amax = __uint_as_float(0x7FC00000u);
-        const uint32_t qb = __float_as_uint(__fdiv_rn(amax, max_pos));
-        const uint32_t ex = (qb >> 23) & 0xFFu;
-        const uint32_t byte = ex + (((qb & 0x7FFFFFu) != 0u && ex < 0xFFu) ? 1u : 0u);
-        // 1 / 2^(byte-127), exact: multiplying by it rounds like the reference's division by the scale
-        // (byte 0 stands for 2^-127, byte 254 needs the denormal 2^-127, byte 255 is NaN)
-        const float rscale = __uint_as_float(byte == 0xFFu ? 0x7F800001u : (byte == 254u ? 0x00400000u : ((254u - byte) << 23)));
-        if(FP4)
+        for(int i = 0; i < 4; ++i)
+            cur[i] = next[i];
+        if(r0 + 4 < 32)
         {
-            // cvt.rn.satfinite.e2m1x2.f32: nearest, ties to even, saturating at 6, sign kept on zero; low nibble = even element
-            uint32_t packed = 0;
 #pragma unroll
             for(int i = 0; i < 4; ++i)
-                packed |= static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(make_float2(v[2 * i] * rscale, v[2 * i + 1] * rscale), __NV_E2M1,
-                                                                         cudaRoundNearest))
-                          << (8 * i);
-            if(ok)
-                *reinterpret_cast<uint32_t*>(prm.out + row * prm.out_ld + static_cast<long long>(tk) * 128 + lane * 4) = packed;
+                next[i] = load_row(r0 + 4 + i);
         }
-        else
-        {
-            uint32_t w[2];
 #pragma unroll
-            for(int h = 0; h < 2; ++h)
-            {
-                const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
-                    make_float2(v[4 * h] * rscale, v[4 * h + 1] * rscale), __NV_SATFINITE, __NV_E4M3);
-                const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(
-                    make_float2(v[4 * h + 2] * rscale, v[4 * h + 3] * rscale), __NV_SATFINITE, __NV_E4M3);
-                w[h] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
-            }
-            if(ok)
-                *reinterpret_cast<uint2*>(prm.out + row * prm.out_ld + static_cast<long long>(tk) * 256 + lane * 8) = make_uint2(w[0], w[1]);
-        }
-        // one lane per block files the scale byte at its place inside the tile's 256-byte chunk
-        if((lane & 3) == 0)
+        for(int u = 0; u < 4; ++u)
         {
-            const int kb = lane >> 2; // block within the tile, 0..7
-            const uint8_t b = ok ? static_cast<uint8_t>(byte) : static_cast<uint8_t>(prm.layout == QSL_M32K4 ? 0x7F : 0);
-            int pos;
-            if(prm.layout == QSL_E8M0_SHUFFLE)
-                pos = (kb & 3) * 64 + (r & 15) * 4 + (kb >> 2) * 2 + (r >> 4);
-            else if(prm.layout == QSL_M32K4)
-                pos = (kb >> 2) * 128 + r * 4 + (kb & 3);
+            const int r     = r0 + u;
+            const uint4 raw = cur[u];
+            const long long row = tm * 32 + r;
+            const bool ok       = blk_ok && row < prm.M;
+            const T* e = reinterpret_cast<const T*>(&raw);
+            float v[8];
+            float amax = 0.f;
+#pragma unroll
+            for(int i = 0; i < 8; ++i)
+            {
+                v[i] = to_f32<T>(e[i]);
+                amax = fmaxf(amax, fabsf(v[i]));
+            }
+            // NaN must survive the maximum (fmaxf drops it): carry it separately
+            bool has_nan = false;
+#pragma unroll
+            for(int i = 0; i < 8; ++i)
+                has_nan |= (v[i] != v[i]);
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            has_nan |= __shfl_xor_sync(0xffffffffu, has_nan ? 1 : 0, 1) != 0;
+            has_nan |= __shfl_xor_sync(0xffffffffu, has_nan ? 1 : 0, 2) != 0;
+            if(has_nan)
+                amax = __uint_as_float(0x7FC00000u);
+            const uint32_t qb = __float_as_uint(__fdiv_rn(amax, max_pos));
+            const uint32_t ex = (qb >> 23) & 0xFFu;
+            const uint32_t byte = ex + (((qb & 0x7FFFFFu) != 0u && ex < 0xFFu) ? 1u : 0u);
+            // 1 / 2^(byte-127), exact: multiplying by it rounds like the reference's division by the scale
+            // (byte 0 stands for 2^-127, byte 254 needs the denormal 2^-127, byte 255 is NaN)
+            const float rscale = __uint_as_float(byte == 0xFFu ? 0x7F800001u : (byte == 254u ? 0x00400000u : ((254u - byte) << 23)));
+            if(FP4)
+            {
+                // cvt.rn.satfinite.e2m1x2.f32: nearest, ties to even, saturating at 6, sign kept on zero; low nibble = even element
+                uint32_t packed = 0;
+#pragma unroll
+                for(int i = 0; i < 4; ++i)
+                    packed |= static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(make_float2(v[2 * i] * rscale, v[2 * i + 1] * rscale), __NV_E2M1,
+                                                                             cudaRoundNearest))
+                              << (8 * i);
+                if(ok)
+                    *reinterpret_cast<uint32_t*>(prm.out + row * prm.out_ld + static_cast<long long>(tk) * 128 + lane * 4) = packed;
+            }
             else
-                pos = r * 8 + kb;
-            sf[pos] = b;
+            {
+                uint32_t w[2];
+#pragma unroll
+                for(int h = 0; h < 2; ++h)
+                {
+                    const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
+                        make_float2(v[4 * h] * rscale, v[4 * h + 1] * rscale), __NV_SATFINITE, __NV_E4M3);
+                    const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(
+                        make_float2(v[4 * h + 2] * rscale, v[4 * h + 3] * rscale), __NV_SATFINITE, __NV_E4M3);
+                    w[h] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+                }
+                if(ok)
+                    *reinterpret_cast<uint2*>(prm.out + row * prm.out_ld + static_cast<long long>(tk) * 256 + lane * 8) = make_uint2(w[0], w[1]);
+            }
+            // one lane per block files the scale byte at its place inside the tile's 256-byte chunk
+            if((lane & 3) == 0)
+            {
+                const int kb = lane >> 2; // block within the tile, 0..7
+                const uint8_t b = ok ? static_cast<uint8_t>(byte) : static_cast<uint8_t>(prm.layout == QSL_M32K4 ? 0x7F : 0);
+                int pos;
+                if(prm.layout == QSL_E8M0_SHUFFLE)
+                    pos = (kb & 3) * 64 + (r & 15) * 4 + (kb >> 2) * 2 + (r >> 4);
+                else if(prm.layout == QSL_M32K4)
+                    pos = (kb >> 2) * 128 + r * 4 + (kb & 3);
+                else
+                    pos = r * 8 + kb;
+                sf[pos] = b;
+            }
         }
     }
     __syncwarp();

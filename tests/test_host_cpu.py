@@ -204,3 +204,26 @@ def test_fused_quantiser_wrappers_validate_arguments_on_cpu():
     assert ab.get_hip_quant(ab.QuantType.per_1x32) is ab.per_1x32_mx_quant_hip
     with pytest.raises(NotImplementedError):
         ab.get_hip_quant(ab.QuantType.per_Tensor)
+
+
+def test_tuner_candidates_use_the_library_name_grammar():
+    """Every candidate the tuner times has a name the library's documented grammar covers and a kernel id that
+    follows `pair*1000 + swap*100 + bn_index*10 + stages` with the library's own tile-width menu."""
+    import re
+
+    import aiter_b200 as ab
+    from aiter_b200 import tune
+
+    menu_text = ab.kernel_list()
+    widths = [int(m.group(2)) for m in re.finditer(r"id (\d+)\.\.: tile 128x(\d+) ", menu_text) if int(m.group(1)) < 100]
+    assert widths == tune.BN_MENU
+    grammar = re.compile(r"^tc5_(128|256)x(\d+)_[nt]_s\d(_k\d)?$")
+    for fam, shapes in tune.BASELINE_SHAPES.items():
+        for (M, N, K) in shapes:
+            cands = tune.candidates(M, N, K, fam)
+            assert cands, (fam, M, N, K)
+            for (pair, swap, bn, st, sk) in cands:
+                assert bn in tune.BN_MENU and pair in (0, 1) and swap in (0, 1) and 0 <= st <= 8 and 0 <= sk <= 5
+                assert not (pair and swap), "CTA-pair tiles are not built for the transposed (decode) orientation"
+                assert grammar.match(tune.kernel_name(pair, swap, bn, st, sk)), tune.kernel_name(pair, swap, bn, st, sk)
+                assert tune.kernel_id(pair, swap, bn, st) == pair * 1000 + swap * 100 + tune.BN_MENU.index(bn) * 10 + st
