@@ -184,6 +184,43 @@ def rotating_sets(make, bytes_per_set, l2_bytes=126e6):
 
 
 # --------------------------------------------------------------------------------------- sweep
+def run_case(torch, ab, device, spec, steps, warmup):
+    """Profiling aid: one sweep case, `kind:M:N:K` with kind in mxfp8 / mxfp4 / a8w4 / bf16 / quant_mxfp4 / quant_mxfp8
+    (N ignored for the quantiser), launched `steps` times on the current stream; prints one JSON line."""
+    kind, M, N, K = spec.split(":")
+    M, N, K = int(M), int(N), int(K)
+
+    def rand_u8(lo, hi, *shape):
+        return torch.randint(lo, hi, shape, dtype=torch.uint8, device=device)
+
+    if kind == "mxfp8":
+        args = (rand_u8(0, 0x78, M, K).view(torch.float8_e4m3fn), rand_u8(0, 0x78, N, K).view(torch.float8_e4m3fn),
+                rand_u8(120, 130, (M + 31) // 32 * 32, K // 32), rand_u8(120, 130, N, K // 32))
+        fn = lambda a, b, sa, sb: ab.gemm_a8w8_mxfp8(a, b, sa, sb, a_preshuffle=False)  # noqa: E731
+    elif kind == "mxfp4":
+        kb = (K // 32 + 7) // 8 * 8
+        args = (rand_u8(0, 256, M, K // 2), rand_u8(0, 256, N, K // 2), rand_u8(120, 130, (M + 255) // 256 * 256, kb),
+                rand_u8(120, 130, (N + 255) // 256 * 256, kb))
+        fn = lambda a, b, sa, sb: ab.gemm_a4w4(a, b, sa, sb)  # noqa: E731
+    elif kind == "a8w4":
+        args = (rand_u8(0, 0x78, M, K).view(torch.float8_e4m3fn), rand_u8(0, 256, N, K // 2),
+                rand_u8(120, 130, (M + 31) // 32 * 32, K // 32), rand_u8(120, 130, N, K // 32))
+        fn = lambda a, b, sa, sb: ab.gemm_a8w4_mxfp8(a, b, sa, sb, a_preshuffle=False)  # noqa: E731
+    elif kind == "bf16":
+        args = (torch.randn(M, K, device=device).to(torch.bfloat16) * 0.1, torch.randn(N, K, device=device).to(torch.bfloat16) * 0.1)
+        fn = lambda a, b: ab.tgemm.mm(a, b)  # noqa: E731
+    elif kind in ("quant_mxfp4", "quant_mxfp8"):
+        args = (torch.randn(M, K, device=device).to(torch.bfloat16),)
+        kw = dict(quant_dtype=ab.dtypes.fp4x2, shuffle=True) if kind == "quant_mxfp4" else dict(
+            quant_dtype=ab.dtypes.fp8, scale_type=ab.dtypes.fp8_e8m0, shuffle=2)
+        fn = lambda x: ab.per_1x32_mx_quant_hip(x, **kw)  # noqa: E731
+    else:
+        raise SystemExit(f"unknown case kind {kind}")
+    us = time_calls(torch, fn, [args], steps, warmup)
+    print(json.dumps({"case": spec, "us_per_call": round(us, 2), "steps": steps, "warmup": warmup,
+                      "kernel": kernel_in_use(ab, kind, M, N, K) if not kind.startswith("quant") else "quant_mx_kernel"}))
+
+
 def run_sweep(torch, ab, device, peaks):
     """Per-M device time of the other benchmark configurations (graph-replayed, rotating buffers)."""
     rows = []
@@ -299,6 +336,9 @@ def run_ours(args, rank, world, local_rank):
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=device)
+    if args.case:
+        run_case(torch, ab, device, args.case, args.steps, args.warmup)
+        return
     peaks = measured_peaks()
     M, N, K = M_DIM, N_DIM, K_DIM
     flops = 2.0 * M * N * K
@@ -415,6 +455,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-M table of the other configurations")
     ap.add_argument("--kernel-only", action="store_true",
                     help="profiling aid: only the device-timed GEMM loop (no end-to-end leg, sweep or CPU baseline)")
+    ap.add_argument("--case", default="", help="profiling aid: run one sweep case only, kind:M:N:K (see run_case)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
