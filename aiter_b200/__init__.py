@@ -27,8 +27,12 @@ from .gemm_op_a4w4 import (  # noqa: E402,F401
 )
 from .gemm_op_a8w4 import gemm_a8w4_mxfp8  # noqa: E402,F401
 from .gemm_op_a8w8 import (  # noqa: E402,F401
+    flatmm_a8w8_blockscale_asm,
     gemm_a8w8_blockscale,
     gemm_a8w8_blockscale_bpreshuffle,
+    gemm_a8w8_blockscale_bpreshuffle_asm,
+    gemm_a8w8_blockscale_bpreshuffle_cktile,
+    gemm_a8w8_blockscale_cktile,
     gemm_a8w8_mxfp8,
     gemm_a8w8_mxfp8_noalloc,
 )

@@ -83,6 +83,12 @@ SIGNATURES = {
     "gemm_a8w8_blockscale_tune": (T, T, T, T, T, I, I),
     "gemm_a8w8_blockscale_bpreshuffle": (T, T, T, T, T, I, S),
     "gemm_a8w8_blockscale_bpreshuffle_tune": (T, T, T, T, T, I, I),
+    "gemm_a8w8_blockscale_cktile": (T, T, T, T, T, I, I, S),
+    "gemm_a8w8_blockscale_cktile_tune": (T, T, T, T, T, I, I, I),
+    "gemm_a8w8_blockscale_bpreshuffle_cktile": (T, T, T, T, T, I, S),
+    "gemm_a8w8_blockscale_bpreshuffle_cktile_tune": (T, T, T, T, T, I, I, I),
+    "flatmm_a8w8_blockscale_asm": (T, T, T, T, T),
+    "gemm_a8w8_blockscale_bpreshuffle_asm": (T, T, T, T, T, T, I, S, I, T),
     "aiter_b200_gemm_a8w8_mxfp8_noalloc": (T, T, T, T, T, I, I),
 }
 EXPORTS = sorted(

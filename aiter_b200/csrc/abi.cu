@@ -318,6 +318,59 @@ extern "C" int gemm_a8w8_blockscale_bpreshuffle_tune(aiter_tensor_t* XQ, aiter_t
     });
 }
 
+// The reference binds the same arithmetic under several back-end names (CK, CK-tile, hand-written assembly); here one
+// kernel family serves them all, with each name's own argument order.
+extern "C" int gemm_a8w8_blockscale_cktile(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale, aiter_tensor_t* w_scale,
+                                           aiter_tensor_t* Out, int preshuffleB, int splitK, const char* kernelName, void* stream)
+{
+    (void)splitK; (void)kernelName;
+    return safe_call([&] { run_blockscale("gemm_a8w8_blockscale_cktile", XQ, WQ, x_scale, w_scale, Out, preshuffleB != 0, stream); });
+}
+extern "C" int gemm_a8w8_blockscale_cktile_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale, aiter_tensor_t* w_scale,
+                                                aiter_tensor_t* Out, int kernelId, int splitK, int preshuffleB, void* stream)
+{
+    (void)splitK;
+    return safe_call([&] {
+        B200_CHECK(kernelId == 0, "gemm_a8w8_blockscale_cktile_tune: Kernel id ", kernelId, " not found");
+        run_blockscale("gemm_a8w8_blockscale_cktile_tune", XQ, WQ, x_scale, w_scale, Out, preshuffleB != 0, stream);
+    });
+}
+extern "C" int gemm_a8w8_blockscale_bpreshuffle_cktile(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
+                                                       aiter_tensor_t* w_scale, aiter_tensor_t* Out, int preshuffleB, const char* kernelName,
+                                                       void* stream)
+{
+    (void)kernelName;
+    return safe_call([&] { run_blockscale("gemm_a8w8_blockscale_bpreshuffle_cktile", XQ, WQ, x_scale, w_scale, Out, preshuffleB != 0, stream); });
+}
+extern "C" int gemm_a8w8_blockscale_bpreshuffle_cktile_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
+                                                            aiter_tensor_t* w_scale, aiter_tensor_t* Out, int kernelId, int splitK,
+                                                            int preshuffleB, void* stream)
+{
+    (void)splitK;
+    return safe_call([&] {
+        B200_CHECK(kernelId == 0, "gemm_a8w8_blockscale_bpreshuffle_cktile_tune: Kernel id ", kernelId, " not found");
+        run_blockscale("gemm_a8w8_blockscale_bpreshuffle_cktile_tune", XQ, WQ, x_scale, w_scale, Out, preshuffleB != 0, stream);
+    });
+}
+// (XQ, WQ, x_scale, w_scale, out): row-major weight, fp32 scales
+extern "C" int flatmm_a8w8_blockscale_asm(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale, aiter_tensor_t* w_scale,
+                                          aiter_tensor_t* out, void* stream)
+{
+    return safe_call([&] { run_blockscale("flatmm_a8w8_blockscale_asm", XQ, WQ, x_scale, w_scale, out, 0, stream); });
+}
+// (A, B, out, A_scale, B_scale, bias?, splitK, kernelName?, bpreshuffle, zero_bias_buf?): the assembly back-end's order;
+// N and K must be multiples of 128 there, and a bias is not part of this library's kernel.
+extern "C" int gemm_a8w8_blockscale_bpreshuffle_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* out, aiter_tensor_t* A_scale,
+                                                    aiter_tensor_t* B_scale, aiter_tensor_t* bias, int splitK, const char* kernelName,
+                                                    int bpreshuffle, aiter_tensor_t* zero_bias_buf, void* stream)
+{
+    (void)splitK; (void)kernelName; (void)zero_bias_buf;
+    return safe_call([&] {
+        B200_CHECK(bias == nullptr, "gemm_a8w8_blockscale_bpreshuffle_asm: a bias is not supported by this kernel");
+        run_blockscale("gemm_a8w8_blockscale_bpreshuffle_asm", A, B, A_scale, B_scale, out, bpreshuffle != 0, stream);
+    });
+}
+
 // ------------------------------------------------------------------------------------------- bf16
 static void run_bf16(const char* fn, const aiter_tensor_t* A, const aiter_tensor_t* B, const aiter_tensor_t* out,
                      const aiter_tensor_t* bias, int bpreshuffle, const KernelConfig& cfg, int batch_index, void* stream)

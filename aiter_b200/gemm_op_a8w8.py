@@ -90,3 +90,34 @@ def gemm_a8w8_mxfp8_noalloc(A: Tensor, B: Tensor, ScaleA: Tensor, ScaleB: Tensor
     _ffi.call("aiter_b200_gemm_a8w8_mxfp8_noalloc", A, B, ScaleA, ScaleB, out, int(bool(a_preshuffle)),
               -1 if log2_k_split is None else int(log2_k_split))
     return out
+
+
+def gemm_a8w8_blockscale_cktile(XQ: Tensor, WQ: Tensor, x_scale: Tensor, w_scale: Tensor, Out: Tensor, preshuffleB: bool = False,
+                                splitK: int = 0, kernelName: str = "") -> Tensor:
+    """The CK-tile back-end's name and argument order (csrc/include/rocm_ops.hpp:749-759); same kernels as gemm_a8w8_blockscale."""
+    xs, ws = _blockscale_scales(x_scale, w_scale)
+    _ffi.call("gemm_a8w8_blockscale_cktile", XQ, WQ, xs, ws, Out, int(bool(preshuffleB)), splitK, kernelName or None)
+    return Out
+
+
+def gemm_a8w8_blockscale_bpreshuffle_cktile(XQ: Tensor, WQ: Tensor, x_scale: Tensor, w_scale: Tensor, Out: Tensor,
+                                            preshuffleB: bool = True, kernelName: str = "") -> Tensor:
+    xs, ws = _blockscale_scales(x_scale, w_scale)
+    _ffi.call("gemm_a8w8_blockscale_bpreshuffle_cktile", XQ, WQ, xs, ws, Out, int(bool(preshuffleB)), kernelName or None)
+    return Out
+
+
+def flatmm_a8w8_blockscale_asm(XQ: Tensor, WQ: Tensor, x_scale: Tensor, w_scale: Tensor, out: Tensor) -> Tensor:
+    """aiter/ops/gemm_op_a8w8.py:342-362: row-major weight, fp32 scales, caller-provided output."""
+    _ffi.call("flatmm_a8w8_blockscale_asm", XQ, WQ, x_scale, w_scale, out)
+    return out
+
+
+def gemm_a8w8_blockscale_bpreshuffle_asm(A: Tensor, B: Tensor, out: Tensor, A_scale: Tensor, B_scale: Tensor, bias: Tensor | None = None,
+                                         splitK: int | None = None, kernelName: str | None = None, bpreshuffle: bool | None = True,
+                                         zero_bias_buf: Tensor | None = None) -> Tensor:
+    """aiter/ops/gemm_op_a8w8.py:397-423 (the assembly back-end's argument order; A_scale K-block-major as in
+    gemm_a8w8_blockscale_bpreshuffle)."""
+    _ffi.call("gemm_a8w8_blockscale_bpreshuffle_asm", A, B, out, A_scale, B_scale, bias, splitK if splitK is not None else -1, kernelName,
+              int(bpreshuffle) if bpreshuffle is not None else 1, zero_bias_buf)
+    return out

@@ -108,6 +108,27 @@ AITER_B200_API int gemm_a8w8_blockscale_bpreshuffle(aiter_tensor_t* XQ, aiter_te
 AITER_B200_API int gemm_a8w8_blockscale_bpreshuffle_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ,
                                                          aiter_tensor_t* x_scale, aiter_tensor_t* w_scale,
                                                          aiter_tensor_t* Out, int kernelId, int splitK, void* stream);
+/* The same arithmetic under the reference's other back-end names, each with its own argument order
+ * (csrc/include/rocm_ops.hpp:749-821 for the CK-tile forms; aiter/ops/gemm_op_a8w8.py:342-381 for the assembly forms:
+ * flatmm_a8w8_blockscale_asm takes a row-major weight, gemm_a8w8_blockscale_bpreshuffle_asm the (16,16)-shuffled one and
+ * accepts no bias here). */
+AITER_B200_API int gemm_a8w8_blockscale_cktile(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale, aiter_tensor_t* w_scale,
+                                               aiter_tensor_t* Out, int preshuffleB, int splitK, const char* kernelName, void* stream);
+AITER_B200_API int gemm_a8w8_blockscale_cktile_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
+                                                    aiter_tensor_t* w_scale, aiter_tensor_t* Out, int kernelId, int splitK,
+                                                    int preshuffleB, void* stream);
+AITER_B200_API int gemm_a8w8_blockscale_bpreshuffle_cktile(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
+                                                           aiter_tensor_t* w_scale, aiter_tensor_t* Out, int preshuffleB,
+                                                           const char* kernelName, void* stream);
+AITER_B200_API int gemm_a8w8_blockscale_bpreshuffle_cktile_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
+                                                                aiter_tensor_t* w_scale, aiter_tensor_t* Out, int kernelId, int splitK,
+                                                                int preshuffleB, void* stream);
+AITER_B200_API int flatmm_a8w8_blockscale_asm(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale, aiter_tensor_t* w_scale,
+                                              aiter_tensor_t* out, void* stream);
+AITER_B200_API int gemm_a8w8_blockscale_bpreshuffle_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* out, aiter_tensor_t* A_scale,
+                                                        aiter_tensor_t* B_scale, aiter_tensor_t* bias, int splitK, const char* kernelName,
+                                                        int bpreshuffle, aiter_tensor_t* zero_bias_buf, void* stream);
+
 
 /* ---- MXFP4 x MXFP4 with the (m/32,k/4,32,4) scale layout.  csrc/py_itfs_cu/asm_f4gemm.cu:396-412
  * (bf16 output only: out_scale must be NULL). */

@@ -314,6 +314,30 @@ def test_a8w8_blockscale_fp32_scales(ab, M, N, K, bpre):
     assert_healthy(ab)
 
 
+def test_a8w8_blockscale_other_backend_names(ab):
+    # the CK-tile and assembly names of the reference reach the same kernels, each in its own argument order
+    M, N, K = 200, 512, 1024
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn)
+    w = torch.randn(N, K, generator=g).to(torch.float8_e4m3fn)
+    xs = torch.rand(M, K // 128, generator=g) + 0.25
+    ws = torch.rand(N // 128, K // 128, generator=g) + 0.25
+    ref = ox.gemm_a8w8_blockscale_ref(x.view(torch.uint8).numpy(), w.view(torch.uint8).numpy(), xs.numpy(), ws.numpy())
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    wq = ab.shuffle_weight(w.cuda(), layout=(16, 16))
+    xs_t = xs.T.contiguous().cuda()
+    check(ref, ab.flatmm_a8w8_blockscale_asm(x.cuda(), w.cuda(), xs.cuda(), ws.cuda(), out), what="flatmm_a8w8_blockscale_asm")
+    out.zero_()
+    check(ref, ab.gemm_a8w8_blockscale_cktile(x.cuda(), w.cuda(), xs.cuda(), ws.cuda(), out), what="gemm_a8w8_blockscale_cktile")
+    out.zero_()
+    check(ref, ab.gemm_a8w8_blockscale_bpreshuffle_cktile(x.cuda(), wq, xs_t.T, ws.cuda(), out), what="..._bpreshuffle_cktile")
+    out.zero_()
+    check(ref, ab.gemm_a8w8_blockscale_bpreshuffle_asm(x.cuda(), wq, out, xs_t.T, ws.cuda()), what="..._bpreshuffle_asm")
+    with pytest.raises(RuntimeError, match="bias"):
+        ab.gemm_a8w8_blockscale_bpreshuffle_asm(x.cuda(), wq, out, xs_t.T, ws.cuda(), bias=torch.zeros(N, device="cuda"))
+    assert_healthy(ab)
+
+
 @pytest.mark.parametrize("M,N,K,bpre", [(64, 256, 512, False), (300, 1024, 2048, True), (1, 128, 128, False)])
 def test_a8w8_blockscale_e8m0_scales_run_as_mxfp8(ab, M, N, K, bpre):
     # power-of-two scales ride the block-scaled MMA: two small expansion launches + the MXFP8 kernel
