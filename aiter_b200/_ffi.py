@@ -115,6 +115,10 @@ def _convert(kind, value, keep):
     raise TypeError(kind)
 
 
+_FUNCS = {}
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def call(name: str, *args):
     """Call an entry point on the current CUDA stream of the first tensor's device."""
     kinds = SIGNATURES[name]
@@ -122,8 +126,16 @@ def call(name: str, *args):
     keep = []
     cargs = [_convert(k, a, keep) for k, a in zip(kinds, args)]
     dev = next((a.device for a in args if isinstance(a, torch.Tensor) and a.is_cuda), None)
-    stream = torch.cuda.current_stream(dev).cuda_stream if dev is not None else 0
-    rc = getattr(_lib, name)(*cargs, ctypes.c_void_p(stream))
+    if dev is None:
+        stream = 0
+    elif _raw_stream is not None:
+        stream = _raw_stream(dev.index if dev.index is not None else torch.cuda.current_device())
+    else:
+        stream = torch.cuda.current_stream(dev).cuda_stream
+    fn = _FUNCS.get(name)
+    if fn is None:
+        fn = _FUNCS[name] = getattr(_lib, name)
+    rc = fn(*cargs, ctypes.c_void_p(stream))
     if rc != 0:
         msg = _lib.aiter_get_last_error()
         raise RuntimeError(f"{name} failed: {msg.decode() if msg else 'unknown error'}")
