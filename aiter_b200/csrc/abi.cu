@@ -238,7 +238,8 @@ extern "C" int mxfp8_mxfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_
 
 // ------------------------------------------------------------------------------------------- fp8, fp32 128-block scales
 static void run_blockscale(const char* fn, aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
-                           aiter_tensor_t* w_scale, aiter_tensor_t* Out, int bpreshuffle, void* stream)
+                           aiter_tensor_t* w_scale, aiter_tensor_t* Out, int bpreshuffle, void* stream,
+                           const char* kernelName = nullptr)
 {
     require_tensor(XQ, fn, "XQ", 2);
     require_tensor(WQ, fn, "WQ", 2);
@@ -279,6 +280,9 @@ static void run_blockscale(const char* fn, aiter_tensor_t* XQ, aiter_tensor_t* W
     }
     p.w_scale = static_cast<const float*>(w_scale->ptr);
     p.scales_are_e8m0 = sx8 && sw8;
+    // with e8m0 scales the problem runs on the MXFP8 kernel family, whose configuration names apply
+    if(p.scales_are_e8m0 && kernelName != nullptr && kernelName[0] != 0)
+        B200_CHECK(parse_config_name(kernelName, p.cfg), fn, ": not find kernel ", kernelName);
     p.out     = Out->ptr;
     p.ldo     = Out->strides[0];
     p.device  = XQ->device_id;
@@ -289,8 +293,8 @@ static void run_blockscale(const char* fn, aiter_tensor_t* XQ, aiter_tensor_t* W
 extern "C" int gemm_a8w8_blockscale(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale, aiter_tensor_t* w_scale,
                                     aiter_tensor_t* Out, int splitK, const char* kernelName, void* stream)
 {
-    (void)splitK; (void)kernelName; // one kernel instance serves this path
-    return safe_call([&] { run_blockscale("gemm_a8w8_blockscale", XQ, WQ, x_scale, w_scale, Out, 0, stream); });
+    (void)splitK; // the fp32-scale kernels have one configuration; kernelName selects among the MXFP8 ones for e8m0 scales
+    return safe_call([&] { run_blockscale("gemm_a8w8_blockscale", XQ, WQ, x_scale, w_scale, Out, 0, stream, kernelName); });
 }
 extern "C" int gemm_a8w8_blockscale_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale, aiter_tensor_t* w_scale,
                                          aiter_tensor_t* Out, int kernelId, int splitK, void* stream)
@@ -305,8 +309,8 @@ extern "C" int gemm_a8w8_blockscale_bpreshuffle(aiter_tensor_t* XQ, aiter_tensor
                                                 aiter_tensor_t* w_scale, aiter_tensor_t* Out, int splitK, const char* kernelName,
                                                 void* stream)
 {
-    (void)splitK; (void)kernelName;
-    return safe_call([&] { run_blockscale("gemm_a8w8_blockscale_bpreshuffle", XQ, WQ, x_scale, w_scale, Out, 1, stream); });
+    (void)splitK;
+    return safe_call([&] { run_blockscale("gemm_a8w8_blockscale_bpreshuffle", XQ, WQ, x_scale, w_scale, Out, 1, stream, kernelName); });
 }
 extern "C" int gemm_a8w8_blockscale_bpreshuffle_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
                                                      aiter_tensor_t* w_scale, aiter_tensor_t* Out, int kernelId, int splitK, void* stream)

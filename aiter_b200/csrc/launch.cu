@@ -254,10 +254,11 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
             cfg.bn = rows_q <= 16 ? 16 : rows_q <= 32 ? 32 : rows_q <= 64 ? 64 : rows_q <= 128 ? 128 : 256;
         else
         {
-            // largest tile whose grid still covers the machine, else the largest that divides N well
+            // largest tile whose grid still covers half the machine
+            // (the tuner's tables agree: a 256-wide tile on half the SMs beats a 128-wide one on all of them)
             cfg.bn = 256;
             const long long tiles_p = (rows_p + kTileP - 1) / kTileP;
-            while(cfg.bn > 64 && tiles_p * ((rows_q + cfg.bn - 1) / cfg.bn) < num_sms)
+            while(cfg.bn > 64 && tiles_p * ((rows_q + cfg.bn - 1) / cfg.bn) < num_sms / 2)
                 cfg.bn >>= 1;
             if(rows_q < cfg.bn)
                 cfg.bn = rows_q <= 16 ? 16 : rows_q <= 32 ? 32 : rows_q <= 64 ? 64 : rows_q <= 128 ? 128 : 256;
@@ -969,6 +970,7 @@ static void launch_blockscale_e8m0(const BlockScaleProblem& prob)
     p.ldo    = prob.ldo;
     p.device = prob.device;
     p.stream = prob.stream;
+    p.cfg    = prob.cfg;
     launch_gemm(p);
 }
 

@@ -116,6 +116,7 @@ struct BlockScaleProblem
     // both scale tensors hold UE8M0 bytes instead of floats (same shapes and strides, in bytes): powers of two ride
     // the block-scaled MMA, so the problem runs on the MXFP8 kernel after a small expansion of the scales
     bool scales_are_e8m0 = false;
+    KernelConfig cfg;             // e8m0 path only: a caller-chosen MXFP8 kernel configuration (unset fields: heuristic)
     void* out = nullptr;
     long long ldo = 0;
     int device = 0;

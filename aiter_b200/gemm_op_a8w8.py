@@ -17,6 +17,12 @@ def get_CKGEMM_config(M: int, N: int, K: int, bpreshuffle: bool = False):
     return (_blockscale_bpreshuffle_table if bpreshuffle else _blockscale_table).lookup(M, N, K)
 
 
+def _mxfp8_kernel_for(m: int, n: int, k: int) -> str:
+    """e8m0-scaled blockscale problems run on the MXFP8 kernels: their tuned table names the configuration."""
+    row = _mxfp8_table.lookup(m, n, k)
+    return str(row.get("kernelName") or "") if row is not None else ""
+
+
 def _is_e8m0(s: Tensor) -> bool:
     return s.dtype in (dtypes.fp8_e8m0, torch.uint8)
 
@@ -42,6 +48,8 @@ def gemm_a8w8_blockscale(XQ: Tensor, WQ: Tensor, x_scale: Tensor, w_scale: Tenso
     cfg = get_CKGEMM_config(m, n, k)
     splitK, kernelName = (int(cfg.get("splitK") or 0), str(cfg.get("kernelName") or "")) if cfg is not None else (0, "")
     xs, ws = _blockscale_scales(x_scale, w_scale)
+    if _is_e8m0(xs) and not kernelName:
+        kernelName = _mxfp8_kernel_for(m, n, k)
     _ffi.call("gemm_a8w8_blockscale", XQ, WQ, xs, ws, Y, splitK, kernelName or None)
     return Y
 
@@ -57,6 +65,8 @@ def gemm_a8w8_blockscale_bpreshuffle(XQ: Tensor, WQ: Tensor, x_scale: Tensor, w_
     cfg = get_CKGEMM_config(m, n, k, bpreshuffle=True)
     splitK, kernelName = (int(cfg.get("splitK") or 0), str(cfg.get("kernelName") or "")) if cfg is not None else (0, "")
     xs, ws = _blockscale_scales(x_scale, w_scale)
+    if _is_e8m0(xs) and not kernelName:
+        kernelName = _mxfp8_kernel_for(m, n, k)
     _ffi.call("gemm_a8w8_blockscale_bpreshuffle", XQ, WQ, xs, ws, Y, splitK, kernelName or None)
     return Y
 

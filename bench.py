@@ -259,6 +259,19 @@ def run_sweep(torch, ab, device, peaks):
         add("a8w4", M, 8192, 8192, lambda a, b, sa, sb: ab.gemm_a8w4_mxfp8(a, b, sa, sb, a_preshuffle=False),
             lambda i, M=M: (rand_u8(0, 0x78, M, 8192).view(torch.float8_e4m3fn), rand_u8(0, 256, 8192, 4096),
                             rand_u8(120, 130, (M + 31) // 32 * 32, 256), rand_u8(120, 130, 8192, 256)))
+    # FP8 with 128-block scales, N = K = 4096: fp32 scales (promotion kernel) and e8m0 scales (MXFP8 kernel)
+    for M in (16, 1024, 8192):
+        for tag, mk in (("blockscale_fp32", lambda M: (torch.rand(M, 32, device=device) + 0.5, torch.rand(32, 32, device=device) + 0.5)),
+                        ("blockscale_e8m0", lambda M: (rand_u8(124, 130, M, 32).view(ab.dtypes.fp8_e8m0), rand_u8(124, 130, 32, 32).view(ab.dtypes.fp8_e8m0)))):
+            sets = rotating_sets(lambda i, M=M, mk=mk: (rand_u8(0, 0x78, M, 4096).view(torch.float8_e4m3fn),
+                                                        rand_u8(0, 0x78, 4096, 4096).view(torch.float8_e4m3fn), *mk(M)),
+                                 algorithmic_bytes("mxfp8", M, 4096, 4096))
+            us = graph_time_calls(torch, lambda a, b, xs, ws: ab.gemm_a8w8_blockscale(a, b, xs, ws), sets, 20, 3)
+            tf = 2.0 * M * 4096 * 4096 / us / 1e6
+            rows.append({"kind": tag, "M": M, "N": 4096, "K": 4096, "us": round(us, 2), "tflops": round(tf, 1),
+                         "gbs": round(algorithmic_bytes("mxfp8", M, 4096, 4096) / us / 1e3, 1), "frac_tensor": round(tf / (2 * peaks["bf16"]), 4),
+                         "frac_hbm": round(algorithmic_bytes("mxfp8", M, 4096, 4096) / us / 1e3 / peaks["hbm_gbs"], 4),
+                         "kernel": "gemm_a8w8_blockscale" + ("_pair_kernel" if tag.endswith("fp32") and M > 128 else "_kernel" if tag.endswith("fp32") else " -> mxfp8")})
     # fused activation quantiser (bf16 -> MX data + scales in the GEMM's layout): HBM-bound
     for (kind, M, K, kw) in (("quant_mxfp4", 16384, 16384, dict(quant_dtype=ab.dtypes.fp4x2, shuffle=True)),
                              ("quant_mxfp8", 8192, 4096, dict(quant_dtype=ab.dtypes.fp8, scale_type=ab.dtypes.fp8_e8m0, shuffle=2)),
