@@ -30,6 +30,11 @@ struct BlockScaleParams
     __nv_bfloat16* out;
     long long ldo;
     unsigned int* status;
+    // K split of the single-CTA kernel (gridDim.z slices): fp32 partial tiles + one ticket per output tile
+    int splits;
+    float* ws_partial;
+    unsigned int* ws_counter;
+    int cluster;             // few-rows kernel: the slices are the CTAs of one cluster and meet in shared memory
 };
 
 __host__ __device__ constexpr uint32_t idesc_f8f6f4_e4m3(uint32_t m, uint32_t n)
@@ -67,7 +72,9 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = blockIdx.x * kTileP;
     const int col0 = blockIdx.y * kBsTileN;
-    const int KB   = prm.k_blocks;
+    // this CTA's K blocks: slice blockIdx.z of prm.splits (all of them without a split)
+    const int kb0  = static_cast<int>(static_cast<long long>(prm.k_blocks) * blockIdx.z / prm.splits);
+    const int KB   = static_cast<int>(static_cast<long long>(prm.k_blocks) * (blockIdx.z + 1) / prm.splits) - kb0;
 
     if(threadIdx.x == 0)
     {
@@ -81,6 +88,7 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             mbar_init(part_full_bar(b), 1);
             mbar_init(part_empty_bar(b), 4);
         }
+        mbar_init(bar_base + 176u, 4);
         *abort_f = 0;
         mbar_fence_init();
         fence_proxy_async_smem();
@@ -109,8 +117,8 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                     break;
                 const uint32_t stage = smem_base + s * kStageBytes;
                 mbar_arrive_expect_tx(full_bar(s), kStageBytes);
-                issue_operand_load(prm.a_mode, stage, &map_a, full_bar(s), row0, j);
-                issue_operand_load(prm.b_mode, stage + kTileP * kTileKBytes, &map_b, full_bar(s), col0, j);
+                issue_operand_load(prm.a_mode, stage, &map_a, full_bar(s), row0, kb0 + j);
+                issue_operand_load(prm.b_mode, stage + kTileP * kTileKBytes, &map_b, full_bar(s), col0, kb0 + j);
                 issued = j + 1;
             }
             if(*abort_f)
@@ -159,8 +167,8 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         const int row        = row0 + r_local;
         const uint32_t tlane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
         const bool row_ok    = row < prm.M;
-        const float* xs      = prm.x_scale + static_cast<long long>(row_ok ? row : 0) * prm.xs_stride_m;
-        const float* ws      = prm.w_scale + static_cast<long long>(blockIdx.y) * KB;
+        const float* xs      = prm.x_scale + static_cast<long long>(row_ok ? row : 0) * prm.xs_stride_m + static_cast<long long>(kb0) * prm.xs_stride_k;
+        const float* ws      = prm.w_scale + static_cast<long long>(blockIdx.y) * prm.k_blocks + kb0;
         float acc[kBsTileN];
 #pragma unroll
         for(int i = 0; i < kBsTileN; ++i)
@@ -193,6 +201,56 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             if(lane == 0)
                 mbar_arrive(part_empty_bar(b));
         }
+        if(ok && prm.splits > 1)
+        {
+            // K split: park this slice's tile ([column][row] floats, coalesced), take a ticket; the last slice to arrive
+            // adds the slices up in a fixed order (deterministic) and stores the tile
+            const unsigned int tile = blockIdx.x * gridDim.y + blockIdx.y;
+            float* mine = prm.ws_partial + (static_cast<size_t>(tile) * prm.splits + blockIdx.z) * (kBsTileN * kTileP);
+#pragma unroll
+            for(int i = 0; i < kBsTileN; ++i)
+                mine[i * kTileP + r_local] = acc[i];
+            __threadfence();
+            // rendezvous of the four promotion warps on an mbarrier (bounded like every other wait here)
+            const uint32_t epi_bar = bar_base + 176u;
+            unsigned int* ticket   = reinterpret_cast<unsigned int*>(smem_gen + kStageBytes * S + 168);
+            __syncwarp();
+            if(lane == 0)
+                mbar_arrive(epi_bar);
+            bool all = bounded_wait(epi_bar, 0, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, 0x1000);
+            all      = __all_sync(0xffffffffu, all);
+            if(all)
+            {
+                if(threadIdx.x == 64)
+                {
+                    *reinterpret_cast<volatile unsigned int*>(ticket) = atomicAdd(prm.ws_counter + tile, 1u);
+                    __threadfence_block();
+                }
+                __syncwarp();
+                if(lane == 0)
+                    mbar_arrive(epi_bar);
+                all = bounded_wait(epi_bar, 1, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, 0x2000);
+                all = __all_sync(0xffffffffu, all);
+            }
+            ok = all && (*reinterpret_cast<volatile unsigned int*>(ticket) == static_cast<unsigned int>(prm.splits - 1));
+            if(ok)
+            {
+                __threadfence();
+                const float* part = prm.ws_partial + static_cast<size_t>(tile) * prm.splits * (kBsTileN * kTileP);
+#pragma unroll
+                for(int i = 0; i < kBsTileN; ++i)
+                    acc[i] = 0.f;
+                for(int z = 0; z < prm.splits; ++z)
+                {
+                    const float* src = part + static_cast<size_t>(z) * (kBsTileN * kTileP);
+#pragma unroll
+                    for(int i = 0; i < kBsTileN; ++i)
+                        acc[i] += __ldcg(src + i * kTileP + r_local);
+                }
+                if(threadIdx.x == 64)
+                    prm.ws_counter[tile] = 0; // ready for the next launch
+            }
+        }
         if(ok && row_ok)
         {
             __nv_bfloat16* dst = prm.out + static_cast<size_t>(row) * prm.ldo + col0;
@@ -219,6 +277,284 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, 256);
+    }
+}
+
+
+// ---------------------------------------------------------------------------------------------------------
+// Few activation rows (M <= 32): the operands trade places.  128 weight rows are the M side of the MMA and the
+// XR (16/32) activation rows its N side, so a K block costs 16 KB + XR * 128 B of staging instead of 32 KB,
+// the TMEM partial is XR columns wide and a promotion thread (= one output COLUMN n) folds XR values per K block
+// with x_scale[m][kb] * w_scale[n/128][kb]; 8 TMEM partials are in flight, so the round trip
+// MMA -> commit -> promotion -> release is paid once per 8 K blocks, not per 2.  gridDim.z slices of K meet either
+// in the reducing CTA's shared memory (the slices form one thread-block cluster and send their fp32 tiles with
+// st.async) or in the fp32 workspace like in the kernel above.  Warps (192 threads): 0 TMA producer, 1 MMA issuer + TMEM owner, 2..5 promotion + store.
+template <int XR>
+__global__ void __launch_bounds__(kBlockScaleThreads, 1)
+gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                    const BlockScaleParams prm)
+{
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen        = smem_raw + (smem_base - smem_u32(smem_raw));
+    const int S              = prm.stages;
+    constexpr uint32_t kWBytes     = kBsTileN * kTileKBytes;         // 16 KB of weights
+    constexpr uint32_t kStageBytes = kWBytes + XR * kTileKBytes;     // + the activation rows
+    constexpr int NP               = 8;                              // TMEM partials in flight
+    static_assert(XR == 16 || XR == 32, "activation rows per tile");
+    constexpr uint32_t kTmemCols   = NP * XR;
+    constexpr uint32_t kSliceBytes = kBsTileN * XR * 4u;             // one CTA's fp32 tile
+    // stages | the other slices' tiles (cluster split: written by those CTAs) | barriers and flags
+    const uint32_t red_off   = kStageBytes * S;
+    const uint32_t bar_off   = red_off + (prm.cluster ? static_cast<uint32_t>(prm.splits - 1) * kSliceBytes : 0u);
+    const uint32_t bar_base  = smem_base + bar_off;
+    auto full_bar       = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar      = [&](int s) { return bar_base + 64u + 8u * s; };
+    auto part_full_bar  = [&](int b) { return bar_base + 128u + 8u * b; };
+    auto part_empty_bar = [&](int b) { return bar_base + 192u + 8u * b; };
+    const uint32_t epi_bar     = bar_base + 256u;
+    const uint32_t red_bar     = bar_base + 264u;
+    uint32_t* tmem_ptr_smem    = reinterpret_cast<uint32_t*>(smem_gen + bar_off + 272);
+    volatile uint32_t* abort_f = reinterpret_cast<volatile uint32_t*>(smem_gen + bar_off + 276);
+    unsigned int* ticket       = reinterpret_cast<unsigned int*>(smem_gen + bar_off + 280);
+    const uint32_t zrank       = prm.cluster ? cluster_ctarank() : blockIdx.z; // K slice; 0 reduces a cluster-split tile
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int col0 = blockIdx.x * kBsTileN;
+    const int kb0  = static_cast<int>(static_cast<long long>(prm.k_blocks) * zrank / prm.splits);
+    const int KB   = static_cast<int>(static_cast<long long>(prm.k_blocks) * (zrank + 1) / prm.splits) - kb0;
+
+    if(threadIdx.x == 0)
+    {
+        for(int s = 0; s < S; ++s)
+        {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for(int b = 0; b < NP; ++b)
+        {
+            mbar_init(part_full_bar(b), 1);
+            mbar_init(part_empty_bar(b), 4);
+        }
+        mbar_init(epi_bar, 4);
+        mbar_init(red_bar, 1);
+        *abort_f = 0;
+        mbar_fence_init();
+        fence_proxy_async_smem();
+    }
+    if(warp == 1)
+    {
+        tmem_alloc(smem_u32(tmem_ptr_smem), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if(prm.cluster)
+        cluster_sync_all(); // the reducing CTA's barrier exists before any slice is sent to it
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_ptr_smem;
+    // programmatic dependent launch: the set-up above may overlap the previous kernel's tail; nothing below touches
+    // global memory before that kernel has completed, and the next kernel's set-up may start from here on
+    grid_dependency_wait();
+    grid_launch_dependents();
+
+    if(warp == 0)
+    {
+        if(lane == 0)
+        {
+            int issued = 0;
+            for(int j = 0; j < KB; ++j)
+            {
+                const int s = j % S;
+                if(!bounded_wait(empty_bar(s), ((j / S) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_PRODUCER, j))
+                    break;
+                const uint32_t stage = smem_base + s * kStageBytes;
+                mbar_arrive_expect_tx(full_bar(s), kStageBytes);
+                issue_operand_load(prm.b_mode, stage, &map_b, full_bar(s), col0, kb0 + j);
+                issue_operand_load(prm.a_mode, stage + kWBytes, &map_a, full_bar(s), 0, kb0 + j);
+                issued = j + 1;
+            }
+            if(*abort_f)
+                for(int j = issued - 1; j >= 0 && j >= issued - S; --j)
+                {
+                    const uint64_t t0 = global_timer_ns();
+                    while(!mbar_try_wait(full_bar(j % S), (j / S) & 1) && global_timer_ns() - t0 < kWaitLimitNs) {}
+                }
+        }
+    }
+    else if(warp == 1)
+    {
+        if(lane == 0)
+        {
+            const uint32_t idesc = idesc_f8f6f4_e4m3(kBsTileN, XR);
+            const bool w_tiled = (prm.b_mode == OPM_TILE16), x_tiled = (prm.a_mode == OPM_TILE16);
+            const uint32_t w_lbo = w_tiled ? kBsTileN * 16u : 16u, w_sbo = w_tiled ? 128u : 1024u, w_lay = w_tiled ? 0u : 2u;
+            const uint32_t w_adv = w_tiled ? 2u * kBsTileN * 16u : 32u;
+            const uint32_t x_lbo = x_tiled ? XR * 16u : 16u, x_sbo = x_tiled ? 128u : 1024u, x_lay = x_tiled ? 0u : 2u;
+            const uint32_t x_adv = x_tiled ? 2u * XR * 16u : 32u;
+            bool ok = true;
+            for(int j = 0; j < KB && ok; ++j)
+            {
+                const int s = j % S, b = j % NP;
+                ok = bounded_wait(part_empty_bar(b), ((j / NP) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_MMA_SF, j);
+                if(ok)
+                    ok = bounded_wait(full_bar(s), (j / S) & 1, abort_f, prm.status, ST_TIMEOUT_MMA_FULL, j);
+                if(!ok)
+                    break;
+                tc_fence_after_sync();
+                const uint32_t stage = smem_base + s * kStageBytes;
+#pragma unroll
+                for(int k = 0; k < 4; ++k)
+                    mma_f8f6f4(tmem_base + b * XR, make_smem_desc(stage + k * w_adv, w_lbo, w_sbo, w_lay),
+                               make_smem_desc(stage + kWBytes + k * x_adv, x_lbo, x_sbo, x_lay), idesc, k > 0 ? 1u : 0u);
+                tc_commit(empty_bar(s));
+                tc_commit(part_full_bar(b));
+            }
+        }
+    }
+    else
+    {
+        // promotion + store: thread = output column n, TMEM columns = output rows m
+        const int quarter    = warp & 3;
+        const int r_local    = quarter * 32 + lane;
+        const int n          = col0 + r_local;
+        const uint32_t tlane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        const float* ws      = prm.w_scale + static_cast<long long>(blockIdx.x) * prm.k_blocks + kb0;
+        const float* xs      = prm.x_scale + static_cast<long long>(kb0) * prm.xs_stride_k;
+        float acc[XR];
+#pragma unroll
+        for(int i = 0; i < XR; ++i)
+            acc[i] = 0.f;
+        bool ok = true;
+        if(prm.cluster && zrank == 0 && threadIdx.x == 64)
+            mbar_arrive_expect_tx(red_bar, static_cast<uint32_t>(prm.splits - 1) * kSliceBytes);
+        for(int j = 0; j < KB && ok; ++j)
+        {
+            const int b = j % NP;
+            // this K block's scales (the same addresses in every thread: broadcast), fetched ahead of the wait
+            float sc[XR];
+            const float wsj = __ldg(ws + j);
+#pragma unroll
+            for(int i = 0; i < XR; ++i)
+                sc[i] = __ldg(xs + static_cast<long long>(i < prm.M ? i : 0) * prm.xs_stride_m + static_cast<long long>(j) * prm.xs_stride_k) * wsj;
+            ok = bounded_wait(part_full_bar(b), (j / NP) & 1, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, j);
+            ok = __all_sync(0xffffffffu, ok);
+            if(!ok)
+                break;
+            tc_fence_after_sync();
+            uint32_t r[XR];
+#pragma unroll
+            for(int c = 0; c < XR / 16; ++c)
+                tmem_ld_x16_at(tlane + b * XR + c * 16, r + c * 16);
+            tmem_ld_wait();
+#pragma unroll
+            for(int i = 0; i < XR; ++i)
+                acc[i] = fmaf(__uint_as_float(r[i]), sc[i], acc[i]);
+            tc_fence_before_sync();
+            __syncwarp();
+            if(lane == 0)
+                mbar_arrive(part_empty_bar(b));
+        }
+        if(ok && prm.cluster)
+        {
+            if(zrank != 0)
+            {
+                // cluster split: this slice goes to the reducing CTA's shared memory ([slice][n][m] floats); the bytes
+                // are counted on its barrier and nothing is waited for here
+                const uint32_t dst = map_to_cta(smem_base + red_off, 0) + ((zrank - 1u) * kBsTileN + static_cast<uint32_t>(r_local)) * (XR * 4u);
+                const uint32_t dst_bar = map_to_cta(red_bar, 0);
+#pragma unroll
+                for(int i = 0; i < XR; i += 4)
+                    st_async_v4(dst + i * 4u, __float_as_uint(acc[i]), __float_as_uint(acc[i + 1]), __float_as_uint(acc[i + 2]),
+                                __float_as_uint(acc[i + 3]), dst_bar);
+                ok = false; // nothing to store from here
+            }
+            else
+            {
+                ok = bounded_wait(red_bar, 0, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, 0x3000);
+                ok = __all_sync(0xffffffffu, ok);
+                if(ok)
+                {
+                    const float4* red = reinterpret_cast<const float4*>(smem_gen + red_off);
+                    for(int z = 0; z < prm.splits - 1; ++z)
+                    {
+                        const float4* mine = red + static_cast<size_t>(z * kBsTileN + r_local) * (XR / 4);
+#pragma unroll
+                        for(int i = 0; i < XR; i += 4)
+                        {
+                            const float4 t = mine[i / 4];
+                            acc[i] += t.x;
+                            acc[i + 1] += t.y;
+                            acc[i + 2] += t.z;
+                            acc[i + 3] += t.w;
+                        }
+                    }
+                }
+            }
+        }
+        else if(ok && prm.splits > 1)
+        {
+            // K split: park this slice ([m][n] floats), take a ticket; the last slice to arrive adds them in a fixed order
+            const unsigned int tile = blockIdx.x;
+            float* mine = prm.ws_partial + (static_cast<size_t>(tile) * prm.splits + blockIdx.z) * (XR * kBsTileN);
+#pragma unroll
+            for(int i = 0; i < XR; ++i)
+                if(i < prm.M)
+                    mine[i * kBsTileN + r_local] = acc[i];
+            __threadfence();
+            __syncwarp();
+            if(lane == 0)
+                mbar_arrive(epi_bar);
+            bool all = bounded_wait(epi_bar, 0, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, 0x1000);
+            all      = __all_sync(0xffffffffu, all);
+            if(all)
+            {
+                if(threadIdx.x == 64)
+                {
+                    *reinterpret_cast<volatile unsigned int*>(ticket) = atomicAdd(prm.ws_counter + tile, 1u);
+                    __threadfence_block();
+                }
+                __syncwarp();
+                if(lane == 0)
+                    mbar_arrive(epi_bar);
+                all = bounded_wait(epi_bar, 1, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, 0x2000);
+                all = __all_sync(0xffffffffu, all);
+            }
+            ok = all && (*reinterpret_cast<volatile unsigned int*>(ticket) == static_cast<unsigned int>(prm.splits - 1));
+            if(ok)
+            {
+                __threadfence();
+                const float* part = prm.ws_partial + static_cast<size_t>(tile) * prm.splits * (XR * kBsTileN);
+#pragma unroll
+                for(int i = 0; i < XR; ++i)
+                    acc[i] = 0.f;
+                for(int z = 0; z < prm.splits; ++z)
+                {
+                    const float* src = part + static_cast<size_t>(z) * (XR * kBsTileN);
+#pragma unroll
+                    for(int i = 0; i < XR; ++i)
+                        if(i < prm.M)
+                            acc[i] += __ldcg(src + i * kBsTileN + r_local);
+                }
+                if(threadIdx.x == 64)
+                    prm.ws_counter[tile] = 0; // ready for the next launch
+            }
+        }
+        if(ok && n < prm.N)
+        {
+#pragma unroll
+            for(int i = 0; i < XR; ++i)
+                if(i < prm.M)
+                    prm.out[static_cast<size_t>(i) * prm.ldo + n] = __float2bfloat16_rn(acc[i]);
+        }
+        tc_fence_before_sync();
+    }
+    __syncthreads();
+    if(prm.cluster)
+        cluster_sync_all(); // nobody leaves while a slice may still be on its way to the reducing CTA
+    if(warp == 1)
+    {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 

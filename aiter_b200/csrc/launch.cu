@@ -974,6 +974,12 @@ static void launch_blockscale_e8m0(const BlockScaleProblem& prob)
     launch_gemm(p);
 }
 
+static bool few_rows_disabled()
+{
+    static const bool off = (std::getenv("AITER_B200_NO_BLOCKSCALE_FEWROWS") != nullptr);
+    return off;
+}
+
 void launch_blockscale(const BlockScaleProblem& prob)
 {
     if(prob.M == 0 && prob.N > 0 && prob.K > 0)
@@ -1027,6 +1033,7 @@ void launch_blockscale(const BlockScaleProblem& prob)
         CUtensorMap mb = operand_map(prob.wgt, kTileP, "weight operand");
         static bool attr_done[64] = {};
         raise_smem_limit(gemm_a8w8_blockscale_pair_kernel, attr_done);
+        prm.splits             = 1;
         const unsigned pairs_m = static_cast<unsigned>((prob.M + 2 * kTileP - 1) / (2 * kTileP));
         const unsigned tiles_n = static_cast<unsigned>((prob.N + kBsPairN - 1) / kBsPairN);
         B200_CHECK(tiles_n <= 65535, "N too large");
@@ -1044,6 +1051,76 @@ void launch_blockscale(const BlockScaleProblem& prob)
         lc.numAttrs = 1;
         B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_pair_kernel, ma, mb, prm));
     }
+    else if(prob.M <= 32 && !few_rows_disabled())
+    {
+        // few activation rows: weights on the M side of the MMA, activations on its N side
+        const int xr          = prob.M <= 16 ? 16 : 32;
+        const int stage_bytes = (kBsTileN + xr) * kTileKBytes;
+        CUtensorMap ma = operand_map(prob.act, xr, "activation operand");
+        CUtensorMap mb = operand_map(prob.wgt, kBsTileN, "weight operand");
+        dim3 grid(static_cast<unsigned>((prob.N + kBsTileN - 1) / kBsTileN), 1, 1);
+        // split K across CTAs while the grid under-fills the machine and every slice keeps two K blocks; up to eight
+        // slices of 16 or 32 rows form one cluster and meet in shared memory, the rest goes through the workspace
+        static const bool no_split   = (std::getenv("AITER_B200_NO_BLOCKSCALE_SPLIT") != nullptr);
+        static const bool no_cluster = (std::getenv("AITER_B200_NO_CLUSTER_SPLIT") != nullptr);
+        const bool may_cluster       = !no_cluster && xr <= 32;
+        int splits = 1;
+        while(!no_split && splits < (may_cluster ? 8 : 16) && static_cast<long long>(grid.x) * (splits * 2) <= st.sm_count &&
+              prm.k_blocks / (splits * 2) >= 2)
+            splits *= 2;
+        prm.cluster = (may_cluster && splits > 1) ? 1 : 0;
+        if(prm.cluster)
+            ; // nothing to reserve: the slices meet in the reducing CTA's shared memory
+        else if(splits > 1 && grid.x <= static_cast<unsigned>(kCounterSlots))
+        {
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            cudaStreamIsCapturing(prob.stream, &cap);
+            const size_t bytes  = static_cast<size_t>(grid.x) * splits * kBsTileN * xr * sizeof(float);
+            StreamWorkspace& w0 = st.ws[prob.stream];
+            if(cap != cudaStreamCaptureStatusNone && (w0.counter == nullptr || w0.partial_bytes < bytes))
+                splits = 1; // the workspace may not grow inside a capture: run unsplit
+            else
+            {
+                StreamWorkspace& w = stream_workspace(st, prob.stream, bytes);
+                prm.ws_partial     = w.partial;
+                prm.ws_counter     = w.counter;
+            }
+        }
+        else
+            splits = 1;
+        prm.splits = splits;
+        grid.z     = static_cast<unsigned>(splits);
+        const int per_slice  = (prm.k_blocks + splits - 1) / splits;
+        const int red_bytes  = prm.cluster ? (splits - 1) * kBsTileN * xr * 4 : 0;
+        prm.stages           = std::max(2, std::min(std::min((st.smem_optin - 2048 - red_bytes) / stage_bytes, kMaxStages), per_slice));
+        const size_t smem    = static_cast<size_t>(stage_bytes) * prm.stages + red_bytes + 512 + 1024;
+        cudaLaunchConfig_t lc{};
+        lc.gridDim          = grid;
+        lc.blockDim         = dim3(kBlockScaleThreads, 1, 1);
+        lc.dynamicSmemBytes = smem;
+        lc.stream           = prob.stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id               = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = prm.cluster ? static_cast<unsigned>(splits) : 1u;
+        attr[1].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        lc.attrs    = attr;
+        lc.numAttrs = pdl_disabled() ? 1 : 2;
+        static bool attr_done[2][64] = {};
+        if(xr == 16)
+        {
+            raise_smem_limit(gemm_a8w8_blockscale_fewrows_kernel<16>, attr_done[0]);
+            B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_fewrows_kernel<16>, ma, mb, prm));
+        }
+        else
+        {
+            raise_smem_limit(gemm_a8w8_blockscale_fewrows_kernel<32>, attr_done[1]);
+            B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_fewrows_kernel<32>, ma, mb, prm));
+        }
+        B200_CUDA(cudaGetLastError());
+    }
     else
     {
         const int stage_bytes = (kTileP + kBsTileN) * kTileKBytes;
@@ -1058,6 +1135,32 @@ void launch_blockscale(const BlockScaleProblem& prob)
         raise_smem_limit(gemm_a8w8_blockscale_kernel, attr_done);
         dim3 grid(static_cast<unsigned>((prob.M + kTileP - 1) / kTileP), static_cast<unsigned>((prob.N + kBsTileN - 1) / kBsTileN), 1);
         B200_CHECK(grid.y <= 65535, "N too large");
+        // few tiles (decode shapes): split K across CTAs while the grid under-fills the machine and every slice keeps
+        // four K blocks; the slices meet in a per-stream fp32 workspace, the last to arrive reduces
+        int splits = 1;
+        const long long tiles = static_cast<long long>(grid.x) * grid.y;
+        static const bool no_split = (std::getenv("AITER_B200_NO_BLOCKSCALE_SPLIT") != nullptr);
+        while(!no_split && splits < 8 && tiles * (splits * 2) <= st.sm_count && prm.k_blocks / (splits * 2) >= 4)
+            splits *= 2;
+        if(splits > 1 && tiles <= kCounterSlots)
+        {
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            cudaStreamIsCapturing(prob.stream, &cap);
+            const size_t bytes = static_cast<size_t>(tiles) * splits * kBsTileN * kTileP * sizeof(float);
+            StreamWorkspace& w0 = st.ws[prob.stream];
+            if(cap != cudaStreamCaptureStatusNone && (w0.counter == nullptr || w0.partial_bytes < bytes))
+                splits = 1; // the workspace may not grow inside a capture: run unsplit
+            else
+            {
+                StreamWorkspace& w = stream_workspace(st, prob.stream, bytes);
+                prm.ws_partial     = w.partial;
+                prm.ws_counter     = w.counter;
+            }
+        }
+        else
+            splits = 1;
+        prm.splits = splits;
+        grid.z     = static_cast<unsigned>(splits);
         gemm_a8w8_blockscale_kernel<<<grid, kBlockScaleThreads, smem, prob.stream>>>(ma, mb, prm);
         B200_CUDA(cudaGetLastError());
     }
