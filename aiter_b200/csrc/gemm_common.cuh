@@ -60,16 +60,28 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
     return false;
 }
 
+// prmt in its default mode: selector nibble bit 3 set = fill the byte with the selected byte's sign bit
+__device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel)
+{
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
 // 8 packed e2m1 codes (one 32-bit word, element n in nibble n) -> 8 e4m3 bytes (exact: every e2m1 value
-// is an e4m3 value).  Magnitude by table look-up (prmt), sign moved to bit 7 of each byte.
+// is an e4m3 value).  Magnitude by table look-up (prmt on the 3-bit magnitude codes); the sign bits sit at bit 7
+// of the bytes of w (odd codes) and of w << 4 (even codes), from where a sign-replicating prmt spreads them over
+// whole bytes and one and-or keeps bit 7.
 __device__ __forceinline__ void e2m1x8_to_e4m3x8(uint32_t w, uint32_t& lo, uint32_t& hi)
 {
     constexpr uint32_t kLutLo = 0x3C383000u; // 0, 0.5, 1, 1.5
     constexpr uint32_t kLutHi = 0x4C484440u; // 2, 3, 4, 6
-    constexpr uint32_t kSign  = 0x00008000u; // byte 0 = 0x00, byte 1 = 0x80
-    lo = __byte_perm(kLutLo, kLutHi, w & 0x7777u) | __byte_perm(kSign, 0u, (w >> 3) & 0x1111u);
-    const uint32_t h = w >> 16;
-    hi = __byte_perm(kLutLo, kLutHi, h & 0x7777u) | __byte_perm(kSign, 0u, (h >> 3) & 0x1111u);
+    const uint32_t mag = w & 0x77777777u;
+    const uint32_t x   = w << 4;
+    const uint32_t s_lo = prmt_b32(w, x, 0x9D8Cu); // codes 0..3: bytes x.0, w.0, x.1, w.1, sign-replicated
+    const uint32_t s_hi = prmt_b32(w, x, 0xBFAEu); // codes 4..7: bytes x.2, w.2, x.3, w.3
+    lo = prmt_b32(kLutLo, kLutHi, mag) | (s_lo & 0x80808080u);
+    hi = prmt_b32(kLutLo, kLutHi, mag >> 16) | (s_hi & 0x80808080u);
 }
 
 __device__ __forceinline__ void issue_operand_load(int mode, uint32_t dst, const CUtensorMap* map, uint32_t bar,

@@ -191,7 +191,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
         for(int s = 0; s < S; ++s)
         {
             // one expect_tx arrival per operand producer and one arrival per scale warp, of every CTA of the pair
-            mbar_init(full_bar(s), (kScaled ? 6 : 2) * CG);
+            mbar_init(full_bar(s), (kMixed ? 10 : (kScaled ? 6 : 2)) * CG); // producers + scale warps (+ widening warps)
             mbar_init(empty_bar(s), 1);
             mbar_init(staged_bar(s), 1);
             mbar_init(sfraw_bar(s), 1);
@@ -540,37 +540,29 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             {
                 const int s = ring.s;
                 // raw scales of stage s have landed (their producer waited for the previous pass's MMAs, so the
-                // TMEM scale buffer of stage s is free as well); mixed kind: so has the packed e2m1 tile
+                // TMEM scale buffer of stage s is free as well)
                 ok = bounded_wait(sfraw_bar(s), ring.phase, abort_f, prm.status, ST_TIMEOUT_SFWARP, g);
-                if(ok && kMixed)
-                    ok = bounded_wait(staged_bar(s), ring.phase, abort_f, prm.status, ST_TIMEOUT_SFWARP, 0x10000 + g);
+                const bool widen_here = kMixed && (p_f4 || q_rows_cta == kTileP); // 128-row packed tile: k chunk 3 is ours
+                if(ok && widen_here)
+                    ok = bounded_wait(staged_bar(s), ring.phase, abort_f, prm.status, ST_TIMEOUT_SFWARP, 0x20000 + g);
                 ok = __all_sync(0xffffffffu, ok);
                 if(!ok)
                     break;
                 if(tracing && warp == 2 && lane == 0 && g < 8) stamp(3 + 4 * g);
                 uint8_t* stage = smem_gen + s * L.stage_bytes;
-                if(kMixed)
+                if(widen_here)
                 {
-                    // widen the packed e2m1 operand of this stage to e4m3 in the MMA's un-swizzled layout:
-                    // staging [4 chunks][rows][16 B] (32 codes each) -> tile [8 chunks][rows][16 B]
-                    const int rows   = p_f4 ? kTileP : q_rows_cta;
-                    const uint4* src = reinterpret_cast<const uint4*>(stage + L.stg_off);
-                    uint4* dst       = reinterpret_cast<uint4*>(stage + (p_f4 ? 0u : L.q_off));
-                    const int items  = rows * 4;
-                    for(int it = (warp - 2) * 32 + lane; it < items; it += 128)
-                    {
-                        const int kc  = it / rows;
-                        const int r   = it - kc * rows;
-                        const uint4 v = src[it];
-                        uint4 o0, o1;
-                        e2m1x8_to_e4m3x8(v.x, o0.x, o0.y);
-                        e2m1x8_to_e4m3x8(v.y, o0.z, o0.w);
-                        e2m1x8_to_e4m3x8(v.z, o1.x, o1.y);
-                        e2m1x8_to_e4m3x8(v.w, o1.z, o1.w);
-                        dst[(2 * kc) * rows + r]     = o0;
-                        dst[(2 * kc + 1) * rows + r] = o1;
-                    }
-                    fence_proxy_async_smem(); // these generic-proxy writes are read by the tensor core
+                    const int tid = (warp - 2) * 32 + lane;
+                    const uint4 v = reinterpret_cast<const uint4*>(stage + L.stg_off)[3 * kTileP + tid];
+                    uint4* dst    = reinterpret_cast<uint4*>(stage + (p_f4 ? 0u : L.q_off));
+                    uint4 o0, o1;
+                    e2m1x8_to_e4m3x8(v.x, o0.x, o0.y);
+                    e2m1x8_to_e4m3x8(v.y, o0.z, o0.w);
+                    e2m1x8_to_e4m3x8(v.z, o1.x, o1.y);
+                    e2m1x8_to_e4m3x8(v.w, o1.z, o1.w);
+                    dst[6 * kTileP + tid] = o0;
+                    dst[7 * kTileP + tid] = o1;
+                    fence_proxy_async_smem(); // read by the tensor core
                 }
                 // TMEM words of this stage, column order [P atom a][Q atom a, block 0][Q atom a, block 1]
                 const uint32_t* rawp = reinterpret_cast<const uint32_t*>(stage + L.sfp_off);
@@ -690,8 +682,77 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
         uint32_t epi_phase = 0;
         int uc = 0;
         bool ok = true;
+        Ring wring{0, 0};
+        const uint32_t full_lead = (CG == 2) ? map_to_cta(full_bar(0), 0) : full_bar(0);
         for(WorkIter w = first_work(); w.valid && ok; next_unit(w), ++uc)
         {
+            if(kMixed)
+            {
+                // Mixed kind: these four warps first widen the packed e2m1 operand of every K tile of this unit to
+                // e4m3 in the MMA's un-swizzled layout (staging [4 chunks][rows][16 B], 32 codes each -> tile
+                // [8 chunks][rows][16 B]) while the scale warps feed the scales, then turn to the unit's epilogue.
+                const int rows = p_f4 ? kTileP : q_rows_cta;
+                const int tid  = (warp - 6) * 32 + lane;
+                for(int i = 0; i < w.n_iters && ok; ++i, wring.advance(S))
+                {
+                    const int s = wring.s;
+                    ok = bounded_wait(staged_bar(s), wring.phase, abort_f, prm.status, ST_TIMEOUT_SFWARP, 0x10000 + i);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if(!ok)
+                        break;
+                    if(tracing && warp == 6 && lane == 0 && uc == 0 && i < 8) stamp(34 + 2 * i);
+                    uint8_t* stage   = smem_gen + s * L.stage_bytes;
+                    const uint4* src = reinterpret_cast<const uint4*>(stage + L.stg_off);
+                    uint4* dst       = reinterpret_cast<uint4*>(stage + (p_f4 ? 0u : L.q_off));
+                    if(rows == kTileP)
+                    {
+                        // 128 rows: one item per thread and 16-byte k chunk (chunk u, row tid); chunks 0..2 here, chunk 3
+                        // by the scale warps, whose own work per stage is shorter.  All loads first, so that their
+                        // latencies overlap instead of adding up
+                        uint4 v[3];
+#pragma unroll
+                        for(int u = 0; u < 3; ++u)
+                            v[u] = src[u * kTileP + tid];
+#pragma unroll
+                        for(int u = 0; u < 3; ++u)
+                        {
+                            uint4 o0, o1;
+                            e2m1x8_to_e4m3x8(v[u].x, o0.x, o0.y);
+                            e2m1x8_to_e4m3x8(v[u].y, o0.z, o0.w);
+                            e2m1x8_to_e4m3x8(v[u].z, o1.x, o1.y);
+                            e2m1x8_to_e4m3x8(v[u].w, o1.z, o1.w);
+                            dst[(2 * u) * kTileP + tid]     = o0;
+                            dst[(2 * u + 1) * kTileP + tid] = o1;
+                        }
+                    }
+                    else
+                        for(int it = tid; it < rows * 4; it += 128)
+                        {
+                            const int kc  = it / rows;
+                            const int r   = it - kc * rows;
+                            const uint4 v = src[it];
+                            uint4 o0, o1;
+                            e2m1x8_to_e4m3x8(v.x, o0.x, o0.y);
+                            e2m1x8_to_e4m3x8(v.y, o0.z, o0.w);
+                            e2m1x8_to_e4m3x8(v.z, o1.x, o1.y);
+                            e2m1x8_to_e4m3x8(v.w, o1.z, o1.w);
+                            dst[(2 * kc) * rows + r]     = o0;
+                            dst[(2 * kc + 1) * rows + r] = o1;
+                        }
+                    fence_proxy_async_smem(); // these generic-proxy writes are read by the tensor core
+                    __syncwarp();
+                    if(lane == 0)
+                    {
+                        if(CG == 2)
+                            mbar_arrive_cluster(full_lead + 8u * s);
+                        else
+                            mbar_arrive(full_lead + 8u * s);
+                        if(tracing && warp == 6 && uc == 0 && i < 8) stamp(35 + 2 * i);
+                    }
+                }
+                if(!ok)
+                    break;
+            }
             const int a       = uc % prm.n_acc;
             const int p       = (w.tp * CG + static_cast<int>(crank)) * kTileP + p_local;
             const int row_q0  = w.tq * bn;
