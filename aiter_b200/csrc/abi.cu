@@ -282,7 +282,10 @@ static void run_blockscale(const char* fn, aiter_tensor_t* XQ, aiter_tensor_t* W
     p.scales_are_e8m0 = sx8 && sw8;
     // with e8m0 scales the problem runs on the MXFP8 kernel family, whose configuration names apply
     if(p.scales_are_e8m0 && kernelName != nullptr && kernelName[0] != 0)
+    {
         B200_CHECK(parse_config_name(kernelName, p.cfg), fn, ": not find kernel ", kernelName);
+        p.cfg_given = true;
+    }
     p.out     = Out->ptr;
     p.ldo     = Out->strides[0];
     p.device  = XQ->device_id;

@@ -34,6 +34,7 @@ struct BlockScaleParams
     int splits;
     float* ws_partial;
     unsigned int* ws_counter;
+    int scales_e8m0;         // few-rows kernel: both scale tensors hold e8m0 bytes (2^(e-127)) instead of floats
     int cluster;             // few-rows kernel: the slices are the CTAs of one cluster and meet in shared memory
 };
 
@@ -50,6 +51,12 @@ __device__ __forceinline__ void mma_f8f6f4(uint32_t d, uint64_t adesc, uint64_t 
         "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+
+// e8m0 byte -> float: 2^(e - 127); 0 is the denormal 2^-127, 255 is NaN
+__device__ __forceinline__ float e8m0_to_float(uint32_t e)
+{
+    return __uint_as_float(e == 0u ? 0x00400000u : (e == 255u ? 0x7FC00000u : e << 23));
 }
 
 __global__ void __launch_bounds__(kBlockScaleThreads, 1)
@@ -432,10 +439,22 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
             const int b = j % NP;
             // this K block's scales (the same addresses in every thread: broadcast), fetched ahead of the wait
             float sc[XR];
-            const float wsj = __ldg(ws + j);
+            if(prm.scales_e8m0)
+            {
+                const uint8_t* ws8 = reinterpret_cast<const uint8_t*>(prm.w_scale) + static_cast<long long>(blockIdx.x) * prm.k_blocks + kb0;
+                const uint8_t* xs8 = reinterpret_cast<const uint8_t*>(prm.x_scale) + static_cast<long long>(kb0) * prm.xs_stride_k;
+                const float wsj    = e8m0_to_float(__ldg(ws8 + j));
 #pragma unroll
-            for(int i = 0; i < XR; ++i)
-                sc[i] = __ldg(xs + static_cast<long long>(i < prm.M ? i : 0) * prm.xs_stride_m + static_cast<long long>(j) * prm.xs_stride_k) * wsj;
+                for(int i = 0; i < XR; ++i)
+                    sc[i] = e8m0_to_float(__ldg(xs8 + static_cast<long long>(i < prm.M ? i : 0) * prm.xs_stride_m + static_cast<long long>(j) * prm.xs_stride_k)) * wsj;
+            }
+            else
+            {
+                const float wsj = __ldg(ws + j);
+#pragma unroll
+                for(int i = 0; i < XR; ++i)
+                    sc[i] = __ldg(xs + static_cast<long long>(i < prm.M ? i : 0) * prm.xs_stride_m + static_cast<long long>(j) * prm.xs_stride_k) * wsj;
+            }
             ok = bounded_wait(part_full_bar(b), (j / NP) & 1, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, j);
             ok = __all_sync(0xffffffffu, ok);
             if(!ok)

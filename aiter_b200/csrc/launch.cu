@@ -984,8 +984,10 @@ void launch_blockscale(const BlockScaleProblem& prob)
 {
     if(prob.M == 0 && prob.N > 0 && prob.K > 0)
         return;
-    if(prob.scales_are_e8m0)
+    if(prob.scales_are_e8m0 && (prob.M > 32 || prob.cfg_given || few_rows_disabled()))
     {
+        // powers of two ride the block-scaled MMA; up to 32 rows stay on the few-rows kernel below, which reads the
+        // e8m0 bytes itself (one launch, no scale expansion pass)
         B200_CHECK(prob.K % 128 == 0, "K must be a multiple of 128 for 128-wide scale blocks (got ", prob.K, ")");
         launch_blockscale_e8m0(prob);
         return;
@@ -1021,6 +1023,7 @@ void launch_blockscale(const BlockScaleProblem& prob)
     prm.out         = static_cast<__nv_bfloat16*>(prob.out);
     prm.ldo         = prob.ldo;
     prm.status      = st.status;
+    prm.scales_e8m0 = prob.scales_are_e8m0 ? 1 : 0;
     if(prob.M > kTileP)
     {
         // 256 x 256 tiles on CTA pairs

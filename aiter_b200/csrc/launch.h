@@ -114,9 +114,11 @@ struct BlockScaleProblem
     long long xs_stride_m = 0, xs_stride_k = 0;
     const float* w_scale = nullptr;
     // both scale tensors hold UE8M0 bytes instead of floats (same shapes and strides, in bytes): powers of two ride
-    // the block-scaled MMA, so the problem runs on the MXFP8 kernel after a small expansion of the scales
+    // the block-scaled MMA, so the problem runs on the MXFP8 kernel after a small expansion of the scales (up to 32
+    // rows without a caller-chosen configuration: on the few-rows kernel, which reads the bytes itself)
     bool scales_are_e8m0 = false;
     KernelConfig cfg;             // e8m0 path only: a caller-chosen MXFP8 kernel configuration (unset fields: heuristic)
+    bool cfg_given = false;
     void* out = nullptr;
     long long ldo = 0;
     int device = 0;

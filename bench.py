@@ -271,7 +271,8 @@ def run_sweep(torch, ab, device, peaks):
             rows.append({"kind": tag, "M": M, "N": 4096, "K": 4096, "us": round(us, 2), "tflops": round(tf, 1),
                          "gbs": round(algorithmic_bytes("mxfp8", M, 4096, 4096) / us / 1e3, 1), "frac_tensor": round(tf / (2 * peaks["bf16"]), 4),
                          "frac_hbm": round(algorithmic_bytes("mxfp8", M, 4096, 4096) / us / 1e3 / peaks["hbm_gbs"], 4),
-                         "kernel": "gemm_a8w8_blockscale" + ("_pair_kernel" if tag.endswith("fp32") and M > 128 else "_kernel" if tag.endswith("fp32") else " -> mxfp8")})
+                         "kernel": "gemm_a8w8_blockscale" + ("_fewrows_kernel" if M <= 32 else "_pair_kernel" if tag.endswith("fp32") and M > 128
+                                                             else "_kernel" if tag.endswith("fp32") else " -> mxfp8")})
     # fused activation quantiser (bf16 -> MX data + scales in the GEMM's layout): HBM-bound
     for (kind, M, K, kw) in (("quant_mxfp4", 16384, 16384, dict(quant_dtype=ab.dtypes.fp4x2, shuffle=True)),
                              ("quant_mxfp8", 8192, 4096, dict(quant_dtype=ab.dtypes.fp8, scale_type=ab.dtypes.fp8_e8m0, shuffle=2)),
