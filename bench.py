@@ -185,8 +185,8 @@ def rotating_sets(make, bytes_per_set, l2_bytes=126e6):
 
 # --------------------------------------------------------------------------------------- sweep
 def run_case(torch, ab, device, spec, steps, warmup):
-    """Profiling aid: one sweep case, `kind:M:N:K` with kind in mxfp8 / mxfp4 / a8w4 / bf16 / quant_mxfp4 / quant_mxfp8
-    (N ignored for the quantiser), launched `steps` times on the current stream; prints one JSON line."""
+    """Profiling aid: one sweep case, `kind:M:N:K` with kind in mxfp8 / mxfp4 / a8w4 / bf16 / blockscale_fp32 /
+    blockscale_e8m0 / quant_mxfp4 / quant_mxfp8 (N ignored for the quantiser), launched `steps` times on the current stream; prints one JSON line."""
     kind, M, N, K = spec.split(":")
     M, N, K = int(M), int(N), int(K)
 
@@ -214,11 +214,23 @@ def run_case(torch, ab, device, spec, steps, warmup):
         kw = dict(quant_dtype=ab.dtypes.fp4x2, shuffle=True) if kind == "quant_mxfp4" else dict(
             quant_dtype=ab.dtypes.fp8, scale_type=ab.dtypes.fp8_e8m0, shuffle=2)
         fn = lambda x: ab.per_1x32_mx_quant_hip(x, **kw)  # noqa: E731
+    elif kind in ("blockscale_fp32", "blockscale_e8m0"):
+        kb, nb = K // 128, (N + 127) // 128
+        scales = (torch.rand(M, kb, device=device) + 0.5, torch.rand(nb, kb, device=device) + 0.5) if kind.endswith("fp32") else (
+            rand_u8(124, 130, M, kb).view(ab.dtypes.fp8_e8m0), rand_u8(124, 130, nb, kb).view(ab.dtypes.fp8_e8m0))
+        args = (rand_u8(0, 0x78, M, K).view(torch.float8_e4m3fn), rand_u8(0, 0x78, N, K).view(torch.float8_e4m3fn), *scales)
+        fn = lambda a, b, xs, ws: ab.gemm_a8w8_blockscale(a, b, xs, ws)  # noqa: E731
     else:
         raise SystemExit(f"unknown case kind {kind}")
     us = time_calls(torch, fn, [args], steps, warmup)
-    print(json.dumps({"case": spec, "us_per_call": round(us, 2), "steps": steps, "warmup": warmup,
-                      "kernel": kernel_in_use(ab, kind, M, N, K) if not kind.startswith("quant") else "quant_mx_kernel"}))
+    if kind.startswith("quant"):
+        kernel = "quant_mx_kernel"
+    elif kind.startswith("blockscale"):
+        kernel = "gemm_a8w8_blockscale" + ("_fewrows_kernel" if M <= 32 else " -> mxfp8" if kind.endswith("e8m0")
+                                           else "_pair_kernel" if M > 128 else "_kernel")
+    else:
+        kernel = kernel_in_use(ab, kind, M, N, K)
+    print(json.dumps({"case": spec, "us_per_call": round(us, 2), "steps": steps, "warmup": warmup, "kernel": kernel}))
 
 
 def run_sweep(torch, ab, device, peaks):
