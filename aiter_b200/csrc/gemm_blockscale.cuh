@@ -16,6 +16,7 @@
 namespace b200 {
 
 constexpr int kBlockScaleThreads = 192;
+constexpr int kFewRowsThreads    = 224; // + a second MMA issuer warp
 constexpr int kBsTileN           = 128;
 
 struct BlockScaleParams
@@ -116,17 +117,24 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     {
         if(lane == 0)
         {
+            // single-thread loops pay every instruction's latency: ring counters, no division
             int issued = 0;
+            int s = 0;
+            uint32_t phase = 0;
             for(int j = 0; j < KB; ++j)
             {
-                const int s = j % S;
-                if(!bounded_wait(empty_bar(s), ((j / S) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_PRODUCER, j))
+                if(j >= S && !bounded_wait(empty_bar(s), phase ^ 1u, abort_f, prm.status, ST_TIMEOUT_PRODUCER, j))
                     break;
                 const uint32_t stage = smem_base + s * kStageBytes;
                 mbar_arrive_expect_tx(full_bar(s), kStageBytes);
                 issue_operand_load(prm.a_mode, stage, &map_a, full_bar(s), row0, kb0 + j);
                 issue_operand_load(prm.b_mode, stage + kTileP * kTileKBytes, &map_b, full_bar(s), col0, kb0 + j);
                 issued = j + 1;
+                if(++s == S)
+                {
+                    s = 0;
+                    phase ^= 1u;
+                }
             }
             if(*abort_f)
                 for(int j = issued - 1; j >= 0 && j >= issued - S; --j)
@@ -146,23 +154,37 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const uint32_t a_adv = a_tiled ? 2u * kTileP * 16u : 32u;
             const uint32_t b_lbo = b_tiled ? kBsTileN * 16u : 16u, b_sbo = b_tiled ? 128u : 1024u, b_lay = b_tiled ? 0u : 2u;
             const uint32_t b_adv = b_tiled ? 2u * kBsTileN * 16u : 32u;
+            // descriptor words once; per MMA only an add on the address field
+            const uint32_t a_hi  = static_cast<uint32_t>(make_smem_desc(0, a_lbo, a_sbo, a_lay) >> 32);
+            const uint32_t b_hi  = static_cast<uint32_t>(make_smem_desc(0, b_lbo, b_sbo, b_lay) >> 32);
+            const uint32_t a_lo0 = static_cast<uint32_t>(make_smem_desc(smem_base, a_lbo, a_sbo, a_lay));
+            const uint32_t b_lo0 = static_cast<uint32_t>(make_smem_desc(smem_base + kTileP * kTileKBytes, b_lbo, b_sbo, b_lay));
+            const uint32_t a_step = a_adv >> 4, b_step = b_adv >> 4;
             bool ok = true;
+            int s = 0;
+            uint32_t phase = 0;
             for(int j = 0; j < KB && ok; ++j)
             {
-                const int s = j % S, b = j & 1;
-                ok = bounded_wait(part_empty_bar(b), ((j >> 1) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_MMA_SF, j);
+                const int b = j & 1;
+                if(j >= 2) // both partials start free
+                    ok = bounded_wait(part_empty_bar(b), ((j >> 1) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_MMA_SF, j);
                 if(ok)
-                    ok = bounded_wait(full_bar(s), (j / S) & 1, abort_f, prm.status, ST_TIMEOUT_MMA_FULL, j);
+                    ok = bounded_wait(full_bar(s), phase, abort_f, prm.status, ST_TIMEOUT_MMA_FULL, j);
                 if(!ok)
                     break;
                 tc_fence_after_sync();
-                const uint32_t stage = smem_base + s * kStageBytes;
+                const uint32_t a_lo = a_lo0 + s * (kStageBytes >> 4), b_lo = b_lo0 + s * (kStageBytes >> 4);
 #pragma unroll
                 for(int k = 0; k < 4; ++k)
-                    mma_f8f6f4(tmem_base + b * kBsTileN, make_smem_desc(stage + k * a_adv, a_lbo, a_sbo, a_lay),
-                               make_smem_desc(stage + kTileP * kTileKBytes + k * b_adv, b_lbo, b_sbo, b_lay), idesc, k > 0 ? 1u : 0u);
+                    mma_f8f6f4(tmem_base + b * kBsTileN, pack_u64(a_lo + k * a_step, a_hi), pack_u64(b_lo + k * b_step, b_hi), idesc,
+                               k > 0 ? 1u : 0u);
                 tc_commit(empty_bar(s));
                 tc_commit(part_full_bar(b));
+                if(++s == S)
+                {
+                    s = 0;
+                    phase ^= 1u;
+                }
             }
         }
     }
@@ -295,9 +317,9 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 // with x_scale[m][kb] * w_scale[n/128][kb]; 8 TMEM partials are in flight, so the round trip
 // MMA -> commit -> promotion -> release is paid once per 8 K blocks, not per 2.  gridDim.z slices of K meet either
 // in the reducing CTA's shared memory (the slices form one thread-block cluster and send their fp32 tiles with
-// st.async) or in the fp32 workspace like in the kernel above.  Warps (192 threads): 0 TMA producer, 1 MMA issuer + TMEM owner, 2..5 promotion + store.
+// st.async) or in the fp32 workspace like in the kernel above.  Warps (224 threads): 0 TMA producer, 1 and 6 MMA issuers (1 owns TMEM), 2..5 promotion + store.
 template <int XR>
-__global__ void __launch_bounds__(kBlockScaleThreads, 1)
+__global__ void __launch_bounds__(kFewRowsThreads, 1)
 gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                     const BlockScaleParams prm)
 {
@@ -324,6 +346,7 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
     uint32_t* tmem_ptr_smem    = reinterpret_cast<uint32_t*>(smem_gen + bar_off + 272);
     volatile uint32_t* abort_f = reinterpret_cast<volatile uint32_t*>(smem_gen + bar_off + 276);
     unsigned int* ticket       = reinterpret_cast<unsigned int*>(smem_gen + bar_off + 280);
+    float* sc_tab              = reinterpret_cast<float*>(smem_gen + bar_off + 512); // [K block of this slice][XR] scale products
     const uint32_t zrank       = prm.cluster ? cluster_ctarank() : blockIdx.z; // K slice; 0 reduces a cluster-split tile
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int col0 = blockIdx.x * kBsTileN;
@@ -368,17 +391,24 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
     {
         if(lane == 0)
         {
+            // single-thread loops pay every instruction's latency: ring counters, no division
             int issued = 0;
+            int s = 0;
+            uint32_t phase = 0;
             for(int j = 0; j < KB; ++j)
             {
-                const int s = j % S;
-                if(!bounded_wait(empty_bar(s), ((j / S) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_PRODUCER, j))
+                if(j >= S && !bounded_wait(empty_bar(s), phase ^ 1u, abort_f, prm.status, ST_TIMEOUT_PRODUCER, j))
                     break;
                 const uint32_t stage = smem_base + s * kStageBytes;
                 mbar_arrive_expect_tx(full_bar(s), kStageBytes);
                 issue_operand_load(prm.b_mode, stage, &map_b, full_bar(s), col0, kb0 + j);
                 issue_operand_load(prm.a_mode, stage + kWBytes, &map_a, full_bar(s), 0, kb0 + j);
                 issued = j + 1;
+                if(++s == S)
+                {
+                    s = 0;
+                    phase ^= 1u;
+                }
             }
             if(*abort_f)
                 for(int j = issued - 1; j >= 0 && j >= issued - S; --j)
@@ -388,45 +418,66 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
                 }
         }
     }
-    else if(warp == 1)
+    else if(warp == 1 || warp == 6)
     {
+        // two MMA issuers, even K blocks from warp 1 and odd ones from warp 6: an issuer needs ~600 cycles per K block
+        // (a barrier wait, four MMAs and two commits at a single thread's instruction latency), the tensor pipe far
+        // less, and the partials of consecutive K blocks are independent
         if(lane == 0)
         {
+            const int first = (warp == 1) ? 0 : 1;
             const uint32_t idesc = idesc_f8f6f4_e4m3(kBsTileN, XR);
             const bool w_tiled = (prm.b_mode == OPM_TILE16), x_tiled = (prm.a_mode == OPM_TILE16);
             const uint32_t w_lbo = w_tiled ? kBsTileN * 16u : 16u, w_sbo = w_tiled ? 128u : 1024u, w_lay = w_tiled ? 0u : 2u;
             const uint32_t w_adv = w_tiled ? 2u * kBsTileN * 16u : 32u;
             const uint32_t x_lbo = x_tiled ? XR * 16u : 16u, x_sbo = x_tiled ? 128u : 1024u, x_lay = x_tiled ? 0u : 2u;
             const uint32_t x_adv = x_tiled ? 2u * XR * 16u : 32u;
+            // descriptor words once; per MMA only an add on the address field (this thread pays every instruction's
+            // latency, so no division, no descriptor assembly and no wait that cannot block inside the loop)
+            const uint32_t w_hi  = static_cast<uint32_t>(make_smem_desc(0, w_lbo, w_sbo, w_lay) >> 32);
+            const uint32_t x_hi  = static_cast<uint32_t>(make_smem_desc(0, x_lbo, x_sbo, x_lay) >> 32);
+            const uint32_t w_lo0 = static_cast<uint32_t>(make_smem_desc(smem_base, w_lbo, w_sbo, w_lay));
+            const uint32_t x_lo0 = static_cast<uint32_t>(make_smem_desc(smem_base + kWBytes, x_lbo, x_sbo, x_lay));
+            const uint32_t w_step = w_adv >> 4, x_step = x_adv >> 4;
             bool ok = true;
-            for(int j = 0; j < KB && ok; ++j)
+            int s = first % S, b = first;
+            uint32_t phase = (first / S) & 1u, bphase = 0;
+            for(int j = first; j < KB && ok; j += 2)
             {
-                const int s = j % S, b = j % NP;
-                ok = bounded_wait(part_empty_bar(b), ((j / NP) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_MMA_SF, j);
+                if(j >= NP) // the first NP partials are free
+                    ok = bounded_wait(part_empty_bar(b), bphase ^ 1u, abort_f, prm.status, ST_TIMEOUT_MMA_SF, j);
                 if(ok)
-                    ok = bounded_wait(full_bar(s), (j / S) & 1, abort_f, prm.status, ST_TIMEOUT_MMA_FULL, j);
+                    ok = bounded_wait(full_bar(s), phase, abort_f, prm.status, ST_TIMEOUT_MMA_FULL, j);
                 if(!ok)
                     break;
                 tc_fence_after_sync();
-                const uint32_t stage = smem_base + s * kStageBytes;
+                const uint32_t w_lo = w_lo0 + s * (kStageBytes >> 4), x_lo = x_lo0 + s * (kStageBytes >> 4);
 #pragma unroll
                 for(int k = 0; k < 4; ++k)
-                    mma_f8f6f4(tmem_base + b * XR, make_smem_desc(stage + k * w_adv, w_lbo, w_sbo, w_lay),
-                               make_smem_desc(stage + kWBytes + k * x_adv, x_lbo, x_sbo, x_lay), idesc, k > 0 ? 1u : 0u);
+                    mma_f8f6f4(tmem_base + b * XR, pack_u64(w_lo + k * w_step, w_hi), pack_u64(x_lo + k * x_step, x_hi), idesc,
+                               k > 0 ? 1u : 0u);
                 tc_commit(empty_bar(s));
                 tc_commit(part_full_bar(b));
+                if((s += 2) >= S)
+                {
+                    s -= S;
+                    phase ^= 1u;
+                }
+                if((b += 2) >= NP) // (the odd issuer passes NP + 1)
+                {
+                    b -= NP;
+                    bphase ^= 1u;
+                }
             }
         }
     }
-    else
+    else if(warp < 6)
     {
         // promotion + store: thread = output column n, TMEM columns = output rows m
         const int quarter    = warp & 3;
         const int r_local    = quarter * 32 + lane;
         const int n          = col0 + r_local;
         const uint32_t tlane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-        const float* ws      = prm.w_scale + static_cast<long long>(blockIdx.x) * prm.k_blocks + kb0;
-        const float* xs      = prm.x_scale + static_cast<long long>(kb0) * prm.xs_stride_k;
         float acc[XR];
 #pragma unroll
         for(int i = 0; i < XR; ++i)
@@ -434,26 +485,32 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
         bool ok = true;
         if(prm.cluster && zrank == 0 && threadIdx.x == 64)
             mbar_arrive_expect_tx(red_bar, static_cast<uint32_t>(prm.splits - 1) * kSliceBytes);
+        // x_scale[m][kb] * w_scale[n/128][kb] of this slice goes to shared memory once (while the first loads are in
+        // flight); the K loop then reads four products per broadcast load instead of assembling XR global addresses
+        // per K block, which a warp that has its scheduler to itself pays instruction by instruction
+        for(int it = threadIdx.x - 64; it < KB * XR; it += 128)
+        {
+            const int j = it / XR, i = it - j * XR;
+            const long long xo = static_cast<long long>(i < prm.M ? i : 0) * prm.xs_stride_m + static_cast<long long>(kb0 + j) * prm.xs_stride_k;
+            const long long wo = static_cast<long long>(blockIdx.x) * prm.k_blocks + kb0 + j;
+            sc_tab[it] = prm.scales_e8m0
+                             ? e8m0_to_float(__ldg(reinterpret_cast<const uint8_t*>(prm.x_scale) + xo)) *
+                                   e8m0_to_float(__ldg(reinterpret_cast<const uint8_t*>(prm.w_scale) + wo))
+                             : __ldg(prm.x_scale + xo) * __ldg(prm.w_scale + wo);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory"); // the four promotion warps (all of them always get here)
         for(int j = 0; j < KB && ok; ++j)
         {
             const int b = j % NP;
-            // this K block's scales (the same addresses in every thread: broadcast), fetched ahead of the wait
             float sc[XR];
-            if(prm.scales_e8m0)
-            {
-                const uint8_t* ws8 = reinterpret_cast<const uint8_t*>(prm.w_scale) + static_cast<long long>(blockIdx.x) * prm.k_blocks + kb0;
-                const uint8_t* xs8 = reinterpret_cast<const uint8_t*>(prm.x_scale) + static_cast<long long>(kb0) * prm.xs_stride_k;
-                const float wsj    = e8m0_to_float(__ldg(ws8 + j));
 #pragma unroll
-                for(int i = 0; i < XR; ++i)
-                    sc[i] = e8m0_to_float(__ldg(xs8 + static_cast<long long>(i < prm.M ? i : 0) * prm.xs_stride_m + static_cast<long long>(j) * prm.xs_stride_k)) * wsj;
-            }
-            else
+            for(int i = 0; i < XR; i += 4)
             {
-                const float wsj = __ldg(ws + j);
-#pragma unroll
-                for(int i = 0; i < XR; ++i)
-                    sc[i] = __ldg(xs + static_cast<long long>(i < prm.M ? i : 0) * prm.xs_stride_m + static_cast<long long>(j) * prm.xs_stride_k) * wsj;
+                const float4 t = *reinterpret_cast<const float4*>(sc_tab + j * XR + i);
+                sc[i] = t.x;
+                sc[i + 1] = t.y;
+                sc[i + 2] = t.z;
+                sc[i + 3] = t.w;
             }
             ok = bounded_wait(part_full_bar(b), (j / NP) & 1, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, j);
             ok = __all_sync(0xffffffffu, ok);

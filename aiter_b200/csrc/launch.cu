@@ -980,11 +980,17 @@ static bool few_rows_disabled()
     return off;
 }
 
+// up to 32 activation rows (and a K whose unsplit scale table, 64 KB at most, fits beside the stages)
+static bool use_few_rows(const BlockScaleProblem& prob)
+{
+    return prob.M <= 32 && prob.K <= 65536 && !few_rows_disabled();
+}
+
 void launch_blockscale(const BlockScaleProblem& prob)
 {
     if(prob.M == 0 && prob.N > 0 && prob.K > 0)
         return;
-    if(prob.scales_are_e8m0 && (prob.M > 32 || prob.cfg_given || few_rows_disabled()))
+    if(prob.scales_are_e8m0 && (prob.cfg_given || !use_few_rows(prob)))
     {
         // powers of two ride the block-scaled MMA; up to 32 rows stay on the few-rows kernel below, which reads the
         // e8m0 bytes itself (one launch, no scale expansion pass)
@@ -1054,7 +1060,7 @@ void launch_blockscale(const BlockScaleProblem& prob)
         lc.numAttrs = 1;
         B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_pair_kernel, ma, mb, prm));
     }
-    else if(prob.M <= 32 && !few_rows_disabled())
+    else if(use_few_rows(prob))
     {
         // few activation rows: weights on the M side of the MMA, activations on its N side
         const int xr          = prob.M <= 16 ? 16 : 32;
@@ -1095,11 +1101,12 @@ void launch_blockscale(const BlockScaleProblem& prob)
         grid.z     = static_cast<unsigned>(splits);
         const int per_slice  = (prm.k_blocks + splits - 1) / splits;
         const int red_bytes  = prm.cluster ? (splits - 1) * kBsTileN * xr * 4 : 0;
-        prm.stages           = std::max(2, std::min(std::min((st.smem_optin - 2048 - red_bytes) / stage_bytes, kMaxStages), per_slice));
-        const size_t smem    = static_cast<size_t>(stage_bytes) * prm.stages + red_bytes + 512 + 1024;
+        const int sc_bytes   = per_slice * xr * 4; // the slice's scale products
+        prm.stages           = std::max(2, std::min(std::min((st.smem_optin - 2048 - red_bytes - sc_bytes) / stage_bytes, kMaxStages), per_slice));
+        const size_t smem    = static_cast<size_t>(stage_bytes) * prm.stages + red_bytes + 512 + sc_bytes + 1024;
         cudaLaunchConfig_t lc{};
         lc.gridDim          = grid;
-        lc.blockDim         = dim3(kBlockScaleThreads, 1, 1);
+        lc.blockDim         = dim3(kFewRowsThreads, 1, 1);
         lc.dynamicSmemBytes = smem;
         lc.stream           = prob.stream;
         cudaLaunchAttribute attr[2];

@@ -296,7 +296,9 @@ def test_a8w4_table_dispatch(ab, tmp_path, monkeypatch):
                                        (128, 4096, 4096, False), (130, 320, 640, True), (1024, 2048, 512, False),
                                        # few rows (weights on the M side of the MMA), K split across CTAs, ragged N
                                        (16, 4096, 4096, False), (17, 1536, 7168, True), (33, 400, 2048, False), (64, 7168, 2048, True),
-                                       (5, 128, 896, False), (100, 1024, 4096, False)])
+                                       (5, 128, 896, False), (100, 1024, 4096, False),
+                                       # more K blocks per slice than TMEM partials and stages: both MMA issuers wrap their rings
+                                       (8, 4096, 8192, False), (24, 2048, 16384, True)])
 def test_a8w8_blockscale_fp32_scales(ab, M, N, K, bpre):
     g = torch.Generator().manual_seed(M + N + K)
     x = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn)
