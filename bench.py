@@ -234,22 +234,30 @@ def run_case(torch, ab, device, spec, steps, warmup):
 
 
 def run_sweep(torch, ab, device, peaks):
-    """Per-M device time of the other benchmark configurations (graph-replayed, rotating buffers)."""
-    rows = []
+    """Per-M device time of the other benchmark configurations (graph-replayed, rotating buffers).
+    The cases run in ascending order of work after a second of idle time, and are reported in the order they are
+    declared: right after a long tensor-bound case the GPU sits at its power cap (SM clock ~1.45 GHz instead of
+    1.97 GHz for some milliseconds), which would inflate the microsecond-sized decode cases by 10-30 %."""
+    import time
+
+    jobs = []  # (work, thunk returning the row)
 
     def rand_u8(lo, hi, *shape):
         return torch.randint(lo, hi, shape, dtype=torch.uint8, device=device)
 
     def add(kind, M, N, K, fn, make):
-        b = algorithmic_bytes(kind, M, N, K)
-        sets = rotating_sets(make, b)
-        us = graph_time_calls(torch, fn, sets, 20, 3)
-        tf = 2.0 * M * N * K / us / 1e6
-        gbs = b / us / 1e3
-        peak_tf = peaks["bf16"] * {"bf16": 1, "mxfp8": 2, "a8w4": 2, "mxfp4": 4}[kind]
-        rows.append({"kind": kind, "M": M, "N": N, "K": K, "us": round(us, 2), "tflops": round(tf, 1), "gbs": round(gbs, 1),
-                     "frac_tensor": round(tf / peak_tf, 4), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4),
-                     "kernel": kernel_in_use(ab, kind, M, N, K)})
+        def job():
+            b = algorithmic_bytes(kind, M, N, K)
+            sets = rotating_sets(make, b)
+            us = graph_time_calls(torch, fn, sets, 20, 3)
+            tf = 2.0 * M * N * K / us / 1e6
+            gbs = b / us / 1e3
+            peak_tf = peaks["bf16"] * {"bf16": 1, "mxfp8": 2, "a8w4": 2, "mxfp4": 4}[kind]
+            return {"kind": kind, "M": M, "N": N, "K": K, "us": round(us, 2), "tflops": round(tf, 1), "gbs": round(gbs, 1),
+                    "frac_tensor": round(tf / peak_tf, 4), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4),
+                    "kernel": kernel_in_use(ab, kind, M, N, K)}
+
+        jobs.append((2.0 * M * N * K, job))
 
     # bf16 a16w16 (the reference's CPU-runnable case)
     add("bf16", 64, 1024, 1024, lambda a, b: ab.tgemm.mm(a, b),
@@ -275,25 +283,36 @@ def run_sweep(torch, ab, device, peaks):
     for M in (16, 1024, 8192):
         for tag, mk in (("blockscale_fp32", lambda M: (torch.rand(M, 32, device=device) + 0.5, torch.rand(32, 32, device=device) + 0.5)),
                         ("blockscale_e8m0", lambda M: (rand_u8(124, 130, M, 32).view(ab.dtypes.fp8_e8m0), rand_u8(124, 130, 32, 32).view(ab.dtypes.fp8_e8m0)))):
-            sets = rotating_sets(lambda i, M=M, mk=mk: (rand_u8(0, 0x78, M, 4096).view(torch.float8_e4m3fn),
-                                                        rand_u8(0, 0x78, 4096, 4096).view(torch.float8_e4m3fn), *mk(M)),
-                                 algorithmic_bytes("mxfp8", M, 4096, 4096))
-            us = graph_time_calls(torch, lambda a, b, xs, ws: ab.gemm_a8w8_blockscale(a, b, xs, ws), sets, 20, 3)
-            tf = 2.0 * M * 4096 * 4096 / us / 1e6
-            rows.append({"kind": tag, "M": M, "N": 4096, "K": 4096, "us": round(us, 2), "tflops": round(tf, 1),
-                         "gbs": round(algorithmic_bytes("mxfp8", M, 4096, 4096) / us / 1e3, 1), "frac_tensor": round(tf / (2 * peaks["bf16"]), 4),
-                         "frac_hbm": round(algorithmic_bytes("mxfp8", M, 4096, 4096) / us / 1e3 / peaks["hbm_gbs"], 4),
-                         "kernel": "gemm_a8w8_blockscale" + ("_fewrows_kernel" if M <= 32 else "_pair_kernel" if tag.endswith("fp32") and M > 128
-                                                             else "_kernel" if tag.endswith("fp32") else " -> mxfp8")})
+            def job(M=M, tag=tag, mk=mk):
+                sets = rotating_sets(lambda i: (rand_u8(0, 0x78, M, 4096).view(torch.float8_e4m3fn),
+                                                rand_u8(0, 0x78, 4096, 4096).view(torch.float8_e4m3fn), *mk(M)),
+                                     algorithmic_bytes("mxfp8", M, 4096, 4096))
+                us = graph_time_calls(torch, lambda a, b, xs, ws: ab.gemm_a8w8_blockscale(a, b, xs, ws), sets, 20, 3)
+                tf = 2.0 * M * 4096 * 4096 / us / 1e6
+                return {"kind": tag, "M": M, "N": 4096, "K": 4096, "us": round(us, 2), "tflops": round(tf, 1),
+                        "gbs": round(algorithmic_bytes("mxfp8", M, 4096, 4096) / us / 1e3, 1), "frac_tensor": round(tf / (2 * peaks["bf16"]), 4),
+                        "frac_hbm": round(algorithmic_bytes("mxfp8", M, 4096, 4096) / us / 1e3 / peaks["hbm_gbs"], 4),
+                        "kernel": "gemm_a8w8_blockscale" + ("_fewrows_kernel" if M <= 32 else "_pair_kernel" if tag.endswith("fp32") and M > 128
+                                                            else "_kernel" if tag.endswith("fp32") else " -> mxfp8")}
+
+            jobs.append((2.0 * M * 4096 * 4096, job))
     # fused activation quantiser (bf16 -> MX data + scales in the GEMM's layout): HBM-bound
     for (kind, M, K, kw) in (("quant_mxfp4", 16384, 16384, dict(quant_dtype=ab.dtypes.fp4x2, shuffle=True)),
                              ("quant_mxfp8", 8192, 4096, dict(quant_dtype=ab.dtypes.fp8, scale_type=ab.dtypes.fp8_e8m0, shuffle=2)),
                              ("quant_mxfp4", 32, 16384, dict(quant_dtype=ab.dtypes.fp4x2, shuffle=True))):
-        b = int(M * K * 2 + M * K * (0.5 if kind == "quant_mxfp4" else 1.0) + M * K / 32)
-        sets = rotating_sets(lambda i, M=M, K=K: (torch.randn(M, K, device=device).to(torch.bfloat16),), M * K * 2)
-        us = graph_time_calls(torch, lambda x, kw=kw: ab.per_1x32_mx_quant_hip(x, **kw), sets, 20, 3)
-        rows.append({"kind": kind, "M": M, "N": 0, "K": K, "us": round(us, 2), "tflops": 0.0, "gbs": round(b / us / 1e3, 1),
-                     "frac_tensor": 0.0, "frac_hbm": round(b / us / 1e3 / peaks["hbm_gbs"], 4), "kernel": "quant_mx_kernel"})
+        def job(kind=kind, M=M, K=K, kw=kw):
+            b = int(M * K * 2 + M * K * (0.5 if kind == "quant_mxfp4" else 1.0) + M * K / 32)
+            sets = rotating_sets(lambda i: (torch.randn(M, K, device=device).to(torch.bfloat16),), M * K * 2)
+            us = graph_time_calls(torch, lambda x: ab.per_1x32_mx_quant_hip(x, **kw), sets, 20, 3)
+            return {"kind": kind, "M": M, "N": 0, "K": K, "us": round(us, 2), "tflops": 0.0, "gbs": round(b / us / 1e3, 1),
+                    "frac_tensor": 0.0, "frac_hbm": round(b / us / 1e3 / peaks["hbm_gbs"], 4), "kernel": "quant_mx_kernel"}
+
+        jobs.append((float(M) * K, job))  # memory-bound: sorts among the small cases
+    torch.cuda.synchronize()
+    time.sleep(1.0)
+    rows = [None] * len(jobs)
+    for idx in sorted(range(len(jobs)), key=lambda i: jobs[i][0]):
+        rows[idx] = jobs[idx][1]()
     return rows
 
 
