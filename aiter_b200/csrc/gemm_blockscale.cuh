@@ -316,8 +316,8 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 // the TMEM partial is XR columns wide and a promotion thread (= one output COLUMN n) folds XR values per K block
 // with x_scale[m][kb] * w_scale[n/128][kb]; 8 TMEM partials are in flight, so the round trip
 // MMA -> commit -> promotion -> release is paid once per 8 K blocks, not per 2.  gridDim.z slices of K meet either
-// in the reducing CTA's shared memory (the slices form one thread-block cluster and send their fp32 tiles with
-// st.async) or in the fp32 workspace like in the kernel above.  Warps (224 threads): 0 TMA producer, 1 and 6 MMA issuers (1 owns TMEM), 2..5 promotion + store.
+// in shared memory (the slices form one thread-block cluster; every CTA reduces its share of the tile's columns
+// and receives the other slices' partial sums of them by st.async) or in the fp32 workspace like in the kernel above.  Warps (224 threads): 0 TMA producer, 1 and 6 MMA issuers (1 owns TMEM), 2..5 promotion + store.
 template <int XR>
 __global__ void __launch_bounds__(kFewRowsThreads, 1)
 gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -335,7 +335,9 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
     constexpr uint32_t kSliceBytes = kBsTileN * XR * 4u;             // one CTA's fp32 tile
     // stages | the other slices' tiles (cluster split: written by those CTAs) | barriers and flags
     const uint32_t red_off   = kStageBytes * S;
-    const uint32_t bar_off   = red_off + (prm.cluster ? static_cast<uint32_t>(prm.splits - 1) * kSliceBytes : 0u);
+    // cluster split: every CTA reduces kBsTileN / splits of the tile's columns and receives the other slices' values of them
+    const uint32_t red_bytes = prm.cluster ? static_cast<uint32_t>(prm.splits - 1) * (kSliceBytes / static_cast<uint32_t>(prm.splits)) : 0u;
+    const uint32_t bar_off   = red_off + red_bytes;
     const uint32_t bar_base  = smem_base + bar_off;
     auto full_bar       = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar      = [&](int s) { return bar_base + 64u + 8u * s; };
@@ -347,7 +349,7 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
     volatile uint32_t* abort_f = reinterpret_cast<volatile uint32_t*>(smem_gen + bar_off + 276);
     unsigned int* ticket       = reinterpret_cast<unsigned int*>(smem_gen + bar_off + 280);
     float* sc_tab              = reinterpret_cast<float*>(smem_gen + bar_off + 512); // [K block of this slice][XR] scale products
-    const uint32_t zrank       = prm.cluster ? cluster_ctarank() : blockIdx.z; // K slice; 0 reduces a cluster-split tile
+    const uint32_t zrank       = prm.cluster ? cluster_ctarank() : blockIdx.z; // K slice
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int col0 = blockIdx.x * kBsTileN;
     const int kb0  = static_cast<int>(static_cast<long long>(prm.k_blocks) * zrank / prm.splits);
@@ -483,8 +485,8 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
         for(int i = 0; i < XR; ++i)
             acc[i] = 0.f;
         bool ok = true;
-        if(prm.cluster && zrank == 0 && threadIdx.x == 64)
-            mbar_arrive_expect_tx(red_bar, static_cast<uint32_t>(prm.splits - 1) * kSliceBytes);
+        if(prm.cluster && threadIdx.x == 64)
+            mbar_arrive_expect_tx(red_bar, red_bytes);
         // x_scale[m][kb] * w_scale[n/128][kb] of this slice goes to shared memory once (while the first loads are in
         // flight); the K loop then reads four products per broadcast load instead of assembling XR global addresses
         // per K block, which a warp that has its scheduler to itself pays instruction by instruction
@@ -530,34 +532,41 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
             if(lane == 0)
                 mbar_arrive(part_empty_bar(b));
         }
+        bool owns = true; // this thread stores its output column
         if(ok && prm.cluster)
         {
-            if(zrank != 0)
+            // Cluster split, reduce-scatter: CTA z adds up columns [z * per, (z + 1) * per) of the tile (per = 128 /
+            // splits).  A thread whose column belongs to another CTA sends its XR partial sums to that CTA's shared
+            // memory ([source slice][column][m] floats; the bytes are counted on that CTA's barrier, nothing is waited
+            // for); a thread that owns its column waits for the other slices' values, adds them in rank order and stores.
+            const uint32_t per   = static_cast<uint32_t>(kBsTileN) / static_cast<uint32_t>(prm.splits);
+            const uint32_t owner = static_cast<uint32_t>(r_local) / per;
+            const uint32_t col   = static_cast<uint32_t>(r_local) - owner * per;
+            owns                 = (owner == zrank);
+            if(!owns)
             {
-                // cluster split: this slice goes to the reducing CTA's shared memory ([slice][n][m] floats); the bytes
-                // are counted on its barrier and nothing is waited for here
-                const uint32_t dst = map_to_cta(smem_base + red_off, 0) + ((zrank - 1u) * kBsTileN + static_cast<uint32_t>(r_local)) * (XR * 4u);
-                const uint32_t dst_bar = map_to_cta(red_bar, 0);
+                const uint32_t slot    = zrank < owner ? zrank : zrank - 1u; // this slice's place among the owner's sources
+                const uint32_t dst     = map_to_cta(smem_base + red_off, owner) + (slot * per + col) * (XR * 4u);
+                const uint32_t dst_bar = map_to_cta(red_bar, owner);
 #pragma unroll
                 for(int i = 0; i < XR; i += 4)
                     st_async_v4(dst + i * 4u, __float_as_uint(acc[i]), __float_as_uint(acc[i + 1]), __float_as_uint(acc[i + 2]),
                                 __float_as_uint(acc[i + 3]), dst_bar);
-                ok = false; // nothing to store from here
             }
-            else
+            if(__any_sync(0xffffffffu, owns)) // (a warp may hold columns of two owners when per < 32)
             {
                 ok = bounded_wait(red_bar, 0, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, 0x3000);
                 ok = __all_sync(0xffffffffu, ok);
-                if(ok)
+                if(ok && owns)
                 {
                     const float4* red = reinterpret_cast<const float4*>(smem_gen + red_off);
-                    for(int z = 0; z < prm.splits - 1; ++z)
+                    for(uint32_t z = 0; z + 1 < static_cast<uint32_t>(prm.splits); ++z)
                     {
-                        const float4* mine = red + static_cast<size_t>(z * kBsTileN + r_local) * (XR / 4);
+                        const float4* src = red + static_cast<size_t>(z * per + col) * (XR / 4);
 #pragma unroll
                         for(int i = 0; i < XR; i += 4)
                         {
-                            const float4 t = mine[i / 4];
+                            const float4 t = src[i / 4];
                             acc[i] += t.x;
                             acc[i + 1] += t.y;
                             acc[i + 2] += t.z;
@@ -615,7 +624,7 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
                     prm.ws_counter[tile] = 0; // ready for the next launch
             }
         }
-        if(ok && n < prm.N)
+        if(ok && owns && n < prm.N)
         {
 #pragma unroll
             for(int i = 0; i < XR; ++i)

@@ -1100,7 +1100,7 @@ void launch_blockscale(const BlockScaleProblem& prob)
         prm.splits = splits;
         grid.z     = static_cast<unsigned>(splits);
         const int per_slice  = (prm.k_blocks + splits - 1) / splits;
-        const int red_bytes  = prm.cluster ? (splits - 1) * kBsTileN * xr * 4 : 0;
+        const int red_bytes  = prm.cluster ? (splits - 1) * (kBsTileN / splits) * xr * 4 : 0; // the other slices' share of this CTA's columns
         const int sc_bytes   = per_slice * xr * 4; // the slice's scale products
         prm.stages           = std::max(2, std::min(std::min((st.smem_optin - 2048 - red_bytes - sc_bytes) / stage_bytes, kMaxStages), per_slice));
         const size_t smem    = static_cast<size_t>(stage_bytes) * prm.stages + red_bytes + 512 + sc_bytes + 1024;
