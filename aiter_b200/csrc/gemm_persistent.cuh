@@ -777,13 +777,22 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                 }
             };
 
-            if(csplit > 1 && zrank != 0)
+            // Cluster-split tile.  Up to 4 slices: reduce-scatter, CTA z adds up and stores rows [z * per, (z + 1) * per)
+            // of the tile (per = 128 / csplit: whole epilogue warps) and receives the other slices' partial sums of
+            // them; 8 slices: the first CTA reduces the whole tile.  A warp whose rows belong to another CTA sends its
+            // partial accumulator to that CTA's shared memory ([source slice][row][bn floats]); the bytes are counted on
+            // that CTA's red barrier and nothing is waited for.
+            const bool scatter    = csplit > 1 && csplit <= 4;
+            const uint32_t per    = scatter ? static_cast<uint32_t>(kTileP / csplit) : static_cast<uint32_t>(kTileP);
+            const uint32_t owner  = scatter ? static_cast<uint32_t>(p_local) / per : 0u;
+            const uint32_t prow   = static_cast<uint32_t>(p_local) - owner * per;
+            if(csplit > 1 && warp == 6 && lane == 0 && (scatter || zrank == 0))
+                mbar_arrive_expect_tx(red_bar, static_cast<uint32_t>(csplit - 1) * per * static_cast<uint32_t>(bn) * 4u);
+            if(csplit > 1 && zrank != owner)
             {
-                // K slice of a cluster-split tile: send this CTA's partial accumulator to the reducing CTA's shared
-                // memory ([slice][row][bn floats]); the bytes are counted on its red barrier, nothing is waited for
-                const uint32_t dst_row = map_to_cta(smem_base + L.red_off, 0) +
-                                         ((zrank - 1u) * kTileP + static_cast<uint32_t>(p_local)) * static_cast<uint32_t>(bn) * 4u;
-                const uint32_t dst_bar = map_to_cta(red_bar, 0);
+                const uint32_t src    = zrank < owner ? zrank : zrank - 1u; // this slice's place among the owner's sources
+                const uint32_t dst_row = map_to_cta(smem_base + L.red_off, owner) + (src * per + prow) * static_cast<uint32_t>(bn) * 4u;
+                const uint32_t dst_bar = map_to_cta(red_bar, owner);
                 for(int c = 0; c < n_chunks; ++c)
                 {
                     uint32_t r[32];
@@ -799,12 +808,6 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                 }
                 release_acc();
                 continue;
-            }
-            if(csplit > 1)
-            {
-                // reducing CTA: expect the other slices' bytes for this tile
-                if(warp == 6 && lane == 0)
-                    mbar_arrive_expect_tx(red_bar, static_cast<uint32_t>(csplit - 1) * static_cast<uint32_t>(bn) * kTileP * 4u);
             }
 
             if(split)
@@ -1022,7 +1025,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                             const float4* red = reinterpret_cast<const float4*>(smem_gen + L.red_off);
                             for(int z = 0; z < csplit - 1; ++z)
                             {
-                                const float4* row = red + (static_cast<size_t>(z * kTileP + p_local) * bn + c * chunk) / 4;
+                                const float4* row = red + (static_cast<size_t>(z * per + prow) * bn + c * chunk) / 4;
 #pragma unroll
                                 for(int j = 0; j < 32; j += 4)
                                     if(j < chunk)
