@@ -55,6 +55,7 @@ struct PersistentParams
     int sf_tmem_base;             // first TMEM column of the per-stage scale buffers
     int sf_cols;                  // TMEM columns per stage for scales
     int csplit;                   // K split across the CTAs of a thread-block cluster (1 = none; CG == 1 only, one tile per cluster)
+    int split_shift;              // log2 of the K split in use (csplit if > 1, else splits) when it is a power of two, else -1
     int tma_store;                // the output goes through shared memory and TMA tile stores (map_out is valid)
     int tmem_cols;                // allocation (power of two)
     // block scales in global memory (wire layout), one "group" = 32 rows; a group row is `sf_row_words` words
@@ -257,14 +258,47 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
         w.valid = w.u < total_units;
         if(!w.valid)
             return;
+        // Every role decodes its first unit before it can start, one thread paying each instruction's latency: the
+        // usual cases (power-of-two K split, a single Q tile) take shifts instead of ~150-cycle integer divisions.
         const int ksplit = (csplit > 1) ? csplit : splits;
-        w.z            = (csplit > 1) ? static_cast<int>(zrank) : w.u % splits;
-        const int tile = (csplit > 1) ? w.u : w.u / splits;
-        w.tq           = tile % prm.tiles_q;
-        w.tp           = tile / prm.tiles_q;
-        // num_k_iters * splits < 2^31 (checked on the host): 32-bit divisions keep this off the critical path
-        w.it_beg       = static_cast<int>(static_cast<uint32_t>(prm.num_k_iters * w.z) / static_cast<uint32_t>(ksplit));
-        w.n_iters      = static_cast<int>(static_cast<uint32_t>(prm.num_k_iters * (w.z + 1)) / static_cast<uint32_t>(ksplit)) - w.it_beg;
+        const int sh     = prm.split_shift;
+        int tile;
+        if(csplit > 1)
+        {
+            w.z  = static_cast<int>(zrank);
+            tile = w.u;
+        }
+        else if(sh >= 0)
+        {
+            w.z  = w.u & (splits - 1);
+            tile = w.u >> sh;
+        }
+        else
+        {
+            w.z  = w.u % splits;
+            tile = w.u / splits;
+        }
+        if(prm.tiles_q == 1)
+        {
+            w.tq = 0;
+            w.tp = tile;
+        }
+        else
+        {
+            w.tq = tile % prm.tiles_q;
+            w.tp = tile / prm.tiles_q;
+        }
+        // num_k_iters * splits < 2^31 (checked on the host)
+        if(sh >= 0)
+        {
+            w.it_beg  = (prm.num_k_iters * w.z) >> sh;
+            w.n_iters = ((prm.num_k_iters * (w.z + 1)) >> sh) - w.it_beg;
+        }
+        else
+        {
+            w.it_beg  = static_cast<int>(static_cast<uint32_t>(prm.num_k_iters * w.z) / static_cast<uint32_t>(ksplit));
+            w.n_iters = static_cast<int>(static_cast<uint32_t>(prm.num_k_iters * (w.z + 1)) / static_cast<uint32_t>(ksplit)) - w.it_beg;
+        }
         w.i            = 0;
     };
     auto first_work = [&]() {

@@ -843,6 +843,13 @@ static void launch_gemm_locked(const GemmProblem& prob)
     prm.acc_stride = (cfg.bn + 31) & ~31;
     prm.sf_cols    = sf_cols;
     prm.csplit            = csplit;
+    {
+        const int ksplit = csplit > 1 ? csplit : splits;
+        int sh           = 0;
+        while((1 << sh) < ksplit)
+            ++sh;
+        prm.split_shift = ((1 << sh) == ksplit) ? sh : -1;
+    }
     const long long units = static_cast<long long>(tiles_p) * tiles_q * splits;
     // a cluster-split tile owns its cluster for the whole launch: one cluster per tile, however many run at once
     const int clusters    = csplit > 1 ? static_cast<int>(units) : static_cast<int>(std::min<long long>(units, st.sm_count / cg));
