@@ -311,8 +311,8 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 
 
 // ---------------------------------------------------------------------------------------------------------
-// Few activation rows (M <= 32): the operands trade places.  128 weight rows are the M side of the MMA and the
-// XR (16/32) activation rows its N side, so a K block costs 16 KB + XR * 128 B of staging instead of 32 KB,
+// Few activation rows (M <= 64): the operands trade places.  128 weight rows are the M side of the MMA and the
+// XR (16/32/64) activation rows its N side, so a K block costs 16 KB + XR * 128 B of staging instead of 32 KB,
 // the TMEM partial is XR columns wide and a promotion thread (= one output COLUMN n) folds XR values per K block
 // with x_scale[m][kb] * w_scale[n/128][kb]; 8 TMEM partials are in flight, so the round trip
 // MMA -> commit -> promotion -> release is paid once per 8 K blocks, not per 2.  gridDim.z slices of K meet either
@@ -330,7 +330,7 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
     constexpr uint32_t kWBytes     = kBsTileN * kTileKBytes;         // 16 KB of weights
     constexpr uint32_t kStageBytes = kWBytes + XR * kTileKBytes;     // + the activation rows
     constexpr int NP               = 8;                              // TMEM partials in flight
-    static_assert(XR == 16 || XR == 32, "activation rows per tile");
+    static_assert(XR == 16 || XR == 32 || XR == 64, "activation rows per tile");
     constexpr uint32_t kTmemCols   = NP * XR;
     constexpr uint32_t kSliceBytes = kBsTileN * XR * 4u;             // one CTA's fp32 tile
     // stages | the other slices' tiles (cluster split: written by those CTAs) | barriers and flags

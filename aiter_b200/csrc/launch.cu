@@ -987,10 +987,10 @@ static bool few_rows_disabled()
     return off;
 }
 
-// up to 32 activation rows (and a K whose unsplit scale table, 64 KB at most, fits beside the stages)
+// up to 64 activation rows (and a K whose unsplit scale table, 64 KB at most, fits beside the stages)
 static bool use_few_rows(const BlockScaleProblem& prob)
 {
-    return prob.M <= 32 && prob.K <= 65536 && !few_rows_disabled();
+    return prob.M <= 64 && prob.K <= 32768 && !few_rows_disabled();
 }
 
 void launch_blockscale(const BlockScaleProblem& prob)
@@ -999,7 +999,7 @@ void launch_blockscale(const BlockScaleProblem& prob)
         return;
     if(prob.scales_are_e8m0 && (prob.cfg_given || !use_few_rows(prob)))
     {
-        // powers of two ride the block-scaled MMA; up to 32 rows stay on the few-rows kernel below, which reads the
+        // powers of two ride the block-scaled MMA; up to 64 rows stay on the few-rows kernel below, which reads the
         // e8m0 bytes itself (one launch, no scale expansion pass)
         B200_CHECK(prob.K % 128 == 0, "K must be a multiple of 128 for 128-wide scale blocks (got ", prob.K, ")");
         launch_blockscale_e8m0(prob);
@@ -1070,7 +1070,7 @@ void launch_blockscale(const BlockScaleProblem& prob)
     else if(use_few_rows(prob))
     {
         // few activation rows: weights on the M side of the MMA, activations on its N side
-        const int xr          = prob.M <= 16 ? 16 : 32;
+        const int xr          = prob.M <= 16 ? 16 : (prob.M <= 32 ? 32 : 64);
         const int stage_bytes = (kBsTileN + xr) * kTileKBytes;
         CUtensorMap ma = operand_map(prob.act, xr, "activation operand");
         CUtensorMap mb = operand_map(prob.wgt, kBsTileN, "weight operand");
@@ -1079,7 +1079,7 @@ void launch_blockscale(const BlockScaleProblem& prob)
         // slices of 16 or 32 rows form one cluster and meet in shared memory, the rest goes through the workspace
         static const bool no_split   = (std::getenv("AITER_B200_NO_BLOCKSCALE_SPLIT") != nullptr);
         static const bool no_cluster = (std::getenv("AITER_B200_NO_CLUSTER_SPLIT") != nullptr);
-        const bool may_cluster       = !no_cluster && xr <= 32;
+        const bool may_cluster       = !no_cluster;
         int splits = 1;
         while(!no_split && splits < (may_cluster ? 8 : 16) && static_cast<long long>(grid.x) * (splits * 2) <= st.sm_count &&
               prm.k_blocks / (splits * 2) >= 2)
@@ -1125,16 +1125,21 @@ void launch_blockscale(const BlockScaleProblem& prob)
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         lc.attrs    = attr;
         lc.numAttrs = pdl_disabled() ? 1 : 2;
-        static bool attr_done[2][64] = {};
+        static bool attr_done[3][64] = {};
         if(xr == 16)
         {
             raise_smem_limit(gemm_a8w8_blockscale_fewrows_kernel<16>, attr_done[0]);
             B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_fewrows_kernel<16>, ma, mb, prm));
         }
-        else
+        else if(xr == 32)
         {
             raise_smem_limit(gemm_a8w8_blockscale_fewrows_kernel<32>, attr_done[1]);
             B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_fewrows_kernel<32>, ma, mb, prm));
+        }
+        else
+        {
+            raise_smem_limit(gemm_a8w8_blockscale_fewrows_kernel<64>, attr_done[2]);
+            B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_fewrows_kernel<64>, ma, mb, prm));
         }
         B200_CUDA(cudaGetLastError());
     }

@@ -114,7 +114,7 @@ struct BlockScaleProblem
     long long xs_stride_m = 0, xs_stride_k = 0;
     const float* w_scale = nullptr;
     // both scale tensors hold UE8M0 bytes instead of floats (same shapes and strides, in bytes): powers of two ride
-    // the block-scaled MMA, so the problem runs on the MXFP8 kernel after a small expansion of the scales (up to 32
+    // the block-scaled MMA, so the problem runs on the MXFP8 kernel after a small expansion of the scales (up to 64
     // rows without a caller-chosen configuration: on the few-rows kernel, which reads the bytes itself)
     bool scales_are_e8m0 = false;
     KernelConfig cfg;             // e8m0 path only: a caller-chosen MXFP8 kernel configuration (unset fields: heuristic)

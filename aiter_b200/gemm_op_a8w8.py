@@ -19,8 +19,8 @@ def get_CKGEMM_config(M: int, N: int, K: int, bpreshuffle: bool = False):
 
 def _mxfp8_kernel_for(m: int, n: int, k: int) -> str:
     """e8m0-scaled blockscale problems run on the MXFP8 kernels: their tuned table names the configuration.
-    Up to 32 rows no name is passed on: the library's few-rows blockscale kernel reads the e8m0 bytes itself."""
-    if m <= 32:
+    Up to 64 rows no name is passed on: the library's few-rows blockscale kernel reads the e8m0 bytes itself."""
+    if m <= 64:
         return ""
     row = _mxfp8_table.lookup(m, n, k)
     return str(row.get("kernelName") or "") if row is not None else ""

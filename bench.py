@@ -226,7 +226,7 @@ def run_case(torch, ab, device, spec, steps, warmup):
     if kind.startswith("quant"):
         kernel = "quant_mx_kernel"
     elif kind.startswith("blockscale"):
-        kernel = "gemm_a8w8_blockscale" + ("_fewrows_kernel" if M <= 32 else " -> mxfp8" if kind.endswith("e8m0")
+        kernel = "gemm_a8w8_blockscale" + ("_fewrows_kernel" if M <= 64 else " -> mxfp8" if kind.endswith("e8m0")
                                            else "_pair_kernel" if M > 128 else "_kernel")
     else:
         kernel = kernel_in_use(ab, kind, M, N, K)
@@ -292,7 +292,7 @@ def run_sweep(torch, ab, device, peaks):
                 return {"kind": tag, "M": M, "N": 4096, "K": 4096, "us": round(us, 2), "tflops": round(tf, 1),
                         "gbs": round(algorithmic_bytes("mxfp8", M, 4096, 4096) / us / 1e3, 1), "frac_tensor": round(tf / (2 * peaks["bf16"]), 4),
                         "frac_hbm": round(algorithmic_bytes("mxfp8", M, 4096, 4096) / us / 1e3 / peaks["hbm_gbs"], 4),
-                        "kernel": "gemm_a8w8_blockscale" + ("_fewrows_kernel" if M <= 32 else "_pair_kernel" if tag.endswith("fp32") and M > 128
+                        "kernel": "gemm_a8w8_blockscale" + ("_fewrows_kernel" if M <= 64 else "_pair_kernel" if tag.endswith("fp32") and M > 128
                                                             else "_kernel" if tag.endswith("fp32") else " -> mxfp8")}
 
             jobs.append((2.0 * M * 4096 * 4096, job))
