@@ -50,22 +50,25 @@ __device__ __forceinline__ float to_f32<__half>(__half v)
     return __half2float(v);
 }
 
-template <typename T, bool FP4>
+// SMALL (few tiles, e.g. a decode batch): the eight warps of a CTA share ONE tile, four rows each, so that every load
+// of the tile is in flight at once and the kernel lasts about one memory round trip instead of eight.
+template <typename T, bool FP4, bool SMALL>
 __global__ void __launch_bounds__(256) quant_mx_kernel(const QuantParams prm)
 {
-    __shared__ __align__(16) uint8_t sf_tile[8][256];
+    __shared__ __align__(16) uint8_t sf_tile[SMALL ? 1 : 8][256];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_tiles       = (prm.kblocks + 7) / 8;
     const long long m_tiles = (prm.M + 31) / 32;
-    const long long tile    = static_cast<long long>(blockIdx.x) * 8 + warp;
+    const long long tile    = SMALL ? static_cast<long long>(blockIdx.x) : static_cast<long long>(blockIdx.x) * 8 + warp;
     if(tile >= m_tiles * k_tiles)
-        return;
+        return; // (SMALL: the grid has exactly one CTA per tile, nobody leaves before the barrier below)
     const long long tm = tile / k_tiles;
     const int tk       = static_cast<int>(tile % k_tiles);
     const int blk      = tk * 8 + (lane >> 2);        // this lane's 32-block along K
     const bool blk_ok  = blk < prm.kblocks;
     const float max_pos = FP4 ? 6.0f : 448.0f;
-    uint8_t* sf = sf_tile[warp];
+    uint8_t* sf = sf_tile[SMALL ? 0 : warp];
+    const int r_begin = SMALL ? warp * 4 : 0, r_end = SMALL ? warp * 4 + 4 : 32;
     const T* in = static_cast<const T*>(prm.in);
 
     // Rows go through in groups of four; the next group's loads are issued before the current group is converted, so
@@ -81,15 +84,15 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const QuantParams prm)
     uint4 next[4];
 #pragma unroll
     for(int i = 0; i < 4; ++i)
-        next[i] = load_row(i);
+        next[i] = load_row(r_begin + i);
 #pragma unroll 1
-    for(int r0 = 0; r0 < 32; r0 += 4)
+    for(int r0 = r_begin; r0 < r_end; r0 += 4)
     {
         uint4 cur[4];
 #pragma unroll
         for(int i = 0; i < 4; ++i)
             cur[i] = next[i];
-        if(r0 + 4 < 32)
+        if(r0 + 4 < r_end)
         {
 #pragma unroll
             for(int i = 0; i < 4; ++i)
@@ -171,7 +174,14 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const QuantParams prm)
             }
         }
     }
-    __syncwarp();
+    if(SMALL)
+    {
+        __syncthreads();
+        if(warp != 0)
+            return;
+    }
+    else
+        __syncwarp();
     if(prm.layout == QSL_E8M0_SHUFFLE)
     {
         // chunk of (row group tm, K tile tk): byte offset (tm * scale_cols) * 32 + tk * 256
@@ -204,15 +214,29 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const QuantParams prm)
 inline void launch_quant_mx(const QuantParams& prm, bool fp4, bool input_is_bf16, cudaStream_t stream)
 {
     const long long tiles = ((prm.M + 31) / 32) * ((prm.kblocks + 7) / 8);
+    if(tiles <= 2048)
+    {
+        // few tiles: one CTA per tile
+        const unsigned blocks = static_cast<unsigned>(tiles);
+        if(fp4 && input_is_bf16)
+            quant_mx_kernel<__nv_bfloat16, true, true><<<blocks, 256, 0, stream>>>(prm);
+        else if(fp4)
+            quant_mx_kernel<__half, true, true><<<blocks, 256, 0, stream>>>(prm);
+        else if(input_is_bf16)
+            quant_mx_kernel<__nv_bfloat16, false, true><<<blocks, 256, 0, stream>>>(prm);
+        else
+            quant_mx_kernel<__half, false, true><<<blocks, 256, 0, stream>>>(prm);
+        return;
+    }
     const unsigned blocks = static_cast<unsigned>((tiles + 7) / 8);
     if(fp4 && input_is_bf16)
-        quant_mx_kernel<__nv_bfloat16, true><<<blocks, 256, 0, stream>>>(prm);
+        quant_mx_kernel<__nv_bfloat16, true, false><<<blocks, 256, 0, stream>>>(prm);
     else if(fp4)
-        quant_mx_kernel<__half, true><<<blocks, 256, 0, stream>>>(prm);
+        quant_mx_kernel<__half, true, false><<<blocks, 256, 0, stream>>>(prm);
     else if(input_is_bf16)
-        quant_mx_kernel<__nv_bfloat16, false><<<blocks, 256, 0, stream>>>(prm);
+        quant_mx_kernel<__nv_bfloat16, false, false><<<blocks, 256, 0, stream>>>(prm);
     else
-        quant_mx_kernel<__half, false><<<blocks, 256, 0, stream>>>(prm);
+        quant_mx_kernel<__half, false, false><<<blocks, 256, 0, stream>>>(prm);
 }
 
 } // namespace b200

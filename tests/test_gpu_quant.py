@@ -34,7 +34,8 @@ def unshuffle_e8m0(s, M, KB):
     return s.reshape(-1)[ox.e8m0_shuffle_offset(mm, kk, s.shape[1])]
 
 
-@pytest.mark.parametrize("M,K", [(1, 32), (33, 320), (300, 1024), (256, 4096), (17, 7168)])
+# (2080 x 8192 is more than 2048 tiles: the warp-per-tile kernel; the others run one CTA per tile)
+@pytest.mark.parametrize("M,K", [(1, 32), (33, 320), (300, 1024), (256, 4096), (17, 7168), (2080, 8192)])
 @pytest.mark.parametrize("kind", ["randn", "edges"])
 def test_quant_mxfp4_bit_exact(ab, M, K, kind):
     x = bf16_input(M, K, seed=M + K, kind=kind)
@@ -52,7 +53,7 @@ def test_quant_mxfp4_bit_exact(ab, M, K, kind):
         assert np.array_equal(got, ref_s), f"scale bytes differ (shuffle={shuffle})"
 
 
-@pytest.mark.parametrize("M,K", [(1, 128), (33, 384), (300, 1024), (64, 4096)])
+@pytest.mark.parametrize("M,K", [(1, 128), (33, 384), (300, 1024), (64, 4096), (4100, 4096)])
 @pytest.mark.parametrize("kind", ["randn", "edges"])
 def test_quant_mxfp8_bit_exact(ab, M, K, kind):
     x = bf16_input(M, K, seed=7 * M + K, kind=kind)
