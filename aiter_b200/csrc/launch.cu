@@ -1037,7 +1037,10 @@ void launch_blockscale(const BlockScaleProblem& prob)
     prm.ldo         = prob.ldo;
     prm.status      = st.status;
     prm.scales_e8m0 = prob.scales_are_e8m0 ? 1 : 0;
-    if(prob.M > kTileP)
+    // 256 x 256 tiles on CTA pairs once the 128 x 128 tiles no longer fit one wave: below that the single-CTA kernel
+    // keeps more SMs busy (M = 300, N = K = 4096: 96 CTAs and 17.6 us against 32 pairs and 29.6 us)
+    const long long tiles128 = ((prob.M + kTileP - 1) / kTileP) * ((prob.N + kBsTileN - 1) / kBsTileN);
+    if(prob.M > kTileP && tiles128 > st.sm_count)
     {
         // 256 x 256 tiles on CTA pairs
         const int stage_bytes = 2 * kTileP * kTileKBytes;

@@ -294,6 +294,8 @@ def test_a8w4_table_dispatch(ab, tmp_path, monkeypatch):
 # ------------------------------------------------------------------------------------------- fp8, fp32 128-block scales
 @pytest.mark.parametrize("M,N,K,bpre", [(1, 128, 128, False), (48, 512, 1024, False), (48, 512, 1024, True), (300, 1024, 2048, True),
                                        (128, 4096, 4096, False), (130, 320, 640, True), (1024, 2048, 512, False),
+                                       # more 128x128 tiles than SMs: the 256x256 CTA-pair kernel (ragged M and N)
+                                       (640, 4096, 512, False), (1300, 2304, 640, True),
                                        # few rows (weights on the M side of the MMA), K split across CTAs, ragged N
                                        (16, 4096, 4096, False), (17, 1536, 7168, True), (33, 400, 2048, False), (64, 7168, 2048, True),
                                        (5, 128, 896, False), (100, 1024, 4096, False),
