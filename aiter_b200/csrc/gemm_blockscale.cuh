@@ -4,18 +4,18 @@
 //   out[m][n] = sum_kb  xs[m][kb] * ws[n/128][kb] * sum_{k in block kb} A[m][k] * B[n][k]
 //
 // fp32 scales cannot ride the block-scaled MMA (its scales are powers of two), so every K block is
-// multiplied unscaled (tcgen05.mma kind::f8f6f4, 4 instructions of K = 32) into one of two TMEM partial
+// multiplied unscaled (tcgen05.mma kind::f8f6f4, 4 instructions of K = 32) into one of four TMEM partial
 // accumulators, and the 128 epilogue threads (one output row each) promote the finished partial into fp32
 // register accumulators with the two scales applied, while the tensor core fills the other partial.
 //
-// One 128x128 output tile per CTA.  Warps (192 threads): 0 TMA producer, 1 MMA issuer + TMEM owner,
-// 2..5 promotion + store.  Every barrier wait is bounded (see bounded_wait).
+// One 128x128 output tile per CTA.  Warps (224 threads): 0 TMA producer, 1 and 6 MMA issuers (even / odd K blocks;
+// 1 owns TMEM), 2..5 promotion + store.  Every barrier wait is bounded (see bounded_wait).
 #pragma once
 #include "gemm_common.cuh"
 
 namespace b200 {
 
-constexpr int kBlockScaleThreads = 192;
+constexpr int kBlockScaleThreads = 224;
 constexpr int kFewRowsThreads    = 224; // + a second MMA issuer warp
 constexpr int kBsTileN           = 128;
 
@@ -73,7 +73,8 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     auto full_bar       = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar      = [&](int s) { return bar_base + 64u + 8u * s; };
     auto part_full_bar  = [&](int b) { return bar_base + 128u + 8u * b; };
-    auto part_empty_bar = [&](int b) { return bar_base + 144u + 8u * b; };
+    auto part_empty_bar = [&](int b) { return bar_base + 192u + 8u * b; };
+    constexpr int NP = 4; // TMEM partials (4 x 128 columns: the whole TMEM)
     uint32_t* tmem_ptr_smem    = reinterpret_cast<uint32_t*>(smem_gen + kStageBytes * S + 160);
     volatile uint32_t* abort_f = reinterpret_cast<volatile uint32_t*>(smem_gen + kStageBytes * S + 164);
 
@@ -91,7 +92,7 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
-        for(int b = 0; b < 2; ++b)
+        for(int b = 0; b < NP; ++b)
         {
             mbar_init(part_full_bar(b), 1);
             mbar_init(part_empty_bar(b), 4);
@@ -105,7 +106,7 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     }
     if(warp == 1)
     {
-        tmem_alloc(smem_u32(tmem_ptr_smem), 256);
+        tmem_alloc(smem_u32(tmem_ptr_smem), 512);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -144,10 +145,13 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 }
         }
     }
-    else if(warp == 1)
+    else if(warp == 1 || warp == 6)
     {
+        // two MMA issuers, even K blocks from warp 1 and odd ones from warp 6 (issuing a block costs a single thread
+        // about twice as long as the tensor pipe needs for it; the partials of consecutive blocks are independent)
         if(lane == 0)
         {
+            const int first = (warp == 1) ? 0 : 1;
             const uint32_t idesc = idesc_f8f6f4_e4m3(kTileP, kBsTileN);
             const bool a_tiled = (prm.a_mode == OPM_TILE16), b_tiled = (prm.b_mode == OPM_TILE16);
             const uint32_t a_lbo = a_tiled ? kTileP * 16u : 16u, a_sbo = a_tiled ? 128u : 1024u, a_lay = a_tiled ? 0u : 2u;
@@ -161,13 +165,13 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const uint32_t b_lo0 = static_cast<uint32_t>(make_smem_desc(smem_base + kTileP * kTileKBytes, b_lbo, b_sbo, b_lay));
             const uint32_t a_step = a_adv >> 4, b_step = b_adv >> 4;
             bool ok = true;
-            int s = 0;
-            uint32_t phase = 0;
-            for(int j = 0; j < KB && ok; ++j)
+            int s = first % S;
+            uint32_t phase = (first / S) & 1u;
+            for(int j = first; j < KB && ok; j += 2)
             {
-                const int b = j & 1;
-                if(j >= 2) // both partials start free
-                    ok = bounded_wait(part_empty_bar(b), ((j >> 1) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_MMA_SF, j);
+                const int b = j & (NP - 1);
+                if(j >= NP) // every partial starts free
+                    ok = bounded_wait(part_empty_bar(b), ((j / NP) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_MMA_SF, j);
                 if(ok)
                     ok = bounded_wait(full_bar(s), phase, abort_f, prm.status, ST_TIMEOUT_MMA_FULL, j);
                 if(!ok)
@@ -180,15 +184,15 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                                k > 0 ? 1u : 0u);
                 tc_commit(empty_bar(s));
                 tc_commit(part_full_bar(b));
-                if(++s == S)
+                if((s += 2) >= S)
                 {
-                    s = 0;
+                    s -= S;
                     phase ^= 1u;
                 }
             }
         }
     }
-    else
+    else if(warp < 6)
     {
         // promotion + store: thread = output row
         const int quarter    = warp & 3;
@@ -206,11 +210,11 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         float scale_next = (KB > 0) ? __ldg(xs) * __ldg(ws) : 0.f;
         for(int j = 0; j < KB && ok; ++j)
         {
-            const int b       = j & 1;
+            const int b       = j & (NP - 1);
             const float scale = scale_next;
             if(j + 1 < KB)
                 scale_next = __ldg(xs + static_cast<long long>(j + 1) * prm.xs_stride_k) * __ldg(ws + j + 1);
-            ok = bounded_wait(part_full_bar(b), (j >> 1) & 1, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, j);
+            ok = bounded_wait(part_full_bar(b), (j / NP) & 1, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, j);
             ok = __all_sync(0xffffffffu, ok);
             if(!ok)
                 break;
@@ -305,7 +309,7 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     if(warp == 1)
     {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, 256);
+        tmem_dealloc(tmem_base, 512);
     }
 }
 
