@@ -192,10 +192,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
         for(int s = 0; s < S; ++s)
         {
             // one expect_tx arrival per operand producer and one arrival per scale warp, of every CTA of the pair
-            mbar_init(full_bar(s), (kMixed ? 10 : (kScaled ? 6 : 2)) * CG); // producers + scale warps (+ widening warps)
+            // producers + scale warps (+ widening warps: all four of them, or one pair of them on a 128-row packed tile)
+            mbar_init(full_bar(s), (kMixed ? ((prm.f4_operand == 1 || prm.bn / CG == kTileP) ? 8 : 10) : (kScaled ? 6 : 2)) * CG);
             mbar_init(empty_bar(s), 1);
             mbar_init(staged_bar(s), 1);
-            mbar_init(sfraw_bar(s), 1);
+            mbar_init(sfraw_bar(s), kMixed ? 2 : 1); // raw scales (+ the packed e2m1 tile of the mixed kind: one wait covers both)
             mbar_init(xch_bar(s), 4);
         }
         for(int a = 0; a < kMaxAcc; ++a)
@@ -353,7 +354,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                         {
                             // the packed e2m1 operand (always 16x16-byte tiled) lands in this CTA's staging area:
                             // 4 chunks of 16 bytes per row, counted on a local barrier for the scale warps
-                            const uint32_t sbar = staged_bar(s);
+                            const uint32_t sbar = sfraw_bar(s);
                             mbar_arrive_expect_tx(sbar, (is_p ? kTileP : q_rows_cta) * 64u);
                             tma_load_3d(smem_base + s * L.stage_bytes + L.stg_off, map, sbar, 0, row0 >> 4, kt * 4);
                             if(CG == 1)
@@ -574,11 +575,9 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             {
                 const int s = ring.s;
                 // raw scales of stage s have landed (their producer waited for the previous pass's MMAs, so the
-                // TMEM scale buffer of stage s is free as well)
+                // TMEM scale buffer of stage s is free as well); mixed kind: the packed e2m1 tile counts on the same barrier
                 ok = bounded_wait(sfraw_bar(s), ring.phase, abort_f, prm.status, ST_TIMEOUT_SFWARP, g);
                 const bool widen_here = kMixed && (p_f4 || q_rows_cta == kTileP); // 128-row packed tile: k chunk 3 is ours
-                if(ok && widen_here)
-                    ok = bounded_wait(staged_bar(s), ring.phase, abort_f, prm.status, ST_TIMEOUT_SFWARP, 0x20000 + g);
                 ok = __all_sync(0xffffffffu, ok);
                 if(!ok)
                     break;
@@ -717,6 +716,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
         int uc = 0;
         bool ok = true;
         Ring wring{0, 0};
+        int wseq = 0; // stages seen by the widening loop
         const uint32_t full_lead = (CG == 2) ? map_to_cta(full_bar(0), 0) : full_bar(0);
         for(WorkIter w = first_work(); w.valid && ok; next_unit(w), ++uc)
         {
@@ -727,10 +727,17 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                 // [8 chunks][rows][16 B]) while the scale warps feed the scales, then turn to the unit's epilogue.
                 const int rows = p_f4 ? kTileP : q_rows_cta;
                 const int tid  = (warp - 6) * 32 + lane;
-                for(int i = 0; i < w.n_iters && ok; ++i, wring.advance(S))
+                // 128-row tiles: warps 6,7 take the even stages of the ring sequence and warps 8,9 the odd ones (six items
+                // per thread), so that the fixed cost of a stage (barrier wait, fence, arrival) is paid per two tiles
+                const bool by_pairs = (rows == kTileP);
+                const int my_pair   = (warp - 6) >> 1;
+                const int tid2      = ((warp - 6) & 1) * 32 + lane;
+                for(int i = 0; i < w.n_iters && ok; ++i, wring.advance(S), ++wseq)
                 {
+                    if(by_pairs && (wseq & 1) != my_pair)
+                        continue;
                     const int s = wring.s;
-                    ok = bounded_wait(staged_bar(s), wring.phase, abort_f, prm.status, ST_TIMEOUT_SFWARP, 0x10000 + i);
+                    ok = bounded_wait(sfraw_bar(s), wring.phase, abort_f, prm.status, ST_TIMEOUT_SFWARP, 0x10000 + i);
                     ok = __all_sync(0xffffffffu, ok);
                     if(!ok)
                         break;
@@ -738,25 +745,25 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                     uint8_t* stage   = smem_gen + s * L.stage_bytes;
                     const uint4* src = reinterpret_cast<const uint4*>(stage + L.stg_off);
                     uint4* dst       = reinterpret_cast<uint4*>(stage + (p_f4 ? 0u : L.q_off));
-                    if(rows == kTileP)
+                    if(by_pairs)
                     {
-                        // 128 rows: one item per thread and 16-byte k chunk (chunk u, row tid); chunks 0..2 here, chunk 3
-                        // by the scale warps, whose own work per stage is shorter.  All loads first, so that their
-                        // latencies overlap instead of adding up
-                        uint4 v[3];
+                        // 128 rows: items (16-byte k chunk u, row); chunks 0..2 here (rows tid2 and tid2 + 64), chunk 3 by the
+                        // scale warps, whose own work per stage is shorter.  All loads first, so that their latencies
+                        // overlap instead of adding up
+                        uint4 v[6];
 #pragma unroll
-                        for(int u = 0; u < 3; ++u)
-                            v[u] = src[u * kTileP + tid];
+                        for(int u = 0; u < 6; ++u)
+                            v[u] = src[(u >> 1) * kTileP + (u & 1) * 64 + tid2];
 #pragma unroll
-                        for(int u = 0; u < 3; ++u)
+                        for(int u = 0; u < 6; ++u)
                         {
                             uint4 o0, o1;
                             e2m1x8_to_e4m3x8(v[u].x, o0.x, o0.y);
                             e2m1x8_to_e4m3x8(v[u].y, o0.z, o0.w);
                             e2m1x8_to_e4m3x8(v[u].z, o1.x, o1.y);
                             e2m1x8_to_e4m3x8(v[u].w, o1.z, o1.w);
-                            dst[(2 * u) * kTileP + tid]     = o0;
-                            dst[(2 * u + 1) * kTileP + tid] = o1;
+                            dst[(2 * (u >> 1)) * kTileP + (u & 1) * 64 + tid2]     = o0;
+                            dst[(2 * (u >> 1) + 1) * kTileP + (u & 1) * 64 + tid2] = o1;
                         }
                     }
                     else
