@@ -1037,10 +1037,14 @@ void launch_blockscale(const BlockScaleProblem& prob)
     prm.ldo         = prob.ldo;
     prm.status      = st.status;
     prm.scales_e8m0 = prob.scales_are_e8m0 ? 1 : 0;
-    // 256 x 256 tiles on CTA pairs once the 128 x 128 tiles no longer fit one wave: below that the single-CTA kernel
-    // keeps more SMs busy (M = 300, N = K = 4096: 96 CTAs and 17.6 us against 32 pairs and 29.6 us)
+    // 256 x 256 tiles on CTA pairs or 128 x 128 tiles on single CTAs: whichever needs less time by waves x cycles per K
+    // block (measured: ~1300 for a pair, ~720 for a single CTA).  Few tiles favour the single-CTA kernel (M = 300,
+    // N = K = 4096: 96 CTAs and 15.3 us against 32 pairs and 29.6 us), many tiles the pairs.
     const long long tiles128 = ((prob.M + kTileP - 1) / kTileP) * ((prob.N + kBsTileN - 1) / kBsTileN);
-    if(prob.M > kTileP && tiles128 > st.sm_count)
+    const long long pairs256 = ((prob.M + 2 * kTileP - 1) / (2 * kTileP)) * ((prob.N + 2 * kBsTileN - 1) / (2 * kBsTileN));
+    const long long single_cost = (tiles128 + st.sm_count - 1) / st.sm_count * 720;
+    const long long pair_cost   = (pairs256 + st.sm_count / 2 - 1) / (st.sm_count / 2) * 1300;
+    if(prob.M > kTileP && pair_cost < single_cost)
     {
         // 256 x 256 tiles on CTA pairs
         const int stage_bytes = 2 * kTileP * kTileKBytes;
