@@ -36,6 +36,7 @@ struct BlockScaleParams
     float* ws_partial;
     unsigned int* ws_counter;
     int scales_e8m0;         // few-rows kernel: both scale tensors hold e8m0 bytes (2^(e-127)) instead of floats
+    int tma_out;             // few-rows kernel: columns per warp-wide TMA tile store of the output (0: plain stores)
     int cluster;             // few-rows kernel: the slices are the CTAs of one cluster and meet in shared memory
 };
 
@@ -325,7 +326,7 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 template <int XR>
 __global__ void __launch_bounds__(kFewRowsThreads, 1)
 gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                                    const BlockScaleParams prm)
+                                    const __grid_constant__ CUtensorMap map_o, const BlockScaleParams prm)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -628,7 +629,36 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
                     prm.ws_counter[tile] = 0; // ready for the next launch
             }
         }
-        if(ok && owns && n < prm.N)
+        if(prm.tma_out)
+        {
+            // Every warp stages the columns it owns ([m][column] bf16, prm.tma_out of them per row: 32, or 16 when the
+            // cluster split leaves a CTA half a warp's columns) in a retired operand stage and stores them as one TMA
+            // tile, which clips rows >= M and columns >= N; cheaper at the end of a short kernel than XR scattered
+            // 2-byte stores per thread.
+            const uint32_t mask = __ballot_sync(0xffffffffu, ok && owns);
+            if(mask != 0u)
+            {
+                const int lead   = __ffs(mask) - 1;              // first owning lane of this warp
+                const int wcols  = prm.tma_out;
+                uint8_t* stg     = smem_gen + (warp - 2) * (XR * 64);
+                __nv_bfloat16* t = reinterpret_cast<__nv_bfloat16*>(stg);
+                if(ok && owns)
+                {
+#pragma unroll
+                    for(int i = 0; i < XR; ++i)
+                        t[i * wcols + (lane - lead)] = __float2bfloat16_rn(acc[i]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if(lane == lead && n < prm.N) // (a tile that starts inside the output; what sticks out is clipped)
+                {
+                    tma_store_2d(&map_o, smem_base + (warp - 2) * (XR * 64), (n) * 2, 0);
+                    bulk_commit_group();
+                    bulk_wait_group<0>(); // complete before the CTA retires
+                }
+            }
+        }
+        else if(ok && owns && n < prm.N)
         {
 #pragma unroll
             for(int i = 0; i < XR; ++i)

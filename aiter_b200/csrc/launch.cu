@@ -1132,21 +1132,32 @@ void launch_blockscale(const BlockScaleProblem& prob)
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         lc.attrs    = attr;
         lc.numAttrs = pdl_disabled() ? 1 : 2;
+        // output as warp-wide TMA tiles: a warp owns 32 columns, or 16 when eight slices share the tile's 128
+        CUtensorMap mo = ma;
+        prm.tma_out    = 0;
+        if((reinterpret_cast<uintptr_t>(prob.out) & 15) == 0 && prob.ldo % 8 == 0)
+        {
+            prm.tma_out                 = (prm.cluster && splits == 8) ? 16 : 32;
+            const cuuint64_t dims[2]    = {static_cast<cuuint64_t>(prob.N) * 2, static_cast<cuuint64_t>(prob.M)};
+            const cuuint64_t strides[1] = {static_cast<cuuint64_t>(prob.ldo) * 2};
+            const cuuint32_t box[2]     = {static_cast<cuuint32_t>(prm.tma_out) * 2u, static_cast<cuuint32_t>(xr)};
+            mo = encode_map(prob.out, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "output");
+        }
         static bool attr_done[3][64] = {};
         if(xr == 16)
         {
             raise_smem_limit(gemm_a8w8_blockscale_fewrows_kernel<16>, attr_done[0]);
-            B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_fewrows_kernel<16>, ma, mb, prm));
+            B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_fewrows_kernel<16>, ma, mb, mo, prm));
         }
         else if(xr == 32)
         {
             raise_smem_limit(gemm_a8w8_blockscale_fewrows_kernel<32>, attr_done[1]);
-            B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_fewrows_kernel<32>, ma, mb, prm));
+            B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_fewrows_kernel<32>, ma, mb, mo, prm));
         }
         else
         {
             raise_smem_limit(gemm_a8w8_blockscale_fewrows_kernel<64>, attr_done[2]);
-            B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_fewrows_kernel<64>, ma, mb, prm));
+            B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_fewrows_kernel<64>, ma, mb, mo, prm));
         }
         B200_CUDA(cudaGetLastError());
     }
