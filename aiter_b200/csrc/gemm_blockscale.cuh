@@ -16,7 +16,7 @@
 namespace b200 {
 
 constexpr int kBlockScaleThreads = 224;
-constexpr int kFewRowsThreads    = 224; // + a second MMA issuer warp
+constexpr int kFewRowsThreads    = 256; // + a second MMA issuer warp and a second producer warp
 constexpr int kBsTileN           = 128;
 
 struct BlockScaleParams
@@ -322,7 +322,7 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 // with x_scale[m][kb] * w_scale[n/128][kb]; 8 TMEM partials are in flight, so the round trip
 // MMA -> commit -> promotion -> release is paid once per 8 K blocks, not per 2.  gridDim.z slices of K meet either
 // in shared memory (the slices form one thread-block cluster; every CTA reduces its share of the tile's columns
-// and receives the other slices' partial sums of them by st.async) or in the fp32 workspace like in the kernel above.  Warps (224 threads): 0 TMA producer, 1 and 6 MMA issuers (1 owns TMEM), 2..5 promotion + store.
+// and receives the other slices' partial sums of them by st.async) or in the fp32 workspace like in the kernel above.  Warps (256 threads): 0 and 7 TMA producers (weights / activations), 1 and 6 MMA issuers (1 owns TMEM), 2..5 promotion + store.
 template <int XR>
 __global__ void __launch_bounds__(kFewRowsThreads, 1)
 gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -364,7 +364,7 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
     {
         for(int s = 0; s < S; ++s)
         {
-            mbar_init(full_bar(s), 1);
+            mbar_init(full_bar(s), 2); // one expect_tx arrival per producer warp
             mbar_init(empty_bar(s), 1);
         }
         for(int b = 0; b < NP; ++b)
@@ -394,10 +394,13 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
     grid_dependency_wait();
     grid_launch_dependents();
 
-    if(warp == 0)
+    if(warp == 0 || warp == 7)
     {
+        // two producer threads: warp 0 loads the weight tiles, warp 7 the activation rows (a producer needs several
+        // hundred cycles per K block at a single thread's instruction latency)
         if(lane == 0)
         {
+            const bool is_w = (warp == 0);
             // single-thread loops pay every instruction's latency: ring counters, no division
             int issued = 0;
             int s = 0;
@@ -407,9 +410,16 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
                 if(j >= S && !bounded_wait(empty_bar(s), phase ^ 1u, abort_f, prm.status, ST_TIMEOUT_PRODUCER, j))
                     break;
                 const uint32_t stage = smem_base + s * kStageBytes;
-                mbar_arrive_expect_tx(full_bar(s), kStageBytes);
-                issue_operand_load(prm.b_mode, stage, &map_b, full_bar(s), col0, kb0 + j);
-                issue_operand_load(prm.a_mode, stage + kWBytes, &map_a, full_bar(s), 0, kb0 + j);
+                if(is_w)
+                {
+                    mbar_arrive_expect_tx(full_bar(s), kWBytes);
+                    issue_operand_load(prm.b_mode, stage, &map_b, full_bar(s), col0, kb0 + j);
+                }
+                else
+                {
+                    mbar_arrive_expect_tx(full_bar(s), XR * kTileKBytes);
+                    issue_operand_load(prm.a_mode, stage + kWBytes, &map_a, full_bar(s), 0, kb0 + j);
+                }
                 issued = j + 1;
                 if(++s == S)
                 {
