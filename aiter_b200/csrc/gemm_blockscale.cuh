@@ -8,14 +8,14 @@
 // accumulators, and the 128 epilogue threads (one output row each) promote the finished partial into fp32
 // register accumulators with the two scales applied, while the tensor core fills the other partial.
 //
-// One 128x128 output tile per CTA.  Warps (224 threads): 0 TMA producer, 1 and 6 MMA issuers (even / odd K blocks;
-// 1 owns TMEM), 2..5 promotion + store.  Every barrier wait is bounded (see bounded_wait).
+// One 128x128 output tile per CTA.  Warps (256 threads): 0 and 7 TMA producers (activations / weights), 1 and 6 MMA
+// issuers (even / odd K blocks; 1 owns TMEM), 2..5 promotion + store.  Every barrier wait is bounded (see bounded_wait).
 #pragma once
 #include "gemm_common.cuh"
 
 namespace b200 {
 
-constexpr int kBlockScaleThreads = 224;
+constexpr int kBlockScaleThreads = 256;
 constexpr int kFewRowsThreads    = 256; // + a second MMA issuer warp and a second producer warp
 constexpr int kBsTileN           = 128;
 
@@ -90,7 +90,7 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     {
         for(int s = 0; s < S; ++s)
         {
-            mbar_init(full_bar(s), 1);
+            mbar_init(full_bar(s), 2); // one expect_tx arrival per producer warp
             mbar_init(empty_bar(s), 1);
         }
         for(int b = 0; b < NP; ++b)
@@ -115,10 +115,12 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
 
-    if(warp == 0)
+    if(warp == 0 || warp == 7)
     {
+        // two producer threads: warp 0 loads the activation tiles, warp 7 the weight tiles
         if(lane == 0)
         {
+            const bool is_a = (warp == 0);
             // single-thread loops pay every instruction's latency: ring counters, no division
             int issued = 0;
             int s = 0;
@@ -128,9 +130,11 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 if(j >= S && !bounded_wait(empty_bar(s), phase ^ 1u, abort_f, prm.status, ST_TIMEOUT_PRODUCER, j))
                     break;
                 const uint32_t stage = smem_base + s * kStageBytes;
-                mbar_arrive_expect_tx(full_bar(s), kStageBytes);
-                issue_operand_load(prm.a_mode, stage, &map_a, full_bar(s), row0, kb0 + j);
-                issue_operand_load(prm.b_mode, stage + kTileP * kTileKBytes, &map_b, full_bar(s), col0, kb0 + j);
+                mbar_arrive_expect_tx(full_bar(s), kStageBytes / 2);
+                if(is_a)
+                    issue_operand_load(prm.a_mode, stage, &map_a, full_bar(s), row0, kb0 + j);
+                else
+                    issue_operand_load(prm.b_mode, stage + kTileP * kTileKBytes, &map_b, full_bar(s), col0, kb0 + j);
                 issued = j + 1;
                 if(++s == S)
                 {
