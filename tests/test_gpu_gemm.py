@@ -321,6 +321,36 @@ def test_a8w8_blockscale_fp32_scales(ab, M, N, K, bpre):
     assert_healthy(ab)
 
 
+@pytest.mark.parametrize("M", [16, 100, 300])
+def test_a8w8_blockscale_replays_from_a_cuda_graph(ab, M):
+    # few-rows kernel (cluster + dependent launch), 128x128 kernel with and without its workspace K split: captured after
+    # one call on the capture stream (the workspace may not grow during capture), replayed, compared with the oracle
+    N, K = 1024, 2048
+    g = torch.Generator().manual_seed(77 + M)
+    x = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn)
+    w = torch.randn(N, K, generator=g).to(torch.float8_e4m3fn)
+    xs = torch.rand(M, K // 128, generator=g) + 0.5
+    ws = torch.rand(N // 128, K // 128, generator=g) + 0.5
+    ref = ox.gemm_a8w8_blockscale_ref(x.view(torch.uint8).numpy(), w.view(torch.uint8).numpy(), xs.numpy(), ws.numpy())
+    xc, wc, xsc, wsc = x.cuda(), w.cuda(), xs.cuda(), ws.cuda()
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        ab.gemm_a8w8_blockscale_cktile(xc, wc, xsc, wsc, out)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(3):
+                ab.gemm_a8w8_blockscale_cktile(xc, wc, xsc, wsc, out)
+        out.fill_(float("nan"))
+        graph.replay()
+        graph.replay()
+    torch.cuda.synchronize()
+    check(ref, out, what=f"blockscale from a CUDA graph, M={M}")
+    assert_healthy(ab)
+
+
 def test_a8w8_blockscale_other_backend_names(ab):
     # the CK-tile and assembly names of the reference reach the same kernels, each in its own argument order
     M, N, K = 200, 512, 1024
