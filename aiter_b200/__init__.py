@@ -16,7 +16,7 @@ if not logger.handlers:
     logger.propagate = False
 
 from . import dtypes, fp4_utils  # noqa: E402
-from ._ffi import device_status, get_padded_m, heuristic_name, kernel_list, launch_count  # noqa: E402,F401
+from ._ffi import debug_wait_control, device_status, get_padded_m, heuristic_name, kernel_list, launch_count, noalloc_status  # noqa: E402,F401
 from .dtypes import MX_DEFAULT_ROUND_MODE, MxDtype, MxScaleRoundMode, QuantType  # noqa: E402,F401
 from .gemm_op_a4w4 import (  # noqa: E402,F401
     gemm_a4w4,

@@ -95,7 +95,8 @@ EXPORTS = sorted(
     list(SIGNATURES)
     + ["getPaddedM", "aiter_ctypes_abi_version", "aiter_get_last_error", "aiter_clear_last_error",
        "opus_gemm_workspace_init", "aiter_b200_device_status", "aiter_b200_kernel_list",
-       "aiter_b200_heuristic_name", "aiter_b200_launch_count"]
+       "aiter_b200_heuristic_name", "aiter_b200_launch_count", "aiter_b200_noalloc_status",
+       "aiter_b200_debug_wait_control"]
 )
 
 
@@ -154,6 +155,25 @@ def device_status(device: int = 0):
         msg = _lib.aiter_get_last_error()
         raise RuntimeError(f"aiter_b200_device_status failed: {msg.decode() if msg else ''}")
     return tuple(int(w) for w in words)
+
+
+def noalloc_status(device: int = 0):
+    """Same record for the allocation-free entry point, which keeps it in its own fixed array."""
+    words = (ctypes.c_uint * 4)()
+    rc = _lib.aiter_b200_noalloc_status(int(device), words)
+    if rc != 0:
+        msg = _lib.aiter_get_last_error()
+        raise RuntimeError(f"aiter_b200_noalloc_status failed: {msg.decode() if msg else ''}")
+    return tuple(int(w) for w in words)
+
+
+def debug_wait_control(device: int = 0, limit_ns: int = 1_000_000_000, withhold_scales: bool = False) -> None:
+    """Bound of the in-kernel waits on `device` and the switch that makes one producer issue nothing (tests of the
+    time-out path).  Call with no arguments to restore the defaults."""
+    rc = _lib.aiter_b200_debug_wait_control(int(device), ctypes.c_ulonglong(int(limit_ns)), int(bool(withhold_scales)))
+    if rc != 0:
+        msg = _lib.aiter_get_last_error()
+        raise RuntimeError(f"aiter_b200_debug_wait_control failed: {msg.decode() if msg else ''}")
 
 
 def kernel_list() -> str:

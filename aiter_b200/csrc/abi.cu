@@ -1,5 +1,6 @@
 // extern "C" entry points: argument checking, aiter_tensor_t -> GemmProblem, error bridge.
 #include "../../include/aiter_b200.h"
+#include "abi_checks.h"
 #include "gemm_common.cuh"
 #include "launch.h"
 #include "quant_mx.cuh"
@@ -35,56 +36,6 @@ static int safe_call(Fn&& fn)
     return -1;
 }
 
-static const char* dtype_name(int d)
-{
-    static const char* names[] = {"fp8", "fp8_e8m0", "fp16", "bf16", "fp32", "i4x2", "fp4x2",
-                                  "u32", "i32", "i16", "i8", "u8", "i64", "u64"};
-    return (d >= 0 && d < 14) ? names[d] : "?";
-}
-
-static bool is_byte_dtype(int d)
-{
-    return d == AITER_DTYPE_fp8 || d == AITER_DTYPE_fp8_e8m0 || d == AITER_DTYPE_fp4x2 || d == AITER_DTYPE_u8 ||
-           d == AITER_DTYPE_i8 || d == AITER_DTYPE_i4x2;
-}
-
-static void require_tensor(const aiter_tensor_t* t, const char* fn, const char* name, int ndim)
-{
-    B200_CHECK(t != nullptr, fn, ": ", name, " is required");
-    B200_CHECK(t->ndim == ndim, fn, ": ", name, " must be ", ndim, "-D (got ", t->ndim, "-D)");
-    B200_CHECK(t->device_id >= 0, fn, ": ", name, " must live on a GPU");
-    B200_CHECK(t->ptr != nullptr || t->numel_ == 0, fn, ": ", name, " has a null data pointer");
-}
-
-static void require_rows_contiguous(const aiter_tensor_t* t, const char* fn, const char* name)
-{
-    B200_CHECK(t->strides[t->ndim - 1] == 1 || t->shape[t->ndim - 1] == 1, fn, ": ", name,
-               " must be contiguous along its last dimension");
-}
-
-static void require_dense(const aiter_tensor_t* t, const char* fn, const char* name)
-{
-    int64_t expect = 1;
-    for(int d = t->ndim - 1; d >= 0; --d)
-    {
-        B200_CHECK(t->shape[d] == 1 || t->strides[d] == expect, fn, ": ", name, " must be contiguous");
-        expect *= t->shape[d];
-    }
-}
-
-static ScaleOperand scale_operand(const aiter_tensor_t* s, int wire, const char* fn, const char* name)
-{
-    require_tensor(s, fn, name, 2);
-    B200_CHECK(is_byte_dtype(s->dtype_), fn, ": ", name, " must be e8m0 / uint8 (got ", dtype_name(s->dtype_), ")");
-    require_dense(s, fn, name);
-    ScaleOperand so;
-    so.ptr         = s->ptr;
-    so.wire        = wire;
-    so.padded_rows = s->shape[0];
-    so.padded_cols = s->shape[1];
-    return so;
-}
-
 static void set_out(GemmProblem& p, const aiter_tensor_t* out, const char* fn, long long M, long long N)
 {
     require_tensor(out, fn, "out", 2);
@@ -98,6 +49,8 @@ static void set_out(GemmProblem& p, const aiter_tensor_t* out, const char* fn, l
 
 static void apply_config(GemmProblem& p, const char* kernelName, int log2_splitk, const char* fn)
 {
+    // -1 (Python None) leaves the split to the heuristic; anything else is log2 of the number of K slices
+    B200_CHECK(log2_splitk >= -1 && log2_splitk <= 8, fn, ": log2 of the K split must be between 0 and 8 (got ", log2_splitk, ")");
     p.cfg.log2_splitk = log2_splitk;
     if(kernelName != nullptr && kernelName[0] != 0) // a "_k<n>" suffix of the name overrides the split argument
         B200_CHECK(parse_config_name(kernelName, p.cfg), fn, ": not find kernel ", kernelName);
@@ -511,6 +464,10 @@ extern "C" void aiter_clear_last_error(void) { g_last_error.clear(); }
 extern "C" int aiter_b200_device_status(int device, unsigned int out_words[4])
 {
     return safe_call([&] { read_device_status(device, out_words); });
+}
+extern "C" int aiter_b200_debug_wait_control(int device, unsigned long long limit_ns, int withhold_scales)
+{
+    return safe_call([&] { set_wait_control(device, limit_ns, withhold_scales); });
 }
 extern "C" const char* aiter_b200_kernel_list(void) { return kernel_menu_text(); }
 extern "C" const char* aiter_b200_heuristic_name(int kind, int M, int N, int K, int* log2_splitk)

@@ -146,7 +146,7 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                 for(int j = issued - 1; j >= 0 && j >= issued - S; --j)
                 {
                     const uint64_t t0 = global_timer_ns();
-                    while(!mbar_try_wait(full_bar(j % S), (j / S) & 1) && global_timer_ns() - t0 < kWaitLimitNs) {}
+                    while(!mbar_try_wait(full_bar(j % S), (j / S) & 1) && global_timer_ns() - t0 < c_wait_ctl.limit_ns) {}
                 }
         }
     }
@@ -435,7 +435,7 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
                 for(int j = issued - 1; j >= 0 && j >= issued - S; --j)
                 {
                     const uint64_t t0 = global_timer_ns();
-                    while(!mbar_try_wait(full_bar(j % S), (j / S) & 1) && global_timer_ns() - t0 < kWaitLimitNs) {}
+                    while(!mbar_try_wait(full_bar(j % S), (j / S) & 1) && global_timer_ns() - t0 < c_wait_ctl.limit_ns) {}
                 }
         }
     }
@@ -850,7 +850,7 @@ gemm_a8w8_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
             {
                 tc_commit_2cta(drain_bar, 1);
                 const uint64_t t0 = global_timer_ns();
-                while(!mbar_try_wait(drain_bar, 0) && global_timer_ns() - t0 < kWaitLimitNs) {}
+                while(!mbar_try_wait(drain_bar, 0) && global_timer_ns() - t0 < c_wait_ctl.limit_ns) {}
             }
         }
     }

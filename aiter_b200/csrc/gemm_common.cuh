@@ -14,7 +14,19 @@ constexpr int kMaxStages  = 8;
 constexpr int kTileP      = 128;
 constexpr int kTileKBytes = 128;
 constexpr int kNumThreads = 224;
-constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull; // 1 s per wait
+constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull; // 1 s per wait unless the host lowers it
+
+// Per-device controls of the bounded waits, in constant memory so that a test can shorten the limit and make a
+// wait run out on purpose without rebuilding.  The host writes it (launch.cu: device set-up, and the
+// aiter_b200_debug_wait_control entry point); kernels read it only on the slow path of a wait.
+struct WaitControl
+{
+    unsigned long long limit_ns;  // wall-time bound of every in-kernel wait
+    unsigned int* host_mirror;    // pinned, device-mapped host word that receives the first failure code (may be null)
+    unsigned int withhold_scales; // test hook: the raw-scale producer of the persistent kernel issues nothing, so
+                                  // the waits of the roles behind it run out after limit_ns
+};
+static __constant__ WaitControl c_wait_ctl = {kWaitLimitNs, nullptr, 0u};
 
 // status codes (word 0 of the status buffer); words 1..3 carry blockIdx / iteration detail
 constexpr uint32_t kParkNs = 20000; // longest single park of a waiting thread; the wall-time bound is checked between parks
@@ -32,7 +44,7 @@ __device__ __forceinline__ uint64_t global_timer_ns()
     return t;
 }
 
-// Wait for an mbarrier phase for at most kWaitLimitNs of wall time.  Returns false when the wait
+// Wait for an mbarrier phase for at most c_wait_ctl.limit_ns of wall time.  Returns false when the wait
 // expired (first expiry records `code` in the status words and raises the CTA abort flag) or when
 // another role of this CTA already aborted.
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
@@ -40,14 +52,15 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
 {
     if(mbar_try_wait(bar, parity))
         return true;
-    const uint64_t t0 = global_timer_ns();
+    const uint64_t t0    = global_timer_ns();
+    const uint64_t limit = c_wait_ctl.limit_ns;
     for(;;)
     {
         if(mbar_try_wait_parked(bar, parity, kParkNs))
             return true;
         if(*abort_flag)
             return false;
-        if(global_timer_ns() - t0 > kWaitLimitNs)
+        if(global_timer_ns() - t0 > limit)
             break;
     }
     *abort_flag = 1;
@@ -56,6 +69,13 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, vola
         status[1] = blockIdx.x | (blockIdx.y << 16);
         status[2] = blockIdx.z;
         status[3] = detail;
+        // the host checks this word before every launch, so the failure surfaces at the caller's next call
+        unsigned int* mirror = c_wait_ctl.host_mirror;
+        if(mirror != nullptr)
+        {
+            *reinterpret_cast<volatile unsigned int*>(mirror) = code;
+            __threadfence_system();
+        }
     }
     return false;
 }

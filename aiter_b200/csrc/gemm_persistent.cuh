@@ -36,6 +36,14 @@
 
 namespace b200 {
 
+// Timestamp probes of the single-thread roles, compiled in only with -DAITER_B200_TRACING (a development aid: a
+// probe in a loop that one thread runs per K tile costs that loop several cycles per dependent instruction).
+#ifdef AITER_B200_TRACING
+#define B200_TRACE(...) __VA_ARGS__
+#else
+#define B200_TRACE(...)
+#endif
+
 constexpr int kPersistentThreads = 384;
 constexpr int kMaxAcc            = 2;
 
@@ -178,11 +186,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     const int cluster_id    = blockIdx.x / cluster_ctas;
     const int n_clusters    = gridDim.x / cluster_ctas;
 
-    const bool tracing = (prm.trace != nullptr) && blockIdx.x == 0;
-    auto stamp = [&](int slot) { if(tracing && slot < 64) prm.trace[slot] = static_cast<unsigned long long>(clock64()); };
-    if(threadIdx.x == 0) stamp(0);
-    if(prm.trace != nullptr && threadIdx.x == 0 && blockIdx.x < 160)
-        prm.trace[64 + 2 * blockIdx.x] = global_timer_ns();
+    B200_TRACE(const bool tracing = (prm.trace != nullptr) && blockIdx.x == 0;)
+    B200_TRACE(auto stamp = [&](int slot) { if(tracing && slot < 64) prm.trace[slot] = static_cast<unsigned long long>(clock64()); };)
+    B200_TRACE(if(threadIdx.x == 0) stamp(0);)
+    B200_TRACE(if(prm.trace != nullptr && threadIdx.x == 0 && blockIdx.x < 160) prm.trace[64 + 2 * blockIdx.x] = global_timer_ns();)
 
     const int splits      = prm.splits;
     const int total_units = prm.tiles_p * prm.tiles_q * (prm.csplit > 1 ? 1 : splits);
@@ -241,7 +248,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
         cluster_sync_all(); // the partner's barriers exist before anything arrives on them remotely
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
-    if(threadIdx.x == 0) stamp(1);
+    B200_TRACE(if(threadIdx.x == 0) stamp(1);)
     // Programmatic dependent launch: everything above (barriers, TMEM, descriptor prefetch) may overlap the tail of
     // the previous kernel in the stream; nothing below may touch global memory before that kernel has completed.
     // The next kernel's CTAs may in turn be scheduled as soon as every CTA of this grid has got here.
@@ -382,7 +389,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                             else
                                 tma_load_4d_pair(dst, map, bar, 0, 0, row0 >> 1, kt);
                         }
-                        if(tracing && is_p && g < 8) stamp(2 + 4 * g);
+                        B200_TRACE(if(tracing && is_p && g < 8) stamp(2 + 4 * g);)
                     }
                 }
             };
@@ -406,7 +413,9 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     else if(warp == 11)
     {
         // ------------------------------------------------------------------ raw scale producer (every CTA)
-        if(kScaled && lane == 0)
+        // (test hook: with c_wait_ctl.withhold_scales set this role issues nothing; the waits behind it then run
+        // out after the shortened limit, which is how the time-out path is exercised without faulting anything)
+        if(kScaled && lane == 0 && c_wait_ctl.withhold_scales == 0u)
         {
             const uint32_t sfp_bytes = 4u * kSfChunk;
             const uint32_t sfq_bytes = static_cast<uint32_t>((bn + 31) / 32) * kSfChunk;
@@ -493,7 +502,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                     if(!ok)
                         break;
                     tc_fence_after_sync();
-                    if(tracing && g < 8) stamp(5 + 4 * g);
+                    B200_TRACE(if(tracing && g < 8) stamp(5 + 4 * g);)
                     const uint32_t p_lo = p_lo0 + s * stage_step;
                     const uint32_t q_lo = q_lo0 + s * stage_step;
                     const uint32_t tsfp = sf0 + s * prm.sf_cols;
@@ -541,7 +550,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                     acc_phase ^= 1u;
                 }
             }
-            stamp(60);
+            B200_TRACE(stamp(60);)
             if(!ok)
             {
                 // abort: let whatever was issued finish before TMEM is released
@@ -550,7 +559,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                 else
                     tc_commit_2cta(drain_bar, 1);
                 const uint64_t t0 = global_timer_ns();
-                while(!mbar_try_wait(drain_bar, 0) && global_timer_ns() - t0 < kWaitLimitNs) {}
+                while(!mbar_try_wait(drain_bar, 0) && global_timer_ns() - t0 < c_wait_ctl.limit_ns) {}
             }
         }
     }
@@ -581,7 +590,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                 ok = __all_sync(0xffffffffu, ok);
                 if(!ok)
                     break;
-                if(tracing && warp == 2 && lane == 0 && g < 8) stamp(3 + 4 * g);
+                B200_TRACE(if(tracing && warp == 2 && lane == 0 && g < 8) stamp(3 + 4 * g);)
                 uint8_t* stage = smem_gen + s * L.stage_bytes;
                 if(widen_here)
                 {
@@ -688,7 +697,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                         mbar_arrive_cluster(full_leader + 8u * s);
                     else
                         mbar_arrive(full_leader + 8u * s);
-                    if(tracing && warp == 2 && g < 8) stamp(4 + 4 * g);
+                    B200_TRACE(if(tracing && warp == 2 && g < 8) stamp(4 + 4 * g);)
                 }
             }
         }
@@ -741,7 +750,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                     ok = __all_sync(0xffffffffu, ok);
                     if(!ok)
                         break;
-                    if(tracing && warp == 6 && lane == 0 && uc == 0 && i < 8) stamp(34 + 2 * i);
+                    B200_TRACE(if(tracing && warp == 6 && lane == 0 && uc == 0 && i < 8) stamp(34 + 2 * i);)
                     uint8_t* stage   = smem_gen + s * L.stage_bytes;
                     const uint4* src = reinterpret_cast<const uint4*>(stage + L.stg_off);
                     uint4* dst       = reinterpret_cast<uint4*>(stage + (p_f4 ? 0u : L.q_off));
@@ -788,7 +797,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                             mbar_arrive_cluster(full_lead + 8u * s);
                         else
                             mbar_arrive(full_lead + 8u * s);
-                        if(tracing && warp == 6 && uc == 0 && i < 8) stamp(35 + 2 * i);
+                        B200_TRACE(if(tracing && warp == 6 && uc == 0 && i < 8) stamp(35 + 2 * i);)
                     }
                 }
                 if(!ok)
@@ -803,7 +812,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             if(!ok)
                 break;
             tc_fence_after_sync();
-            if(warp == 6 && lane == 0 && uc == 0) stamp(61);
+            B200_TRACE(if(warp == 6 && lane == 0 && uc == 0) stamp(61);)
             const uint32_t tacc = tlane + a * prm.acc_stride;
             bool is_last        = !split;
             auto release_acc = [&]() {
@@ -1101,23 +1110,22 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                         finish(v, c);
                     }
                 }
-                if(warp == 6 && lane == 0 && uc == 0) stamp(59);
+                B200_TRACE(if(warp == 6 && lane == 0 && uc == 0) stamp(59);)
                 if(split && warp == 6 && lane == 0)
                     prm.ws_counter[slot] = 0; // ready for the next launch
             }
         }
         if(use_tma && lane == 0)
             bulk_wait_group<0>(); // this warp's tile stores are complete before the CTA retires
-        if(warp == 6 && lane == 0) stamp(62);
+        B200_TRACE(if(warp == 6 && lane == 0) stamp(62);)
         tc_fence_before_sync();
     }
 
     __syncthreads();
     if(CG == 2 || csplit > 1)
         cluster_sync_all(); // nobody leaves while the partner may still arrive on this CTA's barriers
-    if(threadIdx.x == 0) stamp(63);
-    if(prm.trace != nullptr && threadIdx.x == 0 && blockIdx.x < 160)
-        prm.trace[65 + 2 * blockIdx.x] = global_timer_ns();
+    B200_TRACE(if(threadIdx.x == 0) stamp(63);)
+    B200_TRACE(if(prm.trace != nullptr && threadIdx.x == 0 && blockIdx.x < 160) prm.trace[65 + 2 * blockIdx.x] = global_timer_ns();)
     if(warp == 1)
     {
         tc_fence_after_sync();

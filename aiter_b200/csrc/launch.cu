@@ -130,8 +130,13 @@ struct DeviceState
     int sm_count         = 0;
     int smem_optin       = 0;
     unsigned int* status = nullptr;
-    unsigned long long* trace = nullptr; // debugging aid, allocated when AITER_B200_TRACE is set
+    unsigned int* status_host = nullptr; // pinned host word the kernels copy the first failure code to; read before every launch
+    WaitControl wait_ctl{kWaitLimitNs, nullptr, 0u};
+    unsigned long long* trace = nullptr; // AITER_B200_TRACING builds only
     std::map<cudaStream_t, StreamWorkspace> ws;
+    // Buffers that were outgrown.  A CUDA graph captured earlier may still hold their addresses, so they are never
+    // freed while the process lives: replaying such a graph keeps writing into memory this library still owns.
+    std::vector<void*> retired;
 };
 
 static std::mutex g_mutex;
@@ -153,7 +158,40 @@ static DeviceState& device_state(int device)
     st.smem_optin = static_cast<int>(prop.sharedMemPerBlockOptin);
     B200_CUDA(cudaMalloc(&st.status, 4 * sizeof(unsigned int)));
     B200_CUDA(cudaMemset(st.status, 0, 4 * sizeof(unsigned int)));
+    // one pinned host word, mapped into the device: a kernel whose wait runs out stores its code there too, so
+    // the next call on this device can refuse to launch without a device round trip
+    void* host_word = nullptr;
+    if(cudaHostAlloc(&host_word, sizeof(unsigned int), cudaHostAllocMapped) == cudaSuccess)
+    {
+        st.status_host  = static_cast<unsigned int*>(host_word);
+        *st.status_host = 0u;
+        void* dev_view  = nullptr;
+        if(cudaHostGetDevicePointer(&dev_view, host_word, 0) == cudaSuccess)
+            st.wait_ctl.host_mirror = static_cast<unsigned int*>(dev_view);
+    }
+    else
+        cudaGetLastError();
+    B200_CUDA(cudaMemcpyToSymbol(c_wait_ctl, &st.wait_ctl, sizeof(WaitControl)));
     return g_devices.emplace(device, st).first->second;
+}
+
+// A wait that ran out in an earlier kernel left its code in the pinned host word: refuse further launches until the
+// caller has fetched (and thereby cleared) the record.  Caller holds g_mutex.
+static void require_healthy(const DeviceState& st, int device)
+{
+    if(st.status_host != nullptr)
+    {
+        const unsigned int code = *reinterpret_cast<volatile unsigned int*>(st.status_host);
+        B200_CHECK(code == 0u, "an earlier kernel on device ", device, " gave up on a wait (status code 0x", std::hex, code, std::dec,
+                   "); its output is incomplete. Read and clear the record with aiter_b200_device_status before launching again");
+    }
+}
+
+// Retire an outgrown buffer instead of freeing it (see DeviceState::retired).
+static void retire(DeviceState& st, void* p)
+{
+    if(p != nullptr)
+        st.retired.push_back(p);
 }
 
 static StreamWorkspace& stream_workspace(DeviceState& st, cudaStream_t stream, size_t partial_bytes)
@@ -176,14 +214,11 @@ static StreamWorkspace& stream_workspace(DeviceState& st, cudaStream_t stream, s
     }
     if(need_grow)
     {
-        if(w.partial != nullptr)
-        {
-            B200_CUDA(cudaStreamSynchronize(stream));
-            B200_CUDA(cudaFree(w.partial));
-            w.partial       = nullptr;
-            w.partial_bytes = 0;
-        }
-        size_t bytes = std::max(partial_bytes, static_cast<size_t>(8) << 20);
+        // grow geometrically, so that a sequence of ever larger shapes retires only a few buffers
+        size_t bytes = std::max(std::max(partial_bytes, static_cast<size_t>(8) << 20), 2 * w.partial_bytes);
+        retire(st, w.partial);
+        w.partial       = nullptr;
+        w.partial_bytes = 0;
         B200_CUDA(cudaMalloc(&w.partial, bytes));
         w.partial_bytes = bytes;
     }
@@ -211,6 +246,30 @@ void read_device_status(int device, unsigned int out_words[4])
     B200_CUDA(cudaDeviceSynchronize());
     B200_CUDA(cudaMemcpy(out_words, st.status, 4 * sizeof(unsigned int), cudaMemcpyDeviceToHost));
     B200_CUDA(cudaMemset(st.status, 0, 4 * sizeof(unsigned int)));
+    if(st.status_host != nullptr)
+        *st.status_host = 0u;
+    if(out_words[0] != 0u)
+    {
+        // a kernel that gave up may have left split-K tickets half counted: later launches must start from zero
+        for(auto& kv : st.ws)
+            if(kv.second.counter != nullptr)
+                B200_CUDA(cudaMemset(kv.second.counter, 0, kCounterSlots * sizeof(unsigned int)));
+    }
+    cudaSetDevice(prev);
+}
+
+void set_wait_control(int device, unsigned long long limit_ns, int withhold_scales)
+{
+    B200_CHECK(limit_ns >= 1000ull * 1000ull && limit_ns <= 10ull * kWaitLimitNs, "wait limit must be between 1 ms and 10 s");
+    int prev = 0;
+    B200_CUDA(cudaGetDevice(&prev));
+    B200_CUDA(cudaSetDevice(device));
+    std::lock_guard<std::mutex> lk(g_mutex);
+    DeviceState& st = device_state(device);
+    B200_CUDA(cudaDeviceSynchronize()); // no kernel may be reading the constants while they change
+    st.wait_ctl.limit_ns        = limit_ns;
+    st.wait_ctl.withhold_scales = withhold_scales ? 1u : 0u;
+    B200_CUDA(cudaMemcpyToSymbol(c_wait_ctl, &st.wait_ctl, sizeof(WaitControl)));
     cudaSetDevice(prev);
 }
 
@@ -417,14 +476,15 @@ static void launch_persistent_cg(int cg, int ctas, size_t smem, cudaStream_t str
         launch_persistent<KIND, SFW, 1>(ctas, smem, stream, mp, mq, msp, msq, mo, prm);
 }
 
-constexpr int kTraceCtas  = 160;
-constexpr int kTraceWords = 64 + 2 * kTraceCtas;
-
 static bool cluster_split_disabled()
 {
     static const bool off = (std::getenv("AITER_B200_NO_CLUSTER_SPLIT") != nullptr);
     return off;
 }
+
+#ifdef AITER_B200_TRACING
+constexpr int kTraceCtas  = 160;
+constexpr int kTraceWords = 64 + 2 * kTraceCtas;
 
 static void print_trace(DeviceState& st, const GemmProblem& prob, const KernelConfig& cfg, int tiles_p, int tiles_q, int splits,
                         int stages)
@@ -450,6 +510,7 @@ static void print_trace(DeviceState& st, const GemmProblem& prob, const KernelCo
                          static_cast<long long>(t[65 + 2 * b] - first));
     std::fprintf(stderr, "\n");
 }
+#endif // AITER_B200_TRACING
 
 // Packed e2m1 weight in the 16x16-byte tiled layout -> e4m3 in the same tiling (twice the K chunks).  Exact: every
 // e2m1 value is an e4m3 value.  One thread per 16-byte chunk (32 codes of one row).
@@ -557,13 +618,9 @@ void launch_gemm(const GemmProblem& prob)
                 cudaStreamIsCapturing(prob.stream, &cap);
                 if(cap == cudaStreamCaptureStatusNone)
                 {
-                    if(w.relaid != nullptr)
-                    {
-                        B200_CUDA(cudaStreamSynchronize(prob.stream));
-                        B200_CUDA(cudaFree(w.relaid));
-                        w.relaid       = nullptr;
-                        w.relaid_bytes = 0;
-                    }
+                    retire(st, w.relaid);
+                    w.relaid       = nullptr;
+                    w.relaid_bytes = 0;
                     B200_CUDA(cudaMalloc(&w.relaid, bytes));
                     w.relaid_bytes = bytes;
                     usable         = true;
@@ -623,13 +680,9 @@ void launch_gemm(const GemmProblem& prob)
                 cudaStreamIsCapturing(prob.stream, &cap);
                 if(cap == cudaStreamCaptureStatusNone)
                 {
-                    if(w.widened != nullptr)
-                    {
-                        B200_CUDA(cudaStreamSynchronize(prob.stream));
-                        B200_CUDA(cudaFree(w.widened));
-                        w.widened       = nullptr;
-                        w.widened_bytes = 0;
-                    }
+                    retire(st, w.widened);
+                    w.widened       = nullptr;
+                    w.widened_bytes = 0;
                     B200_CUDA(cudaMalloc(&w.widened, bytes));
                     w.widened_bytes = bytes;
                     usable          = true;
@@ -697,9 +750,11 @@ static void launch_gemm_locked(const GemmProblem& prob)
         local_state.status = prob.scratch->status;
     }
     DeviceState& st = (prob.scratch != nullptr) ? local_state : device_state(prob.device);
+    require_healthy(st, prob.device);
 
     KernelConfig cfg = prob.cfg;
     choose_config(prob.kind, prob.M, prob.N, prob.K, st.sm_count, cfg);
+    B200_CHECK(cfg.log2_splitk >= 0 && cfg.log2_splitk <= 8, "log2 of the K split must be between 0 and 8 (got ", cfg.log2_splitk, ")");
     {
         bool ok = false;
         for(int b : kBnMenu)
@@ -753,8 +808,9 @@ static void launch_gemm_locked(const GemmProblem& prob)
     B200_CHECK(splits == 1 || static_cast<long long>(tiles_p) * tiles_q * cg <= counter_slots,
                "split-K supports at most ", counter_slots, " output tiles here");
 
-    static const bool trace_on = (std::getenv("AITER_B200_TRACE") != nullptr);
     unsigned long long* trace = nullptr;
+#ifdef AITER_B200_TRACING
+    static const bool trace_on = (std::getenv("AITER_B200_TRACE") != nullptr);
     if(trace_on && prob.scratch == nullptr)
     {
         if(st.trace == nullptr)
@@ -762,6 +818,7 @@ static void launch_gemm_locked(const GemmProblem& prob)
         B200_CUDA(cudaMemsetAsync(st.trace, 0, kTraceWords * sizeof(unsigned long long), prob.stream));
         trace = st.trace;
     }
+#endif
 
     float* ws_partial        = nullptr;
     unsigned int* ws_counter = nullptr;
@@ -894,8 +951,10 @@ static void launch_gemm_locked(const GemmProblem& prob)
     else
         fail("no kernel instance for kind ", kkind, " with scale layout ", sfw);
 
+#ifdef AITER_B200_TRACING
     if(trace != nullptr)
         print_trace(st, prob, cfg, tiles_p, tiles_q, splits, stages);
+#endif
 }
 
 // One UE8M0 byte per (row, 128-wide K block) -> the (m/32, k/4, 32, 4) order of the MXFP8 kernel: the four 32-blocks
@@ -945,13 +1004,9 @@ static void launch_blockscale_e8m0(const BlockScaleProblem& prob)
             cudaStreamIsCapturing(prob.stream, &cap);
             B200_CHECK(cap == cudaStreamCaptureStatusNone, "the scale buffer must grow (", bytes,
                        " bytes) but the stream is being captured; run this shape once outside capture first");
-            if(w.relaid != nullptr)
-            {
-                B200_CUDA(cudaStreamSynchronize(prob.stream));
-                B200_CUDA(cudaFree(w.relaid));
-                w.relaid       = nullptr;
-                w.relaid_bytes = 0;
-            }
+            retire(st, w.relaid);
+            w.relaid       = nullptr;
+            w.relaid_bytes = 0;
             B200_CUDA(cudaMalloc(&w.relaid, bytes));
             w.relaid_bytes = bytes;
         }
@@ -1022,6 +1077,7 @@ void launch_blockscale(const BlockScaleProblem& prob)
     } restore{prev_dev, prob.device};
     std::lock_guard<std::mutex> lk(g_mutex);
     DeviceState& st = device_state(prob.device);
+    require_healthy(st, prob.device);
 
     BlockScaleParams prm{};
     prm.M           = static_cast<int>(prob.M);

@@ -126,6 +126,9 @@ struct BlockScaleProblem
 };
 void launch_blockscale(const BlockScaleProblem& prob);
 void read_device_status(int device, unsigned int out_words[4]);
+// Bound of every in-kernel wait on `device` (1 ms .. 10 s, default 1 s) and the test hook that makes the persistent
+// kernel's scale producer issue nothing, so that a wait runs out.  Synchronises the device.
+void set_wait_control(int device, unsigned long long limit_ns, int withhold_scales);
 unsigned long long launch_count();
 void count_launch(); // kernels launched outside launch.cu report themselves here
 int device_sm_count(int device);

@@ -12,6 +12,7 @@
 // the previous call's contents, and two calls that overlap on the GPU (different streams, or the same GEMM
 // launched again before the first finished on another stream) race on it.
 #include "../../include/aiter_b200.h"
+#include "abi_checks.h"
 #include "gemm_common.cuh"
 #include "launch.h"
 
@@ -76,18 +77,29 @@ extern "C" int aiter_b200_gemm_a8w8_mxfp8_noalloc(aiter_tensor_t* A, aiter_tenso
     try
     {
         const char* fn = "aiter_b200_gemm_a8w8_mxfp8_noalloc";
-        B200_CHECK(A && B && ScaleA && ScaleB && out, fn, ": all five tensors are required");
-        B200_CHECK(A->ndim == 2 && B->ndim == 2 && ScaleA->ndim == 2 && ScaleB->ndim == 2 && out->ndim == 2, fn, ": tensors must be 2-D");
-        B200_CHECK(A->device_id >= 0, fn, ": tensors must live on a GPU");
+        // the same checks as the regular MXFP8 entry point: nothing else stands between a wrong argument and a
+        // kernel reading the wrong memory
+        require_tensor(A, fn, "A", 2);
+        require_tensor(B, fn, "B", 2);
+        require_tensor(out, fn, "out", 2);
+        B200_CHECK(is_byte_dtype(A->dtype_) && is_byte_dtype(B->dtype_), fn, ": A and B must be 1-byte (fp8) tensors (got ",
+                   dtype_name(A->dtype_), ", ", dtype_name(B->dtype_), ")");
         B200_CHECK(out->dtype_ == AITER_DTYPE_bf16, fn, " only supports BFloat16 output");
         B200_CHECK(a_preshuffle == 0 || a_preshuffle == 1, fn, " a_preshuffle must be 0 or 1");
+        B200_CHECK(log2_k_split >= -1 && log2_k_split <= 8, fn, ": log2 of the K split must be between 0 and 8 (got ", log2_k_split, ")");
         const long long M = A->shape[0], N = B->shape[0], K = A->shape[1];
         B200_CHECK(K % 128 == 0, fn, " K must be divisible by 128 (got K=", K, ")");
         B200_CHECK(B->shape[1] == K, fn, ": B must be [N, K]");
-        B200_CHECK(out->shape[0] >= M && out->shape[1] == N && out->strides[1] == 1, fn, ": out must be [>=M, N], row-contiguous");
-        B200_CHECK(A->strides[1] == 1 && A->strides[0] == K && B->strides[1] == 1 && B->strides[0] == K, fn, ": A and B must be contiguous");
-        B200_CHECK(ScaleA->strides[1] == 1 && ScaleA->strides[0] == ScaleA->shape[1] && ScaleB->strides[1] == 1 &&
-                       ScaleB->strides[0] == ScaleB->shape[1], fn, ": scale tensors must be contiguous");
+        B200_CHECK(out->shape[0] >= M && out->shape[1] == N, fn, ": out must be [>=M, N]");
+        require_rows_contiguous(out, fn, "out");
+        require_dense(A, fn, "A");
+        require_dense(B, fn, "B");
+        const ScaleOperand sfa = scale_operand(ScaleA, SFW_G1250, fn, "ScaleA");
+        const ScaleOperand sfb = scale_operand(ScaleB, SFW_G1250, fn, "ScaleB");
+        require_same_device(A, B, fn, "B");
+        require_same_device(A, ScaleA, fn, "ScaleA");
+        require_same_device(A, ScaleB, fn, "ScaleB");
+        require_same_device(A, out, fn, "out");
 
         unsigned char* base = scratch_base(A->device_id);
         ExternalScratch sc;
@@ -101,9 +113,10 @@ extern "C" int aiter_b200_gemm_a8w8_mxfp8_noalloc(aiter_tensor_t* A, aiter_tenso
         B200_CUDA(cudaGetDevice(&prev));
         if(prev != A->device_id)
             B200_CUDA(cudaSetDevice(A->device_id));
-        // the array keeps the last call's contents: status and tickets must start at zero (partials are
-        // fully overwritten before they are read)
-        cudaError_t e = cudaMemsetAsync(base, 0, kStatusBytes + kCounterBytes, static_cast<cudaStream_t>(stream));
+        // the array keeps the last call's contents: the tickets must start at zero (partials are fully overwritten
+        // before they are read).  The status record is NOT cleared here: a failure stays on record until
+        // aiter_b200_noalloc_status fetches it.
+        cudaError_t e = cudaMemsetAsync(base + kStatusBytes, 0, kCounterBytes, static_cast<cudaStream_t>(stream));
         if(prev != A->device_id)
             cudaSetDevice(prev);
         B200_CUDA(e);
@@ -113,8 +126,8 @@ extern "C" int aiter_b200_gemm_a8w8_mxfp8_noalloc(aiter_tensor_t* A, aiter_tenso
         p.M = M; p.N = N; p.K = K;
         p.act    = Operand{A->ptr, M, K, K, a_preshuffle ? OPM_A2X128 : OPM_ROWMAJOR};
         p.wgt    = Operand{B->ptr, N, K, K, OPM_TILE16};
-        p.act_sf = ScaleOperand{ScaleA->ptr, SFW_G1250, ScaleA->shape[0], ScaleA->shape[1]};
-        p.wgt_sf = ScaleOperand{ScaleB->ptr, SFW_G1250, ScaleB->shape[0], ScaleB->shape[1]};
+        p.act_sf = sfa;
+        p.wgt_sf = sfb;
         p.out    = out->ptr;
         p.ldo    = out->strides[0];
         p.device = A->device_id;
@@ -122,6 +135,41 @@ extern "C" int aiter_b200_gemm_a8w8_mxfp8_noalloc(aiter_tensor_t* A, aiter_tenso
         p.cfg.log2_splitk = log2_k_split;
         p.scratch = &sc;
         launch_gemm(p);
+        aiter_b200_set_last_error("");
+        return 0;
+    }
+    catch(const std::exception& ex)
+    {
+        aiter_b200_set_last_error(ex.what());
+    }
+    catch(...)
+    {
+        aiter_b200_set_last_error("unknown C++ exception");
+    }
+    return -1;
+}
+
+// The status record of the allocation-free entry point (four words at the start of the static array: code, CTA,
+// K slice, iteration; all zero = no wait ever ran out).  Synchronises the device, copies the record out and clears
+// it.  Allocates nothing: the copy goes through the address cudaGetSymbolAddress returned at set-up.
+extern "C" int aiter_b200_noalloc_status(int device, unsigned int out_words[4])
+{
+    try
+    {
+        B200_CHECK(out_words != nullptr, "aiter_b200_noalloc_status: out_words is required");
+        unsigned char* base = scratch_base(device);
+        int prev = 0;
+        B200_CUDA(cudaGetDevice(&prev));
+        if(prev != device)
+            B200_CUDA(cudaSetDevice(device));
+        cudaError_t e = cudaDeviceSynchronize();
+        if(e == cudaSuccess)
+            e = cudaMemcpy(out_words, base, 4 * sizeof(unsigned int), cudaMemcpyDeviceToHost);
+        if(e == cudaSuccess)
+            e = cudaMemset(base, 0, kStatusBytes);
+        if(prev != device)
+            cudaSetDevice(prev);
+        B200_CUDA(e);
         aiter_b200_set_last_error("");
         return 0;
     }

@@ -2,8 +2,9 @@
 
 The bf16 table row for (M, N, K, bias, dtype, outdtype, scaleAB, bpreshuffle) names a `libtype`; the
 back-ends kept here are the ones that exist on this hardware: "opus" and "asm" (both served by the
-tcgen05 kernel family, by kernel id resp. kernel name) and "torch" (only when a table row asks for it).
-An untuned shape runs the library's own heuristic - there is no silent fallback to another library.
+tcgen05 kernel family, by kernel id resp. kernel name).  A row that names any other back-end (the
+reference's tables also know "torch", "hipblaslt", "triton", ...) is an error: nothing here dispatches to
+another library.  An untuned shape runs the library's own heuristic.
 """
 from __future__ import annotations
 
@@ -11,7 +12,6 @@ import logging
 import os
 
 import torch
-import torch.nn.functional as F
 from torch import Tensor
 
 from . import dtypes
@@ -34,11 +34,6 @@ def get_GEMM_A16W16_config(M: int, N: int, K: int, bias: bool, dtype: str, otype
     return default
 
 
-def torch_gemm(inp, weights, solidx, bias=None, otype=None, scale_a=None, scale_b=None, scale_c=None, bpreshuffle=False, config=None):
-    assert not bpreshuffle, "bpreshuffle is not supported in torch_gemm!"
-    return F.linear(inp, weights, bias)
-
-
 def asm_gemm(inp, weights, solidx, bias=None, otype=None, scale_a=None, scale_b=None, scale_c=None, bpreshuffle=False, config=None):
     kernelName = config.get("kernelName") if config else None
     splitK = config.get("splitK") if config else None
@@ -59,7 +54,7 @@ def opus_gemm_backend(inp, weights, solidx, bias=None, otype=None, scale_a=None,
     return Y
 
 
-solMap = {"torch": torch_gemm, "asm": asm_gemm, "opus": opus_gemm_backend}
+solMap = {"asm": asm_gemm, "opus": opus_gemm_backend}
 
 
 def gemm_a16w16(A: Tensor, B: Tensor, bias: Tensor | None = None, otype: torch.dtype | None = None,

@@ -161,6 +161,11 @@ AITER_B200_API int opus_gemm_workspace_init(void);
 AITER_B200_API int aiter_b200_gemm_a8w8_mxfp8_noalloc(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* ScaleA,
                                                       aiter_tensor_t* ScaleB, aiter_tensor_t* out, int a_preshuffle,
                                                       int log2_k_split, void* stream);
+/* The status record of the entry point above (it lives in the same fixed array, not in the record
+ * aiter_b200_device_status reads): 4 words, all zero unless a bounded wait inside one of its kernels ran out
+ * (code, block, split, iteration).  Synchronises the device, copies the record out and clears it; allocates
+ * nothing.  A record stays in place across later calls until it is fetched here.  No counterpart in the reference. */
+AITER_B200_API int aiter_b200_noalloc_status(int device, unsigned int out_words[4]);
 
 /* ---- dynamic 1x32 MX quantisation of activations (the step in front of the GEMM) ----
  * Replaces dynamic_per_group_scaled_quant (csrc/include/quant.h:29-35, kernel csrc/kernels/quant_mxfp4.cu:88-212;
@@ -175,8 +180,16 @@ AITER_B200_API int dynamic_per_group_scaled_quant(aiter_tensor_t* out, aiter_ten
 
 /* ---- library state ---- */
 /* Copies the 4-word device status record of `device` (0 = healthy; non-zero = a bounded wait
- * inside a kernel expired: code, block, split, iteration) and clears it.  Synchronises the device. */
+ * inside a kernel expired: code, block, split, iteration) and clears it.  Synchronises the device.
+ * While a non-zero record is pending every GEMM entry point on that device fails with a message that
+ * names the code (the kernels mirror it into a pinned host word the launcher reads), so a caller that
+ * never polls still learns of an incomplete output at its next call. */
 AITER_B200_API int aiter_b200_device_status(int device, unsigned int out_words[4]);
+/* Test and diagnosis hook (no counterpart in the reference): the wall-time bound of every in-kernel wait on
+ * `device`, 1 ms .. 10 s (default 1 s), and a switch that makes the scale producer of the MX GEMM kernel issue
+ * nothing, so that the waits behind it run out after that bound, the kernel records its status and returns by
+ * itself.  Used to exercise the time-out path without faulting or hanging anything.  Synchronises the device. */
+AITER_B200_API int aiter_b200_debug_wait_control(int device, unsigned long long limit_ns, int withhold_scales);
 /* Human-readable list of the kernel configurations behind `kernelName`/`kernelId`. */
 AITER_B200_API const char* aiter_b200_kernel_list(void);
 /* Name of the configuration the heuristic picks for a problem (kind: 0 bf16, 1 mxfp8, 2 mxfp4, 3 mxfp8 x mxfp4). */

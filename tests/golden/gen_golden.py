@@ -116,6 +116,40 @@ def ref_gemm_mxfp8(fp4_utils, intype, a, b, sa, sb):
     return ((af * saf) @ (bf * sbf).T).to(torch.bfloat16)
 
 
+def ref_gemm_blockscale(fp4_utils, x, weight, x_scale, w_scale, block_shape=(128, 128)):
+    """op_tests/test_gemm_a8w8_blockscale.py:30-56 (einops.rearrange written out as permute + reshape)."""
+    block_n, block_k = block_shape
+    m, k = x.shape
+    n = weight.shape[0]
+    scale_n, scale_k = (n + block_n - 1) // block_n, (k + block_k - 1) // block_k
+    if x_scale.dtype == torch.float8_e8m0fnu:
+        x_scale = fp4_utils.e8m0_to_f32(x_scale)
+    if w_scale.dtype == torch.float8_e8m0fnu:
+        w_scale = fp4_utils.e8m0_to_f32(w_scale)
+    xf = (x.to(x_scale.dtype).view(m, k // block_k, block_k) * x_scale.unsqueeze(-1)).view(m, k)
+    ws = w_scale.view(-1, 1).repeat(1, block_n * block_k).view(scale_n, scale_k, block_n, block_k)
+    ws = ws.permute(0, 2, 1, 3).reshape(scale_n * block_n, scale_k * block_k)[:n, :k]
+    wf = weight.to(ws.dtype) * ws
+    return torch.nn.functional.linear(xf.to(torch.float32), wf.to(torch.float32)).to(torch.bfloat16)
+
+
+def ref_quant_mxfp8_blockN(fp4_utils, MxDtypeInt, x_f32, block=128):
+    """op_tests/test_f4gemm.py:73-88: fp8 e4m3 data + one RoundUp E8M0 scale per 128 output columns."""
+    M, N = x_f32.shape
+    xb = x_f32.reshape(M, N // block, block)
+    amax = xb.abs().amax(dim=-1).clamp(min=torch.finfo(torch.float32).tiny)
+    scale = fp4_utils.f32_to_mx_e8m0_scale(amax, mode=1, dtype=MxDtypeInt.FP8_E4M3)
+    q = (xb / fp4_utils.e8m0_to_f32(scale).unsqueeze(-1)).reshape(M, N).to(torch.float8_e4m3fn)
+    return q, scale
+
+
+def ref_pack_mxfp8_out_scale(rm):
+    """Inverse of unpack_mxfp8_out_scale (aiter/ops/gemm_op_a4w4.py:365-380): row-major [M, N/128] -> the packed
+    (M/64, N/128, 16, 4) byte order."""
+    M, sn = rm.shape
+    return rm.view(torch.uint8).reshape(M // 64, 4, 16, sn).permute(0, 3, 2, 1).contiguous().reshape(M, sn)
+
+
 def bits16(t):
     return t.view(torch.int16).numpy().view(np.uint16).copy()
 
@@ -215,10 +249,37 @@ def main(ref_root: str, out_path: str):
     g["gemm_a8w8_out"] = bits16(ref_gemm_mxfp8(fp4_utils, "a8w8", xa8, wb8, xs8, ws8))
     g["gemm_a8w4_out"] = bits16(ref_gemm_mxfp8(fp4_utils, "a8w4", xa8, wb4, xs8, ws4))
 
+    # ---- fp8 x fp8 with 128-block scales (fp32 and e8m0 scale tensors)
+    torch.manual_seed(1)
+    bx = (torch.randn(40, 384) * 2).to(torch.float8_e4m3fn)
+    bw = (torch.randn(200, 384) * 2).to(torch.float8_e4m3fn)
+    bxs = torch.rand(40, 3) + 0.25
+    bws = torch.rand(2, 3) + 0.25
+    g["bs_x"], g["bs_w"] = bx.view(torch.uint8).numpy(), bw.view(torch.uint8).numpy()
+    g["bs_xs"], g["bs_ws"] = bxs.numpy(), bws.numpy()
+    g["bs_out"] = bits16(ref_gemm_blockscale(fp4_utils, bx, bw, bxs, bws))
+    exs = torch.randint(124, 131, (40, 3), dtype=torch.uint8)
+    ews = torch.randint(124, 131, (2, 3), dtype=torch.uint8)
+    g["bs_xs_e8m0"], g["bs_ws_e8m0"] = exs.numpy(), ews.numpy()
+    g["bs_out_e8m0"] = bits16(ref_gemm_blockscale(fp4_utils, bx, bw, exs.view(torch.float8_e8m0fnu), ews.view(torch.float8_e8m0fnu)))
+
+    # ---- low-precision GEMM outputs: the re-quantisation of an fp32 result (op_tests/test_f4gemm.py:73-88,211-217)
+    torch.manual_seed(2)
+    y = torch.randn(128, 256) * torch.exp2(torch.randint(-6, 7, (128, 1)).float())
+    y[0, :128] = 0.0        # an all-zero 128-column block
+    y[1, :128] = 448.0      # exact maximum: the scale must not bump
+    y[2, 5] = 3.0e4
+    g["requant_in"] = y.numpy()
+    q8, s8 = ref_quant_mxfp8_blockN(fp4_utils, MxDtypeInt, y)
+    g["requant_fp8_data"], g["requant_fp8_scale"] = q8.view(torch.uint8).numpy(), s8.view(torch.uint8).numpy()
+    g["requant_fp8_scale_packed"] = ref_pack_mxfp8_out_scale(s8).numpy()
+    g["requant_fp4_data"] = fp4_utils.f32_to_mxfp4(y).view(torch.uint8).numpy()
+
     np.savez_compressed(out_path, **g)
     print("wrote", out_path, os.path.getsize(out_path), "bytes,", len(g), "arrays")
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
-    main(ref, os.path.join(os.path.dirname(os.path.abspath(__file__)), "mx_golden.npz"))
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/gen_golden.py /path/to/reference [output.npz]")
+    main(sys.argv[1], sys.argv[2] if len(sys.argv) > 2 else os.path.join(os.path.dirname(os.path.abspath(__file__)), "mx_golden.npz"))

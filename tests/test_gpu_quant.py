@@ -92,3 +92,24 @@ def test_quant_rejects_what_is_not_built(ab):
     with pytest.raises(RuntimeError, match="group_size"):
         ab.dynamic_per_group_scaled_quant(torch.empty(4, 32, dtype=torch.uint8, device="cuda"), x,
                                           torch.empty(4, 2, dtype=torch.uint8, device="cuda"), 64, False)
+
+
+def test_torch_quantisers_give_the_same_bytes_on_cpu_and_gpu(ab):
+    """The full-size parity tests and bench.py quantise on the GPU with the torch path and check against a CPU oracle:
+    that is only sound if the torch path produces the same bytes on both devices (elementwise bit operations,
+    divisions by powers of two and dtype casts).  300 x 1024 with every edge case of the quantiser tests."""
+    x = bf16_input(300, 1024, seed=7, kind="edges")
+    x[10:200] = bf16_input(190, 1024, seed=8, kind="randn")
+    for fn, kw in ((ab.per_1x32_f4_quant, {}), (ab.per_1x32_f8_scale_f8_quant, {"scale_type": ab.dtypes.fp8_e8m0})):
+        q_cpu, s_cpu = fn(x, **kw)
+        q_gpu, s_gpu = fn(x.cuda(), **kw)
+        assert torch.equal(q_cpu.view(torch.uint8), q_gpu.view(torch.uint8).cpu()), f"{fn.__name__}: data bytes differ between cpu and cuda"
+        assert torch.equal(s_cpu.view(torch.uint8), s_gpu.view(torch.uint8).cpu()), f"{fn.__name__}: scale bytes differ between cpu and cuda"
+    # and the oracle agrees with both (the CPU tests pin this on the golden vectors; here on this tensor)
+    q4, s4 = ox.quant_mxfp4(x.float().numpy())
+    q, s = ab.per_1x32_f4_quant(x.cuda())
+    assert np.array_equal(q.view(torch.uint8).cpu().numpy(), q4) and np.array_equal(s.view(torch.uint8).cpu().numpy(), s4)
+    q8, s8 = ox.quant_mxfp8(x.float().numpy())
+    q, s = ab.per_1x32_f8_scale_f8_quant(x.cuda(), scale_type=ab.dtypes.fp8_e8m0)
+    ok = np.array_equal(q.view(torch.uint8).cpu().numpy(), q8) and np.array_equal(s.view(torch.uint8).cpu().numpy(), s8)
+    assert ok

@@ -56,6 +56,12 @@ def test_errors_cross_the_abi_as_runtime_error(ab):
         ab.opus_gemm_a16w16_tune(x, x, torch.zeros((1, 4, 4), dtype=torch.bfloat16), None, 999, 0)
     with pytest.raises(ValueError, match="must be 3D"):
         ab.opus_gemm_a16w16_tune(torch.zeros(4, 64), torch.zeros(4, 64), torch.zeros(4, 4))
+    # an out-of-range K split is refused before it can reach a shift (log2 of the split: 0..8, -1 = library's choice)
+    p4 = torch.zeros((32, 64), dtype=torch.uint8)
+    with pytest.raises(RuntimeError, match="gemm_a4w4_asm failed: .*K split must be between 0 and 8"):
+        ab.gemm_a4w4_asm(p4, p4, s, s, torch.zeros((32, 32), dtype=torch.bfloat16), log2_k_split=40)
+    with pytest.raises(RuntimeError, match="aiter_b200_gemm_a8w8_mxfp8_noalloc failed: .*must live on a GPU"):
+        ab.gemm_a8w8_mxfp8_noalloc(a, a, s, s, torch.zeros((4, 4), dtype=torch.bfloat16), a_preshuffle=False)
 
 
 def test_heuristic_and_kernel_menu(ab):

@@ -80,6 +80,25 @@ def test_gemm_references(golden):
     assert ox.mismatch_ratio(golden["gemm_a8w4_out"], out, 1e-2, 1e-2) == 0.0
 
 
+def test_blockscale_reference(golden):
+    out = ox.gemm_a8w8_blockscale_ref(golden["bs_x"], golden["bs_w"], golden["bs_xs"], golden["bs_ws"])
+    assert ox.mismatch_ratio(golden["bs_out"], out, 1e-2, 1e-2) == 0.0
+    out = ox.gemm_a8w8_blockscale_ref(golden["bs_x"], golden["bs_w"], ox.e8m0_to_f32(golden["bs_xs_e8m0"]), ox.e8m0_to_f32(golden["bs_ws_e8m0"]))
+    assert ox.mismatch_ratio(golden["bs_out_e8m0"], out, 1e-2, 1e-2) == 0.0
+
+
+def test_requantising_outputs_bit_exact(golden):
+    y = golden["requant_in"]
+    q8, s8 = ox.requant_mxfp8_blockN(y)
+    assert np.array_equal(s8, golden["requant_fp8_scale"])
+    assert np.array_equal(q8, golden["requant_fp8_data"])
+    assert s8[0, 0] == 1 and s8[1, 0] == 127  # all-zero block -> byte 1 (amax clamped to FLT_MIN); amax 448 -> 2^0
+    packed = ox.pack_mxfp8_out_scale(s8)
+    assert np.array_equal(packed, golden["requant_fp8_scale_packed"])
+    assert np.array_equal(ox.unpack_mxfp8_out_scale(packed, *y.shape), s8)
+    assert np.array_equal(ox.requant_fp4(y), golden["requant_fp4_data"])
+
+
 def test_constant_input_known_answer():
     # A = B = 0.5 with unit scales: every output is 0.25*K (op_tests/test_mxfp8fp4gemm.py:75-98)
     k = 256
