@@ -390,7 +390,7 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
     tc_fence_before_sync();
     __syncthreads();
     if(prm.cluster)
-        cluster_sync_all(); // the reducing CTA's barrier exists before any slice is sent to it
+        cluster_arrive_release(); // "my barriers exist": checked by the promotion warps before their first remote access
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
     // programmatic dependent launch: the set-up above may overlap the previous kernel's tail; nothing below touches
@@ -552,6 +552,8 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
                 mbar_arrive(part_empty_bar(b));
         }
         bool owns = true; // this thread stores its output column
+        if(prm.cluster)
+            cluster_wait_acquire(); // every CTA of the cluster has initialised its barriers (they all ran a K loop since)
         if(ok && prm.cluster)
         {
             // Cluster split, reduce-scatter: CTA z adds up columns [z * per, (z + 1) * per) of the tile (per = 128 /
@@ -668,7 +670,7 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
                 {
                     tma_store_2d(&map_o, smem_base + (warp - 2) * (XR * 64), (n) * 2, 0);
                     bulk_commit_group();
-                    bulk_wait_group<0>(); // complete before the CTA retires
+                    bulk_wait_group_read<0>(); // the store has read its source before the CTA retires (see gemm_persistent.cuh)
                 }
             }
         }
@@ -682,8 +684,8 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
         tc_fence_before_sync();
     }
     __syncthreads();
-    if(prm.cluster)
-        cluster_sync_all(); // nobody leaves while a slice may still be on its way to the reducing CTA
+    // no cluster rendezvous at the end: the only remote traffic into a CTA are the partial sums of the columns it owns,
+    // and the warp that owns them has waited for every byte (red barrier) before the CTA gets here
     if(warp == 1)
     {
         tc_fence_after_sync();

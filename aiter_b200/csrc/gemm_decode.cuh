@@ -1,0 +1,489 @@
+// Decode-shape GEMM (at most 64 activation rows) for sm_100a: a deliberately small kernel.
+//
+//   D[n][m] = sum_k W[n][k] * X[m][k]      W: 128 weight rows per CTA on the TMEM lanes, X: the M <= 64 activation rows
+//                                          on the N side of the MMA (16, 32 or 64 columns); out[m][n] is stored transposed
+//
+// Why a second kernel beside the persistent one: a decode GEMM moves a few MB and lasts a few microseconds, so what it
+// costs is not bytes or flops but the chain of latencies from launch to the last store, paid by single threads.  This
+// kernel is built to keep that chain short:
+//   * little code: one tile per CTA, one operand arrangement (weights on the 128-row slot), no pairs, no work list, so
+//     the lone threads that run each role meet few instruction-cache misses;
+//   * 224 threads, <= 146 registers, <= 110 KB of shared memory and <= 256 TMEM columns: two CTAs fit on an SM, so the
+//     CTAs of the next launch in the stream (programmatic dependent launch) set up - barriers, TMEM, tensor-map
+//     prefetch - while the previous launch still runs, and a grid of up to 296 tiles is one wave;
+//   * the four scale warps are also the epilogue warps (same TMEM lane quarters), and one thread issues both operand
+//     loads of a K tile;
+//   * K split across the CTAs of a cluster (2 or 4) as a reduce-scatter through distributed shared memory, with the
+//     cluster barrier split into an early relaxed arrive and a late wait, so nobody idles at a rendezvous.
+//
+// Warps: 0 operand producer, 1 MMA issuer + TMEM owner, 2..5 scales then epilogue (one per TMEM lane quarter),
+//        6 raw-scale producer.  Every barrier wait is bounded (bounded_wait).
+#pragma once
+#include "gemm_common.cuh"
+
+namespace b200 {
+
+constexpr int kDecodeThreads   = 224;
+constexpr int kDecodeMaxStages = 8;
+
+struct DecodeParams
+{
+    int rows_p, rows_q;      // weight rows (the problem's N), activation rows (the problem's M)
+    int num_k_iters;         // ceil(K bytes / 128)
+    int kblocks;             // valid 32-element scale blocks along K
+    int bn;                  // MMA N: 16, 32 or 64 (>= rows_q)
+    int stages;
+    int p_mode, q_mode;      // OperandMode of the weights / activations
+    int csplit;              // K slices = CTAs per cluster: 1, 2 or 4
+    int tma_store;           // the output leaves as per-warp TMA tile stores (map_out is valid)
+    int tmem_cols;           // allocation (power of two)
+    uint32_t stage_bytes, q_off, sfp_off, sfq_off, red_off, bar_off;
+    __nv_bfloat16* out;
+    long long ldo;
+    const void* bias;        // indexed by weight row, or null
+    int bias_is_bf16;
+    float alpha, beta;
+    unsigned int* status;
+};
+
+// TMEM columns of one stage's scales: [P atom a: 4 columns][Q atom a: 4 columns], a < atoms per K tile
+__host__ __device__ constexpr int decode_sf_cols(int kind) { return kind == KIND_BF16 ? 0 : (kind == KIND_MXF4 ? 16 : 8); }
+
+template <int KIND, int SFW>
+__global__ void __launch_bounds__(kDecodeThreads, 2)
+gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+                   const __grid_constant__ CUtensorMap map_sfp, const __grid_constant__ CUtensorMap map_sfq,
+                   const __grid_constant__ CUtensorMap map_out, const DecodeParams prm)
+{
+    constexpr bool kScaled = (KIND != KIND_BF16);
+    constexpr int kAtomsK  = (KIND == KIND_MXF4) ? 2 : 1; // 4-k-block scale atoms per 128-byte K tile
+    constexpr int kSfCols  = decode_sf_cols(KIND);
+    constexpr bool kE8     = (SFW == SFW_E8M0_SHUFFLE);
+    constexpr int kSfChunk = kE8 ? 256 : 128 * kAtomsK;   // raw scale bytes per 32-row group per K tile
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen        = smem_raw + (smem_base - smem_u32(smem_raw));
+    const int bn             = prm.bn;
+    const int S              = prm.stages;
+    const uint32_t bar_base  = smem_base + prm.bar_off;
+    auto full_bar            = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar           = [&](int s) { return bar_base + 64u + 8u * s; };
+    auto sfraw_bar           = [&](int s) { return bar_base + 128u + 8u * s; };
+    const uint32_t acc_bar   = bar_base + 192u;
+    const uint32_t red_bar   = bar_base + 200u;
+    uint32_t* tmem_ptr_smem    = reinterpret_cast<uint32_t*>(smem_gen + prm.bar_off + 208);
+    volatile uint32_t* abort_f = reinterpret_cast<volatile uint32_t*>(smem_gen + prm.bar_off + 212);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int csplit     = prm.csplit;
+    const uint32_t zrank = csplit > 1 ? cluster_ctarank() : 0u;           // this CTA's K slice
+    const int tile       = csplit > 1 ? static_cast<int>(blockIdx.x) / csplit : static_cast<int>(blockIdx.x);
+    const int row_p0     = tile * kTileP;
+    const int it_beg     = static_cast<int>(static_cast<uint32_t>(prm.num_k_iters) * zrank / static_cast<uint32_t>(csplit));
+    const int n_iters    = static_cast<int>(static_cast<uint32_t>(prm.num_k_iters) * (zrank + 1u) / static_cast<uint32_t>(csplit)) - it_beg;
+    const uint32_t per   = static_cast<uint32_t>(kTileP / csplit); // rows of the tile this CTA adds up and stores (whole warps)
+
+    if(threadIdx.x == 0)
+    {
+        for(int s = 0; s < S; ++s)
+        {
+            mbar_init(full_bar(s), kScaled ? 5 : 1); // the operand producer's expect_tx arrival + one arrival per scale warp
+            mbar_init(empty_bar(s), 1);
+            mbar_init(sfraw_bar(s), 1);
+        }
+        mbar_init(acc_bar, 1);
+        mbar_init(red_bar, 1);
+        *abort_f = 0;
+        mbar_fence_init();
+        fence_proxy_async_smem();
+        if(csplit > 1) // the other slices' partial sums of this CTA's rows: posted before anybody can send
+            mbar_arrive_expect_tx(red_bar, static_cast<uint32_t>(csplit - 1) * per * static_cast<uint32_t>(bn) * 4u);
+    }
+    if(warp == 6 && lane == 0)
+    {
+        tma_prefetch_desc(&map_p);
+        tma_prefetch_desc(&map_q);
+        if(kScaled)
+        {
+            tma_prefetch_desc(&map_sfp);
+            tma_prefetch_desc(&map_sfq);
+        }
+        if(prm.tma_store)
+            tma_prefetch_desc(&map_out);
+    }
+    if(warp == 1)
+    {
+        tmem_alloc(smem_u32(tmem_ptr_smem), static_cast<uint32_t>(prm.tmem_cols));
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if(csplit > 1)
+        cluster_arrive_relaxed(); // "my barriers exist" (made visible by the init fence above); checked before the first remote access
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_ptr_smem;
+    // Programmatic dependent launch: everything above may run while the previous kernel of the stream still does;
+    // nothing below touches global memory before that kernel has completed.
+    grid_dependency_wait();
+    grid_launch_dependents();
+
+    if(warp == 0)
+    {
+        // ------------------------------------------------------------------ operand producer
+        if(lane == 0)
+        {
+            const uint32_t q_bytes = static_cast<uint32_t>(bn) * kTileKBytes;
+            int s = 0;
+            uint32_t phase = 0;
+            int kt = it_beg;
+            for(int i = 0; i < n_iters; ++i, ++kt)
+            {
+                if(!bounded_wait(empty_bar(s), phase ^ 1u, abort_f, prm.status, ST_TIMEOUT_PRODUCER, i))
+                    break;
+                const uint32_t stage = smem_base + s * prm.stage_bytes;
+                const uint32_t bar   = full_bar(s);
+                mbar_arrive_expect_tx(bar, kTileP * kTileKBytes + q_bytes);
+                issue_operand_load(prm.p_mode, stage, &map_p, bar, row_p0, kt);
+                issue_operand_load(prm.q_mode, stage + prm.q_off, &map_q, bar, 0, kt);
+                if(++s == S)
+                {
+                    s = 0;
+                    phase ^= 1u;
+                }
+            }
+            if(*abort_f)
+            {
+                // give loads still in flight time to land before this CTA's shared memory is released (bounded)
+                const uint64_t t0 = global_timer_ns();
+                while(global_timer_ns() - t0 < 200000ull) {}
+            }
+        }
+    }
+    else if(warp == 6)
+    {
+        // ------------------------------------------------------------------ raw scale producer
+        // (test hook: with c_wait_ctl.withhold_scales set this role issues nothing, so the waits behind it run out)
+        if(kScaled && lane == 0 && c_wait_ctl.withhold_scales == 0u)
+        {
+            const uint32_t sfp_bytes = 4u * kSfChunk;
+            const uint32_t sfq_bytes = static_cast<uint32_t>((bn + 31) / 32) * kSfChunk;
+            int s = 0;
+            uint32_t phase = 0;
+            int kc = it_beg * kSfChunk;
+            for(int i = 0; i < n_iters; ++i, kc += kSfChunk)
+            {
+                if(!bounded_wait(empty_bar(s), phase ^ 1u, abort_f, prm.status, ST_TIMEOUT_PRODUCER, 0x20000 + i))
+                    break;
+                const uint32_t stage = smem_base + s * prm.stage_bytes;
+                const uint32_t bar   = sfraw_bar(s);
+                mbar_arrive_expect_tx(bar, sfp_bytes + sfq_bytes);
+                tma_load_2d(stage + prm.sfp_off, &map_sfp, bar, kc, row_p0 >> 5);
+                tma_load_2d(stage + prm.sfq_off, &map_sfq, bar, kc, 0);
+                if(++s == S)
+                {
+                    s = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    }
+    else if(warp == 1)
+    {
+        // ------------------------------------------------------------------ MMA issuer
+        if(lane == 0)
+        {
+            uint32_t idesc;
+            if(KIND == KIND_BF16)
+                idesc = idesc_bf16(kTileP, bn);
+            else if(KIND == KIND_MXF8)
+                idesc = idesc_block_scaled(0, 0, kTileP, bn);
+            else
+                idesc = idesc_block_scaled(1, 1, kTileP, bn);
+            const bool p_tiled   = (prm.p_mode == OPM_TILE16);
+            const bool q_tiled   = (prm.q_mode == OPM_TILE16);
+            const uint32_t p_lbo = p_tiled ? kTileP * 16u : 16u, p_sbo = p_tiled ? 128u : 1024u, p_lay = p_tiled ? 0u : 2u;
+            const uint32_t q_lbo = q_tiled ? bn * 16u : 16u, q_sbo = q_tiled ? 128u : 1024u, q_lay = q_tiled ? 0u : 2u;
+            const uint32_t p_step = (p_tiled ? 2u * kTileP * 16u : 32u) >> 4;
+            const uint32_t q_step = (q_tiled ? 2u * bn * 16u : 32u) >> 4;
+            // descriptor words once; per MMA only an add on the address field (this thread pays every instruction's latency)
+            const uint32_t p_hi  = static_cast<uint32_t>(make_smem_desc(0, p_lbo, p_sbo, p_lay) >> 32);
+            const uint32_t q_hi  = static_cast<uint32_t>(make_smem_desc(0, q_lbo, q_sbo, q_lay) >> 32);
+            const uint32_t p_lo0 = static_cast<uint32_t>(make_smem_desc(smem_base, p_lbo, p_sbo, p_lay));
+            const uint32_t q_lo0 = static_cast<uint32_t>(make_smem_desc(smem_base + prm.q_off, q_lbo, q_sbo, q_lay));
+            const uint32_t stage_step = prm.stage_bytes >> 4;
+            uint32_t idk[4];
+#pragma unroll
+            for(int k = 0; k < 4; ++k)
+                idk[k] = (KIND == KIND_BF16) ? idesc
+                         : (KIND == KIND_MXF4) ? idesc_with_sf(idesc, (k & 1) * 2, (k & 1) * 2)
+                                               : idesc_with_sf(idesc, k, k);
+            const uint32_t sf0 = tmem_base + bn; // the scale buffers follow the accumulator (bn columns)
+            bool ok = true;
+            int s = 0;
+            uint32_t phase = 0;
+            for(int i = 0; i < n_iters; ++i)
+            {
+                ok = bounded_wait(full_bar(s), phase, abort_f, prm.status, ST_TIMEOUT_MMA_FULL, i);
+                if(!ok)
+                    break;
+                tc_fence_after_sync();
+                const uint32_t p_lo = p_lo0 + s * stage_step;
+                const uint32_t q_lo = q_lo0 + s * stage_step;
+                const uint32_t tsfp = sf0 + s * kSfCols;
+                const uint32_t tsfq = tsfp + 4 * kAtomsK;
+#pragma unroll
+                for(int k = 0; k < 4; ++k)
+                {
+                    const uint64_t pd  = pack_u64(p_lo + k * p_step, p_hi);
+                    const uint64_t qd  = pack_u64(q_lo + k * q_step, q_hi);
+                    const uint32_t acc = (k > 0) ? 1u : static_cast<uint32_t>(i > 0);
+                    if(KIND == KIND_BF16)
+                        mma_f16(tmem_base, pd, qd, idk[k], acc);
+                    else if(KIND == KIND_MXF8)
+                        mma_mxf8f6f4(tmem_base, pd, qd, idk[k], acc, tsfp, tsfq);
+                    else
+                        mma_mxf4(tmem_base, pd, qd, idk[k], acc, tsfp + (k >> 1) * 4, tsfq + (k >> 1) * 4);
+                }
+                tc_commit(empty_bar(s));
+                if(++s == S)
+                {
+                    s = 0;
+                    phase ^= 1u;
+                }
+            }
+            if(ok)
+                tc_commit(acc_bar);
+        }
+    }
+    else
+    {
+        // ------------------------------------------------------------------ warps 2..5: scales, then the epilogue
+        const int quarter    = warp & 3;
+        const int p_local    = quarter * 32 + lane;
+        const uint32_t tlane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        bool ok = true;
+        if(kScaled)
+        {
+            const int q_groups = (bn + 31) / 32; // 1 or 2 groups of 32 activation rows (the weights always stage 4)
+            const int r16 = lane & 15, hi = lane >> 4;
+            int s = 0;
+            uint32_t phase = 0;
+            int kt = it_beg;
+            for(int i = 0; i < n_iters && ok; ++i, ++kt)
+            {
+                ok = bounded_wait(sfraw_bar(s), phase, abort_f, prm.status, ST_TIMEOUT_SFWARP, i);
+                ok = __all_sync(0xffffffffu, ok);
+                if(!ok)
+                    break;
+                const uint8_t* stage = smem_gen + s * prm.stage_bytes;
+                uint32_t t[kSfCols > 0 ? kSfCols : 1];
+#pragma unroll
+                for(int c = 0; c < kSfCols; ++c)
+                    t[c] = 0x7F7F7F7Fu;
+                if(kE8)
+                {
+                    // raw: per 32-row group j a 256-byte chunk, byte (k%4)*64 + (m%16)*4 + ((k%8)/4)*2 + (m%32)/16: this lane's
+                    // row has its eight scale bytes in four words (one per k%4), at byte kh*2 + (row half)
+                    const bool tail    = (kt * 8 + 8 > prm.kblocks);
+                    const uint32_t sel = hi ? 0x7351u : 0x6240u;
+                    uint32_t raw[6][4];
+#pragma unroll
+                    for(int j = 0; j < 6; ++j)
+                    {
+                        const uint32_t* grp = reinterpret_cast<const uint32_t*>(stage + (j < 4 ? prm.sfp_off + j * 256 : prm.sfq_off + (j - 4) * 256));
+#pragma unroll
+                        for(int c = 0; c < 4; ++c)
+                            raw[j][c] = (j < 4 + q_groups) ? grp[c * 16 + r16] : 0u;
+                    }
+#pragma unroll
+                    for(int j = 0; j < 6; ++j)
+                    {
+                        const uint32_t lo_part = __byte_perm(raw[j][0], raw[j][1], sel); // k%4 = 0,1 for both k halves
+                        const uint32_t hi_part = __byte_perm(raw[j][2], raw[j][3], sel); // k%4 = 2,3
+                        uint32_t v0 = __byte_perm(lo_part, hi_part, 0x5410);             // k-blocks 0..3 of this row
+                        uint32_t v1 = __byte_perm(lo_part, hi_part, 0x7632);             // k-blocks 4..7
+                        if(tail)
+                        {
+                            // scale bytes beyond K read as 2^0 (their data bytes are zero-filled by the tile loads)
+                            const int valid0  = min(max(prm.kblocks - kt * 8, 0), 4);
+                            const int valid1  = min(max(prm.kblocks - kt * 8 - 4, 0), 4);
+                            const uint32_t m0 = valid0 >= 4 ? 0xFFFFFFFFu : ((1u << (8 * valid0)) - 1u);
+                            const uint32_t m1 = valid1 >= 4 ? 0xFFFFFFFFu : ((1u << (8 * valid1)) - 1u);
+                            v0 = (v0 & m0) | (0x7F7F7F7Fu & ~m0);
+                            v1 = (v1 & m1) | (0x7F7F7F7Fu & ~m1);
+                        }
+                        if(j < 4 + q_groups && kAtomsK == 2)
+                        {
+                            t[(j < 4) ? j : 8 + (j - 4)]      = v0; // K atom 0: P columns 0..3, Q columns 8..11
+                            t[(j < 4) ? 4 + j : 12 + (j - 4)] = v1; // K atom 1: P columns 4..7, Q columns 12..15
+                        }
+                    }
+                }
+                else
+                {
+                    // raw: [group][K atom a][row 0..31][4 k-blocks]: one word per row per K atom
+#pragma unroll
+                    for(int j = 0; j < 6; ++j)
+#pragma unroll
+                        for(int a = 0; a < kAtomsK; ++a)
+                        {
+                            const uint32_t* grp = reinterpret_cast<const uint32_t*>(stage + (j < 4 ? prm.sfp_off + j * kSfChunk : prm.sfq_off + (j - 4) * kSfChunk));
+                            const int col       = (j < 4) ? a * 4 + j : 4 * kAtomsK + a * 4 + (j - 4);
+                            if(j < 4 + q_groups)
+                                t[col] = grp[a * 32 + lane];
+                        }
+                }
+                const uint32_t tsf = tlane + bn + s * kSfCols;
+                if(kSfCols == 16)
+                    tmem_st_x16(tsf, t);
+                else
+                    tmem_st_x8(tsf, t);
+                tmem_st_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if(lane == 0)
+                    mbar_arrive(full_bar(s));
+                if(++s == S)
+                {
+                    s = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+
+        // ---- epilogue: this thread holds row p_local of the tile (one weight row = one output column), bn values
+        if(ok)
+        {
+            ok = bounded_wait(acc_bar, 0, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, 0);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if(ok)
+        {
+            tc_fence_after_sync();
+            float v[64];
+            {
+                uint32_t r[32] = {};
+                if(bn == 16)
+                    tmem_ld_x16(tlane, r);
+                else
+                    tmem_ld_x32(tlane, r);
+                tmem_ld_wait();
+#pragma unroll
+                for(int j = 0; j < 32; ++j)
+                    v[j] = __uint_as_float(r[j]);
+                if(bn == 64)
+                {
+                    tmem_ld_x32(tlane + 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for(int j = 0; j < 32; ++j)
+                        v[32 + j] = __uint_as_float(r[j]);
+                }
+            }
+            bool mine = true; // this warp adds up and stores its rows
+            if(csplit > 1)
+            {
+                // Reduce-scatter over the cluster: CTA z owns rows [z * per, (z + 1) * per) of the tile (whole warps).  A warp
+                // whose rows belong to another CTA sends its partial sums to that CTA's shared memory ([source slice][row][bn
+                // floats], bytes counted on that CTA's red barrier) and is done; an owning warp waits for the other slices.
+                cluster_wait_acquire(); // every CTA of the cluster has initialised its barriers (they all ran a K loop since)
+                const uint32_t owner = static_cast<uint32_t>(p_local) / per;
+                const uint32_t prow  = static_cast<uint32_t>(p_local) - owner * per;
+                mine                 = (owner == zrank);
+                if(!mine)
+                {
+                    const uint32_t src     = zrank < owner ? zrank : zrank - 1u; // this slice's place among the owner's sources
+                    const uint32_t dst_row = map_to_cta(smem_base + prm.red_off, owner) + (src * per + prow) * static_cast<uint32_t>(bn) * 4u;
+                    const uint32_t dst_bar = map_to_cta(red_bar, owner);
+#pragma unroll
+                    for(int j = 0; j < 64; j += 4)
+                        if(j < bn)
+                            st_async_v4(dst_row + static_cast<uint32_t>(j) * 4u, __float_as_uint(v[j]), __float_as_uint(v[j + 1]),
+                                        __float_as_uint(v[j + 2]), __float_as_uint(v[j + 3]), dst_bar);
+                }
+                else
+                {
+                    ok = bounded_wait(red_bar, 0, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, 0x3000);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if(ok)
+                    {
+                        const float4* red = reinterpret_cast<const float4*>(smem_gen + prm.red_off);
+                        for(int z = 0; z < csplit - 1; ++z)
+                        {
+                            const float4* row = red + (static_cast<size_t>(z * per + prow) * bn) / 4;
+#pragma unroll
+                            for(int j = 0; j < 64; j += 4)
+                                if(j < bn)
+                                {
+                                    const float4 t = row[j / 4];
+                                    v[j] += t.x;
+                                    v[j + 1] += t.y;
+                                    v[j + 2] += t.z;
+                                    v[j + 3] += t.w;
+                                }
+                        }
+                    }
+                }
+            }
+            if(ok && mine)
+            {
+                const int p = row_p0 + p_local;
+                if(prm.bias != nullptr)
+                {
+                    const float b = (p < prm.rows_p) ? prm.beta * load_bias(prm.bias, prm.bias_is_bf16, p) : 0.f;
+#pragma unroll
+                    for(int j = 0; j < 64; ++j)
+                        if(j < bn)
+                            v[j] = prm.alpha * v[j] + b;
+                }
+                else if(prm.alpha != 1.0f)
+                {
+#pragma unroll
+                    for(int j = 0; j < 64; ++j)
+                        if(j < bn)
+                            v[j] *= prm.alpha;
+                }
+                if(prm.tma_store)
+                {
+                    // this warp's 32 output columns x bn rows, staged as [row m][32 x bf16] in a retired operand stage (every
+                    // tile load has landed and been consumed once the accumulator is complete) and stored as one TMA tile,
+                    // which clips rows >= M and columns >= N
+                    uint8_t* buf = smem_gen + (warp - 2) * 4096;
+#pragma unroll
+                    for(int j = 0; j < 64; ++j)
+                        if(j < bn)
+                            reinterpret_cast<__nv_bfloat16*>(buf)[j * 32 + lane] = __float2bfloat16_rn(v[j]);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    const int p_warp0 = row_p0 + quarter * 32;
+                    if(lane == 0 && p_warp0 < prm.rows_p)
+                    {
+                        tma_store_2d(&map_out, smem_base + (warp - 2) * 4096, p_warp0 * 2, 0);
+                        bulk_commit_group();
+                        bulk_wait_group_read<0>(); // the store has read its source before the CTA retires
+                    }
+                }
+                else if(p < prm.rows_p)
+                {
+#pragma unroll
+                    for(int j = 0; j < 64; ++j)
+                        if(j < bn && j < prm.rows_q)
+                            prm.out[static_cast<size_t>(j) * prm.ldo + p] = __float2bfloat16_rn(v[j]);
+                }
+            }
+        }
+        tc_fence_before_sync();
+    }
+
+    __syncthreads();
+    // no cluster rendezvous at the end: the only remote traffic into a CTA are the partial sums of the rows it owns, and
+    // the warps that own them have waited for every byte (red barrier) before the CTA gets here
+    if(warp == 1)
+    {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, static_cast<uint32_t>(prm.tmem_cols));
+    }
+}
+
+} // namespace b200

@@ -217,6 +217,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
         *abort_f = 0;
         mbar_fence_init();
         fence_proxy_async_smem();
+        B200_TRACE(stamp(40);)
     }
     if(warp == 10 && lane == 0)
     {
@@ -244,8 +245,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     }
     tc_fence_before_sync();
     __syncthreads();
-    if(CG == 2 || csplit > 1)
+    B200_TRACE(if(threadIdx.x == 0) stamp(41);)
+    if(CG == 2)
         cluster_sync_all(); // the partner's barriers exist before anything arrives on them remotely
+    else if(csplit > 1)
+        cluster_arrive_release(); // K-split cluster: announced here, checked by the epilogue before its first remote access
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
     B200_TRACE(if(threadIdx.x == 0) stamp(1);)
@@ -254,6 +258,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     // The next kernel's CTAs may in turn be scheduled as soon as every CTA of this grid has got here.
     grid_dependency_wait();
     grid_launch_dependents();
+    B200_TRACE(if(threadIdx.x == 0) stamp(42);)
 
     const int q_rows_cta       = bn / CG;
     const uint32_t q_box_bytes = static_cast<uint32_t>(q_rows_cta) * kTileKBytes;
@@ -324,6 +329,174 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             next_unit(w);
     };
 
+    // ------------------------------------------------------------------ one K tile's block scales
+    // Raw scale bytes of stage s (whatever wire layout the caller uses) -> registers -> the stage's TMEM scale buffer,
+    // then this warp's arrival on full[s].  Run by the four scale warps, one per TMEM lane quarter, once per K tile, so
+    // it is kept short: a handful of shared-memory loads, a few byte permutes, one tcgen05.st.  (Letting the four
+    // epilogue warps take every other K tile of decode shapes was measured: slower for short K, 4 % faster at K = 16384.)
+    constexpr bool kE8 = (SFW == SFW_E8M0_SHUFFLE);
+    auto scale_tile = [&](const int s, const uint32_t phase, const int kt, const int g) -> bool {
+        const int quarter    = warp & 3;
+        const uint32_t tlane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        const uint32_t full_leader = (CG == 2) ? map_to_cta(full_bar(0), 0) : full_bar(0);
+        const int r16 = lane & 15, hi = lane >> 4;
+        const int q_groups = (bn + 31) / 32; // 32-row groups of Q staged per stage (P always stages 4)
+        // raw scales of stage s have landed (their producer waited for the previous pass's MMAs, so the
+        // TMEM scale buffer of stage s is free as well); mixed kind: the packed e2m1 tile counts on the same barrier
+        bool ok = bounded_wait(sfraw_bar(s), phase, abort_f, prm.status, ST_TIMEOUT_SFWARP, g);
+        const bool widen_here = kMixed && (p_f4 || q_rows_cta == kTileP); // 128-row packed tile: k chunk 3 is ours
+        ok = __all_sync(0xffffffffu, ok);
+        if(!ok)
+            return false;
+        B200_TRACE(if(tracing && warp == 2 && lane == 0 && g < 8) stamp(3 + 4 * g);)
+        uint8_t* stage = smem_gen + s * L.stage_bytes;
+        if(widen_here)
+        {
+            const int tid = (warp - 2) * 32 + lane;
+            const uint4 v = reinterpret_cast<const uint4*>(stage + L.stg_off)[3 * kTileP + tid];
+            uint4* dst    = reinterpret_cast<uint4*>(stage + (p_f4 ? 0u : L.q_off));
+            uint4 o0, o1;
+            e2m1x8_to_e4m3x8(v.x, o0.x, o0.y);
+            e2m1x8_to_e4m3x8(v.y, o0.z, o0.w);
+            e2m1x8_to_e4m3x8(v.z, o1.x, o1.y);
+            e2m1x8_to_e4m3x8(v.w, o1.z, o1.w);
+            dst[6 * kTileP + tid] = o0;
+            dst[7 * kTileP + tid] = o1;
+            fence_proxy_async_smem(); // read by the tensor core
+        }
+        // TMEM words of this stage, column order [P atom a][Q atom a, block 0][Q atom a, block 1]
+        const uint32_t* rawp = reinterpret_cast<const uint32_t*>(stage + L.sfp_off);
+        const uint32_t* rawq = reinterpret_cast<const uint32_t*>(stage + L.sfq_off);
+            uint32_t t[kTWords];
+#pragma unroll
+        for(int c = 0; c < kTWords; ++c)
+            t[c] = 0x7F7F7F7Fu;
+        if(kE8 && q_groups <= 2)
+        {
+            // Decode tiles (at most 64 rows on the Q side: six groups in all): every warp re-orders all six
+            // chunks itself.  That is 24 shared-memory loads and as many byte permutes per K tile, but no
+            // write-back, no rendezvous with the other three warps and no second round of loads, which at a
+            // lone warp's instruction latency cost more than the re-ordering they share.
+            const uint32_t* chunks = reinterpret_cast<const uint32_t*>(stage + L.sfp_off); // P's 4 chunks, then Q's
+            const bool tail        = (kt * 8 + 8 > prm.kblocks);
+            const uint32_t sel     = hi ? 0x7351u : 0x6240u; // bytes {kh=0, kh=1} of this lane's row half
+            uint32_t raw[6][4];
+#pragma unroll
+            for(int j = 0; j < 6; ++j)
+#pragma unroll
+                for(int c = 0; c < 4; ++c)
+                    raw[j][c] = (j < 4 + q_groups) ? chunks[j * 64 + c * 16 + r16] : 0u;
+#pragma unroll
+            for(int j = 0; j < 6; ++j)
+            {
+                const uint32_t lo_part = __byte_perm(raw[j][0], raw[j][1], sel); // k%4 = 0,1 for both k halves
+                const uint32_t hi_part = __byte_perm(raw[j][2], raw[j][3], sel); // k%4 = 2,3
+                uint32_t v0 = __byte_perm(lo_part, hi_part, 0x5410);             // k-blocks 0..3 of this row
+                uint32_t v1 = __byte_perm(lo_part, hi_part, 0x7632);             // k-blocks 4..7
+                if(tail)
+                {
+                    const int valid0  = min(max(prm.kblocks - kt * 8, 0), 4);
+                    const int valid1  = min(max(prm.kblocks - kt * 8 - 4, 0), 4);
+                    const uint32_t m0 = valid0 >= 4 ? 0xFFFFFFFFu : ((1u << (8 * valid0)) - 1u);
+                    const uint32_t m1 = valid1 >= 4 ? 0xFFFFFFFFu : ((1u << (8 * valid1)) - 1u);
+                    v0 = (v0 & m0) | (0x7F7F7F7Fu & ~m0);
+                    v1 = (v1 & m1) | (0x7F7F7F7Fu & ~m1);
+                }
+                if(j < 4 + q_groups)
+                {
+                    t[(j < 4) ? j : 8 + (j - 4)]      = v0; // K atom 0: P cols 0..3, Q cols 8..
+                    t[(j < 4) ? 4 + j : 16 + (j - 4)] = v1; // K atom 1: P cols 4..7, Q cols 16..
+                }
+            }
+        }
+        else if(kE8)
+        {
+            // raw: per 32-row group j a 256-byte chunk, byte (k%4)*64 + (m%16)*4 + ((k%8)/4)*2 + (m%32)/16:
+            // word column kk = k%4, byte kh*2 + mh (mh = this lane's row half).  The re-ordering is the
+            // same for all four TMEM lane quarters, so the warps share it: warp q re-orders groups q, q+4
+            // and q+8 and writes the two result words per row back over the chunk it just read
+            // ([k half][row 0..31]); after a (bounded) rendezvous every warp reads all 24 columns.
+            uint32_t* chunks = reinterpret_cast<uint32_t*>(stage + L.sfp_off); // 12 chunks, P's 4 then Q's 8
+            const bool tail  = (kt * 8 + 8 > prm.kblocks);
+            uint32_t v0[3], v1[3];
+#pragma unroll
+            for(int jj = 0; jj < 3; ++jj)
+            {
+                const int j         = (warp - 2) + 4 * jj;
+                const uint32_t* grp = chunks + j * 64;
+                const uint32_t w0 = grp[r16], w1 = grp[16 + r16], w2 = grp[32 + r16], w3 = grp[48 + r16];
+                const uint32_t sel     = hi ? 0x7351u : 0x6240u; // bytes {kh=0, kh=1} of this lane's row half
+                const uint32_t lo_part = __byte_perm(w0, w1, sel); // k%4 = 0,1 for both k halves
+                const uint32_t hi_part = __byte_perm(w2, w3, sel); // k%4 = 2,3
+                v0[jj] = __byte_perm(lo_part, hi_part, 0x5410); // k-blocks 0..3 of this row
+                v1[jj] = __byte_perm(lo_part, hi_part, 0x7632); // k-blocks 4..7
+                if(tail)
+                {
+                    const int valid0  = min(max(prm.kblocks - kt * 8, 0), 4);
+                    const int valid1  = min(max(prm.kblocks - kt * 8 - 4, 0), 4);
+                    const uint32_t m0 = valid0 >= 4 ? 0xFFFFFFFFu : ((1u << (8 * valid0)) - 1u);
+                    const uint32_t m1 = valid1 >= 4 ? 0xFFFFFFFFu : ((1u << (8 * valid1)) - 1u);
+                    v0[jj] = (v0[jj] & m0) | (0x7F7F7F7Fu & ~m0);
+                    v1[jj] = (v1[jj] & m1) | (0x7F7F7F7Fu & ~m1);
+                }
+                const bool in = (j < 4) || (j - 4 < q_groups);
+                if(!in)
+                    v0[jj] = v1[jj] = 0x7F7F7F7Fu;
+            }
+            __syncwarp(); // every lane has read this warp's chunks
+#pragma unroll
+            for(int jj = 0; jj < 3; ++jj)
+            {
+                uint32_t* grp = chunks + ((warp - 2) + 4 * jj) * 64;
+                grp[lane]      = v0[jj];
+                grp[32 + lane] = v1[jj];
+            }
+            __syncwarp();
+            if(lane == 0)
+                mbar_arrive(xch_bar(s));
+            ok = bounded_wait(xch_bar(s), phase, abort_f, prm.status, ST_TIMEOUT_SFWARP, 0x30000 + g);
+            ok = __all_sync(0xffffffffu, ok);
+            if(!ok)
+                return false;
+#pragma unroll
+            for(int j = 0; j < 12; ++j)
+            {
+                t[(j < 4) ? j : 8 + (j - 4)]      = chunks[j * 64 + lane];      // K atom 0: P cols 0..3, Q cols 8..15
+                t[(j < 4) ? 4 + j : 16 + (j - 4)] = chunks[j * 64 + 32 + lane]; // K atom 1: P cols 4..7, Q cols 16..23
+            }
+        }
+        else
+        {
+            // raw: [group][k quarter a][row 0..31][4 k-blocks]: one word per row per K atom
+#pragma unroll
+            for(int j = 0; j < 12; ++j)
+#pragma unroll
+                for(int a = 0; a < kAtomsK; ++a)
+                {
+                    const bool in       = (j < 4) || (j - 4 < q_groups);
+                    const uint32_t* grp = (j < 4) ? rawp + j * (32 * kAtomsK) : rawq + (j - 4) * (32 * kAtomsK);
+                    const int col       = (j < 4) ? a * 4 + j : 4 * kAtomsK + a * 8 + (j - 4);
+                    t[col]              = in ? grp[a * 32 + lane] : 0x7F7F7F7Fu;
+                }
+        }
+        const uint32_t tsf = tlane + prm.sf_tmem_base + s * prm.sf_cols;
+        tmem_st_x16(tsf, t);
+        if(kTWords > 16)
+            tmem_st_x8(tsf + 16, t + 16);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if(lane == 0)
+        {
+            if(CG == 2)
+                mbar_arrive_cluster(full_leader + 8u * s);
+            else
+                mbar_arrive(full_leader + 8u * s);
+            B200_TRACE(if(tracing && warp == 2 && g < 8) stamp(4 + 4 * g);)
+        }
+        return true;
+    };
+
     if(warp == 0 || warp == 10)
     {
         // ------------------------------------------------------------------ operand producers (every CTA)
@@ -344,8 +517,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             // One loop per operand layout, so that the per-K-tile path is a wait, an expect_tx and the tile load.
             auto run = [&](auto mode_tag) {
                 constexpr int MODE = decltype(mode_tag)::value;
+                B200_TRACE(if(tracing && is_p) stamp(56);)
                 for(WorkIter w = first_work(); w.valid && ok; next_unit(w))
                 {
+                    B200_TRACE(if(tracing && is_p && w.u == cluster_id) stamp(57);)
                     const int row0 = is_p ? (w.tp * CG + static_cast<int>(crank)) * kTileP
                                           : w.tq * bn + static_cast<int>(crank) * q_rows_cta;
                     int kt         = w.it_beg;
@@ -355,6 +530,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                         ok = bounded_wait(empty0 + 8u * s, ring.phase ^ 1u, abort_f, prm.status, ST_TIMEOUT_PRODUCER, g);
                         if(!ok)
                             break;
+                        B200_TRACE(if(tracing && is_p && g == 0) stamp(58);)
                         const uint32_t dst = tile0 + s * L.stage_bytes;
                         const uint32_t bar = full0 + 8u * s;
                         if(MODE == 3)
@@ -566,140 +742,13 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     else if(warp < 6)
     {
         // ------------------------------------------------------------------ scale warps (every CTA)
-        // A single warp executes this loop once per K tile, so it is kept short: a handful of shared-memory
-        // loads of the stage's raw scale bytes, a few byte permutes, one tcgen05.st.
         if(kScaled)
         {
-            constexpr bool kE8 = (SFW == SFW_E8M0_SHUFFLE);
-            const int quarter    = warp & 3;
-            const uint32_t tlane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-            const uint32_t full_leader = (CG == 2) ? map_to_cta(full_bar(0), 0) : full_bar(0);
-            const int r16 = lane & 15, hi = lane >> 4;
-            const int q_groups = (bn + 31) / 32; // 32-row groups of Q staged per stage (P always stages 4)
-
             int g = 0;
             bool ok = true;
             Ring ring{0, 0};
             for(WorkIter w = first_work(); w.valid && ok; next_iter(w), ++g, ring.advance(S))
-            {
-                const int s = ring.s;
-                // raw scales of stage s have landed (their producer waited for the previous pass's MMAs, so the
-                // TMEM scale buffer of stage s is free as well); mixed kind: the packed e2m1 tile counts on the same barrier
-                ok = bounded_wait(sfraw_bar(s), ring.phase, abort_f, prm.status, ST_TIMEOUT_SFWARP, g);
-                const bool widen_here = kMixed && (p_f4 || q_rows_cta == kTileP); // 128-row packed tile: k chunk 3 is ours
-                ok = __all_sync(0xffffffffu, ok);
-                if(!ok)
-                    break;
-                B200_TRACE(if(tracing && warp == 2 && lane == 0 && g < 8) stamp(3 + 4 * g);)
-                uint8_t* stage = smem_gen + s * L.stage_bytes;
-                if(widen_here)
-                {
-                    const int tid = (warp - 2) * 32 + lane;
-                    const uint4 v = reinterpret_cast<const uint4*>(stage + L.stg_off)[3 * kTileP + tid];
-                    uint4* dst    = reinterpret_cast<uint4*>(stage + (p_f4 ? 0u : L.q_off));
-                    uint4 o0, o1;
-                    e2m1x8_to_e4m3x8(v.x, o0.x, o0.y);
-                    e2m1x8_to_e4m3x8(v.y, o0.z, o0.w);
-                    e2m1x8_to_e4m3x8(v.z, o1.x, o1.y);
-                    e2m1x8_to_e4m3x8(v.w, o1.z, o1.w);
-                    dst[6 * kTileP + tid] = o0;
-                    dst[7 * kTileP + tid] = o1;
-                    fence_proxy_async_smem(); // read by the tensor core
-                }
-                // TMEM words of this stage, column order [P atom a][Q atom a, block 0][Q atom a, block 1]
-                const uint32_t* rawp = reinterpret_cast<const uint32_t*>(stage + L.sfp_off);
-                const uint32_t* rawq = reinterpret_cast<const uint32_t*>(stage + L.sfq_off);
-                const int kt = w.it_beg + w.i;
-                uint32_t t[kTWords];
-#pragma unroll
-                for(int c = 0; c < kTWords; ++c)
-                    t[c] = 0x7F7F7F7Fu;
-                if(kE8)
-                {
-                    // raw: per 32-row group j a 256-byte chunk, byte (k%4)*64 + (m%16)*4 + ((k%8)/4)*2 + (m%32)/16:
-                    // word column kk = k%4, byte kh*2 + mh (mh = this lane's row half).  The re-ordering is the
-                    // same for all four TMEM lane quarters, so the warps share it: warp q re-orders groups q, q+4
-                    // and q+8 and writes the two result words per row back over the chunk it just read
-                    // ([k half][row 0..31]); after a (bounded) rendezvous every warp reads all 24 columns.
-                    uint32_t* chunks = reinterpret_cast<uint32_t*>(stage + L.sfp_off); // 12 chunks, P's 4 then Q's 8
-                    const bool tail  = (kt * 8 + 8 > prm.kblocks);
-                    uint32_t v0[3], v1[3];
-#pragma unroll
-                    for(int jj = 0; jj < 3; ++jj)
-                    {
-                        const int j         = (warp - 2) + 4 * jj;
-                        const uint32_t* grp = chunks + j * 64;
-                        const uint32_t w0 = grp[r16], w1 = grp[16 + r16], w2 = grp[32 + r16], w3 = grp[48 + r16];
-                        const uint32_t sel     = hi ? 0x7351u : 0x6240u; // bytes {kh=0, kh=1} of this lane's row half
-                        const uint32_t lo_part = __byte_perm(w0, w1, sel); // k%4 = 0,1 for both k halves
-                        const uint32_t hi_part = __byte_perm(w2, w3, sel); // k%4 = 2,3
-                        v0[jj] = __byte_perm(lo_part, hi_part, 0x5410); // k-blocks 0..3 of this row
-                        v1[jj] = __byte_perm(lo_part, hi_part, 0x7632); // k-blocks 4..7
-                        if(tail)
-                        {
-                            const int valid0  = min(max(prm.kblocks - kt * 8, 0), 4);
-                            const int valid1  = min(max(prm.kblocks - kt * 8 - 4, 0), 4);
-                            const uint32_t m0 = valid0 >= 4 ? 0xFFFFFFFFu : ((1u << (8 * valid0)) - 1u);
-                            const uint32_t m1 = valid1 >= 4 ? 0xFFFFFFFFu : ((1u << (8 * valid1)) - 1u);
-                            v0[jj] = (v0[jj] & m0) | (0x7F7F7F7Fu & ~m0);
-                            v1[jj] = (v1[jj] & m1) | (0x7F7F7F7Fu & ~m1);
-                        }
-                        const bool in = (j < 4) || (j - 4 < q_groups);
-                        if(!in)
-                            v0[jj] = v1[jj] = 0x7F7F7F7Fu;
-                    }
-                    __syncwarp(); // every lane has read this warp's chunks
-#pragma unroll
-                    for(int jj = 0; jj < 3; ++jj)
-                    {
-                        uint32_t* grp = chunks + ((warp - 2) + 4 * jj) * 64;
-                        grp[lane]      = v0[jj];
-                        grp[32 + lane] = v1[jj];
-                    }
-                    __syncwarp();
-                    if(lane == 0)
-                        mbar_arrive(xch_bar(s));
-                    ok = bounded_wait(xch_bar(s), ring.phase, abort_f, prm.status, ST_TIMEOUT_SFWARP, 0x30000 + g);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if(!ok)
-                        break;
-#pragma unroll
-                    for(int j = 0; j < 12; ++j)
-                    {
-                        t[(j < 4) ? j : 8 + (j - 4)]      = chunks[j * 64 + lane];      // K atom 0: P cols 0..3, Q cols 8..15
-                        t[(j < 4) ? 4 + j : 16 + (j - 4)] = chunks[j * 64 + 32 + lane]; // K atom 1: P cols 4..7, Q cols 16..23
-                    }
-                }
-                else
-                {
-                    // raw: [group][k quarter a][row 0..31][4 k-blocks]: one word per row per K atom
-#pragma unroll
-                    for(int j = 0; j < 12; ++j)
-#pragma unroll
-                        for(int a = 0; a < kAtomsK; ++a)
-                        {
-                            const bool in       = (j < 4) || (j - 4 < q_groups);
-                            const uint32_t* grp = (j < 4) ? rawp + j * (32 * kAtomsK) : rawq + (j - 4) * (32 * kAtomsK);
-                            const int col       = (j < 4) ? a * 4 + j : 4 * kAtomsK + a * 8 + (j - 4);
-                            t[col]              = in ? grp[a * 32 + lane] : 0x7F7F7F7Fu;
-                        }
-                }
-                const uint32_t tsf = tlane + prm.sf_tmem_base + s * prm.sf_cols;
-                tmem_st_x16(tsf, t);
-                if(kTWords > 16)
-                    tmem_st_x8(tsf + 16, t + 16);
-                tmem_st_wait();
-                tc_fence_before_sync();
-                __syncwarp();
-                if(lane == 0)
-                {
-                    if(CG == 2)
-                        mbar_arrive_cluster(full_leader + 8u * s);
-                    else
-                        mbar_arrive(full_leader + 8u * s);
-                    B200_TRACE(if(tracing && warp == 2 && g < 8) stamp(4 + 4 * g);)
-                }
-            }
+                ok = scale_tile(ring.s, ring.phase, w.it_beg + w.i, g);
         }
     }
     else
@@ -836,6 +885,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             const uint32_t per    = scatter ? static_cast<uint32_t>(kTileP / csplit) : static_cast<uint32_t>(kTileP);
             const uint32_t owner  = scatter ? static_cast<uint32_t>(p_local) / per : 0u;
             const uint32_t prow   = static_cast<uint32_t>(p_local) - owner * per;
+            if(csplit > 1)
+                cluster_wait_acquire(); // every CTA of the cluster has initialised its barriers (long ago: they all ran a main loop since)
             if(csplit > 1 && warp == 6 && lane == 0 && (scatter || zrank == 0))
                 mbar_arrive_expect_tx(red_bar, static_cast<uint32_t>(csplit - 1) * per * static_cast<uint32_t>(bn) * 4u);
             if(csplit > 1 && zrank != owner)
@@ -1115,15 +1166,25 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                     prm.ws_counter[slot] = 0; // ready for the next launch
             }
         }
+        // the tile stores have read their shared-memory source before the CTA retires and its shared memory is handed
+        // on; their global writes need not be waited for (they are part of the grid's memory operations, which complete
+        // before anything ordered after the grid runs), and waiting would add the store's full latency to the kernel's tail
         if(use_tma && lane == 0)
-            bulk_wait_group<0>(); // this warp's tile stores are complete before the CTA retires
+            bulk_wait_group_read<0>();
         B200_TRACE(if(warp == 6 && lane == 0) stamp(62);)
+        B200_TRACE(if(lane == 0) stamp(43 + (warp - 6));)
         tc_fence_before_sync();
     }
 
+    B200_TRACE(if(lane == 0 && warp < 6) stamp(47 + warp);)
+    B200_TRACE(if(lane == 0 && warp >= 10) stamp(43 + warp);)
     __syncthreads();
-    if(CG == 2 || csplit > 1)
-        cluster_sync_all(); // nobody leaves while the partner may still arrive on this CTA's barriers
+    B200_TRACE(if(threadIdx.x == 0) stamp(55);)
+    // A CTA pair stays together to the end: the partner's MMAs and commits touch this CTA's shared memory and
+    // barriers.  The CTAs of a cluster K split need no such rendezvous: the only remote traffic into a CTA are the
+    // partial sums it owns, and its epilogue has waited for every byte of them (red barrier) before it got here.
+    if(CG == 2)
+        cluster_sync_all();
     B200_TRACE(if(threadIdx.x == 0) stamp(63);)
     B200_TRACE(if(prm.trace != nullptr && threadIdx.x == 0 && blockIdx.x < 160) prm.trace[65 + 2 * blockIdx.x] = global_timer_ns();)
     if(warp == 1)

@@ -3,6 +3,7 @@
 // needed, cuTensorMapEncodeTiled, is resolved at run time so the library loads without libcuda).
 #include "launch.h"
 #include "gemm_persistent.cuh"
+#include "gemm_decode.cuh"
 #include "gemm_blockscale.cuh"
 
 #include <atomic>
@@ -335,8 +336,12 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
     {
         const long long tiles = ((rows_p + kTileP * cfg.cg - 1) / (kTileP * cfg.cg)) * ((rows_q + cfg.bn - 1) / cfg.bn) * cfg.cg;
         int l2 = 0;
-        // split while the grid under-fills the machine and every split keeps >= 4 K iterations
-        while(l2 < 5 && tiles * (2LL << l2) <= num_sms && (k_iters >> (l2 + 1)) >= 4)
+        // split while the grid under-fills the machine and every split keeps >= 4 K iterations.  Decode tiles (the small
+        // kernel: two CTAs per SM, K split over a cluster of at most four) may fill the machine twice.
+        const bool decode  = cfg.swap && cfg.cg == 1 && cfg.bn <= 64 && kind != PK_MXF8F4;
+        const long long cap = decode ? 2LL * num_sms : num_sms;
+        const int max_l2    = decode ? 2 : 5;
+        while(l2 < max_l2 && tiles * (2LL << l2) <= cap && (k_iters >> (l2 + 1)) >= 4)
             ++l2;
         cfg.log2_splitk = l2;
     }
@@ -569,6 +574,171 @@ static bool widen_prepass_disabled()
 
 static void launch_gemm_locked(const GemmProblem& prob);
 
+// ---------------------------------------------------------------------------------------------
+// decode shapes: the small kernel of gemm_decode.cuh
+// ---------------------------------------------------------------------------------------------
+static bool decode_kernel_disabled()
+{
+    static const bool off = (std::getenv("AITER_B200_NO_DECODE_KERNEL") != nullptr);
+    return off;
+}
+
+struct DecodeLayout
+{
+    uint32_t stage_bytes, q_off, sfp_off, sfq_off, red_off, bar_off, total;
+};
+
+static DecodeLayout make_decode_layout(int bn, int stages, int csplit, bool scaled)
+{
+    DecodeLayout L;
+    L.q_off       = kTileP * kTileKBytes;
+    L.sfp_off     = L.q_off + static_cast<uint32_t>(bn) * kTileKBytes;
+    L.sfq_off     = L.sfp_off + (scaled ? 1024u : 0u);
+    L.stage_bytes = L.sfq_off + (scaled ? 1024u : 0u);
+    L.red_off     = L.stage_bytes * static_cast<uint32_t>(stages);
+    L.bar_off     = L.red_off + (csplit > 1 ? static_cast<uint32_t>(csplit - 1) * static_cast<uint32_t>(kTileP / csplit) * static_cast<uint32_t>(bn) * 4u : 0u);
+    L.total       = L.bar_off + 256u;
+    return L;
+}
+
+template <int KIND, int SFW>
+static void launch_decode_instance(int ctas, int csplit, size_t smem, cudaStream_t stream, const CUtensorMap& mp, const CUtensorMap& mq,
+                                   const CUtensorMap& msp, const CUtensorMap& msq, const CUtensorMap& mo, const DecodeParams& prm)
+{
+    auto kernel = gemm_decode_kernel<KIND, SFW>;
+    static bool attr_done[64] = {};
+    {
+        int dev = 0;
+        B200_CUDA(cudaGetDevice(&dev));
+        if(dev >= 0 && dev < 64 && !attr_done[dev]) // two CTAs of ~100 KB each per SM need the largest shared-memory carve-out
+            B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    }
+    raise_smem_limit(kernel, attr_done);
+    cudaLaunchConfig_t lc{};
+    lc.gridDim          = dim3(ctas, 1, 1);
+    lc.blockDim         = dim3(kDecodeThreads, 1, 1);
+    lc.dynamicSmemBytes = smem;
+    lc.stream           = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id               = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csplit;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs    = attr;
+    lc.numAttrs = pdl_disabled() ? 1 : 2;
+    B200_CUDA(cudaLaunchKernelEx(&lc, kernel, mp, mq, msp, msq, mo, prm));
+    g_launches.fetch_add(1);
+}
+
+// Launches the decode kernel if the problem and configuration fit it; returns false otherwise (the persistent kernel
+// then serves the call).  Caller holds g_mutex and has made the device current.
+static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, int kkind, const DeviceState& st)
+{
+    const int named_stages = prob.cfg.stages; // what the caller's configuration asked for (0: this kernel's own choice)
+    if(decode_kernel_disabled() || !cfg.swap || cfg.cg != 1 || cfg.bn > 64 || prob.M > cfg.bn || kkind == KIND_MXF8F4 || prob.scratch != nullptr)
+        return false;
+    const int num_k_iters = static_cast<int>((prob.act.kbytes + kTileKBytes - 1) / kTileKBytes);
+    int csplit            = 1 << cfg.log2_splitk;
+    while(csplit > num_k_iters)
+        csplit >>= 1;
+    if(csplit > 4)
+        return false; // wider K splits stay with the persistent kernel (workspace or 8-CTA cluster)
+    const bool scaled = (kkind != KIND_BF16);
+    const int bn      = cfg.bn;
+    // as many stages as keep two CTAs on an SM (110 KB each), unless the configuration names a count
+    int stages = 0;
+    const int smem_cap = named_stages > 0 ? st.smem_optin : 110 * 1024;
+    for(int s2 = std::min(named_stages > 0 ? named_stages : kDecodeMaxStages, kDecodeMaxStages); s2 >= 2; --s2)
+        if(static_cast<int>(make_decode_layout(bn, s2, csplit, scaled).total) + 1024 <= smem_cap)
+        {
+            stages = s2;
+            break;
+        }
+    if(stages == 0)
+        return false;
+    stages                  = std::min(stages, std::max(2, (num_k_iters + csplit - 1) / csplit));
+    const DecodeLayout L    = make_decode_layout(bn, stages, csplit, scaled);
+    const Operand& P        = prob.wgt;
+    const Operand& Q        = prob.act;
+    B200_CHECK(P.kbytes == Q.kbytes, "operands disagree on K bytes: ", P.kbytes, " vs ", Q.kbytes);
+    CUtensorMap mp  = operand_map(P, kTileP, "weight operand");
+    CUtensorMap mq  = operand_map(Q, bn, "activation operand");
+    CUtensorMap msp = mp, msq = mq;
+    int sfw = SFW_NONE;
+    const int kblocks = static_cast<int>(prob.K / 32);
+    if(scaled)
+    {
+        const ScaleOperand& SP = prob.wgt_sf;
+        const ScaleOperand& SQ = prob.act_sf;
+        const int atoms_k      = (kkind == KIND_MXF4) ? 2 : 1;
+        B200_CHECK(SP.wire == SQ.wire && SP.wire != SFW_NONE, "both scale tensors must use the same wire layout");
+        sfw = SP.wire;
+        B200_CHECK(sfw != SFW_E8M0_SHUFFLE || kkind == KIND_MXF4, "the e8m0_shuffle scale layout is only wired for MXFP4");
+        const int chunk = (sfw == SFW_E8M0_SHUFFLE) ? 256 : 128 * atoms_k;
+        msp = scale_map(SP, chunk, 4, "weight scales");
+        msq = scale_map(SQ, chunk, (bn + 31) / 32, "activation scales");
+        const long long need_cols = (sfw == SFW_E8M0_SHUFFLE) ? (kblocks + 7) / 8 * 8 : kblocks;
+        B200_CHECK(SP.padded_cols >= need_cols && SQ.padded_cols >= need_cols, "scale tensors have too few columns: need ",
+                   need_cols, ", got ", SP.padded_cols, " and ", SQ.padded_cols);
+        B200_CHECK(SP.padded_rows >= (P.rows + 31) / 32 * 32 && SQ.padded_rows >= (Q.rows + 31) / 32 * 32, "scale tensors have too few rows");
+        if(sfw == SFW_G1250)
+            B200_CHECK(kblocks % (4 * atoms_k) == 0, "K must be a multiple of ", 128 * atoms_k, " for this scale layout");
+    }
+    DecodeParams prm{};
+    prm.rows_p      = static_cast<int>(P.rows);
+    prm.rows_q      = static_cast<int>(Q.rows);
+    prm.num_k_iters = num_k_iters;
+    prm.kblocks     = kblocks;
+    prm.bn          = bn;
+    prm.stages      = stages;
+    prm.p_mode      = P.mode;
+    prm.q_mode      = Q.mode;
+    prm.csplit      = csplit;
+    prm.stage_bytes = L.stage_bytes;
+    prm.q_off       = L.q_off;
+    prm.sfp_off     = L.sfp_off;
+    prm.sfq_off     = L.sfq_off;
+    prm.red_off     = L.red_off;
+    prm.bar_off     = L.bar_off;
+    prm.out         = static_cast<__nv_bfloat16*>(prob.out);
+    prm.ldo         = prob.ldo;
+    prm.bias        = prob.bias;
+    prm.bias_is_bf16 = prob.bias_is_bf16;
+    prm.alpha       = prob.alpha;
+    prm.beta        = prob.beta;
+    prm.status      = st.status;
+    int cols = 32;
+    while(cols < bn + stages * decode_sf_cols(kkind))
+        cols <<= 1;
+    prm.tmem_cols = cols;
+    CUtensorMap mo = mp;
+    prm.tma_store  = ((reinterpret_cast<uintptr_t>(prob.out) & 15) == 0) && (prob.ldo % 8 == 0) ? 1 : 0;
+    if(prm.tma_store)
+    {
+        // bf16 [M][N] seen as bytes; a warp's box is its 32 output columns by the tile's bn rows
+        const cuuint64_t dims[2]    = {static_cast<cuuint64_t>(prob.N) * 2, static_cast<cuuint64_t>(prob.M)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(prob.ldo) * 2};
+        const cuuint32_t box[2]     = {64u, static_cast<cuuint32_t>(bn)};
+        mo = encode_map(prob.out, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "output");
+    }
+    const int tiles_p = static_cast<int>((P.rows + kTileP - 1) / kTileP);
+    const int ctas    = tiles_p * csplit;
+    const size_t smem = L.total + 1024;
+    if(kkind == KIND_BF16)
+        launch_decode_instance<KIND_BF16, SFW_NONE>(ctas, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
+    else if(kkind == KIND_MXF8 && sfw == SFW_G1250)
+        launch_decode_instance<KIND_MXF8, SFW_G1250>(ctas, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
+    else if(kkind == KIND_MXF4 && sfw == SFW_E8M0_SHUFFLE)
+        launch_decode_instance<KIND_MXF4, SFW_E8M0_SHUFFLE>(ctas, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
+    else if(kkind == KIND_MXF4 && sfw == SFW_G1250)
+        launch_decode_instance<KIND_MXF4, SFW_G1250>(ctas, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
+    else
+        fail("no decode kernel instance for kind ", kkind, " with scale layout ", sfw);
+    return true;
+}
+
 // Tall mixed MXFP8 x MXFP4 problems: widening the weight once (N x K bytes through HBM) is cheaper than widening
 // every tile of it in shared memory M / 256 times; the GEMM itself then runs as plain MXFP8.  Below the
 // threshold, inside stream capture without a buffer, or with caller-provided scratch the in-kernel path runs.
@@ -763,6 +933,8 @@ static void launch_gemm_locked(const GemmProblem& prob)
     }
     const int cg = cfg.cg;
     B200_CHECK(cg == 1 || cg == 2, "internal: CTAs per tile");
+    if(try_launch_decode(prob, cfg, kkind, st))
+        return;
     B200_CHECK(cg == 1 || cfg.bn % 32 == 0, "a CTA-pair tile needs a width that is a multiple of 32");
     const Operand& P       = cfg.swap ? prob.wgt : prob.act;
     const Operand& Q       = cfg.swap ? prob.act : prob.wgt;
@@ -811,12 +983,22 @@ static void launch_gemm_locked(const GemmProblem& prob)
     unsigned long long* trace = nullptr;
 #ifdef AITER_B200_TRACING
     static const bool trace_on = (std::getenv("AITER_B200_TRACE") != nullptr);
+    // AITER_B200_TRACE_EVERY=n: every launch stamps, only every n-th is fetched and printed, and nothing is cleared
+    // in between, so that the printed launch ran back to back with its predecessors
+    static const int trace_every = std::getenv("AITER_B200_TRACE_EVERY") ? std::atoi(std::getenv("AITER_B200_TRACE_EVERY")) : 1;
+    static int trace_seq = 0;
+    bool trace_print = false;
     if(trace_on && prob.scratch == nullptr)
     {
         if(st.trace == nullptr)
+        {
             B200_CUDA(cudaMalloc(&st.trace, kTraceWords * sizeof(unsigned long long)));
-        B200_CUDA(cudaMemsetAsync(st.trace, 0, kTraceWords * sizeof(unsigned long long), prob.stream));
-        trace = st.trace;
+            B200_CUDA(cudaMemset(st.trace, 0, kTraceWords * sizeof(unsigned long long)));
+        }
+        if(trace_every <= 1)
+            B200_CUDA(cudaMemsetAsync(st.trace, 0, kTraceWords * sizeof(unsigned long long), prob.stream));
+        trace       = st.trace;
+        trace_print = (trace_every <= 1) || (++trace_seq % trace_every == 0);
     }
 #endif
 
@@ -952,7 +1134,7 @@ static void launch_gemm_locked(const GemmProblem& prob)
         fail("no kernel instance for kind ", kkind, " with scale layout ", sfw);
 
 #ifdef AITER_B200_TRACING
-    if(trace != nullptr)
+    if(trace != nullptr && trace_print)
         print_trace(st, prob, cfg, tiles_p, tiles_q, splits, stages);
 #endif
 }

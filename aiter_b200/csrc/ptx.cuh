@@ -224,6 +224,13 @@ __device__ __forceinline__ void cluster_sync_all()
 {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The two halves of the cluster barrier on their own: a CTA can announce "my barriers are initialised" at once and
+// check that its peers have done so only where it first touches their shared memory, much later.
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+// (relaxed: for an arrival that only has to publish mbarrier initialisations, which fence.mbarrier_init.release.cluster
+// has already ordered; the releasing form costs about a thousand cycles more)
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 // shared::cta address of this CTA -> shared::cluster address of the same offset in CTA `rank`
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank)
 {

@@ -60,6 +60,14 @@ def candidates(M: int, N: int, K: int, family: str):
         for bn in (16, 32, 64, 128, 256):
             if bn < M or (bn >= 2 * max(M, 16) and bn > 16):
                 continue
+            if bn <= 64:
+                # decode kernel: its own stage count (two CTAs per SM) or three stages, K split over a cluster of up to 4
+                for st in (0, 3):
+                    for sk in [s for s in splits if s <= 2]:
+                        out.append((0, 1, bn, st, sk))
+                for sk in [s for s in splits if s > 2]:
+                    out.append((0, 1, bn, 4, sk))
+                continue
             for st in (4, 8):
                 for sk in splits:
                     out.append((0, 1, bn, st, sk))
