@@ -4,6 +4,14 @@
 #include <type_traits>
 #include "ptx.cuh"
 
+// Timestamp probes of the single-thread roles, compiled in only with -DAITER_B200_TRACING (a development aid: a
+// probe in a loop that one thread runs per K tile costs that loop several cycles per dependent instruction).
+#ifdef AITER_B200_TRACING
+#define B200_TRACE(...) __VA_ARGS__
+#else
+#define B200_TRACE(...)
+#endif
+
 namespace b200 {
 
 enum GemmKind : int { KIND_BF16 = 0, KIND_MXF8 = 1, KIND_MXF4 = 2, KIND_MXF8F4 = 3 /* e4m3 activations x e2m1 weights */ };

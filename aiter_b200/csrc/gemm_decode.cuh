@@ -44,6 +44,7 @@ struct DecodeParams
     int bias_is_bf16;
     float alpha, beta;
     unsigned int* status;
+    unsigned long long* trace; // AITER_B200_TRACING builds only
 };
 
 // TMEM columns of one stage's scales: [P atom a: 4 columns][Q atom a: 4 columns], a < atoms per K tile
@@ -76,6 +77,10 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
     volatile uint32_t* abort_f = reinterpret_cast<volatile uint32_t*>(smem_gen + prm.bar_off + 212);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    B200_TRACE(const bool tracing = (prm.trace != nullptr) && blockIdx.x == 0;)
+    B200_TRACE(auto stamp = [&](int slot) { if(tracing && slot < 64) prm.trace[slot] = static_cast<unsigned long long>(clock64()); };)
+    B200_TRACE(if(threadIdx.x == 0) stamp(0);)
+    B200_TRACE(if(prm.trace != nullptr && threadIdx.x == 0 && blockIdx.x < 160) prm.trace[64 + 2 * blockIdx.x] = global_timer_ns();)
     const int csplit     = prm.csplit;
     const uint32_t zrank = csplit > 1 ? cluster_ctarank() : 0u;           // this CTA's K slice
     const int tile       = csplit > 1 ? static_cast<int>(blockIdx.x) / csplit : static_cast<int>(blockIdx.x);
@@ -123,10 +128,12 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
         cluster_arrive_relaxed(); // "my barriers exist" (made visible by the init fence above); checked before the first remote access
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
+    B200_TRACE(if(threadIdx.x == 0) stamp(1);)
     // Programmatic dependent launch: everything above may run while the previous kernel of the stream still does;
     // nothing below touches global memory before that kernel has completed.
     grid_dependency_wait();
     grid_launch_dependents();
+    B200_TRACE(if(threadIdx.x == 0) stamp(2);)
 
     if(warp == 0)
     {
@@ -146,6 +153,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                 mbar_arrive_expect_tx(bar, kTileP * kTileKBytes + q_bytes);
                 issue_operand_load(prm.p_mode, stage, &map_p, bar, row_p0, kt);
                 issue_operand_load(prm.q_mode, stage + prm.q_off, &map_q, bar, 0, kt);
+                B200_TRACE(if(i == 0) stamp(3);)
                 if(++s == S)
                 {
                     s = 0;
@@ -228,6 +236,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                 if(!ok)
                     break;
                 tc_fence_after_sync();
+                B200_TRACE(if(i < 8) stamp(4 + i);)
                 const uint32_t p_lo = p_lo0 + s * stage_step;
                 const uint32_t q_lo = q_lo0 + s * stage_step;
                 const uint32_t tsfp = sf0 + s * kSfCols;
@@ -254,6 +263,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
             }
             if(ok)
                 tc_commit(acc_bar);
+            B200_TRACE(stamp(30);)
         }
     }
     else
@@ -276,6 +286,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                 ok = __all_sync(0xffffffffu, ok);
                 if(!ok)
                     break;
+                B200_TRACE(if(warp == 2 && lane == 0 && i < 8) stamp(12 + i);)
                 const uint8_t* stage = smem_gen + s * prm.stage_bytes;
                 uint32_t t[kSfCols > 0 ? kSfCols : 1];
 #pragma unroll
@@ -344,6 +355,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                 __syncwarp();
                 if(lane == 0)
                     mbar_arrive(full_bar(s));
+                B200_TRACE(if(warp == 2 && lane == 0 && i < 8) stamp(20 + i);)
                 if(++s == S)
                 {
                     s = 0;
@@ -353,11 +365,16 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
         }
 
         // ---- epilogue: this thread holds row p_local of the tile (one weight row = one output column), bn values
+        // (the cluster check sits here, in the slack while the last K tile's MMAs run: every CTA of the cluster has
+        // initialised its barriers - they all ran a K loop since - before this CTA touches their shared memory)
+        if(csplit > 1)
+            cluster_wait_acquire();
         if(ok)
         {
             ok = bounded_wait(acc_bar, 0, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, 0);
             ok = __all_sync(0xffffffffu, ok);
         }
+        B200_TRACE(if(lane == 0) stamp(38 + (warp - 2));)
         if(ok)
         {
             tc_fence_after_sync();
@@ -387,7 +404,6 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                 // Reduce-scatter over the cluster: CTA z owns rows [z * per, (z + 1) * per) of the tile (whole warps).  A warp
                 // whose rows belong to another CTA sends its partial sums to that CTA's shared memory ([source slice][row][bn
                 // floats], bytes counted on that CTA's red barrier) and is done; an owning warp waits for the other slices.
-                cluster_wait_acquire(); // every CTA of the cluster has initialised its barriers (they all ran a K loop since)
                 const uint32_t owner = static_cast<uint32_t>(p_local) / per;
                 const uint32_t prow  = static_cast<uint32_t>(p_local) - owner * per;
                 mine                 = (owner == zrank);
@@ -426,6 +442,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                     }
                 }
             }
+            B200_TRACE(if(lane == 0) stamp(42 + (warp - 2));)
             if(ok && mine)
             {
                 const int p = row_p0 + p_local;
@@ -466,6 +483,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                 }
                 else if(p < prm.rows_p)
                 {
+                    // (output whose pitch or base rules out a tensor map; measured 1 to 1.5 us slower per call than the
+                    // tile store even for one activation row: plain stores take longer to drain at the grid's end, and the
+                    // dependent launch waits for that)
 #pragma unroll
                     for(int j = 0; j < 64; ++j)
                         if(j < bn && j < prm.rows_q)
@@ -473,10 +493,13 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                 }
             }
         }
+        B200_TRACE(if(lane == 0) stamp(46 + (warp - 2));)
         tc_fence_before_sync();
     }
 
     __syncthreads();
+    B200_TRACE(if(threadIdx.x == 0) stamp(63);)
+    B200_TRACE(if(prm.trace != nullptr && threadIdx.x == 0 && blockIdx.x < 160) prm.trace[65 + 2 * blockIdx.x] = global_timer_ns();)
     // no cluster rendezvous at the end: the only remote traffic into a CTA are the partial sums of the rows it owns, and
     // the warps that own them have waited for every byte (red barrier) before the CTA gets here
     if(warp == 1)

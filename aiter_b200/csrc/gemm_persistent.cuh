@@ -36,14 +36,6 @@
 
 namespace b200 {
 
-// Timestamp probes of the single-thread roles, compiled in only with -DAITER_B200_TRACING (a development aid: a
-// probe in a loop that one thread runs per K tile costs that loop several cycles per dependent instruction).
-#ifdef AITER_B200_TRACING
-#define B200_TRACE(...) __VA_ARGS__
-#else
-#define B200_TRACE(...)
-#endif
-
 constexpr int kPersistentThreads = 384;
 constexpr int kMaxAcc            = 2;
 

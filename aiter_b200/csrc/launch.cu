@@ -634,7 +634,7 @@ static void launch_decode_instance(int ctas, int csplit, size_t smem, cudaStream
 
 // Launches the decode kernel if the problem and configuration fit it; returns false otherwise (the persistent kernel
 // then serves the call).  Caller holds g_mutex and has made the device current.
-static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, int kkind, const DeviceState& st)
+static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, int kkind, DeviceState& st)
 {
     const int named_stages = prob.cfg.stages; // what the caller's configuration asked for (0: this kernel's own choice)
     if(decode_kernel_disabled() || !cfg.swap || cfg.cg != 1 || cfg.bn > 64 || prob.M > cfg.bn || kkind == KIND_MXF8F4 || prob.scratch != nullptr)
@@ -709,6 +709,22 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
     prm.alpha       = prob.alpha;
     prm.beta        = prob.beta;
     prm.status      = st.status;
+#ifdef AITER_B200_TRACING
+    static const bool trace_on = (std::getenv("AITER_B200_TRACE") != nullptr);
+    static const int trace_every = std::getenv("AITER_B200_TRACE_EVERY") ? std::atoi(std::getenv("AITER_B200_TRACE_EVERY")) : 1;
+    static int trace_seq = 0;
+    bool trace_print = false;
+    if(trace_on)
+    {
+        if(st.trace == nullptr)
+        {
+            B200_CUDA(cudaMalloc(&st.trace, kTraceWords * sizeof(unsigned long long)));
+            B200_CUDA(cudaMemset(st.trace, 0, kTraceWords * sizeof(unsigned long long)));
+        }
+        prm.trace   = st.trace;
+        trace_print = (++trace_seq % std::max(trace_every, 1) == 0);
+    }
+#endif
     int cols = 32;
     while(cols < bn + stages * decode_sf_cols(kkind))
         cols <<= 1;
@@ -736,6 +752,10 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
         launch_decode_instance<KIND_MXF4, SFW_G1250>(ctas, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else
         fail("no decode kernel instance for kind ", kkind, " with scale layout ", sfw);
+#ifdef AITER_B200_TRACING
+    if(trace_print)
+        print_trace(st, prob, cfg, tiles_p, 1, csplit, stages);
+#endif
     return true;
 }
 
