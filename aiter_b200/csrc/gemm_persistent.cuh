@@ -57,6 +57,8 @@ struct PersistentParams
     int csplit;                   // K split across the CTAs of a thread-block cluster (1 = none; CG == 1 only, one tile per cluster)
     int split_shift;              // log2 of the K split in use (csplit if > 1, else splits) when it is a power of two, else -1
     int tma_store;                // the output goes through shared memory and TMA tile stores (map_out is valid)
+    int epi_bufs;                 // staging areas reserved for that: 0 none, 1, or 2 (wide stores double-buffered)
+    int panel_q;                  // tile order: Q tiles per L2-sized panel (0: Q fastest over the whole width)
     int tmem_cols;                // allocation (power of two)
     // block scales in global memory (wire layout), one "group" = 32 rows; a group row is `sf_row_words` words
     const uint32_t* sfp;
@@ -80,14 +82,15 @@ struct PersistentSmem
     uint32_t stage_bytes, q_off, sfp_off, sfq_off, stg_off, epi_off, red_off, bar_off, total;
 };
 
-constexpr uint32_t kEpiStageBytes = 16384; // 4 epilogue warps x 2 buffers x (32 rows x 64 bytes)
+constexpr uint32_t kEpiStageBytes = 16384; // 4 epilogue warps x 4 KB: two 32 x 64-byte buffers, or one 32 x 128-byte buffer (wide
+                                           // stores); twice that when the wide stores are double-buffered
 
 // scaled: the stage carries 1 KB + 2 KB of raw scale bytes (P groups, Q groups)
 // f4_operand: 0 none, 1 = P, 2 = Q arrives as packed e2m1 and needs a staging area of rows x 64 bytes
-// epi_stage: reserve the epilogue's output staging area (tile stores through TMA)
+// epi_stage: 0 none, 1 the epilogue's output staging area (tile stores through TMA), 2 twice the area
 // csplit: cluster K split; its leader keeps (csplit - 1) partial tiles of 128 x bn floats
 __host__ __device__ inline PersistentSmem make_persistent_smem(int bn, int cg, int stages, int f4_operand, bool scaled,
-                                                               bool epi_stage, int csplit)
+                                                               int epi_stage, int csplit)
 {
     PersistentSmem L;
     uint32_t q_bytes = static_cast<uint32_t>(bn / cg) * kTileKBytes;
@@ -100,7 +103,7 @@ __host__ __device__ inline PersistentSmem make_persistent_smem(int bn, int cg, i
     stg              = (stg + 1023u) & ~1023u;
     L.stage_bytes    = L.stg_off + stg;
     L.epi_off        = L.stage_bytes * static_cast<uint32_t>(stages);
-    L.red_off        = L.epi_off + (epi_stage ? kEpiStageBytes : 0u);
+    L.red_off        = L.epi_off + static_cast<uint32_t>(epi_stage) * kEpiStageBytes;
     L.bar_off        = L.red_off + (csplit > 1 ? static_cast<uint32_t>(csplit - 1) * static_cast<uint32_t>(bn) * kTileP * 4u : 0u);
     L.total          = L.bar_off + 512u;
     return L;
@@ -149,7 +152,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     uint8_t* smem_gen        = smem_raw + (smem_base - smem_u32(smem_raw));
     const int bn             = prm.bn;
     const int S              = prm.stages;
-    const PersistentSmem L   = make_persistent_smem(bn, CG, S, kMixed ? prm.f4_operand : 0, kScaled, prm.tma_store != 0, prm.csplit);
+    const PersistentSmem L   = make_persistent_smem(bn, CG, S, kMixed ? prm.f4_operand : 0, kScaled, prm.epi_bufs, prm.csplit);
     constexpr int kSfChunk   = (SFW == SFW_E8M0_SHUFFLE) ? 256 : 128 * kAtomsK; // raw scale bytes per 32-row group per stage
 
     const uint32_t bar_base  = smem_base + L.bar_off;
@@ -287,6 +290,19 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
         {
             w.tq = 0;
             w.tp = tile;
+        }
+        else if(prm.panel_q > 0)
+        {
+            // L2-sized panels of the Q operand: all P tiles against panel 0's Q tiles (Q fastest inside the panel), then
+            // panel 1, ...  The panel's Q rows stay in L2 while P streams past once per panel; without panels a Q operand
+            // larger than L2 is read from HBM once per row of tiles.
+            const int panel_tiles = prm.tiles_p * prm.panel_q; // every panel but the last is this large
+            const int pn          = tile / panel_tiles;
+            const int r           = tile - pn * panel_tiles;
+            const int q0          = pn * prm.panel_q;
+            const int wq          = min(prm.panel_q, prm.tiles_q - q0);
+            w.tp                  = r / wq;
+            w.tq                  = q0 + (r - w.tp * wq);
         }
         else
         {
@@ -757,9 +773,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
         // Output staging: every epilogue warp owns two 2 KB buffers (32 rows x 64 bytes) and stores them with its
         // own TMA tile stores, so the warps never wait for one another and global memory sees whole 64-byte runs.
         const bool use_tma   = prm.tma_store != 0;
-        uint8_t* epi_gen     = smem_gen + L.epi_off + (warp - 6) * 4096;
-        const uint32_t epi_s = smem_base + L.epi_off + (warp - 6) * 4096;
+        const uint32_t epi_warp_bytes = prm.epi_bufs == 2 ? 8192u : 4096u;
+        uint8_t* epi_gen     = smem_gen + L.epi_off + (warp - 6) * epi_warp_bytes;
+        const uint32_t epi_s = smem_base + L.epi_off + (warp - 6) * epi_warp_bytes;
         int ebuf             = 0;
+        uint32_t wbuf        = 0; // wide stores: which of the two 4 KB buffers comes next (0 when there is only one)
         if(use_tma && lane == 0)
             tma_prefetch_desc(&map_out);
         uint32_t epi_phase = 0;
@@ -1070,10 +1088,17 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                                 r[j] = __float_as_uint(prm.alpha * __uint_as_float(r[j]) + prm.beta * b);
                             }
                         }
+                        // the store that last used this buffer has read it (the previous store with one buffer, the one
+                        // before it with two: then a store's read latency no longer sits between two TMEM loads)
                         if(lane == 0)
-                            bulk_wait_group_read<0>(); // the previous tile store has read this warp's buffer
+                        {
+                            if(prm.epi_bufs == 2)
+                                bulk_wait_group_read<1>();
+                            else
+                                bulk_wait_group_read<0>();
+                        }
                         __syncwarp();
-                        uint8_t* row = epi_gen + lane * 128;
+                        uint8_t* row = epi_gen + wbuf + lane * 128;
 #pragma unroll
                         for(int j = 0; j < 8; ++j)
                             *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) * 16)) =
@@ -1085,9 +1110,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                         __syncwarp();
                         if(lane == 0 && p_warp0 < prm.rows_p && q_first < prm.rows_q)
                         {
-                            tma_store_2d(&map_out, epi_s, q_first * 2, p_warp0);
+                            tma_store_2d(&map_out, epi_s + wbuf, q_first * 2, p_warp0);
                             bulk_commit_group();
                         }
+                        if(prm.epi_bufs == 2)
+                            wbuf ^= 4096u;
                     }
                 }
                 else if(!split)

@@ -294,7 +294,7 @@ static int kernel_kind_of(int problem_kind)
     }
 }
 
-static int max_stages(int bn, int cg, int smem_limit, int f4_operand, bool scaled, bool epi_stage, int csplit = 1)
+static int max_stages(int bn, int cg, int smem_limit, int f4_operand, bool scaled, int epi_stage, int csplit = 1)
 {
     for(int s = kMaxStages; s >= 1; --s)
         if(static_cast<int>(make_persistent_smem(bn, cg, s, f4_operand, scaled, epi_stage, csplit).total) + 1024 <= smem_limit)
@@ -558,6 +558,12 @@ __global__ void relay_e8m0_shuffle_kernel(const uint8_t* __restrict__ src, uint3
         dst[i]             = static_cast<uint32_t>(p[0]) | (static_cast<uint32_t>(p[64]) << 8) | (static_cast<uint32_t>(p[128]) << 16) |
                              (static_cast<uint32_t>(p[192]) << 24);
     }
+}
+
+static bool panel_order_disabled()
+{
+    static const bool off = (std::getenv("AITER_B200_NO_PANELS") != nullptr);
+    return off;
 }
 
 static bool relay_prepass_disabled()
@@ -1123,11 +1129,30 @@ static void launch_gemm_locked(const GemmProblem& prob)
     while(cols < prm.sf_tmem_base + stages * sf_cols)
         cols <<= 1;
     prm.tmem_cols = cols;
-    const PersistentSmem L = make_persistent_smem(cfg.bn, cg, stages, f4_operand, kkind != KIND_BF16, tma_store, csplit);
-    const size_t smem      = L.total + 1024;
     // 2: 64 columns per store (row-major output, tile width a multiple of 64, no K split); 1: 32 per store
     const bool wide_store  = tma_store && !cfg.swap && cfg.bn % 64 == 0 && splits == 1;
     prm.tma_store          = tma_store ? (wide_store ? 2 : 1) : 0;
+    // the wide stores get a second staging buffer where that costs no pipeline stage
+    prm.epi_bufs = tma_store ? 1 : 0;
+    if(wide_store && static_cast<int>(make_persistent_smem(cfg.bn, cg, stages, f4_operand, kkind != KIND_BF16, 2, csplit).total) + 1024 <= st.smem_optin)
+        prm.epi_bufs = 2;
+    const PersistentSmem L = make_persistent_smem(cfg.bn, cg, stages, f4_operand, kkind != KIND_BF16, prm.epi_bufs, csplit);
+    const size_t smem      = L.total + 1024;
+    // Tile order.  When the Q operand (the weights of a tall problem) is much larger than what L2 keeps beside the
+    // streaming P operand and the output, walk it in panels of about 32 MB.
+    prm.panel_q = 0;
+    {
+        const double q_tile_bytes = static_cast<double>(cfg.bn) * static_cast<double>(Q.kbytes);
+        const double q_bytes      = q_tile_bytes * tiles_q;
+        if(!cfg.swap && csplit == 1 && tiles_q > 1 && q_bytes > 48e6 && !panel_order_disabled())
+        {
+            const int w0     = std::max(1, static_cast<int>(32e6 / q_tile_bytes));
+            const int panels = (tiles_q + w0 - 1) / w0;
+            const int w      = (tiles_q + panels - 1) / panels; // equal panels
+            if(w < tiles_q)
+                prm.panel_q = w;
+        }
+    }
     CUtensorMap mo         = mp;
     if(tma_store)
     {
