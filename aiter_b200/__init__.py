@@ -23,7 +23,10 @@ from .gemm_op_a4w4 import (  # noqa: E402,F401
     gemm_a4w4_asm,
     gemm_a4w4_blockscale,
     gemm_a4w4_blockscale_tune,
+    gemm_a4w4o4,
+    gemm_a4w4o8,
     gemm_mxfp4_asm,
+    unpack_mxfp8_out_scale,
 )
 from .gemm_op_a8w4 import gemm_a8w4_mxfp8  # noqa: E402,F401
 from .gemm_op_a8w8 import (  # noqa: E402,F401
@@ -51,7 +54,9 @@ from .shuffle import (  # noqa: E402,F401
     shuffle_mxfp8fp4_b,
     shuffle_mxfp8fp4_scale,
     shuffle_scale,
+    shuffle_scale_f4,
     shuffle_weight,
+    shuffle_weight_f4,
 )
 from .tuned_gemm import TunedGemm, gemm_a16w16, tgemm  # noqa: E402,F401
 from . import torch_ops  # noqa: E402,F401  (registers torch.ops.aiter.* with fake-tensor implementations)

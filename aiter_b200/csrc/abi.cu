@@ -36,6 +36,12 @@ static int safe_call(Fn&& fn)
     return -1;
 }
 
+// OutMode of a plain (not re-quantised) output tensor, or -1
+static int plain_out_mode(int dtype)
+{
+    return dtype == AITER_DTYPE_bf16 ? OUT_BF16 : dtype == AITER_DTYPE_fp16 ? OUT_F16 : dtype == AITER_DTYPE_fp32 ? OUT_F32 : -1;
+}
+
 static void set_out(GemmProblem& p, const aiter_tensor_t* out, const char* fn, long long M, long long N)
 {
     require_tensor(out, fn, "out", 2);
@@ -138,13 +144,68 @@ extern "C" int mxfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor
                               void* stream)
 {
     return safe_call([&] {
-        B200_CHECK(out_scale == nullptr, "mxfp4_gemm_asm: only the bf16 output form is built (out_scale must be absent)");
+        const char* fn = "mxfp4_gemm_asm";
         B200_CHECK(a_preshuffle == 0 || a_preshuffle == 1, "mxfp4_gemm_asm a_preshuffle must be 0 or 1");
         GemmProblem tmp;
-        apply_config(tmp, kernelName, -1, "mxfp4_gemm_asm");
+        apply_config(tmp, kernelName, -1, fn);
         B200_CHECK(A != nullptr && A->ndim == 2 && (A->shape[1] * 2) % 256 == 0, "mxfp4_gemm_asm K must be divisible by 256");
-        run_mxfp4("mxfp4_gemm_asm", A, B, ScaleA, ScaleB, out, nullptr, 1.f, 0.f, a_preshuffle ? OPM_A2X128 : OPM_ROWMAJOR,
-                  OPM_TILE16, SFW_G1250, tmp.cfg, stream);
+        require_tensor(out, fn, "out", 2);
+        const bool out_fp4 = (out->dtype_ == AITER_DTYPE_fp4x2 || out->dtype_ == AITER_DTYPE_u8);
+        const bool out_fp8 = (out->dtype_ == AITER_DTYPE_fp8);
+        if(!out_fp4 && !out_fp8)
+        {
+            B200_CHECK(out_scale == nullptr, "mxfp4_gemm_asm: out_scale goes with the fp8 output only");
+            run_mxfp4(fn, A, B, ScaleA, ScaleB, out, nullptr, 1.f, 0.f, a_preshuffle ? OPM_TILE16 : OPM_ROWMAJOR, OPM_TILE16, SFW_G1250,
+                      tmp.cfg, stream);
+            return;
+        }
+        // Low-precision outputs (the reference's gemm_a4w4o4 / gemm_a4w4o8, aiter/ops/gemm_op_a4w4.py:457-567):
+        //   fp4x2 / uint8 [M, N/2]: packed e2m1 of the UNSCALED product (its fp4-output kernel ignores the block scales);
+        //   fp8 [M, N] + out_scale [M, N/128] e8m0 in the packed (M/64, N/128, 16, 4) byte order.
+        require_tensor(A, fn, "A", 2);
+        require_tensor(B, fn, "B", 2);
+        const long long M = A->shape[0], N = B->shape[0], Kb = A->shape[1];
+        B200_CHECK(B->shape[1] == Kb, fn, ": A and B disagree on K");
+        B200_CHECK(A->dtype_ == AITER_DTYPE_fp4x2 || A->dtype_ == AITER_DTYPE_u8, fn, " Unsupported input_type:", dtype_name(A->dtype_));
+        B200_CHECK(B->dtype_ == AITER_DTYPE_fp4x2 || B->dtype_ == AITER_DTYPE_u8, fn, " Unsupported input_type:", dtype_name(B->dtype_));
+        require_dense(A, fn, "A");
+        require_dense(B, fn, "B");
+        GemmProblem p;
+        p.kind = PK_MXFP4;
+        p.M = M; p.N = N; p.K = Kb * 2;
+        p.act    = Operand{A->ptr, M, Kb, Kb, a_preshuffle ? OPM_TILE16 : OPM_ROWMAJOR};
+        p.wgt    = Operand{B->ptr, N, Kb, Kb, OPM_TILE16};
+        p.act_sf = scale_operand(ScaleA, SFW_G1250, fn, "ScaleA");
+        p.wgt_sf = scale_operand(ScaleB, SFW_G1250, fn, "ScaleB");
+        require_dense(out, fn, "out");
+        if(out_fp4)
+        {
+            B200_CHECK(out_scale == nullptr, fn, ": the packed fp4 output takes no out_scale");
+            B200_CHECK(out->shape[0] == M && out->shape[1] == N / 2, fn, ": the packed fp4 output must be [M, N/2]");
+            p.out_mode = OUT_E2M1;
+            p.noscale  = 1;
+        }
+        else
+        {
+            require_tensor(out_scale, fn, "out_scale", 2);
+            B200_CHECK(is_byte_dtype(out_scale->dtype_), fn, ": out_scale must be e8m0 / uint8");
+            B200_CHECK(out->shape[0] == M && out->shape[1] == N, fn, ": the fp8 output must be [M, N]");
+            B200_CHECK(static_cast<long long>(out_scale->numel_) >= M * (N / 128), fn, ": out_scale must hold M * N/128 bytes");
+            require_dense(out_scale, fn, "out_scale");
+            require_same_device(A, out_scale, fn, "out_scale");
+            p.out_mode  = OUT_MXFP8;
+            p.out_scale = out_scale->ptr;
+        }
+        require_same_device(A, B, fn, "B");
+        require_same_device(A, out, fn, "out");
+        p.out    = out->ptr;
+        p.ldo    = out->strides[0]; // bytes: both outputs have one-byte elements
+        p.alpha  = 1.f;
+        p.beta   = 0.f;
+        p.device = A->device_id;
+        p.stream = static_cast<cudaStream_t>(stream);
+        p.cfg    = tmp.cfg;
+        launch_gemm(p);
     });
 }
 
@@ -204,7 +265,8 @@ static void run_blockscale(const char* fn, aiter_tensor_t* XQ, aiter_tensor_t* W
     const bool sw8 = (w_scale->dtype_ == AITER_DTYPE_fp8_e8m0 || w_scale->dtype_ == AITER_DTYPE_u8);
     B200_CHECK((x_scale->dtype_ == AITER_DTYPE_fp32 && w_scale->dtype_ == AITER_DTYPE_fp32) || (sx8 && sw8), fn,
                ": scales must both be fp32 or both be e8m0 bytes");
-    B200_CHECK(Out->dtype_ == AITER_DTYPE_bf16, fn, ": only bf16 output is built");
+    const int out_mode = plain_out_mode(Out->dtype_);
+    B200_CHECK(out_mode >= 0, fn, ": Out must be bf16, fp16 or fp32 (got ", dtype_name(Out->dtype_), ")");
     const long long M = XQ->shape[0], K = XQ->shape[1], N = WQ->shape[0];
     B200_CHECK(WQ->shape[1] == K, fn, ": XQ and WQ disagree on K");
     B200_CHECK(K % 128 == 0, fn, ": K must be a multiple of 128");
@@ -239,10 +301,11 @@ static void run_blockscale(const char* fn, aiter_tensor_t* XQ, aiter_tensor_t* W
         B200_CHECK(parse_config_name(kernelName, p.cfg), fn, ": not find kernel ", kernelName);
         p.cfg_given = true;
     }
-    p.out     = Out->ptr;
-    p.ldo     = Out->strides[0];
-    p.device  = XQ->device_id;
-    p.stream  = static_cast<cudaStream_t>(stream);
+    p.out      = Out->ptr;
+    p.ldo      = Out->strides[0];
+    p.out_mode = out_mode;
+    p.device   = XQ->device_id;
+    p.stream   = static_cast<cudaStream_t>(stream);
     launch_blockscale(p);
 }
 
@@ -333,13 +396,16 @@ extern "C" int gemm_a8w8_blockscale_bpreshuffle_asm(aiter_tensor_t* A, aiter_ten
 
 // ------------------------------------------------------------------------------------------- bf16
 static void run_bf16(const char* fn, const aiter_tensor_t* A, const aiter_tensor_t* B, const aiter_tensor_t* out,
-                     const aiter_tensor_t* bias, int bpreshuffle, const KernelConfig& cfg, int batch_index, void* stream)
+                     const aiter_tensor_t* bias, int bpreshuffle, const KernelConfig& cfg, void* stream)
 {
-    // A [.., M, K], B [.., N, K], out [.., M, N]; the leading batch dimension (3-D form) is walked by the caller
+    // A [.., M, K], B [.., N, K], out [.., M, N]; a leading batch dimension (3-D form) becomes one more tile coordinate
+    // of the same launch
     const int a0 = A->ndim - 2;
     B200_CHECK(A->dtype_ == AITER_DTYPE_bf16 && B->dtype_ == AITER_DTYPE_bf16, fn, ": only bf16 inputs are supported (got ",
                dtype_name(A->dtype_), ", ", dtype_name(B->dtype_), ")");
-    B200_CHECK(out->dtype_ == AITER_DTYPE_bf16, fn, ": only bf16 output is supported (got ", dtype_name(out->dtype_), ")");
+    B200_CHECK(out->dtype_ == AITER_DTYPE_bf16 || out->dtype_ == AITER_DTYPE_fp32, fn, ": unsupported output dtype, expected bf16 or fp32 (got ",
+               dtype_name(out->dtype_), ")");
+    const long long batch = a0 ? A->shape[0] : 1;
     const long long M = A->shape[a0], K = A->shape[a0 + 1], N = B->shape[a0];
     B200_CHECK(B->shape[a0 + 1] == K, fn, ": A and B disagree on K");
     B200_CHECK(out->shape[a0] == M && out->shape[a0 + 1] == N, fn, ": out must be [M, N]");
@@ -349,25 +415,39 @@ static void run_bf16(const char* fn, const aiter_tensor_t* A, const aiter_tensor
     GemmProblem p;
     p.kind = PK_BF16;
     p.M = M; p.N = N; p.K = K;
-    const char* a_ptr = static_cast<const char*>(A->ptr) + (a0 ? batch_index * A->strides[0] * 2 : 0);
-    const char* b_ptr = static_cast<const char*>(B->ptr) + (a0 ? batch_index * B->strides[0] * 2 : 0);
-    char* o_ptr       = static_cast<char*>(out->ptr) + (a0 ? batch_index * out->strides[0] * 2 : 0);
-    p.act = Operand{a_ptr, M, K * 2, A->strides[a0] * 2, OPM_ROWMAJOR};
+    p.act = Operand{A->ptr, M, K * 2, A->strides[a0] * 2, OPM_ROWMAJOR};
     if(bpreshuffle)
     {
+        B200_CHECK(batch == 1, fn, ": a shuffled weight is not supported with a batch");
         B200_CHECK(B->strides[a0] == K, fn, ": a shuffled weight must be contiguous");
-        p.wgt = Operand{b_ptr, N, K * 2, K * 2, OPM_TILE16};
+        p.wgt = Operand{B->ptr, N, K * 2, K * 2, OPM_TILE16};
     }
     else
-        p.wgt = Operand{b_ptr, N, K * 2, B->strides[a0] * 2, OPM_ROWMAJOR};
-    p.out = o_ptr;
-    p.ldo = out->strides[a0];
+        p.wgt = Operand{B->ptr, N, K * 2, B->strides[a0] * 2, OPM_ROWMAJOR};
+    if(batch > 1)
+    {
+        B200_CHECK(B->shape[0] == batch && out->shape[0] == batch, fn, ": batch mismatch");
+        p.batch                  = batch;
+        p.act.mode               = OPM_BATCHED;
+        p.act.batch              = batch;
+        p.act.batch_stride_bytes = A->strides[0] * 2;
+        p.wgt.mode               = OPM_BATCHED;
+        p.wgt.batch              = batch;
+        p.wgt.batch_stride_bytes = B->strides[0] * 2;
+        p.out_batch_stride       = out->strides[0];
+    }
+    p.out      = out->ptr;
+    p.ldo      = out->strides[a0];
+    p.out_mode = plain_out_mode(out->dtype_);
     if(bias != nullptr)
     {
         B200_CHECK(bias->dtype_ == AITER_DTYPE_bf16 || bias->dtype_ == AITER_DTYPE_fp32, fn, ": bias must be bf16 or fp32");
-        B200_CHECK(static_cast<long long>(bias->numel_) == N, fn, ": bias must have N elements");
-        p.bias         = bias->ptr;
-        p.bias_is_bf16 = (bias->dtype_ == AITER_DTYPE_bf16);
+        // [N] (shared by the batch) or [batch, N]
+        const bool per_pair = (bias->ndim == 2 && bias->shape[0] == batch && bias->shape[1] == N && batch > 1);
+        B200_CHECK(per_pair || static_cast<long long>(bias->numel_) == N, fn, ": bias must have N elements ([N], or [batch, N])");
+        p.bias              = bias->ptr;
+        p.bias_is_bf16      = (bias->dtype_ == AITER_DTYPE_bf16);
+        p.bias_batch_stride = per_pair ? N : 0;
     }
     p.alpha  = 1.f;
     p.beta   = 1.f;
@@ -395,7 +475,7 @@ extern "C" int gemm_a16w16_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tenso
                 ++l2;
         }
         apply_config(tmp, kernelName, l2, "gemm_a16w16_asm");
-        run_bf16("gemm_a16w16_asm", A, B, out, bias, bpreshuffle, tmp.cfg, 0, stream);
+        run_bf16("gemm_a16w16_asm", A, B, out, bias, bpreshuffle, tmp.cfg, stream);
     });
 }
 
@@ -411,25 +491,56 @@ extern "C" int opus_gemm_a16w16_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, ait
         cfg.log2_splitk = splitK;
         const long long batch = XQ->shape[0];
         B200_CHECK(WQ->shape[0] == batch && Y->shape[0] == batch, "opus_gemm_a16w16_tune: batch mismatch");
-        for(long long b = 0; b < batch; ++b)
-            run_bf16("opus_gemm_a16w16_tune", XQ, WQ, Y, bias, 0, cfg, static_cast<int>(b), stream);
+        run_bf16("opus_gemm_a16w16_tune", XQ, WQ, Y, bias, 0, cfg, stream);
     });
+}
+
+// one matrix of a [batch, rows, cols] tensor as a 2-D tensor descriptor
+static aiter_tensor_t batch_slice(const aiter_tensor_t* t, long long b, int elem_bytes)
+{
+    aiter_tensor_t s = *t;
+    s.ptr        = static_cast<char*>(t->ptr) + b * t->strides[0] * elem_bytes;
+    s.ndim       = 2;
+    s.shape[0]   = t->shape[1];
+    s.shape[1]   = t->shape[2];
+    s.strides[0] = t->strides[1];
+    s.strides[1] = t->strides[2];
+    s.numel_     = static_cast<size_t>(t->shape[1] * t->shape[2]);
+    return s;
 }
 
 extern "C" int opus_gemm(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* Y, aiter_tensor_t* group_layout,
                          aiter_tensor_t* x_scale, aiter_tensor_t* w_scale, aiter_tensor_t* bias, void* stream)
 {
     return safe_call([&] {
-        B200_CHECK(group_layout == nullptr && x_scale == nullptr && w_scale == nullptr,
-                   "opus_gemm: only the bf16 no-scale form is built");
+        B200_CHECK(group_layout == nullptr, "opus_gemm: grouped layouts are not built");
         require_tensor(XQ, "opus_gemm", "XQ", 3);
         require_tensor(WQ, "opus_gemm", "WQ", 3);
         require_tensor(Y, "opus_gemm", "Y", 3);
         const long long batch = XQ->shape[0];
         B200_CHECK(WQ->shape[0] == batch && Y->shape[0] == batch, "opus_gemm: batch mismatch");
+        if(XQ->dtype_ == AITER_DTYPE_fp8)
+        {
+            // the reference's a8w8_scale pipeline (csrc/opus_gemm/opus_gemm.cu:153-186): fp8 operands, fp32 scales per
+            // (row, 128 of K) and per 128 x 128 weight block, fp32 output, no bias; here the fp32-blockscale kernels serve it,
+            // one launch per matrix of the batch
+            B200_CHECK(x_scale != nullptr && w_scale != nullptr, "opus_gemm: the fp8 form needs x_scale and w_scale (the unscaled a8w8 pipeline is not built)");
+            B200_CHECK(bias == nullptr, "opus_gemm: bias is not supported on a8w8 / a8w8_scale paths");
+            B200_CHECK(Y->dtype_ == AITER_DTYPE_fp32, "opus_gemm a8w8_scale only supports fp32 output");
+            require_tensor(x_scale, "opus_gemm", "x_scale", 3);
+            require_tensor(w_scale, "opus_gemm", "w_scale", 3);
+            B200_CHECK(x_scale->shape[0] == batch && w_scale->shape[0] == batch, "opus_gemm: scale batch mismatch");
+            for(long long b = 0; b < batch; ++b)
+            {
+                aiter_tensor_t x = batch_slice(XQ, b, 1), w = batch_slice(WQ, b, 1), y = batch_slice(Y, b, 4);
+                aiter_tensor_t xs = batch_slice(x_scale, b, 4), ws = batch_slice(w_scale, b, 4);
+                run_blockscale("opus_gemm", &x, &w, &xs, &ws, &y, 0, stream);
+            }
+            return;
+        }
+        B200_CHECK(x_scale == nullptr && w_scale == nullptr, "opus_gemm: scales go with fp8 operands only");
         KernelConfig cfg;
-        for(long long b = 0; b < batch; ++b)
-            run_bf16("opus_gemm", XQ, WQ, Y, bias, 0, cfg, static_cast<int>(b), stream);
+        run_bf16("opus_gemm", XQ, WQ, Y, bias, 0, cfg, stream);
     });
 }
 

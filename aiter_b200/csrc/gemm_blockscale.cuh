@@ -28,8 +28,9 @@ struct BlockScaleParams
     const float* x_scale;
     long long xs_stride_m, xs_stride_k; // in elements
     const float* w_scale;    // [ceil(N/128)][k_blocks]
-    __nv_bfloat16* out;
+    void* out;               // bf16 / fp16 / fp32 [M][N]
     long long ldo;
+    int out_mode;            // OutMode (OUT_BF16, OUT_F16 or OUT_F32)
     unsigned int* status;
     // K split of the single-CTA kernel (gridDim.z slices): fp32 partial tiles + one ticket per output tile
     int splits;
@@ -291,22 +292,8 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         }
         if(ok && row_ok)
         {
-            __nv_bfloat16* dst = prm.out + static_cast<size_t>(row) * prm.ldo + col0;
-            const bool vec_ok  = ((prm.ldo & 7) == 0) && ((reinterpret_cast<uintptr_t>(prm.out) & 15) == 0) && (col0 + kBsTileN <= prm.N);
-            if(vec_ok)
-            {
-#pragma unroll
-                for(int i = 0; i < kBsTileN; i += 8)
-                    *reinterpret_cast<uint4*>(dst + i) = make_uint4(pack_bf16x2(acc[i], acc[i + 1]), pack_bf16x2(acc[i + 2], acc[i + 3]),
-                                                                    pack_bf16x2(acc[i + 4], acc[i + 5]), pack_bf16x2(acc[i + 6], acc[i + 7]));
-            }
-            else
-            {
-#pragma unroll
-                for(int i = 0; i < kBsTileN; ++i)
-                    if(col0 + i < prm.N)
-                        dst[i] = __float2bfloat16_rn(acc[i]);
-            }
+            const bool vec_ok = ((prm.ldo & 7) == 0) && ((reinterpret_cast<uintptr_t>(prm.out) & 15) == 0);
+            store_row<kBsTileN>(prm.out, prm.out_mode, static_cast<size_t>(row) * prm.ldo + col0, acc, prm.N - col0, vec_ok);
         }
         tc_fence_before_sync();
     }
@@ -657,12 +644,12 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
                 const int lead   = __ffs(mask) - 1;              // first owning lane of this warp
                 const int wcols  = prm.tma_out;
                 uint8_t* stg     = smem_gen + (warp - 2) * (XR * 64);
-                __nv_bfloat16* t = reinterpret_cast<__nv_bfloat16*>(stg);
+                uint16_t* t      = reinterpret_cast<uint16_t*>(stg);
                 if(ok && owns)
                 {
 #pragma unroll
                     for(int i = 0; i < XR; ++i)
-                        t[i * wcols + (lane - lead)] = __float2bfloat16_rn(acc[i]);
+                        t[i * wcols + (lane - lead)] = cvt_out16(acc[i], prm.out_mode == OUT_F16);
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -679,7 +666,7 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
 #pragma unroll
             for(int i = 0; i < XR; ++i)
                 if(i < prm.M)
-                    prm.out[static_cast<size_t>(i) * prm.ldo + n] = __float2bfloat16_rn(acc[i]);
+                    store_out(prm.out, static_cast<size_t>(i) * prm.ldo + n, acc[i], prm.out_mode);
         }
         tc_fence_before_sync();
     }
@@ -902,24 +889,10 @@ gemm_a8w8_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
             if(lane == 0)
                 mbar_arrive_cluster(part_empty_leader + 8u * b);
         }
-        if(ok && row_ok)
+        if(ok && row_ok && ccol0 < prm.N)
         {
-            __nv_bfloat16* dst = prm.out + static_cast<size_t>(row) * prm.ldo + ccol0;
-            const bool vec_ok  = ((prm.ldo & 7) == 0) && ((reinterpret_cast<uintptr_t>(prm.out) & 15) == 0) && (ccol0 + 128 <= prm.N);
-            if(vec_ok)
-            {
-#pragma unroll
-                for(int i = 0; i < 128; i += 8)
-                    *reinterpret_cast<uint4*>(dst + i) = make_uint4(pack_bf16x2(acc[i], acc[i + 1]), pack_bf16x2(acc[i + 2], acc[i + 3]),
-                                                                    pack_bf16x2(acc[i + 4], acc[i + 5]), pack_bf16x2(acc[i + 6], acc[i + 7]));
-            }
-            else
-            {
-#pragma unroll
-                for(int i = 0; i < 128; ++i)
-                    if(ccol0 + i < prm.N)
-                        dst[i] = __float2bfloat16_rn(acc[i]);
-            }
+            const bool vec_ok = ((prm.ldo & 7) == 0) && ((reinterpret_cast<uintptr_t>(prm.out) & 15) == 0);
+            store_row<128>(prm.out, prm.out_mode, static_cast<size_t>(row) * prm.ldo + ccol0, acc, prm.N - ccol0, vec_ok);
         }
         tc_fence_before_sync();
     }

@@ -1,6 +1,9 @@
 // Shared pieces of the tcgen05 GEMM kernels: enums, status codes, bounded waits, small device helpers.
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_fp4.h>
 #include <type_traits>
 #include "ptx.cuh"
 
@@ -15,7 +18,7 @@
 namespace b200 {
 
 enum GemmKind : int { KIND_BF16 = 0, KIND_MXF8 = 1, KIND_MXF4 = 2, KIND_MXF8F4 = 3 /* e4m3 activations x e2m1 weights */ };
-enum OperandMode : int { OPM_ROWMAJOR = 0, OPM_TILE16 = 1, OPM_A2X128 = 2 };
+enum OperandMode : int { OPM_ROWMAJOR = 0, OPM_TILE16 = 1, OPM_A2X128 = 2, OPM_BATCHED = 4 /* row-major, one matrix per batch entry */ };
 enum SfWire : int { SFW_NONE = 0, SFW_G1250 = 1, SFW_E8M0_SHUFFLE = 2 };
 
 constexpr int kMaxStages  = 8;
@@ -133,6 +136,78 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b)
 {
     __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Output element types of the GEMM epilogues.
+enum OutMode : int
+{
+    OUT_BF16  = 0,
+    OUT_F16   = 1,
+    OUT_F32   = 2,
+    OUT_E2M1  = 3, // packed e2m1, two per byte, no scale (the reference's gemm_a4w4o4)
+    OUT_MXFP8 = 4, // e4m3 data + one UE8M0 scale per 128 output columns (the reference's gemm_a4w4o8)
+};
+
+__device__ __forceinline__ uint32_t pack_f16x2(float a, float b)
+{
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// two fp32 values -> two 16-bit outputs (bf16, or fp16 when f16 is set) in one word
+__device__ __forceinline__ uint32_t pack_out16x2(float a, float b, bool f16) { return f16 ? pack_f16x2(a, b) : pack_bf16x2(a, b); }
+__device__ __forceinline__ uint16_t cvt_out16(float a, bool f16)
+{
+    return f16 ? __half_as_ushort(__float2half_rn(a)) : __bfloat16_as_ushort(__float2bfloat16_rn(a));
+}
+// N consecutive outputs of one row, starting at element index `at`; `valid` of them lie inside the matrix.  vec: the row
+// start is 16-byte aligned (whole 16-byte stores may be used when all N are valid)
+template <int N>
+__device__ __forceinline__ void store_row(void* base, int mode, size_t at, const float (&v)[N], int valid, bool vec)
+{
+    if(mode == OUT_F32)
+    {
+        float* dst = static_cast<float*>(base) + at;
+        if(vec && valid >= N)
+        {
+#pragma unroll
+            for(int i = 0; i < N; i += 4)
+                *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        }
+        else
+        {
+#pragma unroll
+            for(int i = 0; i < N; ++i)
+                if(i < valid)
+                    dst[i] = v[i];
+        }
+    }
+    else
+    {
+        const bool f16 = (mode == OUT_F16);
+        uint16_t* dst  = static_cast<uint16_t*>(base) + at;
+        if(vec && valid >= N)
+        {
+#pragma unroll
+            for(int i = 0; i < N; i += 8)
+                *reinterpret_cast<uint4*>(dst + i) = make_uint4(pack_out16x2(v[i], v[i + 1], f16), pack_out16x2(v[i + 2], v[i + 3], f16),
+                                                                pack_out16x2(v[i + 4], v[i + 5], f16), pack_out16x2(v[i + 6], v[i + 7], f16));
+        }
+        else
+        {
+#pragma unroll
+            for(int i = 0; i < N; ++i)
+                if(i < valid)
+                    dst[i] = cvt_out16(v[i], f16);
+        }
+    }
+}
+// one output element of a 16- or 32-bit output array
+__device__ __forceinline__ void store_out(void* base, size_t idx, float v, int mode)
+{
+    if(mode == OUT_F32)
+        static_cast<float*>(base)[idx] = v;
+    else
+        static_cast<uint16_t*>(base)[idx] = cvt_out16(v, mode == OUT_F16);
 }
 
 

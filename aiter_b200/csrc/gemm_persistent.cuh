@@ -65,8 +65,15 @@ struct PersistentParams
     const uint32_t* sfq;
     int sfp_groups, sfq_groups;   // groups present in each scale tensor
     int sfp_row_words, sfq_row_words;
-    __nv_bfloat16* out;
-    long long ldo;
+    void* out;                    // bf16 / fp16 / fp32 [M][N], packed e2m1 [M][N/2] or e4m3 [M][N] (see out_mode)
+    long long ldo;                // row pitch in output elements (bytes for the e2m1 / e4m3 outputs)
+    int out_mode;                 // OutMode
+    uint8_t* out_scale;           // OUT_MXFP8: UE8M0 per (row, 128 columns) in the packed (M/64, N/128, 16, 4) byte order
+    int out_scale_cols;           // N / 128
+    int noscale;                  // the block scales are not applied (every scale byte reads 2^0): the reference's fp4-output GEMM
+    int batch;                    // batched problem: number of [M,K] x [N,K] pairs (1: plain); tiles_p counts one pair's tiles
+    long long out_batch_stride;   // output elements between two pairs' outputs
+    long long bias_batch_stride;  // bias elements between two pairs' bias vectors (0: shared)
     const void* bias;
     int bias_is_bf16;
     int bias_on_q;
@@ -131,7 +138,7 @@ struct Ring
 // Position in the static work list shared by all roles of a CTA.
 struct WorkIter
 {
-    int u, i, tp, tq, it_beg, n_iters, z;
+    int u, i, tp, tq, it_beg, n_iters, z, b; // b: pair of a batched problem
     bool valid;
 };
 
@@ -187,7 +194,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
     B200_TRACE(if(prm.trace != nullptr && threadIdx.x == 0 && blockIdx.x < 160) prm.trace[64 + 2 * blockIdx.x] = global_timer_ns();)
 
     const int splits      = prm.splits;
-    const int total_units = prm.tiles_p * prm.tiles_q * (prm.csplit > 1 ? 1 : splits);
+    const int total_units = prm.batch * prm.tiles_p * prm.tiles_q * (prm.csplit > 1 ? 1 : splits);
 
     if(threadIdx.x == 0)
     {
@@ -286,6 +293,13 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             w.z  = w.u % splits;
             tile = w.u / splits;
         }
+        w.b = 0;
+        if(prm.batch > 1)
+        {
+            const int per_pair = prm.tiles_p * prm.tiles_q;
+            w.b                = tile / per_pair;
+            tile -= w.b * per_pair;
+        }
         if(prm.tiles_q == 1)
         {
             w.tq = 0;
@@ -379,7 +393,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
 #pragma unroll
         for(int c = 0; c < kTWords; ++c)
             t[c] = 0x7F7F7F7Fu;
-        if(kE8 && q_groups <= 2)
+        if(prm.noscale)
+        {
+            // every scale reads 2^0: the raw bytes are loaded (the barrier protocol stays the same) and ignored
+        }
+        else if(kE8 && q_groups <= 2)
         {
             // Decode tiles (at most 64 rows on the Q side: six groups in all): every warp re-orders all six
             // chunks itself.  That is 24 shared-memory loads and as many byte permutes per K tile, but no
@@ -558,6 +576,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                             mbar_arrive_expect_tx(bar, my_bytes);
                             if(MODE == OPM_ROWMAJOR)
                                 tma_load_2d(dst, map, bar, kt * kTileKBytes, row0);
+                            else if(MODE == OPM_BATCHED)
+                                tma_load_3d(dst, map, bar, kt * kTileKBytes, row0, w.b);
                             else if(MODE == OPM_TILE16)
                                 tma_load_3d(dst, map, bar, 0, row0 >> 4, kt * (kTileKBytes / 16));
                             else
@@ -568,6 +588,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                             mbar_arrive_expect_tx_cluster(bar, my_bytes);
                             if(MODE == OPM_ROWMAJOR)
                                 tma_load_2d_pair(dst, map, bar, kt * kTileKBytes, row0);
+                            else if(MODE == OPM_BATCHED)
+                                tma_load_3d_pair(dst, map, bar, kt * kTileKBytes, row0, w.b);
                             else if(MODE == OPM_TILE16)
                                 tma_load_3d_pair(dst, map, bar, 0, row0 >> 4, kt * (kTileKBytes / 16));
                             else
@@ -583,6 +605,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                 run(std::integral_constant<int, OPM_ROWMAJOR>{});
             else if(mode == OPM_TILE16)
                 run(std::integral_constant<int, OPM_TILE16>{});
+            else if(mode == OPM_BATCHED)
+                run(std::integral_constant<int, OPM_BATCHED>{});
             else
                 run(std::integral_constant<int, OPM_A2X128>{});
             if(*abort_f)
@@ -769,7 +793,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
         const int n_chunks   = bn / chunk;
         const bool split     = (splits > 1);
         const uint32_t acc_empty_remote = (CG == 2) ? map_to_cta(acc_empty_bar(0), 0) : 0u;
-        const bool vec_ok = (!prm.transposed_out) && ((prm.ldo & 7) == 0) && ((reinterpret_cast<uintptr_t>(prm.out) & 15) == 0);
+        const bool vec_ok = (!prm.transposed_out) && ((prm.ldo & (prm.out_mode == OUT_F32 ? 3 : 7)) == 0) && ((reinterpret_cast<uintptr_t>(prm.out) & 15) == 0) &&
+                            ((prm.out_batch_stride & 7) == 0);
         // Output staging: every epilogue warp owns two 2 KB buffers (32 rows x 64 bytes) and stores them with its
         // own TMA tile stores, so the warps never wait for one another and global memory sees whole 64-byte runs.
         const bool use_tma   = prm.tma_store != 0;
@@ -865,7 +890,13 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             const int a       = uc % prm.n_acc;
             const int p       = (w.tp * CG + static_cast<int>(crank)) * kTileP + p_local;
             const int row_q0  = w.tq * bn;
-            const int slot    = (w.tp * prm.tiles_q + w.tq) * CG + static_cast<int>(crank); // ticket / partial slot of this CTA tile
+            const int slot    = ((w.b * prm.tiles_p + w.tp) * prm.tiles_q + w.tq) * CG + static_cast<int>(crank); // ticket / partial slot of this CTA tile
+            // this pair's output and bias (batched problems)
+            const bool out_f16 = (prm.out_mode == OUT_F16);
+            void* const out_b  = static_cast<uint8_t*>(prm.out) +
+                                static_cast<size_t>(w.b) * static_cast<size_t>(prm.out_batch_stride) * (prm.out_mode == OUT_F32 ? 4u : 2u);
+            const void* const bias_b = prm.bias == nullptr ? nullptr
+                                       : static_cast<const uint8_t*>(prm.bias) + static_cast<size_t>(w.b) * static_cast<size_t>(prm.bias_batch_stride) * (prm.bias_is_bf16 ? 2u : 4u);
             ok = bounded_wait(acc_full_bar(a), (uc / prm.n_acc) & 1, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, uc);
             ok = __all_sync(0xffffffffu, ok);
             if(!ok)
@@ -972,15 +1003,15 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                 // finish one chunk of columns: alpha / bias, bf16, store
                 auto finish = [&](float (&v)[32], const int c) {
                     const int q_first = row_q0 + c * chunk;
-                    if(prm.bias != nullptr)
+                    if(bias_b != nullptr)
                     {
-                        const float bp = (!prm.bias_on_q && p < prm.rows_p) ? load_bias(prm.bias, prm.bias_is_bf16, p) : 0.f;
+                        const float bp = (!prm.bias_on_q && p < prm.rows_p) ? load_bias(bias_b, prm.bias_is_bf16, p) : 0.f;
 #pragma unroll
                         for(int j = 0; j < 32; ++j)
                         {
                             float b = bp;
                             if(prm.bias_on_q)
-                                b = (j < chunk && q_first + j < prm.rows_q) ? load_bias(prm.bias, prm.bias_is_bf16, q_first + j) : 0.f;
+                                b = (j < chunk && q_first + j < prm.rows_q) ? load_bias(bias_b, prm.bias_is_bf16, q_first + j) : 0.f;
                             v[j] = prm.alpha * v[j] + prm.beta * b;
                         }
                     }
@@ -1002,8 +1033,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
 #pragma unroll
                             for(int j = 0; j < 4; ++j)
                                 *reinterpret_cast<uint4*>(buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) * 16)) =
-                                    make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
-                                               pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
+                                    make_uint4(pack_out16x2(v[8 * j], v[8 * j + 1], out_f16), pack_out16x2(v[8 * j + 2], v[8 * j + 3], out_f16),
+                                               pack_out16x2(v[8 * j + 4], v[8 * j + 5], out_f16), pack_out16x2(v[8 * j + 6], v[8 * j + 7], out_f16));
                         }
                         else
                         {
@@ -1011,7 +1042,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
 #pragma unroll
                             for(int j = 0; j < 32; ++j)
                                 if(j < chunk)
-                                    reinterpret_cast<__nv_bfloat16*>(buf)[j * 32 + lane] = __float2bfloat16_rn(v[j]);
+                                    reinterpret_cast<uint16_t*>(buf)[j * 32 + lane] = cvt_out16(v[j], out_f16);
                         }
                         fence_proxy_async_smem();
                         __syncwarp();
@@ -1030,22 +1061,44 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                     {
                         if(!prm.transposed_out)
                         {
-                            __nv_bfloat16* dst = prm.out + static_cast<size_t>(p) * prm.ldo + q_first;
-                            if(vec_ok && q_first + chunk <= prm.rows_q)
+                            const size_t at = static_cast<size_t>(p) * prm.ldo + q_first;
+                            if(prm.out_mode == OUT_F32)
                             {
+                                float* dst = static_cast<float*>(out_b) + at;
+                                if(vec_ok && q_first + chunk <= prm.rows_q)
+                                {
 #pragma unroll
-                                for(int j = 0; j < 32; j += 8)
-                                    if(j < chunk)
-                                        *reinterpret_cast<uint4*>(dst + j) =
-                                            make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
-                                                       pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
+                                    for(int j = 0; j < 32; j += 4)
+                                        if(j < chunk)
+                                            *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                }
+                                else
+                                {
+#pragma unroll
+                                    for(int j = 0; j < 32; ++j)
+                                        if(j < chunk && q_first + j < prm.rows_q)
+                                            dst[j] = v[j];
+                                }
                             }
                             else
                             {
+                                uint16_t* dst = static_cast<uint16_t*>(out_b) + at;
+                                if(vec_ok && q_first + chunk <= prm.rows_q)
+                                {
 #pragma unroll
-                                for(int j = 0; j < 32; ++j)
-                                    if(j < chunk && q_first + j < prm.rows_q)
-                                        dst[j] = __float2bfloat16_rn(v[j]);
+                                    for(int j = 0; j < 32; j += 8)
+                                        if(j < chunk)
+                                            *reinterpret_cast<uint4*>(dst + j) =
+                                                make_uint4(pack_out16x2(v[j], v[j + 1], out_f16), pack_out16x2(v[j + 2], v[j + 3], out_f16),
+                                                           pack_out16x2(v[j + 4], v[j + 5], out_f16), pack_out16x2(v[j + 6], v[j + 7], out_f16));
+                                }
+                                else
+                                {
+#pragma unroll
+                                    for(int j = 0; j < 32; ++j)
+                                        if(j < chunk && q_first + j < prm.rows_q)
+                                            dst[j] = cvt_out16(v[j], out_f16);
+                                }
                             }
                         }
                         else
@@ -1055,17 +1108,106 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                             {
                                 const int q = q_first + j;
                                 if(j < chunk && q < prm.rows_q)
-                                    prm.out[static_cast<size_t>(q) * prm.ldo + p] = __float2bfloat16_rn(v[j]);
+                                    store_out(out_b, static_cast<size_t>(q) * prm.ldo + p, v[j], prm.out_mode);
                             }
                         }
                     }
                 };
-                if(!split && prm.tma_store == 2)
+                if(prm.out_mode >= OUT_E2M1)
+                {
+                    // Re-quantising epilogue (row-major output, no K split, tile width a multiple of 128): the thread's row
+                    // goes out 128 columns at a time.  e4m3 + UE8M0: the block's maximum first (one pass over the TMEM
+                    // columns), scale byte = RoundUp(amax / 448) with amax clamped below by FLT_MIN, then a second pass
+                    // converts (TMEM can be read twice; 128 fp32 values would not fit the registers).  Packed e2m1: a
+                    // saturating round-to-nearest-even cast, no scale.  Same arithmetic as the activation quantiser.
+                    uint8_t* const out8 = static_cast<uint8_t*>(prm.out);
+                    const bool row_ok   = p < prm.rows_p;
+                    for(int b128 = 0; b128 < (bn >> 7); ++b128)
+                    {
+                        const int q_first = row_q0 + b128 * 128;
+                        const bool col_ok = q_first < prm.rows_q;
+                        float rscale      = 1.f;
+                        if(prm.out_mode == OUT_MXFP8)
+                        {
+                            float amax   = 0.f;
+                            bool has_nan = false;
+#pragma unroll 1
+                            for(int c = 0; c < 4; ++c)
+                            {
+                                uint32_t r[32];
+                                tmem_ld_x32(tacc + b128 * 128 + c * 32, r);
+                                tmem_ld_wait();
+#pragma unroll
+                                for(int j = 0; j < 32; ++j)
+                                {
+                                    const float x = __uint_as_float(r[j]);
+                                    amax          = fmaxf(amax, fabsf(x));
+                                    has_nan |= (x != x);
+                                }
+                            }
+                            amax = has_nan ? __uint_as_float(0x7FC00000u) : fmaxf(amax, 1.17549435e-38f);
+                            const uint32_t qb   = __float_as_uint(__fdiv_rn(amax, 448.0f));
+                            const uint32_t ex   = (qb >> 23) & 0xFFu;
+                            const uint32_t byte = ex + (((qb & 0x7FFFFFu) != 0u && ex < 0xFFu) ? 1u : 0u);
+                            rscale = __uint_as_float(byte == 0xFFu ? 0x7F800001u : (byte == 254u ? 0x00400000u : ((254u - byte) << 23)));
+                            if(row_ok && col_ok)
+                            {
+                                const int m = p, j = q_first >> 7;
+                                prm.out_scale[((static_cast<size_t>(m >> 6) * prm.out_scale_cols + j) * 16 + (m & 15)) * 4 + ((m & 63) >> 4)] = static_cast<uint8_t>(byte);
+                            }
+                        }
+#pragma unroll 1
+                        for(int c = 0; c < 4; ++c)
+                        {
+                            uint32_t r[32];
+                            tmem_ld_x32(tacc + b128 * 128 + c * 32, r);
+                            tmem_ld_wait();
+                            if(prm.out_mode == OUT_MXFP8)
+                            {
+                                uint32_t wds[8];
+#pragma unroll
+                                for(int h = 0; h < 8; ++h)
+                                {
+                                    const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
+                                        make_float2(__uint_as_float(r[4 * h]) * rscale, __uint_as_float(r[4 * h + 1]) * rscale), __NV_SATFINITE, __NV_E4M3);
+                                    const __nv_fp8x2_storage_t hi2 = __nv_cvt_float2_to_fp8x2(
+                                        make_float2(__uint_as_float(r[4 * h + 2]) * rscale, __uint_as_float(r[4 * h + 3]) * rscale), __NV_SATFINITE, __NV_E4M3);
+                                    wds[h] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi2) << 16);
+                                }
+                                if(row_ok && q_first + c * 32 < prm.rows_q)
+                                {
+                                    uint4* dst = reinterpret_cast<uint4*>(out8 + static_cast<size_t>(p) * prm.ldo + q_first + c * 32);
+                                    dst[0]     = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+                                    dst[1]     = make_uint4(wds[4], wds[5], wds[6], wds[7]);
+                                }
+                            }
+                            else
+                            {
+                                uint32_t wds[4];
+#pragma unroll
+                                for(int h = 0; h < 4; ++h)
+                                {
+                                    uint32_t packed = 0;
+#pragma unroll
+                                    for(int i = 0; i < 4; ++i)
+                                        packed |= static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(
+                                                      make_float2(__uint_as_float(r[8 * h + 2 * i]), __uint_as_float(r[8 * h + 2 * i + 1])), __NV_E2M1, cudaRoundNearest))
+                                                  << (8 * i);
+                                    wds[h] = packed;
+                                }
+                                if(row_ok && q_first + c * 32 < prm.rows_q)
+                                    *reinterpret_cast<uint4*>(out8 + static_cast<size_t>(p) * prm.ldo + ((q_first + c * 32) >> 1)) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+                            }
+                        }
+                    }
+                    release_acc();
+                }
+                else if(!split && prm.tma_store == 2)
                 {
                     // Wide path (row-major output, tile width a multiple of 64): 64 columns per step, so that the
                     // one warp per scheduler that runs this code has long runs of independent instructions: one
                     // TMEM load, 32 conversions, 8 shared-memory stores (128B-swizzled rows), one tile store.
-                    const bool epi_math = (prm.bias != nullptr) || (prm.alpha != 1.0f);
+                    const bool epi_math = (bias_b != nullptr) || (prm.alpha != 1.0f);
                     const int p_warp0   = (w.tp * CG + static_cast<int>(crank)) * kTileP + quarter * 32;
                     const int n64       = bn >> 6;
                     for(int c = 0; c < n64; ++c)
@@ -1078,13 +1220,13 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                         const int q_first = row_q0 + c * 64;
                         if(epi_math)
                         {
-                            const float bp = (prm.bias != nullptr && !prm.bias_on_q && p < prm.rows_p) ? load_bias(prm.bias, prm.bias_is_bf16, p) : 0.f;
+                            const float bp = (bias_b != nullptr && !prm.bias_on_q && p < prm.rows_p) ? load_bias(bias_b, prm.bias_is_bf16, p) : 0.f;
 #pragma unroll
                             for(int j = 0; j < 64; ++j)
                             {
                                 float b = bp;
-                                if(prm.bias != nullptr && prm.bias_on_q)
-                                    b = (q_first + j < prm.rows_q) ? load_bias(prm.bias, prm.bias_is_bf16, q_first + j) : 0.f;
+                                if(bias_b != nullptr && prm.bias_on_q)
+                                    b = (q_first + j < prm.rows_q) ? load_bias(bias_b, prm.bias_is_bf16, q_first + j) : 0.f;
                                 r[j] = __float_as_uint(prm.alpha * __uint_as_float(r[j]) + prm.beta * b);
                             }
                         }
@@ -1099,13 +1241,26 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                         }
                         __syncwarp();
                         uint8_t* row = epi_gen + wbuf + lane * 128;
+                        if(out_f16)
+                        {
 #pragma unroll
-                        for(int j = 0; j < 8; ++j)
-                            *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) * 16)) =
-                                make_uint4(pack_bf16x2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1])),
-                                           pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
-                                           pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])),
-                                           pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])));
+                            for(int j = 0; j < 8; ++j)
+                                *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) * 16)) =
+                                    make_uint4(pack_f16x2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1])),
+                                               pack_f16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
+                                               pack_f16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])),
+                                               pack_f16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])));
+                        }
+                        else
+                        {
+#pragma unroll
+                            for(int j = 0; j < 8; ++j)
+                                *reinterpret_cast<uint4*>(row + ((j ^ (lane & 7)) * 16)) =
+                                    make_uint4(pack_bf16x2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1])),
+                                               pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
+                                               pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])),
+                                               pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])));
+                        }
                         fence_proxy_async_smem();
                         __syncwarp();
                         if(lane == 0 && p_warp0 < prm.rows_p && q_first < prm.rows_q)

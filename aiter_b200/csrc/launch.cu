@@ -76,6 +76,17 @@ static CUtensorMap operand_map(const Operand& op, int box_rows, const char* what
         cuuint32_t box[2]     = {kTileKBytes, static_cast<cuuint32_t>(box_rows)};
         return encode_map(op.ptr, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, what);
     }
+    if(op.mode == OPM_BATCHED)
+    {
+        // [batch][rows][K bytes]: the row-major tile of matrix b is box (128 B, rows, 1) at coordinate (k, row, b); rows past
+        // the end of one matrix are zero-filled, never taken from the next one
+        B200_CHECK(op.ld_bytes % 16 == 0 && op.batch_stride_bytes % 16 == 0, what, ": row pitch and batch stride must be multiples of 16 bytes");
+        B200_CHECK(op.batch_stride_bytes > 0, what, ": internal: batch stride missing");
+        cuuint64_t dims[3]    = {static_cast<cuuint64_t>(op.kbytes), static_cast<cuuint64_t>(op.rows), static_cast<cuuint64_t>(op.batch)};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(op.ld_bytes), static_cast<cuuint64_t>(op.batch_stride_bytes)};
+        cuuint32_t box[3]     = {kTileKBytes, static_cast<cuuint32_t>(box_rows), 1};
+        return encode_map(op.ptr, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, what);
+    }
     if(op.mode == OPM_TILE16)
     {
         B200_CHECK(op.rows % 16 == 0 && op.kbytes % 32 == 0, what,
@@ -643,7 +654,8 @@ static void launch_decode_instance(int ctas, int csplit, size_t smem, cudaStream
 static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, int kkind, DeviceState& st)
 {
     const int named_stages = prob.cfg.stages; // what the caller's configuration asked for (0: this kernel's own choice)
-    if(decode_kernel_disabled() || !cfg.swap || cfg.cg != 1 || cfg.bn > 64 || prob.M > cfg.bn || kkind == KIND_MXF8F4 || prob.scratch != nullptr)
+    if(decode_kernel_disabled() || !cfg.swap || cfg.cg != 1 || cfg.bn > 64 || prob.M > cfg.bn || kkind == KIND_MXF8F4 || prob.scratch != nullptr ||
+       prob.out_mode != OUT_BF16 || prob.batch > 1 || prob.noscale)
         return false;
     const int num_k_iters = static_cast<int>((prob.act.kbytes + kTileKBytes - 1) / kTileKBytes);
     int csplit            = 1 << cfg.log2_splitk;
@@ -949,6 +961,22 @@ static void launch_gemm_locked(const GemmProblem& prob)
     require_healthy(st, prob.device);
 
     KernelConfig cfg = prob.cfg;
+    const bool requant = (prob.out_mode == OUT_E2M1 || prob.out_mode == OUT_MXFP8);
+    if(requant)
+    {
+        // the re-quantising epilogue owns whole 128-column blocks of a row: activations on the 128-row slot, no K split,
+        // tile width 128 or 256
+        B200_CHECK(prob.kind == PK_MXFP4, "low-precision outputs are built for the MXFP4 GEMM only");
+        B200_CHECK(prob.N % 128 == 0, "low-precision outputs need N % 128 == 0 (got N=", prob.N, ")");
+        B200_CHECK(prob.out_mode != OUT_MXFP8 || (prob.M % 64 == 0 && prob.out_scale != nullptr), "the mxfp8 output needs M % 64 == 0 and an out_scale tensor");
+        B200_CHECK(prob.bias == nullptr, "low-precision outputs take no bias");
+        cfg.swap        = 0;
+        cfg.log2_splitk = 0;
+        if(cfg.bn != 128 && cfg.bn != 256)
+            cfg.bn = (prob.N % 256 == 0 && prob.M > 256) ? 256 : 128;
+    }
+    B200_CHECK(prob.batch == 1 || (prob.kind == PK_BF16 && prob.act.mode == OPM_BATCHED && prob.wgt.mode == OPM_BATCHED),
+               "internal: batched launches are built for row-major bf16 operands");
     choose_config(prob.kind, prob.M, prob.N, prob.K, st.sm_count, cfg);
     B200_CHECK(cfg.log2_splitk >= 0 && cfg.log2_splitk <= 8, "log2 of the K split must be between 0 and 8 (got ", cfg.log2_splitk, ")");
     {
@@ -984,7 +1012,8 @@ static void launch_gemm_locked(const GemmProblem& prob)
     const int atoms_k  = (kkind == KIND_MXF4) ? 2 : 1;
     const int sf_cols  = sf_cols_per_stage(kkind);
     // the output leaves through shared memory and TMA tile stores when its pitch and base allow a tensor map
-    const bool tma_store = ((reinterpret_cast<uintptr_t>(prob.out) & 15) == 0) && (prob.ldo % 8 == 0) && (cfg.swap || cfg.bn >= 32);
+    const bool tma_store = ((reinterpret_cast<uintptr_t>(prob.out) & 15) == 0) && (prob.ldo % 8 == 0) && (cfg.swap || cfg.bn >= 32) &&
+                           (prob.out_mode == OUT_BF16 || prob.out_mode == OUT_F16) && prob.batch == 1;
     // Decode shapes: the K split runs across the CTAs of a thread-block cluster, one output tile per cluster; the
     // partial accumulators meet in the first CTA's shared memory instead of a global workspace.
     int csplit = 1;
@@ -1003,8 +1032,9 @@ static void launch_gemm_locked(const GemmProblem& prob)
     const int tiles_q = static_cast<int>((Q.rows + cfg.bn - 1) / cfg.bn);
     B200_CHECK(tiles_q <= 65535 && splits <= 65535, "grid too large");
     const int counter_slots = (prob.scratch != nullptr) ? prob.scratch->counter_slots : kCounterSlots;
-    B200_CHECK(splits == 1 || static_cast<long long>(tiles_p) * tiles_q * cg <= counter_slots,
+    B200_CHECK(splits == 1 || static_cast<long long>(tiles_p) * tiles_q * cg * prob.batch <= counter_slots,
                "split-K supports at most ", counter_slots, " output tiles here");
+    B200_CHECK(static_cast<long long>(tiles_p) * tiles_q * prob.batch * std::max(splits, 1) < (1LL << 31), "too many work units");
 
     unsigned long long* trace = nullptr;
 #ifdef AITER_B200_TRACING
@@ -1032,7 +1062,7 @@ static void launch_gemm_locked(const GemmProblem& prob)
     unsigned int* ws_counter = nullptr;
     if(splits > 1)
     {
-        const size_t bytes = static_cast<size_t>(tiles_p) * tiles_q * cg * splits * static_cast<size_t>(cfg.bn) * kTileP * sizeof(float);
+        const size_t bytes = static_cast<size_t>(prob.batch) * tiles_p * tiles_q * cg * splits * static_cast<size_t>(cfg.bn) * kTileP * sizeof(float);
         if(prob.scratch != nullptr)
         {
             B200_CHECK(bytes <= prob.scratch->partial_bytes, "this shape needs ", bytes, " bytes of split-K scratch, more than the ",
@@ -1093,8 +1123,15 @@ static void launch_gemm_locked(const GemmProblem& prob)
     prm.sfq_groups     = static_cast<int>(SQ.padded_rows / 32);
     prm.sfp_row_words  = static_cast<int>(SP.padded_cols * 8);
     prm.sfq_row_words  = static_cast<int>(SQ.padded_cols * 8);
-    prm.out            = static_cast<__nv_bfloat16*>(prob.out);
+    prm.out            = prob.out;
     prm.ldo            = prob.ldo;
+    prm.out_mode       = prob.out_mode;
+    prm.out_scale      = static_cast<uint8_t*>(prob.out_scale);
+    prm.out_scale_cols = static_cast<int>(prob.N / 128);
+    prm.noscale        = prob.noscale;
+    prm.batch          = static_cast<int>(prob.batch);
+    prm.out_batch_stride  = prob.out_batch_stride;
+    prm.bias_batch_stride = prob.bias_batch_stride;
     prm.bias           = prob.bias;
     prm.bias_is_bf16   = prob.bias_is_bf16;
     prm.bias_on_q      = cfg.swap ? 0 : 1;
@@ -1115,7 +1152,7 @@ static void launch_gemm_locked(const GemmProblem& prob)
             ++sh;
         prm.split_shift = ((1 << sh) == ksplit) ? sh : -1;
     }
-    const long long units = static_cast<long long>(tiles_p) * tiles_q * splits;
+    const long long units = static_cast<long long>(prob.batch) * tiles_p * tiles_q * splits;
     // a cluster-split tile owns its cluster for the whole launch: one cluster per tile, however many run at once
     const int clusters    = csplit > 1 ? static_cast<int>(units) : static_cast<int>(std::min<long long>(units, st.sm_count / cg));
     const bool multi_unit = units > clusters;
@@ -1255,11 +1292,12 @@ static void launch_blockscale_e8m0(const BlockScaleProblem& prob)
     p.wgt    = prob.wgt;
     p.act_sf = ScaleOperand{buf, SFW_G1250, ga * 32, prob.K / 32};
     p.wgt_sf = ScaleOperand{buf + ga * 32 * kb128, SFW_G1250, gw * 32, prob.K / 32};
-    p.out    = prob.out;
-    p.ldo    = prob.ldo;
-    p.device = prob.device;
-    p.stream = prob.stream;
-    p.cfg    = prob.cfg;
+    p.out      = prob.out;
+    p.ldo      = prob.ldo;
+    p.out_mode = prob.out_mode;
+    p.device   = prob.device;
+    p.stream   = prob.stream;
+    p.cfg      = prob.cfg;
     launch_gemm(p);
 }
 
@@ -1316,8 +1354,9 @@ void launch_blockscale(const BlockScaleProblem& prob)
     prm.xs_stride_m = prob.xs_stride_m;
     prm.xs_stride_k = prob.xs_stride_k;
     prm.w_scale     = prob.w_scale;
-    prm.out         = static_cast<__nv_bfloat16*>(prob.out);
+    prm.out         = prob.out;
     prm.ldo         = prob.ldo;
+    prm.out_mode    = prob.out_mode;
     prm.status      = st.status;
     prm.scales_e8m0 = prob.scales_are_e8m0 ? 1 : 0;
     // 256 x 256 tiles on CTA pairs or 128 x 128 tiles on single CTAs: whichever needs less time by waves x cycles per K
@@ -1418,7 +1457,7 @@ void launch_blockscale(const BlockScaleProblem& prob)
         // output as warp-wide TMA tiles: a warp owns 32 columns, or 16 when eight slices share the tile's 128
         CUtensorMap mo = ma;
         prm.tma_out    = 0;
-        if((reinterpret_cast<uintptr_t>(prob.out) & 15) == 0 && prob.ldo % 8 == 0)
+        if((reinterpret_cast<uintptr_t>(prob.out) & 15) == 0 && prob.ldo % 8 == 0 && prob.out_mode != OUT_F32)
         {
             prm.tma_out                 = (prm.cluster && splits == 8) ? 16 : 32;
             const cuuint64_t dims[2]    = {static_cast<cuuint64_t>(prob.N) * 2, static_cast<cuuint64_t>(prob.M)};

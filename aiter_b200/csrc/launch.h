@@ -46,6 +46,8 @@ struct Operand
     long long kbytes = 0;    // bytes along K per row
     long long ld_bytes = 0;  // row pitch in bytes (row-major mode only)
     int mode = 0;            // OperandMode
+    long long batch_stride_bytes = 0; // batched problems (mode OPM_BATCHED): bytes between two matrices
+    long long batch = 1;              //                                       number of matrices
 };
 
 struct ScaleOperand
@@ -83,7 +85,13 @@ struct GemmProblem
     Operand act, wgt;
     ScaleOperand act_sf, wgt_sf;
     void* out = nullptr;
-    long long ldo = 0;          // elements
+    long long ldo = 0;          // row pitch in output elements (bytes for the e2m1 / e4m3 outputs)
+    int out_mode = 0;           // OutMode: bf16, fp16, fp32, packed e2m1 (no scale), e4m3 + UE8M0 per 128 columns
+    void* out_scale = nullptr;  // OUT_MXFP8: [M, N/128] bytes, filled in the packed (M/64, N/128, 16, 4) order
+    int noscale = 0;            // ignore the block scales (the reference's fp4-output GEMM is its "noscale" kernel)
+    long long batch = 1;        // [batch, M, K] x [batch, N, K] -> [batch, M, N] in one launch (bf16 operands, row-major)
+    long long out_batch_stride = 0;  // output elements between two matrices
+    long long bias_batch_stride = 0; // bias elements between two matrices' bias vectors (0: shared)
     const void* bias = nullptr; // indexed by n
     int bias_is_bf16 = 0;
     float alpha = 1.f, beta = 1.f;
@@ -121,6 +129,7 @@ struct BlockScaleProblem
     bool cfg_given = false;
     void* out = nullptr;
     long long ldo = 0;
+    int out_mode = 0;             // OutMode: bf16, fp16 or fp32
     int device = 0;
     cudaStream_t stream = nullptr;
 };

@@ -52,6 +52,9 @@ def opus_gemm_a16w16_tune(XQ: Tensor, WQ: Tensor, Y: Tensor, bias=None, kernelId
 
 
 def opus_gemm(XQ: Tensor, WQ: Tensor, Y: Tensor, group_layout=None, x_scale=None, w_scale=None, bias=None) -> Tensor:
+    """Y[b,M,N] = XQ[b,M,K] @ WQ[b,N,K]^T in one launch.  bf16 operands: Y bf16 or fp32, optional bias [N] or [b,N].
+    fp8 operands with x_scale [b,M,K/128] and w_scale [b,N/128,K/128] (fp32): the 128-block-scaled product, Y fp32
+    (the reference's a8w8_scale pipeline, csrc/opus_gemm/opus_gemm.cu:153-186)."""
     _ffi.call("opus_gemm", XQ, WQ, Y, group_layout, x_scale, w_scale, bias)
     return Y
 
@@ -62,8 +65,8 @@ def gemm_a16w16_opus(A: Tensor, B: Tensor, bias: Tensor | None = None, dtype: to
     other shapes go through the library heuristic.  A [M,K] or [b,M,K]; B [N,K] or [b,N,K]."""
     if A.dtype != torch.bfloat16 or B.dtype != torch.bfloat16:
         raise NotImplementedError(f"gemm_a16w16_opus only supports bf16 A/B (got A.dtype={A.dtype}, B.dtype={B.dtype}).")
-    if dtype != torch.bfloat16:
-        raise NotImplementedError("gemm_a16w16_opus: only bf16 output is built")
+    if dtype not in (torch.bfloat16, torch.float32):
+        raise NotImplementedError(f"gemm_a16w16_opus only supports bf16/fp32 output dtype, got {dtype}")
     squeeze = A.dim() == 2
     A3 = A.unsqueeze(0) if squeeze else A
     B3 = B.unsqueeze(0) if B.dim() == 2 else B

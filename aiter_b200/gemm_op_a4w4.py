@@ -4,8 +4,12 @@ from __future__ import annotations
 import torch
 from torch import Tensor
 
+import logging
+
 from . import _ffi, dtypes
 from .config import TunedTable
+
+logger = logging.getLogger("aiter")
 
 _table = TunedTable("a4w4")
 
@@ -41,14 +45,80 @@ def gemm_a4w4_blockscale_tune(XQ: Tensor, WQ: Tensor, x_scale: Tensor, w_scale: 
     return Out
 
 
+# the mxfp8 output of the F4GEMM entry point carries one E8M0 scale per 128 output columns (gemm_op_a4w4.py:327-329)
+MXFP8_OUT_SCALE_BLOCK = 128
+
+
+def _alloc_f4gemm_out(M: int, N: int, dtype: torch.dtype, device) -> Tensor:
+    """bf16 [M, N]; packed fp4 [M, N/2]; fp8 [M, N] (its scale is a separate tensor) (gemm_op_a4w4.py:337-346)."""
+    if dtype == dtypes.fp4x2:
+        assert N % 2 == 0, "packed fp4 output requires even N"
+        return torch.empty((M, N // 2), dtype=torch.uint8, device=device).view(dtypes.fp4x2)
+    return torch.empty((M, N), dtype=dtype, device=device)
+
+
+def _alloc_f4gemm_out_scale(M: int, N: int, dtype: torch.dtype, device):
+    """[M, N/128] e8m0 for the fp8 output, which the kernel fills in the packed (M/64, N/128, 16, 4) order; None
+    otherwise (gemm_op_a4w4.py:349-362)."""
+    if dtype != dtypes.fp8:
+        return None
+    assert N % MXFP8_OUT_SCALE_BLOCK == 0, f"mxfp8 output requires N % {MXFP8_OUT_SCALE_BLOCK} == 0, got N={N}"
+    assert M % 64 == 0, f"mxfp8 output-scale packing requires M % 64 == 0, got M={M}"
+    return torch.empty((M, N // MXFP8_OUT_SCALE_BLOCK), dtype=torch.uint8, device=device).view(dtypes.fp8_e8m0)
+
+
+def unpack_mxfp8_out_scale(packed: Tensor, M: int, N: int) -> Tensor:
+    """Packed (M/64, N/128, 16, 4) scale bytes -> row-major [M, N/128] (gemm_op_a4w4.py:365-380)."""
+    assert M % 64 == 0, f"mxfp8 output-scale packing requires M % 64 == 0, got M={M}"
+    assert N % MXFP8_OUT_SCALE_BLOCK == 0, f"mxfp8 output requires N % {MXFP8_OUT_SCALE_BLOCK} == 0, got N={N}"
+    sn = N // MXFP8_OUT_SCALE_BLOCK
+    u8 = packed.reshape(-1).view(torch.uint8)[: (M // 64) * sn * 64]
+    return u8.reshape(M // 64, sn, 16, 4).permute(0, 3, 2, 1).reshape(M, sn).contiguous().view(dtypes.fp8_e8m0)
+
+
 def gemm_mxfp4_asm(A: Tensor, B: Tensor, ScaleA: Tensor, ScaleB: Tensor, dtype: torch.dtype = dtypes.bf16,
-                   a_preshuffle: bool = False, kernelName: str = "") -> Tensor:
-    """MXFP4 GEMM with the (m/32,k/4,32,4) scale layout and a 16x16-byte tiled B (aiter/ops/gemm_op_a4w4.py:290-330)."""
-    if dtype != dtypes.bf16:
-        raise NotImplementedError("gemm_mxfp4_asm: only bf16 output is built")
-    out = torch.empty((A.shape[0], B.shape[0]), dtype=dtype, device=A.device)
-    _ffi.call("mxfp4_gemm_asm", A, B, ScaleA, ScaleB, out, None, kernelName if kernelName else None, int(bool(a_preshuffle)))
-    return out
+                   a_preshuffle: bool = False, kernelName: str = ""):
+    """MXFP4 GEMM with the (m/32,k/4,32,4) scale layout and 16x16-byte tiled operands (B always, A when a_preshuffle)
+    (aiter/ops/gemm_op_a4w4.py:383-407).  dtype: bf16 [M,N]; fp4x2: packed e2m1 [M,N/2] of the unscaled product; fp8:
+    (e4m3 [M,N], e8m0 scale per 128 columns in the packed (M/64,N/128,16,4) order - see unpack_mxfp8_out_scale)."""
+    M, N = A.shape[0], B.shape[0]
+    out = _alloc_f4gemm_out(M, N, dtype, A.device)
+    out_scale = _alloc_f4gemm_out_scale(M, N, dtype, A.device)
+    _ffi.call("mxfp4_gemm_asm", A, B, ScaleA, ScaleB, out, out_scale, kernelName if kernelName else None, int(bool(a_preshuffle)))
+    return (out, out_scale) if out_scale is not None else out
+
+
+def _f4gemm_dispatch(A, B, A_scale, B_scale, *, dtype, apreshuffle, global_A_scale, global_B_scale, bias, alpha, beta):
+    """The reference's gfx1250 F4GEMM dispatch (gemm_op_a4w4.py:80-122): bias / alpha / beta are not part of these
+    kernels (a warning, as there); per-tensor global scales select NVFP4, which is not built here."""
+    if bias is not None or (alpha is not None and alpha != 1.0) or (beta is not None and beta != 0.0):
+        logger.warning("gemm_a4w4o4 / gemm_a4w4o8 ignore bias/alpha/beta: not supported by the low-precision-output kernels.")
+    if global_A_scale is not None or global_B_scale is not None:
+        raise NotImplementedError("NVFP4 inputs (e4m3 scales per 16 elements plus per-tensor global scales) are not built")
+    m = A.numel() // A.shape[-1]
+    return gemm_mxfp4_asm(A.view(m, A.shape[-1]), B, A_scale, B_scale, dtype=dtype, a_preshuffle=bool(apreshuffle))
+
+
+def gemm_a4w4o4(A: Tensor, B: Tensor, A_scale: Tensor, B_scale: Tensor, bias: Tensor | None = None, alpha: float | None = 1.0,
+                beta: float | None = 0.0, bpreshuffle: bool | None = True, apreshuffle: bool | None = False,
+                global_A_scale: Tensor | None = None, global_B_scale: Tensor | None = None) -> Tensor:
+    """A4W4 GEMM with packed FP4 (e2m1) output [*lead, N/2] (gemm_op_a4w4.py:476-516).  As in the reference, whose
+    fp4-output kernel is its "noscale" variant, the block scales are not applied: the fp32 product of the raw e2m1 values
+    is cast to e2m1 (round to nearest even, saturating).  B 16x16-byte tiled, scales in the (m/32,k/4,32,4) order."""
+    out = _f4gemm_dispatch(A, B, A_scale, B_scale, dtype=dtypes.fp4x2, apreshuffle=apreshuffle, global_A_scale=global_A_scale,
+                           global_B_scale=global_B_scale, bias=bias, alpha=alpha, beta=beta)
+    return out.view(*A.shape[:-1], out.shape[-1])
+
+
+def gemm_a4w4o8(A: Tensor, B: Tensor, A_scale: Tensor, B_scale: Tensor, bias: Tensor | None = None, alpha: float | None = 1.0,
+                beta: float | None = 0.0, bpreshuffle: bool | None = True, apreshuffle: bool | None = False,
+                global_A_scale: Tensor | None = None, global_B_scale: Tensor | None = None):
+    """A4W4 GEMM with mxfp8 output: (e4m3 data [*lead, N], E8M0 scale) with one RoundUp scale per 128 output columns,
+    the scale in the packed (M/64, N/128, 16, 4) order - unpack with unpack_mxfp8_out_scale (gemm_op_a4w4.py:519-567)."""
+    o, sc = _f4gemm_dispatch(A, B, A_scale, B_scale, dtype=dtypes.fp8, apreshuffle=apreshuffle, global_A_scale=global_A_scale,
+                             global_B_scale=global_B_scale, bias=bias, alpha=alpha, beta=beta)
+    lead = A.shape[:-1]
+    return o.view(*lead, o.shape[-1]), sc.view(*lead, sc.shape[-1])
 
 
 def gemm_a4w4(A: Tensor, B: Tensor, A_scale: Tensor, B_scale: Tensor, bias: Tensor | None = None,
@@ -60,7 +130,7 @@ def gemm_a4w4(A: Tensor, B: Tensor, A_scale: Tensor, B_scale: Tensor, bias: Tens
     if dtype in (dtypes.fp4x2, dtypes.fp8):
         raise NotImplementedError("gemm_a4w4 returns one plain-dtype tensor; use gemm_a4w4o4 / gemm_a4w4o8")
     if global_A_scale is not None or global_B_scale is not None:
-        raise NotImplementedError("NVFP4 (per-tensor global scales) is not built")
+        raise NotImplementedError("NVFP4 inputs (e4m3 scales per 16 elements plus per-tensor global scales) are not built")
     m = A.numel() // A.shape[-1]
     n = B.shape[0]
     k = A.shape[-1] * 2

@@ -43,7 +43,7 @@ def gemm_a8w8_blockscale(XQ: Tensor, WQ: Tensor, x_scale: Tensor, w_scale: Tenso
                          isBpreshuffled: bool = False) -> Tensor:
     """Y[M,N] = (XQ * x_scale) @ (WQ * w_scale)^T with fp32 scales per 128-wide K block: x_scale [M, K/128],
     w_scale [ceil(N/128), K/128]; WQ row-major [N, K] (reference: gemm_op_a8w8.py:797-865)."""
-    assert dtype in (dtypes.bf16,), f"Output {dtype=} is currently not supported in gemm_a8w8"
+    assert dtype in (dtypes.bf16, dtypes.fp16), f"Output {dtype=} is currently not supported in gemm_a8w8"
     if isBpreshuffled:
         return gemm_a8w8_blockscale_bpreshuffle(XQ, WQ, x_scale, w_scale, dtype)
     m, n, k = XQ.shape[0], WQ.shape[0], XQ.shape[1]
@@ -62,7 +62,7 @@ def gemm_a8w8_blockscale_bpreshuffle(XQ: Tensor, WQ: Tensor, x_scale: Tensor, w_
     """Same math with WQ (16,16)-shuffled and x_scale stored K-block-major ([K/128][M] in memory, passed either
     as the transposed-strided [M, K/128] view or re-viewed as a contiguous [M, K/128]); e8m0 scales are widened
     to fp32 first (reference: gemm_op_a8w8.py:895-1055)."""
-    assert dtype in (dtypes.bf16,), f"Output {dtype=} is currently not supported in gemm_a8w8"
+    assert dtype in (dtypes.bf16, dtypes.fp16), f"Output {dtype=} is currently not supported in gemm_a8w8"
     m, n, k = XQ.shape[0], WQ.shape[0], XQ.shape[1]
     Y = torch.empty(m, n, dtype=dtype, device=XQ.device)
     cfg = get_CKGEMM_config(m, n, k, bpreshuffle=True)

@@ -92,3 +92,15 @@ def shuffle_mxfp8fp4_scale(src: Tensor) -> Tensor:
     if pad:
         s = F.pad(s, (0, 0, 0, pad), value=0x7F)
     return _retile(s, 32, 4).view(src.dtype)
+
+
+def shuffle_weight_f4(src: Tensor) -> Tensor:
+    """Packed-fp4 operand [rows, K/2] -> 16x16-byte tile transpose (shuffle.py:319-336); the layout the F4GEMM entry
+    point takes for B, and for A when a_preshuffle is set."""
+    return _retile(_as_bytes(src).view(torch.uint8), 16, 16).view(src.dtype)
+
+
+def shuffle_scale_f4(src: Tensor, intype: int = 7) -> Tensor:
+    """F4GEMM scale pre-shuffle (shuffle.py:293-316): [M, K/block] -> tiles of 32 rows x 4 (MXFP4, intype 7) or
+    32 rows x 8 (NVFP4, intype 8) scale columns, rows outer inside a tile.  No row padding: M % 32 == 0."""
+    return _retile(src.view(torch.uint8), 32, 8 if intype == 8 else 4).view(src.dtype)

@@ -75,7 +75,8 @@ def gemm_a16w16(A: Tensor, B: Tensor, bias: Tensor | None = None, otype: torch.d
     libtype = config["libtype"]
     if libtype not in solMap:
         raise RuntimeError(f"bf16 table row for ({m},{n},{k}) names back-end '{libtype}', which does not exist in this build")
-    kernel_otype = dtypes.bf16 if libtype != "torch" else otype
+    # the kernels write bf16 or fp32 themselves (fp32 straight from the accumulator); other output types are a cast of bf16
+    kernel_otype = otype if otype in (dtypes.bf16, torch.float32) else dtypes.bf16
     out = solMap[libtype](inp_view, B, config.get("solidx"), bias, kernel_otype, None, None, None, bpreshuffle, config=config)
     if batched:
         out = out.view(*A.shape[:-1], n)

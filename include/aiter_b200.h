@@ -94,7 +94,7 @@ AITER_B200_API int mxfp8_mxfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, ai
 /* ---- FP8 x FP8 with fp32 scales per 128-wide K block -> bf16.  csrc/include/rocm_ops.hpp:725-765,
  * csrc/ck_gemm_a8w8_blockscale/gemm_a8w8_blockscale.cu:82-112, csrc/py_itfs_cu/asm_a8w8_blockscale_bpreshuffle.cu:59-73.
  * XQ [M,K] e4m3, WQ [N,K] e4m3 (plain, or (16,16)-shuffled for the _bpreshuffle forms), x_scale [M,K/128] fp32
- * (stored K-block-major for the _bpreshuffle forms), w_scale [ceil(N/128),K/128] fp32, Out [M,N] bf16, K % 128 == 0.
+ * (stored K-block-major for the _bpreshuffle forms), w_scale [ceil(N/128),K/128] fp32, Out [M,N] bf16, fp16 or fp32, K % 128 == 0.
  * One kernel instance serves the path: kernelName / splitK are accepted and ignored, kernelId must be 0. */
 AITER_B200_API int gemm_a8w8_blockscale(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
                                         aiter_tensor_t* w_scale, aiter_tensor_t* Out, int splitK,
@@ -130,16 +130,27 @@ AITER_B200_API int gemm_a8w8_blockscale_bpreshuffle_asm(aiter_tensor_t* A, aiter
                                                         int bpreshuffle, aiter_tensor_t* zero_bias_buf, void* stream);
 
 
-/* ---- MXFP4 x MXFP4 with the (m/32,k/4,32,4) scale layout.  csrc/py_itfs_cu/asm_f4gemm.cu:396-412
- * (bf16 output only: out_scale must be NULL). */
+/* ---- MXFP4 x MXFP4 with the (m/32,k/4,32,4) scale layout (the F4GEMM entry point).  csrc/py_itfs_cu/asm_f4gemm.cu:396-412,
+ * Python side aiter/ops/gemm_op_a4w4.py:288-407,457-567 (gemm_mxfp4_asm, gemm_a4w4o4, gemm_a4w4o8).
+ * A [M,K/2] and B [N,K/2] packed e2m1; B, and A when a_preshuffle != 0, as 16x16-byte tiles.  The output tensor selects the form:
+ *   bf16 [M,N], out_scale NULL;
+ *   fp4x2 / uint8 [M,N/2], out_scale NULL: packed e2m1 of the product WITHOUT the block scales (the reference's
+ *     fp4-output kernel is its "noscale" variant), round to nearest even, saturating;
+ *   fp8 [M,N] + out_scale [M,N/128] e8m0: e4m3 data with one RoundUp(amax/448) scale per 128 output columns, the scale
+ *     bytes in the packed (M/64, N/128, 16, 4) order; needs M % 64 == 0.
+ * The low-precision forms need N % 128 == 0.  NVFP4 inputs (nvfp4_gemm_asm) are not built. */
 AITER_B200_API int mxfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* ScaleA,
                                   aiter_tensor_t* ScaleB, aiter_tensor_t* out, aiter_tensor_t* out_scale,
                                   const char* kernelName, int a_preshuffle, void* stream);
 
-/* ---- bf16 x bf16 -> bf16/fp32-accumulated.  aiter/ops/gemm_op_a16w16.py:12-26 (asm form),
+/* ---- bf16 x bf16, fp32 accumulate.  aiter/ops/gemm_op_a16w16.py:12-26 (asm form),
  * csrc/opus_gemm/include/opus_gemm.h:16-39 and csrc/opus_gemm/opus_gemm.cu:133-209,294-350 (opus forms).
- * A [M,K], B [N,K] ((16,16)-shuffled when bpreshuffle != 0), out [M,N] bf16, bias bf16/fp32 [N] or NULL.
- * The opus forms take [batch,M,K] x [batch,N,K] -> [batch,M,N]. splitK: log2 of the K split, <0 = auto. */
+ * A [M,K], B [N,K] ((16,16)-shuffled when bpreshuffle != 0), out [M,N] bf16 or fp32 (fp32 is stored straight from the
+ * accumulator), bias bf16/fp32 [N] or NULL.
+ * The opus forms take [batch,M,K] x [batch,N,K] -> [batch,M,N] as ONE launch (the batch is a tile coordinate), bias [N] or
+ * [batch,N]; splitK: log2 of the K split, <0 = auto.  opus_gemm with fp8 operands, x_scale [batch,M,K/128] and w_scale
+ * [batch,N/128,K/128] (fp32) is the reference's a8w8_scale pipeline: fp32 output, no bias, served by the
+ * fp32-blockscale kernels (one launch per batch entry). */
 AITER_B200_API int gemm_a16w16_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* out,
                                    aiter_tensor_t* semaphore, aiter_tensor_t* bias, int splitK,
                                    const char* kernelName, int bpreshuffle, void* stream);

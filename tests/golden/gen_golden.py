@@ -230,6 +230,11 @@ def main(ref_root: str, out_path: str):
     s3 = (torch.arange(40 * 8) % 253).to(torch.uint8).view(40, 8)
     g["g1250_s_in"], g["g1250_s_out"] = s3.numpy(), shuffle.shuffle_mxfp8fp4_scale(s3).numpy()
 
+    g["f4_w_out"] = shuffle.shuffle_weight_f4(w8).numpy()
+    s4 = (torch.arange(64 * 16) % 253).to(torch.uint8).view(64, 16)
+    g["f4_s_in"] = s4.numpy()
+    g["f4_s_out_mx"], g["f4_s_out_nv"] = shuffle.shuffle_scale_f4(s4, 7).numpy(), shuffle.shuffle_scale_f4(s4, 8).numpy()
+
     # ---- GEMM references on small seeded problems
     torch.manual_seed(0)
     a = (torch.randn(64, 1024) * 0.1).to(torch.bfloat16)

@@ -196,10 +196,13 @@ def test_mxfp4_alpha_bias(ab):
 def test_mxfp4_g1250_scale_layout(ab):
     M, N, K = 64, 512, 1024
     ref, xq, wq, xs, ws = mxfp4_case(ab, M, N, K, seed=11)
-    out = ab.gemm_mxfp4_asm(
-        ab.shuffle_mxfp8fp4_a(to_cuda_u8(xq)), ab.shuffle_mxfp8fp4_b(to_cuda_u8(wq)),
-        ab.shuffle_mxfp8fp4_scale(to_cuda_u8(xs)), ab.shuffle_mxfp8fp4_scale(to_cuda_u8(ws)), a_preshuffle=True)
-    check(ref, out, what="mxfp4_gemm_asm")
+    # the F4GEMM entry point takes both operands as 16x16-byte tiles (op_tests/test_f4gemm.py:155-158)
+    for apre in (True, False):
+        A = to_cuda_u8(xq)
+        out = ab.gemm_mxfp4_asm(
+            ab.shuffle_weight_f4(A) if apre else A, ab.shuffle_weight_f4(to_cuda_u8(wq)),
+            ab.shuffle_scale_f4(to_cuda_u8(xs)), ab.shuffle_scale_f4(to_cuda_u8(ws)), a_preshuffle=apre)
+        check(ref, out, what=f"mxfp4_gemm_asm a_preshuffle={apre}")
     assert_healthy(ab)
 
 

@@ -112,6 +112,17 @@ def _write_csv(path, rows, header="gfx,cu_num,M,N,K,kernelId,splitK,us,kernelNam
     path.write_text(header + "\n" + "\n".join(rows) + "\n")
 
 
+def test_f4gemm_shuffles_against_golden(ab, golden):
+    w8 = torch.from_numpy(golden["shufw_u8_in"].copy())
+    assert np.array_equal(ab.shuffle_weight_f4(w8).numpy(), golden["f4_w_out"])
+    s4 = torch.from_numpy(golden["f4_s_in"].copy())
+    assert np.array_equal(ab.shuffle_scale_f4(s4, 7).numpy(), golden["f4_s_out_mx"])
+    assert np.array_equal(ab.shuffle_scale_f4(s4, 8).numpy(), golden["f4_s_out_nv"])
+    # and the packed order of the mxfp8 output scale is the inverse of the reference's unpacking
+    packed = torch.from_numpy(golden["requant_fp8_scale_packed"].copy())
+    assert np.array_equal(ab.unpack_mxfp8_out_scale(packed, 128, 256).view(torch.uint8).numpy(), golden["requant_fp8_scale"])
+
+
 def test_table_lookup_rules(ab, tmp_path, monkeypatch):
     """The (gfx, cu_num, M, N, K) key: other targets' rows are ignored, padded-M buckets are tried after the
     exact M, merged files keep the fastest row, a legacy file without `gfx` falls back to a cu_num-only key,
