@@ -295,11 +295,19 @@ static void run_blockscale(const char* fn, aiter_tensor_t* XQ, aiter_tensor_t* W
     }
     p.w_scale = static_cast<const float*>(w_scale->ptr);
     p.scales_are_e8m0 = sx8 && sw8;
-    // with e8m0 scales the problem runs on the MXFP8 kernel family, whose configuration names apply
-    if(p.scales_are_e8m0 && kernelName != nullptr && kernelName[0] != 0)
+    // a kernel name from a tuned table: "bs_..." picks one of the fp32-scale kernels and its K split; with e8m0 scales
+    // the problem may also run on the MXFP8 kernel family, whose configuration names then apply
+    if(kernelName != nullptr && kernelName[0] != 0)
     {
-        B200_CHECK(parse_config_name(kernelName, p.cfg), fn, ": not find kernel ", kernelName);
-        p.cfg_given = true;
+        if(parse_blockscale_name(kernelName, p.variant, p.log2_splitk))
+            ;
+        else if(p.scales_are_e8m0)
+        {
+            B200_CHECK(parse_config_name(kernelName, p.cfg), fn, ": not find kernel ", kernelName);
+            p.cfg_given = true;
+        }
+        else
+            fail(fn, ": not find kernel ", kernelName);
     }
     p.out      = Out->ptr;
     p.ldo      = Out->strides[0];

@@ -1313,11 +1313,32 @@ static bool use_few_rows(const BlockScaleProblem& prob)
     return prob.M <= 64 && prob.K <= 32768 && !few_rows_disabled();
 }
 
+bool parse_blockscale_name(const char* name, int& variant, int& log2_splitk)
+{
+    if(name == nullptr || name[0] == 0)
+        return false;
+    static const struct { const char* base; int variant; } kNames[] = {{"bs_fewrows", 1}, {"bs_128x128", 2}, {"bs_256x256", 3}};
+    for(const auto& n : kNames)
+    {
+        const size_t len = std::strlen(n.base);
+        if(std::strncmp(name, n.base, len) != 0)
+            continue;
+        int l2 = -1, more = 0;
+        if(name[len] != 0 && (std::sscanf(name + len, "_k%d%n", &l2, &more) != 1 || name[len + more] != 0 || l2 < 0 || l2 > 4))
+            return false;
+        variant     = n.variant;
+        log2_splitk = l2;
+        return true;
+    }
+    return false;
+}
+
 void launch_blockscale(const BlockScaleProblem& prob)
 {
     if(prob.M == 0 && prob.N > 0 && prob.K > 0)
         return;
-    if(prob.scales_are_e8m0 && (prob.cfg_given || !use_few_rows(prob)))
+    B200_CHECK(!(prob.scales_are_e8m0 && prob.variant > 1), "bs_128x128 / bs_256x256 take fp32 scales; e8m0 scales run on bs_fewrows or an MXFP8 kernel name");
+    if(prob.scales_are_e8m0 && prob.variant == 0 && (prob.cfg_given || !use_few_rows(prob)))
     {
         // powers of two ride the block-scaled MMA; up to 64 rows stay on the few-rows kernel below, which reads the
         // e8m0 bytes itself (one launch, no scale expansion pass)
@@ -1366,7 +1387,12 @@ void launch_blockscale(const BlockScaleProblem& prob)
     const long long pairs256 = ((prob.M + 2 * kTileP - 1) / (2 * kTileP)) * ((prob.N + 2 * kBsTileN - 1) / (2 * kBsTileN));
     const long long single_cost = (tiles128 + st.sm_count - 1) / st.sm_count * 720;
     const long long pair_cost   = (pairs256 + st.sm_count / 2 - 1) / (st.sm_count / 2) * 1300;
-    if(prob.M > kTileP && pair_cost < single_cost)
+    B200_CHECK(prob.variant != 1 || use_few_rows(prob), "bs_fewrows serves at most 64 activation rows");
+    B200_CHECK(prob.variant != 3 || prob.M > kTileP, "bs_256x256 needs more than 128 activation rows");
+    const bool want_pair = prob.variant == 3 || (prob.variant == 0 && prob.M > kTileP && pair_cost < single_cost);
+    const bool want_few  = prob.variant == 1 || (prob.variant == 0 && use_few_rows(prob));
+    const int forced_splits = prob.log2_splitk >= 0 ? (1 << prob.log2_splitk) : 0; // 0: the cost model below decides
+    if(want_pair)
     {
         // 256 x 256 tiles on CTA pairs
         const int stage_bytes = 2 * kTileP * kTileKBytes;
@@ -1396,7 +1422,7 @@ void launch_blockscale(const BlockScaleProblem& prob)
         lc.numAttrs = 1;
         B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_pair_kernel, ma, mb, prm));
     }
-    else if(use_few_rows(prob))
+    else if(want_few)
     {
         // few activation rows: weights on the M side of the MMA, activations on its N side
         const int xr          = prob.M <= 16 ? 16 : (prob.M <= 32 ? 32 : 64);
@@ -1413,6 +1439,8 @@ void launch_blockscale(const BlockScaleProblem& prob)
         while(!no_split && splits < (may_cluster ? 8 : 16) && static_cast<long long>(grid.x) * (splits * 2) <= st.sm_count &&
               prm.k_blocks / (splits * 2) >= 2)
             splits *= 2;
+        if(forced_splits > 0)
+            splits = std::max(1, std::min(std::min(forced_splits, may_cluster ? 8 : 16), prm.k_blocks));
         prm.cluster = (may_cluster && splits > 1) ? 1 : 0;
         if(prm.cluster)
             ; // nothing to reserve: the slices meet in the reducing CTA's shared memory
@@ -1504,6 +1532,8 @@ void launch_blockscale(const BlockScaleProblem& prob)
         static const bool no_split = (std::getenv("AITER_B200_NO_BLOCKSCALE_SPLIT") != nullptr);
         while(!no_split && splits < 8 && tiles * (splits * 2) <= st.sm_count && prm.k_blocks / (splits * 2) >= 4)
             splits *= 2;
+        if(forced_splits > 0)
+            splits = std::max(1, std::min(std::min(forced_splits, 8), prm.k_blocks));
         if(splits > 1 && tiles <= kCounterSlots)
         {
             cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;

@@ -130,10 +130,16 @@ struct BlockScaleProblem
     void* out = nullptr;
     long long ldo = 0;
     int out_mode = 0;             // OutMode: bf16, fp16 or fp32
+    // fp32-scale kernels: which one runs and its K split, for tuned tables (0 / -1: the launcher's own cost model).
+    // Names: "bs_fewrows" (<= 64 rows), "bs_128x128", "bs_256x256" (CTA pairs), each with an optional "_k<log2 split>".
+    int variant = 0;              // 1 few-rows, 2 128x128 single CTA, 3 256x256 CTA pair
+    int log2_splitk = -1;
     int device = 0;
     cudaStream_t stream = nullptr;
 };
 void launch_blockscale(const BlockScaleProblem& prob);
+// "bs_fewrows" | "bs_128x128" | "bs_256x256" [+ "_k<n>"] -> (variant, log2 split); false when the name is not one of these
+bool parse_blockscale_name(const char* name, int& variant, int& log2_splitk);
 void read_device_status(int device, unsigned int out_words[4]);
 // Bound of every in-kernel wait on `device` (1 ms .. 10 s, default 1 s) and the test hook that makes the persistent
 // kernel's scale producer issue nothing, so that a wait runs out.  Synchronises the device.

@@ -21,6 +21,8 @@ FILES = {
     "a8w8_mxfp8": "a8w8_mxfp8_tuned_gemm.csv",
     "a8w4_mxfp8": "a8w4_mxfp8_tuned_gemm.csv",
     "bf16": "bf16_tuned_gemm.csv",
+    "a8w8_blockscale": "a8w8_blockscale_tuned_gemm.csv",
+    "a8w8_blockscale_bpreshuffle": "a8w8_blockscale_bpreshuffle_tuned_gemm.csv",
 }
 
 
@@ -29,7 +31,7 @@ def _rows():
     for family, name in FILES.items():
         with open(os.path.join(CONFIG_DIR, name), newline="") as f:
             for r in csv.DictReader(f):
-                out.append((family, int(r["M"]), int(r["N"]), int(r["K"]), r["kernelName"], int(float(r["splitK"] or 0))))
+                out.append((family, int(r["M"]), int(r["N"]), int(r["K"]), r["kernelName"] or "", int(float(r["splitK"] or 0))))
     # rows that share a weight run back to back, so the weight is quantised and dequantised once
     return sorted(out, key=lambda t: (t[0], t[2], t[3], t[1]))
 
@@ -61,6 +63,14 @@ def _weight(ab, family, N, K):
         if family == "bf16":
             dev = (w,)
             deq = w.float().cpu().numpy()
+        elif family.startswith("a8w8_blockscale"):
+            # e4m3 weight with one fp32 scale per 128 x 128 block
+            wq = (w.float() * 2).to(torch.float8_e4m3fn)
+            g = torch.Generator(device="cuda").manual_seed(5)
+            ws = torch.rand((N + 127) // 128, K // 128, generator=g, device="cuda") + 0.25
+            dev = (ab.shuffle_weight(wq, layout=(16, 16)) if family.endswith("bpreshuffle") else wq, ws)
+            deq = (ox.e4m3fn_to_f32(wq.view(torch.uint8).cpu().numpy()) *
+                   np.repeat(np.repeat(ws.cpu().numpy(), 128, axis=0)[:N], 128, axis=1)).astype(np.float32)
         elif family == "a8w8_mxfp8":
             wq, ws = ab.per_1x32_f8_scale_f8_quant(w, scale_type=ab.dtypes.fp8_e8m0)
             ws = ws.view(torch.uint8)
@@ -87,13 +97,15 @@ def _table_row(ab, family, M, N, K):
         return gemm_op_a8w8.get_MXFP8_config(M, N, K)
     if family == "a8w4_mxfp8":
         return gemm_op_a8w4.get_A8W4_config(M, N, K)
+    if family.startswith("a8w8_blockscale"):
+        return gemm_op_a8w8.get_CKGEMM_config(M, N, K, bpreshuffle=family.endswith("bpreshuffle"))
     return gemm_op_a16w16._bf16_table.lookup(M, N, K, False, "torch.bfloat16", "torch.bfloat16", False, False)
 
 
 @pytest.mark.parametrize("family,M,N,K,kernel,split", ROWS, ids=[f"{r[0]}-{r[1]}x{r[2]}x{r[3]}-{r[4]}" for r in ROWS])
 def test_tuned_row(ab, family, M, N, K, kernel, split):
     row = _table_row(ab, family, M, N, K)
-    assert row is not None and row["kernelName"] == kernel, f"the table does not serve ({M},{N},{K}) with {kernel}: {row}"
+    assert row is not None and (row["kernelName"] or "") == kernel, f"the table does not serve ({M},{N},{K}) with {kernel}: {row}"
     dev_w, deq_w = _weight(ab, family, N, K)
     x = _randn(M, K, 1, 0.1 if family == "bf16" else 1.0)
     pick = np.sort(np.random.default_rng(M + N + K).choice(M, size=min(64, M), replace=False))
@@ -101,6 +113,15 @@ def test_tuned_row(ab, family, M, N, K, kernel, split):
     if family == "bf16":
         out = ab.tgemm.mm(x, dev_w[0])
         deq_x = x[pick].float().cpu().numpy()
+    elif family.startswith("a8w8_blockscale"):
+        xq = (x.float() * 2).to(torch.float8_e4m3fn)
+        g = torch.Generator(device="cuda").manual_seed(6)
+        xs = torch.rand(M, K // 128, generator=g, device="cuda") + 0.25
+        if family.endswith("bpreshuffle"):
+            out = ab.gemm_a8w8_blockscale_bpreshuffle(xq, dev_w[0], xs.T.contiguous().view(M, K // 128), dev_w[1])
+        else:
+            out = ab.gemm_a8w8_blockscale(xq, dev_w[0], xs, dev_w[1])
+        deq_x = (ox.e4m3fn_to_f32(xq.view(torch.uint8)[pick].cpu().numpy()) * np.repeat(xs[pick].cpu().numpy(), 128, axis=1)).astype(np.float32)
     elif family == "a4w4":
         xq, xs = ab.per_1x32_f4_quant(x)
         xs = xs.view(torch.uint8)

@@ -239,8 +239,45 @@ def test_tuner_candidates_use_the_library_name_grammar():
         for (M, N, K) in shapes:
             cands = tune.candidates(M, N, K, fam)
             assert cands, (fam, M, N, K)
+            if fam.startswith("a8w8_blockscale"):  # these candidates are kernel names of the fp32-scale kernels
+                assert all(c == "" or re.match(r"^bs_(fewrows|128x128|256x256)(_k\d)?$", c) for c in cands), cands
+                continue
             for (pair, swap, bn, st, sk) in cands:
                 assert bn in tune.BN_MENU and pair in (0, 1) and swap in (0, 1) and 0 <= st <= 8 and 0 <= sk <= 5
                 assert not (pair and swap), "CTA-pair tiles are not built for the transposed (decode) orientation"
                 assert grammar.match(tune.kernel_name(pair, swap, bn, st, sk)), tune.kernel_name(pair, swap, bn, st, sk)
                 assert tune.kernel_id(pair, swap, bn, st) == pair * 1000 + swap * 100 + tune.BN_MENU.index(bn) * 10 + st
+
+
+def test_tuner_worker_pool_survives_a_crash_and_a_hang(tmp_path, monkeypatch):
+    """--mp: one worker process per GPU; a worker that exits with an error or outlives the watchdog loses only its
+    unfinished shapes, which another worker gets once (reference: aiter/utility/mp_tuner.py:168-189).  Workers are
+    replaced by a stand-in that needs no GPU."""
+    import sys
+
+    from aiter_b200 import tune
+
+    marks = tmp_path / "marks"
+    marks.mkdir()
+    monkeypatch.setenv("AITER_B200_TUNE_WORKER_CMD", f"{sys.executable} {os.path.join(ROOT, 'tests', 'fake_tune_worker.py')}")
+    monkeypatch.setenv("FAKE_WORKER_MARKS", str(marks))
+    out = tmp_path / "tuned.csv"
+    shapes = "1,256,512;13,256,512;2,256,512;17,256,512;3,256,512;19,256,512;4,256,512"
+    rc = tune.main(["--family", "a4w4", "--shapes", shapes, "-o", str(out), "--mp", "3", "--timeout", "3"])
+    assert rc == 1  # one shape has no valid result
+    rows = tune.read_rows(str(out), "a4w4")
+    got = sorted(k[2] for k in rows)
+    assert got == [1, 2, 3, 4, 13, 17], got  # the crashed (13) and the hung (17) worker's shapes were retried; 19 failed twice
+    assert all(r["kernelName"].startswith("tc5_128x64_n_s0_gpu") for r in rows.values())
+
+
+def test_tuner_reads_shape_files_and_blockscale_names(tmp_path):
+    from aiter_b200 import tune
+
+    f = tmp_path / "untuned.csv"
+    f.write_text("M,N,K,bias,dtype,outdtype,scaleAB,bpreshuffle\n64,1024,1024,False,torch.bfloat16,torch.bfloat16,False,False\n"
+                 "64,1024,1024,False,torch.bfloat16,torch.bfloat16,False,False\n8,512,256,False,torch.bfloat16,torch.bfloat16,False,False\n")
+    assert tune.shapes_from_file(str(f)) == [(64, 1024, 1024), (8, 512, 256)]
+    names = tune.candidates(16, 4096, 4096, "a8w8_blockscale")
+    assert "" in names and "bs_fewrows_k2" in names and "bs_128x128_k0" in names and "bs_256x256" not in names
+    assert "bs_256x256" in tune.candidates(1024, 4096, 4096, "a8w8_blockscale_bpreshuffle")
