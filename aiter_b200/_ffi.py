@@ -60,6 +60,10 @@ def _load():
 
 
 _lib = _load()
+if int(os.getenv("AITER_LOG_MORE", "0")) >= 1:
+    import logging as _logging
+
+    _logging.getLogger("aiter").info("loaded %s", LIB_PATH)
 _lib.aiter_get_last_error.restype = ctypes.c_char_p
 _lib.aiter_b200_kernel_list.restype = ctypes.c_char_p
 _lib.aiter_b200_heuristic_name.restype = ctypes.c_char_p
@@ -120,10 +124,25 @@ _FUNCS = {}
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
+# AITER_LOG_MORE=2 logs every call that crosses the C ABI with its arguments (tensors as shape / dtype / device), as
+# the reference's ctypes caller does (aiter/jit/core.py:1466-1469); 1 logs the library path at load
+AITER_LOG_MORE = int(os.getenv("AITER_LOG_MORE", "0"))
+
+
+def _describe(a):
+    if isinstance(a, torch.Tensor):
+        return f"Tensor{tuple(a.shape)} {str(a.dtype).replace('torch.', '')} {a.device} stride{tuple(a.stride())}"
+    return repr(a)
+
+
 def call(name: str, *args):
     """Call an entry point on the current CUDA stream of the first tensor's device."""
     kinds = SIGNATURES[name]
     assert len(args) == len(kinds), f"{name} takes {len(kinds)} arguments, got {len(args)}"
+    if AITER_LOG_MORE == 2:
+        import logging
+
+        logging.getLogger("aiter").info("calling %s(%s)", name, ", ".join(_describe(a) for a in args))
     keep = []
     cargs = [_convert(k, a, keep) for k, a in zip(kinds, args)]
     dev = next((a.device for a in args if isinstance(a, torch.Tensor) and a.is_cuda), None)

@@ -39,7 +39,7 @@ METRIC = "GEMM TFLOPS (MXFP4 A4W4, M=16384 N=57344 K=7168, weight N-sharded over
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the 7168-column shard (M=16384, N=7168, K=7168), from
 # the ncu capture summarised under profiles/; a launch over more columns moves proportionally more (every
 # 7168-column block reads the activations again and writes its own output block)
-NCU_TRAFFIC_BYTES_PER_BLOCK = None
+NCU_TRAFFIC_BYTES_PER_BLOCK = 295.2e6  # 95.3 MB read + 199.9 MB written (algorithmic 325 MB: part of the output is still in L2 at the end)
 NOMINAL = {"bf16": 2250.0, "mxfp8": 4500.0, "mxfp4": 9000.0, "a8w4": 4500.0, "hbm_gbs": 8000.0}
 CPU_SAMPLE_ROWS, CPU_SAMPLE_COLS = 256, 7168
 
