@@ -37,7 +37,8 @@ struct DecodeParams
     int csplit;              // K slices = CTAs per cluster: 1, 2 or 4
     int tma_store;           // the output leaves as per-warp TMA tile stores (map_out is valid)
     int tmem_cols;           // allocation (power of two)
-    uint32_t stage_bytes, q_off, sfp_off, sfq_off, red_off, bar_off;
+    uint32_t stage_bytes, q_off, sfp_off, sfq_off, cook_off, red_off, bar_off;
+    int sf_via_cp;           // the scale warps only re-order the scales in shared memory; the MMA thread copies them to TMEM (tcgen05.cp)
     __nv_bfloat16* out;
     long long ldo;
     const void* bias;        // indexed by weight row, or null
@@ -220,6 +221,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
             const uint32_t p_lo0 = static_cast<uint32_t>(make_smem_desc(smem_base, p_lbo, p_sbo, p_lay));
             const uint32_t q_lo0 = static_cast<uint32_t>(make_smem_desc(smem_base + prm.q_off, q_lbo, q_sbo, q_lay));
             const uint32_t stage_step = prm.stage_bytes >> 4;
+            // re-ordered scales: 32 rows of 16 bytes, 8-row groups 128 bytes apart, no swizzle
+            const uint32_t cook_hi  = static_cast<uint32_t>(make_smem_desc(0, 16u, 128u, 0u) >> 32);
+            const uint32_t cook_lo0 = static_cast<uint32_t>(make_smem_desc(smem_base + prm.cook_off, 16u, 128u, 0u));
             uint32_t idk[4];
 #pragma unroll
             for(int k = 0; k < 4; ++k)
@@ -241,6 +245,19 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                 const uint32_t q_lo = q_lo0 + s * stage_step;
                 const uint32_t tsfp = sf0 + s * kSfCols;
                 const uint32_t tsfq = tsfp + 4 * kAtomsK;
+                if(kScaled && prm.sf_via_cp)
+                {
+                    // the stage's re-ordered scales: per K atom 32 rows x 16 bytes for the weights and as much for the
+                    // activations, copied to TMEM and replicated over the four lane quarters by the tensor core's own copy
+                    // unit; issued by this thread right before the MMAs that read them, which the pipe keeps in order
+                    const uint32_t c_lo = cook_lo0 + s * stage_step;
+#pragma unroll
+                    for(int a = 0; a < kAtomsK; ++a)
+                    {
+                        tc_cp_32x128b_warpx4(tsfp + a * 4, pack_u64(c_lo + a * 32u, cook_hi));
+                        tc_cp_32x128b_warpx4(tsfq + a * 4, pack_u64(c_lo + (kAtomsK + a) * 32u, cook_hi));
+                    }
+                }
 #pragma unroll
                 for(int k = 0; k < 4; ++k)
                 {
@@ -288,6 +305,61 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                     break;
                 B200_TRACE(if(warp == 2 && lane == 0 && i < 8) stamp(12 + i);)
                 const uint8_t* stage = smem_gen + s * prm.stage_bytes;
+                if(prm.sf_via_cp)
+                {
+                    // This warp re-orders only its share of the groups (warp w: group w of the weights and, if there is
+                    // one, group w of the activations) and leaves the result where the MMA thread's tcgen05.cp finds it:
+                    // cooked[K atom a][row 0..31][group g] words for the weights, then the same for the activations.
+                    uint32_t* cooked = reinterpret_cast<uint32_t*>(smem_gen + s * prm.stage_bytes + prm.cook_off);
+                    const int wq     = warp - 2;
+#pragma unroll
+                    for(int side = 0; side < 2; ++side)
+                    {
+                        if(side == 1 && wq >= q_groups)
+                            break;
+                        uint32_t* dst = cooked + (side ? kAtomsK * 128 : 0) + lane * 4 + wq;
+                        if(kE8)
+                        {
+                            const uint32_t* grp = reinterpret_cast<const uint32_t*>(stage + (side ? prm.sfq_off : prm.sfp_off) + wq * 256);
+                            const uint32_t w0 = grp[r16], w1 = grp[16 + r16], w2 = grp[32 + r16], w3 = grp[48 + r16];
+                            const uint32_t sel     = hi ? 0x7351u : 0x6240u;
+                            const uint32_t lo_part = __byte_perm(w0, w1, sel);
+                            const uint32_t hi_part = __byte_perm(w2, w3, sel);
+                            uint32_t v0 = __byte_perm(lo_part, hi_part, 0x5410);
+                            uint32_t v1 = __byte_perm(lo_part, hi_part, 0x7632);
+                            if(kt * 8 + 8 > prm.kblocks)
+                            {
+                                const int valid0  = min(max(prm.kblocks - kt * 8, 0), 4);
+                                const int valid1  = min(max(prm.kblocks - kt * 8 - 4, 0), 4);
+                                const uint32_t m0 = valid0 >= 4 ? 0xFFFFFFFFu : ((1u << (8 * valid0)) - 1u);
+                                const uint32_t m1 = valid1 >= 4 ? 0xFFFFFFFFu : ((1u << (8 * valid1)) - 1u);
+                                v0 = (v0 & m0) | (0x7F7F7F7Fu & ~m0);
+                                v1 = (v1 & m1) | (0x7F7F7F7Fu & ~m1);
+                            }
+                            dst[0] = v0;
+                            if(kAtomsK == 2)
+                                dst[128] = v1;
+                        }
+                        else
+                        {
+                            const uint32_t* grp = reinterpret_cast<const uint32_t*>(stage + (side ? prm.sfq_off : prm.sfp_off) + wq * kSfChunk);
+#pragma unroll
+                            for(int a = 0; a < kAtomsK; ++a)
+                                dst[a * 128] = grp[a * 32 + lane];
+                        }
+                    }
+                    fence_proxy_async_smem(); // read by the tensor core's copy unit
+                    __syncwarp();
+                    if(lane == 0)
+                        mbar_arrive(full_bar(s));
+                    B200_TRACE(if(warp == 2 && lane == 0 && i < 8) stamp(20 + i);)
+                    if(++s == S)
+                    {
+                        s = 0;
+                        phase ^= 1u;
+                    }
+                    continue;
+                }
                 uint32_t t[kSfCols > 0 ? kSfCols : 1];
 #pragma unroll
                 for(int c = 0; c < kSfCols; ++c)

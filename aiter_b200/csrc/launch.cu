@@ -602,16 +602,17 @@ static bool decode_kernel_disabled()
 
 struct DecodeLayout
 {
-    uint32_t stage_bytes, q_off, sfp_off, sfq_off, red_off, bar_off, total;
+    uint32_t stage_bytes, q_off, sfp_off, sfq_off, cook_off, red_off, bar_off, total;
 };
 
-static DecodeLayout make_decode_layout(int bn, int stages, int csplit, bool scaled)
+static DecodeLayout make_decode_layout(int bn, int stages, int csplit, bool scaled, bool cook)
 {
     DecodeLayout L;
     L.q_off       = kTileP * kTileKBytes;
     L.sfp_off     = L.q_off + static_cast<uint32_t>(bn) * kTileKBytes;
     L.sfq_off     = L.sfp_off + (scaled ? 1024u : 0u);
-    L.stage_bytes = L.sfq_off + (scaled ? 1024u : 0u);
+    L.cook_off    = L.sfq_off + (scaled ? 1024u : 0u); // re-ordered scales: 2 sides x up to 2 K atoms x 512 bytes
+    L.stage_bytes = L.cook_off + (cook ? 2048u : 0u);
     L.red_off     = L.stage_bytes * static_cast<uint32_t>(stages);
     L.bar_off     = L.red_off + (csplit > 1 ? static_cast<uint32_t>(csplit - 1) * static_cast<uint32_t>(kTileP / csplit) * static_cast<uint32_t>(bn) * 4u : 0u);
     L.total       = L.bar_off + 256u;
@@ -665,11 +666,15 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
         return false; // wider K splits stay with the persistent kernel (workspace or 8-CTA cluster)
     const bool scaled = (kkind != KIND_BF16);
     const int bn      = cfg.bn;
+    // e8m0_shuffle scales: the four scale warps share the byte transpose and the MMA thread copies the result to TMEM
+    // (tcgen05.cp); the (m/32,k/4,32,4) order needs no transpose, there the warps write TMEM themselves
+    static const bool no_cp = (std::getenv("AITER_B200_DECODE_NO_CP") != nullptr);
+    const bool cook = scaled && !no_cp && prob.wgt_sf.wire == SFW_E8M0_SHUFFLE;
     // as many stages as keep two CTAs on an SM (110 KB each), unless the configuration names a count
     int stages = 0;
     const int smem_cap = named_stages > 0 ? st.smem_optin : 110 * 1024;
     for(int s2 = std::min(named_stages > 0 ? named_stages : kDecodeMaxStages, kDecodeMaxStages); s2 >= 2; --s2)
-        if(static_cast<int>(make_decode_layout(bn, s2, csplit, scaled).total) + 1024 <= smem_cap)
+        if(static_cast<int>(make_decode_layout(bn, s2, csplit, scaled, cook).total) + 1024 <= smem_cap)
         {
             stages = s2;
             break;
@@ -677,7 +682,7 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
     if(stages == 0)
         return false;
     stages                  = std::min(stages, std::max(2, (num_k_iters + csplit - 1) / csplit));
-    const DecodeLayout L    = make_decode_layout(bn, stages, csplit, scaled);
+    const DecodeLayout L    = make_decode_layout(bn, stages, csplit, scaled, cook);
     const Operand& P        = prob.wgt;
     const Operand& Q        = prob.act;
     B200_CHECK(P.kbytes == Q.kbytes, "operands disagree on K bytes: ", P.kbytes, " vs ", Q.kbytes);
@@ -718,6 +723,8 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
     prm.q_off       = L.q_off;
     prm.sfp_off     = L.sfp_off;
     prm.sfq_off     = L.sfq_off;
+    prm.cook_off    = L.cook_off;
+    prm.sf_via_cp   = cook ? 1 : 0;
     prm.red_off     = L.red_off;
     prm.bar_off     = L.bar_off;
     prm.out         = static_cast<__nv_bfloat16*>(prob.out);
