@@ -37,7 +37,7 @@ struct DecodeParams
     int csplit;              // K slices = CTAs per cluster: 1, 2 or 4
     int tma_store;           // the output leaves as per-warp TMA tile stores (map_out is valid)
     int tmem_cols;           // allocation (power of two)
-    uint32_t stage_bytes, q_off, sfp_off, sfq_off, cook_off, red_off, bar_off;
+    uint32_t stage_bytes, q_off, sfp_off, sfq_off, cook_off, stg_off, red_off, bar_off;
     int sf_via_cp;           // the scale warps only re-order the scales in shared memory; the MMA thread copies them to TMEM (tcgen05.cp)
     __nv_bfloat16* out;
     long long ldo;
@@ -50,6 +50,8 @@ struct DecodeParams
 
 // TMEM columns of one stage's scales: [P atom a: 4 columns][Q atom a: 4 columns], a < atoms per K tile
 __host__ __device__ constexpr int decode_sf_cols(int kind) { return kind == KIND_BF16 ? 0 : (kind == KIND_MXF4 ? 16 : 8); }
+// (the mixed kind, e4m3 activations x packed e2m1 weights, is MXF8 once the scale warps have widened the weight tile to
+// e4m3 in shared memory: exact, every e2m1 value is an e4m3 value)
 
 template <int KIND, int SFW>
 __global__ void __launch_bounds__(kDecodeThreads, 2)
@@ -58,6 +60,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                    const __grid_constant__ CUtensorMap map_out, const DecodeParams prm)
 {
     constexpr bool kScaled = (KIND != KIND_BF16);
+    constexpr bool kMixed  = (KIND == KIND_MXF8F4);
     constexpr int kAtomsK  = (KIND == KIND_MXF4) ? 2 : 1; // 4-k-block scale atoms per 128-byte K tile
     constexpr int kSfCols  = decode_sf_cols(KIND);
     constexpr bool kE8     = (SFW == SFW_E8M0_SHUFFLE);
@@ -96,7 +99,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
         {
             mbar_init(full_bar(s), kScaled ? 5 : 1); // the operand producer's expect_tx arrival + one arrival per scale warp
             mbar_init(empty_bar(s), 1);
-            mbar_init(sfraw_bar(s), 1);
+            mbar_init(sfraw_bar(s), kMixed ? 2 : 1); // raw scales (+ the packed e2m1 weight tile of the mixed kind: one wait covers both)
         }
         mbar_init(acc_bar, 1);
         mbar_init(red_bar, 1);
@@ -151,8 +154,19 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                     break;
                 const uint32_t stage = smem_base + s * prm.stage_bytes;
                 const uint32_t bar   = full_bar(s);
-                mbar_arrive_expect_tx(bar, kTileP * kTileKBytes + q_bytes);
-                issue_operand_load(prm.p_mode, stage, &map_p, bar, row_p0, kt);
+                if(kMixed)
+                {
+                    // the packed e2m1 weight tile (16x16-byte tiled: 4 chunks of 16 bytes = 32 codes per row) lands in the
+                    // staging area and is counted on the raw-scale barrier, which the widening warps wait on
+                    mbar_arrive_expect_tx(sfraw_bar(s), kTileP * 64u);
+                    tma_load_3d(stage + prm.stg_off, &map_p, sfraw_bar(s), 0, row_p0 >> 4, kt * 4);
+                    mbar_arrive_expect_tx(bar, q_bytes);
+                }
+                else
+                {
+                    mbar_arrive_expect_tx(bar, kTileP * kTileKBytes + q_bytes);
+                    issue_operand_load(prm.p_mode, stage, &map_p, bar, row_p0, kt);
+                }
                 issue_operand_load(prm.q_mode, stage + prm.q_off, &map_q, bar, 0, kt);
                 B200_TRACE(if(i == 0) stamp(3);)
                 if(++s == S)
@@ -205,7 +219,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
             uint32_t idesc;
             if(KIND == KIND_BF16)
                 idesc = idesc_bf16(kTileP, bn);
-            else if(KIND == KIND_MXF8)
+            else if(KIND == KIND_MXF8 || KIND == KIND_MXF8F4)
                 idesc = idesc_block_scaled(0, 0, kTileP, bn);
             else
                 idesc = idesc_block_scaled(1, 1, kTileP, bn);
@@ -266,7 +280,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                     const uint32_t acc = (k > 0) ? 1u : static_cast<uint32_t>(i > 0);
                     if(KIND == KIND_BF16)
                         mma_f16(tmem_base, pd, qd, idk[k], acc);
-                    else if(KIND == KIND_MXF8)
+                    else if(KIND == KIND_MXF8 || KIND == KIND_MXF8F4)
                         mma_mxf8f6f4(tmem_base, pd, qd, idk[k], acc, tsfp, tsfq);
                     else
                         mma_mxf4(tmem_base, pd, qd, idk[k], acc, tsfp + (k >> 1) * 4, tsfq + (k >> 1) * 4);
@@ -305,6 +319,30 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                     break;
                 B200_TRACE(if(warp == 2 && lane == 0 && i < 8) stamp(12 + i);)
                 const uint8_t* stage = smem_gen + s * prm.stage_bytes;
+                if(kMixed)
+                {
+                    // widen this thread's weight row: 4 chunks of 32 packed codes -> 8 chunks of 16 e4m3 bytes, in the
+                    // un-swizzled K-major layout the MMA reads ([chunk][row][16 B]); all loads first so their latencies overlap
+                    const int t_row  = (warp - 2) * 32 + lane;
+                    const uint4* src = reinterpret_cast<const uint4*>(stage + prm.stg_off);
+                    uint4* dst       = reinterpret_cast<uint4*>(smem_gen + s * prm.stage_bytes);
+                    uint4 v[4];
+#pragma unroll
+                    for(int c = 0; c < 4; ++c)
+                        v[c] = src[c * kTileP + t_row];
+#pragma unroll
+                    for(int c = 0; c < 4; ++c)
+                    {
+                        uint4 o0, o1;
+                        e2m1x8_to_e4m3x8(v[c].x, o0.x, o0.y);
+                        e2m1x8_to_e4m3x8(v[c].y, o0.z, o0.w);
+                        e2m1x8_to_e4m3x8(v[c].z, o1.x, o1.y);
+                        e2m1x8_to_e4m3x8(v[c].w, o1.z, o1.w);
+                        dst[(2 * c) * kTileP + t_row]     = o0;
+                        dst[(2 * c + 1) * kTileP + t_row] = o1;
+                    }
+                    fence_proxy_async_smem(); // read by the tensor core
+                }
                 if(prm.sf_via_cp)
                 {
                     // This warp re-orders only its share of the groups (warp w: group w of the weights and, if there is

@@ -349,7 +349,7 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
         int l2 = 0;
         // split while the grid under-fills the machine and every split keeps >= 4 K iterations.  Decode tiles (the small
         // kernel: two CTAs per SM, K split over a cluster of at most four) may fill the machine twice.
-        const bool decode  = cfg.swap && cfg.cg == 1 && cfg.bn <= 64 && kind != PK_MXF8F4;
+        const bool decode  = cfg.swap && cfg.cg == 1 && cfg.bn <= 64;
         const long long cap = decode ? 2LL * num_sms : num_sms;
         const int max_l2    = decode ? 2 : 5;
         while(l2 < max_l2 && tiles * (2LL << l2) <= cap && (k_iters >> (l2 + 1)) >= 4)
@@ -600,19 +600,26 @@ static bool decode_kernel_disabled()
     return off;
 }
 
+static bool decode_mixed_disabled()
+{
+    static const bool off = (std::getenv("AITER_B200_DECODE_NO_MIXED") != nullptr);
+    return off;
+}
+
 struct DecodeLayout
 {
-    uint32_t stage_bytes, q_off, sfp_off, sfq_off, cook_off, red_off, bar_off, total;
+    uint32_t stage_bytes, q_off, sfp_off, sfq_off, cook_off, stg_off, red_off, bar_off, total;
 };
 
-static DecodeLayout make_decode_layout(int bn, int stages, int csplit, bool scaled, bool cook)
+static DecodeLayout make_decode_layout(int bn, int stages, int csplit, bool scaled, bool cook, bool mixed)
 {
     DecodeLayout L;
     L.q_off       = kTileP * kTileKBytes;
     L.sfp_off     = L.q_off + static_cast<uint32_t>(bn) * kTileKBytes;
     L.sfq_off     = L.sfp_off + (scaled ? 1024u : 0u);
     L.cook_off    = L.sfq_off + (scaled ? 1024u : 0u); // re-ordered scales: 2 sides x up to 2 K atoms x 512 bytes
-    L.stage_bytes = L.cook_off + (cook ? 2048u : 0u);
+    L.stg_off     = L.cook_off + (cook ? 2048u : 0u);      // mixed kind: the packed e2m1 weight tile, 128 rows x 64 bytes
+    L.stage_bytes = L.stg_off + (mixed ? kTileP * 64u : 0u);
     L.red_off     = L.stage_bytes * static_cast<uint32_t>(stages);
     L.bar_off     = L.red_off + (csplit > 1 ? static_cast<uint32_t>(csplit - 1) * static_cast<uint32_t>(kTileP / csplit) * static_cast<uint32_t>(bn) * 4u : 0u);
     L.total       = L.bar_off + 256u;
@@ -655,8 +662,11 @@ static void launch_decode_instance(int ctas, int csplit, size_t smem, cudaStream
 static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, int kkind, DeviceState& st)
 {
     const int named_stages = prob.cfg.stages; // what the caller's configuration asked for (0: this kernel's own choice)
-    if(decode_kernel_disabled() || !cfg.swap || cfg.cg != 1 || cfg.bn > 64 || prob.M > cfg.bn || kkind == KIND_MXF8F4 || prob.scratch != nullptr ||
+    if(decode_kernel_disabled() || !cfg.swap || cfg.cg != 1 || cfg.bn > 64 || prob.M > cfg.bn || prob.scratch != nullptr ||
        prob.out_mode != OUT_BF16 || prob.batch > 1 || prob.noscale)
+        return false;
+    const bool mixed = (kkind == KIND_MXF8F4);
+    if(mixed && decode_mixed_disabled())
         return false;
     const int num_k_iters = static_cast<int>((prob.act.kbytes + kTileKBytes - 1) / kTileKBytes);
     int csplit            = 1 << cfg.log2_splitk;
@@ -674,7 +684,7 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
     int stages = 0;
     const int smem_cap = named_stages > 0 ? st.smem_optin : 110 * 1024;
     for(int s2 = std::min(named_stages > 0 ? named_stages : kDecodeMaxStages, kDecodeMaxStages); s2 >= 2; --s2)
-        if(static_cast<int>(make_decode_layout(bn, s2, csplit, scaled, cook).total) + 1024 <= smem_cap)
+        if(static_cast<int>(make_decode_layout(bn, s2, csplit, scaled, cook, mixed).total) + 1024 <= smem_cap)
         {
             stages = s2;
             break;
@@ -682,11 +692,15 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
     if(stages == 0)
         return false;
     stages                  = std::min(stages, std::max(2, (num_k_iters + csplit - 1) / csplit));
-    const DecodeLayout L    = make_decode_layout(bn, stages, csplit, scaled, cook);
+    const DecodeLayout L    = make_decode_layout(bn, stages, csplit, scaled, cook, mixed);
     const Operand& P        = prob.wgt;
     const Operand& Q        = prob.act;
-    B200_CHECK(P.kbytes == Q.kbytes, "operands disagree on K bytes: ", P.kbytes, " vs ", Q.kbytes);
-    CUtensorMap mp  = operand_map(P, kTileP, "weight operand");
+    if(mixed)
+        B200_CHECK(Q.kbytes == 2 * P.kbytes && P.mode == OPM_TILE16,
+                   "mixed MXFP8 x MXFP4: the weight must be packed e2m1 in the 16x16-byte tiled layout");
+    else
+        B200_CHECK(P.kbytes == Q.kbytes, "operands disagree on K bytes: ", P.kbytes, " vs ", Q.kbytes);
+    CUtensorMap mp  = operand_map(P, kTileP, "weight operand", mixed ? 64 : kTileKBytes);
     CUtensorMap mq  = operand_map(Q, bn, "activation operand");
     CUtensorMap msp = mp, msq = mq;
     int sfw = SFW_NONE;
@@ -716,7 +730,7 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
     prm.kblocks     = kblocks;
     prm.bn          = bn;
     prm.stages      = stages;
-    prm.p_mode      = P.mode;
+    prm.p_mode      = P.mode; // (mixed kind: the widened tile has the same 16x16-byte tiled arrangement)
     prm.q_mode      = Q.mode;
     prm.csplit      = csplit;
     prm.stage_bytes = L.stage_bytes;
@@ -724,6 +738,7 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
     prm.sfp_off     = L.sfp_off;
     prm.sfq_off     = L.sfq_off;
     prm.cook_off    = L.cook_off;
+    prm.stg_off     = L.stg_off;
     prm.sf_via_cp   = cook ? 1 : 0;
     prm.red_off     = L.red_off;
     prm.bar_off     = L.bar_off;
@@ -775,6 +790,8 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
         launch_decode_instance<KIND_MXF4, SFW_E8M0_SHUFFLE>(ctas, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else if(kkind == KIND_MXF4 && sfw == SFW_G1250)
         launch_decode_instance<KIND_MXF4, SFW_G1250>(ctas, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
+    else if(kkind == KIND_MXF8F4 && sfw == SFW_G1250)
+        launch_decode_instance<KIND_MXF8F4, SFW_G1250>(ctas, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else
         fail("no decode kernel instance for kind ", kkind, " with scale layout ", sfw);
 #ifdef AITER_B200_TRACING
