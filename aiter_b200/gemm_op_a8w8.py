@@ -39,6 +39,16 @@ def _blockscale_scales(x_scale: Tensor, w_scale: Tensor):
             fp4_utils.e8m0_to_f32(w_scale) if _is_e8m0(w_scale) else w_scale)
 
 
+def _blockscale_choice(cfg, scales_are_e8m0: bool, m: int, n: int, k: int):
+    """-> (splitK, kernelName) for the library call.  The blockscale tables are tuned with fp32 scales: their
+    bs_128x128 / bs_256x256 rows do not apply to e8m0-scaled problems, which run on the few-rows kernel (a
+    bs_fewrows row stays valid: that kernel reads either scale type) or on the MXFP8 kernel its own table names."""
+    splitK, kernelName = (int(cfg.get("splitK") or 0), str(cfg.get("kernelName") or "")) if cfg is not None else (0, "")
+    if scales_are_e8m0 and not kernelName.startswith("bs_fewrows"):
+        splitK, kernelName = 0, _mxfp8_kernel_for(m, n, k)
+    return splitK, kernelName
+
+
 def gemm_a8w8_blockscale(XQ: Tensor, WQ: Tensor, x_scale: Tensor, w_scale: Tensor, dtype: torch.dtype = dtypes.bf16,
                          isBpreshuffled: bool = False) -> Tensor:
     """Y[M,N] = (XQ * x_scale) @ (WQ * w_scale)^T with fp32 scales per 128-wide K block: x_scale [M, K/128],
@@ -48,11 +58,8 @@ def gemm_a8w8_blockscale(XQ: Tensor, WQ: Tensor, x_scale: Tensor, w_scale: Tenso
         return gemm_a8w8_blockscale_bpreshuffle(XQ, WQ, x_scale, w_scale, dtype)
     m, n, k = XQ.shape[0], WQ.shape[0], XQ.shape[1]
     Y = torch.empty(m, n, dtype=dtype, device=XQ.device)
-    cfg = get_CKGEMM_config(m, n, k)
-    splitK, kernelName = (int(cfg.get("splitK") or 0), str(cfg.get("kernelName") or "")) if cfg is not None else (0, "")
     xs, ws = _blockscale_scales(x_scale, w_scale)
-    if _is_e8m0(xs) and not kernelName:
-        kernelName = _mxfp8_kernel_for(m, n, k)
+    splitK, kernelName = _blockscale_choice(get_CKGEMM_config(m, n, k), _is_e8m0(xs), m, n, k)
     _ffi.call("gemm_a8w8_blockscale", XQ, WQ, xs, ws, Y, splitK, kernelName or None)
     return Y
 
@@ -65,11 +72,8 @@ def gemm_a8w8_blockscale_bpreshuffle(XQ: Tensor, WQ: Tensor, x_scale: Tensor, w_
     assert dtype in (dtypes.bf16, dtypes.fp16), f"Output {dtype=} is currently not supported in gemm_a8w8"
     m, n, k = XQ.shape[0], WQ.shape[0], XQ.shape[1]
     Y = torch.empty(m, n, dtype=dtype, device=XQ.device)
-    cfg = get_CKGEMM_config(m, n, k, bpreshuffle=True)
-    splitK, kernelName = (int(cfg.get("splitK") or 0), str(cfg.get("kernelName") or "")) if cfg is not None else (0, "")
     xs, ws = _blockscale_scales(x_scale, w_scale)
-    if _is_e8m0(xs) and not kernelName:
-        kernelName = _mxfp8_kernel_for(m, n, k)
+    splitK, kernelName = _blockscale_choice(get_CKGEMM_config(m, n, k, bpreshuffle=True), _is_e8m0(xs), m, n, k)
     _ffi.call("gemm_a8w8_blockscale_bpreshuffle", XQ, WQ, xs, ws, Y, splitK, kernelName or None)
     return Y
 

@@ -379,7 +379,9 @@ def test_a8w8_blockscale_other_backend_names(ab):
 
 
 @pytest.mark.parametrize("M,N,K,bpre", [(64, 256, 512, False), (300, 1024, 2048, True), (1, 128, 128, False),
-                                       (16, 4096, 4096, False), (32, 1536, 7168, True), (7, 400, 1024, True)])
+                                       (16, 4096, 4096, False), (32, 1536, 7168, True), (7, 400, 1024, True),
+                                       # shapes whose tuned-table row names an fp32-scale kernel (bs_128x128, bs_256x256)
+                                       (128, 4096, 4096, False), (1024, 4096, 4096, True)])
 def test_a8w8_blockscale_e8m0_scales_run_as_mxfp8(ab, M, N, K, bpre):
     # power-of-two scales ride the block-scaled MMA: two small expansion launches + the MXFP8 kernel; up to 64 rows
     # the few-rows blockscale kernel reads the e8m0 bytes itself

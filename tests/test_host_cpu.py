@@ -281,3 +281,17 @@ def test_tuner_reads_shape_files_and_blockscale_names(tmp_path):
     names = tune.candidates(16, 4096, 4096, "a8w8_blockscale")
     assert "" in names and "bs_fewrows_k2" in names and "bs_128x128_k0" in names and "bs_256x256" not in names
     assert "bs_256x256" in tune.candidates(1024, 4096, 4096, "a8w8_blockscale_bpreshuffle")
+
+
+def test_blockscale_table_rows_do_not_leak_onto_e8m0_scaled_calls(ab):
+    # the blockscale tables are tuned with fp32 scales; an e8m0-scaled call keeps only a few-rows row
+    from aiter_b200 import gemm_op_a8w8 as g
+
+    fp32_row = {"splitK": 1, "kernelName": "bs_128x128_k1"}
+    few_row = {"splitK": 2, "kernelName": "bs_fewrows_k2"}
+    assert g._blockscale_choice(fp32_row, False, 128, 4096, 4096) == (1, "bs_128x128_k1")
+    assert g._blockscale_choice(few_row, True, 16, 4096, 4096) == (2, "bs_fewrows_k2")
+    split, name = g._blockscale_choice(fp32_row, True, 128, 4096, 4096)
+    assert split == 0 and not name.startswith("bs_")
+    assert g._blockscale_choice({"splitK": 0, "kernelName": "bs_256x256"}, True, 16, 4096, 4096) == (0, "")
+    assert g._blockscale_choice(None, False, 5, 6, 7) == (0, "")
