@@ -26,6 +26,7 @@ from .gemm_op_a4w4 import (  # noqa: E402,F401
     gemm_a4w4o4,
     gemm_a4w4o8,
     gemm_mxfp4_asm,
+    gemm_nvfp4_asm,
     unpack_mxfp8_out_scale,
 )
 from .gemm_op_a8w4 import gemm_a8w4_mxfp8  # noqa: E402,F401

@@ -79,6 +79,7 @@ SIGNATURES = {
     "mxfp8_mxfp8_gemm_asm": (T, T, T, T, T, S, I),
     "mxfp8_mxfp4_gemm_asm": (T, T, T, T, T, S, I),
     "mxfp4_gemm_asm": (T, T, T, T, T, T, S, I),
+    "nvfp4_gemm_asm": (T, T, T, T, F, F, T, T, S, I),
     "gemm_a16w16_asm": (T, T, T, T, T, I, S, I),
     "opus_gemm_a16w16_tune": (T, T, T, T, I, I),
     "opus_gemm": (T, T, T, T, T, T, T),

@@ -139,28 +139,31 @@ extern "C" int gemm_a4w4_blockscale_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ,
     });
 }
 
-extern "C" int mxfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* ScaleA, aiter_tensor_t* ScaleB,
-                              aiter_tensor_t* out, aiter_tensor_t* out_scale, const char* kernelName, int a_preshuffle,
-                              void* stream)
+// The F4GEMM family (aiter/ops/gemm_op_a4w4.py:290-443): packed e2m1 operands in 16x16-byte tiles (A optionally row-major),
+// scales in tiles of 32 rows x 4 e8m0 bytes (MXFP4, one per 32 elements) or 32 rows x 8 e4m3 bytes (NVFP4, one per 16
+// elements, `nv`), and for NVFP4 the product of the two per-tensor scales folded into the result.
+static void run_f4gemm(const char* fn, bool nv, float global_scale, aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* ScaleA,
+                       aiter_tensor_t* ScaleB, aiter_tensor_t* out, aiter_tensor_t* out_scale, const char* kernelName,
+                       int a_preshuffle, void* stream)
 {
-    return safe_call([&] {
-        const char* fn = "mxfp4_gemm_asm";
-        B200_CHECK(a_preshuffle == 0 || a_preshuffle == 1, "mxfp4_gemm_asm a_preshuffle must be 0 or 1");
+    {
+        B200_CHECK(a_preshuffle == 0 || a_preshuffle == 1, fn, " a_preshuffle must be 0 or 1");
         GemmProblem tmp;
         apply_config(tmp, kernelName, -1, fn);
-        B200_CHECK(A != nullptr && A->ndim == 2 && (A->shape[1] * 2) % 256 == 0, "mxfp4_gemm_asm K must be divisible by 256");
+        B200_CHECK(A != nullptr && A->ndim == 2 && (A->shape[1] * 2) % 256 == 0, fn, " K must be divisible by 256");
         require_tensor(out, fn, "out", 2);
         const bool out_fp4 = (out->dtype_ == AITER_DTYPE_fp4x2 || out->dtype_ == AITER_DTYPE_u8);
         const bool out_fp8 = (out->dtype_ == AITER_DTYPE_fp8);
-        if(!out_fp4 && !out_fp8)
+        if(!out_fp4 && !out_fp8 && !nv)
         {
-            B200_CHECK(out_scale == nullptr, "mxfp4_gemm_asm: out_scale goes with the fp8 output only");
+            B200_CHECK(out_scale == nullptr, fn, ": out_scale goes with the fp8 output only");
             run_mxfp4(fn, A, B, ScaleA, ScaleB, out, nullptr, 1.f, 0.f, a_preshuffle ? OPM_TILE16 : OPM_ROWMAJOR, OPM_TILE16, SFW_G1250,
                       tmp.cfg, stream);
             return;
         }
         // Low-precision outputs (the reference's gemm_a4w4o4 / gemm_a4w4o8, aiter/ops/gemm_op_a4w4.py:457-567):
-        //   fp4x2 / uint8 [M, N/2]: packed e2m1 of the UNSCALED product (its fp4-output kernel ignores the block scales);
+        //   fp4x2 / uint8 [M, N/2]: packed e2m1 of the product WITHOUT the block scales (its fp4-output kernel ignores them;
+        //   the per-tensor scales of NVFP4 still apply);
         //   fp8 [M, N] + out_scale [M, N/128] e8m0 in the packed (M/64, N/128, 16, 4) byte order.
         require_tensor(A, fn, "A", 2);
         require_tensor(B, fn, "B", 2);
@@ -171,14 +174,21 @@ extern "C" int mxfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor
         require_dense(A, fn, "A");
         require_dense(B, fn, "B");
         GemmProblem p;
-        p.kind = PK_MXFP4;
+        p.kind = nv ? PK_NVFP4 : PK_MXFP4;
         p.M = M; p.N = N; p.K = Kb * 2;
         p.act    = Operand{A->ptr, M, Kb, Kb, a_preshuffle ? OPM_TILE16 : OPM_ROWMAJOR};
         p.wgt    = Operand{B->ptr, N, Kb, Kb, OPM_TILE16};
         p.act_sf = scale_operand(ScaleA, SFW_G1250, fn, "ScaleA");
         p.wgt_sf = scale_operand(ScaleB, SFW_G1250, fn, "ScaleB");
         require_dense(out, fn, "out");
-        if(out_fp4)
+        if(!out_fp4 && !out_fp8)
+        {
+            B200_CHECK(out_scale == nullptr, fn, ": out_scale goes with the fp8 output only");
+            B200_CHECK(out->dtype_ == AITER_DTYPE_bf16, fn, ": out must be bf16, packed fp4 or fp8 (got ", dtype_name(out->dtype_), ")");
+            B200_CHECK(out->shape[0] == M && out->shape[1] == N, fn, ": the bf16 output must be [M, N]");
+            p.out_mode = OUT_BF16;
+        }
+        else if(out_fp4)
         {
             B200_CHECK(out_scale == nullptr, fn, ": the packed fp4 output takes no out_scale");
             B200_CHECK(out->shape[0] == M && out->shape[1] == N / 2, fn, ": the packed fp4 output must be [M, N/2]");
@@ -199,13 +209,31 @@ extern "C" int mxfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor
         require_same_device(A, B, fn, "B");
         require_same_device(A, out, fn, "out");
         p.out    = out->ptr;
-        p.ldo    = out->strides[0]; // bytes: both outputs have one-byte elements
-        p.alpha  = 1.f;
+        p.ldo    = out->strides[0]; // elements of the output's own type (bf16, or one-byte fp8 / packed fp4)
+        p.alpha  = global_scale;
         p.beta   = 0.f;
         p.device = A->device_id;
         p.stream = static_cast<cudaStream_t>(stream);
         p.cfg    = tmp.cfg;
         launch_gemm(p);
+    }
+}
+
+extern "C" int mxfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* ScaleA, aiter_tensor_t* ScaleB,
+                              aiter_tensor_t* out, aiter_tensor_t* out_scale, const char* kernelName, int a_preshuffle,
+                              void* stream)
+{
+    return safe_call([&] { run_f4gemm("mxfp4_gemm_asm", false, 1.f, A, B, ScaleA, ScaleB, out, out_scale, kernelName, a_preshuffle, stream); });
+}
+
+extern "C" int nvfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* ScaleA, aiter_tensor_t* ScaleB,
+                              float GlobalScaleA, float GlobalScaleB, aiter_tensor_t* out, aiter_tensor_t* out_scale,
+                              const char* kernelName, int a_preshuffle, void* stream)
+{
+    return safe_call([&] {
+        // the reference folds float(gA) * float(gB), a double product, into the fp32 result
+        const float g = static_cast<float>(static_cast<double>(GlobalScaleA) * static_cast<double>(GlobalScaleB));
+        run_f4gemm("nvfp4_gemm_asm", true, g, A, B, ScaleA, ScaleB, out, out_scale, kernelName, a_preshuffle, stream);
     });
 }
 

@@ -17,7 +17,14 @@
 
 namespace b200 {
 
-enum GemmKind : int { KIND_BF16 = 0, KIND_MXF8 = 1, KIND_MXF4 = 2, KIND_MXF8F4 = 3 /* e4m3 activations x e2m1 weights */ };
+enum GemmKind : int
+{
+    KIND_BF16   = 0,
+    KIND_MXF8   = 1,
+    KIND_MXF4   = 2,
+    KIND_MXF8F4 = 3, // e4m3 activations x e2m1 weights
+    KIND_NVF4   = 4, // e2m1 x e2m1 with one e4m3 scale per 16 elements (NVFP4); wire scale tiles are 32 rows x 8 bytes
+};
 enum OperandMode : int { OPM_ROWMAJOR = 0, OPM_TILE16 = 1, OPM_A2X128 = 2, OPM_BATCHED = 4 /* row-major, one matrix per batch entry */ };
 enum SfWire : int { SFW_NONE = 0, SFW_G1250 = 1, SFW_E8M0_SHUFFLE = 2 };
 

@@ -92,11 +92,12 @@ struct PersistentSmem
 constexpr uint32_t kEpiStageBytes = 16384; // 4 epilogue warps x 4 KB: two 32 x 64-byte buffers, or one 32 x 128-byte buffer (wide
                                            // stores); twice that when the wide stores are double-buffered
 
-// scaled: the stage carries 1 KB + 2 KB of raw scale bytes (P groups, Q groups)
+// scaled: 0 no scales; 1 the stage carries 1 KB + 2 KB of raw scale bytes (P groups, Q groups: 256 bytes per group of 32
+//         rows); 2 twice that (NVFP4: 512 bytes per group) - sf_unit_of(kind)
 // f4_operand: 0 none, 1 = P, 2 = Q arrives as packed e2m1 and needs a staging area of rows x 64 bytes
 // epi_stage: 0 none, 1 the epilogue's output staging area (tile stores through TMA), 2 twice the area
 // csplit: cluster K split; its leader keeps (csplit - 1) partial tiles of 128 x bn floats
-__host__ __device__ inline PersistentSmem make_persistent_smem(int bn, int cg, int stages, int f4_operand, bool scaled,
+__host__ __device__ inline PersistentSmem make_persistent_smem(int bn, int cg, int stages, int f4_operand, int scaled,
                                                                int epi_stage, int csplit)
 {
     PersistentSmem L;
@@ -104,8 +105,8 @@ __host__ __device__ inline PersistentSmem make_persistent_smem(int bn, int cg, i
     q_bytes          = (q_bytes + 1023u) & ~1023u;
     L.q_off          = kTileP * kTileKBytes;
     L.sfp_off        = L.q_off + q_bytes;
-    L.sfq_off        = L.sfp_off + (scaled ? 1024u : 0u);
-    L.stg_off        = L.sfq_off + (scaled ? 2048u : 0u);
+    L.sfq_off        = L.sfp_off + 1024u * static_cast<uint32_t>(scaled);
+    L.stg_off        = L.sfq_off + 2048u * static_cast<uint32_t>(scaled);
     uint32_t stg     = f4_operand == 1 ? kTileP * 64u : (f4_operand == 2 ? static_cast<uint32_t>(bn / cg) * 64u : 0u);
     stg              = (stg + 1023u) & ~1023u;
     L.stage_bytes    = L.stg_off + stg;
@@ -117,7 +118,12 @@ __host__ __device__ inline PersistentSmem make_persistent_smem(int bn, int cg, i
 }
 
 // TMEM columns one stage's scales occupy: [P atoms: 4 per K atom][Q atoms: 8 per K atom (two 128-row blocks)]
-__host__ __device__ constexpr int sf_cols_per_stage(int kind) { return kind == KIND_BF16 ? 0 : (kind == KIND_MXF4 ? 24 : 16); }
+__host__ __device__ constexpr int sf_cols_per_stage(int kind)
+{
+    return kind == KIND_BF16 ? 0 : (kind == KIND_NVF4 ? 48 : (kind == KIND_MXF4 ? 24 : 16));
+}
+// raw scale bytes of a stage in units of 256 per 32-row group (the `scaled` argument of make_persistent_smem)
+__host__ __device__ constexpr int sf_unit_of(int kind) { return kind == KIND_BF16 ? 0 : (kind == KIND_NVF4 ? 2 : 1); }
 
 // Stage ring position kept by increments: these loops run on one thread (or one warp) per K tile, where a
 // division by the run-time stage count would cost more than the work itself.
@@ -150,16 +156,19 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
 {
     constexpr bool kScaled = (KIND != KIND_BF16);
     constexpr bool kMixed  = (KIND == KIND_MXF8F4);
-    constexpr int kAtomsK  = (KIND == KIND_MXF4) ? 2 : 1;      // 4-k-block scale atoms per 128-byte K tile
+    constexpr bool kNvf4   = (KIND == KIND_NVF4);
+    // scale atoms per 128-byte K tile: one 32-bit word per row each (MX: the scales of 4 blocks of 32; NVFP4: of 4 blocks of 16)
+    constexpr int kAtomsK  = kNvf4 ? 4 : ((KIND == KIND_MXF4) ? 2 : 1);
     constexpr int kSfCols  = sf_cols_per_stage(KIND);
-    constexpr int kTWords  = kSfCols > 16 ? 24 : 16;
+    constexpr int kTWords  = kSfCols > 24 ? 48 : (kSfCols > 16 ? 24 : 16);
+    constexpr uint32_t kNeutralSf = kNvf4 ? 0x38383838u : 0x7F7F7F7Fu; // four scale bytes of 1.0 (e4m3 / e8m0)
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen        = smem_raw + (smem_base - smem_u32(smem_raw));
     const int bn             = prm.bn;
     const int S              = prm.stages;
-    const PersistentSmem L   = make_persistent_smem(bn, CG, S, kMixed ? prm.f4_operand : 0, kScaled, prm.epi_bufs, prm.csplit);
+    const PersistentSmem L   = make_persistent_smem(bn, CG, S, kMixed ? prm.f4_operand : 0, sf_unit_of(KIND), prm.epi_bufs, prm.csplit);
     constexpr int kSfChunk   = (SFW == SFW_E8M0_SHUFFLE) ? 256 : 128 * kAtomsK; // raw scale bytes per 32-row group per stage
 
     const uint32_t bar_base  = smem_base + L.bar_off;
@@ -392,7 +401,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             uint32_t t[kTWords];
 #pragma unroll
         for(int c = 0; c < kTWords; ++c)
-            t[c] = 0x7F7F7F7Fu;
+            t[c] = kNeutralSf;
         if(prm.noscale)
         {
             // every scale reads 2^0: the raw bytes are loaded (the barrier protocol stays the same) and ignored
@@ -491,6 +500,21 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                 t[(j < 4) ? 4 + j : 16 + (j - 4)] = chunks[j * 64 + 32 + lane]; // K atom 1: P cols 4..7, Q cols 16..23
             }
         }
+        else if(kNvf4)
+        {
+            // raw: [group][wire tile h = 0, 1][row 0..31][8 scales]: two words per row per wire tile, K atoms 2h and 2h + 1
+#pragma unroll
+            for(int j = 0; j < 12; ++j)
+#pragma unroll
+                for(int h = 0; h < 2; ++h)
+                {
+                    const bool in    = (j < 4) || (j - 4 < q_groups);
+                    const uint2* grp = reinterpret_cast<const uint2*>((j < 4) ? rawp + j * 128 : rawq + (j - 4) * 128);
+                    const uint2 v    = in ? grp[h * 32 + lane] : make_uint2(kNeutralSf, kNeutralSf);
+                    t[(j < 4) ? (2 * h) * 4 + j : 16 + (2 * h) * 8 + (j - 4)]         = v.x;
+                    t[(j < 4) ? (2 * h + 1) * 4 + j : 16 + (2 * h + 1) * 8 + (j - 4)] = v.y;
+                }
+        }
         else
         {
             // raw: [group][k quarter a][row 0..31][4 k-blocks]: one word per row per K atom
@@ -502,13 +526,18 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                     const bool in       = (j < 4) || (j - 4 < q_groups);
                     const uint32_t* grp = (j < 4) ? rawp + j * (32 * kAtomsK) : rawq + (j - 4) * (32 * kAtomsK);
                     const int col       = (j < 4) ? a * 4 + j : 4 * kAtomsK + a * 8 + (j - 4);
-                    t[col]              = in ? grp[a * 32 + lane] : 0x7F7F7F7Fu;
+                    t[col]              = in ? grp[a * 32 + lane] : kNeutralSf;
                 }
         }
         const uint32_t tsf = tlane + prm.sf_tmem_base + s * prm.sf_cols;
         tmem_st_x16(tsf, t);
-        if(kTWords > 16)
+        if(kTWords == 24)
             tmem_st_x8(tsf + 16, t + 16);
+        if(kTWords == 48)
+        {
+            tmem_st_x16(tsf + 16, t + 16);
+            tmem_st_x16(tsf + 32, t + 32);
+        }
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();
@@ -644,8 +673,16 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                     const uint32_t stage = smem_base + s * L.stage_bytes;
                     const uint32_t bar   = sfraw_bar(s);
                     mbar_arrive_expect_tx(bar, sfp_bytes + sfq_bytes);
-                    tma_load_2d(stage + L.sfp_off, &map_sfp, bar, kc, grp_p);
-                    tma_load_2d(stage + L.sfq_off, &map_sfq, bar, kc, grp_q);
+                    if(kNvf4) // 512-byte chunks are two 256-byte pieces of a 3-D view (a box dimension holds 256 elements)
+                    {
+                        tma_load_3d(stage + L.sfp_off, &map_sfp, bar, 0, kc >> 8, grp_p);
+                        tma_load_3d(stage + L.sfq_off, &map_sfq, bar, 0, kc >> 8, grp_q);
+                    }
+                    else
+                    {
+                        tma_load_2d(stage + L.sfp_off, &map_sfp, bar, kc, grp_p);
+                        tma_load_2d(stage + L.sfq_off, &map_sfq, bar, kc, grp_q);
+                    }
                 }
             }
         }
@@ -662,7 +699,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             else if(KIND == KIND_MXF8 || KIND == KIND_MXF8F4)
                 idesc = idesc_block_scaled(0, 0, kM, bn); // the e2m1 operand has been widened to e4m3 in shared memory
             else
-                idesc = idesc_block_scaled(1, 1, kM, bn);
+                idesc = idesc_block_scaled(1, 1, kM, bn, !kNvf4);
             const bool p_tiled   = (prm.p_mode == OPM_TILE16);
             const bool q_tiled   = (prm.q_mode == OPM_TILE16);
             const uint32_t p_lbo = p_tiled ? kTileP * 16u : 16u;
@@ -684,9 +721,9 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
             uint32_t idk[4];
 #pragma unroll
             for(int k = 0; k < 4; ++k)
-                idk[k] = (KIND == KIND_BF16) ? idesc
-                         : (KIND == KIND_MXF4) ? idesc_with_sf(idesc, (k & 1) * 2, (k & 1) * 2)
-                                               : idesc_with_sf(idesc, k, k);
+                idk[k] = (KIND == KIND_BF16 || kNvf4) ? idesc
+                         : (KIND == KIND_MXF4)        ? idesc_with_sf(idesc, (k & 1) * 2, (k & 1) * 2)
+                                                      : idesc_with_sf(idesc, k, k);
             const uint32_t sf0 = tmem_base + prm.sf_tmem_base;
             const uint32_t full0 = full_bar(0), empty0 = empty_bar(0);
 
@@ -727,6 +764,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                                 mma_f16(d_col, pd, qd, idk[k], acc);
                             else if(KIND == KIND_MXF8 || KIND == KIND_MXF8F4)
                                 mma_mxf8f6f4(d_col, pd, qd, idk[k], acc, tsfp, tsfq);
+                            else if(kNvf4)
+                                mma_nvf4(d_col, pd, qd, idk[k], acc, tsfp + k * 4, tsfq + k * 8);
                             else
                                 mma_mxf4(d_col, pd, qd, idk[k], acc, tsfp + (k >> 1) * 4, tsfq + (k >> 1) * 8);
                         }
@@ -736,6 +775,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                                 mma_f16_2cta(d_col, pd, qd, idk[k], acc);
                             else if(KIND == KIND_MXF8 || KIND == KIND_MXF8F4)
                                 mma_mxf8f6f4_2cta(d_col, pd, qd, idk[k], acc, tsfp, tsfq);
+                            else if(kNvf4)
+                                mma_nvf4_2cta(d_col, pd, qd, idk[k], acc, tsfp + k * 4, tsfq + k * 8);
                             else
                                 mma_mxf4_2cta(d_col, pd, qd, idk[k], acc, tsfp + (k >> 1) * 4, tsfq + (k >> 1) * 8);
                         }
@@ -1122,6 +1163,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                     // saturating round-to-nearest-even cast, no scale.  Same arithmetic as the activation quantiser.
                     uint8_t* const out8 = static_cast<uint8_t*>(prm.out);
                     const bool row_ok   = p < prm.rows_p;
+                    const float al      = prm.alpha; // the product of the per-tensor scales of NVFP4 inputs; 1 otherwise
                     for(int b128 = 0; b128 < (bn >> 7); ++b128)
                     {
                         const int q_first = row_q0 + b128 * 128;
@@ -1140,7 +1182,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
 #pragma unroll
                                 for(int j = 0; j < 32; ++j)
                                 {
-                                    const float x = __uint_as_float(r[j]);
+                                    const float x = __uint_as_float(r[j]) * al;
                                     amax          = fmaxf(amax, fabsf(x));
                                     has_nan |= (x != x);
                                 }
@@ -1162,6 +1204,12 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                             uint32_t r[32];
                             tmem_ld_x32(tacc + b128 * 128 + c * 32, r);
                             tmem_ld_wait();
+                            if(al != 1.0f)
+                            {
+#pragma unroll
+                                for(int j = 0; j < 32; ++j)
+                                    r[j] = __float_as_uint(__uint_as_float(r[j]) * al);
+                            }
                             if(prm.out_mode == OUT_MXFP8)
                             {
                                 uint32_t wds[8];

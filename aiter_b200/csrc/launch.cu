@@ -116,6 +116,16 @@ static CUtensorMap scale_map(const ScaleOperand& sf, int chunk, int groups_per_t
     B200_CHECK((reinterpret_cast<uintptr_t>(sf.ptr) & 15) == 0, what, ": base address must be 16-byte aligned");
     B200_CHECK(sf.padded_rows % 32 == 0, what, ": scale rows must be padded to a multiple of 32 (got ", sf.padded_rows, ")");
     const cuuint64_t row_bytes = static_cast<cuuint64_t>(sf.padded_cols) * 32;
+    if(chunk > 256)
+    {
+        // a box dimension holds at most 256 elements: a 512-byte chunk (NVFP4) is two 256-byte pieces of a 3-D view
+        // [group][row bytes / 256][256], which lands in shared memory in the same order as the 2-D form would
+        B200_CHECK(chunk == 512 && row_bytes % 256 == 0, what, ": internal: scale chunk ", chunk);
+        cuuint64_t dims3[3]    = {256, row_bytes / 256, static_cast<cuuint64_t>(sf.padded_rows / 32)};
+        cuuint64_t strides3[2] = {256, row_bytes};
+        cuuint32_t box3[3]     = {256, 2, static_cast<cuuint32_t>(groups_per_tile)};
+        return encode_map(sf.ptr, 3, dims3, strides3, box3, CU_TENSOR_MAP_SWIZZLE_NONE, what);
+    }
     cuuint64_t dims[2]    = {row_bytes, static_cast<cuuint64_t>(sf.padded_rows / 32)};
     cuuint64_t strides[1] = {row_bytes};
     cuuint32_t box[2]     = {static_cast<cuuint32_t>(chunk), static_cast<cuuint32_t>(groups_per_tile)};
@@ -301,11 +311,12 @@ static int kernel_kind_of(int problem_kind)
     case PK_MXFP8: return KIND_MXF8;
     case PK_MXFP4: return KIND_MXF4;
     case PK_MXF8F4: return KIND_MXF8F4;
+    case PK_NVFP4: return KIND_NVF4;
     default: fail("problem kind ", problem_kind, " has no kernel in this build");
     }
 }
 
-static int max_stages(int bn, int cg, int smem_limit, int f4_operand, bool scaled, int epi_stage, int csplit = 1)
+static int max_stages(int bn, int cg, int smem_limit, int f4_operand, int scaled, int epi_stage, int csplit = 1)
 {
     for(int s = kMaxStages; s >= 1; --s)
         if(static_cast<int>(make_persistent_smem(bn, cg, s, f4_operand, scaled, epi_stage, csplit).total) + 1024 <= smem_limit)
@@ -341,7 +352,7 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
         const long long pair_tiles = ((rows_p + 2 * kTileP - 1) / (2 * kTileP)) * ((rows_q + cfg.bn - 1) / cfg.bn);
         cfg.cg = (!cfg.swap && cfg.bn >= 128 && cfg.bn % 32 == 0 && rows_p >= 512 && pair_tiles * 2 >= num_sms) ? 2 : 1;
     }
-    const int elems_per_iter = (kind == PK_BF16) ? 64 : (kind == PK_MXFP4 ? 256 : 128);
+    const int elems_per_iter = (kind == PK_BF16) ? 64 : ((kind == PK_MXFP4 || kind == PK_NVFP4) ? 256 : 128);
     const long long k_iters  = (K + elems_per_iter - 1) / elems_per_iter;
     if(cfg.log2_splitk < 0)
     {
@@ -358,7 +369,7 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
     }
     if(cfg.stages <= 0)
     {
-        int s        = max_stages(cfg.bn, cfg.cg, 227 * 1024, kind == PK_MXF8F4 ? (cfg.swap ? 1 : 2) : 0, kind != PK_BF16, true);
+        int s        = max_stages(cfg.bn, cfg.cg, 227 * 1024, kind == PK_MXF8F4 ? (cfg.swap ? 1 : 2) : 0, sf_unit_of(kernel_kind_of(kind)), true);
         cfg.stages   = s > kMaxStages ? kMaxStages : s;
     }
 }
@@ -663,7 +674,7 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
 {
     const int named_stages = prob.cfg.stages; // what the caller's configuration asked for (0: this kernel's own choice)
     if(decode_kernel_disabled() || !cfg.swap || cfg.cg != 1 || cfg.bn > 64 || prob.M > cfg.bn || prob.scratch != nullptr ||
-       prob.out_mode != OUT_BF16 || prob.batch > 1 || prob.noscale)
+       prob.out_mode != OUT_BF16 || prob.batch > 1 || prob.noscale || kkind == KIND_NVF4)
         return false;
     const bool mixed = (kkind == KIND_MXF8F4);
     if(mixed && decode_mixed_disabled())
@@ -990,7 +1001,7 @@ static void launch_gemm_locked(const GemmProblem& prob)
     {
         // the re-quantising epilogue owns whole 128-column blocks of a row: activations on the 128-row slot, no K split,
         // tile width 128 or 256
-        B200_CHECK(prob.kind == PK_MXFP4, "low-precision outputs are built for the MXFP4 GEMM only");
+        B200_CHECK(prob.kind == PK_MXFP4 || prob.kind == PK_NVFP4, "low-precision outputs are built for the MXFP4 / NVFP4 GEMM only");
         B200_CHECK(prob.N % 128 == 0, "low-precision outputs need N % 128 == 0 (got N=", prob.N, ")");
         B200_CHECK(prob.out_mode != OUT_MXFP8 || (prob.M % 64 == 0 && prob.out_scale != nullptr), "the mxfp8 output needs M % 64 == 0 and an out_scale tensor");
         B200_CHECK(prob.bias == nullptr, "low-precision outputs take no bias");
@@ -1033,8 +1044,9 @@ static void launch_gemm_locked(const GemmProblem& prob)
     while(splits > num_k_iters)
         splits >>= 1;
     B200_CHECK(static_cast<long long>(num_k_iters) * (splits + 1) < (1LL << 31), "K x split count too large");
-    const int atoms_k  = (kkind == KIND_MXF4) ? 2 : 1;
+    const int atoms_k  = (kkind == KIND_NVF4) ? 4 : ((kkind == KIND_MXF4) ? 2 : 1);
     const int sf_cols  = sf_cols_per_stage(kkind);
+    const int sf_unit  = sf_unit_of(kkind);
     // the output leaves through shared memory and TMA tile stores when its pitch and base allow a tensor map
     const bool tma_store = ((reinterpret_cast<uintptr_t>(prob.out) & 15) == 0) && (prob.ldo % 8 == 0) && (cfg.swap || cfg.bn >= 32) &&
                            (prob.out_mode == OUT_BF16 || prob.out_mode == OUT_F16) && prob.batch == 1;
@@ -1042,12 +1054,12 @@ static void launch_gemm_locked(const GemmProblem& prob)
     // partial accumulators meet in the first CTA's shared memory instead of a global workspace.
     int csplit = 1;
     if(cfg.swap && cg == 1 && splits > 1 && splits <= 8 && prob.scratch == nullptr && !cluster_split_disabled() &&
-       max_stages(cfg.bn, cg, st.smem_optin, f4_operand, kkind != KIND_BF16, tma_store, splits) >= 4)
+       max_stages(cfg.bn, cg, st.smem_optin, f4_operand, sf_unit, tma_store, splits) >= 4)
     {
         csplit = splits;
         splits = 1;
     }
-    const int max_st = max_stages(cfg.bn, cg, st.smem_optin, f4_operand, kkind != KIND_BF16, tma_store, csplit);
+    const int max_st = max_stages(cfg.bn, cg, st.smem_optin, f4_operand, sf_unit, tma_store, csplit);
     B200_CHECK(max_st >= 2, "tile ", 128 * cg, "x", cfg.bn, " does not fit in shared memory");
     int stages = cfg.stages <= 0 ? max_st : std::min(cfg.stages, max_st);
 
@@ -1116,7 +1128,8 @@ static void launch_gemm_locked(const GemmProblem& prob)
         msp = scale_map(SP, chunk, 4, cfg.swap ? "weight scales" : "activation scales");
         msq = scale_map(SQ, chunk, (cfg.bn + 31) / 32, cfg.swap ? "activation scales" : "weight scales");
         B200_CHECK(sfw != SFW_E8M0_SHUFFLE || kkind == KIND_MXF4, "the e8m0_shuffle scale layout is only wired for MXFP4");
-        const long long need_cols = (sfw == SFW_E8M0_SHUFFLE) ? (kblocks + 7) / 8 * 8 : kblocks;
+        B200_CHECK(kkind != KIND_NVF4 || sfw == SFW_G1250, "NVFP4 scales arrive in tiles of 32 rows x 8 scales");
+        const long long need_cols = (kkind == KIND_NVF4) ? prob.K / 16 : (sfw == SFW_E8M0_SHUFFLE) ? (kblocks + 7) / 8 * 8 : kblocks;
         B200_CHECK(SP.padded_cols >= need_cols && SQ.padded_cols >= need_cols, "scale tensors have too few columns: need ",
                    need_cols, ", got ", SP.padded_cols, " and ", SQ.padded_cols);
         B200_CHECK(SP.padded_rows % 32 == 0 && SQ.padded_rows % 32 == 0, "scale rows must be padded to a multiple of 32");
@@ -1125,7 +1138,8 @@ static void launch_gemm_locked(const GemmProblem& prob)
         B200_CHECK(((reinterpret_cast<uintptr_t>(SP.ptr) | reinterpret_cast<uintptr_t>(SQ.ptr)) & 3) == 0,
                    "scale tensors must be 4-byte aligned");
         if(sfw == SFW_G1250)
-            B200_CHECK(kblocks % (4 * atoms_k) == 0, "K must be a multiple of ", 128 * atoms_k, " for this scale layout");
+            B200_CHECK(prob.K % (kkind == KIND_MXF8 || kkind == KIND_MXF8F4 ? 128 : 256) == 0, "K must be a multiple of ",
+                       (kkind == KIND_MXF8 || kkind == KIND_MXF8F4 ? 128 : 256), " for this scale layout");
     }
 
     PersistentParams prm{};
@@ -1195,9 +1209,9 @@ static void launch_gemm_locked(const GemmProblem& prob)
     prm.tma_store          = tma_store ? (wide_store ? 2 : 1) : 0;
     // the wide stores get a second staging buffer where that costs no pipeline stage
     prm.epi_bufs = tma_store ? 1 : 0;
-    if(wide_store && static_cast<int>(make_persistent_smem(cfg.bn, cg, stages, f4_operand, kkind != KIND_BF16, 2, csplit).total) + 1024 <= st.smem_optin)
+    if(wide_store && static_cast<int>(make_persistent_smem(cfg.bn, cg, stages, f4_operand, sf_unit, 2, csplit).total) + 1024 <= st.smem_optin)
         prm.epi_bufs = 2;
-    const PersistentSmem L = make_persistent_smem(cfg.bn, cg, stages, f4_operand, kkind != KIND_BF16, prm.epi_bufs, csplit);
+    const PersistentSmem L = make_persistent_smem(cfg.bn, cg, stages, f4_operand, sf_unit, prm.epi_bufs, csplit);
     const size_t smem      = L.total + 1024;
     // Tile order.  When the Q operand (the weights of a tall problem) is much larger than what L2 keeps beside the
     // streaming P operand and the output, walk it in panels of about 32 MB.
@@ -1236,6 +1250,8 @@ static void launch_gemm_locked(const GemmProblem& prob)
         launch_persistent_cg<KIND_MXF4, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else if(kkind == KIND_MXF8F4 && sfw == SFW_G1250)
         launch_persistent_cg<KIND_MXF8F4, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, mo, prm);
+    else if(kkind == KIND_NVF4 && sfw == SFW_G1250)
+        launch_persistent_cg<KIND_NVF4, SFW_G1250>(cg, ctas, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else
         fail("no kernel instance for kind ", kkind, " with scale layout ", sfw);
 

@@ -37,6 +37,7 @@ enum ProblemKind : int
     PK_MXFP8  = 1, // e4m3 x e4m3, e8m0 per 32
     PK_MXFP4  = 2, // e2m1 x e2m1, e8m0 per 32
     PK_MXF8F4 = 3, // e4m3 activations x e2m1 weights
+    PK_NVFP4  = 4, // e2m1 x e2m1, e4m3 per 16 (the per-tensor scales ride in alpha)
 };
 
 struct Operand

@@ -163,6 +163,17 @@ __device__ __forceinline__ void mma_mxf4(uint32_t d, uint64_t adesc, uint64_t bd
         ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
         : "memory");
 }
+// NVFP4: four e4m3 scales per row per instruction (K = 64, one per 16 elements): a whole 32-bit scale column each.
+__device__ __forceinline__ void mma_nvf4(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate, uint32_t tsfa, uint32_t tsfb)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
+        : "memory");
+}
 // shared memory (32 rows x 16 B, described by sdesc) -> TMEM, replicated to the four lane quarters.
 __device__ __forceinline__ void tc_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc)
 {
@@ -299,6 +310,16 @@ __device__ __forceinline__ void mma_mxf4_2cta(uint32_t d, uint64_t adesc, uint64
         ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
         : "memory");
 }
+__device__ __forceinline__ void mma_nvf4_2cta(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate, uint32_t tsfa, uint32_t tsfb)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
+        : "memory");
+}
 
 // registers -> TMEM: lane i of the warp writes four consecutive 32-bit columns of TMEM lane (quarter*32 + i)
 __device__ __forceinline__ void tmem_st_x4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
@@ -368,11 +389,11 @@ __host__ __device__ constexpr uint32_t idesc_bf16(uint32_t m, uint32_t n)
 {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
-// Block-scaled instruction descriptor: formats per kind (mxf8f6f4: e4m3 = 0, e2m1 = 5; mxf4: e2m1 = 1),
-// UE8M0 scales (bit 23), scale-factor byte selectors for A [29,31) and B [4,6).
-__host__ __device__ constexpr uint32_t idesc_block_scaled(uint32_t afmt, uint32_t bfmt, uint32_t m, uint32_t n)
+// Block-scaled instruction descriptor: formats per kind (mxf8f6f4: e4m3 = 0, e2m1 = 5; mxf4 / mxf4nvf4: e2m1 = 1),
+// scale type in bit 23 (1 = UE8M0, 0 = UE4M3), scale-factor byte selectors for A [29,31) and B [4,6).
+__host__ __device__ constexpr uint32_t idesc_block_scaled(uint32_t afmt, uint32_t bfmt, uint32_t m, uint32_t n, bool ue8m0 = true)
 {
-    return (afmt << 7) | (bfmt << 10) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24);
+    return (afmt << 7) | (bfmt << 10) | ((n >> 3) << 17) | ((ue8m0 ? 1u : 0u) << 23) | ((m >> 4) << 24);
 }
 // programmatic dependent launch (no-ops when the launch carries no programmatic dependency)
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

@@ -88,15 +88,40 @@ def gemm_mxfp4_asm(A: Tensor, B: Tensor, ScaleA: Tensor, ScaleB: Tensor, dtype: 
     return (out, out_scale) if out_scale is not None else out
 
 
+def gemm_nvfp4_asm(A: Tensor, B: Tensor, ScaleA: Tensor, ScaleB: Tensor, GlobalScaleA: float, GlobalScaleB: float,
+                   dtype: torch.dtype = dtypes.bf16, a_preshuffle: bool = True, kernelName: str = ""):
+    """NVFP4 GEMM (aiter/ops/gemm_op_a4w4.py:410-443): D = gA * gB * (deq A)(deq B)^T with one e4m3 scale per 16
+    elements, scales in tiles of 32 rows x 8 (shuffle_scale_f4(s, 8)), operands 16x16-byte tiled (B always, A when
+    a_preshuffle).  dtype: bf16 [M,N]; fp4x2: packed e2m1 [M,N/2] of gA * gB * (raw product, block scales dropped);
+    fp8: (e4m3 [M,N], e8m0 scale per 128 columns in the packed (M/64,N/128,16,4) order)."""
+    M, N = A.shape[0], B.shape[0]
+    out = _alloc_f4gemm_out(M, N, dtype, A.device)
+    out_scale = _alloc_f4gemm_out_scale(M, N, dtype, A.device)
+    _ffi.call("nvfp4_gemm_asm", A, B, ScaleA, ScaleB, float(GlobalScaleA), float(GlobalScaleB), out, out_scale,
+              kernelName if kernelName else None, int(bool(a_preshuffle)))
+    return (out, out_scale) if out_scale is not None else out
+
+
+def _as_global_scale(scale) -> float:
+    """An NVFP4 per-tensor scale given as a float or a one-element tensor -> float (gemm_op_a4w4.py:445-451)."""
+    if scale is None:
+        return 1.0
+    if torch.is_tensor(scale):
+        return float(scale.detach().reshape(-1)[0].item())
+    return float(scale)
+
+
 def _f4gemm_dispatch(A, B, A_scale, B_scale, *, dtype, apreshuffle, global_A_scale, global_B_scale, bias, alpha, beta):
     """The reference's gfx1250 F4GEMM dispatch (gemm_op_a4w4.py:80-122): bias / alpha / beta are not part of these
-    kernels (a warning, as there); per-tensor global scales select NVFP4, which is not built here."""
+    kernels (a warning, as there); the presence of a per-tensor global scale selects NVFP4 over MXFP4."""
     if bias is not None or (alpha is not None and alpha != 1.0) or (beta is not None and beta != 0.0):
-        logger.warning("gemm_a4w4o4 / gemm_a4w4o8 ignore bias/alpha/beta: not supported by the low-precision-output kernels.")
-    if global_A_scale is not None or global_B_scale is not None:
-        raise NotImplementedError("NVFP4 inputs (e4m3 scales per 16 elements plus per-tensor global scales) are not built")
+        logger.warning("the F4GEMM kernels ignore bias/alpha/beta.")
     m = A.numel() // A.shape[-1]
-    return gemm_mxfp4_asm(A.view(m, A.shape[-1]), B, A_scale, B_scale, dtype=dtype, a_preshuffle=bool(apreshuffle))
+    A2 = A.view(m, A.shape[-1])
+    if global_A_scale is not None or global_B_scale is not None:
+        return gemm_nvfp4_asm(A2, B, A_scale, B_scale, _as_global_scale(global_A_scale), _as_global_scale(global_B_scale),
+                              dtype=dtype, a_preshuffle=bool(apreshuffle))
+    return gemm_mxfp4_asm(A2, B, A_scale, B_scale, dtype=dtype, a_preshuffle=bool(apreshuffle))
 
 
 def gemm_a4w4o4(A: Tensor, B: Tensor, A_scale: Tensor, B_scale: Tensor, bias: Tensor | None = None, alpha: float | None = 1.0,
@@ -130,7 +155,11 @@ def gemm_a4w4(A: Tensor, B: Tensor, A_scale: Tensor, B_scale: Tensor, bias: Tens
     if dtype in (dtypes.fp4x2, dtypes.fp8):
         raise NotImplementedError("gemm_a4w4 returns one plain-dtype tensor; use gemm_a4w4o4 / gemm_a4w4o8")
     if global_A_scale is not None or global_B_scale is not None:
-        raise NotImplementedError("NVFP4 inputs (e4m3 scales per 16 elements plus per-tensor global scales) are not built")
+        # NVFP4 inputs come in the F4GEMM wire formats (16x16-byte tiled B, scales in tiles of 32 rows x 8), as on the
+        # reference's F4GEMM architecture (gemm_op_a4w4.py:178-193)
+        out = _f4gemm_dispatch(A, B, A_scale, B_scale, dtype=dtype, apreshuffle=bool(apreshuffle), global_A_scale=global_A_scale,
+                               global_B_scale=global_B_scale, bias=bias, alpha=alpha, beta=beta)
+        return out.view(*A.shape[:-1], out.shape[-1])
     m = A.numel() // A.shape[-1]
     n = B.shape[0]
     k = A.shape[-1] * 2

@@ -138,10 +138,21 @@ AITER_B200_API int gemm_a8w8_blockscale_bpreshuffle_asm(aiter_tensor_t* A, aiter
  *     fp4-output kernel is its "noscale" variant), round to nearest even, saturating;
  *   fp8 [M,N] + out_scale [M,N/128] e8m0: e4m3 data with one RoundUp(amax/448) scale per 128 output columns, the scale
  *     bytes in the packed (M/64, N/128, 16, 4) order; needs M % 64 == 0.
- * The low-precision forms need N % 128 == 0.  NVFP4 inputs (nvfp4_gemm_asm) are not built. */
+ * The low-precision forms need N % 128 == 0. */
 AITER_B200_API int mxfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* ScaleA,
                                   aiter_tensor_t* ScaleB, aiter_tensor_t* out, aiter_tensor_t* out_scale,
                                   const char* kernelName, int a_preshuffle, void* stream);
+
+/* ---- NVFP4 x NVFP4: the same entry point with e4m3 scales per 16 elements and two per-tensor scales.
+ * Python side aiter/ops/gemm_op_a4w4.py:305-321,410-443 (_nvfp4_gemm_asm, gemm_nvfp4_asm); reference
+ * arithmetic op_tests/test_f4gemm.py:122-133: out = float(gA) * float(gB) * (deq A)(deq B)^T, deq x = e2m1(x) * e4m3(scale).
+ * ScaleA [M, K/16], ScaleB [N, K/16]: non-negative e4m3 bytes (fp8 or uint8 tensors) in tiles of 32 rows x 8 scales
+ * (aiter/ops/shuffle.py:293-316 with intype 8); rows padded to a multiple of 32; K % 256 == 0.
+ * Output forms as for mxfp4_gemm_asm; the packed-fp4 form drops the block scales and keeps the per-tensor ones. */
+AITER_B200_API int nvfp4_gemm_asm(aiter_tensor_t* A, aiter_tensor_t* B, aiter_tensor_t* ScaleA,
+                                  aiter_tensor_t* ScaleB, float GlobalScaleA, float GlobalScaleB,
+                                  aiter_tensor_t* out, aiter_tensor_t* out_scale, const char* kernelName,
+                                  int a_preshuffle, void* stream);
 
 /* ---- bf16 x bf16, fp32 accumulate.  aiter/ops/gemm_op_a16w16.py:12-26 (asm form),
  * csrc/opus_gemm/include/opus_gemm.h:16-39 and csrc/opus_gemm/opus_gemm.cu:133-209,294-350 (opus forms).

@@ -107,6 +107,17 @@ def ref_gemm_a4w4(fp4_utils, x, w, xs, ws):
     return torch.mm(xf, wf.T).to(torch.bfloat16)
 
 
+def ref_gemm_nvfp4(fp4_utils, xq, wq, xs, ws, gA, gB, noscale=False):
+    """op_tests/test_f4gemm.py:122-133 (run_torch_nvfp4): fp32 result, e4m3 scales per 16 elements, per-tensor factors."""
+    x_f32 = fp4_utils.mxfp4_to_f32(xq)
+    w_f32 = fp4_utils.mxfp4_to_f32(wq)
+    if noscale:
+        return float(gA) * float(gB) * (x_f32 @ w_f32.T)
+    xsf = xs.view(torch.float8_e4m3fn).to(torch.float32).repeat_interleave(16, dim=1)
+    wsf = ws.view(torch.float8_e4m3fn).to(torch.float32).repeat_interleave(16, dim=1)
+    return float(gA) * float(gB) * (x_f32 * xsf) @ (w_f32 * wsf).T
+
+
 def ref_gemm_mxfp8(fp4_utils, intype, a, b, sa, sb):
     """op_tests/test_mxfp8fp4gemm.py:63-72."""
     af = a.view(torch.float8_e4m3fn).to(torch.float32)
@@ -279,6 +290,19 @@ def main(ref_root: str, out_path: str):
     g["requant_fp8_data"], g["requant_fp8_scale"] = q8.view(torch.uint8).numpy(), s8.view(torch.uint8).numpy()
     g["requant_fp8_scale_packed"] = ref_pack_mxfp8_out_scale(s8).numpy()
     g["requant_fp4_data"] = fp4_utils.f32_to_mxfp4(y).view(torch.uint8).numpy()
+
+    # ---- NVFP4 inputs: packed e2m1 data, e4m3 scales per 16 elements (positive, around 0.34 as the reference's bench
+    # initialiser draws them, op_tests/test_f4gemm.py:175-181), per-tensor factors
+    torch.manual_seed(3)
+    nx = torch.randint(0, 256, (48, 256), dtype=torch.uint8)   # [48, K=512] packed
+    nw = torch.randint(0, 256, (64, 256), dtype=torch.uint8)
+    nxs = (torch.randn(48, 32) * 0.08 + 0.34375).clamp(0.015625, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+    nws = (torch.randn(64, 32) * 0.08 + 0.34375).clamp(0.015625, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+    g["nv_x"], g["nv_w"], g["nv_xs"], g["nv_ws"] = nx.numpy(), nw.numpy(), nxs.numpy(), nws.numpy()
+    g["nv_g"] = np.array([0.75, 1.3], dtype=np.float64)
+    g["nv_out_f32"] = ref_gemm_nvfp4(fp4_utils, nx, nw, nxs, nws, 0.75, 1.3).numpy()
+    g["nv_out_bf16"] = bits16(ref_gemm_nvfp4(fp4_utils, nx, nw, nxs, nws, 0.75, 1.3).to(torch.bfloat16))
+    g["nv_out_noscale_f32"] = ref_gemm_nvfp4(fp4_utils, nx, nw, nxs, nws, 0.75, 1.3, noscale=True).numpy()
 
     np.savez_compressed(out_path, **g)
     print("wrote", out_path, os.path.getsize(out_path), "bytes,", len(g), "arrays")

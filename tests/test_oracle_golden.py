@@ -99,6 +99,23 @@ def test_requantising_outputs_bit_exact(golden):
     assert np.array_equal(ox.requant_fp4(y), golden["requant_fp4_data"])
 
 
+def test_nvfp4_reference(golden):
+    ga, gb = golden["nv_g"]
+    args = (golden["nv_x"], golden["nv_w"], golden["nv_xs"], golden["nv_ws"], ga, gb)
+    y = ox.gemm_nvfp4_f32(*args)
+    assert np.allclose(y, golden["nv_out_f32"], rtol=1e-5, atol=1e-4)  # fp32 sums in a different order
+    assert ox.mismatch_ratio(golden["nv_out_bf16"], ox.gemm_nvfp4_ref(*args), 1e-2, 1e-2) == 0.0
+    assert np.allclose(ox.gemm_nvfp4_f32(*args, noscale=True), golden["nv_out_noscale_f32"], rtol=1e-5, atol=1e-3)
+    # the constant case of the reference's F4GEMM test (op_tests/test_f4gemm.py:169-178): A = 0x22 (1.0), B = 0x33 (1.5),
+    # e4m3 scales 0x38 (1.0): every output is 1.5 * K
+    k = 256
+    a = np.full((4, k // 2), 0x22, dtype=np.uint8)
+    b = np.full((8, k // 2), 0x33, dtype=np.uint8)
+    one = lambda rows: np.full((rows, k // 16), 0x38, dtype=np.uint8)
+    assert (ox.gemm_nvfp4_f32(a, b, one(4), one(8)) == 1.5 * k).all()
+    assert (ox.gemm_nvfp4_f32(a, b, one(4), one(8), 0.5, 4.0) == 3.0 * k).all()
+
+
 def test_constant_input_known_answer():
     # A = B = 0.5 with unit scales: every output is 0.25*K (op_tests/test_mxfp8fp4gemm.py:75-98)
     k = 256
