@@ -29,6 +29,7 @@ from .gemm_op_a4w4 import (  # noqa: E402,F401
     gemm_nvfp4_asm,
     unpack_mxfp8_out_scale,
 )
+from .batched_gemm_op_bf16 import batched_gemm_bf16, batched_gemm_bf16_CK, batched_gemm_bf16_tune  # noqa: E402,F401
 from .gemm_op_a8w4 import gemm_a8w4_mxfp8  # noqa: E402,F401
 from .gemm_op_a8w8 import (  # noqa: E402,F401
     flatmm_a8w8_blockscale_asm,

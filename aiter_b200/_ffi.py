@@ -83,6 +83,8 @@ SIGNATURES = {
     "gemm_a16w16_asm": (T, T, T, T, T, I, S, I),
     "opus_gemm_a16w16_tune": (T, T, T, T, I, I),
     "opus_gemm": (T, T, T, T, T, T, T),
+    "batched_gemm_bf16": (T, T, T, T, I),
+    "batched_gemm_bf16_tune": (T, T, T, I, I),
     "dynamic_per_group_scaled_quant": (T, T, T, I, I, T, I),
     "gemm_a8w8_blockscale": (T, T, T, T, T, I, S),
     "gemm_a8w8_blockscale_tune": (T, T, T, T, T, I, I),

@@ -28,10 +28,11 @@ TABLES = {
     "bf16": ("AITER_CONFIG_GEMM_BF16", "bf16_tuned_gemm.csv"),
     "a8w8_mxfp8": ("AITER_CONFIG_GEMM_A8W8_MXFP8", "a8w8_mxfp8_tuned_gemm.csv"),
     "a8w4_mxfp8": ("AITER_CONFIG_GEMM_A8W4_MXFP8", "a8w4_mxfp8_tuned_gemm.csv"),
+    "bf16_batched": ("AITER_CONFIG_BF16_BATCHED_GEMM", "bf16_tuned_batched_gemm.csv"),  # keyed (B, M, N, K)
 }
 SHAPE_KEYS = ("M", "N", "K")
 BF16_EXTRA_KEYS = ("bias", "dtype", "outdtype", "scaleAB", "bpreshuffle")
-_INT_COLS = {"cu_num", "M", "N", "K", "kernelId", "splitK", "solidx"}
+_INT_COLS = {"cu_num", "B", "M", "N", "K", "kernelId", "splitK", "solidx"}
 _BOOL_COLS = {"bias", "scaleAB", "bpreshuffle"}
 
 

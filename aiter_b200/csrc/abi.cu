@@ -439,7 +439,7 @@ static void run_bf16(const char* fn, const aiter_tensor_t* A, const aiter_tensor
     const int a0 = A->ndim - 2;
     B200_CHECK(A->dtype_ == AITER_DTYPE_bf16 && B->dtype_ == AITER_DTYPE_bf16, fn, ": only bf16 inputs are supported (got ",
                dtype_name(A->dtype_), ", ", dtype_name(B->dtype_), ")");
-    B200_CHECK(out->dtype_ == AITER_DTYPE_bf16 || out->dtype_ == AITER_DTYPE_fp32, fn, ": unsupported output dtype, expected bf16 or fp32 (got ",
+    B200_CHECK(plain_out_mode(out->dtype_) >= 0, fn, ": unsupported output dtype, expected bf16, fp16 or fp32 (got ",
                dtype_name(out->dtype_), ")");
     const long long batch = a0 ? A->shape[0] : 1;
     const long long M = A->shape[a0], K = A->shape[a0 + 1], N = B->shape[a0];
@@ -528,6 +528,49 @@ extern "C" int opus_gemm_a16w16_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, ait
         const long long batch = XQ->shape[0];
         B200_CHECK(WQ->shape[0] == batch && Y->shape[0] == batch, "opus_gemm_a16w16_tune: batch mismatch");
         run_bf16("opus_gemm_a16w16_tune", XQ, WQ, Y, bias, 0, cfg, stream);
+    });
+}
+
+// The CK batched bf16 GEMM's entry points (csrc/ck_batched_gemm_bf16/batched_gemm_bf16.cu:126-148, its _tune twin
+// csrc/ck_batched_gemm_bf16/batched_gemm_bf16_tune.cu): Y[b] = XQ[b] WQ[b]^T, all of the batch in one launch.  As there,
+// a bias is checked (its dtype must be the output's) and then NOT added - the reference's instances carry no D tensor
+// (include/batched_gemm_bf16_common.cuh:165-185) - and its splitK argument is accepted but the K split stays the kernel's
+// own choice (KBatch is fixed to 1 there).  Unlike the reference, row and batch strides are free (multiples of 8
+// elements), so the [m, b, k] storage of a transposed view is served without a copy.
+static void run_batched_bf16(const char* fn, aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* Y, aiter_tensor_t* bias,
+                             const KernelConfig& cfg, void* stream)
+{
+    require_tensor(XQ, fn, "XQ", 3);
+    require_tensor(WQ, fn, "WQ", 3);
+    require_tensor(Y, fn, "Y", 3);
+    B200_CHECK(XQ->dtype_ == AITER_DTYPE_bf16 && WQ->dtype_ == AITER_DTYPE_bf16, fn, ": Weights and activations should both be bf16!");
+    B200_CHECK(Y->dtype_ == AITER_DTYPE_bf16 || Y->dtype_ == AITER_DTYPE_fp16, fn, ": the output must be bf16 or fp16 (got ",
+               dtype_name(Y->dtype_), ")");
+    if(bias != nullptr)
+        B200_CHECK(bias->dtype_ == Y->dtype_, fn, ": Out and bias should have the same dtype!");
+    B200_CHECK(WQ->shape[0] == XQ->shape[0] && Y->shape[0] == XQ->shape[0], fn, ": batch mismatch");
+    run_bf16(fn, XQ, WQ, Y, nullptr, 0, cfg, stream);
+}
+
+extern "C" int batched_gemm_bf16(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* out, aiter_tensor_t* bias, int splitK,
+                                 void* stream)
+{
+    (void)splitK;
+    return safe_call([&] {
+        KernelConfig cfg;
+        run_batched_bf16("batched_gemm_bf16", XQ, WQ, out, bias, cfg, stream);
+    });
+}
+
+extern "C" int batched_gemm_bf16_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* out, int kernelId, int splitK,
+                                      void* stream)
+{
+    return safe_call([&] {
+        KernelConfig cfg;
+        B200_CHECK(config_from_id(kernelId, cfg), "batched_gemm_bf16_tune: Kernel id ", kernelId, " not found");
+        B200_CHECK(splitK >= 0 && splitK <= 8, "batched_gemm_bf16_tune: splitK is log2 of the K split, 0..8");
+        cfg.log2_splitk = splitK;
+        run_batched_bf16("batched_gemm_bf16_tune", XQ, WQ, out, nullptr, cfg, stream);
     });
 }
 

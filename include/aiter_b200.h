@@ -172,6 +172,16 @@ AITER_B200_API int opus_gemm(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tenso
                              aiter_tensor_t* bias, void* stream);
 AITER_B200_API int opus_gemm_workspace_init(void);
 
+/* ---- batched bf16: out[b,M,N] = XQ[b,M,K] WQ[b,N,K]^T, bf16 or fp16 out, the whole batch in one launch.
+ * csrc/ck_batched_gemm_bf16/batched_gemm_bf16.cu:126-148 (pybind there: csrc/include/rocm_ops.hpp:249-262), Python side
+ * aiter/ops/batched_gemm_op_bf16.py:27-148.  As in the reference the bias is only checked (same dtype as out), never
+ * added, and splitK of the plain form is accepted and ignored; the _tune form takes a kernel id of the menu and log2 of
+ * the K split.  K-contiguous operands; row and batch strides multiples of 8 elements (a transposed [M,b,K] view works). */
+AITER_B200_API int batched_gemm_bf16(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* out, aiter_tensor_t* bias,
+                                     int splitK, void* stream);
+AITER_B200_API int batched_gemm_bf16_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* out, int kernelId,
+                                          int splitK, void* stream);
+
 /* ---- MXFP8 x MXFP8 -> bf16 without any device allocation.  No counterpart in the reference.
  * For callers that must not call cudaMalloc (a pre-sized arena, a plugin that may not touch the host's
  * allocator, a latency-critical loop): same arguments and results as mxfp8_mxfp8_gemm_asm, but the split-K

@@ -201,6 +201,15 @@ def test_torch_library_ops_have_fake_implementations():
                                              torch.empty(128, 256, dtype=torch.float8_e4m3fn, device="meta"),
                                              torch.empty(9, 2, device="meta"), torch.empty(1, 2, device="meta"))
     assert o.shape == (9, 128)
+    o4 = torch.ops.aiter.gemm_a4w4o4(a, b, s, s)
+    assert o4.shape == (3, 5, 128) and o4.dtype == torch.uint8
+    o8, sc = torch.ops.aiter.gemm_a4w4o8(a, b, s, s, False, 0.5, 2.0)
+    assert o8.shape == (3, 5, 256) and o8.dtype == torch.float8_e4m3fn and sc.shape == (3, 5, 2)
+    o = torch.ops.aiter.gemm_nvfp4(a[0], b, s, s, 0.5, 2.0)
+    assert o.shape == (5, 256) and o.dtype == torch.bfloat16
+    o = torch.ops.aiter.batched_gemm_bf16(torch.empty(4, 7, 32, dtype=torch.bfloat16, device="meta"),
+                                          torch.empty(4, 48, 32, dtype=torch.bfloat16, device="meta"))
+    assert o.shape == (4, 7, 48) and o.dtype == torch.bfloat16
 
 
 def test_fused_quantiser_wrappers_validate_arguments_on_cpu():
