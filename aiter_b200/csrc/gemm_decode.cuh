@@ -31,7 +31,7 @@ struct DecodeParams
     int rows_p, rows_q;      // weight rows (the problem's N), activation rows (the problem's M)
     int num_k_iters;         // ceil(K bytes / 128)
     int kblocks;             // valid 32-element scale blocks along K
-    int bn;                  // MMA N: 16, 32 or 64 (>= rows_q)
+    int bn;                  // MMA N: 16, 32 or 64; blockIdx.y counts tiles of bn activation rows (more than one only for bn = 64)
     int stages;
     int p_mode, q_mode;      // OperandMode of the weights / activations
     int csplit;              // K slices = CTAs per cluster: 1, 2 or 4
@@ -89,6 +89,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
     const uint32_t zrank = csplit > 1 ? cluster_ctarank() : 0u;           // this CTA's K slice
     const int tile       = csplit > 1 ? static_cast<int>(blockIdx.x) / csplit : static_cast<int>(blockIdx.x);
     const int row_p0     = tile * kTileP;
+    const int row_q0     = static_cast<int>(blockIdx.y) * bn; // this CTA's activation rows (the same weight tile serves every y)
     const int it_beg     = static_cast<int>(static_cast<uint32_t>(prm.num_k_iters) * zrank / static_cast<uint32_t>(csplit));
     const int n_iters    = static_cast<int>(static_cast<uint32_t>(prm.num_k_iters) * (zrank + 1u) / static_cast<uint32_t>(csplit)) - it_beg;
     const uint32_t per   = static_cast<uint32_t>(kTileP / csplit); // rows of the tile this CTA adds up and stores (whole warps)
@@ -167,7 +168,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                     mbar_arrive_expect_tx(bar, kTileP * kTileKBytes + q_bytes);
                     issue_operand_load(prm.p_mode, stage, &map_p, bar, row_p0, kt);
                 }
-                issue_operand_load(prm.q_mode, stage + prm.q_off, &map_q, bar, 0, kt);
+                issue_operand_load(prm.q_mode, stage + prm.q_off, &map_q, bar, row_q0, kt);
                 B200_TRACE(if(i == 0) stamp(3);)
                 if(++s == S)
                 {
@@ -202,7 +203,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                 const uint32_t bar   = sfraw_bar(s);
                 mbar_arrive_expect_tx(bar, sfp_bytes + sfq_bytes);
                 tma_load_2d(stage + prm.sfp_off, &map_sfp, bar, kc, row_p0 >> 5);
-                tma_load_2d(stage + prm.sfq_off, &map_sfq, bar, kc, 0);
+                tma_load_2d(stage + prm.sfq_off, &map_sfq, bar, kc, row_q0 >> 5);
                 if(++s == S)
                 {
                     s = 0;
@@ -586,7 +587,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                     const int p_warp0 = row_p0 + quarter * 32;
                     if(lane == 0 && p_warp0 < prm.rows_p)
                     {
-                        tma_store_2d(&map_out, smem_base + (warp - 2) * 4096, p_warp0 * 2, 0);
+                        tma_store_2d(&map_out, smem_base + (warp - 2) * 4096, p_warp0 * 2, row_q0);
                         bulk_commit_group();
                         bulk_wait_group_read<0>(); // the store has read its source before the CTA retires
                     }
@@ -598,8 +599,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                     // dependent launch waits for that)
 #pragma unroll
                     for(int j = 0; j < 64; ++j)
-                        if(j < bn && j < prm.rows_q)
-                            prm.out[static_cast<size_t>(j) * prm.ldo + p] = __float2bfloat16_rn(v[j]);
+                        if(j < bn && row_q0 + j < prm.rows_q)
+                            prm.out[static_cast<size_t>(row_q0 + j) * prm.ldo + p] = __float2bfloat16_rn(v[j]);
                 }
             }
         }

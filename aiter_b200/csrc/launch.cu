@@ -638,7 +638,7 @@ static DecodeLayout make_decode_layout(int bn, int stages, int csplit, bool scal
 }
 
 template <int KIND, int SFW>
-static void launch_decode_instance(int ctas, int csplit, size_t smem, cudaStream_t stream, const CUtensorMap& mp, const CUtensorMap& mq,
+static void launch_decode_instance(int ctas, int tiles_q, int csplit, size_t smem, cudaStream_t stream, const CUtensorMap& mp, const CUtensorMap& mq,
                                    const CUtensorMap& msp, const CUtensorMap& msq, const CUtensorMap& mo, const DecodeParams& prm)
 {
     auto kernel = gemm_decode_kernel<KIND, SFW>;
@@ -651,7 +651,7 @@ static void launch_decode_instance(int ctas, int csplit, size_t smem, cudaStream
     }
     raise_smem_limit(kernel, attr_done);
     cudaLaunchConfig_t lc{};
-    lc.gridDim          = dim3(ctas, 1, 1);
+    lc.gridDim          = dim3(ctas, tiles_q, 1);
     lc.blockDim         = dim3(kDecodeThreads, 1, 1);
     lc.dynamicSmemBytes = smem;
     lc.stream           = stream;
@@ -673,7 +673,9 @@ static void launch_decode_instance(int ctas, int csplit, size_t smem, cudaStream
 static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, int kkind, DeviceState& st)
 {
     const int named_stages = prob.cfg.stages; // what the caller's configuration asked for (0: this kernel's own choice)
-    if(decode_kernel_disabled() || !cfg.swap || cfg.cg != 1 || cfg.bn > 64 || prob.M > cfg.bn || prob.scratch != nullptr ||
+    // one tile of activation rows, or up to four tiles of 64 (each a CTA of its own on the same weight tile)
+    const int tiles_q = static_cast<int>((prob.M + cfg.bn - 1) / std::max(cfg.bn, 1));
+    if(decode_kernel_disabled() || !cfg.swap || cfg.cg != 1 || cfg.bn > 64 || (tiles_q > 1 && (cfg.bn != 64 || tiles_q > 4)) || prob.scratch != nullptr ||
        prob.out_mode != OUT_BF16 || prob.batch > 1 || prob.noscale || kkind == KIND_NVF4)
         return false;
     const bool mixed = (kkind == KIND_MXF8F4);
@@ -794,20 +796,20 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
     const int ctas    = tiles_p * csplit;
     const size_t smem = L.total + 1024;
     if(kkind == KIND_BF16)
-        launch_decode_instance<KIND_BF16, SFW_NONE>(ctas, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
+        launch_decode_instance<KIND_BF16, SFW_NONE>(ctas, tiles_q, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else if(kkind == KIND_MXF8 && sfw == SFW_G1250)
-        launch_decode_instance<KIND_MXF8, SFW_G1250>(ctas, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
+        launch_decode_instance<KIND_MXF8, SFW_G1250>(ctas, tiles_q, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else if(kkind == KIND_MXF4 && sfw == SFW_E8M0_SHUFFLE)
-        launch_decode_instance<KIND_MXF4, SFW_E8M0_SHUFFLE>(ctas, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
+        launch_decode_instance<KIND_MXF4, SFW_E8M0_SHUFFLE>(ctas, tiles_q, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else if(kkind == KIND_MXF4 && sfw == SFW_G1250)
-        launch_decode_instance<KIND_MXF4, SFW_G1250>(ctas, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
+        launch_decode_instance<KIND_MXF4, SFW_G1250>(ctas, tiles_q, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else if(kkind == KIND_MXF8F4 && sfw == SFW_G1250)
-        launch_decode_instance<KIND_MXF8F4, SFW_G1250>(ctas, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
+        launch_decode_instance<KIND_MXF8F4, SFW_G1250>(ctas, tiles_q, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else
         fail("no decode kernel instance for kind ", kkind, " with scale layout ", sfw);
 #ifdef AITER_B200_TRACING
     if(trace_print)
-        print_trace(st, prob, cfg, tiles_p, 1, csplit, stages);
+        print_trace(st, prob, cfg, tiles_p, tiles_q, csplit, stages);
 #endif
     return true;
 }

@@ -101,6 +101,11 @@ def candidates(M: int, N: int, K: int, family: str):
             for st in (4, 8):
                 for sk in splits:
                     out.append((0, 1, bn, st, sk))
+    if 64 < M <= 256:
+        # the decode kernel on up to four tiles of 64 activation rows, each streaming the same weight tile
+        for st in (0, 3):
+            for sk in [s for s in splits if s <= 2]:
+                out.append((0, 1, 64, st, sk))
     if M >= 64:
         for pair in (0, 1):
             for bn in (64, 128, 192, 224, 256):

@@ -407,6 +407,31 @@ def test_a8w8_blockscale_e8m0_scales_run_as_mxfp8(ab, M, N, K, bpre):
     assert_healthy(ab)
 
 
+# ------------------------------------------------------------------------------------------- decode kernel, several activation tiles
+@pytest.mark.parametrize("M", [65, 128, 200, 256])
+def test_decode_kernel_on_up_to_four_tiles_of_64_rows(ab, M):
+    # a 128x64 tile with the weights on the 128-row slot and a K split of at most 4 runs on the decode kernel; with more
+    # than 64 activation rows every tile of 64 is a CTA of its own on the same weight tile (ragged last tile included)
+    N, K = 640, 1024
+    for name in ("tc5_128x64_t_s0_k0", "tc5_128x64_t_s3_k1", "tc5_128x64_t_s0_k2"):
+        apre = 1 if M % 2 == 0 else 0  # the (m/2,k/128,2,128) activation tiling needs an even row count
+        ref, args = mxfp8_case(ab, M, N, K, apre, seed=M)
+        check(ref, ab.gemm_a8w8_mxfp8(*args, a_preshuffle=bool(apre), kernelName=name), what=f"mxfp8 {M} rows {name}")
+        ref, args = a8w4_case(ab, M, N, K, 0, seed=M + 1)
+        check(ref, ab.gemm_a8w4_mxfp8(*args, a_preshuffle=False, kernelName=name), what=f"a8w4 {M} rows {name}")
+        ref, xq, wq, xs, ws = mxfp4_case(ab, M, N, K, seed=M + 2)
+        out = torch.full(((M + 31) // 32 * 32, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ab.gemm_a4w4_asm(to_cuda_u8(xq, ab.dtypes.fp4x2), ab.shuffle_weight(to_cuda_u8(wq), layout=(16, 16)),
+                         ab.fp4_utils.e8m0_shuffle(to_cuda_u8(xs)), ab.fp4_utils.e8m0_shuffle(to_cuda_u8(ws)), out, name)
+        check(ref, out[:M], what=f"mxfp4 {M} rows {name}")
+        assert torch.isnan(out[M:].float()).all(), "rows beyond M must stay untouched"
+        a, b = randn_bf16(M, K, M + 3, 0.1), randn_bf16(N, K, M + 4, 0.1)
+        y = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ab.gemm_a16w16_asm(a.cuda(), b.cuda(), y, kernelName=name)
+        check(ox.gemm_a16w16_ref(bf16_bits(a), bf16_bits(b)), y, what=f"bf16 {M} rows {name}")
+    assert_healthy(ab)
+
+
 # ------------------------------------------------------------------------------------------- persistent paths
 def test_many_units_per_cta(ab):
     # more output tiles than SMs: the persistent loop, both accumulators and the stage ring wrap many times
