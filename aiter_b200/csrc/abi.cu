@@ -382,8 +382,8 @@ extern "C" int gemm_a8w8_blockscale_bpreshuffle_tune(aiter_tensor_t* XQ, aiter_t
 extern "C" int gemm_a8w8_blockscale_cktile(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale, aiter_tensor_t* w_scale,
                                            aiter_tensor_t* Out, int preshuffleB, int splitK, const char* kernelName, void* stream)
 {
-    (void)splitK; (void)kernelName;
-    return safe_call([&] { run_blockscale("gemm_a8w8_blockscale_cktile", XQ, WQ, x_scale, w_scale, Out, preshuffleB != 0, stream); });
+    (void)splitK;
+    return safe_call([&] { run_blockscale("gemm_a8w8_blockscale_cktile", XQ, WQ, x_scale, w_scale, Out, preshuffleB != 0, stream, kernelName); });
 }
 extern "C" int gemm_a8w8_blockscale_cktile_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale, aiter_tensor_t* w_scale,
                                                 aiter_tensor_t* Out, int kernelId, int splitK, int preshuffleB, void* stream)
@@ -398,8 +398,7 @@ extern "C" int gemm_a8w8_blockscale_bpreshuffle_cktile(aiter_tensor_t* XQ, aiter
                                                        aiter_tensor_t* w_scale, aiter_tensor_t* Out, int preshuffleB, const char* kernelName,
                                                        void* stream)
 {
-    (void)kernelName;
-    return safe_call([&] { run_blockscale("gemm_a8w8_blockscale_bpreshuffle_cktile", XQ, WQ, x_scale, w_scale, Out, preshuffleB != 0, stream); });
+    return safe_call([&] { run_blockscale("gemm_a8w8_blockscale_bpreshuffle_cktile", XQ, WQ, x_scale, w_scale, Out, preshuffleB != 0, stream, kernelName); });
 }
 extern "C" int gemm_a8w8_blockscale_bpreshuffle_cktile_tune(aiter_tensor_t* XQ, aiter_tensor_t* WQ, aiter_tensor_t* x_scale,
                                                             aiter_tensor_t* w_scale, aiter_tensor_t* Out, int kernelId, int splitK,

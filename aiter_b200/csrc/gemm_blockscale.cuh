@@ -348,6 +348,7 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
     const uint32_t zrank       = prm.cluster ? cluster_ctarank() : blockIdx.z; // K slice
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int col0 = blockIdx.x * kBsTileN;
+    const int m0   = static_cast<int>(blockIdx.y) * XR; // this CTA's activation rows (more than one tile of rows only for XR = 64)
     const int kb0  = static_cast<int>(static_cast<long long>(prm.k_blocks) * zrank / prm.splits);
     const int KB   = static_cast<int>(static_cast<long long>(prm.k_blocks) * (zrank + 1) / prm.splits) - kb0;
 
@@ -409,7 +410,7 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
                 else
                 {
                     mbar_arrive_expect_tx(full_bar(s), XR * kTileKBytes);
-                    issue_operand_load(prm.a_mode, stage + kWBytes, &map_a, full_bar(s), 0, kb0 + j);
+                    issue_operand_load(prm.a_mode, stage + kWBytes, &map_a, full_bar(s), m0, kb0 + j);
                 }
                 issued = j + 1;
                 if(++s == S)
@@ -499,7 +500,7 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
         for(int it = threadIdx.x - 64; it < KB * XR; it += 128)
         {
             const int j = it / XR, i = it - j * XR;
-            const long long xo = static_cast<long long>(i < prm.M ? i : 0) * prm.xs_stride_m + static_cast<long long>(kb0 + j) * prm.xs_stride_k;
+            const long long xo = static_cast<long long>(m0 + i < prm.M ? m0 + i : 0) * prm.xs_stride_m + static_cast<long long>(kb0 + j) * prm.xs_stride_k;
             const long long wo = static_cast<long long>(blockIdx.x) * prm.k_blocks + kb0 + j;
             sc_tab[it] = prm.scales_e8m0
                              ? e8m0_to_float(__ldg(reinterpret_cast<const uint8_t*>(prm.x_scale) + xo)) *
@@ -587,11 +588,11 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
         else if(ok && prm.splits > 1)
         {
             // K split: park this slice ([m][n] floats), take a ticket; the last slice to arrive adds them in a fixed order
-            const unsigned int tile = blockIdx.x;
+            const unsigned int tile = blockIdx.y * gridDim.x + blockIdx.x;
             float* mine = prm.ws_partial + (static_cast<size_t>(tile) * prm.splits + blockIdx.z) * (XR * kBsTileN);
 #pragma unroll
             for(int i = 0; i < XR; ++i)
-                if(i < prm.M)
+                if(m0 + i < prm.M)
                     mine[i * kBsTileN + r_local] = acc[i];
             __threadfence();
             __syncwarp();
@@ -625,7 +626,7 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
                     const float* src = part + static_cast<size_t>(z) * (XR * kBsTileN);
 #pragma unroll
                     for(int i = 0; i < XR; ++i)
-                        if(i < prm.M)
+                        if(m0 + i < prm.M)
                             acc[i] += __ldcg(src + i * kBsTileN + r_local);
                 }
                 if(threadIdx.x == 64)
@@ -655,7 +656,7 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
                 __syncwarp();
                 if(lane == lead && n < prm.N) // (a tile that starts inside the output; what sticks out is clipped)
                 {
-                    tma_store_2d(&map_o, smem_base + (warp - 2) * (XR * 64), (n) * 2, 0);
+                    tma_store_2d(&map_o, smem_base + (warp - 2) * (XR * 64), (n) * 2, m0);
                     bulk_commit_group();
                     bulk_wait_group_read<0>(); // the store has read its source before the CTA retires (see gemm_persistent.cuh)
                 }
@@ -665,8 +666,8 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
         {
 #pragma unroll
             for(int i = 0; i < XR; ++i)
-                if(i < prm.M)
-                    store_out(prm.out, static_cast<size_t>(i) * prm.ldo + n, acc[i], prm.out_mode);
+                if(m0 + i < prm.M)
+                    store_out(prm.out, static_cast<size_t>(m0 + i) * prm.ldo + n, acc[i], prm.out_mode);
         }
         tc_fence_before_sync();
     }

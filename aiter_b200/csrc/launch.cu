@@ -1354,6 +1354,11 @@ static bool use_few_rows(const BlockScaleProblem& prob)
 {
     return prob.M <= 64 && prob.K <= 32768 && !few_rows_disabled();
 }
+// by name the same kernel also takes up to four tiles of 64 rows, each a CTA of its own on the same weight tile
+static bool few_rows_can_serve(const BlockScaleProblem& prob)
+{
+    return prob.M <= 256 && prob.K <= 32768 && !few_rows_disabled();
+}
 
 bool parse_blockscale_name(const char* name, int& variant, int& log2_splitk)
 {
@@ -1429,7 +1434,7 @@ void launch_blockscale(const BlockScaleProblem& prob)
     const long long pairs256 = ((prob.M + 2 * kTileP - 1) / (2 * kTileP)) * ((prob.N + 2 * kBsTileN - 1) / (2 * kBsTileN));
     const long long single_cost = (tiles128 + st.sm_count - 1) / st.sm_count * 720;
     const long long pair_cost   = (pairs256 + st.sm_count / 2 - 1) / (st.sm_count / 2) * 1300;
-    B200_CHECK(prob.variant != 1 || use_few_rows(prob), "bs_fewrows serves at most 64 activation rows");
+    B200_CHECK(prob.variant != 1 || few_rows_can_serve(prob), "bs_fewrows serves at most 256 activation rows");
     B200_CHECK(prob.variant != 3 || prob.M > kTileP, "bs_256x256 needs more than 128 activation rows");
     const bool want_pair = prob.variant == 3 || (prob.variant == 0 && prob.M > kTileP && pair_cost < single_cost);
     const bool want_few  = prob.variant == 1 || (prob.variant == 0 && use_few_rows(prob));
@@ -1471,14 +1476,15 @@ void launch_blockscale(const BlockScaleProblem& prob)
         const int stage_bytes = (kBsTileN + xr) * kTileKBytes;
         CUtensorMap ma = operand_map(prob.act, xr, "activation operand");
         CUtensorMap mb = operand_map(prob.wgt, kBsTileN, "weight operand");
-        dim3 grid(static_cast<unsigned>((prob.N + kBsTileN - 1) / kBsTileN), 1, 1);
+        dim3 grid(static_cast<unsigned>((prob.N + kBsTileN - 1) / kBsTileN), static_cast<unsigned>((prob.M + xr - 1) / xr), 1);
+        const long long tiles = static_cast<long long>(grid.x) * grid.y;
         // split K across CTAs while the grid under-fills the machine and every slice keeps two K blocks; up to eight
         // slices of 16 or 32 rows form one cluster and meet in shared memory, the rest goes through the workspace
         static const bool no_split   = (std::getenv("AITER_B200_NO_BLOCKSCALE_SPLIT") != nullptr);
         static const bool no_cluster = (std::getenv("AITER_B200_NO_CLUSTER_SPLIT") != nullptr);
         const bool may_cluster       = !no_cluster;
         int splits = 1;
-        while(!no_split && splits < (may_cluster ? 8 : 16) && static_cast<long long>(grid.x) * (splits * 2) <= st.sm_count &&
+        while(!no_split && splits < (may_cluster ? 8 : 16) && tiles * (splits * 2) <= st.sm_count &&
               prm.k_blocks / (splits * 2) >= 2)
             splits *= 2;
         if(forced_splits > 0)
@@ -1486,11 +1492,11 @@ void launch_blockscale(const BlockScaleProblem& prob)
         prm.cluster = (may_cluster && splits > 1) ? 1 : 0;
         if(prm.cluster)
             ; // nothing to reserve: the slices meet in the reducing CTA's shared memory
-        else if(splits > 1 && grid.x <= static_cast<unsigned>(kCounterSlots))
+        else if(splits > 1 && tiles <= kCounterSlots)
         {
             cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
             cudaStreamIsCapturing(prob.stream, &cap);
-            const size_t bytes  = static_cast<size_t>(grid.x) * splits * kBsTileN * xr * sizeof(float);
+            const size_t bytes  = static_cast<size_t>(tiles) * splits * kBsTileN * xr * sizeof(float);
             StreamWorkspace& w0 = st.ws[prob.stream];
             if(cap != cudaStreamCaptureStatusNone && (w0.counter == nullptr || w0.partial_bytes < bytes))
                 splits = 1; // the workspace may not grow inside a capture: run unsplit

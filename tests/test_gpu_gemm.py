@@ -324,6 +324,37 @@ def test_a8w8_blockscale_fp32_scales(ab, M, N, K, bpre):
     assert_healthy(ab)
 
 
+@pytest.mark.parametrize("M", [65, 128, 200, 256])
+def test_a8w8_blockscale_few_rows_kernel_on_up_to_four_tiles_of_64_rows(ab, M):
+    # by name the few-rows kernel takes up to 256 rows: every tile of 64 is a CTA of its own on the same weight tile;
+    # unsplit, cluster K splits and fp16 output, fp32 and e8m0 scales, ragged N
+    N, K = 400, 2048
+    g = torch.Generator().manual_seed(M)
+    x = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn)
+    w = torch.randn(N, K, generator=g).to(torch.float8_e4m3fn)
+    xs = torch.rand(M, K // 128, generator=g) + 0.25
+    ws = torch.rand((N + 127) // 128, K // 128, generator=g) + 0.25
+    ref = ox.gemm_a8w8_blockscale_ref(x.view(torch.uint8).numpy(), w.view(torch.uint8).numpy(), xs.numpy(), ws.numpy())
+    for name in ("bs_fewrows_k0", "bs_fewrows_k1", "bs_fewrows_k3"):
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ab.gemm_a8w8_blockscale_cktile(x.cuda(), w.cuda(), xs.cuda(), ws.cuda(), out, kernelName=name)
+        check(ref, out, what=f"blockscale {M} rows {name}")
+    out16 = torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda")
+    xs_t = xs.T.contiguous().cuda()  # the preshuffled form stores x_scale K-block-major
+    ab.gemm_a8w8_blockscale_cktile(x.cuda(), ab.shuffle_weight(w.cuda(), layout=(16, 16)), xs_t.view(M, K // 128), ws.cuda(), out16,
+                                   preshuffleB=True, kernelName="bs_fewrows_k2")
+    got, want = out16.float().cpu().numpy(), ox.bf16_bits_to_f32(ref)
+    assert np.all(np.abs(got - want) <= 1e-2 + 1e-2 * np.abs(want))
+    exs = torch.randint(124, 130, (M, K // 128), generator=g, dtype=torch.uint8)
+    ews = torch.randint(124, 130, ((N + 127) // 128, K // 128), generator=g, dtype=torch.uint8)
+    ref8 = ox.gemm_a8w8_blockscale_ref(x.view(torch.uint8).numpy(), w.view(torch.uint8).numpy(), ox.e8m0_to_f32(exs.numpy()), ox.e8m0_to_f32(ews.numpy()))
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ab.gemm_a8w8_blockscale_cktile(x.cuda(), w.cuda(), exs.cuda().view(ab.dtypes.fp8_e8m0), ews.cuda().view(ab.dtypes.fp8_e8m0), out,
+                                   kernelName="bs_fewrows_k1")
+    check(ref8, out, what=f"blockscale {M} rows, e8m0 scales, bs_fewrows_k1")
+    assert_healthy(ab)
+
+
 @pytest.mark.parametrize("M", [16, 100, 300])
 def test_a8w8_blockscale_replays_from_a_cuda_graph(ab, M):
     # few-rows kernel (cluster + dependent launch), 128x128 kernel with and without its workspace K split: captured after
@@ -399,7 +430,12 @@ def test_a8w8_blockscale_e8m0_scales_run_as_mxfp8(ab, M, N, K, bpre):
                                                   xs_t.T.view(ab.dtypes.fp8_e8m0), ws.cuda().view(ab.dtypes.fp8_e8m0))
     else:
         out = ab.gemm_a8w8_blockscale(x.cuda(), w.cuda(), xs.cuda().view(ab.dtypes.fp8_e8m0), ws.cuda().view(ab.dtypes.fp8_e8m0))
-    assert ab.launch_count() == before + (1 if M <= 64 else 3)
+    # one launch where the few-rows kernel serves the call (up to 64 rows, or a tuned row that names it: it reads the e8m0
+    # bytes itself), else two expansion launches + the MXFP8 kernel
+    from aiter_b200 import gemm_op_a8w8
+    row = gemm_op_a8w8.get_CKGEMM_config(M, N, K, bpreshuffle=bpre)
+    few = M <= 64 or (row is not None and str(row.get("kernelName") or "").startswith("bs_fewrows"))
+    assert ab.launch_count() == before + (1 if few else 3)
     check(ref, out, what=f"blockscale with e8m0 scales {M}x{N}x{K} bpre={bpre}")
     # one e8m0 and one fp32 scale tensor: the e8m0 one is widened, the fp32 kernel runs
     out = ab.gemm_a8w8_blockscale(x.cuda(), w.cuda(), xs.cuda().view(ab.dtypes.fp8_e8m0), ab.fp4_utils.e8m0_to_f32(ws.cuda()))

@@ -290,6 +290,7 @@ def test_tuner_reads_shape_files_and_blockscale_names(tmp_path):
     names = tune.candidates(16, 4096, 4096, "a8w8_blockscale")
     assert "" in names and "bs_fewrows_k2" in names and "bs_128x128_k0" in names and "bs_256x256" not in names
     assert "bs_256x256" in tune.candidates(1024, 4096, 4096, "a8w8_blockscale_bpreshuffle")
+    assert "bs_fewrows_k1" in tune.candidates(128, 4096, 4096, "a8w8_blockscale") and "bs_fewrows_k1" not in tune.candidates(300, 4096, 4096, "a8w8_blockscale")
 
 
 def test_blockscale_table_rows_do_not_leak_onto_e8m0_scaled_calls(ab):
