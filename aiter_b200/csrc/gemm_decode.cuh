@@ -31,7 +31,7 @@ struct DecodeParams
     int rows_p, rows_q;      // weight rows (the problem's N), activation rows (the problem's M)
     int num_k_iters;         // ceil(K bytes / 128)
     int kblocks;             // valid 32-element scale blocks along K
-    int bn;                  // MMA N: 16, 32 or 64; blockIdx.y counts tiles of bn activation rows (more than one only for bn = 64)
+    int bn;                  // MMA N: 16, 32, 64 or 128; blockIdx.y counts tiles of bn activation rows (more than one only for bn >= 64)
     int stages;
     int p_mode, q_mode;      // OperandMode of the weights / activations
     int csplit;              // K slices = CTAs per cluster: 1, 2 or 4
@@ -49,7 +49,12 @@ struct DecodeParams
 };
 
 // TMEM columns of one stage's scales: [P atom a: 4 columns][Q atom a: 4 columns], a < atoms per K tile
-__host__ __device__ constexpr int decode_sf_cols(int kind) { return kind == KIND_BF16 ? 0 : (kind == KIND_MXF4 ? 16 : 8); }
+__host__ __device__ constexpr int decode_sf_cols(int kind)
+{
+    return kind == KIND_BF16 ? 0 : (kind == KIND_NVF4 ? 32 : (kind == KIND_MXF4 ? 16 : 8));
+}
+// raw scale bytes per 32-row group per K tile in units of 256 (NVFP4: 512 bytes)
+__host__ __device__ constexpr int decode_sf_unit(int kind) { return kind == KIND_BF16 ? 0 : (kind == KIND_NVF4 ? 2 : 1); }
 // (the mixed kind, e4m3 activations x packed e2m1 weights, is MXF8 once the scale warps have widened the weight tile to
 // e4m3 in shared memory: exact, every e2m1 value is an e4m3 value)
 
@@ -61,7 +66,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
 {
     constexpr bool kScaled = (KIND != KIND_BF16);
     constexpr bool kMixed  = (KIND == KIND_MXF8F4);
-    constexpr int kAtomsK  = (KIND == KIND_MXF4) ? 2 : 1; // 4-k-block scale atoms per 128-byte K tile
+    constexpr bool kNvf4   = (KIND == KIND_NVF4);
+    constexpr int kAtomsK  = kNvf4 ? 4 : ((KIND == KIND_MXF4) ? 2 : 1); // scale atoms (one 32-bit word per row) per 128-byte K tile
+    constexpr uint32_t kNeutralSf = kNvf4 ? 0x38383838u : 0x7F7F7F7Fu; // four scale bytes of 1.0 (e4m3 / e8m0)
     constexpr int kSfCols  = decode_sf_cols(KIND);
     constexpr bool kE8     = (SFW == SFW_E8M0_SHUFFLE);
     constexpr int kSfChunk = kE8 ? 256 : 128 * kAtomsK;   // raw scale bytes per 32-row group per K tile
@@ -202,8 +209,16 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                 const uint32_t stage = smem_base + s * prm.stage_bytes;
                 const uint32_t bar   = sfraw_bar(s);
                 mbar_arrive_expect_tx(bar, sfp_bytes + sfq_bytes);
-                tma_load_2d(stage + prm.sfp_off, &map_sfp, bar, kc, row_p0 >> 5);
-                tma_load_2d(stage + prm.sfq_off, &map_sfq, bar, kc, row_q0 >> 5);
+                if(kNvf4) // 512-byte chunks are two 256-byte pieces of a 3-D view (a box dimension holds 256 elements)
+                {
+                    tma_load_3d(stage + prm.sfp_off, &map_sfp, bar, 0, kc >> 8, row_p0 >> 5);
+                    tma_load_3d(stage + prm.sfq_off, &map_sfq, bar, 0, kc >> 8, row_q0 >> 5);
+                }
+                else
+                {
+                    tma_load_2d(stage + prm.sfp_off, &map_sfp, bar, kc, row_p0 >> 5);
+                    tma_load_2d(stage + prm.sfq_off, &map_sfq, bar, kc, row_q0 >> 5);
+                }
                 if(++s == S)
                 {
                     s = 0;
@@ -223,7 +238,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
             else if(KIND == KIND_MXF8 || KIND == KIND_MXF8F4)
                 idesc = idesc_block_scaled(0, 0, kTileP, bn);
             else
-                idesc = idesc_block_scaled(1, 1, kTileP, bn);
+                idesc = idesc_block_scaled(1, 1, kTileP, bn, !kNvf4);
             const bool p_tiled   = (prm.p_mode == OPM_TILE16);
             const bool q_tiled   = (prm.q_mode == OPM_TILE16);
             const uint32_t p_lbo = p_tiled ? kTileP * 16u : 16u, p_sbo = p_tiled ? 128u : 1024u, p_lay = p_tiled ? 0u : 2u;
@@ -242,9 +257,9 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
             uint32_t idk[4];
 #pragma unroll
             for(int k = 0; k < 4; ++k)
-                idk[k] = (KIND == KIND_BF16) ? idesc
-                         : (KIND == KIND_MXF4) ? idesc_with_sf(idesc, (k & 1) * 2, (k & 1) * 2)
-                                               : idesc_with_sf(idesc, k, k);
+                idk[k] = (KIND == KIND_BF16 || kNvf4) ? idesc
+                         : (KIND == KIND_MXF4)        ? idesc_with_sf(idesc, (k & 1) * 2, (k & 1) * 2)
+                                                      : idesc_with_sf(idesc, k, k);
             const uint32_t sf0 = tmem_base + bn; // the scale buffers follow the accumulator (bn columns)
             bool ok = true;
             int s = 0;
@@ -283,6 +298,8 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                         mma_f16(tmem_base, pd, qd, idk[k], acc);
                     else if(KIND == KIND_MXF8 || KIND == KIND_MXF8F4)
                         mma_mxf8f6f4(tmem_base, pd, qd, idk[k], acc, tsfp, tsfq);
+                    else if(kNvf4)
+                        mma_nvf4(tmem_base, pd, qd, idk[k], acc, tsfp + k * 4, tsfq + k * 4);
                     else
                         mma_mxf4(tmem_base, pd, qd, idk[k], acc, tsfp + (k >> 1) * 4, tsfq + (k >> 1) * 4);
                 }
@@ -307,7 +324,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
         bool ok = true;
         if(kScaled)
         {
-            const int q_groups = (bn + 31) / 32; // 1 or 2 groups of 32 activation rows (the weights always stage 4)
+            const int q_groups = (bn + 31) / 32; // 1 to 4 groups of 32 activation rows (the weights always stage 4)
             const int r16 = lane & 15, hi = lane >> 4;
             int s = 0;
             uint32_t phase = 0;
@@ -402,16 +419,16 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                 uint32_t t[kSfCols > 0 ? kSfCols : 1];
 #pragma unroll
                 for(int c = 0; c < kSfCols; ++c)
-                    t[c] = 0x7F7F7F7Fu;
+                    t[c] = kNeutralSf;
                 if(kE8)
                 {
                     // raw: per 32-row group j a 256-byte chunk, byte (k%4)*64 + (m%16)*4 + ((k%8)/4)*2 + (m%32)/16: this lane's
                     // row has its eight scale bytes in four words (one per k%4), at byte kh*2 + (row half)
                     const bool tail    = (kt * 8 + 8 > prm.kblocks);
                     const uint32_t sel = hi ? 0x7351u : 0x6240u;
-                    uint32_t raw[6][4];
+                    uint32_t raw[8][4];
 #pragma unroll
-                    for(int j = 0; j < 6; ++j)
+                    for(int j = 0; j < 8; ++j)
                     {
                         const uint32_t* grp = reinterpret_cast<const uint32_t*>(stage + (j < 4 ? prm.sfp_off + j * 256 : prm.sfq_off + (j - 4) * 256));
 #pragma unroll
@@ -419,7 +436,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                             raw[j][c] = (j < 4 + q_groups) ? grp[c * 16 + r16] : 0u;
                     }
 #pragma unroll
-                    for(int j = 0; j < 6; ++j)
+                    for(int j = 0; j < 8; ++j)
                     {
                         const uint32_t lo_part = __byte_perm(raw[j][0], raw[j][1], sel); // k%4 = 0,1 for both k halves
                         const uint32_t hi_part = __byte_perm(raw[j][2], raw[j][3], sel); // k%4 = 2,3
@@ -442,11 +459,28 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                         }
                     }
                 }
+                else if(kNvf4)
+                {
+                    // raw: [group][wire tile h = 0, 1][row 0..31][8 scales]: two words per row per wire tile, K atoms 2h and 2h + 1
+#pragma unroll
+                    for(int j = 0; j < 8; ++j)
+#pragma unroll
+                        for(int h = 0; h < 2; ++h)
+                        {
+                            const uint2* grp = reinterpret_cast<const uint2*>(stage + (j < 4 ? prm.sfp_off + j * 512 : prm.sfq_off + (j - 4) * 512));
+                            if(j < 4 + q_groups)
+                            {
+                                const uint2 v = grp[h * 32 + lane];
+                                t[(j < 4) ? (2 * h) * 4 + j : 16 + (2 * h) * 4 + (j - 4)]         = v.x;
+                                t[(j < 4) ? (2 * h + 1) * 4 + j : 16 + (2 * h + 1) * 4 + (j - 4)] = v.y;
+                            }
+                        }
+                }
                 else
                 {
                     // raw: [group][K atom a][row 0..31][4 k-blocks]: one word per row per K atom
 #pragma unroll
-                    for(int j = 0; j < 6; ++j)
+                    for(int j = 0; j < 8; ++j)
 #pragma unroll
                         for(int a = 0; a < kAtomsK; ++a)
                         {
@@ -457,7 +491,12 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                         }
                 }
                 const uint32_t tsf = tlane + bn + s * kSfCols;
-                if(kSfCols == 16)
+                if(kSfCols == 32)
+                {
+                    tmem_st_x16(tsf, t);
+                    tmem_st_x16(tsf + 16, t + 16);
+                }
+                else if(kSfCols == 16)
                     tmem_st_x16(tsf, t);
                 else
                     tmem_st_x8(tsf, t);
@@ -489,20 +528,26 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
         if(ok)
         {
             tc_fence_after_sync();
+            // the thread's row goes out in chunks of at most 64 columns (one chunk unless bn = 128)
+            const int n_chunks = (bn + 63) >> 6;
+            for(int h = 0; h < n_chunks && ok; ++h)
+            {
+            const int c0 = h * 64;                  // first column (activation row of the tile) of this chunk
+            const int bw = min(bn - c0, 64);        // its width: 16, 32 or 64
             float v[64];
             {
                 uint32_t r[32] = {};
-                if(bn == 16)
-                    tmem_ld_x16(tlane, r);
+                if(bw == 16)
+                    tmem_ld_x16(tlane + c0, r);
                 else
-                    tmem_ld_x32(tlane, r);
+                    tmem_ld_x32(tlane + c0, r);
                 tmem_ld_wait();
 #pragma unroll
                 for(int j = 0; j < 32; ++j)
                     v[j] = __uint_as_float(r[j]);
-                if(bn == 64)
+                if(bw == 64)
                 {
-                    tmem_ld_x32(tlane + 32, r);
+                    tmem_ld_x32(tlane + c0 + 32, r);
                     tmem_ld_wait();
 #pragma unroll
                     for(int j = 0; j < 32; ++j)
@@ -514,34 +559,39 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
             {
                 // Reduce-scatter over the cluster: CTA z owns rows [z * per, (z + 1) * per) of the tile (whole warps).  A warp
                 // whose rows belong to another CTA sends its partial sums to that CTA's shared memory ([source slice][row][bn
-                // floats], bytes counted on that CTA's red barrier) and is done; an owning warp waits for the other slices.
+                // floats], bytes counted on that CTA's red barrier) and is done; an owning warp waits for the other slices
+                // (once: the barrier counts the bytes of every chunk).
                 const uint32_t owner = static_cast<uint32_t>(p_local) / per;
                 const uint32_t prow  = static_cast<uint32_t>(p_local) - owner * per;
                 mine                 = (owner == zrank);
                 if(!mine)
                 {
                     const uint32_t src     = zrank < owner ? zrank : zrank - 1u; // this slice's place among the owner's sources
-                    const uint32_t dst_row = map_to_cta(smem_base + prm.red_off, owner) + (src * per + prow) * static_cast<uint32_t>(bn) * 4u;
+                    const uint32_t dst_row = map_to_cta(smem_base + prm.red_off, owner) +
+                                             ((src * per + prow) * static_cast<uint32_t>(bn) + static_cast<uint32_t>(c0)) * 4u;
                     const uint32_t dst_bar = map_to_cta(red_bar, owner);
 #pragma unroll
                     for(int j = 0; j < 64; j += 4)
-                        if(j < bn)
+                        if(j < bw)
                             st_async_v4(dst_row + static_cast<uint32_t>(j) * 4u, __float_as_uint(v[j]), __float_as_uint(v[j + 1]),
                                         __float_as_uint(v[j + 2]), __float_as_uint(v[j + 3]), dst_bar);
                 }
                 else
                 {
-                    ok = bounded_wait(red_bar, 0, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, 0x3000);
-                    ok = __all_sync(0xffffffffu, ok);
+                    if(h == 0)
+                    {
+                        ok = bounded_wait(red_bar, 0, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, 0x3000);
+                        ok = __all_sync(0xffffffffu, ok);
+                    }
                     if(ok)
                     {
                         const float4* red = reinterpret_cast<const float4*>(smem_gen + prm.red_off);
                         for(int z = 0; z < csplit - 1; ++z)
                         {
-                            const float4* row = red + (static_cast<size_t>(z * per + prow) * bn) / 4;
+                            const float4* row = red + (static_cast<size_t>(z * per + prow) * bn + c0) / 4;
 #pragma unroll
                             for(int j = 0; j < 64; j += 4)
-                                if(j < bn)
+                                if(j < bw)
                                 {
                                     const float4 t = row[j / 4];
                                     v[j] += t.x;
@@ -553,7 +603,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                     }
                 }
             }
-            B200_TRACE(if(lane == 0) stamp(42 + (warp - 2));)
+            B200_TRACE(if(lane == 0 && h == 0) stamp(42 + (warp - 2));)
             if(ok && mine)
             {
                 const int p = row_p0 + p_local;
@@ -562,32 +612,33 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                     const float b = (p < prm.rows_p) ? prm.beta * load_bias(prm.bias, prm.bias_is_bf16, p) : 0.f;
 #pragma unroll
                     for(int j = 0; j < 64; ++j)
-                        if(j < bn)
+                        if(j < bw)
                             v[j] = prm.alpha * v[j] + b;
                 }
                 else if(prm.alpha != 1.0f)
                 {
 #pragma unroll
                     for(int j = 0; j < 64; ++j)
-                        if(j < bn)
+                        if(j < bw)
                             v[j] *= prm.alpha;
                 }
                 if(prm.tma_store)
                 {
-                    // this warp's 32 output columns x bn rows, staged as [row m][32 x bf16] in a retired operand stage (every
-                    // tile load has landed and been consumed once the accumulator is complete) and stored as one TMA tile,
-                    // which clips rows >= M and columns >= N
-                    uint8_t* buf = smem_gen + (warp - 2) * 4096;
+                    // this warp's 32 output columns x bw rows, staged as [row m][32 x bf16] in a retired operand stage (every
+                    // tile load has landed and been consumed once the accumulator is complete; a buffer per warp and chunk)
+                    // and stored as one TMA tile, which clips rows >= M and columns >= N
+                    const uint32_t buf_off = static_cast<uint32_t>((warp - 2) * 2 + h) * 4096u;
+                    uint8_t* buf           = smem_gen + buf_off;
 #pragma unroll
                     for(int j = 0; j < 64; ++j)
-                        if(j < bn)
+                        if(j < bw)
                             reinterpret_cast<__nv_bfloat16*>(buf)[j * 32 + lane] = __float2bfloat16_rn(v[j]);
                     fence_proxy_async_smem();
                     __syncwarp();
                     const int p_warp0 = row_p0 + quarter * 32;
                     if(lane == 0 && p_warp0 < prm.rows_p)
                     {
-                        tma_store_2d(&map_out, smem_base + (warp - 2) * 4096, p_warp0 * 2, row_q0);
+                        tma_store_2d(&map_out, smem_base + buf_off, p_warp0 * 2, row_q0 + c0);
                         bulk_commit_group();
                         bulk_wait_group_read<0>(); // the store has read its source before the CTA retires
                     }
@@ -599,10 +650,11 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_const
                     // dependent launch waits for that)
 #pragma unroll
                     for(int j = 0; j < 64; ++j)
-                        if(j < bn && row_q0 + j < prm.rows_q)
-                            prm.out[static_cast<size_t>(row_q0 + j) * prm.ldo + p] = __float2bfloat16_rn(v[j]);
+                        if(j < bw && row_q0 + c0 + j < prm.rows_q)
+                            prm.out[static_cast<size_t>(row_q0 + c0 + j) * prm.ldo + p] = __float2bfloat16_rn(v[j]);
                 }
             }
+            } // chunks of 64 columns
         }
         B200_TRACE(if(lane == 0) stamp(46 + (warp - 2));)
         tc_fence_before_sync();

@@ -622,13 +622,14 @@ struct DecodeLayout
     uint32_t stage_bytes, q_off, sfp_off, sfq_off, cook_off, stg_off, red_off, bar_off, total;
 };
 
-static DecodeLayout make_decode_layout(int bn, int stages, int csplit, bool scaled, bool cook, bool mixed)
+// scaled: raw scale bytes per 32-row group per K tile in units of 256 (decode_sf_unit)
+static DecodeLayout make_decode_layout(int bn, int stages, int csplit, int scaled, bool cook, bool mixed)
 {
     DecodeLayout L;
     L.q_off       = kTileP * kTileKBytes;
     L.sfp_off     = L.q_off + static_cast<uint32_t>(bn) * kTileKBytes;
-    L.sfq_off     = L.sfp_off + (scaled ? 1024u : 0u);
-    L.cook_off    = L.sfq_off + (scaled ? 1024u : 0u); // re-ordered scales: 2 sides x up to 2 K atoms x 512 bytes
+    L.sfq_off     = L.sfp_off + 1024u * static_cast<uint32_t>(scaled);
+    L.cook_off    = L.sfq_off + 1024u * static_cast<uint32_t>(scaled); // re-ordered scales: 2 sides x up to 2 K atoms x 512 bytes
     L.stg_off     = L.cook_off + (cook ? 2048u : 0u);      // mixed kind: the packed e2m1 weight tile, 128 rows x 64 bytes
     L.stage_bytes = L.stg_off + (mixed ? kTileP * 64u : 0u);
     L.red_off     = L.stage_bytes * static_cast<uint32_t>(stages);
@@ -673,10 +674,12 @@ static void launch_decode_instance(int ctas, int tiles_q, int csplit, size_t sme
 static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, int kkind, DeviceState& st)
 {
     const int named_stages = prob.cfg.stages; // what the caller's configuration asked for (0: this kernel's own choice)
-    // one tile of activation rows, or up to four tiles of 64 (each a CTA of its own on the same weight tile)
+    // one tile of activation rows, or up to four tiles of 64 / two of 128 (each a CTA of its own on the same weight tile);
+    // a 128-column tile named with more than four stages stays with the persistent kernel
     const int tiles_q = static_cast<int>((prob.M + cfg.bn - 1) / std::max(cfg.bn, 1));
-    if(decode_kernel_disabled() || !cfg.swap || cfg.cg != 1 || cfg.bn > 64 || (tiles_q > 1 && (cfg.bn != 64 || tiles_q > 4)) || prob.scratch != nullptr ||
-       prob.out_mode != OUT_BF16 || prob.batch > 1 || prob.noscale || kkind == KIND_NVF4)
+    if(decode_kernel_disabled() || !cfg.swap || cfg.cg != 1 || cfg.bn > 128 || cfg.bn % 16 != 0 || (cfg.bn > 64 && cfg.bn != 128) ||
+       (tiles_q > 1 && (cfg.bn < 64 || tiles_q * cfg.bn > 256)) || (cfg.bn == 128 && named_stages > 4) || prob.scratch != nullptr ||
+       prob.out_mode != OUT_BF16 || prob.batch > 1 || prob.noscale)
         return false;
     const bool mixed = (kkind == KIND_MXF8F4);
     if(mixed && decode_mixed_disabled())
@@ -697,7 +700,7 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
     int stages = 0;
     const int smem_cap = named_stages > 0 ? st.smem_optin : 110 * 1024;
     for(int s2 = std::min(named_stages > 0 ? named_stages : kDecodeMaxStages, kDecodeMaxStages); s2 >= 2; --s2)
-        if(static_cast<int>(make_decode_layout(bn, s2, csplit, scaled, cook, mixed).total) + 1024 <= smem_cap)
+        if(static_cast<int>(make_decode_layout(bn, s2, csplit, decode_sf_unit(kkind), cook, mixed).total) + 1024 <= smem_cap)
         {
             stages = s2;
             break;
@@ -705,7 +708,7 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
     if(stages == 0)
         return false;
     stages                  = std::min(stages, std::max(2, (num_k_iters + csplit - 1) / csplit));
-    const DecodeLayout L    = make_decode_layout(bn, stages, csplit, scaled, cook, mixed);
+    const DecodeLayout L    = make_decode_layout(bn, stages, csplit, decode_sf_unit(kkind), cook, mixed);
     const Operand& P        = prob.wgt;
     const Operand& Q        = prob.act;
     if(mixed)
@@ -722,19 +725,21 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
     {
         const ScaleOperand& SP = prob.wgt_sf;
         const ScaleOperand& SQ = prob.act_sf;
-        const int atoms_k      = (kkind == KIND_MXF4) ? 2 : 1;
+        const int atoms_k      = (kkind == KIND_NVF4) ? 4 : ((kkind == KIND_MXF4) ? 2 : 1);
         B200_CHECK(SP.wire == SQ.wire && SP.wire != SFW_NONE, "both scale tensors must use the same wire layout");
         sfw = SP.wire;
         B200_CHECK(sfw != SFW_E8M0_SHUFFLE || kkind == KIND_MXF4, "the e8m0_shuffle scale layout is only wired for MXFP4");
+        B200_CHECK(kkind != KIND_NVF4 || sfw == SFW_G1250, "NVFP4 scales arrive in tiles of 32 rows x 8 scales");
         const int chunk = (sfw == SFW_E8M0_SHUFFLE) ? 256 : 128 * atoms_k;
         msp = scale_map(SP, chunk, 4, "weight scales");
         msq = scale_map(SQ, chunk, (bn + 31) / 32, "activation scales");
-        const long long need_cols = (sfw == SFW_E8M0_SHUFFLE) ? (kblocks + 7) / 8 * 8 : kblocks;
+        const long long need_cols = (kkind == KIND_NVF4) ? prob.K / 16 : (sfw == SFW_E8M0_SHUFFLE) ? (kblocks + 7) / 8 * 8 : kblocks;
         B200_CHECK(SP.padded_cols >= need_cols && SQ.padded_cols >= need_cols, "scale tensors have too few columns: need ",
                    need_cols, ", got ", SP.padded_cols, " and ", SQ.padded_cols);
         B200_CHECK(SP.padded_rows >= (P.rows + 31) / 32 * 32 && SQ.padded_rows >= (Q.rows + 31) / 32 * 32, "scale tensors have too few rows");
         if(sfw == SFW_G1250)
-            B200_CHECK(kblocks % (4 * atoms_k) == 0, "K must be a multiple of ", 128 * atoms_k, " for this scale layout");
+            B200_CHECK(prob.K % (kkind == KIND_MXF8 || kkind == KIND_MXF8F4 ? 128 : 256) == 0, "K must be a multiple of ",
+                       (kkind == KIND_MXF8 || kkind == KIND_MXF8F4 ? 128 : 256), " for this scale layout");
     }
     DecodeParams prm{};
     prm.rows_p      = static_cast<int>(P.rows);
@@ -789,7 +794,7 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
         // bf16 [M][N] seen as bytes; a warp's box is its 32 output columns by the tile's bn rows
         const cuuint64_t dims[2]    = {static_cast<cuuint64_t>(prob.N) * 2, static_cast<cuuint64_t>(prob.M)};
         const cuuint64_t strides[1] = {static_cast<cuuint64_t>(prob.ldo) * 2};
-        const cuuint32_t box[2]     = {64u, static_cast<cuuint32_t>(bn)};
+        const cuuint32_t box[2]     = {64u, static_cast<cuuint32_t>(std::min(bn, 64))}; // (a 128-column tile leaves in two chunks)
         mo = encode_map(prob.out, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "output");
     }
     const int tiles_p = static_cast<int>((P.rows + kTileP - 1) / kTileP);
@@ -805,6 +810,8 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
         launch_decode_instance<KIND_MXF4, SFW_G1250>(ctas, tiles_q, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else if(kkind == KIND_MXF8F4 && sfw == SFW_G1250)
         launch_decode_instance<KIND_MXF8F4, SFW_G1250>(ctas, tiles_q, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
+    else if(kkind == KIND_NVF4 && sfw == SFW_G1250)
+        launch_decode_instance<KIND_NVF4, SFW_G1250>(ctas, tiles_q, csplit, smem, prob.stream, mp, mq, msp, msq, mo, prm);
     else
         fail("no decode kernel instance for kind ", kkind, " with scale layout ", sfw);
 #ifdef AITER_B200_TRACING

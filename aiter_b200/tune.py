@@ -102,10 +102,12 @@ def candidates(M: int, N: int, K: int, family: str):
                 for sk in splits:
                     out.append((0, 1, bn, st, sk))
     if 64 < M <= 256:
-        # the decode kernel on up to four tiles of 64 activation rows, each streaming the same weight tile
+        # the decode kernel on up to four tiles of 64 (or two of 128) activation rows, each streaming the same weight tile
         for st in (0, 3):
             for sk in [s for s in splits if s <= 2]:
                 out.append((0, 1, 64, st, sk))
+            for sk in [s for s in splits if s <= 1]:
+                out.append((0, 1, 128, st, sk))
     if M >= 64:
         for pair in (0, 1):
             for bn in (64, 128, 192, 224, 256):

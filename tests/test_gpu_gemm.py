@@ -446,10 +446,11 @@ def test_a8w8_blockscale_e8m0_scales_run_as_mxfp8(ab, M, N, K, bpre):
 # ------------------------------------------------------------------------------------------- decode kernel, several activation tiles
 @pytest.mark.parametrize("M", [65, 128, 200, 256])
 def test_decode_kernel_on_up_to_four_tiles_of_64_rows(ab, M):
-    # a 128x64 tile with the weights on the 128-row slot and a K split of at most 4 runs on the decode kernel; with more
-    # than 64 activation rows every tile of 64 is a CTA of its own on the same weight tile (ragged last tile included)
+    # a 128x64 or 128x128 tile with the weights on the 128-row slot and a K split of at most 4 runs on the decode kernel;
+    # with more activation rows than the tile is wide every tile is a CTA of its own on the same weight tile (ragged last
+    # tile included); a 128-column tile leaves the epilogue in two chunks of 64 columns
     N, K = 640, 1024
-    for name in ("tc5_128x64_t_s0_k0", "tc5_128x64_t_s3_k1", "tc5_128x64_t_s0_k2"):
+    for name in ("tc5_128x64_t_s0_k0", "tc5_128x64_t_s3_k1", "tc5_128x64_t_s0_k2", "tc5_128x128_t_s0_k0", "tc5_128x128_t_s2_k1"):
         apre = 1 if M % 2 == 0 else 0  # the (m/2,k/128,2,128) activation tiling needs an even row count
         ref, args = mxfp8_case(ab, M, N, K, apre, seed=M)
         check(ref, ab.gemm_a8w8_mxfp8(*args, a_preshuffle=bool(apre), kernelName=name), what=f"mxfp8 {M} rows {name}")

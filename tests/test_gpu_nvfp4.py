@@ -51,7 +51,10 @@ def _operands(ab, xq, wq, xs, ws, apre):
 @pytest.mark.parametrize("M,N,K,apre,name", [
     (32, 128, 256, 0, ""), (1, 256, 512, 0, ""), (20, 384, 768, 0, ""), (192, 384, 512, 1, ""), (512, 1024, 1024, 1, ""),
     (64, 512, 2048, 0, "tc5_128x64_t_s4_k2"),   # weights on the 128-row slot, K split over a cluster
-    (16, 256, 4096, 0, "tc5_128x16_t_s0_k3"),
+    (16, 256, 4096, 0, "tc5_128x16_t_s0_k3"),   # (eight slices: the persistent kernel)
+    (8, 640, 2048, 0, "tc5_128x16_t_s3_k2"),    # decode kernel
+    (200, 384, 512, 0, "tc5_128x64_t_s0_k1"),   # decode kernel, four tiles of 64 rows, ragged
+    (256, 256, 1024, 1, "tc5_128x128_t_s0_k0"), # decode kernel, two tiles of 128 rows
     (300, 640, 512, 0, "tc5_128x128_n_s0"),     # ragged rows and a ragged last tile
     (300, 640, 1024, 0, "tc5_128x64_n_s3_k1"),  # workspace K split
     (1024, 768, 512, 1, "tc5_256x256_n_s0"),    # CTA pair
