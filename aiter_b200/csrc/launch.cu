@@ -829,14 +829,16 @@ constexpr long long kWidenPrepassMinM = 512;
 // memory on every K tile; re-laying both scale tensors once into the (m/32,k/4,32,4) order (a few MB) lets the
 // main loop run the cheaper path.
 constexpr long long kScalePrepassMinM = 1024;
-constexpr long long kScalePrepassMinK = 4096; // the two extra launches (~6 us) must be won back over the K loop
+constexpr long long kScalePrepassMinK = 4096; // the two extra launches (~6 us) must be won back over the K loop ...
+constexpr long long kScalePrepassTallM = 8192; // ... which from this many rows on they are at any K >= 1024 (16384x7168x2048: 142 -> 133 us)
 
 void launch_gemm(const GemmProblem& prob)
 {
     if(prob.M == 0 && prob.N > 0 && prob.K > 0)
         return; // no activation rows: nothing to compute, the (empty) output is already complete
     if(prob.kind == PK_MXFP4 && prob.M >= kScalePrepassMinM && prob.scratch == nullptr && prob.act_sf.wire == SFW_E8M0_SHUFFLE &&
-       prob.wgt_sf.wire == SFW_E8M0_SHUFFLE && prob.K % 256 == 0 && prob.K >= kScalePrepassMinK && !relay_prepass_disabled())
+       prob.wgt_sf.wire == SFW_E8M0_SHUFFLE && prob.K % 256 == 0 && prob.K >= (prob.M >= kScalePrepassTallM ? 1024 : kScalePrepassMinK) &&
+       !relay_prepass_disabled())
     {
         int prev_dev = 0;
         B200_CUDA(cudaGetDevice(&prev_dev));
