@@ -330,6 +330,7 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
         cfg.swap = (M <= 64) ? 1 : 0;
     const long long rows_q = cfg.swap ? M : N;
     const long long rows_p = cfg.swap ? N : M;
+    const bool bn_was_open = (cfg.bn <= 0);
     if(cfg.bn <= 0)
     {
         if(cfg.swap)
@@ -346,6 +347,13 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
                 cfg.bn = rows_q <= 16 ? 16 : rows_q <= 32 ? 32 : rows_q <= 64 ? 64 : rows_q <= 128 ? 128 : 256;
         }
     }
+    // Tall 4-bit problems with a short K: a 256 x 256 tile has TMEM for one accumulator only, so every tile's epilogue
+    // (~3.6 k cycles) is exposed, a third of a tile's time at K = 1536; 192 columns leave room for two accumulators and
+    // the epilogue runs under the next tile's main loop (tuner: 16384 x 24576 x 1536 355 -> 326 us, 16384 x 7168 x 2048
+    // 140 -> 123 us).  From 8192 rows on, where the library re-lays e8m0_shuffle scales once per call; below that the
+    // scale warps' in-kernel transpose bounds the main loop either way.
+    if(bn_was_open && !cfg.swap && cfg.bn == 256 && (kind == PK_MXFP4 || kind == PK_NVFP4) && rows_p >= 8192 && K <= 2560)
+        cfg.bn = 192;
     if(cfg.cg <= 0)
     {
         // a CTA pair halves the Q bytes each SM stages per flop; worth it once there are enough 256-row tiles

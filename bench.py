@@ -154,6 +154,8 @@ def algorithmic_bytes(kind, M, N, K):
         return M * K + N * K + (M + N) * K // 32 + 2 * M * N
     if kind == "mxfp4":
         return (M * K + N * K) // 2 + (M + N) * K // 32 + 2 * M * N
+    if kind == "nvfp4":
+        return (M * K + N * K) // 2 + (M + N) * K // 16 + 2 * M * N
     return M * K + N * K // 2 + (M + N) * K // 32 + 2 * M * N
 
 
@@ -240,7 +242,7 @@ def kernel_in_use(ab, kind, M, N, K):
         name = str(row["kernelName"])
         split = row.get("splitK")
         return name if "_k" in name or not split else f"{name}_k{int(split)}"
-    return ab.heuristic_name({"bf16": 0, "mxfp8": 1, "mxfp4": 2, "a8w4": 3}[kind], M, N, K)[0]
+    return ab.heuristic_name({"bf16": 0, "mxfp8": 1, "mxfp4": 2, "a8w4": 3, "nvfp4": 4}[kind], M, N, K)[0]
 
 
 def rotating_sets(make, bytes_per_set, l2_bytes=126e6):
@@ -322,7 +324,7 @@ def run_sweep(torch, ab, device, peaks):
             us, mhz = graph_time_calls(torch, fn, sets, 20, 3, clock_of=gpu_index)
             tf = 2.0 * M * N * K / us / 1e6
             gbs = b / us / 1e3
-            peak_tf = peaks["bf16"] * {"bf16": 1, "mxfp8": 2, "a8w4": 2, "mxfp4": 4}[kind]
+            peak_tf = peaks["bf16"] * {"bf16": 1, "mxfp8": 2, "a8w4": 2, "mxfp4": 4, "nvfp4": 4}[kind]
             return {"kind": kind, "M": M, "N": N, "K": K, "us": round(us, 2), "tflops": round(tf, 1), "gbs": round(gbs, 1),
                     "frac_tensor": round(tf / peak_tf, 4), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4),
                     "kernel": kernel_in_use(ab, kind, M, N, K), **clock_fields(us, mhz)}
@@ -350,13 +352,19 @@ def run_sweep(torch, ab, device, peaks):
     # the 8-GPU shard of the headline workload
     add("mxfp4", 16384, 7168, 7168, lambda a, b, sa, sb: ab.gemm_a4w4(a, b, sa, sb),
         lambda i: (rand_u8(0, 256, 16384, 3584), rand_u8(0, 256, 7168, 3584), rand_u8(120, 130, 16384, 224), rand_u8(120, 130, 7168, 224)))
+    # NVFP4 inputs of the same entry-point family (e4m3 scales per 16, per-tensor factors): a decode and a tall shape
+    for M in (1, 16384):
+        rows_a = (M + 31) // 32 * 32
+        add("nvfp4", M, 7168, 7168, lambda a, b, sa, sb: ab.gemm_nvfp4_asm(a, b, sa, sb, 0.75, 1.25, a_preshuffle=False),
+            lambda i, M=M, rows_a=rows_a: (rand_u8(0, 256, M, 3584), rand_u8(0, 256, 7168, 3584),
+                                           rand_u8(0x28, 0x40, rows_a, 448), rand_u8(0x28, 0x40, 7168, 448)))
     # MXFP8 activations x MXFP4 weights, N = K = 8192
     for M in (1, 16, 128, 1024, 4096, 16384):
         add("a8w4", M, 8192, 8192, lambda a, b, sa, sb: ab.gemm_a8w4_mxfp8(a, b, sa, sb, a_preshuffle=False),
             lambda i, M=M: (rand_u8(0, 0x78, M, 8192).view(torch.float8_e4m3fn), rand_u8(0, 256, 8192, 4096),
                             rand_u8(120, 130, (M + 31) // 32 * 32, 256), rand_u8(120, 130, 8192, 256)))
     # FP8 with 128-block scales, N = K = 4096: fp32 scales (promotion kernel) and e8m0 scales (MXFP8 kernel)
-    for M in (16, 1024, 8192):
+    for M in (16, 128, 1024, 8192):
         for tag, mk in (("blockscale_fp32", lambda M: (torch.rand(M, 32, device=device) + 0.5, torch.rand(32, 32, device=device) + 0.5)),
                         ("blockscale_e8m0", lambda M: (rand_u8(124, 130, M, 32).view(ab.dtypes.fp8_e8m0), rand_u8(124, 130, 32, 32).view(ab.dtypes.fp8_e8m0)))):
             def job(M=M, tag=tag, mk=mk):
@@ -368,8 +376,8 @@ def run_sweep(torch, ab, device, peaks):
                 return {"kind": tag, "M": M, "N": 4096, "K": 4096, "us": round(us, 2), "tflops": round(tf, 1),
                         "gbs": round(algorithmic_bytes("mxfp8", M, 4096, 4096) / us / 1e3, 1), "frac_tensor": round(tf / (2 * peaks["bf16"]), 4),
                         "frac_hbm": round(algorithmic_bytes("mxfp8", M, 4096, 4096) / us / 1e3 / peaks["hbm_gbs"], 4),
-                        "kernel": "gemm_a8w8_blockscale" + ("_fewrows_kernel" if M <= 64 else "_pair_kernel" if tag.endswith("fp32") and M > 128
-                                                            else "_kernel" if tag.endswith("fp32") else " -> mxfp8"), **clock_fields(us, mhz)}
+                        "kernel": "gemm_a8w8_blockscale" + ("_fewrows_kernel" if M <= 128 else "_pair_kernel" if tag.endswith("fp32")
+                                                            else " -> mxfp8"), **clock_fields(us, mhz)}
 
             jobs.append((2.0 * M * 4096 * 4096, job))
     # fused activation quantiser (bf16 -> MX data + scales in the GEMM's layout): HBM-bound
