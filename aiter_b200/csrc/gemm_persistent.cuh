@@ -1268,14 +1268,30 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_c
                         const int q_first = row_q0 + c * 64;
                         if(epi_math)
                         {
-                            const float bp = (bias_b != nullptr && !prm.bias_on_q && p < prm.rows_p) ? load_bias(bias_b, prm.bias_is_bf16, p) : 0.f;
-#pragma unroll
-                            for(int j = 0; j < 64; ++j)
+                            // three plain loops (a per-element test of the bias form inside one loop cost 17 % of a
+                            // 16384 x 7168 x 7168 NVFP4 GEMM, whose per-tensor factors arrive as alpha)
+                            const float al = prm.alpha;
+                            if(bias_b == nullptr)
                             {
-                                float b = bp;
-                                if(bias_b != nullptr && prm.bias_on_q)
-                                    b = (q_first + j < prm.rows_q) ? load_bias(bias_b, prm.bias_is_bf16, q_first + j) : 0.f;
-                                r[j] = __float_as_uint(prm.alpha * __uint_as_float(r[j]) + prm.beta * b);
+#pragma unroll
+                                for(int j = 0; j < 64; ++j)
+                                    r[j] = __float_as_uint(al * __uint_as_float(r[j]));
+                            }
+                            else if(!prm.bias_on_q)
+                            {
+                                const float bb = prm.beta * ((p < prm.rows_p) ? load_bias(bias_b, prm.bias_is_bf16, p) : 0.f);
+#pragma unroll
+                                for(int j = 0; j < 64; ++j)
+                                    r[j] = __float_as_uint(al * __uint_as_float(r[j]) + bb);
+                            }
+                            else
+                            {
+#pragma unroll
+                                for(int j = 0; j < 64; ++j)
+                                {
+                                    const float b = (q_first + j < prm.rows_q) ? load_bias(bias_b, prm.bias_is_bf16, q_first + j) : 0.f;
+                                    r[j] = __float_as_uint(al * __uint_as_float(r[j]) + prm.beta * b);
+                                }
                             }
                         }
                         // the store that last used this buffer has read it (the previous store with one buffer, the one

@@ -14,7 +14,8 @@ checks 64 rows x 4096 columns of its output against the CPU oracle.
 `value` is whole-job TFLOP/s with inputs resident in HBM; `e2e` is the same metric through the operator call
 with pinned HOST buffers for the step's activations, their scales and the output shard (the weight, a model
 parameter, stays resident).  The optional NCCL all-gather of the bf16 output shards is timed apart
-(`allgather`).  `sweep` adds the per-M figures of the other configurations.
+(`allgather`).  `sweep` adds the per-M figures of the other configurations, each sustained (`us`, with the SM clock
+seen) and, for the large cases, in a short burst from an idle GPU (`us_burst`).
 
 `--impl reference` times the reference's CPU path (dequantise to fp32 -> matmul -> bf16; the torch-on-CPU
 restatement under oracle/) on the host cores, on a bounded slice of the same workload.
@@ -191,10 +192,13 @@ def sm_clock_mhz(index):
         return None
 
 
-def graph_time_calls(torch, fn, arg_sets, iters, warmup, clock_of=None):
+def graph_time_calls(torch, fn, arg_sets, iters, warmup, clock_of=None, burst=False):
     """Same, but the calls are replayed from one CUDA graph so that host launch cost does not hide
     the device time of microsecond-sized kernels.  With `clock_of` (a GPU index) the graph is replayed for a
-    further ~20 ms after the timed replay and the SM clock is read from NVML while that runs: -> (us, MHz)."""
+    further ~20 ms after the timed replay and the SM clock is read from NVML while that runs: -> (us, MHz).
+    With `burst` a case of 50 us or more per call is timed once more after 0.4 s of idle, one replay from a GPU that
+    is back at its full clock: -> (us, MHz, us_burst); the first figure is what the GPU sustains under its power cap
+    (the clock beside it says how far that pulled it down), the second what the same kernel does in a short burst."""
     n = len(arg_sets)
     torch.cuda.synchronize()
     s = torch.cuda.Stream()
@@ -223,6 +227,18 @@ def graph_time_calls(torch, fn, arg_sets, iters, warmup, clock_of=None):
         for _ in range(max(1, min(2000, int(20000.0 / max(us * iters, 1.0))))):
             g.replay()
         mhz = sm_clock_mhz(clock_of)
+        if burst:
+            us_burst = None
+            if us >= 50.0:
+                torch.cuda.synchronize()
+                time.sleep(0.4)
+                b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                b0.record(s)
+                g.replay()
+                b1.record(s)
+                torch.cuda.synchronize()
+                us_burst = b0.elapsed_time(b1) * 1e3 / iters
+            return us, mhz, us_burst
     torch.cuda.synchronize()
     return us, mhz
 
@@ -321,13 +337,16 @@ def run_sweep(torch, ab, device, peaks):
         def job():
             b = algorithmic_bytes(kind, M, N, K)
             sets = rotating_sets(make, b)
-            us, mhz = graph_time_calls(torch, fn, sets, 20, 3, clock_of=gpu_index)
+            us, mhz, us_burst = graph_time_calls(torch, fn, sets, 20, 3, clock_of=gpu_index, burst=True)
             tf = 2.0 * M * N * K / us / 1e6
             gbs = b / us / 1e3
             peak_tf = peaks["bf16"] * {"bf16": 1, "mxfp8": 2, "a8w4": 2, "mxfp4": 4, "nvfp4": 4}[kind]
-            return {"kind": kind, "M": M, "N": N, "K": K, "us": round(us, 2), "tflops": round(tf, 1), "gbs": round(gbs, 1),
-                    "frac_tensor": round(tf / peak_tf, 4), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4),
-                    "kernel": kernel_in_use(ab, kind, M, N, K), **clock_fields(us, mhz)}
+            row = {"kind": kind, "M": M, "N": N, "K": K, "us": round(us, 2), "tflops": round(tf, 1), "gbs": round(gbs, 1),
+                   "frac_tensor": round(tf / peak_tf, 4), "frac_hbm": round(gbs / peaks["hbm_gbs"], 4),
+                   "kernel": kernel_in_use(ab, kind, M, N, K), **clock_fields(us, mhz)}
+            if us_burst is not None:
+                row["us_burst"], row["tflops_burst"] = round(us_burst, 2), round(2.0 * M * N * K / us_burst / 1e6, 1)
+            return row
 
         jobs.append((2.0 * M * N * K, job))
 
@@ -371,9 +390,11 @@ def run_sweep(torch, ab, device, peaks):
                 sets = rotating_sets(lambda i: (rand_u8(0, 0x78, M, 4096).view(torch.float8_e4m3fn),
                                                 rand_u8(0, 0x78, 4096, 4096).view(torch.float8_e4m3fn), *mk(M)),
                                      algorithmic_bytes("mxfp8", M, 4096, 4096))
-                us, mhz = graph_time_calls(torch, lambda a, b, xs, ws: ab.gemm_a8w8_blockscale(a, b, xs, ws), sets, 20, 3, clock_of=gpu_index)
+                us, mhz, us_burst = graph_time_calls(torch, lambda a, b, xs, ws: ab.gemm_a8w8_blockscale(a, b, xs, ws), sets, 20, 3,
+                                                     clock_of=gpu_index, burst=True)
                 tf = 2.0 * M * 4096 * 4096 / us / 1e6
-                return {"kind": tag, "M": M, "N": 4096, "K": 4096, "us": round(us, 2), "tflops": round(tf, 1),
+                extra = {} if us_burst is None else {"us_burst": round(us_burst, 2), "tflops_burst": round(2.0 * M * 4096 * 4096 / us_burst / 1e6, 1)}
+                return {**extra, "kind": tag, "M": M, "N": 4096, "K": 4096, "us": round(us, 2), "tflops": round(tf, 1),
                         "gbs": round(algorithmic_bytes("mxfp8", M, 4096, 4096) / us / 1e3, 1), "frac_tensor": round(tf / (2 * peaks["bf16"]), 4),
                         "frac_hbm": round(algorithmic_bytes("mxfp8", M, 4096, 4096) / us / 1e3 / peaks["hbm_gbs"], 4),
                         "kernel": "gemm_a8w8_blockscale" + ("_fewrows_kernel" if M <= 128 else "_pair_kernel" if tag.endswith("fp32")
@@ -711,6 +732,9 @@ def run_ours(args, rank, world, local_rank):
                                  "note": "NCCL all_gather_into_tensor of the bf16 output shards over NVLink, not part of `value`"}
         if sweep is not None:
             line["sweep"] = sweep
+            line["sweep_method"] = ("CUDA-graph replay of 20 calls over rotating buffers larger than L2; `us` after ~40 earlier calls, "
+                                    "back to back with the case before it (what the GPU sustains under its 1 kW power cap; `sm_mhz` is the "
+                                    "clock read while it runs), `us_burst` (cases of 50 us or more) one replay after 0.4 s of idle")
         print(json.dumps(line))
     if dist is not None:
         dist.barrier()
