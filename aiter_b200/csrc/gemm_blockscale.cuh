@@ -115,6 +115,10 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
+    // programmatic dependent launch: the set-up above may overlap the previous kernel's tail; nothing below touches
+    // global memory before that kernel has completed
+    grid_dependency_wait();
+    grid_launch_dependents();
 
     if(warp == 0 || warp == 7)
     {
@@ -760,6 +764,9 @@ gemm_a8w8_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
     cluster_sync_all();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
+    // programmatic dependent launch (see the 128 x 128 kernel)
+    grid_dependency_wait();
+    grid_launch_dependents();
 
     if(warp == 0)
     {

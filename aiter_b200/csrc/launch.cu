@@ -1489,13 +1489,15 @@ void launch_blockscale(const BlockScaleProblem& prob)
         lc.blockDim         = dim3(kBlockScalePairThreads, 1, 1);
         lc.dynamicSmemBytes = smem;
         lc.stream           = prob.stream;
-        cudaLaunchAttribute attr[1];
+        cudaLaunchAttribute attr[2];
         attr[0].id               = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = 2;
         attr[0].val.clusterDim.y = 1;
         attr[0].val.clusterDim.z = 1;
+        attr[1].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
         lc.attrs    = attr;
-        lc.numAttrs = 1;
+        lc.numAttrs = pdl_disabled() ? 1 : 2;
         B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_pair_kernel, ma, mb, prm));
     }
     else if(want_few)
@@ -1630,7 +1632,19 @@ void launch_blockscale(const BlockScaleProblem& prob)
             splits = 1;
         prm.splits = splits;
         grid.z     = static_cast<unsigned>(splits);
-        gemm_a8w8_blockscale_kernel<<<grid, kBlockScaleThreads, smem, prob.stream>>>(ma, mb, prm);
+        {
+            cudaLaunchConfig_t lc{};
+            lc.gridDim          = grid;
+            lc.blockDim         = dim3(kBlockScaleThreads, 1, 1);
+            lc.dynamicSmemBytes = smem;
+            lc.stream           = prob.stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            lc.attrs    = attr;
+            lc.numAttrs = pdl_disabled() ? 0 : 1;
+            B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_kernel, ma, mb, prm));
+        }
         B200_CUDA(cudaGetLastError());
     }
     g_launches.fetch_add(1);
