@@ -193,6 +193,23 @@ def test_mxfp4_alpha_bias(ab):
     assert_healthy(ab)
 
 
+@pytest.mark.parametrize("M,name", [(300, "tc5_128x128_n_s0"), (1024, "tc5_256x256_n_s0"), (700, "tc5_128x64_n_s3"), (200, "tc5_128x32_n_s3")])
+def test_mxfp4_alpha_bias_on_row_major_tiles(ab, M, name):
+    # the wide (64 columns per step) and narrow epilogues of tiles that keep the activations on the 128-row slot: alpha
+    # alone, and alpha with a bias per output column
+    N, K = 512, 512
+    ref, xq, wq, xs, ws = mxfp4_case(ab, M, N, K, seed=M)
+    args = (to_cuda_u8(xq), ab.shuffle_weight(to_cuda_u8(wq)), ab.fp4_utils.e8m0_shuffle(to_cuda_u8(xs)), ab.fp4_utils.e8m0_shuffle(to_cuda_u8(ws)))
+    bias = torch.randn(1, N, generator=torch.Generator().manual_seed(4))
+    base = ox.bf16_bits_to_f32(ref)
+    out = torch.full(((M + 31) // 32 * 32, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ab.gemm_a4w4_asm(*args, out, name, None, 0.25, 0.0, True)
+    check(ox.f32_to_bf16_bits((0.25 * base).astype(np.float32)), out[:M], rtol=2e-2, atol=2e-2, what=f"alpha only, {name}")
+    ab.gemm_a4w4_asm(*args, out, name, bias.cuda(), 0.5, 2.0, True)
+    check(ox.f32_to_bf16_bits((0.5 * base + 2.0 * bias.numpy()).astype(np.float32)), out[:M], rtol=2e-2, atol=2e-2, what=f"alpha, beta, bias, {name}")
+    assert_healthy(ab)
+
+
 def test_mxfp4_g1250_scale_layout(ab):
     M, N, K = 64, 512, 1024
     ref, xq, wq, xs, ws = mxfp4_case(ab, M, N, K, seed=11)
