@@ -112,7 +112,9 @@ __host__ __device__ inline PersistentSmem make_persistent_smem(int bn, int cg, i
     L.stage_bytes    = L.stg_off + stg;
     L.epi_off        = L.stage_bytes * static_cast<uint32_t>(stages);
     L.red_off        = L.epi_off + static_cast<uint32_t>(epi_stage) * kEpiStageBytes;
-    L.bar_off        = L.red_off + (csplit > 1 ? static_cast<uint32_t>(csplit - 1) * static_cast<uint32_t>(bn) * kTileP * 4u : 0u);
+    // up to four slices: every CTA receives the other slices' share of its own 128 / csplit rows; eight: the first CTA all
+    const uint32_t red_rows = csplit <= 1 ? 0u : static_cast<uint32_t>(csplit - 1) * (csplit <= 4 ? static_cast<uint32_t>(kTileP / csplit) : static_cast<uint32_t>(kTileP));
+    L.bar_off        = L.red_off + red_rows * static_cast<uint32_t>(bn) * 4u;
     L.total          = L.bar_off + 512u;
     return L;
 }

@@ -1084,6 +1084,8 @@ static void launch_gemm_locked(const GemmProblem& prob)
     // Decode shapes: the K split runs across the CTAs of a thread-block cluster, one output tile per cluster; the
     // partial accumulators meet in the first CTA's shared memory instead of a global workspace.
     int csplit = 1;
+    // (only with the weights on the 128-row slot: for row-major tiles, whose partial tiles are wide, it was measured two to
+    // five times slower than the workspace split)
     if(cfg.swap && cg == 1 && splits > 1 && splits <= 8 && prob.scratch == nullptr && !cluster_split_disabled() &&
        max_stages(cfg.bn, cg, st.smem_optin, f4_operand, sf_unit, tma_store, splits) >= 4)
     {
