@@ -1467,8 +1467,12 @@ void launch_blockscale(const BlockScaleProblem& prob)
     const long long pair_cost   = (pairs256 + st.sm_count / 2 - 1) / (st.sm_count / 2) * 1300;
     B200_CHECK(prob.variant != 1 || few_rows_can_serve(prob), "bs_fewrows serves at most 256 activation rows");
     B200_CHECK(prob.variant != 3 || prob.M > kTileP, "bs_256x256 needs more than 128 activation rows");
-    const bool want_pair = prob.variant == 3 || (prob.variant == 0 && prob.M > kTileP && pair_cost < single_cost);
-    const bool want_few  = prob.variant == 1 || (prob.variant == 0 && use_few_rows(prob));
+    // 65..256 rows: tiles of 64 rows on the few-rows kernel while all of them fit the machine at once (measured against the
+    // 128 x 128 kernel: 256 x 4096 x 4096 15.1 -> 13.3 us, 96 x 4096 x 4096 14.1 -> 10.4 us, 200 x 1536 x 7168 16.3 -> 13.5 us;
+    // with more tiles than SMs it loses: 256 x 7168 x 2048 10.7 -> 15.7 us)
+    const long long few_tiles = ((prob.N + kBsTileN - 1) / kBsTileN) * ((prob.M + 63) / 64);
+    const bool want_few  = prob.variant == 1 || (prob.variant == 0 && (use_few_rows(prob) || (few_rows_can_serve(prob) && few_tiles <= st.sm_count)));
+    const bool want_pair = prob.variant == 3 || (prob.variant == 0 && !want_few && prob.M > kTileP && pair_cost < single_cost);
     const int forced_splits = prob.log2_splitk >= 0 ? (1 << prob.log2_splitk) : 0; // 0: the cost model below decides
     if(want_pair)
     {
