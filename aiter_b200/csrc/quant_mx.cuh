@@ -50,6 +50,30 @@ __device__ __forceinline__ float to_f32<__half>(__half v)
     return __half2float(v);
 }
 
+// Largest magnitude of eight 16-bit floats (bf16 or fp16) as its bit pattern: for non-negative floats the integer order of
+// the patterns is the order of the values, infinity sorts above every finite value and NaN above infinity, so the
+// unsigned maximum of the sign-less patterns IS the maximum, with a NaN surviving by itself (fmaxf would drop it).
+// Two values per instruction (unsigned halfword maximum).
+__device__ __forceinline__ uint32_t amax_bits16x8(const uint4& raw)
+{
+    const uint32_t a = __vmaxu2(raw.x & 0x7FFF7FFFu, raw.y & 0x7FFF7FFFu);
+    const uint32_t b = __vmaxu2(raw.z & 0x7FFF7FFFu, raw.w & 0x7FFF7FFFu);
+    const uint32_t c = __vmaxu2(a, b);
+    return max(c & 0xFFFFu, c >> 16);
+}
+template <typename T>
+__device__ __forceinline__ float bits16_to_f32(uint32_t bits);
+template <>
+__device__ __forceinline__ float bits16_to_f32<__nv_bfloat16>(uint32_t bits)
+{
+    return __uint_as_float(bits << 16);
+}
+template <>
+__device__ __forceinline__ float bits16_to_f32<__half>(uint32_t bits)
+{
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(bits)));
+}
+
 // SMALL (few tiles, e.g. a decode batch): the eight warps of a CTA share ONE tile, four rows each, so that every load
 // of the tile is in flight at once and the kernel lasts about one memory round trip instead of eight.
 template <typename T, bool FP4, bool SMALL>
@@ -107,24 +131,14 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const QuantParams prm)
             const bool ok       = blk_ok && row < prm.M;
             const T* e = reinterpret_cast<const T*>(&raw);
             float v[8];
-            float amax = 0.f;
 #pragma unroll
             for(int i = 0; i < 8; ++i)
-            {
                 v[i] = to_f32<T>(e[i]);
-                amax = fmaxf(amax, fabsf(v[i]));
-            }
-            // NaN must survive the maximum (fmaxf drops it): carry it separately
-            bool has_nan = false;
-#pragma unroll
-            for(int i = 0; i < 8; ++i)
-                has_nan |= (v[i] != v[i]);
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-            has_nan |= __shfl_xor_sync(0xffffffffu, has_nan ? 1 : 0, 1) != 0;
-            has_nan |= __shfl_xor_sync(0xffffffffu, has_nan ? 1 : 0, 2) != 0;
-            if(has_nan)
-                amax = __uint_as_float(0x7FC00000u);
+            // the block's largest magnitude, NaN included, on the 16-bit patterns; the four lanes of a block share it
+            uint32_t ab = amax_bits16x8(raw);
+            ab          = max(ab, __shfl_xor_sync(0xffffffffu, ab, 1));
+            ab          = max(ab, __shfl_xor_sync(0xffffffffu, ab, 2));
+            const float amax  = bits16_to_f32<T>(ab);
             const uint32_t qb = __float_as_uint(__fdiv_rn(amax, max_pos));
             const uint32_t ex = (qb >> 23) & 0xFFu;
             const uint32_t byte = ex + (((qb & 0x7FFFFFu) != 0u && ex < 0xFFu) ? 1u : 0u);
