@@ -268,7 +268,7 @@ def rotating_sets(make, bytes_per_set, l2_bytes=126e6):
 
 # --------------------------------------------------------------------------------------- sweep
 def run_case(torch, ab, device, spec, steps, warmup):
-    """Profiling aid: one sweep case, `kind:M:N:K` with kind in mxfp8 / mxfp4 / a8w4 / bf16 / blockscale_fp32 /
+    """Profiling aid: one sweep case, `kind:M:N:K` with kind in mxfp8 / mxfp4 / nvfp4 / a8w4 / bf16 / blockscale_fp32 /
     blockscale_e8m0 / quant_mxfp4 / quant_mxfp8 (N ignored for the quantiser), launched `steps` times on the current stream; prints one JSON line."""
     kind, M, N, K = spec.split(":")
     M, N, K = int(M), int(N), int(K)
@@ -285,6 +285,10 @@ def run_case(torch, ab, device, spec, steps, warmup):
         args = (rand_u8(0, 256, M, K // 2), rand_u8(0, 256, N, K // 2), rand_u8(120, 130, (M + 255) // 256 * 256, kb),
                 rand_u8(120, 130, (N + 255) // 256 * 256, kb))
         fn = lambda a, b, sa, sb: ab.gemm_a4w4(a, b, sa, sb)  # noqa: E731
+    elif kind == "nvfp4":
+        args = (rand_u8(0, 256, M, K // 2), rand_u8(0, 256, N, K // 2), rand_u8(0x28, 0x40, (M + 31) // 32 * 32, K // 16),
+                rand_u8(0x28, 0x40, (N + 31) // 32 * 32, K // 16))
+        fn = lambda a, b, sa, sb: ab.gemm_nvfp4_asm(a, b, sa, sb, 0.75, 1.25, a_preshuffle=False)  # noqa: E731
     elif kind == "a8w4":
         args = (rand_u8(0, 0x78, M, K).view(torch.float8_e4m3fn), rand_u8(0, 256, N, K // 2),
                 rand_u8(120, 130, (M + 31) // 32 * 32, K // 32), rand_u8(120, 130, N, K // 32))
