@@ -53,7 +53,7 @@ def torch_to_aiter(t: torch.Tensor) -> aiter_tensor_t:
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m aiter_b200.build` (needs nvcc). "
+            f"{LIB_PATH} is missing: build it with `python aiter_b200/build.py` (needs nvcc). "
             "aiter_b200 has no CPU or PyTorch fallback."
         )
     return ctypes.CDLL(LIB_PATH)

@@ -1,4 +1,4 @@
-"""Ahead-of-time build of the CUDA library (sm_100a only).  `python -m aiter_b200.build`."""
+"""Ahead-of-time build of the CUDA library (sm_100a only).  `python aiter_b200/build.py` (run as a script: importing the package needs the library it produces)."""
 from __future__ import annotations
 
 import os
