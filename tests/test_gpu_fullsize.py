@@ -77,6 +77,27 @@ def test_a8w4_full_size(ab):
     assert ab.device_status(0) == (0, 0, 0, 0)
 
 
+def test_nvfp4_full_size(ab):
+    # the 8-GPU shard shape with NVFP4 inputs: random codes, e4m3 scales around 0.34, per-tensor factors; the
+    # size-independent property here is linearity in a per-tensor factor (a power of two commutes with every rounding)
+    M, N, K = 16384, 7168, 7168
+    g = torch.Generator(device="cuda").manual_seed(10)
+    xq = torch.randint(0, 256, (M, K // 2), generator=g, device="cuda", dtype=torch.uint8)
+    wq = torch.randint(0, 256, (N, K // 2), generator=g, device="cuda", dtype=torch.uint8)
+    xs = (torch.randn(M, K // 16, generator=g, device="cuda") * 0.08 + 0.34375).clamp(2.0 ** -6, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+    ws = (torch.randn(N, K // 16, generator=g, device="cuda") * 0.08 + 0.34375).clamp(2.0 ** -6, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+    A, B = ab.shuffle_weight_f4(xq), ab.shuffle_weight_f4(wq)
+    sA, sB = ab.shuffle_scale_f4(xs, 8), ab.shuffle_scale_f4(ws, 8)
+    out = ab.gemm_nvfp4_asm(A, B, sA, sB, 0.75, 1.25, a_preshuffle=True)
+    assert out.shape == (M, N)
+    rows = _rows(M, 11)
+    ref = ox.gemm_nvfp4_ref(xq[rows].cpu().numpy(), wq.cpu().numpy(), xs[rows].cpu().numpy(), ws.cpu().numpy(), 0.75, 1.25)
+    check(ref, out[rows], what=f"gemm_nvfp4_asm {M}x{N}x{K}, 64 rows")
+    out2 = ab.gemm_nvfp4_asm(A, B, sA, sB, 1.5, 1.25, a_preshuffle=True)
+    assert torch.equal(out2.float(), out.float() * 2.0)
+    assert ab.device_status(0) == (0, 0, 0, 0)
+
+
 def test_bf16_full_size(ab):
     # 8192^3: 64 rows against the oracle; property: doubling the activations doubles the output exactly
     M = N = K = 8192
