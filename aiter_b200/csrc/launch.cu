@@ -324,6 +324,11 @@ static int max_stages(int bn, int cg, int smem_limit, int f4_operand, int scaled
     return 0;
 }
 
+// A tall MXFP4 / NVFP4 problem: enough output tiles that the per-call re-layout of e8m0_shuffle scales (two small
+// launches) and the narrower two-accumulator tile pay back even at a short K.  Measured with the tuner at K = 1536 / 2048:
+// 16384 x 7168 142 -> 133 us, 4096 x 24576 98.5 -> 92.3 us; 2048 x 24576 a tie; 4096 x 7168 42.9 -> 44.1 us (not tall).
+static bool tall_problem(long long M, long long N) { return M >= 8192 || (M >= 4096 && M * N >= 8192LL * 7168); }
+
 void choose_config(int kind, long long M, long long N, long long K, int num_sms, KernelConfig& cfg)
 {
     if(cfg.swap < 0)
@@ -362,9 +367,9 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
     // Tall 4-bit problems with a short K: a 256 x 256 tile has TMEM for one accumulator only, so every tile's epilogue
     // (~3.6 k cycles) is exposed, a third of a tile's time at K = 1536; 192 columns leave room for two accumulators and
     // the epilogue runs under the next tile's main loop (tuner: 16384 x 24576 x 1536 355 -> 326 us, 16384 x 7168 x 2048
-    // 140 -> 123 us).  From 8192 rows on, where the library re-lays e8m0_shuffle scales once per call; below that the
-    // scale warps' in-kernel transpose bounds the main loop either way.
-    if(bn_was_open && !cfg.swap && cfg.bn == 256 && (kind == PK_MXFP4 || kind == PK_NVFP4) && rows_p >= 8192 && K <= 2560)
+    // 140 -> 123 us).  On tall problems only, where the library re-lays e8m0_shuffle scales once per call; below that
+    // the scale warps' in-kernel transpose bounds the main loop either way.
+    if(bn_was_open && !cfg.swap && cfg.bn == 256 && (kind == PK_MXFP4 || kind == PK_NVFP4) && tall_problem(rows_p, rows_q) && K <= 2560)
         cfg.bn = 192;
     if(cfg.cg <= 0)
     {
@@ -850,14 +855,14 @@ constexpr long long kWidenPrepassMinM = 512;
 // main loop run the cheaper path.
 constexpr long long kScalePrepassMinM = 1024;
 constexpr long long kScalePrepassMinK = 4096; // the two extra launches (~6 us) must be won back over the K loop ...
-constexpr long long kScalePrepassTallM = 8192; // ... which from this many rows on they are at any K >= 1024 (16384x7168x2048: 142 -> 133 us)
+                                              // ... which on a tall problem (tall_problem) they are at any K >= 1024
 
 void launch_gemm(const GemmProblem& prob)
 {
     if(prob.M == 0 && prob.N > 0 && prob.K > 0)
         return; // no activation rows: nothing to compute, the (empty) output is already complete
     if(prob.kind == PK_MXFP4 && prob.M >= kScalePrepassMinM && prob.scratch == nullptr && prob.act_sf.wire == SFW_E8M0_SHUFFLE &&
-       prob.wgt_sf.wire == SFW_E8M0_SHUFFLE && prob.K % 256 == 0 && prob.K >= (prob.M >= kScalePrepassTallM ? 1024 : kScalePrepassMinK) &&
+       prob.wgt_sf.wire == SFW_E8M0_SHUFFLE && prob.K % 256 == 0 && prob.K >= (tall_problem(prob.M, prob.N) ? 1024 : kScalePrepassMinK) &&
        !relay_prepass_disabled())
     {
         int prev_dev = 0;
