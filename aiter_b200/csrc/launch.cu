@@ -642,6 +642,8 @@ static bool decode_mixed_disabled()
     return off;
 }
 
+constexpr uint32_t kDecodeBarrierBytes = 256; // the decode kernel's barriers and flags (gemm_decode.cuh)
+
 struct DecodeLayout
 {
     uint32_t stage_bytes, q_off, sfp_off, sfq_off, cook_off, stg_off, red_off, bar_off, total;
@@ -651,15 +653,25 @@ struct DecodeLayout
 static DecodeLayout make_decode_layout(int bn, int stages, int csplit, int scaled, bool cook, bool mixed)
 {
     DecodeLayout L;
+    const uint32_t q_groups = static_cast<uint32_t>((bn + 31) / 32);
     L.q_off       = kTileP * kTileKBytes;
     L.sfp_off     = L.q_off + static_cast<uint32_t>(bn) * kTileKBytes;
     L.sfq_off     = L.sfp_off + 1024u * static_cast<uint32_t>(scaled);
-    L.cook_off    = L.sfq_off + 1024u * static_cast<uint32_t>(scaled); // re-ordered scales: 2 sides x up to 2 K atoms x 512 bytes
-    L.stg_off     = L.cook_off + (cook ? 2048u : 0u);      // mixed kind: the packed e2m1 weight tile, 128 rows x 64 bytes
-    L.stage_bytes = L.stg_off + (mixed ? kTileP * 64u : 0u);
+    L.cook_off    = L.sfq_off + 256u * q_groups * static_cast<uint32_t>(scaled); // (the activation scales' box holds q_groups groups)
+    L.stg_off     = L.cook_off + (cook ? 2048u : 0u);      // re-ordered scales: 2 sides x up to 2 K atoms x 512 bytes
+    const uint32_t used = L.stg_off + (mixed ? kTileP * 64u : 0u); // mixed kind: the packed e2m1 weight tile, 128 rows x 64 bytes
+    L.stage_bytes = (used + 1023u) & ~1023u;               // every stage starts on the swizzle atom's 1024-byte boundary
     L.red_off     = L.stage_bytes * static_cast<uint32_t>(stages);
     L.bar_off     = L.red_off + (csplit > 1 ? static_cast<uint32_t>(csplit - 1) * static_cast<uint32_t>(kTileP / csplit) * static_cast<uint32_t>(bn) * 4u : 0u);
-    L.total       = L.bar_off + 256u;
+    L.total       = L.bar_off + kDecodeBarrierBytes;
+    // The barrier block fits into the last stage's padding where that has room to spare; with 64 activation rows and
+    // e8m0_shuffle scales this is what lets a fourth stage in beside a second CTA on the SM
+    // (never inside the first 32 KB of the ring, which the epilogue reuses as its staging buffers)
+    if(csplit == 1 && L.stage_bytes - used >= kDecodeBarrierBytes && L.red_off - kDecodeBarrierBytes >= 32768u)
+    {
+        L.bar_off = L.red_off - kDecodeBarrierBytes;
+        L.total   = L.red_off;
+    }
     return L;
 }
 
@@ -721,9 +733,10 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
     // (tcgen05.cp); the (m/32,k/4,32,4) order needs no transpose, there the warps write TMEM themselves
     static const bool no_cp = (std::getenv("AITER_B200_DECODE_NO_CP") != nullptr);
     const bool cook = scaled && !no_cp && prob.wgt_sf.wire == SFW_E8M0_SHUFFLE;
-    // as many stages as keep two CTAs on an SM (110 KB each), unless the configuration names a count
+    // as many stages as keep two CTAs on an SM (228 KB, of which each CTA also takes 1 KB of system space), unless the
+    // configuration names a count
     int stages = 0;
-    const int smem_cap = named_stages > 0 ? st.smem_optin : 110 * 1024;
+    const int smem_cap = named_stages > 0 ? st.smem_optin : (228 * 1024) / 2 - 1024;
     for(int s2 = std::min(named_stages > 0 ? named_stages : kDecodeMaxStages, kDecodeMaxStages); s2 >= 2; --s2)
         if(static_cast<int>(make_decode_layout(bn, s2, csplit, decode_sf_unit(kkind), cook, mixed).total) + 1024 <= smem_cap)
         {

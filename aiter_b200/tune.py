@@ -276,7 +276,7 @@ def write_rows(path, family, rows):
     header = BF16_HEADER if family == "bf16" else (BLOCKSCALE_HEADER if family.startswith("a8w8_blockscale") else HEADER)
     tmp = path + ".tmp"
     with open(tmp, "w", newline="") as f:
-        w = csv.DictWriter(f, fieldnames=header)
+        w = csv.DictWriter(f, fieldnames=header, lineterminator="\n")
         w.writeheader()
         for key in sorted(rows):
             w.writerow(rows[key])
