@@ -8,7 +8,7 @@
 // kernel is built to keep that chain short:
 //   * little code: one tile per CTA, one operand arrangement (weights on the 128-row slot), no pairs, no work list, so
 //     the lone threads that run each role meet few instruction-cache misses;
-//   * 224 threads, <= 146 registers, <= 110 KB of shared memory and <= 256 TMEM columns: two CTAs fit on an SM, so the
+//   * 224 threads, <= 146 registers, <= 113 KB of shared memory and <= 256 TMEM columns: two CTAs fit on an SM, so the
 //     CTAs of the next launch in the stream (programmatic dependent launch) set up - barriers, TMEM, tensor-map
 //     prefetch - while the previous launch still runs, and a grid of up to 296 tiles is one wave;
 //   * the four scale warps are also the epilogue warps (same TMEM lane quarters), and one thread issues both operand

@@ -684,7 +684,7 @@ static void launch_decode_instance(int ctas, int tiles_q, int csplit, size_t sme
     {
         int dev = 0;
         B200_CUDA(cudaGetDevice(&dev));
-        if(dev >= 0 && dev < 64 && !attr_done[dev]) // two CTAs of ~100 KB each per SM need the largest shared-memory carve-out
+        if(dev >= 0 && dev < 64 && !attr_done[dev]) // two CTAs of up to 113 KB each per SM need the largest shared-memory carve-out
             B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     }
     raise_smem_limit(kernel, attr_done);
