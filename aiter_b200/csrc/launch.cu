@@ -324,6 +324,13 @@ static int max_stages(int bn, int cg, int smem_limit, int f4_operand, int scaled
     return 0;
 }
 
+// Tall MXFP4 problems with e8m0_shuffle scales: that byte order costs the scale warps a transpose through shared
+// memory on every K tile; re-laying both scale tensors once into the (m/32,k/4,32,4) order (a few MB) lets the
+// main loop run the cheaper path.
+constexpr long long kScalePrepassMinM = 1024;
+constexpr long long kScalePrepassMinK = 4096; // the two extra launches (~6 us) must be won back over the K loop ...
+                                              // ... which on a tall problem (tall_problem) they are at any K >= 1024
+
 // A tall MXFP4 / NVFP4 problem: enough output tiles that the per-call re-layout of e8m0_shuffle scales (two small
 // launches) and the narrower two-accumulator tile pay back even at a short K.  Measured with the tuner at K = 1536 / 2048:
 // 16384 x 7168 142 -> 133 us, 4096 x 24576 98.5 -> 92.3 us; 2048 x 24576 a tie; 4096 x 7168 42.9 -> 44.1 us (not tall).
@@ -338,11 +345,28 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
         // kernel on tiles of 64 rows, each on the same weight tile, while all those CTAs are resident at once (two per SM);
         // measured against the persistent kernel's 128-wide tiles: MXFP4 256 x 7168 x 2048 10.5 -> 8.2 us, 256 x 8192 x 8192
         // 23.9 -> 20.8 us, MXFP8 128 x 4096 x 4096 15.7 -> 12.4 us; 256 x 24576 x 1536 (768 CTAs) 15.6 -> 20.3 us
-        if(M > 64 && M <= 256 && cfg.bn <= 0 && cfg.cg <= 0 && (kind == PK_MXFP8 || kind == PK_MXFP4 || kind == PK_NVFP4) &&
-           ((N + kTileP - 1) / kTileP) * ((M + 63) / 64) <= 2LL * num_sms)
+        // Tiles of 128 rows instead (the tuner's choices over the reference's model shapes): for up to 128 rows of a large
+        // weight (N >= 5120, N x K >= 48 M elements) one tile with four stages, a CTA alone on its SM (128 x 7168 x 16384
+        // 24.8 -> 22.9 us); for 129..256 rows where four tiles of 64 per weight tile no longer fit the machine but two of 128 do.
+        if(M > 64 && M <= 256 && cfg.bn <= 0 && cfg.cg <= 0 && (kind == PK_MXFP8 || kind == PK_MXFP4 || kind == PK_NVFP4))
         {
-            cfg.swap = 1;
-            cfg.bn   = 64;
+            const long long tiles_p = (N + kTileP - 1) / kTileP;
+            if(M <= 128 && N >= 5120 && N * K >= 48LL * 1024 * 1024 && tiles_p <= num_sms && cfg.stages <= 0)
+            {
+                cfg.swap          = 1;
+                cfg.bn            = 128;
+                cfg.decode_stages = 4;
+            }
+            else if(tiles_p * ((M + 63) / 64) <= 2LL * num_sms)
+            {
+                cfg.swap = 1;
+                cfg.bn   = 64;
+            }
+            else if(tiles_p * ((M + 127) / 128) <= 2LL * num_sms)
+            {
+                cfg.swap = 1;
+                cfg.bn   = 128;
+            }
         }
     }
     const long long rows_q = cfg.swap ? M : N;
@@ -364,16 +388,40 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
                 cfg.bn = rows_q <= 16 ? 16 : rows_q <= 32 ? 32 : rows_q <= 64 ? 64 : rows_q <= 128 ? 128 : 256;
         }
     }
-    // Tall 4-bit problems with a short K: a 256 x 256 tile has TMEM for one accumulator only, so every tile's epilogue
-    // (~3.6 k cycles) is exposed, a third of a tile's time at K = 1536; 192 columns leave room for two accumulators and
-    // the epilogue runs under the next tile's main loop (tuner: 16384 x 24576 x 1536 355 -> 326 us, 16384 x 7168 x 2048
-    // 140 -> 123 us).  On tall problems only, where the library re-lays e8m0_shuffle scales once per call; below that
-    // the scale warps' in-kernel transpose bounds the main loop either way.
-    if(bn_was_open && !cfg.swap && cfg.bn == 256 && (kind == PK_MXFP4 || kind == PK_NVFP4) && tall_problem(rows_p, rows_q) && K <= 2560)
-        cfg.bn = 192;
+    const bool four_bit = (kind == PK_MXFP4 || kind == PK_NVFP4);
+    if(bn_was_open && cfg.cg <= 0 && !cfg.swap && rows_p >= 512)
+    {
+        // CTA pairs (each SM stages half of the Q tile per flop) pay from about two dozen 256 x 256 tiles on: the tuner's
+        // tables name a pair tile for every such shape of the reference's model list, down to 512 x 2560
+        const long long pair_rows = (rows_p + 2 * kTileP - 1) / (2 * kTileP);
+        if(pair_rows * ((rows_q + 255) / 256) >= 24)
+        {
+            cfg.cg = 2;
+            cfg.bn = 256;
+            if(four_bit)
+            {
+                // 256 x 256 (TMEM for one accumulator: the epilogue is exposed) against 256 x 192 (two accumulators, 7/8
+                // of the operand bytes for 3/4 of the flops): waves over the SM pairs x time per tile, fitted to the
+                // tuner's measurements in units of 10 ns.  Where the scales are in the cheap order (tall problems:
+                // re-laid once per call; NVFP4's wire order) a tile takes 0.42 / 0.40 us per K tile of 256 elements plus
+                // 2.0 / 0.6 us; otherwise the scale warps set the pace and both widths take 0.38 us per K tile plus
+                // 3.1 us, so only the number of waves (then the padding of the last tile) decides.
+                const long long k_tiles = (K + 255) / 256;
+                const bool cheap_scales = (kind == PK_NVFP4) || (rows_p >= kScalePrepassMinM && K % 256 == 0 && K >= (tall_problem(rows_p, rows_q) ? 1024 : kScalePrepassMinK));
+                const long long t256    = cheap_scales ? k_tiles * 42 + 200 : k_tiles * 38 + 310;
+                const long long t192    = cheap_scales ? k_tiles * 40 + 57 : k_tiles * 38 + 310;
+                const long long pairs   = std::max(num_sms / 2, 1);
+                auto waves = [&](long long bn) { return (pair_rows * ((rows_q + bn - 1) / bn) + pairs - 1) / pairs; };
+                auto pad   = [&](long long bn) { return (rows_q + bn - 1) / bn * bn - rows_q; };
+                const long long c256 = waves(256) * t256, c192 = waves(192) * t192;
+                if(c192 < c256 || (c192 == c256 && pad(192) <= pad(256)))
+                    cfg.bn = 192;
+            }
+        }
+    }
     if(cfg.cg <= 0)
     {
-        // a CTA pair halves the Q bytes each SM stages per flop; worth it once there are enough 256-row tiles
+        // (below that: pairs only where the chosen tile still gives every SM pair work)
         const long long pair_tiles = ((rows_p + 2 * kTileP - 1) / (2 * kTileP)) * ((rows_q + cfg.bn - 1) / cfg.bn);
         cfg.cg = (!cfg.swap && cfg.bn >= 128 && cfg.bn % 32 == 0 && rows_p >= 512 && pair_tiles * 2 >= num_sms) ? 2 : 1;
     }
@@ -388,7 +436,21 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
         const bool decode  = cfg.swap && cfg.cg == 1 && cfg.bn <= 64;
         const long long cap = decode ? 2LL * num_sms : num_sms;
         const int max_l2    = decode ? 2 : 5;
-        while(l2 < max_l2 && tiles * (2LL << l2) <= cap && (k_iters >> (l2 + 1)) >= 4)
+        // Fitted to the tuner's choices over the reference's model shapes: pair tiles never split (no shape where the
+        // workspace split paid); single-CTA tiles of a problem with 512 rows or more only for slices of 24 K tiles; decode
+        // tiles of 64 rows stream 24 KB per K tile and want slices of 6 K tiles while the split grid still fits one CTA
+        // per SM, 16 beyond.  Clusters do not pack the machine to the last slot (they may not straddle a GPC): a split
+        // into clusters of four may take 7/8 of the two-CTAs-per-SM capacity (64 x 9216 x 16384: 288 CTAs in clusters of four
+        // 34 us, in pairs 23.8 us).
+        auto min_iters = [&](int next_l2) -> long long {
+            if(decode && cfg.bn == 64)
+                return tiles * (1LL << next_l2) <= num_sms ? 6 : 16;
+            if(!cfg.swap && rows_p >= 512)
+                return 24;
+            return 4;
+        };
+        auto capacity = [&](int next_l2) -> long long { return decode && next_l2 >= 2 ? cap - cap / 8 : cap; };
+        while(cfg.cg == 1 && l2 < max_l2 && tiles * (2LL << l2) <= capacity(l2 + 1) && (k_iters >> (l2 + 1)) >= min_iters(l2 + 1))
             ++l2;
         cfg.log2_splitk = l2;
     }
@@ -710,7 +772,8 @@ static void launch_decode_instance(int ctas, int tiles_q, int csplit, size_t sme
 // then serves the call).  Caller holds g_mutex and has made the device current.
 static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, int kkind, DeviceState& st)
 {
-    const int named_stages = prob.cfg.stages; // what the caller's configuration asked for (0: this kernel's own choice)
+    // what the caller's configuration asked for, else what the heuristic did (0: this kernel's own choice)
+    const int named_stages = prob.cfg.stages > 0 ? prob.cfg.stages : cfg.decode_stages;
     // one tile of activation rows, or up to four tiles of 64 / two of 128 (each a CTA of its own on the same weight tile);
     // a 128-column tile named with more than four stages stays with the persistent kernel
     const int tiles_q = static_cast<int>((prob.M + cfg.bn - 1) / std::max(cfg.bn, 1));
@@ -863,12 +926,6 @@ static bool try_launch_decode(const GemmProblem& prob, const KernelConfig& cfg, 
 // every tile of it in shared memory M / 256 times; the GEMM itself then runs as plain MXFP8.  Below the
 // threshold, inside stream capture without a buffer, or with caller-provided scratch the in-kernel path runs.
 constexpr long long kWidenPrepassMinM = 512;
-// Tall MXFP4 problems with e8m0_shuffle scales: that byte order costs the scale warps a transpose through shared
-// memory on every K tile; re-laying both scale tensors once into the (m/32,k/4,32,4) order (a few MB) lets the
-// main loop run the cheaper path.
-constexpr long long kScalePrepassMinM = 1024;
-constexpr long long kScalePrepassMinK = 4096; // the two extra launches (~6 us) must be won back over the K loop ...
-                                              // ... which on a tall problem (tall_problem) they are at any K >= 1024
 
 void launch_gemm(const GemmProblem& prob)
 {

@@ -66,6 +66,8 @@ struct KernelConfig
     int stages = 0;  // 0: choose
     int log2_splitk = -1; // -1: choose
     int cg = 0;      // CTAs per tile: 1, or 2 (a 256-row tile on a CTA pair); 0: choose
+    int decode_stages = 0; // set by the heuristic only: the decode kernel runs with this many stages, a CTA alone on its SM
+                           // (0: as many as keep two CTAs on an SM, or what `stages` names)
 };
 
 // Caller-provided scratch for a launch that must not allocate: split-K partials, ticket counters and the
