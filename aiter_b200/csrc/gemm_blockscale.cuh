@@ -39,6 +39,7 @@ struct BlockScaleParams
     int scales_e8m0;         // few-rows kernel: both scale tensors hold e8m0 bytes (2^(e-127)) instead of floats
     int tma_out;             // few-rows kernel: columns per warp-wide TMA tile store of the output (0: plain stores)
     int cluster;             // few-rows kernel: the slices are the CTAs of one cluster and meet in shared memory
+    int pairs_m, tiles_n;    // pair kernel (persistent): 256-row tiles x 256-column tiles of the output
 };
 
 __host__ __device__ constexpr uint32_t idesc_f8f6f4_e4m3(uint32_t m, uint32_t n)
@@ -687,7 +688,9 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
 
 
 // ---------------------------------------------------------------------------------------------------------
-// Same arithmetic on CTA pairs: a 256 x 256 output tile per pair (cta_group::2).  Every CTA stages its own 128
+// Same arithmetic on CTA pairs: 256 x 256 output tiles (cta_group::2), a persistent pair walking a static list of
+// them, so that barrier set-up, TMEM allocation and the pipeline fill are paid once and a tile's rows go out while the
+// next tile's operands arrive and its first K blocks are multiplied.  Every CTA stages its own 128
 // rows of A and its own 128 of the tile's 256 rows of B per K block (24 B of operand per 512 cycles of MMA and
 // SM less than the 128 x 128 tile moves), the leader issues 256 x 256 x 32 MMAs into one of two 256-column
 // TMEM partials, and eight promotion warps per CTA (two per TMEM lane quarter, 128 columns each) fold the
@@ -708,29 +711,35 @@ __device__ __forceinline__ void mma_f8f6f4_2cta(uint32_t d, uint64_t adesc, uint
 
 __global__ void __launch_bounds__(kBlockScalePairThreads, 1)
 gemm_a8w8_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                                 const BlockScaleParams prm)
+                                 const __grid_constant__ CUtensorMap map_o, const BlockScaleParams prm)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen        = smem_raw + (smem_base - smem_u32(smem_raw));
     const int S              = prm.stages;
     constexpr uint32_t kStageBytes = 2u * kTileP * kTileKBytes; // 16 KB of A + 16 KB of B per CTA
-    const uint32_t bar_base  = smem_base + kStageBytes * S;
+    // stages | one 4 KB output staging buffer per promotion warp (32 rows x 64 columns of 16 bits, 128-byte swizzle) | barriers
+    constexpr uint32_t kEpiBytes = 8u * 4096u;
+    const uint32_t epi_off   = kStageBytes * S;
+    const uint32_t bar_base  = smem_base + epi_off + kEpiBytes;
     auto full_bar       = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar      = [&](int s) { return bar_base + 64u + 8u * s; };
     auto part_full_bar  = [&](int b) { return bar_base + 128u + 8u * b; };
     auto part_empty_bar = [&](int b) { return bar_base + 144u + 8u * b; };
     const uint32_t drain_bar   = bar_base + 160u;
-    uint32_t* tmem_ptr_smem    = reinterpret_cast<uint32_t*>(smem_gen + kStageBytes * S + 168);
-    volatile uint32_t* abort_f = reinterpret_cast<volatile uint32_t*>(smem_gen + kStageBytes * S + 172);
+    uint32_t* tmem_ptr_smem    = reinterpret_cast<uint32_t*>(smem_gen + epi_off + kEpiBytes + 168);
+    volatile uint32_t* abort_f = reinterpret_cast<volatile uint32_t*>(smem_gen + epi_off + kEpiBytes + 172);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t crank = cluster_ctarank();
     const bool leader    = (crank == 0);
-    const int pair_x     = blockIdx.x >> 1;                 // 256-row tile index
-    const int row0       = (pair_x * 2 + static_cast<int>(crank)) * kTileP;
-    const int col0       = blockIdx.y * kBsPairN;
     const int KB         = prm.k_blocks;
+    // persistent: cluster c takes tiles c, c + clusters, ...; consecutive tiles share a column tile of B (L2)
+    const int n_clusters = static_cast<int>(gridDim.x >> 1);
+    const int tile0      = static_cast<int>(blockIdx.x >> 1);
+    const int n_tiles    = prm.pairs_m * prm.tiles_n;
+    auto tile_row0 = [&](int t) { return ((t % prm.pairs_m) * 2 + static_cast<int>(crank)) * kTileP; };
+    auto tile_col0 = [&](int t) { return (t / prm.pairs_m) * kBsPairN; };
 
     if(threadIdx.x == 0)
     {
@@ -740,6 +749,273 @@ gemm_a8w8_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
             mbar_init(empty_bar(s), 1);
         }
         for(int b = 0; b < 2; ++b)
+        {
+            mbar_init(part_full_bar(b), 1);
+            mbar_init(part_empty_bar(b), 16); // eight promotion warps in each CTA
+        }
+        mbar_init(drain_bar, 1);
+        *abort_f = 0;
+        mbar_fence_init();
+        fence_proxy_async_smem();
+    }
+    if(warp == 10 && lane == 0)
+    {
+        tma_prefetch_desc(&map_a);
+        tma_prefetch_desc(&map_b);
+        if(prm.tma_out)
+            tma_prefetch_desc(&map_o);
+    }
+    if(warp == 1)
+    {
+        tmem_alloc_2cta(smem_u32(tmem_ptr_smem), 512);
+        tmem_relinquish_2cta();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_ptr_smem;
+    // programmatic dependent launch (see the 128 x 128 kernel)
+    grid_dependency_wait();
+    grid_launch_dependents();
+
+    if(warp == 0)
+    {
+        if(lane == 0)
+        {
+            const uint32_t full0 = map_to_cta(full_bar(0), 0);
+            int s = 0;
+            uint32_t phase = 0;
+            bool live = true;
+            for(int t = tile0; t < n_tiles && live; t += n_clusters)
+            {
+            const int row0 = tile_row0(t), col0 = tile_col0(t);
+            for(int j = 0; j < KB; ++j)
+            {
+                if(!bounded_wait(empty_bar(s), phase ^ 1u, abort_f, prm.status, ST_TIMEOUT_PRODUCER, j))
+                {
+                    live = false;
+                    break;
+                }
+                const uint32_t stage = smem_base + s * kStageBytes;
+                const uint32_t bar   = full0 + 8u * s;
+                mbar_arrive_expect_tx_cluster(bar, kStageBytes);
+                if(prm.a_mode == OPM_ROWMAJOR)
+                    tma_load_2d_pair(stage, &map_a, bar, j * kTileKBytes, row0);
+                else
+                    tma_load_3d_pair(stage, &map_a, bar, 0, row0 >> 4, j * (kTileKBytes / 16));
+                const int brow = col0 + static_cast<int>(crank) * kTileP;
+                if(prm.b_mode == OPM_ROWMAJOR)
+                    tma_load_2d_pair(stage + kTileP * kTileKBytes, &map_b, bar, j * kTileKBytes, brow);
+                else
+                    tma_load_3d_pair(stage + kTileP * kTileKBytes, &map_b, bar, 0, brow >> 4, j * (kTileKBytes / 16));
+                if(++s == S)
+                {
+                    s = 0;
+                    phase ^= 1u;
+                }
+            }
+            }
+            if(*abort_f)
+            {
+                const uint64_t t0 = global_timer_ns();
+                while(global_timer_ns() - t0 < 200000ull) {}
+            }
+        }
+    }
+    else if(warp == 1)
+    {
+        if(lane == 0 && leader)
+        {
+            const uint32_t idesc = idesc_f8f6f4_e4m3(2 * kTileP, kBsPairN);
+            const bool a_tiled = (prm.a_mode == OPM_TILE16), b_tiled = (prm.b_mode == OPM_TILE16);
+            const uint32_t a_lbo = a_tiled ? kTileP * 16u : 16u, a_sbo = a_tiled ? 128u : 1024u, a_lay = a_tiled ? 0u : 2u;
+            const uint32_t a_step = (a_tiled ? 2u * kTileP * 16u : 32u) >> 4;
+            const uint32_t b_lbo = b_tiled ? kTileP * 16u : 16u, b_sbo = b_tiled ? 128u : 1024u, b_lay = b_tiled ? 0u : 2u;
+            const uint32_t b_step = (b_tiled ? 2u * kTileP * 16u : 32u) >> 4;
+            const uint32_t a_hi  = static_cast<uint32_t>(make_smem_desc(0, a_lbo, a_sbo, a_lay) >> 32);
+            const uint32_t b_hi  = static_cast<uint32_t>(make_smem_desc(0, b_lbo, b_sbo, b_lay) >> 32);
+            const uint32_t a_lo0 = static_cast<uint32_t>(make_smem_desc(smem_base, a_lbo, a_sbo, a_lay));
+            const uint32_t b_lo0 = static_cast<uint32_t>(make_smem_desc(smem_base + kTileP * kTileKBytes, b_lbo, b_sbo, b_lay));
+            bool ok = true;
+            int s = 0;
+            uint32_t phase = 0;
+            uint32_t g = 0; // K blocks issued so far, over all tiles: partial g & 1, its barriers' phase (g >> 1) & 1
+            for(int t = tile0; t < n_tiles && ok; t += n_clusters)
+            for(int j = 0; j < KB && ok; ++j, ++g)
+            {
+                const int b = static_cast<int>(g & 1u);
+                ok = bounded_wait(part_empty_bar(b), ((g >> 1) & 1u) ^ 1u, abort_f, prm.status, ST_TIMEOUT_MMA_SF, j);
+                if(ok)
+                    ok = bounded_wait(full_bar(s), phase, abort_f, prm.status, ST_TIMEOUT_MMA_FULL, j);
+                if(!ok)
+                    break;
+                tc_fence_after_sync();
+                const uint32_t a_lo = a_lo0 + s * (kStageBytes >> 4), b_lo = b_lo0 + s * (kStageBytes >> 4);
+#pragma unroll
+                for(int k = 0; k < 4; ++k)
+                    mma_f8f6f4_2cta(tmem_base + b * kBsPairN, pack_u64(a_lo + k * a_step, a_hi), pack_u64(b_lo + k * b_step, b_hi), idesc,
+                                    k > 0 ? 1u : 0u);
+                tc_commit_2cta(empty_bar(s), 3);
+                tc_commit_2cta(part_full_bar(b), 3);
+                if(++s == S)
+                {
+                    s = 0;
+                    phase ^= 1u;
+                }
+            }
+            if(!ok)
+            {
+                tc_commit_2cta(drain_bar, 1);
+                const uint64_t t0 = global_timer_ns();
+                while(!mbar_try_wait(drain_bar, 0) && global_timer_ns() - t0 < c_wait_ctl.limit_ns) {}
+            }
+        }
+    }
+    else if(warp < 10)
+    {
+        // promotion + store: thread = output row, 128 of the tile's 256 columns
+        const int quarter    = warp & 3;
+        const int half       = (warp - 2) >> 2;
+        const int r_local    = quarter * 32 + lane;
+        const uint32_t tlane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * 128;
+        const uint32_t part_empty_leader = map_to_cta(part_empty_bar(0), 0);
+        const bool vec_ok    = ((prm.ldo & 7) == 0) && ((reinterpret_cast<uintptr_t>(prm.out) & 15) == 0);
+        bool ok = true;
+        uint32_t g = 0;
+        for(int t = tile0; t < n_tiles && ok; t += n_clusters)
+        {
+            const int row        = tile_row0(t) + r_local;
+            const int ccol0      = tile_col0(t) + half * 128;
+            const bool row_ok    = row < prm.M;
+            const float* xs      = prm.x_scale + static_cast<long long>(row_ok ? row : 0) * prm.xs_stride_m;
+            const int nblk       = min(ccol0 / 128, (prm.N + 127) / 128 - 1);
+            const float* ws      = prm.w_scale + static_cast<long long>(nblk) * KB;
+            float acc[128];
+#pragma unroll
+            for(int i = 0; i < 128; ++i)
+                acc[i] = 0.f;
+            float scale_next = (KB > 0) ? __ldg(xs) * __ldg(ws) : 0.f;
+            for(int j = 0; j < KB && ok; ++j, ++g)
+            {
+                const int b       = static_cast<int>(g & 1u);
+                const float scale = scale_next;
+                if(j + 1 < KB)
+                    scale_next = __ldg(xs + static_cast<long long>(j + 1) * prm.xs_stride_k) * __ldg(ws + j + 1);
+                ok = bounded_wait(part_full_bar(b), (g >> 1) & 1u, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, j);
+                ok = __all_sync(0xffffffffu, ok);
+                if(!ok)
+                    break;
+                tc_fence_after_sync();
+#pragma unroll
+                for(int c = 0; c < 4; ++c)
+                {
+                    uint32_t r[32];
+                    tmem_ld_x32(tlane + b * kBsPairN + c * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for(int i = 0; i < 32; ++i)
+                        acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), scale, acc[c * 32 + i]);
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if(lane == 0)
+                    mbar_arrive_cluster(part_empty_leader + 8u * b);
+            }
+            // (the tensor core is already at work on the next tile's first K blocks while the rows go out)
+            if(ok && prm.tma_out)
+            {
+                // 16-bit outputs: the warp's 32 rows x 128 columns leave as two tile stores of 64 columns, staged in this
+                // warp's buffer with the 128-byte swizzle the store expects; the store clips rows >= M and columns >= N
+                const bool f16       = (prm.out_mode == OUT_F16);
+                const uint32_t boff  = epi_off + static_cast<uint32_t>(warp - 2) * 4096u;
+                uint8_t* rowp        = smem_gen + boff + lane * 128;
+                const int warp_row0  = tile_row0(t) + quarter * 32;
+#pragma unroll
+                for(int c = 0; c < 2; ++c)
+                {
+                    if(lane == 0)
+                        bulk_wait_group_read<0>(); // the store that last used the buffer has read it
+                    __syncwarp();
+#pragma unroll
+                    for(int q = 0; q < 8; ++q)
+                        *reinterpret_cast<uint4*>(rowp + ((q ^ (lane & 7)) * 16)) =
+                            make_uint4(pack_out16x2(acc[c * 64 + 8 * q], acc[c * 64 + 8 * q + 1], f16),
+                                       pack_out16x2(acc[c * 64 + 8 * q + 2], acc[c * 64 + 8 * q + 3], f16),
+                                       pack_out16x2(acc[c * 64 + 8 * q + 4], acc[c * 64 + 8 * q + 5], f16),
+                                       pack_out16x2(acc[c * 64 + 8 * q + 6], acc[c * 64 + 8 * q + 7], f16));
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if(lane == 0 && warp_row0 < prm.M && ccol0 + c * 64 < prm.N)
+                    {
+                        tma_store_2d(&map_o, smem_base + boff, (ccol0 + c * 64) * 2, warp_row0);
+                        bulk_commit_group();
+                    }
+                }
+            }
+            else if(ok && row_ok && ccol0 < prm.N)
+                store_row<128>(prm.out, prm.out_mode, static_cast<size_t>(row) * prm.ldo + ccol0, acc, prm.N - ccol0, vec_ok);
+        }
+        if(lane == 0)
+            bulk_wait_group_read<0>(); // the last stores have read this warp's buffer before the CTA retires
+        tc_fence_before_sync();
+    }
+    __syncthreads();
+    cluster_sync_all();
+    if(warp == 1)
+    {
+        tc_fence_after_sync();
+        tmem_dealloc_2cta(tmem_base, 512);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// CTA pairs on a 256 x 128 output tile.  The 256 x 256 tile above keeps 128 fp32 accumulators per promotion thread and
+// has registers left for a quarter of a TMEM partial at a time: four loads per K block, each queued behind the MMAs of
+// the next K block, and the partial is released only after the last of them.  Here a promotion thread owns 64 columns:
+// ONE tcgen05.ld brings its whole share of a partial into registers, the partial goes back to the tensor core at once
+// (before the multiply-adds), and with 128-column partials TMEM holds four of them, so the MMAs run up to three K
+// blocks ahead.  Per K block every CTA stages 16 KB of A and 8 KB (its 64 of the tile's 128 rows) of B.
+// Warps (352 threads): 0 TMA producer, 1 MMA issuer (leader) + TMEM owner, 2..9 promotion + store, 10 descriptor prefetch.
+constexpr int kBsPairNarrowN = 128;
+
+__global__ void __launch_bounds__(kBlockScalePairThreads, 1)
+gemm_a8w8_blockscale_pair_narrow_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                        const BlockScaleParams prm)
+{
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen        = smem_raw + (smem_base - smem_u32(smem_raw));
+    const int S              = prm.stages;
+    constexpr uint32_t kABytes     = kTileP * kTileKBytes;               // 16 KB: this CTA's 128 rows of A
+    constexpr uint32_t kBRows      = kBsPairNarrowN / 2;                 // this CTA's 64 of the tile's 128 rows of B
+    constexpr uint32_t kStageBytes = kABytes + kBRows * kTileKBytes;     // 24 KB
+    constexpr int NP               = 4;                                  // TMEM partials of 128 columns
+    const uint32_t bar_base  = smem_base + kStageBytes * S;
+    auto full_bar       = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar      = [&](int s) { return bar_base + 64u + 8u * s; };
+    auto part_full_bar  = [&](int b) { return bar_base + 128u + 8u * b; };
+    auto part_empty_bar = [&](int b) { return bar_base + 160u + 8u * b; };
+    const uint32_t drain_bar   = bar_base + 192u;
+    uint32_t* tmem_ptr_smem    = reinterpret_cast<uint32_t*>(smem_gen + kStageBytes * S + 200);
+    volatile uint32_t* abort_f = reinterpret_cast<volatile uint32_t*>(smem_gen + kStageBytes * S + 204);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t crank = cluster_ctarank();
+    const bool leader    = (crank == 0);
+    const int pair_x     = blockIdx.x >> 1;                 // 256-row tile index
+    const int row0       = (pair_x * 2 + static_cast<int>(crank)) * kTileP;
+    const int col0       = blockIdx.y * kBsPairNarrowN;
+    const int KB         = prm.k_blocks;
+
+    if(threadIdx.x == 0)
+    {
+        for(int s = 0; s < S; ++s)
+        {
+            mbar_init(full_bar(s), 2);  // one expect_tx arrival per CTA of the pair
+            mbar_init(empty_bar(s), 1);
+        }
+        for(int b = 0; b < NP; ++b)
         {
             mbar_init(part_full_bar(b), 1);
             mbar_init(part_empty_bar(b), 16); // eight promotion warps in each CTA
@@ -786,11 +1062,11 @@ gemm_a8w8_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
                     tma_load_2d_pair(stage, &map_a, bar, j * kTileKBytes, row0);
                 else
                     tma_load_3d_pair(stage, &map_a, bar, 0, row0 >> 4, j * (kTileKBytes / 16));
-                const int brow = col0 + static_cast<int>(crank) * kTileP;
+                const int brow = col0 + static_cast<int>(crank * kBRows);
                 if(prm.b_mode == OPM_ROWMAJOR)
-                    tma_load_2d_pair(stage + kTileP * kTileKBytes, &map_b, bar, j * kTileKBytes, brow);
+                    tma_load_2d_pair(stage + kABytes, &map_b, bar, j * kTileKBytes, brow);
                 else
-                    tma_load_3d_pair(stage + kTileP * kTileKBytes, &map_b, bar, 0, brow >> 4, j * (kTileKBytes / 16));
+                    tma_load_3d_pair(stage + kABytes, &map_b, bar, 0, brow >> 4, j * (kTileKBytes / 16));
                 if(++s == S)
                 {
                     s = 0;
@@ -808,23 +1084,23 @@ gemm_a8w8_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
     {
         if(lane == 0 && leader)
         {
-            const uint32_t idesc = idesc_f8f6f4_e4m3(2 * kTileP, kBsPairN);
+            const uint32_t idesc = idesc_f8f6f4_e4m3(2 * kTileP, kBsPairNarrowN);
             const bool a_tiled = (prm.a_mode == OPM_TILE16), b_tiled = (prm.b_mode == OPM_TILE16);
             const uint32_t a_lbo = a_tiled ? kTileP * 16u : 16u, a_sbo = a_tiled ? 128u : 1024u, a_lay = a_tiled ? 0u : 2u;
             const uint32_t a_step = (a_tiled ? 2u * kTileP * 16u : 32u) >> 4;
-            const uint32_t b_lbo = b_tiled ? kTileP * 16u : 16u, b_sbo = b_tiled ? 128u : 1024u, b_lay = b_tiled ? 0u : 2u;
-            const uint32_t b_step = (b_tiled ? 2u * kTileP * 16u : 32u) >> 4;
+            const uint32_t b_lbo = b_tiled ? kBRows * 16u : 16u, b_sbo = b_tiled ? 128u : 1024u, b_lay = b_tiled ? 0u : 2u;
+            const uint32_t b_step = (b_tiled ? 2u * kBRows * 16u : 32u) >> 4;
             const uint32_t a_hi  = static_cast<uint32_t>(make_smem_desc(0, a_lbo, a_sbo, a_lay) >> 32);
             const uint32_t b_hi  = static_cast<uint32_t>(make_smem_desc(0, b_lbo, b_sbo, b_lay) >> 32);
             const uint32_t a_lo0 = static_cast<uint32_t>(make_smem_desc(smem_base, a_lbo, a_sbo, a_lay));
-            const uint32_t b_lo0 = static_cast<uint32_t>(make_smem_desc(smem_base + kTileP * kTileKBytes, b_lbo, b_sbo, b_lay));
+            const uint32_t b_lo0 = static_cast<uint32_t>(make_smem_desc(smem_base + kABytes, b_lbo, b_sbo, b_lay));
             bool ok = true;
             int s = 0;
             uint32_t phase = 0;
             for(int j = 0; j < KB && ok; ++j)
             {
-                const int b = j & 1;
-                ok = bounded_wait(part_empty_bar(b), ((j >> 1) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_MMA_SF, j);
+                const int b = j & (NP - 1);
+                ok = bounded_wait(part_empty_bar(b), ((j >> 2) & 1) ^ 1, abort_f, prm.status, ST_TIMEOUT_MMA_SF, j);
                 if(ok)
                     ok = bounded_wait(full_bar(s), phase, abort_f, prm.status, ST_TIMEOUT_MMA_FULL, j);
                 if(!ok)
@@ -833,7 +1109,7 @@ gemm_a8w8_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
                 const uint32_t a_lo = a_lo0 + s * (kStageBytes >> 4), b_lo = b_lo0 + s * (kStageBytes >> 4);
 #pragma unroll
                 for(int k = 0; k < 4; ++k)
-                    mma_f8f6f4_2cta(tmem_base + b * kBsPairN, pack_u64(a_lo + k * a_step, a_hi), pack_u64(b_lo + k * b_step, b_hi), idesc,
+                    mma_f8f6f4_2cta(tmem_base + b * kBsPairNarrowN, pack_u64(a_lo + k * a_step, a_hi), pack_u64(b_lo + k * b_step, b_hi), idesc,
                                     k > 0 ? 1u : 0u);
                 tc_commit_2cta(empty_bar(s), 3);
                 tc_commit_2cta(part_full_bar(b), 3);
@@ -853,54 +1129,68 @@ gemm_a8w8_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
     }
     else if(warp < 10)
     {
-        // promotion + store: thread = output row, 128 of the tile's 256 columns
+        // promotion + store: thread = output row, 64 of the tile's 128 columns
         const int quarter    = warp & 3;
         const int half       = (warp - 2) >> 2;
         const int r_local    = quarter * 32 + lane;
         const int row        = row0 + r_local;
-        const int ccol0      = col0 + half * 128;
-        const uint32_t tlane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * 128;
+        const int ccol0      = col0 + half * 64;
+        const uint32_t tlane = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * 64;
         const bool row_ok    = row < prm.M;
         const float* xs      = prm.x_scale + static_cast<long long>(row_ok ? row : 0) * prm.xs_stride_m;
-        const int nblk       = min(ccol0 / 128, (prm.N + 127) / 128 - 1);
-        const float* ws      = prm.w_scale + static_cast<long long>(nblk) * KB;
+        const float* ws      = prm.w_scale + static_cast<long long>(blockIdx.y) * KB; // the tile is one 128-column scale block wide
         const uint32_t part_empty_leader = map_to_cta(part_empty_bar(0), 0);
-        float acc[128];
+        float acc[64];
 #pragma unroll
-        for(int i = 0; i < 128; ++i)
+        for(int i = 0; i < 64; ++i)
             acc[i] = 0.f;
         bool ok = true;
-        float scale_next = (KB > 0) ? __ldg(xs) * __ldg(ws) : 0.f;
-        for(int j = 0; j < KB && ok; ++j)
+        // The scales of the next four K blocks wait in registers: with the shared-memory carve-out at its maximum the L1
+        // that is left does not hold a line per row, so every scale load is an L2 round trip, which a look-ahead of
+        // one K block does not cover.
+        float xq[NP], wq[NP];
+#pragma unroll
+        for(int d = 0; d < NP; ++d)
         {
-            const int b       = j & 1;
-            const float scale = scale_next;
-            if(j + 1 < KB)
-                scale_next = __ldg(xs + static_cast<long long>(j + 1) * prm.xs_stride_k) * __ldg(ws + j + 1);
-            ok = bounded_wait(part_full_bar(b), (j >> 1) & 1, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, j);
-            ok = __all_sync(0xffffffffu, ok);
-            if(!ok)
-                break;
-            tc_fence_after_sync();
+            xq[d] = (d < KB) ? __ldg(xs + static_cast<long long>(d) * prm.xs_stride_k) : 0.f;
+            wq[d] = (d < KB) ? __ldg(ws + d) : 0.f;
+        }
+        for(int j0 = 0; j0 < KB && ok; j0 += NP)
+        {
 #pragma unroll
-            for(int c = 0; c < 4; ++c)
+            for(int d = 0; d < NP; ++d)
             {
-                uint32_t r[32];
-                tmem_ld_x32(tlane + b * kBsPairN + c * 32, r);
+                const int j = j0 + d; // partial j & 3 = d
+                if(j >= KB || !ok)
+                    break;
+                const float scale = xq[d] * wq[d];
+                if(j + NP < KB)
+                {
+                    xq[d] = __ldg(xs + static_cast<long long>(j + NP) * prm.xs_stride_k);
+                    wq[d] = __ldg(ws + j + NP);
+                }
+                ok = bounded_wait(part_full_bar(d), (j >> 2) & 1, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, j);
+                ok = __all_sync(0xffffffffu, ok);
+                if(!ok)
+                    break;
+                tc_fence_after_sync();
+                uint32_t r[64];
+                tmem_ld_x64(tlane + d * kBsPairNarrowN, r);
                 tmem_ld_wait();
+                // the partial is in registers: hand it back before the arithmetic
+                tc_fence_before_sync();
+                __syncwarp();
+                if(lane == 0)
+                    mbar_arrive_cluster(part_empty_leader + 8u * d);
 #pragma unroll
-                for(int i = 0; i < 32; ++i)
-                    acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), scale, acc[c * 32 + i]);
+                for(int i = 0; i < 64; ++i)
+                    acc[i] = fmaf(__uint_as_float(r[i]), scale, acc[i]);
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if(lane == 0)
-                mbar_arrive_cluster(part_empty_leader + 8u * b);
         }
         if(ok && row_ok && ccol0 < prm.N)
         {
             const bool vec_ok = ((prm.ldo & 7) == 0) && ((reinterpret_cast<uintptr_t>(prm.out) & 15) == 0);
-            store_row<128>(prm.out, prm.out_mode, static_cast<size_t>(row) * prm.ldo + ccol0, acc, prm.N - ccol0, vec_ok);
+            store_row<64>(prm.out, prm.out_mode, static_cast<size_t>(row) * prm.ldo + ccol0, acc, prm.N - ccol0, vec_ok);
         }
         tc_fence_before_sync();
     }

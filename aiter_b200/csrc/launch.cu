@@ -1470,7 +1470,7 @@ bool parse_blockscale_name(const char* name, int& variant, int& log2_splitk)
 {
     if(name == nullptr || name[0] == 0)
         return false;
-    static const struct { const char* base; int variant; } kNames[] = {{"bs_fewrows", 1}, {"bs_128x128", 2}, {"bs_256x256", 3}};
+    static const struct { const char* base; int variant; } kNames[] = {{"bs_fewrows", 1}, {"bs_128x128", 2}, {"bs_256x256", 3}, {"bs_256x128", 4}};
     for(const auto& n : kNames)
     {
         const size_t len = std::strlen(n.base);
@@ -1490,7 +1490,7 @@ void launch_blockscale(const BlockScaleProblem& prob)
 {
     if(prob.M == 0 && prob.N > 0 && prob.K > 0)
         return;
-    B200_CHECK(!(prob.scales_are_e8m0 && prob.variant > 1), "bs_128x128 / bs_256x256 take fp32 scales; e8m0 scales run on bs_fewrows or an MXFP8 kernel name");
+    B200_CHECK(!(prob.scales_are_e8m0 && prob.variant > 1), "bs_128x128 / bs_256x256 / bs_256x128 take fp32 scales; e8m0 scales run on bs_fewrows or an MXFP8 kernel name");
     if(prob.scales_are_e8m0 && prob.variant == 0 && (prob.cfg_given || !use_few_rows(prob)))
     {
         // powers of two ride the block-scaled MMA; up to 64 rows stay on the few-rows kernel below, which reads the
@@ -1541,7 +1541,7 @@ void launch_blockscale(const BlockScaleProblem& prob)
     const long long single_cost = (tiles128 + st.sm_count - 1) / st.sm_count * 720;
     const long long pair_cost   = (pairs256 + st.sm_count / 2 - 1) / (st.sm_count / 2) * 1300;
     B200_CHECK(prob.variant != 1 || few_rows_can_serve(prob), "bs_fewrows serves at most 256 activation rows");
-    B200_CHECK(prob.variant != 3 || prob.M > kTileP, "bs_256x256 needs more than 128 activation rows");
+    B200_CHECK((prob.variant != 3 && prob.variant != 4) || prob.M > kTileP, "bs_256x256 / bs_256x128 need more than 128 activation rows");
     // 65..256 rows: tiles of 64 rows on the few-rows kernel while all of them fit the machine at once (measured against the
     // 128 x 128 kernel: 256 x 4096 x 4096 15.1 -> 13.3 us, 96 x 4096 x 4096 14.1 -> 10.4 us, 200 x 1536 x 7168 16.3 -> 13.5 us;
     // with more tiles than SMs it loses: 256 x 7168 x 2048 10.7 -> 15.7 us)
@@ -1549,21 +1549,21 @@ void launch_blockscale(const BlockScaleProblem& prob)
     const bool want_few  = prob.variant == 1 || (prob.variant == 0 && (use_few_rows(prob) || (few_rows_can_serve(prob) && few_tiles <= st.sm_count)));
     const bool want_pair = prob.variant == 3 || (prob.variant == 0 && !want_few && prob.M > kTileP && pair_cost < single_cost);
     const int forced_splits = prob.log2_splitk >= 0 ? (1 << prob.log2_splitk) : 0; // 0: the cost model below decides
-    if(want_pair)
+    if(prob.variant == 4)
     {
-        // 256 x 256 tiles on CTA pairs
-        const int stage_bytes = 2 * kTileP * kTileKBytes;
+        // 256 x 128 tiles on CTA pairs
+        const int stage_bytes = (kTileP + kBsPairNarrowN / 2) * kTileKBytes;
         int stages            = std::min((st.smem_optin - 2048) / stage_bytes, kMaxStages);
         stages                = std::max(2, std::min(stages, prm.k_blocks));
         prm.stages            = stages;
         const size_t smem     = static_cast<size_t>(stage_bytes) * stages + 512 + 1024;
         CUtensorMap ma = operand_map(prob.act, kTileP, "activation operand");
-        CUtensorMap mb = operand_map(prob.wgt, kTileP, "weight operand");
+        CUtensorMap mb = operand_map(prob.wgt, kBsPairNarrowN / 2, "weight operand");
         static bool attr_done[64] = {};
-        raise_smem_limit(gemm_a8w8_blockscale_pair_kernel, attr_done);
+        raise_smem_limit(gemm_a8w8_blockscale_pair_narrow_kernel, attr_done);
         prm.splits             = 1;
         const unsigned pairs_m = static_cast<unsigned>((prob.M + 2 * kTileP - 1) / (2 * kTileP));
-        const unsigned tiles_n = static_cast<unsigned>((prob.N + kBsPairN - 1) / kBsPairN);
+        const unsigned tiles_n = static_cast<unsigned>((prob.N + kBsPairNarrowN - 1) / kBsPairNarrowN);
         B200_CHECK(tiles_n <= 65535, "N too large");
         cudaLaunchConfig_t lc{};
         lc.gridDim          = dim3(pairs_m * 2, tiles_n, 1);
@@ -1579,7 +1579,55 @@ void launch_blockscale(const BlockScaleProblem& prob)
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         lc.attrs    = attr;
         lc.numAttrs = pdl_disabled() ? 1 : 2;
-        B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_pair_kernel, ma, mb, prm));
+        B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_pair_narrow_kernel, ma, mb, prm));
+    }
+    else if(want_pair)
+    {
+        // 256 x 256 tiles on CTA pairs
+        const int stage_bytes = 2 * kTileP * kTileKBytes;
+        const int epi_bytes   = 8 * 4096; // one output staging buffer per promotion warp
+        int stages            = std::min((st.smem_optin - 2048 - epi_bytes) / stage_bytes, kMaxStages);
+        stages                = std::max(2, std::min(stages, prm.k_blocks));
+        prm.stages            = stages;
+        const size_t smem     = static_cast<size_t>(stage_bytes) * stages + epi_bytes + 512 + 1024;
+        CUtensorMap ma = operand_map(prob.act, kTileP, "activation operand");
+        CUtensorMap mb = operand_map(prob.wgt, kTileP, "weight operand");
+        // 16-bit outputs leave as warp-wide TMA tiles of 32 rows x 64 columns (bytes; 128-byte swizzle)
+        CUtensorMap mo = ma;
+        prm.tma_out    = 0;
+        if((reinterpret_cast<uintptr_t>(prob.out) & 15) == 0 && prob.ldo % 8 == 0 && prob.out_mode != OUT_F32)
+        {
+            prm.tma_out                 = 64;
+            const cuuint64_t dims[2]    = {static_cast<cuuint64_t>(prob.N) * 2, static_cast<cuuint64_t>(prob.M)};
+            const cuuint64_t strides[1] = {static_cast<cuuint64_t>(prob.ldo) * 2};
+            const cuuint32_t box[2]     = {128u, 32u};
+            mo = encode_map(prob.out, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "output");
+        }
+        static bool attr_done[64] = {};
+        raise_smem_limit(gemm_a8w8_blockscale_pair_kernel, attr_done);
+        prm.splits             = 1;
+        // persistent: one CTA pair per two SMs (or per tile, if there are fewer), each walking tiles pair, pair + pairs, ...
+        const long long pairs_m = (prob.M + 2 * kTileP - 1) / (2 * kTileP);
+        const long long tiles_n = (prob.N + kBsPairN - 1) / kBsPairN;
+        B200_CHECK(pairs_m * tiles_n < (1LL << 30), "too many output tiles");
+        prm.pairs_m = static_cast<int>(pairs_m);
+        prm.tiles_n = static_cast<int>(tiles_n);
+        const unsigned clusters = static_cast<unsigned>(std::min<long long>(pairs_m * tiles_n, std::max(st.sm_count / 2, 1)));
+        cudaLaunchConfig_t lc{};
+        lc.gridDim          = dim3(clusters * 2, 1, 1);
+        lc.blockDim         = dim3(kBlockScalePairThreads, 1, 1);
+        lc.dynamicSmemBytes = smem;
+        lc.stream           = prob.stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id               = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        lc.attrs    = attr;
+        lc.numAttrs = pdl_disabled() ? 1 : 2;
+        B200_CUDA(cudaLaunchKernelEx(&lc, gemm_a8w8_blockscale_pair_kernel, ma, mb, mo, prm));
     }
     else if(want_few)
     {

@@ -42,7 +42,7 @@ FAMILIES = {
     "a8w8_blockscale_bpreshuffle": ("a8w8_blockscale_bpreshuffle", 1),
 }
 BLOCKSCALE_HEADER = ["gfx", "cu_num", "M", "N", "K", "libtype", "kernelId", "splitK", "us", "kernelName", "tflops", "bw", "errRatio"]
-BLOCKSCALE_VARIANTS = {"bs_fewrows": 1, "bs_128x128": 2, "bs_256x256": 3}
+BLOCKSCALE_VARIANTS = {"bs_fewrows": 1, "bs_128x128": 2, "bs_256x256": 3, "bs_256x128": 4}
 HEADER = ["gfx", "cu_num", "M", "N", "K", "kernelId", "splitK", "us", "kernelName", "tflops", "bw", "errRatio"]
 BF16_HEADER = ["gfx", "cu_num", "M", "N", "K", "bias", "dtype", "outdtype", "scaleAB", "bpreshuffle", "libtype", "solidx", "splitK",
                "us", "kernelName", "err_ratio", "tflops", "bw"]
@@ -74,7 +74,7 @@ def blockscale_candidates(M: int, N: int, K: int):
         names += [f"bs_fewrows_k{s}" for s in range(0, 4) if (kb >> s) >= 1]
     names += [f"bs_128x128_k{s}" for s in range(0, 4) if (kb >> s) >= 2]
     if M > 128:
-        names.append("bs_256x256")
+        names += ["bs_256x256", "bs_256x128"]
     return names
 
 

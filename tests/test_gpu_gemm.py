@@ -372,6 +372,38 @@ def test_a8w8_blockscale_few_rows_kernel_on_up_to_four_tiles_of_64_rows(ab, M):
     assert_healthy(ab)
 
 
+@pytest.mark.parametrize("M,N,K", [(2500, 2320, 384), (300, 640, 1024), (4100, 4608, 128)])
+def test_a8w8_blockscale_pair_kernels_by_name(ab, M, N, K):
+    # the CTA-pair kernels: bs_256x256 is persistent (the first shape gives every pair more than one tile, with an odd
+    # number of K blocks so that the TMEM partials change parity from tile to tile; the last one three tiles of one K
+    # block each), bs_256x128 runs one tile per pair; ragged M and N, row-major and preshuffled weights, 16- and 32-bit outputs
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn)
+    w = torch.randn(N, K, generator=g).to(torch.float8_e4m3fn)
+    xs = torch.rand(M, K // 128, generator=g) + 0.25
+    ws = torch.rand((N + 127) // 128, K // 128, generator=g) + 0.25
+    ref = ox.gemm_a8w8_blockscale_ref(x.view(torch.uint8).numpy(), w.view(torch.uint8).numpy(), xs.numpy(), ws.numpy())
+    want = ox.bf16_bits_to_f32(ref)
+    xc, wc, xsc, wsc = x.cuda(), w.cuda(), xs.cuda(), ws.cuda()
+    wq, xs_t = ab.shuffle_weight(wc, layout=(16, 16)), xs.T.contiguous().cuda()
+    for name in ("bs_256x256", "bs_256x128"):
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+        before = ab.launch_count()
+        ab.gemm_a8w8_blockscale_cktile(xc, wc, xsc, wsc, out, kernelName=name)
+        assert ab.launch_count() == before + 1
+        check(ref, out, what=f"blockscale {M}x{N}x{K} {name}")
+        out16 = torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda")
+        ab.gemm_a8w8_blockscale_cktile(xc, wq, xs_t.view(M, K // 128), wsc, out16, preshuffleB=True, kernelName=name)
+        got = out16.float().cpu().numpy()
+        assert np.all(np.abs(got - want) <= 1e-2 + 1e-2 * np.abs(want)), f"{name} preshuffled, fp16 output"
+        # an output pitch that rules out tile stores (rows start on odd 2-byte offsets): plain stores
+        wide = torch.full((M, N + 3), float("nan"), dtype=torch.bfloat16, device="cuda")
+        ab.gemm_a8w8_blockscale_cktile(xc, wc, xsc, wsc, wide[:, :N], kernelName=name)
+        check(ref, wide[:, :N], what=f"blockscale {M}x{N}x{K} {name}, strided output")
+        assert torch.isnan(wide[:, N:]).all()
+    assert_healthy(ab)
+
+
 @pytest.mark.parametrize("M", [16, 100, 300])
 def test_a8w8_blockscale_replays_from_a_cuda_graph(ab, M):
     # few-rows kernel (cluster + dependent launch), 128x128 kernel with and without its workspace K split: captured after
