@@ -249,7 +249,7 @@ def test_tuner_candidates_use_the_library_name_grammar():
             cands = tune.candidates(M, N, K, fam)
             assert cands, (fam, M, N, K)
             if fam.startswith("a8w8_blockscale"):  # these candidates are kernel names of the fp32-scale kernels
-                assert all(c == "" or re.match(r"^bs_(fewrows|128x128|256x256)(_k\d)?$", c) for c in cands), cands
+                assert all(c == "" or re.match(r"^bs_(fewrows|128x128|256x256|256x128)(_k\d)?$", c) for c in cands), cands
                 continue
             for (pair, swap, bn, st, sk) in cands:
                 assert bn in tune.BN_MENU and pair in (0, 1) and swap in (0, 1) and 0 <= st <= 8 and 0 <= sk <= 5
