@@ -218,32 +218,55 @@ gemm_a8w8_blockscale_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         for(int i = 0; i < kBsTileN; ++i)
             acc[i] = 0.f;
         bool ok = true;
-        float scale_next = (KB > 0) ? __ldg(xs) * __ldg(ws) : 0.f;
-        for(int j = 0; j < KB && ok; ++j)
-        {
-            const int b       = j & (NP - 1);
-            const float scale = scale_next;
-            if(j + 1 < KB)
-                scale_next = __ldg(xs + static_cast<long long>(j + 1) * prm.xs_stride_k) * __ldg(ws + j + 1);
+        // One K block: wait for its partial, fold it into the accumulators, hand the partial back.
+        auto promote = [&](int j, float scale) {
+            const int b = j & (NP - 1);
             ok = bounded_wait(part_full_bar(b), (j / NP) & 1, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, j);
             ok = __all_sync(0xffffffffu, ok);
             if(!ok)
-                break;
+                return;
             tc_fence_after_sync();
+            // sixteen columns at a time through two register buffers: the load of the next chunk is in flight while this
+            // one is folded in
+            uint32_t ra[16], rb[16];
+            const uint32_t t0 = tlane + b * kBsTileN;
+            tmem_ld_x16_at(t0, ra);
+            tmem_ld_wait();
 #pragma unroll
-            for(int c = 0; c < kBsTileN / 32; ++c)
+            for(int c = 0; c < kBsTileN / 16; ++c)
             {
-                uint32_t r[32];
-                tmem_ld_x32(tlane + b * kBsTileN + c * 32, r);
-                tmem_ld_wait();
+                if(c + 1 < kBsTileN / 16)
+                    tmem_ld_x16_at(t0 + (c + 1) * 16, (c & 1) ? ra : rb);
 #pragma unroll
-                for(int i = 0; i < 32; ++i)
-                    acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), scale, acc[c * 32 + i]);
+                for(int i = 0; i < 16; ++i)
+                    acc[c * 16 + i] = fmaf(__uint_as_float(((c & 1) ? rb : ra)[i]), scale, acc[c * 16 + i]);
+                if(c + 1 < kBsTileN / 16)
+                    tmem_ld_wait();
             }
             tc_fence_before_sync();
             __syncwarp();
             if(lane == 0)
                 mbar_arrive(part_empty_bar(b));
+        };
+        // The scales of K blocks j and j + 1 wait in registers as loaded (the product is taken when block j's partial is
+        // there): a K-block-major x_scale puts every K block on a cache line of its own, an L2 round trip that a
+        // look-ahead of one K block does not cover.
+        auto ld_x = [&](int j) { return j < KB ? __ldg(xs + static_cast<long long>(j) * prm.xs_stride_k) : 0.f; };
+        auto ld_w = [&](int j) { return j < KB ? __ldg(ws + j) : 0.f; };
+        float xa = ld_x(0), wa = ld_w(0), xb = ld_x(1), wb = ld_w(1);
+        for(int j = 0; j < KB && ok; j += 2)
+        {
+            const float sa = xa * wa;
+            xa = ld_x(j + 2);
+            wa = ld_w(j + 2);
+            promote(j, sa);
+            if(j + 1 < KB && ok)
+            {
+                const float sb = xb * wb;
+                xb = ld_x(j + 3);
+                wb = ld_w(j + 3);
+                promote(j + 1, sb);
+            }
         }
         if(ok && prm.splits > 1)
         {
@@ -895,32 +918,56 @@ gemm_a8w8_blockscale_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
 #pragma unroll
             for(int i = 0; i < 128; ++i)
                 acc[i] = 0.f;
-            float scale_next = (KB > 0) ? __ldg(xs) * __ldg(ws) : 0.f;
-            for(int j = 0; j < KB && ok; ++j, ++g)
-            {
-                const int b       = static_cast<int>(g & 1u);
-                const float scale = scale_next;
-                if(j + 1 < KB)
-                    scale_next = __ldg(xs + static_cast<long long>(j + 1) * prm.xs_stride_k) * __ldg(ws + j + 1);
+            // One K block: wait for its partial, fold it into the accumulators, hand the partial back.
+            auto promote = [&](int j, float scale) {
+                const int b = static_cast<int>(g & 1u);
                 ok = bounded_wait(part_full_bar(b), (g >> 1) & 1u, abort_f, prm.status, ST_TIMEOUT_EPILOGUE, j);
                 ok = __all_sync(0xffffffffu, ok);
                 if(!ok)
-                    break;
+                    return;
                 tc_fence_after_sync();
+                // sixteen columns at a time through two register buffers: the load of the next chunk is in flight while
+                // this one is folded in
+                uint32_t ra[16], rb[16];
+                const uint32_t t0 = tlane + b * kBsPairN;
+                tmem_ld_x16_at(t0, ra);
+                tmem_ld_wait();
 #pragma unroll
-                for(int c = 0; c < 4; ++c)
+                for(int c = 0; c < 8; ++c)
                 {
-                    uint32_t r[32];
-                    tmem_ld_x32(tlane + b * kBsPairN + c * 32, r);
-                    tmem_ld_wait();
+                    if(c < 7)
+                        tmem_ld_x16_at(t0 + (c + 1) * 16, (c & 1) ? ra : rb);
 #pragma unroll
-                    for(int i = 0; i < 32; ++i)
-                        acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), scale, acc[c * 32 + i]);
+                    for(int i = 0; i < 16; ++i)
+                        acc[c * 16 + i] = fmaf(__uint_as_float(((c & 1) ? rb : ra)[i]), scale, acc[c * 16 + i]);
+                    if(c < 7)
+                        tmem_ld_wait();
                 }
                 tc_fence_before_sync();
                 __syncwarp();
                 if(lane == 0)
                     mbar_arrive_cluster(part_empty_leader + 8u * b);
+                ++g;
+            };
+            // The scales of K blocks j and j + 1 wait in registers as loaded (the product is taken when block j's partial
+            // is there): a K-block-major x_scale puts every K block on a cache line of its own, an L2 round trip that a
+            // look-ahead of one K block no longer covers.
+            auto ld_x = [&](int j) { return j < KB ? __ldg(xs + static_cast<long long>(j) * prm.xs_stride_k) : 0.f; };
+            auto ld_w = [&](int j) { return j < KB ? __ldg(ws + j) : 0.f; };
+            float xa = ld_x(0), wa = ld_w(0), xb = ld_x(1), wb = ld_w(1);
+            for(int j = 0; j < KB && ok; j += 2)
+            {
+                const float sa = xa * wa;
+                xa = ld_x(j + 2);
+                wa = ld_w(j + 2);
+                promote(j, sa);
+                if(j + 1 < KB && ok)
+                {
+                    const float sb = xb * wb;
+                    xb = ld_x(j + 3);
+                    wb = ld_w(j + 3);
+                    promote(j + 1, sb);
+                }
             }
             // (the tensor core is already at work on the next tile's first K blocks while the rows go out)
             if(ok && prm.tma_out)
