@@ -1534,14 +1534,14 @@ void launch_blockscale(const BlockScaleProblem& prob)
     prm.status      = st.status;
     prm.scales_e8m0 = prob.scales_are_e8m0 ? 1 : 0;
     // 256 x 256 tiles on persistent CTA pairs or 128 x 128 tiles on single CTAs: whichever needs less time by rounds x
-    // (cycles per K block x K blocks + cycles per tile), as measured: ~1290 + 4000 for a pair (the tile's rows leave under
+    // (cycles per K block x K blocks + cycles per tile), as measured: ~1050 + 4000 for a pair (the tile's rows leave under
     // the next tile's first K blocks), ~810 + 6300 for a single CTA (one tile per CTA: set-up, pipeline fill and the
     // stores are paid per tile).  Few tiles favour the single-CTA kernel (M = 300, N = K = 4096: 96 CTAs and 15.3 us
     // against 32 pairs and 29.6 us), many tiles the pairs.
     const long long tiles128 = ((prob.M + kTileP - 1) / kTileP) * ((prob.N + kBsTileN - 1) / kBsTileN);
     const long long pairs256 = ((prob.M + 2 * kTileP - 1) / (2 * kTileP)) * ((prob.N + 2 * kBsTileN - 1) / (2 * kBsTileN));
     const long long single_cost = (tiles128 + st.sm_count - 1) / st.sm_count * (prm.k_blocks * 810LL + 6300);
-    const long long pair_cost   = (pairs256 + st.sm_count / 2 - 1) / (st.sm_count / 2) * (prm.k_blocks * 1290LL + 4000);
+    const long long pair_cost   = (pairs256 + st.sm_count / 2 - 1) / (st.sm_count / 2) * (prm.k_blocks * 1050LL + 4000);
     B200_CHECK(prob.variant != 1 || few_rows_can_serve(prob), "bs_fewrows serves at most 256 activation rows");
     B200_CHECK((prob.variant != 3 && prob.variant != 4) || prob.M > kTileP, "bs_256x256 / bs_256x128 need more than 128 activation rows");
     // 65..256 rows: tiles of 64 rows on the few-rows kernel while all of them fit the machine at once (measured against the
