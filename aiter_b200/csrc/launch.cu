@@ -1491,10 +1491,14 @@ void launch_blockscale(const BlockScaleProblem& prob)
     if(prob.M == 0 && prob.N > 0 && prob.K > 0)
         return;
     B200_CHECK(!(prob.scales_are_e8m0 && prob.variant > 1), "bs_128x128 / bs_256x256 / bs_256x128 take fp32 scales; e8m0 scales run on bs_fewrows or an MXFP8 kernel name");
-    if(prob.scales_are_e8m0 && prob.variant == 0 && (prob.cfg_given || !use_few_rows(prob)))
+    // (65..256 rows: tiles of 64 rows on the few-rows kernel while all of them fit the machine at once, as for fp32 scales)
+    auto few_by_tiles = [&]() {
+        return few_rows_can_serve(prob) && ((prob.N + kBsTileN - 1) / kBsTileN) * ((prob.M + 63) / 64) <= device_sm_count(prob.device);
+    };
+    if(prob.scales_are_e8m0 && prob.variant == 0 && (prob.cfg_given || !(use_few_rows(prob) || few_by_tiles())))
     {
-        // powers of two ride the block-scaled MMA; up to 64 rows stay on the few-rows kernel below, which reads the
-        // e8m0 bytes itself (one launch, no scale expansion pass)
+        // powers of two ride the block-scaled MMA; few rows stay on the few-rows kernel below, which reads the
+        // e8m0 bytes itself (one launch, no scale expansion pass: 128 x 4096 x 4096 18.6 -> 10.6 us)
         B200_CHECK(prob.K % 128 == 0, "K must be a multiple of 128 for 128-wide scale blocks (got ", prob.K, ")");
         launch_blockscale_e8m0(prob);
         return;

@@ -5,7 +5,7 @@ import torch
 from torch import Tensor
 
 from . import _ffi, dtypes, fp4_utils
-from .config import TunedTable
+from .config import TunedTable, get_cu_num
 
 _mxfp8_table = TunedTable("a8w8_mxfp8")
 _blockscale_table = TunedTable("a8w8_blockscale")
@@ -19,8 +19,11 @@ def get_CKGEMM_config(M: int, N: int, K: int, bpreshuffle: bool = False):
 
 def _mxfp8_kernel_for(m: int, n: int, k: int) -> str:
     """e8m0-scaled blockscale problems run on the MXFP8 kernels: their tuned table names the configuration.
-    Up to 64 rows no name is passed on: the library's few-rows blockscale kernel reads the e8m0 bytes itself."""
+    For few rows no name is passed on: the library's few-rows blockscale kernel reads the e8m0 bytes itself."""
     if m <= 64:
+        return ""
+    # 65..256 rows: the same kernel on tiles of 64 rows while all of them fit the machine at once (the launcher's rule)
+    if m <= 256 and k <= 32768 and -(-n // 128) * -(-m // 64) <= get_cu_num():
         return ""
     row = _mxfp8_table.lookup(m, n, k)
     return str(row.get("kernelName") or "") if row is not None else ""

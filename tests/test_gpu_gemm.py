@@ -479,11 +479,14 @@ def test_a8w8_blockscale_e8m0_scales_run_as_mxfp8(ab, M, N, K, bpre):
                                                   xs_t.T.view(ab.dtypes.fp8_e8m0), ws.cuda().view(ab.dtypes.fp8_e8m0))
     else:
         out = ab.gemm_a8w8_blockscale(x.cuda(), w.cuda(), xs.cuda().view(ab.dtypes.fp8_e8m0), ws.cuda().view(ab.dtypes.fp8_e8m0))
-    # one launch where the few-rows kernel serves the call (up to 64 rows, or a tuned row that names it: it reads the e8m0
-    # bytes itself), else two expansion launches + the MXFP8 kernel
+    # one launch where the few-rows kernel serves the call (up to 64 rows; up to 256 while its tiles of 64 rows all fit the
+    # machine at once; or a tuned row that names it: it reads the e8m0 bytes itself), else two expansion launches + the
+    # MXFP8 kernel
     from aiter_b200 import gemm_op_a8w8
+    from aiter_b200.config import get_cu_num
     row = gemm_op_a8w8.get_CKGEMM_config(M, N, K, bpreshuffle=bpre)
-    few = M <= 64 or (row is not None and str(row.get("kernelName") or "").startswith("bs_fewrows"))
+    fits = M <= 256 and -(-N // 128) * -(-M // 64) <= get_cu_num()
+    few = M <= 64 or fits or (row is not None and str(row.get("kernelName") or "").startswith("bs_fewrows"))
     assert ab.launch_count() == before + (1 if few else 3)
     check(ref, out, what=f"blockscale with e8m0 scales {M}x{N}x{K} bpre={bpre}")
     # one e8m0 and one fp32 scale tensor: the e8m0 one is widened, the fp32 kernel runs
