@@ -72,6 +72,36 @@ def test_heuristic_and_kernel_menu(ab):
     assert "kernelId" in ab.kernel_list()
 
 
+def test_heuristic_follows_the_tuned_choices_it_was_fitted_to(ab):
+    """choose_config on shapes of the reference's model list (MXFP4 = kind 2; 148 SMs assumed when no GPU is present):
+    the tile family and K split the tuner picked for them on B200."""
+    import re
+
+    def pick(kind, M, N, K):
+        name, l2 = ab.heuristic_name(kind, M, N, K)
+        return re.sub(r"_s\d+$", "", name), l2
+
+    # tall problems: CTA pairs; 192 columns (two accumulators) where the scales are re-laid and K is short, 256 at long K
+    assert pick(2, 16384, 7168, 2048) == ("tc5_256x192_n", 0)
+    assert pick(2, 16384, 7168, 16384) == ("tc5_256x256_n", 0)
+    assert pick(2, 4096, 24576, 1536) == ("tc5_256x192_n", 0)   # tall by M x N
+    assert pick(2, 4096, 7168, 2048) == ("tc5_256x256_n", 0)    # not tall: the scale warps set the pace, waves decide
+    assert pick(4, 16384, 7168, 2048) == ("tc5_256x192_n", 0)   # NVFP4: its wire order is the cheap one
+    # pairs from two dozen 256 x 256 tiles on, never split; below that single CTAs on the largest tile that fills half the machine
+    assert pick(2, 512, 7168, 2048) == ("tc5_256x256_n", 0)
+    assert pick(1, 1024, 4096, 4096) == ("tc5_256x256_n", 0)
+    assert pick(2, 512, 2048, 6144) == ("tc5_128x64_n", 0)
+    assert pick(2, 1024, 512, 4096) == ("tc5_128x64_n", 0)      # (a workspace split needs slices of 24 K tiles)
+    # 65..256 rows: decode tiles of 64 rows while they fit the machine, of 128 rows for a large weight or when only those fit
+    assert pick(2, 256, 7168, 2048) == ("tc5_128x64_t", 0)
+    assert pick(2, 128, 4096, 4096) == ("tc5_128x64_t", 1)
+    assert pick(2, 128, 7168, 16384) == ("tc5_128x128_t", 1)
+    assert pick(2, 256, 16384, 4096) == ("tc5_128x128_t", 0)
+    # clusters of four may take 7/8 of the two-CTAs-per-SM capacity: 72 weight tiles split two ways, not four
+    assert pick(2, 64, 9216, 16384) == ("tc5_128x64_t", 1)
+    assert pick(2, 16, 7168, 16384) == ("tc5_128x16_t", 2)
+
+
 def test_host_numerics_against_golden(ab, golden):
     x = torch.from_numpy(golden["quant_in_bf16"].view(np.int16).copy()).view(torch.bfloat16)
     q4, s4 = ab.per_1x32_f4_quant(x)
