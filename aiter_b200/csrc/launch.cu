@@ -389,7 +389,7 @@ void choose_config(int kind, long long M, long long N, long long K, int num_sms,
         }
     }
     const bool four_bit = (kind == PK_MXFP4 || kind == PK_NVFP4);
-    if(bn_was_open && cfg.cg <= 0 && !cfg.swap && rows_p >= 512)
+    if(bn_was_open && cfg.cg <= 0 && !cfg.swap && rows_p >= 512 && rows_q >= 192)
     {
         // CTA pairs (each SM stages half of the Q tile per flop) pay from about two dozen 256 x 256 tiles on: the tuner's
         // tables name a pair tile for every such shape of the reference's model list, down to 512 x 2560
