@@ -1460,10 +1460,11 @@ static bool use_few_rows(const BlockScaleProblem& prob)
 {
     return prob.M <= 64 && prob.K <= 32768 && !few_rows_disabled();
 }
-// by name the same kernel also takes up to four tiles of 64 rows, each a CTA of its own on the same weight tile
-static bool few_rows_can_serve(const BlockScaleProblem& prob)
+// the same kernel also takes several tiles of 64 rows, each a CTA of its own on the same weight tile: up to four by the
+// launcher's own rule (while all of them fit the machine at once), up to sixteen by name
+static bool few_rows_can_serve(const BlockScaleProblem& prob, long long max_rows = 256)
 {
-    return prob.M <= 256 && prob.K <= 32768 && !few_rows_disabled();
+    return prob.M <= max_rows && prob.K <= 32768 && !few_rows_disabled();
 }
 
 bool parse_blockscale_name(const char* name, int& variant, int& log2_splitk)
@@ -1546,7 +1547,7 @@ void launch_blockscale(const BlockScaleProblem& prob)
     const long long pairs256 = ((prob.M + 2 * kTileP - 1) / (2 * kTileP)) * ((prob.N + 2 * kBsTileN - 1) / (2 * kBsTileN));
     const long long single_cost = (tiles128 + st.sm_count - 1) / st.sm_count * (prm.k_blocks * 810LL + 6300);
     const long long pair_cost   = (pairs256 + st.sm_count / 2 - 1) / (st.sm_count / 2) * (prm.k_blocks * 1050LL + 4000);
-    B200_CHECK(prob.variant != 1 || few_rows_can_serve(prob), "bs_fewrows serves at most 256 activation rows");
+    B200_CHECK(prob.variant != 1 || few_rows_can_serve(prob, 1024), "bs_fewrows serves at most 1024 activation rows");
     B200_CHECK((prob.variant != 3 && prob.variant != 4) || prob.M > kTileP, "bs_256x256 / bs_256x128 need more than 128 activation rows");
     // 65..256 rows: tiles of 64 rows on the few-rows kernel while all of them fit the machine at once (measured against the
     // 128 x 128 kernel: 256 x 4096 x 4096 15.1 -> 13.3 us, 96 x 4096 x 4096 14.1 -> 10.4 us, 200 x 1536 x 7168 16.3 -> 13.5 us;

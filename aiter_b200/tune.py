@@ -70,7 +70,7 @@ def blockscale_candidates(M: int, N: int, K: int):
     """Kernel names of the fp32-scale kernels worth timing: which kernel and its K split ("" = the launcher's own model)."""
     kb = K // 128
     names = [""]
-    if M <= 256:  # (beyond 64 rows: several tiles of 64 rows on the same weight tile)
+    if M <= 256 or (M <= 1024 and N <= 1024):  # (beyond 64 rows: several tiles of 64 rows on the same weight tile)
         names += [f"bs_fewrows_k{s}" for s in range(0, 4) if (kb >> s) >= 1]
     names += [f"bs_128x128_k{s}" for s in range(0, 4) if (kb >> s) >= 2]
     if M > 128:

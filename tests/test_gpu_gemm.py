@@ -341,9 +341,9 @@ def test_a8w8_blockscale_fp32_scales(ab, M, N, K, bpre):
     assert_healthy(ab)
 
 
-@pytest.mark.parametrize("M", [65, 128, 200, 256])
-def test_a8w8_blockscale_few_rows_kernel_on_up_to_four_tiles_of_64_rows(ab, M):
-    # by name the few-rows kernel takes up to 256 rows: every tile of 64 is a CTA of its own on the same weight tile;
+@pytest.mark.parametrize("M", [65, 128, 200, 256, 520, 1024])
+def test_a8w8_blockscale_few_rows_kernel_on_several_tiles_of_64_rows(ab, M):
+    # by name the few-rows kernel takes up to 1024 rows: every tile of 64 is a CTA of its own on the same weight tile;
     # unsplit, cluster K splits and fp16 output, fp32 and e8m0 scales, ragged N
     N, K = 400, 2048
     g = torch.Generator().manual_seed(M)
