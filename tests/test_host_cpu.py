@@ -321,6 +321,9 @@ def test_tuner_reads_shape_files_and_blockscale_names(tmp_path):
     assert "" in names and "bs_fewrows_k2" in names and "bs_128x128_k0" in names and "bs_256x256" not in names
     assert "bs_256x256" in tune.candidates(1024, 4096, 4096, "a8w8_blockscale_bpreshuffle")
     assert "bs_fewrows_k1" in tune.candidates(128, 4096, 4096, "a8w8_blockscale") and "bs_fewrows_k1" not in tune.candidates(300, 4096, 4096, "a8w8_blockscale")
+    # beyond 256 rows the few-rows kernel is a candidate for narrow outputs only (up to 1024 rows by name)
+    assert "bs_fewrows_k2" in tune.candidates(512, 512, 7168, "a8w8_blockscale") and "bs_256x128" in tune.candidates(512, 512, 7168, "a8w8_blockscale")
+    assert "bs_fewrows_k0" not in tune.candidates(2048, 512, 7168, "a8w8_blockscale")
 
 
 def test_blockscale_table_rows_do_not_leak_onto_e8m0_scaled_calls(ab):
@@ -335,3 +338,11 @@ def test_blockscale_table_rows_do_not_leak_onto_e8m0_scaled_calls(ab):
     assert split == 0 and not name.startswith("bs_")
     assert g._blockscale_choice({"splitK": 0, "kernelName": "bs_256x256"}, True, 16, 4096, 4096) == (0, "")
     assert g._blockscale_choice(None, False, 5, 6, 7) == (0, "")
+    # 65..256 rows whose tiles of 64 rows fit the machine at once: no name, the launcher keeps the call on the few-rows
+    # kernel (one launch); beyond that the MXFP8 table's row for the shape is passed on
+    assert g._blockscale_choice({"splitK": 0, "kernelName": ""}, True, 128, 4096, 4096) == (0, "")
+    assert g._blockscale_choice(fp32_row, True, 256, 4096, 4096) == (0, "")
+    split, name = g._blockscale_choice(None, True, 1024, 4096, 4096)
+    assert split == 0 and name.startswith("tc5_")
+    split, name = g._blockscale_choice(None, True, 256, 16384, 4096)  # 128 x 4 tiles: more than the machine has SMs
+    assert split == 0 and not name.startswith("bs_")
