@@ -713,12 +713,13 @@ gemm_a8w8_blockscale_fewrows_kernel(const __grid_constant__ CUtensorMap map_a, c
 // ---------------------------------------------------------------------------------------------------------
 // Same arithmetic on CTA pairs: 256 x 256 output tiles (cta_group::2), a persistent pair walking a static list of
 // them, so that barrier set-up, TMEM allocation and the pipeline fill are paid once and a tile's rows go out while the
-// next tile's operands arrive and its first K blocks are multiplied.  Every CTA stages its own 128
-// rows of A and its own 128 of the tile's 256 rows of B per K block (24 B of operand per 512 cycles of MMA and
-// SM less than the 128 x 128 tile moves), the leader issues 256 x 256 x 32 MMAs into one of two 256-column
-// TMEM partials, and eight promotion warps per CTA (two per TMEM lane quarter, 128 columns each) fold the
-// finished partial into fp32 registers with x_scale[m][kb] * w_scale[n/128][kb].
-// Warps (352 threads): 0 TMA producer, 1 MMA issuer (leader) + TMEM owner, 2..9 promotion + store, 10 idle.
+// next tile's operands arrive and its first K blocks are multiplied.  Every CTA stages its own 128 rows of A and its
+// own 128 of the tile's 256 rows of B per K block (half the operand bytes per flop of the 128 x 128 tile), the leader
+// issues 256 x 256 x 32 MMAs into one of two 256-column TMEM partials, and eight promotion warps per CTA (two per
+// TMEM lane quarter, 128 columns each) fold the finished partial into fp32 registers with
+// x_scale[m][kb] * w_scale[n/128][kb]: 16 columns per tcgen05.ld through two register buffers, the scales loaded two
+// K blocks ahead.  16-bit outputs leave as TMA tile stores from a staging buffer per warp, others as plain stores.
+// Warps (352 threads): 0 TMA producer, 1 MMA issuer (leader) + TMEM owner, 2..9 promotion + store, 10 descriptor prefetch.
 constexpr int kBlockScalePairThreads = 352;
 constexpr int kBsPairN               = 256;
 
