@@ -396,6 +396,10 @@ def test_a8w8_blockscale_pair_kernels_by_name(ab, M, N, K):
         ab.gemm_a8w8_blockscale_cktile(xc, wq, xs_t.view(M, K // 128), wsc, out16, preshuffleB=True, kernelName=name)
         got = out16.float().cpu().numpy()
         assert np.all(np.abs(got - want) <= 1e-2 + 1e-2 * np.abs(want)), f"{name} preshuffled, fp16 output"
+        out32 = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+        ab.gemm_a8w8_blockscale_cktile(xc, wc, xsc, wsc, out32, kernelName=name)
+        got = out32.cpu().numpy()
+        assert np.all(np.abs(got - want) <= 1e-2 + 1e-2 * np.abs(want)), f"{name} fp32 output"
         # an output pitch that rules out tile stores (rows start on odd 2-byte offsets): plain stores
         wide = torch.full((M, N + 3), float("nan"), dtype=torch.bfloat16, device="cuda")
         ab.gemm_a8w8_blockscale_cktile(xc, wc, xsc, wsc, wide[:, :N], kernelName=name)
